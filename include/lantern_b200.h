@@ -1,0 +1,237 @@
+/*
+ * lantern_b200.h -- C ABI of the B200-native tensor backend for Lantern.
+ *
+ * Lantern's Scala front end stages model code into one C++/CUDA host program; every
+ * tensor operation in that program is whatever text the active `Backend` object spliced in
+ * (trait Backend, src/main/scala/lantern/TensorDifferentiation.scala:137-379).  This header is
+ * the set of C symbols a `BackendB200` emits calls to: one entry point per Backend method on
+ * the CNN/RNN training path, taking the information the Scala method has in hand when it
+ * prints the call (raw arena pointers + integer shapes + scalars by value).
+ *
+ * Conventions (identical to the reference's generated code):
+ *   - all tensors are dense row-major float32; 4-D tensors are NCHW, filters OIHW;
+ *     indices and class targets are int32;
+ *   - "ow" = the destination is overwritten, "acc" = the result is ADDED into the destination
+ *     (the reference CPU backend accumulates every gradient, TensorDslCPU.scala passim);
+ *   - buffers are owned by the caller and come from the arena below; the library keeps no
+ *     pointer past a call (exception: the communicator);
+ *   - all work is issued on one stream in program order; only ltb_d2h / ltb_sync block.
+ *
+ * Every function returns 0 on success or a negative LTB_E_* code (pointer-returning functions
+ * return NULL).  In fatal mode (the default, matching CUDA_CALL/CUBLAS_CALL/CUDNN_CALL in
+ * src/main/scala/lantern/DslAPI.scala:435-451) an error prints to stderr and exit()s; with
+ * ltb_set_fatal(0) the code is returned and ltb_last_error() holds the message.
+ *
+ * The same declarations, compiled with -DLTB_FN(n)=ora_##n, are the ABI of the CPU oracle used
+ * by the tests (host pointers instead of device pointers).
+ */
+#ifndef LANTERN_B200_H
+#define LANTERN_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifndef LTB_FN
+#define LTB_FN(name) ltb_##name
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  LTB_OK = 0,
+  LTB_E_CUDA = -1,      /* a CUDA runtime/driver call failed */
+  LTB_E_ARG = -2,       /* bad shape / null pointer / unsupported combination */
+  LTB_E_OOM = -3,       /* arena exhausted (reference: abort(), DslAPI.scala:462-464) */
+  LTB_E_STATE = -4,     /* not initialised / initialised twice */
+  LTB_E_COMM = -5,      /* NCCL failure or timeout */
+  LTB_E_DEVICE = -6,    /* a kernel reported a bounded wait that ran out */
+  LTB_E_LIMIT = -7      /* a stated size limit of the entry point was exceeded */
+};
+
+/* Binary op codes for the broadcasting family (Backend + - * /, TD.scala:222-258). */
+enum { LTB_ADD = 0, LTB_SUB = 1, LTB_MUL = 2, LTB_DIV = 3 };
+/* Unary op codes (Backend relu/tanh/sigmoid/exp/log/sqrt/square, TD.scala:319-335). */
+enum { LTB_RELU = 0, LTB_TANH = 1, LTB_SIGMOID = 2, LTB_EXP = 3, LTB_LOG = 4, LTB_SQRT = 5, LTB_SQUARE = 6 };
+/* Math mode, the counterpart of `cudnnMathType` (TensorDslCudnn.scala:133-136). */
+enum { LTB_MATH_FP32 = 0, LTB_MATH_TF32 = 1 };
+
+/* ---------------------------------------------------------------- lifetime / context
+ * Replaces backend.setup()/cleanup(): TensorDslCublas.scala:113-124, TensorDslCudnn.scala:143-151
+ * and the arena globals of DslAPI.scala:453-473. heap_bytes==0 selects the reference's 8 GiB + 16. */
+int    LTB_FN(init)(int device, size_t heap_bytes);
+int    LTB_FN(shutdown)(void);
+int    LTB_FN(set_fatal)(int on);
+int    LTB_FN(last_error)(char* buf, int len);          /* returns the last status code */
+int    LTB_FN(set_stream)(void* cuda_stream);           /* adopt a caller stream (cudaStream_t) */
+void*  LTB_FN(get_stream)(void);
+int    LTB_FN(sync)(void);
+int    LTB_FN(set_math)(int mode);                      /* LTB_MATH_TF32 (default) or LTB_MATH_FP32 */
+int    LTB_FN(device_status)(void);                     /* 0, or LTB_E_DEVICE if a kernel's bounded wait expired */
+int64_t LTB_FN(kernel_launches)(void);                  /* kernels launched by this library so far */
+
+/* ---------------------------------------------------------------- arena
+ * myGpuMalloc / myGpuFree (DslAPI.scala:453-473), getCudaMallocAddr / resetCudaMallocAddr
+ * (TensorDslCublas.scala:18-25).  Memory is ZERO when handed out by ltb_malloc, because
+ * Tensor.zeros is a bare mallocArray (TD.scala:1075-1076).  ltb_malloc_uninit is for op outputs
+ * that are fully overwritten by the next call; it skips the zero fill. Granule 256 B. */
+void*  LTB_FN(malloc)(size_t bytes);
+void*  LTB_FN(malloc_uninit)(size_t bytes);
+int    LTB_FN(free)(void* p, size_t bytes);             /* LIFO pop: p must be the newest block */
+void*  LTB_FN(mark)(void);
+int    LTB_FN(reset)(void* mark);
+size_t LTB_FN(arena_used)(void);
+
+/* Transfers: gpu_array_copy_* of src/main/scala/common/GPUOps.scala:51-95. d2h blocks. */
+int LTB_FN(h2d)(void* dst, const void* src, size_t bytes);
+int LTB_FN(d2h)(void* dst, const void* src, size_t bytes);
+int LTB_FN(d2d)(void* dst, const void* src, size_t bytes);   /* copyFloatArray, TD.scala:150 */
+/* Pinned host staging and a non-blocking read-back, so the per-step loss copy (MnistCNN.scala:185) need not
+ * stall the stream; the value is valid after the next ltb_sync(). */
+void* LTB_FN(host_alloc)(size_t bytes);
+int   LTB_FN(host_free)(void* p);
+int   LTB_FN(d2h_async)(void* dst_pinned, const void* src, size_t bytes);
+
+/* Whole-step replay. Shapes are static and the bump arena hands out the same addresses every iteration after
+ * ltb_reset, so one training step can be recorded once and replayed: graph_begin starts recording the calls
+ * that follow on the library's stream, graph_end returns a handle, graph_launch replays it.  Calls that
+ * touch the host (randinit, dropout, d2h) are not allowed while recording. */
+int   LTB_FN(graph_begin)(void);
+void* LTB_FN(graph_end)(void);
+int   LTB_FN(graph_launch)(void* graph);
+int   LTB_FN(graph_destroy)(void* graph);
+
+/* ---------------------------------------------------------------- fill / init (CPU.scala:30-67, 101-119) */
+int LTB_FN(fill)(float* x, float value, int64_t n);                                  /* fill, fillInPlace */
+int LTB_FN(fill_with_bias)(float* out, const float* bias, int outer, int c, int inner); /* fillWithBias */
+/* randinit: (rand()/RAND_MAX - 0.5)*scale drawn on the HOST with glibc rand() in element order, then
+ * uploaded (TensorDslCublas.scala:154-155); seed >= 0 calls srand(seed) first. */
+int LTB_FN(randinit)(float* x, int64_t n, float scale, int seed);
+int LTB_FN(clip)(float* x, float bound, int64_t n);                                  /* clipAt */
+
+/* ---------------------------------------------------------------- dot family (TD.scala:186-219, CPU.scala:135-225) */
+int LTB_FN(vv_dot)(const float* x, const float* y, float* out, int n);               /* out[0] = x.y           ow */
+int LTB_FN(vv_dot_grad)(float* dx, float* dy, const float* x, const float* y, const float* dout, int n); /* acc; dx/dy nullable */
+int LTB_FN(mv_dot)(const float* a, const float* x, float* out, int m, int k);        /* out[m] = A[m,k] x[k]   ow */
+int LTB_FN(mm_dot)(const float* a, const float* b, float* out, int m, int k, int n); /* out[m,n] = A[m,k]B[k,n] ow */
+int LTB_FN(add_cartesian)(float* da, const float* y, const float* dout, int m, int k);   /* dA[i,j] += y[j]*dout[i] */
+int LTB_FN(add_composition)(float* dx, const float* a, const float* dout, int m, int k); /* dx[k] += A^T dout      */
+int LTB_FN(add_dot_trans1)(float* db, const float* a, const float* dc, int m, int k, int n); /* dB[k,n] += A^T dC   */
+int LTB_FN(add_dot_trans2)(float* da, const float* dc, const float* b, int m, int k, int n); /* dA[m,k] += dC B^T   */
+
+/* gemm / gemm_grad (TD.scala:279-280, CPU.scala:379-472): C[M,N] = alpha * op(A) op(B), op(A) is M x K.
+ * A is stored [M,K] (transA=0) or [K,M] (transA=1); B is [K,N] or [N,K]. Gradients accumulate;
+ * dA or dB may be NULL (isInput). */
+int LTB_FN(gemm)(const float* a, int trans_a, const float* b, int trans_b, float alpha, float* c, int M, int N, int K);
+int LTB_FN(gemm_grad)(const float* a, float* da, int trans_a, const float* b, float* db, int trans_b,
+                      float alpha, const float* dc, int M, int N, int K);
+
+/* ---------------------------------------------------------------- convolution (TD.scala:292-296, CPU.scala:484-692)
+ * x[N,C,H,W], w[K,C,R,S], bias[K] or NULL, y[N,K,Ho,Wo] ow, Ho=(H+2ph-R)/sh+1. Cross-correlation,
+ * dilation 1, groups 1.  Backward: dx acc (NULL when the input is a leaf), dw acc, dbias acc (nullable). */
+int LTB_FN(conv2d_fwd)(const float* x, const float* w, const float* bias, float* y,
+                       int N, int C, int H, int W, int K, int R, int S, int sh, int sw, int ph, int pw);
+int LTB_FN(conv2d_bwd)(const float* x, float* dx, const float* w, float* dw, float* dbias, const float* dy,
+                       int N, int C, int H, int W, int K, int R, int S, int sh, int sw, int ph, int pw);
+
+/* ---------------------------------------------------------------- pooling (TD.scala:298-302, CPU.scala:848-1038)
+ * Max pool: output starts at -FLT_MAX, window scanned row-major with strict '>', so the first maximum
+ * wins; idx[i] is the flat int32 index of the winner in the WHOLE batch tensor (CPU.scala:906-909).
+ * pad must be 0 for avg pool (CPU.scala:1003-1005). Backward passes accumulate. */
+int LTB_FN(maxpool_fwd)(const float* x, float* y, int32_t* idx, int N, int C, int H, int W,
+                        int kh, int kw, int sh, int sw, int pad);
+int LTB_FN(maxpool_bwd)(float* dx, const float* dy, const int32_t* idx, int64_t n_out);
+int LTB_FN(avgpool_fwd)(const float* x, float* y, int N, int C, int H, int W, int kh, int kw, int sh, int sw);
+int LTB_FN(avgpool_bwd)(float* dx, const float* dy, int N, int C, int H, int W, int kh, int kw, int sh, int sw);
+
+/* ---------------------------------------------------------------- batch norm (TD.scala:304-306)
+ * Spatial BN over N*HW per channel.  Forward follows CPU.scala:1047-1056 (mean, biased variance,
+ * eps inside the sqrt); saved statistics and running-stat update follow what the reference's GPU
+ * backend gets from cuDNN (TensorDslCudnn.scala:1025-1109): save_mean, save_istd = 1/sqrt(var+eps),
+ * run = (1-momentum)*run + momentum*batch (unbiased variance for run_var); run_* may be NULL.
+ * Backward accumulates dx, dgamma, dbeta (alpha=beta=1 at TensorDslCudnn.scala:1106-1108). */
+int LTB_FN(bn_train_fwd)(const float* x, float* y, const float* gamma, const float* beta,
+                         float* run_mean, float* run_var, float* save_mean, float* save_istd,
+                         int N, int C, int HW, float eps, float momentum);
+int LTB_FN(bn_bwd)(const float* x, float* dx, const float* dy, const float* gamma, float* dgamma, float* dbeta,
+                   const float* save_mean, const float* save_istd, int N, int C, int HW);
+int LTB_FN(bn_inference)(const float* x, float* y, const float* gamma, const float* beta,
+                         const float* run_mean, const float* run_var, int N, int C, int HW, float eps);
+
+/* ---------------------------------------------------------------- broadcasting elementwise (TD.scala:222-275, CPU.scala:227-374)
+ * Shapes are what Tensor.dimBroadcast (TD.scala:998-1016) returns: both right-aligned and padded
+ * with leading 1s to the same rank (<= 4); every dim pair is equal or one side is 1. */
+int LTB_FN(ew_binary)(int op, const float* a, const int* ashape, const float* b, const int* bshape, float* out, int rank); /* ow */
+int LTB_FN(ew_binary_grad)(int op, const float* a, float* da, const int* ashape, const float* b, float* db, const int* bshape,
+                           const float* dout, int rank);                              /* acc; da/db nullable */
+int LTB_FN(ew_scalar)(int op, const float* a, float s, float* out, int64_t n);         /* tensor (op) scalar, ow */
+int LTB_FN(ew_inplace)(int op, float* x, const int* xshape, const float* y, const int* yshape, int rank); /* x = x (op) y, y broadcast or reduced into x */
+int LTB_FN(ew_inplace_scalar)(int op, float* x, float s, int64_t n);
+/* plusBias / plusEqual and their grads are ew_inplace(LTB_ADD, ...) with the roles the Backend gives them
+ * (CPU.scala:281-296); provided as named entry points for the emitted code. */
+int LTB_FN(plus_bias)(float* main, const int* mshape, const float* bias, const int* bshape, int rank);
+int LTB_FN(plus_bias_grad)(float* dbias, const int* bshape, const float* dmain, const int* mshape, int rank);
+/* geam (TD.scala:273): out = alpha*op(x) + beta*op(y); out is rows x cols; may alias x or y when no transpose. */
+int LTB_FN(geam)(const float* x, int trans_x, float alpha, const float* y, int trans_y, float beta, float* out, int rows, int cols);
+int LTB_FN(trans)(const float* x, float* out, int rows, int cols);                    /* out[cols,rows] ow */
+int LTB_FN(trans_grad)(float* dx, const float* dy, int rows, int cols);               /* dx[rows,cols] += dy^T */
+
+/* ---------------------------------------------------------------- activations (TD.scala:319-335, CPU.scala:710-781)
+ * unary: out may alias x (relu in place). unary_grad: dx acc, from x (input), y (result), dy.
+ * relu in place: the caller passes dx == dy and in_place=1; the gradient is masked where the
+ * (already clamped) value is not positive -- see the note at ltb_unary_grad in the sources. */
+int LTB_FN(unary)(int op, const float* x, float* out, int64_t n);
+int LTB_FN(unary_grad)(int op, const float* x, float* dx, const float* y, const float* dy, int64_t n, int in_place);
+
+/* ---------------------------------------------------------------- softmax / loss (TD.scala:338-346, CPU.scala:783-846, 1090-1110) */
+int LTB_FN(softmax)(const float* x, float* y, int rows, int cols);
+int LTB_FN(log_softmax)(const float* x, float* y, int rows, int cols);
+int LTB_FN(softmax_grad)(float* dx, const float* y, const float* dy, int rows, int cols);      /* acc */
+int LTB_FN(log_softmax_grad)(float* dx, const float* y, const float* dy, int rows, int cols);  /* acc */
+int LTB_FN(nll)(const float* x, const int32_t* target, float* out, int rows, int cols);        /* out[b] = -x[b,t[b]] */
+int LTB_FN(nll_grad)(float* dx, const float* dout, const int32_t* target, int rows, int cols); /* dx[b,t[b]] -= dout[b] */
+
+/* ---------------------------------------------------------------- reductions (TD.scala:352-366, CPU.scala:1115-1164) */
+int LTB_FN(sum)(const float* x, float* out, int64_t n);            /* out[0] ow */
+int LTB_FN(sum_grad)(float* dx, const float* dout, int64_t n);     /* dx[i] += dout[0] */
+int LTB_FN(mean)(const float* x, float* out, int64_t n);
+int LTB_FN(mean_grad)(float* dx, const float* dout, int64_t n);    /* dx[i] += dout[0]/n */
+int LTB_FN(sum_dim)(const float* x, float* out, int outer, int d, int inner);         /* out[outer,inner] ow */
+int LTB_FN(sum_dim_grad)(float* dx, const float* dout, int outer, int d, int inner);  /* acc */
+
+/* ---------------------------------------------------------------- concat (TD.scala:369-370, CPU.scala:1166-1212)
+ * Inputs i has shape [outer, dims[i], inner]; out is [outer, sum(dims), inner]. */
+int LTB_FN(concat)(float* out, const float* const* inputs, const int* dims, int n_inputs, int outer, int inner);
+int LTB_FN(concat_grad)(float* const* dinputs, const float* dout, const int* dims, int n_inputs, int outer, int inner); /* acc; entries nullable */
+
+/* ---------------------------------------------------------------- dropout (TD.scala:312-313, CPU.scala:1066-1088)
+ * ltb_dropout draws the keep mask on the host from glibc rand() in element order (rand()/RAND_MAX > p
+ * keeps and scales by 1/(1-p)), exactly the stream the CPU backend consumes, and uploads it.
+ * ltb_dropout_masked applies a mask the caller already has on the device. */
+int LTB_FN(dropout)(const float* x, float* y, float* mask, float p, int64_t n);
+int LTB_FN(dropout_masked)(const float* x, float* y, const float* mask, int64_t n);
+int LTB_FN(dropout_grad)(float* dx, const float* mask, const float* dy, int64_t n);   /* acc */
+
+/* ---------------------------------------------------------------- optimizers (NNModule.scala:265-303, CPU.scala:1217-1246)
+ * sgd_step = geam(x, 1, d, -lr) followed by clear_grad, fused; the multi form walks n tensors in one launch. */
+int LTB_FN(sgd_step)(float* x, float* d, float lr, int64_t n);
+int LTB_FN(sgd_step_multi)(float* const* xs, float* const* ds, const int64_t* sizes, int n_tensors, float lr);
+int LTB_FN(adagrad_update)(float* x, float* d, float* h, float lr, float clip, int descent, int64_t n);
+int LTB_FN(momentum_update)(float* x, float* d, float* m, float lr, float mu, float clip, int nesterov, int descent, int64_t n);
+
+/* ---------------------------------------------------------------- data parallelism (no counterpart in the reference,
+ * which is single-GPU: src/out/PLDI19evaluation/run_exp.sh:7).  One process per GPU; rank 0 creates the id
+ * and the launcher distributes it.  allreduce_sgd_step: d <- sum over ranks of d, then
+ * x -= lr * d / world, d = 0, bucket by bucket so the update of one bucket overlaps the reduction of the next. */
+int LTB_FN(comm_unique_id)(void* out128);
+int LTB_FN(comm_init)(int rank, int world, const void* id128);
+int LTB_FN(comm_destroy)(void);
+int LTB_FN(comm_world)(void);
+int LTB_FN(allreduce_sum)(float* x, int64_t n);
+int LTB_FN(allreduce_sgd_step)(float* x, float* d, float lr, int64_t n);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LANTERN_B200_H */

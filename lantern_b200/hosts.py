@@ -1,0 +1,107 @@
+"""Binding of the host programs (lantern_b200/hosts/*.cpp): whole training steps of the reference's apps
+issued through the C ABI from C++, the way Lantern's generated code would issue them."""
+import ctypes
+import os
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+
+_SIGS = {
+    "model_create": (ctypes.c_void_p, [ctypes.c_char_p, ctypes.c_int, ctypes.c_int]),
+    "model_destroy": (None, [ctypes.c_void_p]),
+    "model_num_params": (ctypes.c_int, [ctypes.c_void_p]),
+    "model_param_count": (ctypes.c_int64, [ctypes.c_void_p, ctypes.c_int]),
+    "model_param_ptr": (ctypes.c_void_p, [ctypes.c_void_p, ctypes.c_int]),
+    "model_grad_ptr": (ctypes.c_void_p, [ctypes.c_void_p, ctypes.c_int]),
+    "model_slab_count": (ctypes.c_int64, [ctypes.c_void_p]),
+    "model_slab_params": (ctypes.c_void_p, [ctypes.c_void_p]),
+    "model_slab_grads": (ctypes.c_void_p, [ctypes.c_void_p]),
+    "model_input_count": (ctypes.c_int64, [ctypes.c_void_p]),
+    "model_use_graph": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int]),
+    "model_step": (ctypes.c_float, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_float, ctypes.c_int]),
+    "model_step_async": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_float]),
+    "model_last_loss": (ctypes.c_float, [ctypes.c_void_p]),
+}
+
+
+class HostPrograms:
+    """`lib` is the BoundLibrary the programs compute with; `path`/`prefix` select the matching hosts build."""
+
+    def __init__(self, lib, path=None, prefix="ltbh_"):
+        self.lib = lib
+        path = path or os.path.join(_HERE, "liblantern_b200_hosts.so")
+        if not os.path.exists(path):
+            raise ImportError("%s is not built" % path)
+        self.cdll = ctypes.CDLL(path, mode=ctypes.RTLD_LOCAL)
+        self.fn = {}
+        for name, (ret, args) in _SIGS.items():
+            f = getattr(self.cdll, prefix + name)
+            f.restype, f.argtypes = ret, args
+            self.fn[name] = f
+
+    def model(self, name, batch, seed=42):
+        return Model(self, name, batch, seed)
+
+
+class Model:
+    def __init__(self, hp, name, batch, seed):
+        self.hp, self.lib, self.name, self.batch = hp, hp.lib, name, batch
+        self.h = hp.fn["model_create"](name.encode(), batch, seed)
+        if not self.h:
+            raise ValueError("unknown model %r" % name)
+        self.num_params = hp.fn["model_num_params"](self.h)
+        self.input_count = hp.fn["model_input_count"](self.h)
+        self.slab_count = hp.fn["model_slab_count"](self.h)
+
+    def _arrs(self, x, y):
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        y = np.ascontiguousarray(y, dtype=np.int32)
+        assert x.size == self.input_count and y.size == self.batch
+        return x, y
+
+    def step(self, x, y, lr, update=True):
+        x, y = self._arrs(x, y)
+        return float(self.hp.fn["model_step"](self.h, x.ctypes.data, y.ctypes.data, lr, int(update)))
+
+    def step_async(self, x, y, lr):
+        x, y = self._arrs(x, y)
+        rc = self.hp.fn["model_step_async"](self.h, x.ctypes.data, y.ctypes.data, lr)
+        if rc:
+            raise RuntimeError("model_step_async failed: %d %s" % (rc, self.lib.error_message()))
+
+    def last_loss(self):
+        return float(self.hp.fn["model_last_loss"](self.h))
+
+    def use_graph(self, on=True):
+        self.hp.fn["model_use_graph"](self.h, int(on))
+
+    def _read(self, ptr, n):
+        out = np.empty(n, dtype=np.float32)
+        self.lib.d2h(out.ctypes.data, ptr, out.nbytes)
+        return out
+
+    def param(self, i):
+        return self._read(self.hp.fn["model_param_ptr"](self.h, i), self.hp.fn["model_param_count"](self.h, i))
+
+    def grad(self, i):
+        return self._read(self.hp.fn["model_grad_ptr"](self.h, i), self.hp.fn["model_param_count"](self.h, i))
+
+    def slab_params(self):
+        return self._read(self.hp.fn["model_slab_params"](self.h), self.slab_count)
+
+    def slab_grads(self):
+        return self._read(self.hp.fn["model_slab_grads"](self.h), self.slab_count)
+
+    def slab_ptrs(self):
+        return self.hp.fn["model_slab_params"](self.h), self.hp.fn["model_slab_grads"](self.h)
+
+    def set_slab_params(self, arr):
+        arr = np.ascontiguousarray(arr, dtype=np.float32)
+        assert arr.size == self.slab_count
+        self.lib.h2d(self.hp.fn["model_slab_params"](self.h), arr.ctypes.data, arr.nbytes)
+
+    def close(self):
+        if self.h:
+            self.hp.fn["model_destroy"](self.h)
+            self.h = None

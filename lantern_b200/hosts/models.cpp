@@ -1,0 +1,274 @@
+// Hand-mirrored host programs for the reference's training apps.
+//
+// The Scala generator cannot run without a JVM, so each program below is written the way the staged output
+// of the corresponding app is structured: parameters allocated first (before the arena mark), then per batch
+// upload -> forward -> seed gradient -> backward (reverse order) -> loss read-back -> SGD over every parameter
+// tensor -> arena reset.  References:
+//   MNIST CNN   src/main/scala/lantern/NIPS18App/MnistCNN.scala:36-60, 168-194 and its shipped output
+//               src/out/NIPS18evaluation/evaluationCNN/Lantern/Lantern.cpp
+//   ResNet-50   src/main/scala/lantern/PLDI19APP/resnet50FromOnnx.scala:135-214 with the architecture of
+//               src/out/PLDI19evaluation/resnet50/pytorch/resnet50.py:55-160 (op mapping ONNXLib.scala:833-1071)
+//   SqueezeNet  src/main/scala/lantern/PLDI19APP/squeezenetFromOnnx.scala:111-226 with the architecture of
+//               src/out/PLDI19evaluation/squeezenet/pytorch/pytorch_squeeze_cifar10.py:21-92
+// The exported C functions carry the prefix given by HOST_FN (ltbh_ for the CUDA library).
+#include <cmath>
+#include <cstring>
+#include <memory>
+#include <string>
+
+#include "tape.hpp"
+
+#ifndef HOST_FN
+#define HOST_FN(name) ltbh_##name
+#endif
+
+using namespace lantern_host;
+
+namespace {
+
+struct ParamDecl { std::vector<int> shape; int init; float scale; int64_t count; int64_t offset; };
+enum { INIT_ZERO = 0, INIT_RAND = 1, INIT_ONE = 2 };
+
+struct Model {
+  virtual ~Model() {}
+  std::string name;
+  int batch = 0;
+  int in_c = 0, in_h = 0, in_w = 0;
+  std::vector<ParamDecl> decls;
+  float* slab_x = nullptr;   // all parameter tensors, contiguous (each padded to 64 floats)
+  float* slab_d = nullptr;   // their gradients, same layout
+  int64_t slab_count = 0;
+  void* mark = nullptr;
+  float* stage_x = nullptr;  // pinned staging for the batch
+  int32_t* stage_y = nullptr;
+  float* loss_host = nullptr;  // pinned, 1 float
+  void* graph = nullptr;
+  bool use_graph = false;
+  float graph_lr = 0.f;
+
+  int declare(std::initializer_list<int> shape, int init, float scale = 0.f) {
+    ParamDecl d; d.shape.assign(shape.begin(), shape.end()); d.init = init; d.scale = scale;
+    d.count = 1; for (int s : d.shape) d.count *= s;
+    d.offset = slab_count;
+    slab_count += (d.count + 63) / 64 * 64;
+    decls.push_back(d);
+    return (int)decls.size() - 1;
+  }
+  TR P(int i) const {
+    const ParamDecl& d = decls[i];
+    TR t; t.rank = (int)d.shape.size(); for (int k = 0; k < t.rank; ++k) t.shape[k] = d.shape[k];
+    t.x = slab_x + d.offset; t.d = slab_d + d.offset; return t;
+  }
+  // Allocation and initialisation in declaration order; rand() is consumed only by INIT_RAND tensors, in order,
+  // after srand(seed) -- the order MnistCNN's generated code draws its weights in.
+  void finalize(int seed) {
+    slab_x = alloc_zero(slab_count);
+    slab_d = alloc_zero(slab_count);
+    bool first = true;
+    for (auto& d : decls) {
+      if (d.init == INIT_RAND) { BK(randinit)(slab_x + d.offset, d.count, d.scale, first ? seed : -1); first = false; }
+      else if (d.init == INIT_ONE) BK(fill)(slab_x + d.offset, 1.0f, d.count);
+    }
+    if (first && seed >= 0) srand((unsigned)seed);
+    stage_x = (float*)BK(host_alloc)((size_t)batch * in_c * in_h * in_w * 4);
+    stage_y = (int32_t*)BK(host_alloc)((size_t)batch * 4);
+    loss_host = (float*)BK(host_alloc)(4);
+    mark = BK(mark)();
+  }
+  virtual TR forward(Tape& t, const TR& x, const int32_t* y) = 0;
+
+  // One training step's device work, in the order of the generated programs.
+  void enqueue(float lr, bool update) {
+    Tape tape;
+    int64_t nin = (int64_t)batch * in_c * in_h * in_w;
+    TR x; x.rank = 4; x.shape[0] = batch; x.shape[1] = in_c; x.shape[2] = in_h; x.shape[3] = in_w; x.is_input = true;
+    x.x = alloc_value(nin);
+    int32_t* y = (int32_t*)BK(malloc_uninit)((size_t)batch * 4);
+    BK(h2d)(x.x, stage_x, (size_t)nin * 4);
+    BK(h2d)(y, stage_y, (size_t)batch * 4);
+    TR loss = forward(tape, x, y);
+    BK(fill)(loss.d, 1.0f, 1);                       // gradR_loss: y.d.setAsOne(), TD.scala:1763-1780
+    float* loss_copy = alloc_value(1);
+    BK(d2d)(loss_copy, loss.x, 4);
+    tape.backward();
+    BK(d2h_async)(loss_host, loss_copy, 4);
+    if (update) {
+      if (BK(comm_world)() > 1) BK(allreduce_sgd_step)(slab_x, slab_d, lr, slab_count);
+      else BK(sgd_step)(slab_x, slab_d, lr, slab_count);
+    }
+    BK(reset)(mark);
+  }
+  void load(const float* xh, const int32_t* yh) {
+    memcpy(stage_x, xh, (size_t)batch * in_c * in_h * in_w * 4);
+    memcpy(stage_y, yh, (size_t)batch * 4);
+  }
+  int step_async(const float* xh, const int32_t* yh, float lr, bool update) {
+    load(xh, yh);
+    if (use_graph && update) {
+      if (graph && graph_lr != lr) { BK(graph_destroy)(graph); graph = nullptr; }
+      if (!graph) {
+        int rc = BK(graph_begin)(); if (rc) return rc;
+        enqueue(lr, true);
+        graph = BK(graph_end)(); graph_lr = lr;
+        if (!graph) return LTB_E_CUDA;
+      }
+      return BK(graph_launch)(graph);
+    }
+    enqueue(lr, update);
+    return 0;
+  }
+  float step(const float* xh, const int32_t* yh, float lr, bool update) {
+    step_async(xh, yh, lr, update);
+    BK(sync)();
+    return *loss_host;
+  }
+};
+
+// ------------------------------------------------------------------------------------------------ MNIST CNN
+struct Mnist : Model {
+  int c1w, c1b, c2w, c2b, l1w, l1b, l2w, l2b;
+  Mnist(int b, int seed) {
+    name = "mnist"; batch = b; in_c = 1; in_h = in_w = 28;
+    // Conv2D: uniform(+-sqrt(6/fan_in)) == (rand-0.5)*2*sqrt(6/fan_in), bias 0 (NNModule.scala:128-146);
+    // Linear1D: (rand-0.5)/sqrt(in), weight stored [in,out] (NNModule.scala:112-117).
+    c1w = declare({10, 1, 5, 5}, INIT_RAND, 2.0f * sqrtf(6.0f / 25.0f));  c1b = declare({10}, INIT_ZERO);
+    c2w = declare({20, 10, 5, 5}, INIT_RAND, 2.0f * sqrtf(6.0f / 250.0f)); c2b = declare({20}, INIT_ZERO);
+    l1w = declare({320, 50}, INIT_RAND, 1.0f / sqrtf(320.0f)); l1b = declare({50}, INIT_ZERO);
+    l2w = declare({50, 10}, INIT_RAND, 1.0f / sqrtf(50.0f));   l2b = declare({10}, INIT_ZERO);
+    finalize(seed);
+  }
+  TR forward(Tape& t, const TR& x, const int32_t* y) override {   // MnistCNN.scala:43-59
+    TR b1 = P(c1b), b2 = P(c2b);
+    TR s0 = t.conv(x, P(c1w), &b1, 1, 0);
+    TR s1 = t.max_pool(t.relu(s0, false), 2, 2);
+    TR s2 = t.conv(s1, P(c2w), &b2, 1, 0);
+    TR s25 = t.max_pool(t.relu(s2, false), 2, 2);
+    TR flat = view(s25, {batch, 320});
+    TR s3 = t.dropout(t.plus_bias(t.dot(flat, P(l1w)), P(l1b)), 0.5f);
+    TR out = t.plus_bias(t.dot(s3, P(l2w)), P(l2b));
+    return t.sum(t.nll(t.log_softmax(out), y));
+  }
+};
+
+// ------------------------------------------------------------------------------------------------ ResNet-50 (CIFAR)
+struct ResNet50 : Model {
+  struct ConvBN { int w, gamma, beta, rmean, rvar; };
+  struct Block { ConvBN a, b, c, down; bool has_down; int stride; };
+  ConvBN stem; std::vector<Block> blocks; int fcw, fcb;
+  std::vector<int> running;   // indices of running-stat tensors (their gradient stays zero)
+
+  ConvBN conv_bn(int cin, int cout, int k) {
+    ConvBN cb;
+    cb.w = declare({cout, cin, k, k}, INIT_RAND, 2.0f * sqrtf(6.0f / (float)(cin * k * k)));
+    cb.gamma = declare({cout}, INIT_ONE); cb.beta = declare({cout}, INIT_ZERO);
+    cb.rmean = declare({cout}, INIT_ZERO); cb.rvar = declare({cout}, INIT_ONE);
+    return cb;
+  }
+  ResNet50(int b, int seed) {
+    name = "resnet50"; batch = b; in_c = 3; in_h = in_w = 32;
+    stem = conv_bn(3, 64, 3);
+    int inplanes = 64; const int layers[4] = {3, 4, 6, 3}; const int planes[4] = {64, 128, 256, 512};
+    for (int s = 0; s < 4; ++s)
+      for (int i = 0; i < layers[s]; ++i) {
+        Block bl; bl.stride = (i == 0 && s > 0) ? 2 : 1;
+        bl.a = conv_bn(inplanes, planes[s], 1); bl.b = conv_bn(planes[s], planes[s], 3); bl.c = conv_bn(planes[s], planes[s] * 4, 1);
+        bl.has_down = (i == 0);
+        if (bl.has_down) bl.down = conv_bn(inplanes, planes[s] * 4, 1);
+        inplanes = planes[s] * 4;
+        blocks.push_back(bl);
+      }
+    fcw = declare({10, 2048}, INIT_RAND, 1.0f / sqrtf(2048.0f)); fcb = declare({10}, INIT_ZERO);
+    finalize(seed);
+  }
+  TR cbn(Tape& t, const TR& x, const ConvBN& p, int stride, int pad, bool relu) {
+    TR y = t.batch_norm(t.conv(x, P(p.w), nullptr, stride, pad), P(p.gamma), P(p.beta), P(p.rmean).x, P(p.rvar).x);
+    return relu ? t.relu(y, true) : y;
+  }
+  TR forward(Tape& t, const TR& x, const int32_t* y) override {
+    TR h = t.max_pool(cbn(t, x, stem, 1, 1, true), 2, 2);
+    for (const Block& bl : blocks) {     // Bottleneck.forward, resnet50.py:72-93
+      TR o = cbn(t, h, bl.a, 1, 0, true);
+      o = cbn(t, o, bl.b, bl.stride, 1, true);
+      o = cbn(t, o, bl.c, 1, 0, false);
+      TR res = bl.has_down ? cbn(t, h, bl.down, bl.stride, 0, false) : h;
+      h = t.relu(t.binary(LTB_ADD, o, res), true);
+    }
+    TR p = t.avg_pool(h, 2, 1);
+    TR flat = view(p, {batch, 2048});
+    TR logits = t.plus_bias(t.gemm(flat, false, P(fcw), true, 1.0f), P(fcb));   // ONNX Gemm, ONNXLib.scala:956-974
+    return t.mean(t.nll(t.log_softmax(logits), y));                              // resnet50FromOnnx.scala:153-156
+  }
+};
+
+// ------------------------------------------------------------------------------------------------ SqueezeNet (CIFAR)
+struct SqueezeNet : Model {
+  struct Conv { int w, b; };
+  struct Fire { Conv s, e1, e3; };
+  Conv first, last; std::vector<Fire> fires;
+  Conv conv(int cin, int cout, int k) {
+    Conv c; c.w = declare({cout, cin, k, k}, INIT_RAND, 2.0f * sqrtf(6.0f / (float)(cin * k * k))); c.b = declare({cout}, INIT_ZERO); return c;
+  }
+  SqueezeNet(int b, int seed) {
+    name = "squeezenet"; batch = b; in_c = 3; in_h = in_w = 32;
+    first = conv(3, 96, 3);
+    const int cfg[8][4] = {{96, 16, 64, 64}, {128, 16, 64, 64}, {128, 32, 128, 128}, {256, 32, 128, 128},
+                           {256, 48, 192, 192}, {384, 48, 192, 192}, {384, 64, 256, 256}, {512, 64, 256, 256}};
+    for (auto& c : cfg) { Fire f; f.s = conv(c[0], c[1], 1); f.e1 = conv(c[1], c[2], 1); f.e3 = conv(c[1], c[3], 3); fires.push_back(f); }
+    last = conv(512, 10, 4);
+    finalize(seed);
+  }
+  TR cr(Tape& t, const TR& x, const Conv& c, int pad) { TR b = P(c.b); return t.relu(t.conv(x, P(c.w), &b, 1, pad), true); }
+  TR fire(Tape& t, const TR& x, const Fire& f) {
+    TR s = cr(t, x, f.s, 0);
+    return t.concat1(cr(t, s, f.e1, 0), cr(t, s, f.e3, 1));
+  }
+  TR forward(Tape& t, const TR& x, const int32_t* y) override {
+    TR h = t.max_pool(cr(t, x, first, 1), 2, 2);
+    for (int i = 0; i < 3; ++i) h = fire(t, h, fires[i]);
+    h = t.max_pool(h, 2, 2);
+    for (int i = 3; i < 7; ++i) h = fire(t, h, fires[i]);
+    h = t.max_pool(h, 2, 2);
+    h = fire(t, h, fires[7]);
+    TR lb = P(last.b);
+    TR logits = view(t.conv(h, P(last.w), &lb, 1, 0), {batch, 10});
+    return t.mean(t.nll(t.log_softmax(logits), y));
+  }
+};
+
+}  // namespace
+
+extern "C" {
+
+void* HOST_FN(model_create)(const char* name, int batch, int seed) {
+  std::string n(name);
+  if (n == "mnist") return new Mnist(batch, seed);
+  if (n == "resnet50") return new ResNet50(batch, seed);
+  if (n == "squeezenet") return new SqueezeNet(batch, seed);
+  return nullptr;
+}
+void HOST_FN(model_destroy)(void* m) {
+  Model* M = (Model*)m;
+  if (M->graph) BK(graph_destroy)(M->graph);
+  BK(host_free)(M->stage_x); BK(host_free)(M->stage_y); BK(host_free)(M->loss_host);
+  delete M;
+}
+int HOST_FN(model_num_params)(void* m) { return (int)((Model*)m)->decls.size(); }
+int64_t HOST_FN(model_param_count)(void* m, int i) { return ((Model*)m)->decls[i].count; }
+float* HOST_FN(model_param_ptr)(void* m, int i) { Model* M = (Model*)m; return M->slab_x + M->decls[i].offset; }
+float* HOST_FN(model_grad_ptr)(void* m, int i) { Model* M = (Model*)m; return M->slab_d + M->decls[i].offset; }
+int64_t HOST_FN(model_slab_count)(void* m) { return ((Model*)m)->slab_count; }
+float* HOST_FN(model_slab_params)(void* m) { return ((Model*)m)->slab_x; }
+float* HOST_FN(model_slab_grads)(void* m) { return ((Model*)m)->slab_d; }
+int64_t HOST_FN(model_input_count)(void* m) { Model* M = (Model*)m; return (int64_t)M->batch * M->in_c * M->in_h * M->in_w; }
+int HOST_FN(model_use_graph)(void* m, int on) { ((Model*)m)->use_graph = on != 0; return 0; }
+// Blocking step: returns the loss of this batch. update=0 leaves the parameter gradients in place for inspection.
+float HOST_FN(model_step)(void* m, const float* x_host, const int32_t* y_host, float lr, int update) {
+  return ((Model*)m)->step(x_host, y_host, lr, update != 0);
+}
+// Non-blocking step: the loss is available from model_last_loss after the library's sync.
+int HOST_FN(model_step_async)(void* m, const float* x_host, const int32_t* y_host, float lr) {
+  return ((Model*)m)->step_async(x_host, y_host, lr, true);
+}
+float HOST_FN(model_last_loss)(void* m) { return *((Model*)m)->loss_host; }
+
+}  // extern "C"

@@ -1,0 +1,211 @@
+// Host-side runtime for hand-mirrored "as-if-generated" Lantern programs.
+//
+// Lantern's TensorR operators run the forward computation, call the continuation, and then run the
+// gradient code as the continuation returns (shift/reset, src/main/scala/lantern/TensorDifferentiation.scala:
+// 1146-1506).  The staged result is straight-line code: forward calls in program order followed by the
+// *_grad calls in exactly the reverse order.  `Tape` reproduces that order without a staging compiler: every
+// operator issues its forward backend call immediately and pushes its gradient call; backward() pops them.
+//
+// All tensor math goes through the C ABI of include/lantern_b200.h (LTB_FN picks the library the file is
+// compiled against), so this file contains no arithmetic of its own.
+#pragma once
+#include <cstdint>
+#include <cstdio>
+#include <cstdlib>
+#include <functional>
+#include <vector>
+
+#include "../../include/lantern_b200.h"
+
+#define BK(name) LTB_FN(name)
+
+namespace lantern_host {
+
+// TensorR: value + gradient (TD.scala:1146-1160). rank 1, 2 or 4.
+struct TR {
+  float* x = nullptr;
+  float* d = nullptr;
+  int shape[4] = {1, 1, 1, 1};
+  int rank = 0;
+  bool is_input = false;   // leaf without gradient (TensorR.isInput)
+  int64_t count() const { int64_t n = 1; for (int i = 0; i < rank; ++i) n *= shape[i]; return n; }
+};
+
+inline float* alloc_value(int64_t n) { return (float*)BK(malloc_uninit)((size_t)n * 4); }
+inline float* alloc_zero(int64_t n) { return (float*)BK(malloc)((size_t)n * 4); }
+
+inline TR make(std::initializer_list<int> shp, bool with_grad = true) {
+  TR t; t.rank = (int)shp.size(); int i = 0; for (int s : shp) t.shape[i++] = s;
+  t.x = alloc_value(t.count());
+  if (with_grad) t.d = alloc_zero(t.count());
+  return t;
+}
+inline TR view(const TR& t, std::initializer_list<int> shp) {   // Tensor.resize: same buffers, new shape
+  TR v = t; v.rank = (int)shp.size(); int i = 0; for (int s : shp) v.shape[i++] = s; for (; i < 4; ++i) v.shape[i] = 1;
+  return v;
+}
+
+struct Tape {
+  std::vector<std::function<void()>> grads;
+  void push(std::function<void()> f) { grads.push_back(std::move(f)); }
+  void backward() { for (auto it = grads.rbegin(); it != grads.rend(); ++it) (*it)(); grads.clear(); }
+
+  // convBBP, TD.scala:1394-1410
+  TR conv(const TR& in, const TR& w, const TR* bias, int stride, int pad) {
+    int N = in.shape[0], C = in.shape[1], H = in.shape[2], W = in.shape[3], K = w.shape[0], R = w.shape[2], S = w.shape[3];
+    TR y = make({N, K, (H + 2 * pad - R) / stride + 1, (W + 2 * pad - S) / stride + 1});
+    BK(conv2d_fwd)(in.x, w.x, bias ? bias->x : nullptr, y.x, N, C, H, W, K, R, S, stride, stride, pad, pad);
+    float* dbias = bias ? bias->d : nullptr;
+    push([=] { BK(conv2d_bwd)(in.x, in.is_input ? nullptr : in.d, w.x, w.d, dbias, y.d, N, C, H, W, K, R, S, stride, stride, pad, pad); });
+    return y;
+  }
+  // batchNorm, TD.scala:1324-1329
+  TR batch_norm(const TR& in, const TR& gamma, const TR& beta, float* run_mean, float* run_var) {
+    int N = in.shape[0], C = in.shape[1], HW = in.shape[2] * in.shape[3];
+    TR y = make({N, C, in.shape[2], in.shape[3]});
+    float* sm = alloc_value(C); float* si = alloc_value(C);
+    BK(bn_train_fwd)(in.x, y.x, gamma.x, beta.x, run_mean, run_var, sm, si, N, C, HW, 1e-5f, 0.1f);
+    push([=] { BK(bn_bwd)(in.x, in.is_input ? nullptr : in.d, y.d, gamma.x, gamma.d, beta.d, sm, si, N, C, HW); });
+    return y;
+  }
+  // relu, TD.scala:1276-1284
+  TR relu(const TR& in, bool in_place) {
+    int64_t n = in.count();
+    if (in_place) {
+      BK(unary)(LTB_RELU, in.x, in.x, n);
+      push([=] { BK(unary_grad)(LTB_RELU, in.x, in.d, in.x, in.d, n, 1); });
+      return in;
+    }
+    TR y = in; y.x = alloc_value(n); y.d = alloc_zero(n); y.is_input = false;
+    BK(unary)(LTB_RELU, in.x, y.x, n);
+    push([=] { BK(unary_grad)(LTB_RELU, in.x, in.d, y.x, y.d, n, 0); });
+    return y;
+  }
+  TR unary(int op, const TR& in) {     // tanh / sigmoid / exp / log, TD.scala:1252-1316
+    int64_t n = in.count();
+    TR y = in; y.x = alloc_value(n); y.d = alloc_zero(n); y.is_input = false;
+    BK(unary)(op, in.x, y.x, n);
+    push([=] { if (!in.is_input) BK(unary_grad)(op, in.x, in.d, y.x, y.d, n, 0); });
+    return y;
+  }
+  // maxPoolBK, TD.scala:1413-1423
+  TR max_pool(const TR& in, int k, int s) {
+    int N = in.shape[0], C = in.shape[1], H = in.shape[2], W = in.shape[3];
+    TR y = make({N, C, (H - k) / s + 1, (W - k) / s + 1});
+    int32_t* idx = (int32_t*)BK(malloc_uninit)((size_t)y.count() * 4);
+    BK(maxpool_fwd)(in.x, y.x, idx, N, C, H, W, k, k, s, s, 0);
+    int64_t n_out = y.count();
+    push([=] { if (!in.is_input) BK(maxpool_bwd)(in.d, y.d, idx, n_out); });
+    return y;
+  }
+  // averagePoolBK, TD.scala:1385-1391
+  TR avg_pool(const TR& in, int k, int s) {
+    int N = in.shape[0], C = in.shape[1], H = in.shape[2], W = in.shape[3];
+    TR y = make({N, C, (H - k) / s + 1, (W - k) / s + 1});
+    BK(avgpool_fwd)(in.x, y.x, N, C, H, W, k, k, s, s);
+    push([=] { if (!in.is_input) BK(avgpool_bwd)(in.d, y.d, N, C, H, W, k, k, s, s); });
+    return y;
+  }
+  // broadcasting binary operators, TD.scala:1162-1218 (shapes padded to a common rank by dimBroadcast)
+  TR binary(int op, const TR& a, const TR& b) {
+    int rank = a.rank > b.rank ? a.rank : b.rank;
+    struct Sh { int a[4], b[4], r[4]; } s;
+    for (int i = 0; i < rank; ++i) {
+      int ia = i - (rank - a.rank), ib = i - (rank - b.rank);
+      s.a[i] = ia >= 0 ? a.shape[ia] : 1; s.b[i] = ib >= 0 ? b.shape[ib] : 1;
+      s.r[i] = s.a[i] > s.b[i] ? s.a[i] : s.b[i];
+    }
+    TR y; y.rank = rank; for (int i = 0; i < rank; ++i) y.shape[i] = s.r[i];
+    y.x = alloc_value(y.count()); y.d = alloc_zero(y.count());
+    BK(ew_binary)(op, a.x, s.a, b.x, s.b, y.x, rank);
+    push([=] { BK(ew_binary_grad)(op, a.x, a.is_input ? nullptr : a.d, s.a, b.x, b.is_input ? nullptr : b.d, s.b, y.d, rank); });
+    return y;
+  }
+  // plusBias, TD.scala:1220-1226 region / CPU.scala:281-288: in place on `main`
+  TR plus_bias(const TR& main, const TR& bias) {
+    struct Sh { int m[4], b[4]; } s;
+    int rank = main.rank;
+    for (int i = 0; i < rank; ++i) { int ib = i - (rank - bias.rank); s.m[i] = main.shape[i]; s.b[i] = ib >= 0 ? bias.shape[ib] : 1; }
+    BK(plus_bias)(main.x, s.m, bias.x, s.b, rank);
+    push([=] { if (!bias.is_input) BK(plus_bias_grad)(bias.d, s.b, main.d, s.m, rank); });
+    return main;
+  }
+  // dot (2,2) and (2,1), TD.scala:1220-1226
+  TR dot(const TR& a, const TR& b) {
+    if (b.rank == 2) {
+      int m = a.shape[0], k = a.shape[1], n = b.shape[1];
+      TR y = make({m, n});
+      BK(mm_dot)(a.x, b.x, y.x, m, k, n);
+      push([=] {
+        if (!a.is_input) BK(add_dot_trans2)(a.d, y.d, b.x, m, k, n);
+        if (!b.is_input) BK(add_dot_trans1)(b.d, a.x, y.d, m, k, n);
+      });
+      return y;
+    }
+    int m = a.shape[0], k = a.shape[1];
+    TR y = make({m});
+    BK(mv_dot)(a.x, b.x, y.x, m, k);
+    push([=] {
+      if (!a.is_input) BK(add_cartesian)(a.d, b.x, y.d, m, k);
+      if (!b.is_input) BK(add_composition)(b.d, a.x, y.d, m, k);
+    });
+    return y;
+  }
+  // gemm, TD.scala:1228-1233
+  TR gemm(const TR& a, bool ta, const TR& b, bool tb, float alpha) {
+    int M = ta ? a.shape[1] : a.shape[0], K = ta ? a.shape[0] : a.shape[1], N = tb ? b.shape[0] : b.shape[1];
+    TR y = make({M, N});
+    BK(gemm)(a.x, ta, b.x, tb, alpha, y.x, M, N, K);
+    push([=] { BK(gemm_grad)(a.x, a.is_input ? nullptr : a.d, ta, b.x, b.is_input ? nullptr : b.d, tb, alpha, y.d, M, N, K); });
+    return y;
+  }
+  // dropout, TD.scala:1437-1445
+  TR dropout(const TR& in, float p) {
+    int64_t n = in.count();
+    TR y = in; y.x = alloc_value(n); y.d = alloc_zero(n);
+    float* mask = alloc_value(n);
+    BK(dropout)(in.x, y.x, mask, p, n);
+    push([=] { if (!in.is_input) BK(dropout_grad)(in.d, mask, y.d, n); });
+    return y;
+  }
+  // concat along dim 1 of 4-D tensors, TD.scala:1481-1490
+  TR concat1(const TR& a, const TR& b) {
+    int N = a.shape[0], inner = a.shape[2] * a.shape[3];
+    TR y = make({N, a.shape[1] + b.shape[1], a.shape[2], a.shape[3]});
+    struct P { const float* in[2]; float* din[2]; int dims[2]; } p = {{a.x, b.x}, {a.d, b.d}, {a.shape[1], b.shape[1]}};
+    BK(concat)(y.x, p.in, p.dims, 2, N, inner);
+    push([=] { BK(concat_grad)(p.din, y.d, p.dims, 2, N, inner); });
+    return y;
+  }
+  // logSoftmaxB, nllLossB, sum, mean: TD.scala:1352-1383, 1492-1506
+  TR log_softmax(const TR& in) {
+    int r = in.shape[0], c = in.shape[1];
+    TR y = make({r, c});
+    BK(log_softmax)(in.x, y.x, r, c);
+    push([=] { BK(log_softmax_grad)(in.d, y.x, y.d, r, c); });
+    return y;
+  }
+  TR nll(const TR& in, const int32_t* target) {
+    int r = in.shape[0], c = in.shape[1];
+    TR y = make({r});
+    BK(nll)(in.x, target, y.x, r, c);
+    push([=] { BK(nll_grad)(in.d, y.d, target, r, c); });
+    return y;
+  }
+  TR sum(const TR& in) {
+    int64_t n = in.count();
+    TR y = make({1});
+    BK(sum)(in.x, y.x, n);
+    push([=] { BK(sum_grad)(in.d, y.d, n); });
+    return y;
+  }
+  TR mean(const TR& in) {
+    int64_t n = in.count();
+    TR y = make({1});
+    BK(mean)(in.x, y.x, n);
+    push([=] { BK(mean_grad)(in.d, y.d, n); });
+    return y;
+  }
+};
+
+}  // namespace lantern_host

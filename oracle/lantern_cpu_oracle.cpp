@@ -1,0 +1,817 @@
+// TEST INFRASTRUCTURE -- not part of the product.
+//
+// CPU restatement of Lantern's CPU backend (class BackendCPU,
+// src/main/scala/lantern/TensorDslCPU.scala) behind the same C ABI as the CUDA library, with the
+// prefix ora_ instead of ltb_ and host pointers instead of device pointers.  Only tests/, the smoke
+// check and bench.py's cpu_baseline / reference arm may load this library; the product never does.
+//
+// Each function cites the reference lines it follows.  Loop orders and float/double usage follow the
+// reference so that sequential-summation effects are the reference's own.  Deviations, all deliberate:
+//   * cblas_sgemm / cblas_sgemv come from OpenBLAS in the reference (version unpinned, -lopenblas at
+//     src/main/scala/lantern/DslAPI.scala:962); here they are a plain float triple loop.
+//   * relu_grad in place: the reference tests the already-clamped value with `< 0` and therefore never
+//     masks anything (TensorDslCPU.scala:726); the GPU backend of the reference masks by y > 0
+//     (cudnnActivationBackward, TensorDslCudnn.scala:1392-1429).  The oracle masks by y > 0.
+//   * batchNorm_grad and softmax_grad are `???` on the reference CPU backend (TensorDslCPU.scala:1058-1060,
+//     835); they are restated from the cuDNN semantics the reference's GPU backend relies on
+//     (TensorDslCudnn.scala:1025-1109, 1431-1504) and pinned by the known-answer vectors of
+//     src/test/scala/lantern/TestCudnn.scala:1051-1118 and 751-795.
+//   * maxpool with padding: the reference forgets the batch base in the saved index (TensorDslCPU.scala:939);
+//     the oracle adds it (the padded path is never used with pads on the training path).
+//
+// Parity status: pinned -- see tests/test_oracle_golden.py (known-answer vectors copied from the
+// reference's ScalaTest files) and tests/test_oracle_vs_generated.py (loss trajectory of the
+// reference's shipped generated MNIST program compiled from its own source).
+#define LTB_FN(name) ora_##name
+#include "../include/lantern_b200.h"
+
+#include <cfloat>
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <string>
+#include <vector>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+namespace {
+
+struct Ctx {
+  bool inited = false;
+  char* heap = nullptr;
+  size_t heap_bytes = 0;
+  size_t used = 0;
+  int fatal = 1;
+  int last = 0;
+  std::string msg;
+  int threads = 1;
+  int64_t calls = 0;
+} g;
+
+int fail(int code, const char* what) {
+  g.last = code;
+  g.msg = what;
+  if (g.fatal) {
+    fprintf(stderr, "lantern oracle error %d: %s\n", code, what);
+    exit(code < 0 ? -code : code);
+  }
+  return code;
+}
+#define REQUIRE(cond, what) do { if (!(cond)) return fail(LTB_E_ARG, what); } while (0)
+
+const size_t kGranule = 256;
+size_t round_up(size_t b) { return (b + kGranule - 1) / kGranule * kGranule; }
+
+// Plain row-major sgemm with the cblas contract: C = alpha*op(A)*op(B) + beta*C.
+// Summation over k is sequential in float for every output element.
+void sgemm(bool ta, bool tb, int M, int N, int K, float alpha, const float* A, int lda, const float* B, int ldb,
+           float beta, float* C, int ldc) {
+  const bool par = (double)M * N * K > 2e6 && g.threads > 1;
+#pragma omp parallel for if (par) num_threads(g.threads) schedule(static)
+  for (int i = 0; i < M; ++i) {
+    float* c = C + (size_t)i * ldc;
+    std::vector<float> acc(N, 0.0f);
+    if (!tb) {
+      for (int k = 0; k < K; ++k) {
+        const float a = ta ? A[(size_t)k * lda + i] : A[(size_t)i * lda + k];
+        const float* b = B + (size_t)k * ldb;
+        for (int j = 0; j < N; ++j) acc[j] += a * b[j];
+      }
+    } else {
+      for (int j = 0; j < N; ++j) {
+        const float* b = B + (size_t)j * ldb;
+        float s = 0.0f;
+        if (!ta) {
+          const float* a = A + (size_t)i * lda;
+          for (int k = 0; k < K; ++k) s += a[k] * b[k];
+        } else {
+          for (int k = 0; k < K; ++k) s += A[(size_t)k * lda + i] * b[k];
+        }
+        acc[j] = s;
+      }
+    }
+    if (beta == 0.0f) for (int j = 0; j < N; ++j) c[j] = alpha * acc[j];
+    else for (int j = 0; j < N; ++j) c[j] = alpha * acc[j] + beta * c[j];
+  }
+}
+
+inline float apply_op(int op, float a, float b) {
+  switch (op) {
+    case LTB_ADD: return a + b;
+    case LTB_SUB: return a - b;
+    case LTB_MUL: return a * b;
+    default: return a / b;
+  }
+}
+
+// Strides with 0 on broadcast (size-1) dims: "xStridesShadow", TensorDslCPU.scala:233-234.
+void shadow_strides(const int* shape, int rank, int64_t* st) {
+  int64_t s = 1;
+  for (int i = rank - 1; i >= 0; --i) { st[i] = shape[i] == 1 ? 0 : s; s *= shape[i]; }
+}
+int64_t prod(const int* s, int rank) { int64_t p = 1; for (int i = 0; i < rank; ++i) p *= s[i]; return p; }
+
+bool bcast_shape(const int* a, const int* b, int rank, int* r) {
+  if (rank < 1 || rank > 8) return false;
+  for (int i = 0; i < rank; ++i) {
+    if (a[i] < 1 || b[i] < 1) return false;
+    if (a[i] != b[i] && a[i] != 1 && b[i] != 1) return false;
+    r[i] = a[i] > b[i] ? a[i] : b[i];
+  }
+  return true;
+}
+
+// Row-major traversal of the broadcast shape calling f(idxA, idxB, idxR).
+template <class F>
+void traverse(const int* rshape, const int64_t* sa, const int64_t* sb, int rank, F f) {
+  int idx[8] = {0};
+  int64_t total = prod(rshape, rank);
+  int64_t ia = 0, ib = 0;
+  for (int64_t r = 0; r < total; ++r) {
+    f(ia, ib, r);
+    for (int d = rank - 1; d >= 0; --d) {
+      ++idx[d]; ia += sa[d]; ib += sb[d];
+      if (idx[d] < rshape[d]) break;
+      ia -= sa[d] * rshape[d]; ib -= sb[d] * rshape[d]; idx[d] = 0;
+    }
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+// ------------------------------------------------------------------ lifetime / arena
+// CPU arena: calloc(HEAP_SIZE_CPU) + bump pointer + memset-on-reset, DslAPI.scala:372-383, TD.scala:1782-1789.
+int ora_init(int /*device*/, size_t heap_bytes) {
+  if (g.inited) return fail(LTB_E_STATE, "ora_init: already initialised");
+  if (heap_bytes == 0) heap_bytes = (size_t)1 << 30;
+  g.heap = (char*)calloc(heap_bytes, 1);
+  if (!g.heap) return fail(LTB_E_OOM, "ora_init: calloc failed");
+  g.heap_bytes = heap_bytes; g.used = 0; g.inited = true; g.last = 0;
+  return LTB_OK;
+}
+int ora_shutdown(void) { free(g.heap); g.heap = nullptr; g.inited = false; g.used = 0; return LTB_OK; }
+int ora_set_fatal(int on) { g.fatal = on; return LTB_OK; }
+int ora_last_error(char* buf, int len) {
+  if (buf && len > 0) { strncpy(buf, g.msg.c_str(), len - 1); buf[len - 1] = 0; }
+  return g.last;
+}
+int ora_set_stream(void*) { return LTB_OK; }
+void* ora_get_stream(void) { return nullptr; }
+int ora_sync(void) { return LTB_OK; }
+int ora_set_math(int) { return LTB_OK; }
+int ora_device_status(void) { return LTB_OK; }
+int64_t ora_kernel_launches(void) { return 0; }
+// Not in the shared header: number of host threads the oracle may use (1 = the reference's protocol,
+// OPENBLAS_NUM_THREADS=1 in src/out/NIPS18evaluation/run_exp.sh:12).
+int ora_set_threads(int n) { g.threads = n < 1 ? 1 : n; return LTB_OK; }
+
+void* ora_malloc(size_t bytes) {
+  if (!g.inited) { fail(LTB_E_STATE, "ora_malloc: not initialised"); return nullptr; }
+  size_t b = round_up(bytes);
+  if (g.used + b > g.heap_bytes) { fail(LTB_E_OOM, "ora_malloc: arena exhausted"); return nullptr; }
+  void* p = g.heap + g.used; g.used += b;
+  return p;  // zero: calloc at start, memset on reset/free
+}
+void* ora_malloc_uninit(size_t bytes) { return ora_malloc(bytes); }
+int ora_free(void* p, size_t bytes) {
+  size_t b = round_up(bytes);
+  if (!p || b > g.used || (char*)p != g.heap + g.used - b) return fail(LTB_E_ARG, "ora_free: not the newest block");
+  memset(p, 0, b); g.used -= b; return LTB_OK;
+}
+void* ora_mark(void) { return g.heap + g.used; }
+int ora_reset(void* mark) {
+  char* m = (char*)mark;
+  if (m < g.heap || m > g.heap + g.used) return fail(LTB_E_ARG, "ora_reset: mark outside the used span");
+  memset(m, 0, g.heap + g.used - m); g.used = m - g.heap; return LTB_OK;
+}
+size_t ora_arena_used(void) { return g.used; }
+int ora_h2d(void* d, const void* s, size_t n) { memcpy(d, s, n); return LTB_OK; }
+int ora_d2h(void* d, const void* s, size_t n) { memcpy(d, s, n); return LTB_OK; }
+int ora_d2d(void* d, const void* s, size_t n) { memmove(d, s, n); return LTB_OK; }
+
+// ------------------------------------------------------------------ fill / init
+// fill, fillInPlace: TensorDslCPU.scala:30-35, 65-67.
+int ora_fill(float* x, float v, int64_t n) { for (int64_t i = 0; i < n; ++i) x[i] = v; return LTB_OK; }
+// fillWithBias: TensorDslCPU.scala:41-61.
+int ora_fill_with_bias(float* out, const float* bias, int outer, int c, int inner) {
+  REQUIRE(out && bias && outer >= 0 && c >= 0 && inner >= 0, "fill_with_bias: bad argument");
+  size_t off = 0;
+  for (int h = 0; h < outer; ++h) for (int cd = 0; cd < c; ++cd) for (int l = 0; l < inner; ++l) out[off++] = bias[cd];
+  return LTB_OK;
+}
+// randinit: TensorDslCPU.scala:101-110 with Random.rand() = (float)rand()/RAND_MAX (TD.scala:1018-1026).
+int ora_randinit(float* x, int64_t n, float scale, int seed) {
+  if (seed >= 0) srand((unsigned)seed);
+  for (int64_t i = 0; i < n; ++i) x[i] = ((float)rand() / RAND_MAX - 0.5f) * scale;
+  return LTB_OK;
+}
+// clipAt: TensorDslCPU.scala:113-119.
+int ora_clip(float* x, float bound, int64_t n) {
+  for (int64_t i = 0; i < n; ++i) { float t = x[i]; if (t > bound) x[i] = bound; if (t < -1.0f * bound) x[i] = -1.0f * bound; }
+  return LTB_OK;
+}
+
+// ------------------------------------------------------------------ dot family
+// vectorVectorDot: TensorDslCPU.scala:135-144.
+int ora_vv_dot(const float* x, const float* y, float* out, int n) {
+  float v = 0.0f; for (int i = 0; i < n; ++i) v += x[i] * y[i]; out[0] = v; return LTB_OK;
+}
+// dot_grad case (1,1): addMul(output.d.data(0), other), TensorDslCPU.scala:173-175, TD.scala:766-773.
+int ora_vv_dot_grad(float* dx, float* dy, const float* x, const float* y, const float* dout, int n) {
+  float a = dout[0];
+  if (dx) for (int i = 0; i < n; ++i) dx[i] = dx[i] + a * y[i];
+  if (dy) for (int i = 0; i < n; ++i) dy[i] = dy[i] + a * x[i];
+  return LTB_OK;
+}
+// matrixVectorDot: cblas_sgemv NoTrans beta 0, TensorDslCPU.scala:146-156.
+int ora_mv_dot(const float* a, const float* x, float* out, int m, int k) {
+  for (int i = 0; i < m; ++i) { float s = 0.0f; for (int j = 0; j < k; ++j) s += a[(size_t)i * k + j] * x[j]; out[i] = s; }
+  return LTB_OK;
+}
+// matrixMatrixDot: TensorDslCPU.scala:158-169.
+int ora_mm_dot(const float* a, const float* b, float* out, int m, int k, int n) {
+  sgemm(false, false, m, n, k, 1.0f, a, k, b, n, 0.0f, out, n); return LTB_OK;
+}
+// add_cartesian: TensorDslCPU.scala:186-196.
+int ora_add_cartesian(float* da, const float* y, const float* dout, int m, int k) {
+  for (int i = 0; i < m; ++i) for (int j = 0; j < k; ++j) da[(size_t)i * k + j] = da[(size_t)i * k + j] + y[j] * dout[i];
+  return LTB_OK;
+}
+// add_composition: cblas_sgemv Trans beta 1, TensorDslCPU.scala:198-206.
+int ora_add_composition(float* dx, const float* a, const float* dout, int m, int k) {
+  for (int j = 0; j < k; ++j) { float s = 0.0f; for (int i = 0; i < m; ++i) s += a[(size_t)i * k + j] * dout[i]; dx[j] += s; }
+  return LTB_OK;
+}
+// add_dotTrans1: x += y^T . output, TensorDslCPU.scala:208-215.
+int ora_add_dot_trans1(float* db, const float* a, const float* dc, int m, int k, int n) {
+  sgemm(true, false, k, n, m, 1.0f, a, k, dc, n, 1.0f, db, n); return LTB_OK;
+}
+// add_dotTrans2: x += y . output^T, TensorDslCPU.scala:217-225.
+int ora_add_dot_trans2(float* da, const float* dc, const float* b, int m, int k, int n) {
+  sgemm(false, true, m, k, n, 1.0f, dc, n, b, n, 1.0f, da, k); return LTB_OK;
+}
+
+// gemm: TensorDslCPU.scala:379-426 (four cblas_sgemm cases, beta 0).
+int ora_gemm(const float* a, int ta, const float* b, int tb, float alpha, float* c, int M, int N, int K) {
+  REQUIRE(a && b && c && M > 0 && N > 0 && K > 0, "gemm: bad argument");
+  sgemm(ta, tb, M, N, K, alpha, a, ta ? M : K, b, tb ? K : N, 0.0f, c, N);
+  return LTB_OK;
+}
+// gemm_grad: TensorDslCPU.scala:428-472 (beta 1 in all eight calls).
+int ora_gemm_grad(const float* a, float* da, int ta, const float* b, float* db, int tb, float alpha, const float* dc,
+                  int M, int N, int K) {
+  REQUIRE(a && b && dc && M > 0 && N > 0 && K > 0, "gemm_grad: bad argument");
+  if (!ta && !tb) {
+    if (da) sgemm(false, true, M, K, N, alpha, dc, N, b, N, 1.0f, da, K);
+    if (db) sgemm(true, false, K, N, M, alpha, a, K, dc, N, 1.0f, db, N);
+  } else if (!ta && tb) {
+    if (da) sgemm(false, false, M, K, N, alpha, dc, N, b, K, 1.0f, da, K);
+    if (db) sgemm(true, false, N, K, M, alpha, dc, N, a, K, 1.0f, db, K);
+  } else if (ta && !tb) {
+    if (da) sgemm(false, true, K, M, N, alpha, b, N, dc, N, 1.0f, da, M);
+    if (db) sgemm(false, false, K, N, M, alpha, a, M, dc, N, 1.0f, db, N);
+  } else {
+    if (da) sgemm(true, true, K, M, N, alpha, b, K, dc, N, 1.0f, da, M);
+    if (db) sgemm(true, true, N, K, M, alpha, dc, N, a, M, 1.0f, db, K);
+  }
+  return LTB_OK;
+}
+
+// ------------------------------------------------------------------ convolution
+namespace {
+// unfoldedCopy: TensorDslCPU.scala:484-530. The reference offsets the kw slot by outputWidth*outputWidth (line 491),
+// which equals outputHeight*outputWidth only for square outputs; the oracle uses the rectangular form.
+void unfolded_copy(float* finput, const float* input, int kW, int kH, int dW, int dH, int padW, int padH, int nIn,
+                   int iW, int iH, int oW, int oH) {
+  for (int k = 0; k < nIn * kH * kW; ++k) {
+    int nip = k / (kH * kW), rest = k % (kH * kW), kh = rest / kW, kw = rest % kW;
+    float* dst = finput + (size_t)k * oH * oW;
+    const float* src = input + (size_t)nip * iH * iW;
+    for (int y = 0; y < oH; ++y) {
+      int iy = y * dH - padH + kh;
+      for (int x = 0; x < oW; ++x) {
+        int ix = x * dW - padW + kw;
+        dst[y * oW + x] = (iy < 0 || iy >= iH || ix < 0 || ix >= iW) ? 0.0f : src[iy * iW + ix];
+      }
+    }
+  }
+}
+// unfoldedAcc: TensorDslCPU.scala:647-692 (same traversal order: plane, kh, kw, y, x).
+void unfolded_acc(const float* finput, float* input, int kW, int kH, int dW, int dH, int padW, int padH, int nIn,
+                  int iW, int iH, int oW, int oH) {
+  for (int nip = 0; nip < nIn; ++nip)
+    for (int kh = 0; kh < kH; ++kh)
+      for (int kw = 0; kw < kW; ++kw) {
+        const float* src = finput + ((size_t)(nip * kH + kh) * kW + kw) * oH * oW;
+        float* dst = input + (size_t)nip * iH * iW;
+        for (int y = 0; y < oH; ++y) {
+          int iy = y * dH - padH + kh;
+          if (iy < 0 || iy >= iH) continue;
+          for (int x = 0; x < oW; ++x) {
+            int ix = x * dW - padW + kw;
+            if (ix < 0 || ix >= iW) continue;
+            dst[iy * iW + ix] += src[y * oW + x];
+          }
+        }
+      }
+}
+}  // namespace
+
+// conv2D_batch: TensorDslCPU.scala:532-571. Output pre-filled with the bias (or zero), then per image
+// im2col + sgemm(Cout x HoWo x CinKhKw, beta 1).
+int ora_conv2d_fwd(const float* x, const float* w, const float* bias, float* y, int N, int C, int H, int W, int K, int R,
+                   int S, int sh, int sw, int ph, int pw) {
+  REQUIRE(x && w && y && N > 0 && C > 0 && K > 0 && R > 0 && S > 0 && sh > 0 && sw > 0 && ph >= 0 && pw >= 0, "conv2d_fwd: bad argument");
+  int oH = (H + 2 * ph - R) / sh + 1, oW = (W + 2 * pw - S) / sw + 1;
+  REQUIRE(oH > 0 && oW > 0, "conv2d_fwd: empty output");
+  size_t ohw = (size_t)oH * oW;
+  if (bias) ora_fill_with_bias(y, bias, N, K, (int)ohw); else memset(y, 0, sizeof(float) * N * K * ohw);
+  const bool par = g.threads > 1 && N > 1;
+#pragma omp parallel for if (par) num_threads(g.threads) schedule(static)
+  for (int t = 0; t < N; ++t) {
+    std::vector<float> fin((size_t)C * R * S * ohw);
+    unfolded_copy(fin.data(), x + (size_t)t * C * H * W, S, R, sw, sh, pw, ph, C, W, H, oW, oH);
+    int save = g.threads; // nested sgemm stays serial inside the parallel region
+    (void)save;
+    // sgemm body inlined serially to keep per-element summation order
+    const int dim1 = K, dim2 = C * R * S, dim3 = (int)ohw;
+    float* out = y + (size_t)t * K * ohw;
+    for (int i = 0; i < dim1; ++i) {
+      std::vector<float> acc(dim3, 0.0f);
+      for (int k = 0; k < dim2; ++k) {
+        float a = w[(size_t)i * dim2 + k];
+        const float* b = fin.data() + (size_t)k * dim3;
+        for (int j = 0; j < dim3; ++j) acc[j] += a * b[j];
+      }
+      for (int j = 0; j < dim3; ++j) out[(size_t)i * dim3 + j] = acc[j] + out[(size_t)i * dim3 + j];
+    }
+  }
+  return LTB_OK;
+}
+
+// conv2D_batch_grad: TensorDslCPU.scala:575-645. ConvGradInput (per image W^T.dY into the unfolded buffer, then
+// unfoldedAcc into dX) and ConvGradParam (per image dY.finput^T accumulated into dW, row sums into dbias).
+int ora_conv2d_bwd(const float* x, float* dx, const float* w, float* dw, float* dbias, const float* dy, int N, int C, int H,
+                   int W, int K, int R, int S, int sh, int sw, int ph, int pw) {
+  REQUIRE(x && w && dy && N > 0 && C > 0 && K > 0 && R > 0 && S > 0 && sh > 0 && sw > 0, "conv2d_bwd: bad argument");
+  int oH = (H + 2 * ph - R) / sh + 1, oW = (W + 2 * pw - S) / sw + 1;
+  size_t ohw = (size_t)oH * oW;
+  const int ckk = C * R * S;
+  if (dx) {
+    const bool par = g.threads > 1 && N > 1;
+#pragma omp parallel for if (par) num_threads(g.threads) schedule(static)
+    for (int t = 0; t < N; ++t) {
+      std::vector<float> fg((size_t)ckk * ohw);
+      const float* go = dy + (size_t)t * K * ohw;
+      // sgemm(Trans, NoTrans, ckk, ohw, K, 1, w, ckk, go, ohw, 0, fg, ohw)
+      for (int i = 0; i < ckk; ++i) {
+        float* row = fg.data() + (size_t)i * ohw;
+        for (size_t j = 0; j < ohw; ++j) row[j] = 0.0f;
+        for (int k = 0; k < K; ++k) {
+          float a = w[(size_t)k * ckk + i];
+          const float* b = go + (size_t)k * ohw;
+          for (size_t j = 0; j < ohw; ++j) row[j] += a * b[j];
+        }
+      }
+      unfolded_acc(fg.data(), dx + (size_t)t * C * H * W, S, R, sw, sh, pw, ph, C, W, H, oW, oH);
+    }
+  }
+  if (dw) {
+    // images are visited in order so that dW accumulates image by image as in the reference
+    std::vector<float> fin((size_t)ckk * ohw);
+    for (int t = 0; t < N; ++t) {
+      unfolded_copy(fin.data(), x + (size_t)t * C * H * W, S, R, sw, sh, pw, ph, C, W, H, oW, oH);
+      const float* go = dy + (size_t)t * K * ohw;
+      sgemm(false, true, K, ckk, (int)ohw, 1.0f, go, (int)ohw, fin.data(), (int)ohw, 1.0f, dw, ckk);
+      if (dbias)
+        for (int i = 0; i < K; ++i) {
+          float s = 0.0f; const float* d = go + (size_t)i * ohw;
+          for (size_t k = 0; k < ohw; ++k) s += d[k];
+          dbias[i] += 1.0f * s;
+        }
+    }
+  } else if (dbias) {
+    for (int t = 0; t < N; ++t) for (int i = 0; i < K; ++i) {
+      float s = 0.0f; const float* d = dy + ((size_t)t * K + i) * ohw;
+      for (size_t k = 0; k < ohw; ++k) s += d[k];
+      dbias[i] += s;
+    }
+  }
+  return LTB_OK;
+}
+
+// ------------------------------------------------------------------ pooling
+// maxPool2D_batch / maxPool_k_inplace: TensorDslCPU.scala:848-948.
+int ora_maxpool_fwd(const float* x, float* y, int32_t* idx, int N, int C, int H, int W, int kh, int kw, int sh, int sw, int pad) {
+  REQUIRE(x && y && idx && N > 0 && C > 0 && kh >= 1 && kw >= 1 && sh >= 1 && sw >= 1 && pad >= 0, "maxpool_fwd: bad argument");
+  REQUIRE(H + 2 * pad >= kh && W + 2 * pad >= kw, "maxpool_fwd: image too small");
+  int oH = (H + 2 * pad - kh) / sh + 1, oW = (W + 2 * pad - kw) / sw + 1;
+  for (int n = 0; n < N; ++n) for (int c = 0; c < C; ++c) {
+    const size_t ibase = ((size_t)n * C + c) * H * W, obase = ((size_t)n * C + c) * oH * oW;
+    for (int r = 0; r < oH; ++r) for (int q = 0; q < oW; ++q) {
+      float best = -FLT_MAX; int32_t bi = 0;  // Float.MinValue; zero-initialised savedIdx if nothing beats it
+      for (int a = 0; a < kh; ++a) for (int b = 0; b < kw; ++b) {
+        int ir = r * sh - pad + a, ic = q * sw - pad + b;
+        if (ir < 0 || ir >= H || ic < 0 || ic >= W) continue;
+        size_t ii = ibase + (size_t)ir * W + ic;
+        if (x[ii] > best) { best = x[ii]; bi = (int32_t)ii; }
+      }
+      y[obase + (size_t)r * oW + q] = best; idx[obase + (size_t)r * oW + q] = bi;
+    }
+  }
+  return LTB_OK;
+}
+// maxPool2D_batch_grad: TensorDslCPU.scala:950-959.
+int ora_maxpool_bwd(float* dx, const float* dy, const int32_t* idx, int64_t n_out) {
+  for (int64_t i = 0; i < n_out; ++i) dx[idx[i]] += dy[i];
+  return LTB_OK;
+}
+// averagePool2D_batch / averagePool_inplace: TensorDslCPU.scala:961-1006.
+int ora_avgpool_fwd(const float* x, float* y, int N, int C, int H, int W, int kh, int kw, int sh, int sw) {
+  REQUIRE(x && y && N > 0 && C > 0 && kh >= 1 && kw >= 1 && sh >= 1 && sw >= 1 && H >= kh && W >= kw, "avgpool_fwd: bad argument");
+  int oH = (H - kh) / sh + 1, oW = (W - kw) / sw + 1;
+  float ksz = kh * kw * 1.0f;
+  for (size_t p = 0; p < (size_t)N * C; ++p) for (int r = 0; r < oH; ++r) for (int q = 0; q < oW; ++q) {
+    float s = 0.0f;
+    for (int a = 0; a < kh; ++a) for (int b = 0; b < kw; ++b) s += x[p * H * W + (size_t)(r * sh + a) * W + q * sw + b];
+    y[p * oH * oW + (size_t)r * oW + q] = s / ksz;
+  }
+  return LTB_OK;
+}
+// averagePool2D_batch_grad: TensorDslCPU.scala:1008-1038.
+int ora_avgpool_bwd(float* dx, const float* dy, int N, int C, int H, int W, int kh, int kw, int sh, int sw) {
+  int oH = (H - kh) / sh + 1, oW = (W - kw) / sw + 1;
+  int ksz = kh * kw;
+  for (size_t p = 0; p < (size_t)N * C; ++p) for (int r = 0; r < oH; ++r) for (int q = 0; q < oW; ++q) {
+    float d = dy[p * oH * oW + (size_t)r * oW + q] / ksz;
+    for (int a = 0; a < kh; ++a) for (int b = 0; b < kw; ++b) dx[p * H * W + (size_t)(r * sh + a) * W + q * sw + b] += d;
+  }
+  return LTB_OK;
+}
+
+// ------------------------------------------------------------------ batch norm
+namespace {
+// batchNormAv: TD.scala:521-538 -- per channel, summed image by image in float, divided by N*H*W.
+void bn_average(const float* x, int N, int C, int HW, std::vector<float>& out, bool squared_diff, const float* mean) {
+  out.assign(C, 0.0f);
+  for (int n = 0; n < N; ++n) for (int c = 0; c < C; ++c) {
+    const float* p = x + ((size_t)n * C + c) * HW;
+    float r = out[c];
+    if (!squared_diff) for (int l = 0; l < HW; ++l) r = r + p[l];
+    else for (int l = 0; l < HW; ++l) { float d = p[l] - mean[c]; r = r + d * d; }
+    out[c] = r;
+  }
+  float base = (float)N * HW * 1.0f;
+  for (int c = 0; c < C; ++c) out[c] = out[c] / base;
+}
+}  // namespace
+
+// batchNormTraining: TensorDslCPU.scala:1047-1056 for y; saved stats / running stats as cuDNN gives them to the
+// reference's GPU backend (TensorDslCudnn.scala:1025-1056): exponentialAverageFactor = momentum, unbiased running var.
+int ora_bn_train_fwd(const float* x, float* y, const float* gamma, const float* beta, float* run_mean, float* run_var,
+                     float* save_mean, float* save_istd, int N, int C, int HW, float eps, float momentum) {
+  REQUIRE(x && y && gamma && beta && save_mean && save_istd && N > 0 && C > 0 && HW > 0, "bn_train_fwd: bad argument");
+  std::vector<float> mean, var;
+  bn_average(x, N, C, HW, mean, false, nullptr);
+  bn_average(x, N, C, HW, var, true, mean.data());
+  const bool par = g.threads > 1;
+#pragma omp parallel for if (par) num_threads(g.threads) schedule(static)
+  for (int n = 0; n < N; ++n) for (int c = 0; c < C; ++c) {
+    float sd = (float)sqrt((double)(var[c] + eps));
+    const float* p = x + ((size_t)n * C + c) * HW; float* q = y + ((size_t)n * C + c) * HW;
+    for (int l = 0; l < HW; ++l) q[l] = (p[l] - mean[c]) / sd * gamma[c] + beta[c];
+  }
+  double m = (double)N * HW;
+  for (int c = 0; c < C; ++c) {
+    save_mean[c] = mean[c];
+    save_istd[c] = 1.0f / (float)sqrt((double)(var[c] + eps));
+    if (run_mean) run_mean[c] = (1.0f - momentum) * run_mean[c] + momentum * mean[c];
+    if (run_var) run_var[c] = (1.0f - momentum) * run_var[c] + momentum * (float)(var[c] * (m > 1 ? m / (m - 1) : 1.0));
+  }
+  return LTB_OK;
+}
+// batchNorm_grad: `???` on the reference CPU backend; restated from cudnnBatchNormalizationBackward as the reference
+// calls it (alpha/beta = 1 for data and params, TensorDslCudnn.scala:1086-1109):
+//   dbeta += sum dy; dgamma += sum dy*xhat; dx += gamma*istd/m * (m*dy - sum dy - xhat * sum dy*xhat).
+int ora_bn_bwd(const float* x, float* dx, const float* dy, const float* gamma, float* dgamma, float* dbeta,
+               const float* save_mean, const float* save_istd, int N, int C, int HW) {
+  REQUIRE(x && dy && gamma && save_mean && save_istd && N > 0 && C > 0 && HW > 0, "bn_bwd: bad argument");
+  double m = (double)N * HW;
+  const bool par = g.threads > 1;
+#pragma omp parallel for if (par) num_threads(g.threads) schedule(static)
+  for (int c = 0; c < C; ++c) {
+    double s1 = 0, s2 = 0; float mu = save_mean[c], is = save_istd[c];
+    for (int n = 0; n < N; ++n) {
+      const float* p = x + ((size_t)n * C + c) * HW; const float* d = dy + ((size_t)n * C + c) * HW;
+      for (int l = 0; l < HW; ++l) { s1 += d[l]; s2 += (double)d[l] * ((p[l] - mu) * is); }
+    }
+    if (dbeta) dbeta[c] += (float)s1;
+    if (dgamma) dgamma[c] += (float)s2;
+    if (dx) {
+      float k = (float)(gamma[c] * is / m);
+      for (int n = 0; n < N; ++n) {
+        const float* p = x + ((size_t)n * C + c) * HW; const float* d = dy + ((size_t)n * C + c) * HW;
+        float* o = dx + ((size_t)n * C + c) * HW;
+        for (int l = 0; l < HW; ++l) { float xh = (p[l] - mu) * is; o[l] += k * (float)(m * d[l] - s1 - xh * s2); }
+      }
+    }
+  }
+  return LTB_OK;
+}
+// batchNormInference: TensorDslCPU.scala:1040-1045.
+int ora_bn_inference(const float* x, float* y, const float* gamma, const float* beta, const float* rm, const float* rv,
+                     int N, int C, int HW, float eps) {
+  REQUIRE(x && y && gamma && beta && rm && rv, "bn_inference: bad argument");
+  for (int n = 0; n < N; ++n) for (int c = 0; c < C; ++c) {
+    float sd = (float)sqrt((double)(rv[c] + eps));
+    const float* p = x + ((size_t)n * C + c) * HW; float* q = y + ((size_t)n * C + c) * HW;
+    for (int l = 0; l < HW; ++l) q[l] = (p[l] - rm[c]) / sd * gamma[c] + beta[c];
+  }
+  return LTB_OK;
+}
+
+// ------------------------------------------------------------------ broadcasting elementwise
+// elementWiseOpWithBroadCast: TensorDslCPU.scala:227-244.
+int ora_ew_binary(int op, const float* a, const int* as, const float* b, const int* bs, float* out, int rank) {
+  int rs[8]; REQUIRE(a && b && out && as && bs && bcast_shape(as, bs, rank, rs), "ew_binary: shapes do not broadcast");
+  int64_t sa[8], sb[8]; shadow_strides(as, rank, sa); shadow_strides(bs, rank, sb);
+  traverse(rs, sa, sb, rank, [&](int64_t ia, int64_t ib, int64_t ir) { out[ir] = apply_op(op, a[ia], b[ib]); });
+  return LTB_OK;
+}
+// backpropElementWiseOpWithBroadCast with the op1/op2 of add_grad, minus_grad, mul_grad, div_grad:
+// TensorDslCPU.scala:246-263, 300-337.
+int ora_ew_binary_grad(int op, const float* a, float* da, const int* as, const float* b, float* db, const int* bs,
+                       const float* dout, int rank) {
+  int rs[8]; REQUIRE(a && b && dout && bcast_shape(as, bs, rank, rs), "ew_binary_grad: shapes do not broadcast");
+  int64_t sa[8], sb[8]; shadow_strides(as, rank, sa); shadow_strides(bs, rank, sb);
+  traverse(rs, sa, sb, rank, [&](int64_t ia, int64_t ib, int64_t ir) {
+    float x = a[ia], y = b[ib], c = dout[ir];
+    float g1, g2;
+    switch (op) {
+      case LTB_ADD: g1 = c; g2 = c; break;
+      case LTB_SUB: g1 = c; g2 = 0.0f - c; break;
+      case LTB_MUL: g1 = c * y; g2 = c * x; break;
+      default: g1 = c / y; g2 = -1.0f * x * c / (y * y); break;
+    }
+    if (da) da[ia] += g1;
+    if (db) db[ib] += g2;
+  });
+  return LTB_OK;
+}
+// map(x, s => s op y): TensorDslCPU.scala:298, 309, 320, 331.
+int ora_ew_scalar(int op, const float* a, float s, float* out, int64_t n) {
+  for (int64_t i = 0; i < n; ++i) out[i] = apply_op(op, a[i], s);
+  return LTB_OK;
+}
+// inplaceElementWiseOpWithBroadCastOrReduce: TensorDslCPU.scala:265-279.
+int ora_ew_inplace(int op, float* x, const int* xs, const float* y, const int* ys, int rank) {
+  int rs[8]; REQUIRE(x && y && bcast_shape(xs, ys, rank, rs), "ew_inplace: shapes do not broadcast");
+  int64_t sx[8], sy[8]; shadow_strides(xs, rank, sx); shadow_strides(ys, rank, sy);
+  traverse(rs, sx, sy, rank, [&](int64_t ix, int64_t iy, int64_t) { x[ix] = apply_op(op, x[ix], y[iy]); });
+  return LTB_OK;
+}
+int ora_ew_inplace_scalar(int op, float* x, float s, int64_t n) {
+  for (int64_t i = 0; i < n; ++i) x[i] = apply_op(op, x[i], s);
+  return LTB_OK;
+}
+// plusBias / plusBias_grad: TensorDslCPU.scala:281-288.
+int ora_plus_bias(float* main, const int* ms, const float* bias, const int* bs, int rank) { return ora_ew_inplace(LTB_ADD, main, ms, bias, bs, rank); }
+int ora_plus_bias_grad(float* dbias, const int* bs, const float* dmain, const int* ms, int rank) { return ora_ew_inplace(LTB_ADD, dbias, bs, dmain, ms, rank); }
+// geam: TensorDslCPU.scala:342-347 (no-transpose case only on the CPU; the transposed cases follow cublasSgeam's
+// definition as used at TensorDslCublas.scala:318-373).
+int ora_geam(const float* x, int tx, float alpha, const float* y, int ty, float beta, float* out, int rows, int cols) {
+  REQUIRE(x && y && out && rows > 0 && cols > 0, "geam: bad argument");
+  REQUIRE(!((tx || ty) && (out == x || out == y)), "geam: in-place with transpose");
+  for (int i = 0; i < rows; ++i) for (int j = 0; j < cols; ++j) {
+    float xv = tx ? x[(size_t)j * rows + i] : x[(size_t)i * cols + j];
+    float yv = ty ? y[(size_t)j * rows + i] : y[(size_t)i * cols + j];
+    out[(size_t)i * cols + j] = xv * alpha + yv * beta;
+  }
+  return LTB_OK;
+}
+// trans / trans_grad: TensorDslCPU.scala:349-374.
+int ora_trans(const float* x, float* out, int rows, int cols) {
+  for (int i = 0; i < cols; ++i) for (int j = 0; j < rows; ++j) out[(size_t)i * rows + j] = x[(size_t)j * cols + i];
+  return LTB_OK;
+}
+int ora_trans_grad(float* dx, const float* dy, int rows, int cols) {
+  for (int i = 0; i < cols; ++i) for (int j = 0; j < rows; ++j) dx[(size_t)j * cols + i] += dy[(size_t)i * rows + j];
+  return LTB_OK;
+}
+
+// ------------------------------------------------------------------ activations
+// relu, tanh, sigmoid, exp, log, sqrt, square: TensorDslCPU.scala:710-781 (double libm, cast to float).
+int ora_unary(int op, const float* x, float* out, int64_t n) {
+  REQUIRE(x && out && n >= 0, "unary: bad argument");
+  for (int64_t i = 0; i < n; ++i) {
+    float v = x[i], r;
+    switch (op) {
+      case LTB_RELU: r = v < 0.0f ? 0.0f : v; break;
+      case LTB_TANH: r = (float)tanh((double)v); break;
+      case LTB_SIGMOID: r = 1.0f / ((float)exp((double)(-1.0f * v)) + 1.0f); break;
+      case LTB_EXP: r = (float)exp((double)v); break;
+      case LTB_LOG: r = (float)log((double)v); break;
+      case LTB_SQRT: r = (float)sqrt((double)v); break;
+      case LTB_SQUARE: r = v * v; break;
+      default: return fail(LTB_E_ARG, "unary: unknown op");
+    }
+    out[i] = r;
+  }
+  return LTB_OK;
+}
+// *_grad: TensorDslCPU.scala:722-781, TD.scala:789-809.
+int ora_unary_grad(int op, const float* x, float* dx, const float* y, const float* dy, int64_t n, int in_place) {
+  REQUIRE(dx && dy && n >= 0, "unary_grad: bad argument");
+  for (int64_t i = 0; i < n; ++i) {
+    switch (op) {
+      case LTB_RELU:
+        if (in_place) { if (!(y[i] > 0.0f)) dx[i] = 0.0f; }   // deviation from TensorDslCPU.scala:726, see header
+        else dx[i] += (x[i] < 0.0f ? 0.0f : dy[i]);
+        break;
+      case LTB_TANH: dx[i] = dx[i] + (1.0f - y[i] * y[i]) * dy[i]; break;
+      case LTB_SIGMOID: dx[i] = dx[i] + ((1.0f - y[i]) * y[i]) * dy[i]; break;
+      case LTB_EXP: dx[i] += dy[i] * y[i]; break;
+      case LTB_LOG: dx[i] += dy[i] / x[i]; break;
+      case LTB_SQRT: dx[i] += dy[i] / y[i] / 2.0f; break;
+      case LTB_SQUARE: dx[i] += dy[i] * x[i] * 2.0f; break;
+      default: return fail(LTB_E_ARG, "unary_grad: unknown op");
+    }
+  }
+  return LTB_OK;
+}
+
+// ------------------------------------------------------------------ softmax / loss
+// softmax: TensorDslCPU.scala:783-805; max2D TD.scala:552-571; sum(dim=1) accumulates left to right.
+int ora_softmax(const float* x, float* y, int rows, int cols) {
+  REQUIRE(x && y && rows > 0 && cols > 0, "softmax: bad argument");
+  for (int b = 0; b < rows; ++b) {
+    const float* p = x + (size_t)b * cols; float* q = y + (size_t)b * cols;
+    float mx = -FLT_MAX; for (int i = 0; i < cols; ++i) if (p[i] > mx) mx = p[i];
+    float s = 0.0f;
+    for (int i = 0; i < cols; ++i) { q[i] = (float)exp((double)(p[i] - mx)); s += q[i]; }
+    for (int i = 0; i < cols; ++i) q[i] = q[i] / s;
+  }
+  return LTB_OK;
+}
+// logSoftmax: TensorDslCPU.scala:807-832.
+int ora_log_softmax(const float* x, float* y, int rows, int cols) {
+  REQUIRE(x && y && rows > 0 && cols > 0, "log_softmax: bad argument");
+  for (int b = 0; b < rows; ++b) {
+    const float* p = x + (size_t)b * cols; float* q = y + (size_t)b * cols;
+    float mx = -FLT_MAX; for (int i = 0; i < cols; ++i) if (p[i] > mx) mx = p[i];
+    float s = 0.0f;
+    for (int i = 0; i < cols; ++i) s += (float)exp((double)(p[i] - mx));
+    float logsum = mx + (float)log((double)s);
+    for (int i = 0; i < cols; ++i) q[i] = p[i] - logsum;
+  }
+  return LTB_OK;
+}
+// softmax_grad: `???` on the CPU backend; cudnnSoftmaxBackward ACCURATE as called at TensorDslCudnn.scala:1465-1504:
+// dx += y * (dy - sum_j dy_j*y_j).
+int ora_softmax_grad(float* dx, const float* y, const float* dy, int rows, int cols) {
+  for (int b = 0; b < rows; ++b) {
+    const float* yy = y + (size_t)b * cols; const float* d = dy + (size_t)b * cols; float* o = dx + (size_t)b * cols;
+    float s = 0.0f; for (int i = 0; i < cols; ++i) s += d[i] * yy[i];
+    for (int i = 0; i < cols; ++i) o[i] += yy[i] * (d[i] - s);
+  }
+  return LTB_OK;
+}
+// logSoftmax_grad: TensorDslCPU.scala:837-846.
+int ora_log_softmax_grad(float* dx, const float* y, const float* dy, int rows, int cols) {
+  for (int b = 0; b < rows; ++b) {
+    const float* yy = y + (size_t)b * cols; const float* d = dy + (size_t)b * cols; float* o = dx + (size_t)b * cols;
+    float s = 0.0f; for (int i = 0; i < cols; ++i) s += d[i];
+    for (int i = 0; i < cols; ++i) o[i] += d[i] - (float)exp((double)yy[i]) * s;
+  }
+  return LTB_OK;
+}
+// nllLoss / nllLoss_grad: TensorDslCPU.scala:1090-1110.
+int ora_nll(const float* x, const int32_t* t, float* out, int rows, int cols) {
+  REQUIRE(x && t && out, "nll: bad argument");
+  for (int b = 0; b < rows; ++b) {
+    REQUIRE(t[b] >= 0 && t[b] < cols, "nll: target out of range");
+    out[b] = -1.0f * x[(size_t)b * cols + t[b]];
+  }
+  return LTB_OK;
+}
+int ora_nll_grad(float* dx, const float* dout, const int32_t* t, int rows, int cols) {
+  for (int b = 0; b < rows; ++b) dx[(size_t)b * cols + t[b]] += -1.0f * dout[b];
+  return LTB_OK;
+}
+
+// ------------------------------------------------------------------ reductions
+// sum / mean and grads: TensorDslCPU.scala:1115-1124 (sequential float fold).
+int ora_sum(const float* x, float* out, int64_t n) { float s = 0.0f; for (int64_t i = 0; i < n; ++i) s = s + x[i]; out[0] = s; return LTB_OK; }
+int ora_sum_grad(float* dx, const float* dout, int64_t n) { for (int64_t i = 0; i < n; ++i) dx[i] = dx[i] + dout[0]; return LTB_OK; }
+int ora_mean(const float* x, float* out, int64_t n) { float s = 0.0f; for (int64_t i = 0; i < n; ++i) s = s + x[i]; out[0] = s / (float)n; return LTB_OK; }
+int ora_mean_grad(float* dx, const float* dout, int64_t n) { float g1 = dout[0] / (float)n; for (int64_t i = 0; i < n; ++i) dx[i] = dx[i] + g1; return LTB_OK; }
+// sum(dim) / sum_grad(dim): TensorDslCPU.scala:1125-1164.
+int ora_sum_dim(const float* x, float* out, int outer, int d, int inner) {
+  for (int h = 0; h < outer; ++h) {
+    float* o = out + (size_t)h * inner;
+    for (int l = 0; l < inner; ++l) o[l] = 0.0f;
+    for (int s = 0; s < d; ++s) { const float* p = x + ((size_t)h * d + s) * inner; for (int l = 0; l < inner; ++l) o[l] += p[l]; }
+  }
+  return LTB_OK;
+}
+int ora_sum_dim_grad(float* dx, const float* dout, int outer, int d, int inner) {
+  for (int h = 0; h < outer; ++h) for (int s = 0; s < d; ++s) {
+    float* p = dx + ((size_t)h * d + s) * inner; const float* o = dout + (size_t)h * inner;
+    for (int l = 0; l < inner; ++l) p[l] += o[l];
+  }
+  return LTB_OK;
+}
+
+// ------------------------------------------------------------------ concat
+// concat / concat_grad: TensorDslCPU.scala:1166-1212.
+int ora_concat(float* out, const float* const* inputs, const int* dims, int n_inputs, int outer, int inner) {
+  REQUIRE(out && inputs && dims && n_inputs > 0, "concat: bad argument");
+  size_t t = 0;
+  for (int h = 0; h < outer; ++h) for (int k = 0; k < n_inputs; ++k) {
+    size_t stride = (size_t)dims[k] * inner; const float* p = inputs[k] + h * stride;
+    for (size_t l = 0; l < stride; ++l) out[t++] = p[l];
+  }
+  return LTB_OK;
+}
+int ora_concat_grad(float* const* dinputs, const float* dout, const int* dims, int n_inputs, int outer, int inner) {
+  size_t t = 0;
+  for (int h = 0; h < outer; ++h) for (int k = 0; k < n_inputs; ++k) {
+    size_t stride = (size_t)dims[k] * inner;
+    if (dinputs[k]) { float* p = dinputs[k] + h * stride; for (size_t l = 0; l < stride; ++l) p[l] += dout[t + l]; }
+    t += stride;
+  }
+  return LTB_OK;
+}
+
+// ------------------------------------------------------------------ dropout
+// dropout / dropout_grad: TensorDslCPU.scala:1066-1088.
+int ora_dropout(const float* x, float* y, float* mask, float p, int64_t n) {
+  REQUIRE(x && y && mask && p >= 0.0f && p < 1.0f, "dropout: rate must be in [0,1)");
+  float scale = 1.0f / (1.0f - p);
+  for (int64_t i = 0; i < n; ++i) {
+    if ((float)rand() / RAND_MAX > p) { y[i] = x[i] * scale; mask[i] = scale; } else { y[i] = 0.0f; mask[i] = 0.0f; }
+  }
+  return LTB_OK;
+}
+int ora_dropout_masked(const float* x, float* y, const float* mask, int64_t n) { for (int64_t i = 0; i < n; ++i) y[i] = x[i] * mask[i]; return LTB_OK; }
+int ora_dropout_grad(float* dx, const float* mask, const float* dy, int64_t n) { for (int64_t i = 0; i < n; ++i) dx[i] += mask[i] * dy[i]; return LTB_OK; }
+
+// ------------------------------------------------------------------ optimizers
+// SGD.step: geam(x, 1, d, -lr) then clear_grad, NNModule.scala:265-287 with geam of TensorDslCPU.scala:342-347.
+int ora_sgd_step(float* x, float* d, float lr, int64_t n) {
+  float beta = -1.0f * lr;
+  for (int64_t i = 0; i < n; ++i) { x[i] = x[i] * 1.0f + d[i] * beta; d[i] = 0.0f; }
+  return LTB_OK;
+}
+int ora_sgd_step_multi(float* const* xs, float* const* ds, const int64_t* sizes, int nt, float lr) {
+  for (int t = 0; t < nt; ++t) ora_sgd_step(xs[t], ds[t], lr, sizes[t]);
+  return LTB_OK;
+}
+// adagrad_update: TensorDslCPU.scala:1217-1230.
+int ora_adagrad_update(float* x, float* d, float* h, float lr, float clip, int descent, int64_t n) {
+  for (int64_t i = 0; i < n; ++i) {
+    float t = d[i]; if (t > clip) t = clip; if (t < -clip) t = -clip;
+    h[i] += t * t;
+    float upd = lr * t / (float)sqrt((double)(h[i] + 1e-8f));
+    if (descent) x[i] -= upd; else x[i] += upd;
+    d[i] = 0.0f;
+  }
+  return LTB_OK;
+}
+// momentum_update: TensorDslCPU.scala:1232-1246.
+int ora_momentum_update(float* x, float* d, float* m, float lr, float mu, float clip, int nesterov, int descent, int64_t n) {
+  for (int64_t i = 0; i < n; ++i) {
+    float t = d[i]; if (t > clip) t = clip; if (t < -clip) t = -clip;
+    m[i] *= mu; m[i] += t;
+    if (nesterov) t += mu * m[i]; else t = m[i];
+    if (descent) x[i] -= lr * t; else x[i] += lr * t;
+    d[i] = 0.0f;
+  }
+  return LTB_OK;
+}
+
+// ------------------------------------------------------------------ data parallelism: a single-rank communicator.
+// Multi-rank behaviour is exercised by the tests with torch.distributed (gloo) around these calls.
+int ora_comm_unique_id(void* out128) { memset(out128, 0, 128); return LTB_OK; }
+int ora_comm_init(int, int world, const void*) { return world == 1 ? LTB_OK : fail(LTB_E_COMM, "oracle communicator is single-rank"); }
+int ora_comm_destroy(void) { return LTB_OK; }
+int ora_comm_world(void) { return 1; }
+int ora_allreduce_sum(float*, int64_t) { return LTB_OK; }
+int ora_allreduce_sgd_step(float* x, float* d, float lr, int64_t n) { return ora_sgd_step(x, d, lr, n); }
+
+}  // extern "C"
+
+// ------------------------------------------------------------------ staging / replay: plain host equivalents.
+extern "C" {
+void* ora_host_alloc(size_t bytes) { return malloc(bytes); }
+int ora_host_free(void* p) { free(p); return LTB_OK; }
+int ora_d2h_async(void* d, const void* s, size_t n) { memcpy(d, s, n); return LTB_OK; }
+int ora_graph_begin(void) { return fail(LTB_E_ARG, "the CPU oracle does not record steps"); }
+void* ora_graph_end(void) { return nullptr; }
+int ora_graph_launch(void*) { return fail(LTB_E_ARG, "the CPU oracle does not record steps"); }
+int ora_graph_destroy(void*) { return LTB_OK; }
+}
