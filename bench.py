@@ -1,0 +1,301 @@
+#!/usr/bin/env python
+"""Benchmark of the ResNet-50 (CIFAR shape) training step through the lantern_b200 C ABI.
+
+    python bench.py --gpus 1 --steps 20 --warmup 5
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P bench.py --gpus N ...
+    python bench.py --impl reference ...        # the CPU path (oracle port of the reference's CPU backend) on the host cores
+
+One step = upload of one synthetic batch (128 x 3 x 32 x 32 per GPU, N(0,1), labels uniform 0..9) -> forward ->
+backward -> loss read-back -> SGD (lr 0.1) over every parameter tensor, issued by the host program in
+lantern_b200/hosts/models.cpp the way Lantern's generated code issues it, replayed from a recorded CUDA graph.
+Prints ONE JSON line (rank 0).
+"""
+import argparse
+import ctypes
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+BATCH = 128
+LR = 0.1
+METRIC = "train samples/s (ResNet-50 CIFAR shape, batch 128 per GPU)"
+
+
+# --------------------------------------------------------------------------------------------- workload arithmetic
+def resnet50_convs():
+    """(Cin, Cout, k, stride, pad, Hin) for the 53 convolutions, in forward order."""
+    convs = [(3, 64, 3, 1, 1, 32)]
+    inpl, h = 64, 16
+    for s, (planes, nblk) in enumerate(((64, 3), (128, 4), (256, 6), (512, 3))):
+        for i in range(nblk):
+            stride = 2 if (i == 0 and s > 0) else 1
+            convs.append((inpl, planes, 1, 1, 0, h))
+            convs.append((planes, planes, 3, stride, 1, h))
+            ho = h // stride
+            convs.append((planes, planes * 4, 1, 1, 0, ho))
+            if i == 0:
+                convs.append((inpl, planes * 4, 1, stride, 0, h))
+            inpl, h = planes * 4, ho
+    return convs
+
+
+def step_flops(batch):
+    """Algorithmic FLOPs of one training step: 2*N*Cout*Ho*Wo*Cin*k*k per conv pass; forward + weight-grad for all,
+    data-grad for all but the stem (its input is a leaf); FC 2048x10 three times."""
+    fwd = 0.0
+    total = 0.0
+    for (ci, co, k, s, p, h) in resnet50_convs():
+        ho = (h + 2 * p - k) // s + 1
+        f = 2.0 * batch * co * ho * ho * ci * k * k
+        fwd += f
+        total += 3 * f if ci != 3 else 2 * f
+    fc = 2.0 * batch * 2048 * 10
+    return fwd + fc, total + 3 * fc
+
+
+# --------------------------------------------------------------------------------------------- clocks
+class ClockSampler:
+    Q = "index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown," \
+        "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q, "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc:
+            self.proc.terminate()
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[1])); mx.append(float(r[2]))
+            except (ValueError, IndexError):
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"], "bf16_tflops_sustained": d.get("bf16_tflops_sustained", d["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+# --------------------------------------------------------------------------------------------- CPU legs
+def cpu_steps(batch, steps, warmup, threads):
+    """Time the CPU port (oracle/) of the same host program: `steps` training steps of `batch` samples."""
+    from lantern_b200._ffi import BoundLibrary
+    from lantern_b200.hosts import HostPrograms
+    ora = BoundLibrary(os.path.join(ROOT, "oracle", "liblantern_oracle.so"), "ora_")
+    ora.init(0, 8 << 30)
+    ora.cdll.ora_set_threads(threads)
+    m = HostPrograms(ora, os.path.join(ROOT, "oracle", "liblantern_oracle_hosts.so"), "orah_").model("resnet50", batch, seed=42)
+    rng = np.random.default_rng(1)
+    x = rng.standard_normal(batch * 3072).astype(np.float32)
+    y = rng.integers(0, 10, batch).astype(np.int32)
+    for _ in range(warmup):
+        m.step(x, y, LR)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        m.step(x, y, LR)
+    dt = time.perf_counter() - t0
+    m.close(); ora.shutdown()
+    return dt / max(1, steps)
+
+
+def reference_arm(args, rank):
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    sample = 8                                      # samples per step: a bounded slice of the 128-sample batch
+    probe = cpu_steps(sample, 1, 1, threads)        # also warms the page cache / allocator
+    steps = args.steps
+    if probe * (steps + args.warmup) > 240:         # keep the whole run within a few minutes
+        steps = max(1, int(240 / probe) - args.warmup)
+    sec = cpu_steps(sample, steps, args.warmup, threads)
+    v = sample / sec
+    line = {"impl": "reference", "metric": METRIC, "value": v, "unit": "samples/s", "n_gpus": args.gpus, "steps": steps, "warmup": args.warmup,
+            "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "resnet50_cifar_train_step_sgd_lr0.1", "batch_per_gpu": BATCH, "sample_per_step": sample,
+                       "note": "the reference's CPU backend cannot train ResNet-50 (batchNorm_grad is unimplemented) and its Scala generator "
+                               "needs a JVM; this arm times the CPU port of that backend (oracle/) running the same host program"},
+            "cpu_baseline": {"value": v, "unit": "samples/s", "cores": threads, "kind": "port",
+                             "sample": "%d steps of %d samples (slice of the 128-sample batch), all host threads" % (steps, sample)},
+            "e2e": {"value": v, "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------------------------- GPU arm
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--math", default="tf32", choices=["tf32", "fp32"])
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0")); local = int(os.environ.get("LOCAL_RANK", "0")); world = int(os.environ.get("WORLD_SIZE", "1"))
+    args.warmup = max(3, args.warmup)
+    if args.impl == "reference":
+        reference_arm(args, rank)
+        return
+    if args.gpus != world:
+        raise SystemExit("--gpus %d needs %d ranks (launch with torch.distributed.run --nproc-per-node %d)" % (args.gpus, args.gpus, args.gpus))
+
+    import torch
+    import torch.distributed as dist
+    import lantern_b200
+    from lantern_b200.hosts import HostPrograms
+
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    lib = lantern_b200.load()
+    lib.init(local, 14 << 30)
+    lib.set_math(1 if args.math == "tf32" else 0)
+    stream = torch.cuda.Stream(device=local)
+    lib.set_stream(stream.cuda_stream)
+    if world > 1:
+        idt = torch.zeros(128, dtype=torch.uint8, device="cuda")
+        if rank == 0:
+            buf = ctypes.create_string_buffer(128)
+            lib.comm_unique_id(buf)
+            idt.copy_(torch.frombuffer(bytearray(buf.raw), dtype=torch.uint8))
+        dist.broadcast(idt, 0)
+        raw = bytes(idt.cpu().numpy().tobytes())
+        lib.comm_init(rank, world, ctypes.create_string_buffer(raw, 128))
+
+    model = HostPrograms(lib).model("resnet50", BATCH, seed=42)      # identical replica on every rank
+    model.use_graph(True)
+    rng = np.random.default_rng(1000 + rank)                          # each rank its own shard of the global batch
+    pool = [(rng.standard_normal(BATCH * 3072).astype(np.float32), rng.integers(0, 10, BATCH).astype(np.int32)) for _ in range(4)]
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(stream):
+            a.record(stream)
+            for i in range(steps):
+                fn(i)
+            b.record(stream)
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b)
+        barrier()
+        if world > 1:
+            t = torch.tensor([ms], device="cuda"); dist.all_reduce(t, op=dist.ReduceOp.MAX); ms = float(t.item())
+        return ms
+
+    # ---- value: device-resident batch, the recorded step replayed back to back
+    model.set_resident(*pool[0])
+    for _ in range(args.warmup):
+        model.step_async(None if False else pool[0][0], pool[0][1], LR)
+    lib.sync()
+    sampler = ClockSampler(local); sampler.start()
+    l0 = lib.kernel_launches()
+    ms = timed(lambda i: model.step_async(pool[0][0], pool[0][1], LR), args.steps)
+    launches = lib.kernel_launches() - l0
+    clocks = sampler.stop()
+    loss_resident = model.last_loss()
+    value = BATCH * world * args.steps / (ms / 1e3)
+
+    # ---- e2e: host buffers in, loss out, every step (upload + read-back inside the timed region)
+    model.set_resident(None)
+    losses = []
+
+    def e2e_step(i):
+        x, y = pool[i % len(pool)]
+        model.step_async(x, y, LR)
+        lib.sync()
+        losses.append(model.last_loss())
+    for i in range(3):
+        e2e_step(i)
+    ms_e2e = timed(e2e_step, args.steps)
+    e2e = BATCH * world * args.steps / (ms_e2e / 1e3)
+
+    # ---- per-kernel timing of one eagerly issued step (CUDA events on the launching stream around every launch)
+    model.use_graph(False)
+    model.step(pool[0][0], pool[0][1], LR)
+    lib.profile(1)
+    prof_steps = 2
+    for i in range(prof_steps):
+        model.step(pool[i][0], pool[i][1], LR)
+    lib.profile(0)
+    buf = ctypes.create_string_buffer(1 << 16)
+    lib.profile_report(buf, 1 << 16)
+    kern = {}
+    for line in buf.value.decode().strip().split("\n"):
+        if line:
+            name, cnt, tms = line.split("\t")
+            kern[name] = (int(cnt) / prof_steps, float(tms) / prof_steps)
+    status = lib.device_status()
+
+    if rank == 0:
+        peaks = measured_peaks()
+        fwd_flops, flops = step_flops(BATCH)
+        total_ms = sum(t for _, t in kern.values())
+        contraction = {k: v for k, v in kern.items() if "gemm" in k}
+        c_ms = sum(t for _, t in contraction.values()); c_n = sum(c for c, _ in contraction.values())
+        top = max(kern.items(), key=lambda kv: kv[1][1]) if kern else ("none", (0, 0.0))
+        tf32_peak = peaks["bf16_tflops_sustained"] / 2.0
+        roofline = {"bound": "tensor", "kernel": "contraction engine (all conv fwd/dgrad/wgrad and gemm launches of one step)",
+                    "achieved": flops / (c_ms / 1e3) / 1e12 if c_ms else None, "peak": tf32_peak, "unit": "TFLOP/s",
+                    "frac": (flops / (c_ms / 1e3) / 1e12 / tf32_peak) if c_ms else None, "traffic": None,
+                    "peak_source": "%s bf16 sustained / 2 (TF32 rate is half the bf16 rate)" % peaks["source"],
+                    "launches_per_step": c_n, "ms_per_step": c_ms, "share_of_step_kernel_time": c_ms / total_ms if total_ms else None,
+                    "top_kernel": top[0][:80], "top_kernel_ms": top[1][1]}
+        line = {"metric": METRIC, "value": value, "unit": "samples/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+                "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                "dtype": args.math if args.math == "tf32" else "f32", "data": "synthetic",
+                "config": {"workload": "resnet50_cifar_train_step_sgd_lr0.1", "batch_per_gpu": BATCH, "global_batch": BATCH * world,
+                           "parallelism": "dp%d" % world, "replay": "cuda_graph", "l2": "per-step working set (~3 GB of activations and gradients) exceeds the 126 MB L2",
+                           "step_gflop": flops / 1e9},
+                "e2e": {"value": e2e, "unit": "samples/s", "ms_per_step": ms_e2e / args.steps, "h2d_bytes_per_step": BATCH * 3072 * 4 + BATCH * 4, "d2h_bytes_per_step": 4},
+                "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline, "device_status": status,
+                "loss": {"resident_last": loss_resident, "e2e_first": losses[3] if len(losses) > 3 else None, "e2e_last": losses[-1]},
+                "kernels_ms_per_step": {k[:60]: round(v[1], 4) for k, v in sorted(kern.items(), key=lambda kv: -kv[1][1])[:12]}}
+        if world == 1 and not args.no_cpu_baseline:
+            threads = os.cpu_count() or 1
+            sample = 8
+            sec = cpu_steps(sample, 3, 1, threads)
+            line["cpu_baseline"] = {"value": sample / sec, "unit": "samples/s", "cores": threads, "kind": "port",
+                                    "sample": "3 steps of %d samples (slice of the 128-sample batch) after 1 warm-up, all host threads" % sample}
+        print(json.dumps(line), flush=True)
+    model.close()
+    lib.shutdown()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -102,6 +102,11 @@ void* LTB_FN(graph_end)(void);
 int   LTB_FN(graph_launch)(void* graph);
 int   LTB_FN(graph_destroy)(void* graph);
 
+/* Built-in launch profiler: while on, every kernel launch of the library is bracketed by a CUDA event pair on the
+ * launching stream. The report has one line per kernel: name<TAB>launches<TAB>total milliseconds. */
+int   LTB_FN(profile)(int on);
+int   LTB_FN(profile_report)(char* buf, int len);
+
 /* ---------------------------------------------------------------- fill / init (CPU.scala:30-67, 101-119) */
 int LTB_FN(fill)(float* x, float value, int64_t n);                                  /* fill, fillInPlace */
 int LTB_FN(fill_with_bias)(float* out, const float* bias, int outer, int c, int inner); /* fillWithBias */

@@ -52,7 +52,7 @@ class LanternError(RuntimeError):
 
 
 class BoundLibrary:
-    """A loaded backend library (`ltb_` = CUDA product, `ora_` = CPU oracle) with checked calls.
+    """A loaded backend library (prefix `ltb_` = the CUDA product; tests bind their CPU checker under its own prefix).
 
     Attribute access gives the entry point without its prefix; integer-returning entry points raise
     LanternError on a negative status (the library is switched to non-fatal mode at load)."""

@@ -1,0 +1,71 @@
+// Shared state and helpers of liblantern_b200 (internal; the public contract is include/lantern_b200.h).
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <cstdio>
+#include <cstdlib>
+#include <string>
+
+#include "../../include/lantern_b200.h"
+
+namespace ltb {
+
+constexpr int kSMs = 148;             // B200: 2 dies x 74 SMs; grids are sized in multiples of this
+constexpr size_t kGranule = 256;      // arena granule (TMA wants 16 B bases/strides; 256 keeps every tensor sector-aligned)
+
+struct Context {
+  bool inited = false;
+  int device = 0;
+  cudaStream_t stream = nullptr;
+  bool own_stream = false;
+  char* heap = nullptr;
+  size_t heap_bytes = 0;
+  size_t used = 0;
+  int fatal = 1;
+  int last = 0;
+  std::string msg;
+  int math = LTB_MATH_TF32;
+  int64_t launches = 0;
+  bool capturing = false;
+  int64_t capture_launch_base = 0;
+  int* dev_status = nullptr;          // device word set by kernels whose bounded waits run out
+  int* host_status = nullptr;         // pinned mirror
+  float* scratch = nullptr;           // private workspace for multi-stage reductions
+  size_t scratch_bytes = 0;
+  int sm_count = kSMs;
+  bool profiling = false;             // per-launch CUDA-event timing (ltb_profile)
+  const char* label = nullptr;        // optional name override for the next launches
+};
+extern Context g;
+
+int fail(int code, const char* fmt, ...);
+void profile_before(const char* name);
+void profile_after();
+
+#define LTB_REQUIRE(cond, ...) do { if (!(cond)) return ::ltb::fail(LTB_E_ARG, __VA_ARGS__); } while (0)
+#define LTB_CUDA(call) do { cudaError_t e_ = (call); if (e_ != cudaSuccess) return ::ltb::fail(LTB_E_CUDA, "%s failed: %s (%s:%d)", #call, cudaGetErrorString(e_), __FILE__, __LINE__); } while (0)
+#define LTB_INITED() do { if (!::ltb::g.inited) return ::ltb::fail(LTB_E_STATE, "%s: library not initialised (call ltb_init)", __func__); } while (0)
+
+// Every kernel launch of the library goes through this macro so that ltb_kernel_launches() is exact.
+#define LTB_LAUNCH(kernel, grid, block, smem, ...)                                           \
+  do {                                                                                       \
+    if (::ltb::g.profiling) ::ltb::profile_before(::ltb::g.label ? ::ltb::g.label : #kernel); \
+    kernel<<<(grid), (block), (smem), ::ltb::g.stream>>>(__VA_ARGS__);                       \
+    if (::ltb::g.profiling) ::ltb::profile_after();                                          \
+    ++::ltb::g.launches;                                                                     \
+    cudaError_t e_ = cudaGetLastError();                                                     \
+    if (e_ != cudaSuccess) return ::ltb::fail(LTB_E_CUDA, "launch of %s failed: %s", #kernel, cudaGetErrorString(e_)); \
+  } while (0)
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+// Grid for a grid-stride kernel over `work` thread-items: enough CTAs to cover it, capped at `per_sm` CTAs per SM.
+inline int grid_for(int64_t work, int block, int per_sm = 8) {
+  int64_t need = ceil_div(work, block);
+  int64_t cap = (int64_t)g.sm_count * per_sm;
+  if (need < 1) need = 1;
+  return (int)(need < cap ? need : cap);
+}
+
+}  // namespace ltb

@@ -1,0 +1,252 @@
+// Context, arena, transfers and step replay of liblantern_b200.
+//
+// Replaces the runtime preamble the reference prints into every generated .cu file
+// (src/main/scala/lantern/DslAPI.scala:433-473: CUDA_CALL macro, gpuMallocBase/gpuMallocAddr bump arena,
+// myGpuMalloc/myGpuFree) and backend.setup()/cleanup() (TensorDslCublas.scala:113-124).
+#include <cstdarg>
+#include <cstring>
+#include <vector>
+
+#include "common.cuh"
+
+namespace ltb {
+
+Context g;
+
+int fail(int code, const char* fmt, ...) {
+  char buf[512];
+  va_list ap; va_start(ap, fmt); vsnprintf(buf, sizeof buf, fmt, ap); va_end(ap);
+  g.last = code; g.msg = buf;
+  if (g.fatal) {   // reference convention: print and exit (DslAPI.scala:435-451)
+    fprintf(stderr, "lantern_b200 error %d: %s\n", code, buf);
+    exit(code < 0 ? -code : code);
+  }
+  return code;
+}
+
+// ---- per-launch timing with CUDA events on the launching stream (enabled by ltb_profile) ----------------------------
+struct ProfRec { const char* name; cudaEvent_t a, b; };
+static std::vector<ProfRec> prof_recs;
+void profile_before(const char* name) {
+  ProfRec r; r.name = name;
+  cudaEventCreate(&r.a); cudaEventCreate(&r.b);
+  cudaEventRecord(r.a, g.stream);
+  prof_recs.push_back(r);
+}
+void profile_after() { cudaEventRecord(prof_recs.back().b, g.stream); }
+
+struct Graph { cudaGraphExec_t exec; cudaGraph_t graph; int64_t launches; };
+
+static size_t round_up(size_t b) { return (b + kGranule - 1) / kGranule * kGranule; }
+
+}  // namespace ltb
+
+using namespace ltb;
+
+extern "C" {
+
+int ltb_set_fatal(int on) { g.fatal = on; return LTB_OK; }
+int ltb_last_error(char* buf, int len) {
+  if (buf && len > 0) { strncpy(buf, g.msg.c_str(), len - 1); buf[len - 1] = 0; }
+  return g.last;
+}
+
+int ltb_init(int device, size_t heap_bytes) {
+  if (g.inited) return fail(LTB_E_STATE, "ltb_init: already initialised");
+  int count = 0;
+  cudaError_t e = cudaGetDeviceCount(&count);
+  if (e != cudaSuccess || count == 0)
+    return fail(LTB_E_CUDA, "ltb_init: no CUDA device (%s); this library has no CPU path", cudaGetErrorString(e));
+  LTB_REQUIRE(device >= 0 && device < count, "ltb_init: device %d out of range (%d devices)", device, count);
+  LTB_CUDA(cudaSetDevice(device));
+  cudaDeviceProp prop;
+  LTB_CUDA(cudaGetDeviceProperties(&prop, device));
+  if (prop.major != 10)
+    return fail(LTB_E_CUDA, "ltb_init: device is sm_%d%d; this library is built for sm_100a only", prop.major, prop.minor);
+  g.device = device; g.sm_count = prop.multiProcessorCount;
+  if (heap_bytes == 0) heap_bytes = (size_t)8 * 1024 * 1024 * 1024 + 16;   // HEAP_SIZE, DslAPI.scala:453
+  heap_bytes = round_up(heap_bytes);
+  LTB_CUDA(cudaStreamCreateWithFlags(&g.stream, cudaStreamNonBlocking));
+  g.own_stream = true;
+  LTB_CUDA(cudaMalloc((void**)&g.heap, heap_bytes));
+  g.heap_bytes = heap_bytes; g.used = 0;
+  LTB_CUDA(cudaMalloc((void**)&g.dev_status, 256));
+  LTB_CUDA(cudaMemset(g.dev_status, 0, 256));
+  LTB_CUDA(cudaMallocHost((void**)&g.host_status, 256));
+  g.host_status[0] = 0;
+  g.scratch_bytes = (size_t)8 << 20;
+  LTB_CUDA(cudaMalloc((void**)&g.scratch, g.scratch_bytes));
+  g.launches = 0; g.last = 0; g.msg.clear(); g.capturing = false; g.math = LTB_MATH_TF32;
+  g.inited = true;
+  return LTB_OK;
+}
+
+int ltb_comm_destroy(void);
+
+int ltb_shutdown(void) {
+  if (!g.inited) return LTB_OK;
+  ltb_comm_destroy();
+  cudaStreamSynchronize(g.stream);
+  cudaFree(g.heap); cudaFree(g.dev_status); cudaFree(g.scratch); cudaFreeHost(g.host_status);
+  if (g.own_stream) cudaStreamDestroy(g.stream);
+  g = Context();
+  return LTB_OK;
+}
+
+int ltb_set_stream(void* s) {
+  LTB_INITED();
+  if (g.own_stream) { cudaStreamSynchronize(g.stream); cudaStreamDestroy(g.stream); g.own_stream = false; }
+  g.stream = (cudaStream_t)s;
+  return LTB_OK;
+}
+void* ltb_get_stream(void) { return (void*)g.stream; }
+int ltb_sync(void) { LTB_INITED(); LTB_CUDA(cudaStreamSynchronize(g.stream)); return LTB_OK; }
+int ltb_set_math(int mode) {
+  LTB_REQUIRE(mode == LTB_MATH_FP32 || mode == LTB_MATH_TF32, "ltb_set_math: unknown mode %d", mode);
+  g.math = mode; return LTB_OK;
+}
+int ltb_device_status(void) {
+  if (!g.inited) return LTB_OK;
+  if (cudaMemcpyAsync(g.host_status, g.dev_status, 4, cudaMemcpyDeviceToHost, g.stream) != cudaSuccess) return LTB_E_CUDA;
+  if (cudaStreamSynchronize(g.stream) != cudaSuccess) return LTB_E_CUDA;
+  return g.host_status[0] ? LTB_E_DEVICE : LTB_OK;
+}
+int64_t ltb_kernel_launches(void) { return g.launches; }
+
+// ------------------------------------------------------------------ arena (DslAPI.scala:453-473)
+static void* arena_alloc(size_t bytes, bool zero) {
+  if (!g.inited) { fail(LTB_E_STATE, "ltb_malloc: library not initialised"); return nullptr; }
+  size_t b = round_up(bytes ? bytes : 1);
+  if (g.used + b > g.heap_bytes) {
+    fail(LTB_E_OOM, "ltb_malloc: arena exhausted (%zu used + %zu requested > %zu)", g.used, b, g.heap_bytes);
+    return nullptr;
+  }
+  char* p = g.heap + g.used;
+  g.used += b;
+  if (zero && cudaMemsetAsync(p, 0, b, g.stream) != cudaSuccess) { fail(LTB_E_CUDA, "ltb_malloc: memset failed"); return nullptr; }
+  return p;
+}
+void* ltb_malloc(size_t bytes) { return arena_alloc(bytes, true); }
+void* ltb_malloc_uninit(size_t bytes) { return arena_alloc(bytes, false); }
+int ltb_free(void* p, size_t bytes) {
+  LTB_INITED();
+  size_t b = round_up(bytes ? bytes : 1);
+  LTB_REQUIRE(p && b <= g.used && (char*)p == g.heap + g.used - b, "ltb_free: not the newest block (LIFO arena)");
+  g.used -= b;
+  return LTB_OK;
+}
+void* ltb_mark(void) { return g.heap + g.used; }
+int ltb_reset(void* mark) {
+  LTB_INITED();
+  char* m = (char*)mark;
+  LTB_REQUIRE(m >= g.heap && m <= g.heap + g.used, "ltb_reset: mark outside the used span");
+  g.used = (size_t)(m - g.heap);   // zeroing happens when a block is handed out again by ltb_malloc
+  return LTB_OK;
+}
+size_t ltb_arena_used(void) { return g.used; }
+
+// ------------------------------------------------------------------ transfers (GPUOps.scala:51-95)
+int ltb_h2d(void* dst, const void* src, size_t bytes) {
+  LTB_INITED(); LTB_REQUIRE(dst && src, "ltb_h2d: null pointer");
+  if (bytes) LTB_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, g.stream));
+  return LTB_OK;
+}
+int ltb_d2h(void* dst, const void* src, size_t bytes) {
+  LTB_INITED(); LTB_REQUIRE(dst && src, "ltb_d2h: null pointer");
+  LTB_REQUIRE(!g.capturing, "ltb_d2h: blocking read-back while recording a step");
+  if (bytes) LTB_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, g.stream));
+  LTB_CUDA(cudaStreamSynchronize(g.stream));
+  return LTB_OK;
+}
+int ltb_d2d(void* dst, const void* src, size_t bytes) {
+  LTB_INITED(); LTB_REQUIRE(dst && src, "ltb_d2d: null pointer");
+  if (bytes) LTB_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, g.stream));
+  return LTB_OK;
+}
+void* ltb_host_alloc(size_t bytes) {
+  void* p = nullptr;
+  if (cudaMallocHost(&p, bytes ? bytes : 1) != cudaSuccess) { fail(LTB_E_CUDA, "ltb_host_alloc: cudaMallocHost failed"); return nullptr; }
+  return p;
+}
+int ltb_host_free(void* p) { if (p) LTB_CUDA(cudaFreeHost(p)); return LTB_OK; }
+int ltb_d2h_async(void* dst, const void* src, size_t bytes) {
+  LTB_INITED(); LTB_REQUIRE(dst && src, "ltb_d2h_async: null pointer");
+  if (bytes) LTB_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, g.stream));
+  return LTB_OK;
+}
+
+// ------------------------------------------------------------------ whole-step replay
+int ltb_graph_begin(void) {
+  LTB_INITED(); LTB_REQUIRE(!g.capturing, "ltb_graph_begin: already recording");
+  LTB_CUDA(cudaStreamBeginCapture(g.stream, cudaStreamCaptureModeThreadLocal));
+  g.capturing = true; g.capture_launch_base = g.launches;
+  return LTB_OK;
+}
+void* ltb_graph_end(void) {
+  if (!g.capturing) { fail(LTB_E_STATE, "ltb_graph_end: not recording"); return nullptr; }
+  g.capturing = false;
+  cudaGraph_t graph = nullptr;
+  cudaError_t e = cudaStreamEndCapture(g.stream, &graph);
+  if (e != cudaSuccess || !graph) { fail(LTB_E_CUDA, "ltb_graph_end: capture failed: %s", cudaGetErrorString(e)); return nullptr; }
+  Graph* G = new Graph();
+  G->graph = graph; G->launches = g.launches - g.capture_launch_base;
+  g.launches = g.capture_launch_base;      // recording launched nothing
+  e = cudaGraphInstantiate(&G->exec, graph, 0);
+  if (e != cudaSuccess) { cudaGraphDestroy(graph); delete G; fail(LTB_E_CUDA, "ltb_graph_end: instantiate failed: %s", cudaGetErrorString(e)); return nullptr; }
+  return G;
+}
+int ltb_graph_launch(void* graph) {
+  LTB_INITED(); LTB_REQUIRE(graph, "ltb_graph_launch: null graph");
+  Graph* G = (Graph*)graph;
+  LTB_CUDA(cudaGraphLaunch(G->exec, g.stream));
+  g.launches += G->launches;
+  return LTB_OK;
+}
+int ltb_graph_destroy(void* graph) {
+  if (!graph) return LTB_OK;
+  Graph* G = (Graph*)graph;
+  cudaGraphExecDestroy(G->exec); cudaGraphDestroy(G->graph); delete G;
+  return LTB_OK;
+}
+
+// ------------------------------------------------------------------ built-in launch profiler
+// ltb_profile(1) starts timing every kernel launch of the library with a CUDA event pair on the launching stream;
+// ltb_profile(0) stops.  ltb_profile_report writes one line per kernel name: "name<TAB>launches<TAB>total_ms".
+int ltb_profile(int on) {
+  LTB_INITED(); LTB_REQUIRE(!g.capturing, "ltb_profile: not while recording a step");
+  if (on) { for (auto& r : prof_recs) { cudaEventDestroy(r.a); cudaEventDestroy(r.b); } prof_recs.clear(); }
+  g.profiling = on != 0;
+  return LTB_OK;
+}
+int ltb_profile_report(char* buf, int len) {
+  LTB_INITED(); LTB_REQUIRE(buf && len > 0, "ltb_profile_report: bad buffer");
+  LTB_CUDA(cudaStreamSynchronize(g.stream));
+  std::vector<std::string> names; std::vector<double> ms; std::vector<int64_t> cnt;
+  for (auto& r : prof_recs) {
+    float t = 0; cudaEventElapsedTime(&t, r.a, r.b);
+    size_t i = 0; for (; i < names.size(); ++i) if (names[i] == r.name) break;
+    if (i == names.size()) { names.push_back(r.name); ms.push_back(0); cnt.push_back(0); }
+    ms[i] += t; cnt[i] += 1;
+  }
+  std::string out;
+  for (size_t i = 0; i < names.size(); ++i) { char line[512]; snprintf(line, sizeof line, "%s\t%lld\t%.6f\n", names[i].c_str(), (long long)cnt[i], ms[i]); out += line; }
+  strncpy(buf, out.c_str(), len - 1); buf[len - 1] = 0;
+  return (int)out.size() < len ? LTB_OK : LTB_E_LIMIT;
+}
+int ltb_set_label(const char* label) { g.label = label; return LTB_OK; }
+
+// ------------------------------------------------------------------ host-RNG initialisation
+// randinit on the reference's GPU backends draws on the CPU and uploads (TensorDslCublas.scala:154-155);
+// the stream is glibc rand(), consumed in element order (TensorDslCPU.scala:101-110).
+int ltb_randinit(float* x, int64_t n, float scale, int seed) {
+  LTB_INITED(); LTB_REQUIRE(x && n >= 0, "ltb_randinit: bad argument");
+  LTB_REQUIRE(!g.capturing, "ltb_randinit: host RNG while recording a step");
+  if (seed >= 0) srand((unsigned)seed);
+  std::vector<float> h((size_t)n);
+  for (int64_t i = 0; i < n; ++i) h[i] = ((float)rand() / RAND_MAX - 0.5f) * scale;
+  if (n) LTB_CUDA(cudaMemcpyAsync(x, h.data(), (size_t)n * 4, cudaMemcpyHostToDevice, g.stream));
+  LTB_CUDA(cudaStreamSynchronize(g.stream));
+  return LTB_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,302 @@
+// Pooling and batch normalisation: HBM-streaming kernels.
+//
+// Replaces cudnnPooling* (TensorDslCudnn.scala:882-982) and cudnnBatchNormalization* (TensorDslCudnn.scala:984-1131).
+// Max pooling emits the int32 arg-max indices the reference's CPU backend saves (TensorDslCPU.scala:889-923),
+// which the reference's GPU backend does not produce at all (it returns None, TensorDslCudnn.scala:930).
+#include <cfloat>
+
+#include "common.cuh"
+
+namespace ltb {
+
+// ------------------------------------------------------------------------------------------------ max pool
+// One thread per output; window scanned row-major with strict '>' from -FLT_MAX so the first maximum wins.
+__global__ void maxpool_fwd_kernel(const float* __restrict__ x, float* __restrict__ y, int32_t* __restrict__ idx, int64_t n_out,
+                                   int H, int W, int oH, int oW, int kh, int kw, int sh, int sw, int pad) {
+  for (int64_t o = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; o < n_out; o += (int64_t)gridDim.x * blockDim.x) {
+    int q = (int)(o % oW); int64_t t = o / oW; int r = (int)(t % oH); int64_t plane = t / oH;
+    const int64_t base = plane * H * W;
+    float best = -FLT_MAX; int32_t bi = 0;
+    for (int a = 0; a < kh; ++a) {
+      int ir = r * sh - pad + a;
+      if (ir < 0 || ir >= H) continue;
+      for (int b = 0; b < kw; ++b) {
+        int ic = q * sw - pad + b;
+        if (ic < 0 || ic >= W) continue;
+        int64_t ii = base + (int64_t)ir * W + ic;
+        float v = x[ii];
+        if (v > best) { best = v; bi = (int32_t)ii; }
+      }
+    }
+    y[o] = best; idx[o] = bi;
+  }
+}
+// 2x2 stride 2, no padding, even W: each thread produces two adjacent outputs from two float4 loads
+// (4 B read per input element, 1+1 B written: the compulsory traffic).
+__global__ void maxpool2x2_fwd_kernel(const float* __restrict__ x, float* __restrict__ y, int32_t* __restrict__ idx, int64_t n_pairs,
+                                      int H, int W, int oH, int oW2) {
+  for (int64_t p = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; p < n_pairs; p += (int64_t)gridDim.x * blockDim.x) {
+    int q2 = (int)(p % oW2); int64_t t = p / oW2; int r = (int)(t % oH); int64_t plane = t / oH;
+    int64_t i0 = plane * H * W + (int64_t)(2 * r) * W + 4 * q2;
+    float4 top = *reinterpret_cast<const float4*>(x + i0), bot = *reinterpret_cast<const float4*>(x + i0 + W);
+    float b0 = -FLT_MAX, b1 = -FLT_MAX; int32_t k0 = 0, k1 = 0;
+    if (top.x > b0) { b0 = top.x; k0 = (int32_t)i0; }
+    if (top.y > b0) { b0 = top.y; k0 = (int32_t)i0 + 1; }
+    if (bot.x > b0) { b0 = bot.x; k0 = (int32_t)(i0 + W); }
+    if (bot.y > b0) { b0 = bot.y; k0 = (int32_t)(i0 + W) + 1; }
+    if (top.z > b1) { b1 = top.z; k1 = (int32_t)i0 + 2; }
+    if (top.w > b1) { b1 = top.w; k1 = (int32_t)i0 + 3; }
+    if (bot.z > b1) { b1 = bot.z; k1 = (int32_t)(i0 + W) + 2; }
+    if (bot.w > b1) { b1 = bot.w; k1 = (int32_t)(i0 + W) + 3; }
+    int64_t o = (plane * oH + r) * (int64_t)(2 * oW2) + 2 * q2;
+    *reinterpret_cast<float2*>(y + o) = make_float2(b0, b1);
+    *reinterpret_cast<int2*>(idx + o) = make_int2(k0, k1);
+  }
+}
+// dx[idx[i]] += dy[i] (TensorDslCPU.scala:955-957); windows may overlap, so the add is atomic.
+__global__ void maxpool_bwd_kernel(float* dx, const float* __restrict__ dy, const int32_t* __restrict__ idx, int64_t n) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) atomicAdd(dx + idx[i], dy[i]);
+}
+
+// ------------------------------------------------------------------------------------------------ average pool
+__global__ void avgpool_fwd_kernel(const float* __restrict__ x, float* __restrict__ y, int64_t n_out, int H, int W, int oH, int oW,
+                                   int kh, int kw, int sh, int sw) {
+  float ksz = (float)(kh * kw);
+  for (int64_t o = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; o < n_out; o += (int64_t)gridDim.x * blockDim.x) {
+    int q = (int)(o % oW); int64_t t = o / oW; int r = (int)(t % oH); int64_t plane = t / oH;
+    const float* p = x + plane * H * W + (int64_t)(r * sh) * W + q * sw;
+    float s = 0.0f;
+    for (int a = 0; a < kh; ++a) for (int b = 0; b < kw; ++b) s += p[a * W + b];
+    y[o] = s / ksz;
+  }
+}
+// One thread per INPUT element gathers dy/k over the windows that cover it (no atomics, deterministic).
+__global__ void avgpool_bwd_kernel(float* dx, const float* __restrict__ dy, int64_t n_in, int H, int W, int oH, int oW,
+                                   int kh, int kw, int sh, int sw) {
+  float ksz = (float)(kh * kw);
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_in; i += (int64_t)gridDim.x * blockDim.x) {
+    int c = (int)(i % W); int64_t t = i / W; int r = (int)(t % H); int64_t plane = t / H;
+    float s = 0.0f;
+    int r_lo = r - kh + 1 > 0 ? (r - kh + 1 + sh - 1) / sh : 0, c_lo = c - kw + 1 > 0 ? (c - kw + 1 + sw - 1) / sw : 0;
+    for (int orow = r_lo; orow < oH && orow * sh <= r; ++orow)
+      for (int ocol = c_lo; ocol < oW && ocol * sw <= c; ++ocol) s += dy[(plane * oH + orow) * oW + ocol] / ksz;
+    dx[i] += s;
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ batch norm
+__device__ __forceinline__ float wsum(float v) { for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o); return v; }
+__device__ void block_sum2(float& a, float& b) {
+  __shared__ float sa[32], sb[32];
+  int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  a = wsum(a); b = wsum(b);
+  __syncthreads();
+  if (lane == 0) { sa[w] = a; sb[w] = b; }
+  __syncthreads();
+  a = threadIdx.x < nw ? sa[threadIdx.x] : 0.0f; b = threadIdx.x < nw ? sb[threadIdx.x] : 0.0f;
+  if (w == 0) { a = wsum(a); b = wsum(b); }
+}
+
+// Pass 1 of the forward: per (channel, split) shifted sums  S1 = sum(x-K), S2 = sum((x-K)^2), K = x[0,c,0]
+// (shifting by a sample of the data keeps E[x^2]-E[x]^2 well conditioned).  grid = (C, S); split s takes images
+// s, s+S, ...  MODE 1 (backward): S1 = sum(dy), S2 = sum(dy * xhat).
+template <int MODE>
+__global__ void bn_reduce_kernel(const float* __restrict__ x, const float* __restrict__ dy, const float* __restrict__ mean,
+                                 const float* __restrict__ istd, float* __restrict__ partial, int N, int C, int HW) {
+  int c = blockIdx.x, s = blockIdx.y, S = gridDim.y;
+  float k = MODE == 0 ? x[(int64_t)c * HW] : mean[c];
+  float is = MODE == 0 ? 1.0f : istd[c];
+  float a = 0.0f, b = 0.0f;
+  if ((HW & 3) == 0) {
+    int hw4 = HW >> 2;
+    for (int n = s; n < N; n += S) {
+      const float4* px = reinterpret_cast<const float4*>(x + ((int64_t)n * C + c) * HW);
+      const float4* pd = MODE == 1 ? reinterpret_cast<const float4*>(dy + ((int64_t)n * C + c) * HW) : nullptr;
+      for (int i = threadIdx.x; i < hw4; i += blockDim.x) {
+        float4 v = px[i];
+        if (MODE == 0) {
+          float d0 = v.x - k, d1 = v.y - k, d2 = v.z - k, d3 = v.w - k;
+          a += (d0 + d1) + (d2 + d3); b += (d0 * d0 + d1 * d1) + (d2 * d2 + d3 * d3);
+        } else {
+          float4 d = pd[i];
+          a += (d.x + d.y) + (d.z + d.w);
+          b += (d.x * ((v.x - k) * is) + d.y * ((v.y - k) * is)) + (d.z * ((v.z - k) * is) + d.w * ((v.w - k) * is));
+        }
+      }
+    }
+  } else {
+    for (int n = s; n < N; n += S) {
+      const float* px = x + ((int64_t)n * C + c) * HW;
+      const float* pd = MODE == 1 ? dy + ((int64_t)n * C + c) * HW : nullptr;
+      for (int i = threadIdx.x; i < HW; i += blockDim.x) {
+        float v = px[i] - k;
+        if (MODE == 0) { a += v; b += v * v; } else { a += pd[i]; b += pd[i] * (v * is); }
+      }
+    }
+  }
+  block_sum2(a, b);
+  if (threadIdx.x == 0) { partial[((int64_t)c * S + s) * 2] = a; partial[((int64_t)c * S + s) * 2 + 1] = b; }
+}
+// Forward finalize: mean, biased variance (TensorDslCPU.scala:1047-1056), saved mean / inverse std and the running
+// statistics update the reference gets from cuDNN (factor `momentum`, unbiased variance; TensorDslCudnn.scala:1025-1056).
+__global__ void bn_fwd_finalize_kernel(const float* __restrict__ x, const float* __restrict__ partial, int S, int C, int HW, double m,
+                                       float eps, float momentum, float* save_mean, float* save_istd, float* run_mean, float* run_var) {
+  int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  double s1 = 0, s2 = 0;
+  for (int s = 0; s < S; ++s) { s1 += partial[((int64_t)c * S + s) * 2]; s2 += partial[((int64_t)c * S + s) * 2 + 1]; }
+  double k = x[(int64_t)c * HW];
+  double dm = s1 / m, var = s2 / m - dm * dm;
+  if (var < 0) var = 0;
+  float mean = (float)(k + dm);
+  save_mean[c] = mean;
+  save_istd[c] = 1.0f / sqrtf((float)var + eps);
+  if (run_mean) run_mean[c] = (1.0f - momentum) * run_mean[c] + momentum * mean;
+  if (run_var) run_var[c] = (1.0f - momentum) * run_var[c] + momentum * (float)(var * (m > 1 ? m / (m - 1) : 1.0));
+}
+// y = (x - mean) * istd * gamma + beta, 8 B per element.
+__global__ void bn_apply_kernel(const float* __restrict__ x, float* __restrict__ y, const float* __restrict__ mean,
+                                const float* __restrict__ istd, const float* __restrict__ gamma, const float* __restrict__ beta,
+                                int C, int HW, int64_t n, bool vec) {
+  if (vec) {
+    int hw4 = HW >> 2; int64_t n4 = n >> 2;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x) {
+      int c = (int)((i / hw4) % C);
+      float mu = mean[c], sc = istd[c] * gamma[c], sh = beta[c];
+      float4 v = reinterpret_cast<const float4*>(x)[i];
+      v.x = (v.x - mu) * sc + sh; v.y = (v.y - mu) * sc + sh; v.z = (v.z - mu) * sc + sh; v.w = (v.w - mu) * sc + sh;
+      reinterpret_cast<float4*>(y)[i] = v;
+    }
+  } else {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+      int c = (int)((i / HW) % C);
+      y[i] = (x[i] - mean[c]) * (istd[c] * gamma[c]) + beta[c];
+    }
+  }
+}
+// Backward finalize: dbeta += sum dy, dgamma += sum dy*xhat; coef[c] = {gamma*istd, sum dy / m, sum dy*xhat / m}.
+__global__ void bn_bwd_finalize_kernel(const float* __restrict__ partial, int S, int C, double m, const float* __restrict__ gamma,
+                                       const float* __restrict__ istd, float* dgamma, float* dbeta, float* __restrict__ coef) {
+  int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  double s1 = 0, s2 = 0;
+  for (int s = 0; s < S; ++s) { s1 += partial[((int64_t)c * S + s) * 2]; s2 += partial[((int64_t)c * S + s) * 2 + 1]; }
+  if (dbeta) dbeta[c] += (float)s1;
+  if (dgamma) dgamma[c] += (float)s2;
+  coef[c * 3] = gamma[c] * istd[c]; coef[c * 3 + 1] = (float)(s1 / m); coef[c * 3 + 2] = (float)(s2 / m);
+}
+// dx += gamma*istd * (dy - mean(dy) - xhat * mean(dy*xhat)): reads x, dy, dx and writes dx, 16 B per element.
+__global__ void bn_bwd_apply_kernel(const float* __restrict__ x, const float* __restrict__ dy, float* dx, const float* __restrict__ mean,
+                                    const float* __restrict__ istd, const float* __restrict__ coef, int C, int HW, int64_t n, bool vec) {
+  if (vec) {
+    int hw4 = HW >> 2; int64_t n4 = n >> 2;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x) {
+      int c = (int)((i / hw4) % C);
+      float mu = mean[c], is = istd[c], a = coef[c * 3], b = coef[c * 3 + 1], c2 = coef[c * 3 + 2];
+      float4 v = reinterpret_cast<const float4*>(x)[i], d = reinterpret_cast<const float4*>(dy)[i], o = reinterpret_cast<float4*>(dx)[i];
+      o.x += a * (d.x - b - (v.x - mu) * is * c2); o.y += a * (d.y - b - (v.y - mu) * is * c2);
+      o.z += a * (d.z - b - (v.z - mu) * is * c2); o.w += a * (d.w - b - (v.w - mu) * is * c2);
+      reinterpret_cast<float4*>(dx)[i] = o;
+    }
+  } else {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+      int c = (int)((i / HW) % C);
+      dx[i] += coef[c * 3] * (dy[i] - coef[c * 3 + 1] - (x[i] - mean[c]) * istd[c] * coef[c * 3 + 2]);
+    }
+  }
+}
+__global__ void bn_inference_kernel(const float* __restrict__ x, float* __restrict__ y, const float* __restrict__ gamma, const float* __restrict__ beta,
+                                    const float* __restrict__ rm, const float* __restrict__ rv, int C, int HW, int64_t n, float eps) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    int c = (int)((i / HW) % C);
+    y[i] = (x[i] - rm[c]) / sqrtf(rv[c] + eps) * gamma[c] + beta[c];   // TensorDslCPU.scala:1040-1045
+  }
+}
+
+static int bn_splits(int N, int C) {
+  int s = (int)ceil_div(2 * (int64_t)g.sm_count, C);
+  if (s > N) s = N;
+  if (s > 64) s = 64;
+  return s < 1 ? 1 : s;
+}
+
+}  // namespace ltb
+
+using namespace ltb;
+
+extern "C" {
+
+int ltb_maxpool_fwd(const float* x, float* y, int32_t* idx, int N, int C, int H, int W, int kh, int kw, int sh, int sw, int pad) {
+  LTB_INITED();
+  LTB_REQUIRE(x && y && idx && N > 0 && C > 0 && kh >= 1 && kw >= 1 && sh >= 1 && sw >= 1 && pad >= 0, "ltb_maxpool_fwd: bad argument");
+  LTB_REQUIRE(H + 2 * pad >= kh && W + 2 * pad >= kw, "ltb_maxpool_fwd: image too small for the window");
+  LTB_REQUIRE((int64_t)N * C * H * W < ((int64_t)1 << 31), "ltb_maxpool_fwd: tensor too large for int32 indices");
+  int oH = (H + 2 * pad - kh) / sh + 1, oW = (W + 2 * pad - kw) / sw + 1;
+  int64_t n_out = (int64_t)N * C * oH * oW;
+  if (kh == 2 && kw == 2 && sh == 2 && sw == 2 && pad == 0 && (W & 3) == 0 && (H & 1) == 0 && aligned16(x) && aligned16(y) && aligned16(idx)) {
+    int64_t pairs = n_out / 2;
+    LTB_LAUNCH(maxpool2x2_fwd_kernel, grid_for(pairs, 256), 256, 0, x, y, idx, pairs, H, W, oH, oW / 2);
+  } else {
+    LTB_LAUNCH(maxpool_fwd_kernel, grid_for(n_out, 256), 256, 0, x, y, idx, n_out, H, W, oH, oW, kh, kw, sh, sw, pad);
+  }
+  return LTB_OK;
+}
+int ltb_maxpool_bwd(float* dx, const float* dy, const int32_t* idx, int64_t n_out) {
+  LTB_INITED(); LTB_REQUIRE(dx && dy && idx && n_out >= 0, "ltb_maxpool_bwd: bad argument");
+  if (n_out) LTB_LAUNCH(maxpool_bwd_kernel, grid_for(n_out, 256), 256, 0, dx, dy, idx, n_out);
+  return LTB_OK;
+}
+int ltb_avgpool_fwd(const float* x, float* y, int N, int C, int H, int W, int kh, int kw, int sh, int sw) {
+  LTB_INITED();
+  LTB_REQUIRE(x && y && N > 0 && C > 0 && kh >= 1 && kw >= 1 && sh >= 1 && sw >= 1 && H >= kh && W >= kw, "ltb_avgpool_fwd: bad argument");
+  int oH = (H - kh) / sh + 1, oW = (W - kw) / sw + 1;
+  int64_t n_out = (int64_t)N * C * oH * oW;
+  LTB_LAUNCH(avgpool_fwd_kernel, grid_for(n_out, 256), 256, 0, x, y, n_out, H, W, oH, oW, kh, kw, sh, sw);
+  return LTB_OK;
+}
+int ltb_avgpool_bwd(float* dx, const float* dy, int N, int C, int H, int W, int kh, int kw, int sh, int sw) {
+  LTB_INITED();
+  LTB_REQUIRE(dx && dy && N > 0 && C > 0 && kh >= 1 && kw >= 1 && sh >= 1 && sw >= 1 && H >= kh && W >= kw, "ltb_avgpool_bwd: bad argument");
+  int oH = (H - kh) / sh + 1, oW = (W - kw) / sw + 1;
+  int64_t n_in = (int64_t)N * C * H * W;
+  LTB_LAUNCH(avgpool_bwd_kernel, grid_for(n_in, 256), 256, 0, dx, dy, n_in, H, W, oH, oW, kh, kw, sh, sw);
+  return LTB_OK;
+}
+
+int ltb_bn_train_fwd(const float* x, float* y, const float* gamma, const float* beta, float* run_mean, float* run_var,
+                     float* save_mean, float* save_istd, int N, int C, int HW, float eps, float momentum) {
+  LTB_INITED();
+  LTB_REQUIRE(x && y && gamma && beta && save_mean && save_istd && N > 0 && C > 0 && HW > 0, "ltb_bn_train_fwd: bad argument");
+  int S = bn_splits(N, C);
+  LTB_REQUIRE((size_t)C * S * 2 * 4 <= g.scratch_bytes, "ltb_bn_train_fwd: too many channels");
+  int64_t n = (int64_t)N * C * HW;
+  bool vec = (HW & 3) == 0 && aligned16(x) && aligned16(y);
+  LTB_LAUNCH(bn_reduce_kernel<0>, dim3(C, S), 256, 0, x, nullptr, nullptr, nullptr, g.scratch, N, C, HW);
+  LTB_LAUNCH(bn_fwd_finalize_kernel, (C + 127) / 128, 128, 0, x, (const float*)g.scratch, S, C, HW, (double)N * HW, eps, momentum,
+             save_mean, save_istd, run_mean, run_var);
+  LTB_LAUNCH(bn_apply_kernel, grid_for(vec ? n / 4 : n, 256), 256, 0, x, y, (const float*)save_mean, (const float*)save_istd, gamma, beta, C, HW, n, vec);
+  return LTB_OK;
+}
+int ltb_bn_bwd(const float* x, float* dx, const float* dy, const float* gamma, float* dgamma, float* dbeta,
+               const float* save_mean, const float* save_istd, int N, int C, int HW) {
+  LTB_INITED();
+  LTB_REQUIRE(x && dy && gamma && save_mean && save_istd && N > 0 && C > 0 && HW > 0, "ltb_bn_bwd: bad argument");
+  int S = bn_splits(N, C);
+  LTB_REQUIRE((size_t)C * (S * 2 + 3) * 4 <= g.scratch_bytes, "ltb_bn_bwd: too many channels");
+  float* coef = g.scratch + (size_t)C * S * 2;
+  int64_t n = (int64_t)N * C * HW;
+  bool vec = (HW & 3) == 0 && aligned16(x) && aligned16(dy) && aligned16(dx);
+  LTB_LAUNCH(bn_reduce_kernel<1>, dim3(C, S), 256, 0, x, dy, save_mean, save_istd, g.scratch, N, C, HW);
+  LTB_LAUNCH(bn_bwd_finalize_kernel, (C + 127) / 128, 128, 0, (const float*)g.scratch, S, C, (double)N * HW, gamma, save_istd, dgamma, dbeta, coef);
+  if (dx) LTB_LAUNCH(bn_bwd_apply_kernel, grid_for(vec ? n / 4 : n, 256), 256, 0, x, dy, dx, save_mean, save_istd, (const float*)coef, C, HW, n, vec);
+  return LTB_OK;
+}
+int ltb_bn_inference(const float* x, float* y, const float* gamma, const float* beta, const float* rm, const float* rv,
+                     int N, int C, int HW, float eps) {
+  LTB_INITED(); LTB_REQUIRE(x && y && gamma && beta && rm && rv && N > 0 && C > 0 && HW > 0, "ltb_bn_inference: bad argument");
+  int64_t n = (int64_t)N * C * HW;
+  LTB_LAUNCH(bn_inference_kernel, grid_for(n, 256), 256, 0, x, y, gamma, beta, rm, rv, C, HW, n, eps);
+  return LTB_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,234 @@
+// Reductions, softmax family, NLL loss and the vector/matrix-vector dot family.
+//
+// Replaces cudnnReduceTensor / cudnnSoftmax* (TensorDslCudnn.scala:1431-1576), the one-thread-per-block nllLoss
+// kernels (DslAPI.scala:506-516) and cublasSdot/Sgemv (TensorDslCublas.scala:173-201, 257-264).  Semantics follow
+// TensorDslCPU.scala (cited per entry point).  Rows are reduced by one warp each with shuffles; full reductions
+// use a block tree in shared memory and, for large inputs, a second pass over per-block partials.
+#include <cfloat>
+
+#include "common.cuh"
+
+namespace ltb {
+
+__device__ __forceinline__ float warp_sum(float v) { for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o); return v; }
+__device__ __forceinline__ float warp_max(float v) { for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o)); return v; }
+
+__device__ float block_sum(float v) {
+  __shared__ float sh[32];
+  int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) sh[w] = v;
+  __syncthreads();
+  int nw = (blockDim.x + 31) >> 5;
+  v = threadIdx.x < nw ? sh[threadIdx.x] : 0.0f;
+  if (w == 0) v = warp_sum(v);
+  return v;   // valid in warp 0
+}
+
+// out[0] = scale * sum(x) (single block) or partial[b] = sum of the block's slice.
+__global__ void sum_kernel(const float* __restrict__ x, float* out, int64_t n, float scale, bool partial) {
+  float s = 0.0f;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) s += x[i];
+  s = block_sum(s);
+  if (threadIdx.x == 0) out[partial ? blockIdx.x : 0] = partial ? s : s * scale;
+}
+__global__ void add_scalar_from_kernel(float* dx, const float* __restrict__ dout, float scale, int64_t n) {
+  float v = dout[0] * scale;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) dx[i] += v;
+}
+// out[o, l] = sum_s x[o, s, l]
+__global__ void sum_dim_kernel(const float* __restrict__ x, float* out, int outer, int d, int inner) {
+  int64_t n = (int64_t)outer * inner;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    int64_t o = i / inner, l = i % inner;
+    const float* p = x + o * d * inner + l;
+    float s = 0.0f;
+    for (int k = 0; k < d; ++k) s += p[(int64_t)k * inner];
+    out[i] = s;
+  }
+}
+// inner == 1: one warp per output
+__global__ void sum_lastdim_kernel(const float* __restrict__ x, float* out, int outer, int d) {
+  int64_t w = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; int lane = threadIdx.x & 31;
+  if (w >= outer) return;
+  float s = 0.0f;
+  for (int k = lane; k < d; k += 32) s += x[w * d + k];
+  s = warp_sum(s);
+  if (lane == 0) out[w] = s;
+}
+__global__ void sum_dim_grad_kernel(float* dx, const float* __restrict__ dout, int outer, int d, int inner) {
+  int64_t n = (int64_t)outer * d * inner;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    int64_t l = i % inner, o = i / ((int64_t)d * inner);
+    dx[i] += dout[o * inner + l];
+  }
+}
+
+// One warp per row. MODE 0 softmax, 1 logSoftmax (TensorDslCPU.scala:783-832).
+template <int MODE>
+__global__ void softmax_kernel(const float* __restrict__ x, float* y, int rows, int cols) {
+  int64_t r = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; int lane = threadIdx.x & 31;
+  if (r >= rows) return;
+  const float* p = x + r * cols; float* q = y + r * cols;
+  float mx = -FLT_MAX;
+  for (int i = lane; i < cols; i += 32) mx = fmaxf(mx, p[i]);
+  mx = warp_max(mx);
+  float s = 0.0f;
+  for (int i = lane; i < cols; i += 32) s += expf(p[i] - mx);
+  s = warp_sum(s);
+  if (MODE == 0) { for (int i = lane; i < cols; i += 32) q[i] = expf(p[i] - mx) / s; }
+  else { float logsum = mx + logf(s); for (int i = lane; i < cols; i += 32) q[i] = p[i] - logsum; }
+}
+// MODE 0: dx += y*(dy - sum dy*y) (cudnnSoftmaxBackward ACCURATE, TensorDslCudnn.scala:1465-1504);
+// MODE 1: dx += dy - exp(y)*sum dy (TensorDslCPU.scala:837-846).
+template <int MODE>
+__global__ void softmax_grad_kernel(float* dx, const float* __restrict__ y, const float* __restrict__ dy, int rows, int cols) {
+  int64_t r = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; int lane = threadIdx.x & 31;
+  if (r >= rows) return;
+  const float* yy = y + r * cols; const float* d = dy + r * cols; float* o = dx + r * cols;
+  float s = 0.0f;
+  for (int i = lane; i < cols; i += 32) s += MODE == 0 ? d[i] * yy[i] : d[i];
+  s = warp_sum(s);
+  for (int i = lane; i < cols; i += 32) o[i] += MODE == 0 ? yy[i] * (d[i] - s) : d[i] - expf(yy[i]) * s;
+}
+__global__ void nll_kernel(const float* __restrict__ x, const int32_t* __restrict__ t, float* out, int rows, int cols) {
+  int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b < rows) { int k = t[b]; out[b] = (k >= 0 && k < cols) ? -1.0f * x[(int64_t)b * cols + k] : 0.0f; }
+}
+__global__ void nll_grad_kernel(float* dx, const float* __restrict__ dout, const int32_t* __restrict__ t, int rows, int cols) {
+  int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b < rows) { int k = t[b]; if (k >= 0 && k < cols) dx[(int64_t)b * cols + k] += -1.0f * dout[b]; }
+}
+
+// y[m] (+)= A[m,k] x[k]: one warp per row, float4 when k % 4 == 0 (memory-bound: A is read once).
+template <bool ACC>
+__global__ void gemv_rows_kernel(const float* __restrict__ a, const float* __restrict__ x, float* y, int m, int k) {
+  int64_t r = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; int lane = threadIdx.x & 31;
+  if (r >= m) return;
+  const float* row = a + r * k;
+  float s = 0.0f;
+  if ((k & 3) == 0 && ((reinterpret_cast<uintptr_t>(row) | reinterpret_cast<uintptr_t>(x)) & 15) == 0) {
+    for (int i = lane * 4; i < k; i += 128) {
+      float4 av = *reinterpret_cast<const float4*>(row + i), xv = *reinterpret_cast<const float4*>(x + i);
+      s += av.x * xv.x + av.y * xv.y + av.z * xv.z + av.w * xv.w;
+    }
+  } else for (int i = lane; i < k; i += 32) s += row[i] * x[i];
+  s = warp_sum(s);
+  if (lane == 0) y[r] = ACC ? y[r] + s : s;
+}
+// dx[k] += sum_i A[i,k] dout[i]: threads along k (coalesced), loop over rows.
+__global__ void gemv_cols_kernel(const float* __restrict__ a, const float* __restrict__ dout, float* dx, int m, int k) {
+  int j = blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= k) return;
+  float s = 0.0f;
+  for (int i = 0; i < m; ++i) s += a[(int64_t)i * k + j] * dout[i];
+  dx[j] += s;
+}
+__global__ void outer_acc_kernel(float* da, const float* __restrict__ y, const float* __restrict__ dout, int m, int k) {
+  int64_t n = (int64_t)m * k;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) da[i] += y[i % k] * dout[i / k];
+}
+__global__ void dot_kernel(const float* __restrict__ x, const float* __restrict__ y, float* out, int n) {
+  float s = 0.0f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) s += x[i] * y[i];
+  s = block_sum(s);
+  if (threadIdx.x == 0) out[0] = s;
+}
+__global__ void axpy_from_scalar_kernel(float* dx, const float* __restrict__ y, const float* __restrict__ a, int n) {
+  float av = a[0];
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) dx[i] += av * y[i];
+}
+
+static int full_sum(const float* x, float* out, int64_t n, float scale) {
+  if (n <= (1 << 16)) { LTB_LAUNCH(sum_kernel, 1, 1024, 0, x, out, n, scale, false); return LTB_OK; }
+  int blocks = grid_for(n, 1024, 2);
+  LTB_LAUNCH(sum_kernel, blocks, 1024, 0, x, g.scratch, n, 1.0f, true);
+  LTB_LAUNCH(sum_kernel, 1, 1024, 0, (const float*)g.scratch, out, (int64_t)blocks, scale, false);
+  return LTB_OK;
+}
+
+}  // namespace ltb
+
+using namespace ltb;
+
+extern "C" {
+
+// sum / mean and their grads: TensorDslCPU.scala:1115-1124.
+int ltb_sum(const float* x, float* out, int64_t n) { LTB_INITED(); LTB_REQUIRE(x && out && n >= 0, "ltb_sum: bad argument"); return full_sum(x, out, n, 1.0f); }
+int ltb_mean(const float* x, float* out, int64_t n) { LTB_INITED(); LTB_REQUIRE(x && out && n > 0, "ltb_mean: bad argument"); return full_sum(x, out, n, 1.0f / (float)n); }
+int ltb_sum_grad(float* dx, const float* dout, int64_t n) {
+  LTB_INITED(); LTB_REQUIRE(dx && dout && n >= 0, "ltb_sum_grad: bad argument");
+  if (n) LTB_LAUNCH(add_scalar_from_kernel, grid_for(n, 256), 256, 0, dx, dout, 1.0f, n);
+  return LTB_OK;
+}
+int ltb_mean_grad(float* dx, const float* dout, int64_t n) {
+  LTB_INITED(); LTB_REQUIRE(dx && dout && n > 0, "ltb_mean_grad: bad argument");
+  LTB_LAUNCH(add_scalar_from_kernel, grid_for(n, 256), 256, 0, dx, dout, 1.0f / (float)n, n);
+  return LTB_OK;
+}
+// sum(dim) / sum_grad(dim): TensorDslCPU.scala:1125-1164.
+int ltb_sum_dim(const float* x, float* out, int outer, int d, int inner) {
+  LTB_INITED(); LTB_REQUIRE(x && out && outer > 0 && d > 0 && inner > 0, "ltb_sum_dim: bad argument");
+  if (inner == 1) LTB_LAUNCH(sum_lastdim_kernel, (unsigned)ceil_div((int64_t)outer * 32, 256), 256, 0, x, out, outer, d);
+  else LTB_LAUNCH(sum_dim_kernel, grid_for((int64_t)outer * inner, 256), 256, 0, x, out, outer, d, inner);
+  return LTB_OK;
+}
+int ltb_sum_dim_grad(float* dx, const float* dout, int outer, int d, int inner) {
+  LTB_INITED(); LTB_REQUIRE(dx && dout && outer > 0 && d > 0 && inner > 0, "ltb_sum_dim_grad: bad argument");
+  LTB_LAUNCH(sum_dim_grad_kernel, grid_for((int64_t)outer * d * inner, 256), 256, 0, dx, dout, outer, d, inner);
+  return LTB_OK;
+}
+
+// softmax / logSoftmax and grads: TensorDslCPU.scala:783-846.
+int ltb_softmax(const float* x, float* y, int rows, int cols) {
+  LTB_INITED(); LTB_REQUIRE(x && y && rows > 0 && cols > 0, "ltb_softmax: bad argument");
+  LTB_LAUNCH(softmax_kernel<0>, (unsigned)ceil_div((int64_t)rows * 32, 256), 256, 0, x, y, rows, cols); return LTB_OK;
+}
+int ltb_log_softmax(const float* x, float* y, int rows, int cols) {
+  LTB_INITED(); LTB_REQUIRE(x && y && rows > 0 && cols > 0, "ltb_log_softmax: bad argument");
+  LTB_LAUNCH(softmax_kernel<1>, (unsigned)ceil_div((int64_t)rows * 32, 256), 256, 0, x, y, rows, cols); return LTB_OK;
+}
+int ltb_softmax_grad(float* dx, const float* y, const float* dy, int rows, int cols) {
+  LTB_INITED(); LTB_REQUIRE(dx && y && dy && rows > 0 && cols > 0, "ltb_softmax_grad: bad argument");
+  LTB_LAUNCH(softmax_grad_kernel<0>, (unsigned)ceil_div((int64_t)rows * 32, 256), 256, 0, dx, y, dy, rows, cols); return LTB_OK;
+}
+int ltb_log_softmax_grad(float* dx, const float* y, const float* dy, int rows, int cols) {
+  LTB_INITED(); LTB_REQUIRE(dx && y && dy && rows > 0 && cols > 0, "ltb_log_softmax_grad: bad argument");
+  LTB_LAUNCH(softmax_grad_kernel<1>, (unsigned)ceil_div((int64_t)rows * 32, 256), 256, 0, dx, y, dy, rows, cols); return LTB_OK;
+}
+// nllLoss / nllLoss_grad: TensorDslCPU.scala:1090-1110.
+int ltb_nll(const float* x, const int32_t* t, float* out, int rows, int cols) {
+  LTB_INITED(); LTB_REQUIRE(x && t && out && rows > 0 && cols > 0, "ltb_nll: bad argument");
+  LTB_LAUNCH(nll_kernel, (rows + 127) / 128, 128, 0, x, t, out, rows, cols); return LTB_OK;
+}
+int ltb_nll_grad(float* dx, const float* dout, const int32_t* t, int rows, int cols) {
+  LTB_INITED(); LTB_REQUIRE(dx && dout && t && rows > 0 && cols > 0, "ltb_nll_grad: bad argument");
+  LTB_LAUNCH(nll_grad_kernel, (rows + 127) / 128, 128, 0, dx, dout, t, rows, cols); return LTB_OK;
+}
+
+// vectorVectorDot / matrixVectorDot and the (1,1), (2,1) cases of dot_grad: TensorDslCPU.scala:135-206.
+int ltb_vv_dot(const float* x, const float* y, float* out, int n) {
+  LTB_INITED(); LTB_REQUIRE(x && y && out && n > 0, "ltb_vv_dot: bad argument");
+  LTB_LAUNCH(dot_kernel, 1, 1024, 0, x, y, out, n); return LTB_OK;
+}
+int ltb_vv_dot_grad(float* dx, float* dy, const float* x, const float* y, const float* dout, int n) {
+  LTB_INITED(); LTB_REQUIRE(x && y && dout && n > 0, "ltb_vv_dot_grad: bad argument");
+  if (dx) LTB_LAUNCH(axpy_from_scalar_kernel, grid_for(n, 256), 256, 0, dx, y, dout, n);
+  if (dy) LTB_LAUNCH(axpy_from_scalar_kernel, grid_for(n, 256), 256, 0, dy, x, dout, n);
+  return LTB_OK;
+}
+int ltb_mv_dot(const float* a, const float* x, float* out, int m, int k) {
+  LTB_INITED(); LTB_REQUIRE(a && x && out && m > 0 && k > 0, "ltb_mv_dot: bad argument");
+  LTB_LAUNCH(gemv_rows_kernel<false>, (unsigned)ceil_div((int64_t)m * 32, 256), 256, 0, a, x, out, m, k); return LTB_OK;
+}
+int ltb_add_cartesian(float* da, const float* y, const float* dout, int m, int k) {
+  LTB_INITED(); LTB_REQUIRE(da && y && dout && m > 0 && k > 0, "ltb_add_cartesian: bad argument");
+  LTB_LAUNCH(outer_acc_kernel, grid_for((int64_t)m * k, 256), 256, 0, da, y, dout, m, k); return LTB_OK;
+}
+int ltb_add_composition(float* dx, const float* a, const float* dout, int m, int k) {
+  LTB_INITED(); LTB_REQUIRE(dx && a && dout && m > 0 && k > 0, "ltb_add_composition: bad argument");
+  LTB_LAUNCH(gemv_cols_kernel, (k + 127) / 128, 128, 0, a, dout, dx, m, k); return LTB_OK;
+}
+
+}  // extern "C"

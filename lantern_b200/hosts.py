@@ -19,6 +19,7 @@ _SIGS = {
     "model_slab_grads": (ctypes.c_void_p, [ctypes.c_void_p]),
     "model_input_count": (ctypes.c_int64, [ctypes.c_void_p]),
     "model_use_graph": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int]),
+    "model_set_resident": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]),
     "model_step": (ctypes.c_float, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_float, ctypes.c_int]),
     "model_step_async": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_float]),
     "model_last_loss": (ctypes.c_float, [ctypes.c_void_p]),
@@ -72,6 +73,14 @@ class Model:
 
     def last_loss(self):
         return float(self.hp.fn["model_last_loss"](self.h))
+
+    def set_resident(self, x=None, y=None):
+        """Keep one batch in device memory (steps then upload nothing); None switches back to per-step uploads."""
+        if x is None:
+            self.hp.fn["model_set_resident"](self.h, None, None)
+            return
+        x, y = self._arrs(x, y)
+        self.hp.fn["model_set_resident"](self.h, x.ctypes.data, y.ctypes.data)
 
     def use_graph(self, on=True):
         self.hp.fn["model_use_graph"](self.h, int(on))

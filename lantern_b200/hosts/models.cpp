@@ -45,6 +45,8 @@ struct Model {
   void* graph = nullptr;
   bool use_graph = false;
   float graph_lr = 0.f;
+  bool resident = false;       // read the batch from dev_x/dev_y instead of uploading it
+  float* dev_x = nullptr; int32_t* dev_y = nullptr;
 
   int declare(std::initializer_list<int> shape, int init, float scale = 0.f) {
     ParamDecl d; d.shape.assign(shape.begin(), shape.end()); d.init = init; d.scale = scale;
@@ -73,6 +75,8 @@ struct Model {
     stage_x = (float*)BK(host_alloc)((size_t)batch * in_c * in_h * in_w * 4);
     stage_y = (int32_t*)BK(host_alloc)((size_t)batch * 4);
     loss_host = (float*)BK(host_alloc)(4);
+    dev_x = alloc_value((int64_t)batch * in_c * in_h * in_w);
+    dev_y = (int32_t*)BK(malloc_uninit)((size_t)batch * 4);
     mark = BK(mark)();
   }
   virtual TR forward(Tape& t, const TR& x, const int32_t* y) = 0;
@@ -82,10 +86,15 @@ struct Model {
     Tape tape;
     int64_t nin = (int64_t)batch * in_c * in_h * in_w;
     TR x; x.rank = 4; x.shape[0] = batch; x.shape[1] = in_c; x.shape[2] = in_h; x.shape[3] = in_w; x.is_input = true;
-    x.x = alloc_value(nin);
-    int32_t* y = (int32_t*)BK(malloc_uninit)((size_t)batch * 4);
-    BK(h2d)(x.x, stage_x, (size_t)nin * 4);
-    BK(h2d)(y, stage_y, (size_t)batch * 4);
+    int32_t* y;
+    if (resident) {           // batch already in device memory (measurement of the device-side step alone)
+      x.x = dev_x; y = dev_y;
+    } else {                  // the generated programs upload every batch: resnet50FromOnnx.scala:173-174
+      x.x = alloc_value(nin);
+      y = (int32_t*)BK(malloc_uninit)((size_t)batch * 4);
+      BK(h2d)(x.x, stage_x, (size_t)nin * 4);
+      BK(h2d)(y, stage_y, (size_t)batch * 4);
+    }
     TR loss = forward(tape, x, y);
     BK(fill)(loss.d, 1.0f, 1);                       // gradR_loss: y.d.setAsOne(), TD.scala:1763-1780
     float* loss_copy = alloc_value(1);
@@ -103,7 +112,7 @@ struct Model {
     memcpy(stage_y, yh, (size_t)batch * 4);
   }
   int step_async(const float* xh, const int32_t* yh, float lr, bool update) {
-    load(xh, yh);
+    if (!resident) load(xh, yh);
     if (use_graph && update) {
       if (graph && graph_lr != lr) { BK(graph_destroy)(graph); graph = nullptr; }
       if (!graph) {
@@ -261,6 +270,18 @@ float* HOST_FN(model_slab_params)(void* m) { return ((Model*)m)->slab_x; }
 float* HOST_FN(model_slab_grads)(void* m) { return ((Model*)m)->slab_d; }
 int64_t HOST_FN(model_input_count)(void* m) { Model* M = (Model*)m; return (int64_t)M->batch * M->in_c * M->in_h * M->in_w; }
 int HOST_FN(model_use_graph)(void* m, int on) { ((Model*)m)->use_graph = on != 0; return 0; }
+// Keep one batch resident in device memory; later steps read it there and upload nothing (x_host/y_host are ignored).
+int HOST_FN(model_set_resident)(void* m, const float* x_host, const int32_t* y_host) {
+  Model* M = (Model*)m;
+  if (M->graph) { BK(graph_destroy)(M->graph); M->graph = nullptr; }
+  if (!x_host) { M->resident = false; return 0; }
+  M->load(x_host, y_host);
+  BK(h2d)(M->dev_x, M->stage_x, (size_t)M->batch * M->in_c * M->in_h * M->in_w * 4);
+  BK(h2d)(M->dev_y, M->stage_y, (size_t)M->batch * 4);
+  BK(sync)();
+  M->resident = true;
+  return 0;
+}
 // Blocking step: returns the loss of this batch. update=0 leaves the parameter gradients in place for inspection.
 float HOST_FN(model_step)(void* m, const float* x_host, const int32_t* y_host, float lr, int update) {
   return ((Model*)m)->step(x_host, y_host, lr, update != 0);

@@ -814,4 +814,6 @@ int ora_graph_begin(void) { return fail(LTB_E_ARG, "the CPU oracle does not reco
 void* ora_graph_end(void) { return nullptr; }
 int ora_graph_launch(void*) { return fail(LTB_E_ARG, "the CPU oracle does not record steps"); }
 int ora_graph_destroy(void*) { return LTB_OK; }
+int ora_profile(int) { return LTB_OK; }
+int ora_profile_report(char* buf, int len) { if (buf && len > 0) buf[0] = 0; return LTB_OK; }
 }

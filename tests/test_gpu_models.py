@@ -1,0 +1,96 @@
+"""Whole-step parity: the same host program (lantern_b200/hosts) on the CPU oracle and on the CUDA library must give
+the same loss and the same gradient for every parameter tensor on the same seeded weights and batch."""
+import os
+
+import numpy as np
+import pytest
+
+from tests.parity import FP32_RTOL, TF32_RTOL, assert_close
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+ORA_HOSTS = os.path.join(ROOT, "oracle", "liblantern_oracle_hosts.so")
+
+
+def _pair(oracle_lib, cuda_lib, name, batch):
+    from lantern_b200.hosts import HostPrograms
+    mo = HostPrograms(oracle_lib, ORA_HOSTS, "orah_").model(name, batch, seed=42)
+    mg = HostPrograms(cuda_lib).model(name, batch, seed=42)
+    assert mo.slab_count == mg.slab_count
+    np.testing.assert_array_equal(mo.slab_params(), mg.slab_params())      # same rand() stream on both sides
+    return mo, mg
+
+
+def _batch(model, seed, kind):
+    rng = np.random.default_rng(seed)
+    n = model.input_count
+    x = rng.random(n, dtype=np.float32) if kind == "uniform" else rng.standard_normal(n).astype(np.float32)
+    if kind == "uniform":
+        x = (x - np.float32(0.1307)) / np.float32(0.3081)
+    return x, rng.integers(0, 10, model.batch).astype(np.int32)
+
+
+@pytest.mark.parametrize("name,batch,kind,math,rtol", [
+    ("mnist", 100, "uniform", 0, FP32_RTOL), ("squeezenet", 8, "normal", 0, 3e-4), ("resnet50", 8, "normal", 0, 1e-3),
+    ("mnist", 100, "uniform", 1, TF32_RTOL), ("squeezenet", 8, "normal", 1, TF32_RTOL), ("resnet50", 8, "normal", 1, 5e-3)])
+def test_step_loss_and_every_gradient(oracle_lib, cuda_lib, name, batch, kind, math, rtol):
+    mo_mark, mg_mark = oracle_lib.mark(), cuda_lib.mark()
+    cuda_lib.set_math(math)
+    mo, mg = _pair(oracle_lib, cuda_lib, name, batch)
+    x, y = _batch(mo, 7, kind)
+    import ctypes
+    libc = ctypes.CDLL(None)
+    libc.srand(123); lo = mo.step(x, y, 0.0, update=False)
+    libc.srand(123); lg = mg.step(x, y, 0.0, update=False)
+    assert abs(lo - lg) <= rtol * max(1.0, abs(lo)), (lo, lg)
+    worst = 0.0
+    for i in range(mo.num_params):
+        go, gg = mo.grad(i), mg.grad(i)
+        if not go.any() and not gg.any():
+            continue                                              # running statistics: gradient stays zero
+        assert_close(go, gg, rtol, "%s grad %d" % (name, i))
+    # one update step, then the parameters must agree too
+    libc.srand(5); mo.step(x, y, 0.01); libc.srand(5); mg.step(x, y, 0.01)
+    assert_close(mo.slab_params(), mg.slab_params(), rtol, "params after update")
+    assert not mg.slab_grads().any()
+    mo.close(); mg.close()
+    cuda_lib.set_math(1)
+    oracle_lib.reset(mo_mark); cuda_lib.reset(mg_mark)
+
+
+def test_training_trajectory_and_graph_replay(oracle_lib, cuda_lib):
+    """Ten SGD steps of the MNIST program: oracle vs CUDA; then the ResNet-50 step replayed from a recorded graph
+    must reproduce the eagerly issued step bit for bit."""
+    import ctypes
+    from lantern_b200.hosts import HostPrograms
+    libc = ctypes.CDLL(None)
+    mo_mark, mg_mark = oracle_lib.mark(), cuda_lib.mark()
+    cuda_lib.set_math(0)
+    mo, mg = _pair(oracle_lib, cuda_lib, "mnist", 100)
+    lo, lg = [], []
+    for m, out in ((mo, lo), (mg, lg)):
+        libc.srand(9)
+        for s in range(10):
+            x, y = _batch(m, s, "uniform")
+            out.append(m.step(x, y, 0.0005))
+    assert np.allclose(lo, lg, rtol=2e-4), (lo, lg)
+    mo.close(); mg.close()
+    cuda_lib.set_math(1)
+    oracle_lib.reset(mo_mark); cuda_lib.reset(mg_mark)
+
+    hp = HostPrograms(cuda_lib)
+    eager, replay = hp.model("resnet50", 4, seed=1), hp.model("resnet50", 4, seed=1)
+    replay.use_graph(True)
+    le, lr_ = [], []
+    for s in range(3):
+        x, y = _batch(eager, s, "normal")
+        le.append(eager.step(x, y, 0.05))
+    before = cuda_lib.kernel_launches()
+    for s in range(3):
+        x, y = _batch(replay, s, "normal")
+        replay.step_async(x, y, 0.05); cuda_lib.sync(); lr_.append(replay.last_loss())
+    assert cuda_lib.kernel_launches() > before
+    assert le == lr_, (le, lr_)
+    np.testing.assert_array_equal(eager.slab_params(), replay.slab_params())
+    eager.close(); replay.close()
+    cuda_lib.reset(mg_mark)

@@ -1,0 +1,287 @@
+"""Op-by-op parity of the CUDA library against the CPU oracle on seeded inputs, through the C ABI.
+FP32 paths: 1e-4 relative; TF32 tensor-core paths: 2e-3 relative; indices bit-exact."""
+import numpy as np
+import pytest
+
+from lantern_b200.backend import TensorR
+from tests.golden.reference_known_answers import CASES
+from tests.parity import FP32_RTOL, TF32_RTOL, check
+
+pytestmark = pytest.mark.gpu
+R = lambda seed: np.random.default_rng(seed)
+
+
+@pytest.mark.parametrize("case", CASES, ids=[c.__name__ for c in CASES])
+def test_reference_known_answers_on_gpu(gpu, case):
+    case(gpu)
+
+
+@pytest.mark.parametrize("n", [1, 3, 4, 7, 1023, 4096, 100003])
+@pytest.mark.parametrize("op", range(7))
+def test_unary_and_grad(ora, gpu, n, op):
+    v = R(n + op).random(n, dtype=np.float32) * 3 - (1.5 if op < 3 else -0.05)
+    dy = R(1).standard_normal(n).astype(np.float32)
+
+    def f(b):
+        x = TensorR(b.fromNumpy(v))
+        y = b._unary(op, x.x)
+        b._unary_grad(op, x, TensorR(y, b.fromNumpy(dy)))
+        return {"y": y.toCPU(), "dx": x.d.toCPU()}
+    check(f, ora, gpu)
+
+
+def test_relu_in_place_and_unaligned_views(ora, gpu):
+    v = R(5).standard_normal(1001).astype(np.float32)
+
+    def f(b):
+        t = b.fromNumpy(v)
+        view = t.offset(1, (1000,))                      # 4-byte aligned only: scalar path
+        b.relu(view, True)
+        x = TensorR(view, b.fromNumpy(np.ones(1000, np.float32)))
+        b.relu_grad(x, x, True)
+        return {"y": t.toCPU(), "d": x.d.toCPU()}
+    check(f, ora, gpu)
+
+
+SHAPES = [((2, 3), (2, 3)), ((2, 3), (2, 1)), ((2, 3), (1, 3)), ((2, 3), (3,)), ((4, 5, 6, 7), (5, 1, 1)), ((4, 5, 6, 7), (4, 5, 6, 7)),
+          ((1, 5, 1, 7), (4, 1, 6, 1)), ((128, 10), (10,)), ((3, 1), (1, 4)), ((37, 64, 4, 4), (37, 64, 4, 4))]
+
+
+@pytest.mark.parametrize("sa,sb", SHAPES)
+@pytest.mark.parametrize("op", range(4))
+def test_broadcast_binary_and_grad(ora, gpu, sa, sb, op):
+    a = R(1).random(sa, dtype=np.float32) + 0.5
+    c = R(2).random(sb, dtype=np.float32) + 0.5
+
+    def f(b):
+        A, C = TensorR(b.fromNumpy(a)), TensorR(b.fromNumpy(c))
+        out, xs, ys = b._binary(op, A.x, C.x)
+        dout = b.fromNumpy(R(3).standard_normal(out.shape).astype(np.float32))
+        b._binary_grad(op, A, C, TensorR(out, dout))
+        return {"out": out.toCPU(), "da": A.d.toCPU(), "db": C.d.toCPU()}
+    check(f, ora, gpu, rtol=2e-4 if op == 3 else FP32_RTOL)
+
+
+@pytest.mark.parametrize("xs,ys", [((4, 6), (4, 6)), ((4, 6), (6,)), ((6,), (4, 6)), ((1, 5, 1, 1), (3, 5, 2, 2)), ((3, 5, 2, 2), (1, 5, 1, 1)),
+                                   ((10,), (128, 10)), ((4, 1), (4, 9))])
+@pytest.mark.parametrize("op", range(4))
+def test_inplace_broadcast_or_reduce(ora, gpu, xs, ys, op):
+    x0 = R(1).random(xs, dtype=np.float32) + 0.5
+    y0 = R(2).random(ys, dtype=np.float32) * 0.2 + 0.9
+
+    def f(b):
+        x = b.fromNumpy(x0)
+        b._inplace(op, x, b.fromNumpy(y0))
+        b._inplace(op, x, 1.25)
+        return {"x": x.toCPU(), "s": b._binary(op, x, 0.75).toCPU()}
+    check(f, ora, gpu, rtol=5e-4 if op >= 2 else FP32_RTOL)
+
+
+@pytest.mark.parametrize("ta,tb", [(0, 0), (0, 1), (1, 0), (1, 1)])
+@pytest.mark.parametrize("M,N,K", [(2, 4, 3), (100, 50, 320), (128, 10, 2048), (65, 129, 33), (256, 100, 100), (1, 80, 100)])
+def test_gemm_and_grad_fp32(ora, gpu, ta, tb, M, N, K):
+    a = R(1).standard_normal((K, M) if ta else (M, K)).astype(np.float32)
+    c = R(2).standard_normal((N, K) if tb else (K, N)).astype(np.float32)
+    dc = R(3).standard_normal((M, N)).astype(np.float32)
+
+    def f(b):
+        b.lib.set_math(0)
+        A, C = TensorR(b.fromNumpy(a)), TensorR(b.fromNumpy(c))
+        out = b.gemm(A.x, ta, C.x, tb, 0.5)
+        b.gemm_grad(A, ta, C, tb, 0.5, TensorR(out, b.fromNumpy(dc)))
+        b.lib.set_math(1)
+        return {"out": out.toCPU(), "da": A.d.toCPU(), "db": C.d.toCPU()}
+    check(f, ora, gpu)
+
+
+@pytest.mark.parametrize("m,k,n", [(100, 320, 50), (20, 50, 26), (7, 5, 3)])
+def test_dot_family(ora, gpu, m, k, n):
+    a, bm, v = (R(i).standard_normal(s).astype(np.float32) for i, s in enumerate(((m, k), (k, n), (k,))))
+
+    def f(b):
+        b.lib.set_math(0)
+        A, Bm, V = TensorR(b.fromNumpy(a)), TensorR(b.fromNumpy(bm)), TensorR(b.fromNumpy(v))
+        mm = b.dot(A.x, Bm.x); b.dot_grad(A, Bm, TensorR(mm, b.fromNumpy(R(9).standard_normal((m, n)).astype(np.float32))))
+        mv = b.dot(A.x, V.x); b.dot_grad(A, V, TensorR(mv, b.fromNumpy(R(8).standard_normal(m).astype(np.float32))))
+        V2 = TensorR(b.fromNumpy(v * 2))
+        vv = b.dot(V.x, V2.x); b.dot_grad(V, V2, TensorR(vv, b.fromNumpy(np.array([0.7], np.float32))))
+        b.lib.set_math(1)
+        return {"mm": mm.toCPU(), "mv": mv.toCPU(), "vv": vv.toCPU(), "dA": A.d.toCPU(), "dB": Bm.d.toCPU(), "dV": V.d.toCPU(), "dV2": V2.d.toCPU()}
+    check(f, ora, gpu)
+
+
+CONVS = [  # N, C, H, W, K, R, stride, pad, bias
+    (2, 1, 28, 28, 10, 5, 1, 0, True), (2, 10, 12, 12, 20, 5, 1, 0, True), (3, 3, 32, 32, 64, 3, 1, 1, False),
+    (2, 64, 16, 16, 64, 1, 1, 0, False), (2, 64, 16, 16, 64, 3, 1, 1, False), (2, 128, 16, 16, 128, 3, 2, 1, False),
+    (2, 256, 16, 16, 512, 1, 2, 0, False), (4, 512, 4, 4, 10, 4, 1, 0, True), (2, 16, 9, 7, 24, 3, 2, 1, True),
+    (1, 5, 6, 6, 7, 2, 3, 1, True)]
+
+
+@pytest.mark.parametrize("cfg", CONVS, ids=[str(c) for c in CONVS])
+def test_conv_fwd_bwd_fp32(ora, gpu, cfg):
+    N, C, H, W, K, Rk, s, p, has_bias = cfg
+    x0 = R(1).standard_normal((N, C, H, W)).astype(np.float32)
+    w0 = (R(2).standard_normal((K, C, Rk, Rk)) / np.sqrt(C * Rk * Rk)).astype(np.float32)
+    b0 = R(3).standard_normal(K).astype(np.float32)
+
+    def f(b):
+        b.lib.set_math(0)
+        x, w = TensorR(b.fromNumpy(x0)), TensorR(b.fromNumpy(w0))
+        bias = TensorR(b.fromNumpy(b0)) if has_bias else None
+        y, _, _ = b.conv2D_batch(x.x, w.x, bias.x if bias else None, (s, s), (p, p, p, p))
+        dy = b.fromNumpy(R(4).standard_normal(y.shape).astype(np.float32))
+        b.conv2D_batch_grad(x, None, w, TensorR(y, dy), bias, (p, p), (s, s))
+        b.lib.set_math(1)
+        out = {"y": y.toCPU(), "dx": x.d.toCPU(), "dw": w.d.toCPU()}
+        if bias:
+            out["db"] = bias.d.toCPU()
+        return out
+    check(f, ora, gpu)
+
+
+@pytest.mark.parametrize("cfg", [(2, 3, 8, 8, 2, 2, 0), (2, 3, 9, 7, 3, 2, 1), (4, 16, 32, 32, 2, 2, 0), (1, 1, 3, 3, 2, 1, 0), (3, 5, 6, 10, 2, 2, 0)])
+def test_maxpool_indices_bit_exact(ora, gpu, cfg):
+    N, C, H, W, k, s, pad = cfg
+    v = np.round(R(1).standard_normal((N, C, H, W)) * 2).astype(np.float32) / 2      # many ties
+
+    def f(b):
+        x = TensorR(b.fromNumpy(v))
+        y, idx = b.maxPool2D_batch(x.x, (k, k), (s, s), None if pad == 0 else (pad,) * 4)
+        b.maxPool2D_batch_grad(x, TensorR(y, b.fromNumpy(R(2).standard_normal(y.shape).astype(np.float32))), idx)
+        return {"y": y.toCPU(), "idx": idx.toCPU(), "dx": x.d.toCPU()}
+    check(f, ora, gpu, exact=("idx", "y"))
+
+
+@pytest.mark.parametrize("cfg", [(2, 3, 4, 4, 2, 2), (2, 3, 4, 4, 2, 1), (8, 2048, 2, 2, 2, 1), (1, 2, 7, 5, 3, 2)])
+def test_avgpool(ora, gpu, cfg):
+    N, C, H, W, k, s = cfg
+    v = R(1).standard_normal((N, C, H, W)).astype(np.float32)
+
+    def f(b):
+        x = TensorR(b.fromNumpy(v))
+        y = b.averagePool2D_batch(x.x, (k, k), (s, s))
+        b.averagePool2D_batch_grad(x, TensorR(y, b.fromNumpy(R(2).standard_normal(y.shape).astype(np.float32))), (k, k), (s, s))
+        return {"y": y.toCPU(), "dx": x.d.toCPU()}
+    check(f, ora, gpu)
+
+
+@pytest.mark.parametrize("cfg", [(3, 2, 3, 3), (16, 64, 16, 16), (8, 256, 4, 4), (32, 512, 2, 2), (5, 7, 3, 5), (128, 10, 1, 1)])
+def test_batchnorm_train_fwd_bwd(ora, gpu, cfg):
+    N, C, H, W = cfg
+    v = (R(1).standard_normal((N, C, H, W)) * 2 + 3).astype(np.float32)      # non-zero mean: exercises the shifted sums
+    g0, b0 = (R(2).random(C, dtype=np.float32) + 0.5), R(3).standard_normal(C).astype(np.float32)
+
+    def f(b):
+        x = TensorR(b.fromNumpy(v))
+        scale, bias = TensorR(b.fromNumpy(g0)), TensorR(b.fromNumpy(b0))
+        rm, rv = b.fill((C,), 0.0), b.fill((C,), 1.0)
+        y, sm, si, _ = b.batchNormTraining(x.x, scale.x, bias.x, rm, rv)
+        b.batchNorm_grad(x, TensorR(y, b.fromNumpy(R(4).standard_normal(v.shape).astype(np.float32))), scale, bias, sm, si)
+        yi = b.batchNormInference(x.x, scale.x, bias.x, rm, rv)
+        return {"y": y.toCPU(), "mean": sm.toCPU(), "istd": si.toCPU(), "rm": rm.toCPU(), "rv": rv.toCPU(), "dx": x.d.toCPU(),
+                "dgamma": scale.d.toCPU(), "dbeta": bias.d.toCPU(), "yi": yi.toCPU()}
+    check(f, ora, gpu, rtol=2e-4)
+
+
+@pytest.mark.parametrize("rows,cols", [(2, 3), (128, 10), (100, 10), (20, 80), (1, 5), (7, 1000)])
+def test_softmax_family_and_nll(ora, gpu, rows, cols):
+    v = (R(1).standard_normal((rows, cols)) * 3).astype(np.float32)
+    t = R(2).integers(0, cols, rows).astype(np.int32)
+
+    def f(b):
+        x, x2 = TensorR(b.fromNumpy(v)), TensorR(b.fromNumpy(v))
+        tgt = b.fromNumpy(t)
+        ls = TensorR(b.logSoftmax(x.x))
+        loss = b.nllLoss(ls.x, tgt)
+        total, avg = b.sum(loss), b.mean(loss)
+        L = TensorR(loss)
+        b.sum_grad(L, TensorR(total, b.fill((1,), 1.0))); b.mean_grad(L, TensorR(avg, b.fill((1,), 2.0)))
+        b.nllLoss_grad(ls, L, tgt); b.logSoftmax_grad(x, ls)
+        sm = b.softmax(x2.x)
+        b.softmax_grad(x2, TensorR(sm, b.fromNumpy(R(3).standard_normal(v.shape).astype(np.float32))))
+        return {"ls": ls.x.toCPU(), "loss": loss.toCPU(), "sum": total.toCPU(), "mean": avg.toCPU(), "dx": x.d.toCPU(),
+                "sm": sm.toCPU(), "dx2": x2.d.toCPU()}
+    check(f, ora, gpu, rtol=2e-4)
+
+
+def test_reductions_concat_trans_geam(ora, gpu):
+    v = R(1).standard_normal((6, 5, 8)).astype(np.float32)
+    big = R(2).standard_normal(300001).astype(np.float32)
+
+    def f(b):
+        x = TensorR(b.fromNumpy(v))
+        out = {"sum_big": b.sum(b.fromNumpy(big)).toCPU()}
+        for d in range(3):
+            s = b.sum(x.x, d); out["sum%d" % d] = s.toCPU()
+            b.sum_grad(x, TensorR(s, b.fromNumpy(R(3 + d).standard_normal(s.shape).astype(np.float32))), d)
+        out["dx"] = x.d.toCPU()
+        a4, c4 = R(7).standard_normal((3, 4, 5, 5)).astype(np.float32), R(8).standard_normal((3, 6, 5, 5)).astype(np.float32)
+        A, C = TensorR(b.fromNumpy(a4)), TensorR(b.fromNumpy(c4))
+        cat = b.concat(1, [A.x, C.x]); out["cat"] = cat.toCPU()
+        b.concat_grad(1, [A, C], TensorR(cat, b.fromNumpy(R(9).standard_normal(cat.shape).astype(np.float32))))
+        out["dA"], out["dC"] = A.d.toCPU(), C.d.toCPU()
+        m = TensorR(b.fromNumpy(R(10).standard_normal((37, 53)).astype(np.float32)))
+        t = b.trans(m.x); out["t"] = t.toCPU()
+        b.trans_grad(m, TensorR(t, b.fromNumpy(R(11).standard_normal((53, 37)).astype(np.float32)))); out["dm"] = m.d.toCPU()
+        o = b.empty(37, 53); b.geam(m.x, False, 0.3, m.d, False, -1.7, o); out["geam"] = o.toCPU()
+        o2 = b.empty(53, 37); b.geam(t, False, 2.0, m.x, True, 0.5, o2); out["geam_t"] = o2.toCPU()
+        fb = b.fillWithBias((2, 5, 3), b.fromNumpy(np.arange(5, dtype=np.float32)), 1); out["fb"] = fb.toCPU()
+        c = b.fromNumpy(R(12).standard_normal(1000).astype(np.float32) * 3); b.clipAt(c, 1.5); out["clip"] = c.toCPU()
+        return out
+    check(f, ora, gpu, rtol=3e-4)
+
+
+def test_dropout_and_randinit_follow_the_host_rand_stream(ora, gpu):
+    v = R(1).standard_normal(5000).astype(np.float32)
+
+    def f(b):
+        w = b.randinit((7, 11), 0.3, seed=42)
+        x = TensorR(b.fromNumpy(v))
+        y, mask, _ = b.dropout(x.x, 0.5)
+        b.dropout_grad(x, TensorR(y, b.fill(y.shape, 2.0)), 0.5, mask)
+        return {"w": w.toCPU(), "y": y.toCPU(), "mask": mask.toCPU(), "dx": x.d.toCPU()}
+    check(f, ora, gpu, exact=("w", "mask", "y"))
+
+
+def test_optimizers(ora, gpu):
+    n = 10007
+    x0, d0 = R(1).standard_normal(n).astype(np.float32), (R(2).standard_normal(n) * 3).astype(np.float32)
+
+    def f(b):
+        out = {}
+        p = TensorR(b.fromNumpy(x0), b.fromNumpy(d0)); b.sgd_step(p, 0.1); out["sgd_x"], out["sgd_d"] = p.x.toCPU(), p.d.toCPU()
+        p = TensorR(b.fromNumpy(x0), b.fromNumpy(d0)); h = b.zeros(n)
+        b.adagrad_update(p, h, 0.1, 1.0); p.d = b.fromNumpy(d0 * 0.5); b.adagrad_update(p, h, 0.1, 1.0)
+        out["ada_x"], out["ada_h"], out["ada_d"] = p.x.toCPU(), h.toCPU(), p.d.toCPU()
+        for nest in (0, 1):
+            p = TensorR(b.fromNumpy(x0), b.fromNumpy(d0)); m = b.zeros(n)
+            b.momentum_update(p, m, 0.05, 0.9, 5.0, nest); p.d = b.fromNumpy(d0); b.momentum_update(p, m, 0.05, 0.9, 5.0, nest)
+            out["mom%d_x" % nest], out["mom%d_m" % nest] = p.x.toCPU(), m.toCPU()
+        return out
+    check(f, ora, gpu)
+
+
+def test_arena_semantics_and_error_codes(gpu):
+    import lantern_b200
+    lib = gpu.lib
+    used = lib.arena_used()
+    p = lib.malloc(1000)
+    assert p % 256 == 0 and lib.arena_used() == used + 1024
+    z = np.empty(250, np.float32); lib.d2h(z.ctypes.data, p, 1000)
+    assert not z.any()                                   # zero on hand-out
+    lib.fill(p, 3.0, 250)
+    q = lib.malloc_uninit(8)
+    with pytest.raises(lantern_b200.LanternError):
+        lib.free(p, 1000)                                # not the newest block
+    lib.free(q, 8); lib.free(p, 1000)
+    p2 = lib.malloc(1000)
+    assert p2 == p
+    lib.d2h(z.ctypes.data, p2, 1000)
+    assert not z.any()                                   # zero again after reuse
+    with pytest.raises(lantern_b200.LanternError) as e:
+        lib.malloc(1 << 50)
+    assert e.value.code == -3
+    with pytest.raises(lantern_b200.LanternError) as e:
+        lib.gemm(0, 0, 0, 0, 1.0, 0, 4, 4, 4)
+    assert e.value.code == -2
+    assert lib.kernel_launches() > 0
