@@ -23,6 +23,7 @@ _SIGS = {
     "model_step": (ctypes.c_float, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_float, ctypes.c_int]),
     "model_step_async": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_float]),
     "model_last_loss": (ctypes.c_float, [ctypes.c_void_p]),
+    "model_trace": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_char_p, ctypes.c_int]),
 }
 
 
@@ -81,6 +82,17 @@ class Model:
             return
         x, y = self._arrs(x, y)
         self.hp.fn["model_set_resident"](self.h, x.ctypes.data, y.ctypes.data)
+
+    def trace(self, x, y):
+        """Debug: per-operator (index, count, shape, sum|x|, sum|d|) rows of one step without update."""
+        x, y = self._arrs(x, y)
+        buf = ctypes.create_string_buffer(1 << 20)
+        self.hp.fn["model_trace"](self.h, x.ctypes.data, y.ctypes.data, buf, 1 << 20)
+        rows = []
+        for line in buf.value.decode().strip().split("\n"):
+            p = line.split()
+            rows.append((int(p[0]), int(p[1]), p[2], float(p[3]), float(p[4])) + tuple(float(v) for v in p[5:]))
+        return rows
 
     def use_graph(self, on=True):
         self.hp.fn["model_use_graph"](self.h, int(on))

@@ -105,7 +105,25 @@ struct Model {
       if (BK(comm_world)() > 1) BK(allreduce_sgd_step)(slab_x, slab_d, lr, slab_count);
       else BK(sgd_step)(slab_x, slab_d, lr, slab_count);
     }
+    if (tracing()) dump_trace();
     BK(reset)(mark);
+  }
+  std::string trace_text;
+  // One line per operator output, in forward order: index, element count, sum|x|, sum|d| (read back before the reset).
+  void dump_trace() {
+    trace_text.clear();
+    std::vector<float> h;
+    int idx = 0;
+    for (const TR& t : trace_list()) {
+      int64_t n = t.count(); h.resize((size_t)n);
+      double ax = 0, ad = 0, minx = 1e30; long long nzx = 0, nzd = 0;
+      BK(d2h)(h.data(), t.x, (size_t)n * 4);
+      for (int64_t i = 0; i < n; ++i) { double v = std::fabs((double)h[i]); ax += v; if (v != 0) { ++nzx; if (v < minx) minx = v; } }
+      if (t.d) { BK(d2h)(h.data(), t.d, (size_t)n * 4); for (int64_t i = 0; i < n; ++i) { ad += std::fabs((double)h[i]); nzd += h[i] != 0; } }
+      char line[200]; snprintf(line, sizeof line, "%d %lld [%d,%d,%d,%d] %.9e %.9e %lld %lld %.3e\n", idx++, (long long)n, t.shape[0], t.shape[1], t.shape[2], t.shape[3], ax, ad, nzx, nzd, minx);
+      trace_text += line;
+    }
+    trace_list().clear();
   }
   void load(const float* xh, const int32_t* yh) {
     memcpy(stage_x, xh, (size_t)batch * in_c * in_h * in_w * 4);
@@ -291,5 +309,14 @@ int HOST_FN(model_step_async)(void* m, const float* x_host, const int32_t* y_hos
   return ((Model*)m)->step_async(x_host, y_host, lr, true);
 }
 float HOST_FN(model_last_loss)(void* m) { return *((Model*)m)->loss_host; }
+// Debug: run one step without update and write per-operator checksums (see Model::dump_trace) into buf.
+int HOST_FN(model_trace)(void* m, const float* x_host, const int32_t* y_host, char* buf, int len) {
+  Model* M = (Model*)m;
+  tracing() = true; trace_list().clear();
+  M->step(x_host, y_host, 0.0f, false);
+  tracing() = false;
+  strncpy(buf, M->trace_text.c_str(), len - 1); buf[len - 1] = 0;
+  return (int)M->trace_text.size();
+}
 
 }  // extern "C"

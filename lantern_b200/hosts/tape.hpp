@@ -34,11 +34,17 @@ struct TR {
 inline float* alloc_value(int64_t n) { return (float*)BK(malloc_uninit)((size_t)n * 4); }
 inline float* alloc_zero(int64_t n) { return (float*)BK(malloc)((size_t)n * 4); }
 
+// Debug trace: when on, every tensor an operator allocates is remembered so that a step can be dumped
+// (per-tensor checksums of value and gradient) and two libraries compared operator by operator.
+inline bool& tracing() { static bool on = false; return on; }
+inline std::vector<TR>& trace_list() { static std::vector<TR> v; return v; }
+inline TR traced(const TR& t) { if (tracing()) trace_list().push_back(t); return t; }
+
 inline TR make(std::initializer_list<int> shp, bool with_grad = true) {
   TR t; t.rank = (int)shp.size(); int i = 0; for (int s : shp) t.shape[i++] = s;
   t.x = alloc_value(t.count());
   if (with_grad) t.d = alloc_zero(t.count());
-  return t;
+  return traced(t);
 }
 inline TR view(const TR& t, std::initializer_list<int> shp) {   // Tensor.resize: same buffers, new shape
   TR v = t; v.rank = (int)shp.size(); int i = 0; for (int s : shp) v.shape[i++] = s; for (; i < 4; ++i) v.shape[i] = 1;
@@ -76,14 +82,14 @@ struct Tape {
       push([=] { BK(unary_grad)(LTB_RELU, in.x, in.d, in.x, in.d, n, 1); });
       return in;
     }
-    TR y = in; y.x = alloc_value(n); y.d = alloc_zero(n); y.is_input = false;
+    TR y = in; y.x = alloc_value(n); y.d = alloc_zero(n); y.is_input = false; traced(y);
     BK(unary)(LTB_RELU, in.x, y.x, n);
     push([=] { BK(unary_grad)(LTB_RELU, in.x, in.d, y.x, y.d, n, 0); });
     return y;
   }
   TR unary(int op, const TR& in) {     // tanh / sigmoid / exp / log, TD.scala:1252-1316
     int64_t n = in.count();
-    TR y = in; y.x = alloc_value(n); y.d = alloc_zero(n); y.is_input = false;
+    TR y = in; y.x = alloc_value(n); y.d = alloc_zero(n); y.is_input = false; traced(y);
     BK(unary)(op, in.x, y.x, n);
     push([=] { if (!in.is_input) BK(unary_grad)(op, in.x, in.d, y.x, y.d, n, 0); });
     return y;
@@ -116,7 +122,7 @@ struct Tape {
       s.r[i] = s.a[i] > s.b[i] ? s.a[i] : s.b[i];
     }
     TR y; y.rank = rank; for (int i = 0; i < rank; ++i) y.shape[i] = s.r[i];
-    y.x = alloc_value(y.count()); y.d = alloc_zero(y.count());
+    y.x = alloc_value(y.count()); y.d = alloc_zero(y.count()); traced(y);
     BK(ew_binary)(op, a.x, s.a, b.x, s.b, y.x, rank);
     push([=] { BK(ew_binary_grad)(op, a.x, a.is_input ? nullptr : a.d, s.a, b.x, b.is_input ? nullptr : b.d, s.b, y.d, rank); });
     return y;
