@@ -43,17 +43,18 @@ def build_all(force=False, verbose=False):
     os.makedirs(OBJ, exist_ok=True)
     headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))]
     headers.append(os.path.join(os.path.dirname(HERE), "include", "lantern_b200.h"))
-    sources = sorted(f for f in os.listdir(CSRC) if f.endswith(".cu"))
+    sources = sorted(f for f in os.listdir(CSRC) if f.endswith((".cu", ".cpp")))
     jobs = []
     for s in sources:
-        src, obj = os.path.join(CSRC, s), os.path.join(OBJ, s[:-3] + ".o")
+        stem = os.path.splitext(s)[0]
+        src, obj = os.path.join(CSRC, s), os.path.join(OBJ, stem + ".o")
         if force or _newer(obj, [src] + headers):
-            jobs.append(([NVCC] + NVCC_FLAGS + ["-c", src, "-o", obj], os.path.join(OBJ, s[:-3] + ".ptxas.log")))
+            jobs.append(([NVCC] + NVCC_FLAGS + ["-c", src, "-o", obj], os.path.join(OBJ, stem + ".ptxas.log")))
     with concurrent.futures.ThreadPoolExecutor(max_workers=8) as ex:
         for out in ex.map(lambda j: _run(*j), jobs):
             if verbose:
                 print(out)
-    objs = [os.path.join(OBJ, s[:-3] + ".o") for s in sources]
+    objs = [os.path.join(OBJ, os.path.splitext(s)[0] + ".o") for s in sources]
     if force or jobs or _newer(LIB, objs):
         _run([NVCC, "-shared", "-o", LIB] + objs + ["-ldl", "-lpthread"])
     hsrc = os.path.join(HERE, "hosts", "models.cpp")

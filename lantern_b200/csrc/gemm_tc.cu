@@ -1,8 +1,420 @@
-// TF32 tensor-core engine (placeholder routing: every problem is declined so the FP32 path runs).
+// TF32 tensor-core engine for sm_100a: one warp-specialised kernel for every dense contraction of the training step
+// (convolution forward / data-grad / weight-grad and gemm), driven by the plans of tc_plan.cpp.
+//
+//   warp 0      : TMA producer.  One lane issues cp.async.bulk.tensor loads of the A and B boxes of each k-iteration into a
+//                 4-stage shared-memory ring; completion is signalled on the stage's "full" mbarrier by byte count.
+//   warp 1      : owns the tensor memory (tcgen05.alloc / dealloc) and issues tcgen05.mma.kind::tf32 (M = 128, N = tile
+//                 width, K = 8) from one lane, four per stage, accumulating in TMEM; tcgen05.commit releases the stage
+//                 ("empty" mbarrier) and finally signals the epilogue.
+//   warps 2..5  : epilogue.  Each warp reads its 32-lane quarter of the accumulator with tcgen05.ld (32 columns at a time)
+//                 and writes the result: pixel-major for convolutions (a warp store covers 32 consecutive pixels of one
+//                 channel: 128 contiguous bytes), row-major for gemm / weight-grad; optional bias, alpha, accumulation,
+//                 and atomic accumulation under split-K.
+// Activations stay NCHW: the pixel index is the contiguous one, so the activation operand is fed M/N-major (tcgen05 allows
+// it for tf32) straight from the tensor with a 4-D tiled tensor map; no layout conversion pass exists.
+// Every mbarrier wait is bounded: after about a second it records a code in the library's device status word and the CTA
+// runs to its normal teardown (TMEM is released on every path).
+#include <cuda.h>
+
 #include "gemm.cuh"
+#include "tc_plan.h"
+
+extern "C" void* ltb_malloc_uninit(size_t bytes);
+extern "C" int ltb_free(void* p, size_t bytes);
+
 namespace ltb {
-int gemm_tc(const float*, bool, const float*, bool, float*, bool, int, int, int, float, bool) { return 0; }
-int conv_fwd_tc(const float*, const float*, const float*, float*, const ConvDims&) { return 0; }
-int conv_dgrad_tc(const float*, const float*, float*, const ConvDims&) { return 0; }
-int conv_wgrad_tc(const float*, const float*, float*, const ConvDims&) { return 0; }
+
+constexpr int kStages = 4;
+constexpr int kTcThreads = 192;
+constexpr long long kWaitCycles = 2000000000ll;    // bound of every spin wait (~1 s)
+
+struct TcOperandDev {
+  int t_div[5], t_mod[5], t_mul[5], k_div[5], k_mod[5], k_mul[5];
+  int rank, nk;
+  uint32_t stage_bytes, desc_lo, desc_hi;     // descriptor without the start address
+  uint32_t kstep_off[8];
+};
+struct TcParams {
+  TcOperandDev a, b;
+  int M, N, bn, k_iters, k_per_split, epilogue, accumulate, atomic;
+  uint32_t idesc;
+  float* out; const float* bias; float alpha;
+  long long pix_per_img, img_stride, chan_stride, ld;
+  int* status;
+  float* dump;                 // diagnostics: when set, CTA (0,0,0) copies its first stage (A then B) here before the first MMA
+};
+
+// ---- PTX wrappers ---------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+               : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait: false when it gave up (the code is recorded, the shared abort flag raised).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (!mbar_try_wait(bar, parity)) {
+    if (*abort_flag) return false;
+    if (clock64() - t0 > kWaitCycles) { *abort_flag = 1; atomicExch(status, code); return false; }
+  }
+  return true;
+}
+__device__ __forceinline__ void tma_load(const CUtensorMap* map, uint64_t* bar, void* dst, int rank, const int* c) {
+  const uint32_t d = smem_u32(dst), b = smem_u32(bar);
+  const uint64_t m = reinterpret_cast<uint64_t>(map);
+  if (rank == 2)
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(d), "l"(m), "r"(b), "r"(c[0]), "r"(c[1]) : "memory");
+  else if (rank == 3)
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+                 ::"r"(d), "l"(m), "r"(b), "r"(c[0]), "r"(c[1]), "r"(c[2]) : "memory");
+  else if (rank == 4)
+    asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+                 ::"r"(d), "l"(m), "r"(b), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3]) : "memory");
+  else
+    asm volatile("cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+                 ::"r"(d), "l"(m), "r"(b), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3]), "r"(c[4]) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_mma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+               ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, "
+      "%20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]),
+        "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]),
+        "=r"(r[31])
+      : "r"(taddr) : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void box_coords(const TcOperandDev& o, int tile, int kiter, int* c) {
+#pragma unroll
+  for (int d = 0; d < 5; ++d) c[d] = ((tile / o.t_div[d]) % o.t_mod[d]) * o.t_mul[d] + ((kiter / o.k_div[d]) % o.k_mod[d]) * o.k_mul[d];
+}
+
+// ---- the engine -------------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kTcThreads, 1)
+tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ TcParams P) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t full_bar[kStages];
+  __shared__ __align__(8) uint64_t empty_bar[kStages];
+  __shared__ __align__(8) uint64_t accum_bar;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m_tile = blockIdx.x, n_tile = blockIdx.y;
+  const int k_begin = blockIdx.z * P.k_per_split;
+  const int k_end = min(P.k_iters, k_begin + P.k_per_split);
+  const int n_iter = k_end - k_begin;
+
+  // stage buffers, aligned to the 1024-byte swizzle atom
+  uint8_t* stage_base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t stage_bytes = P.a.stage_bytes + P.b.stage_bytes;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    mbar_init(&accum_bar, 1);
+    abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"((uint32_t)P.bn) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0 && n_iter > 0) {
+      for (int it = 0; it < n_iter; ++it) {
+        const int s = it % kStages; const uint32_t ph = (uint32_t)(it / kStages) & 1u;
+        if (!mbar_wait(&empty_bar[s], ph ^ 1u, &abort_flag, P.status, 1)) break;
+        uint8_t* sa = stage_base + (size_t)s * stage_bytes; uint8_t* sb = sa + P.a.stage_bytes;
+        mbar_expect_tx(&full_bar[s], stage_bytes);
+        int c[5];
+        box_coords(P.a, m_tile, k_begin + it, c); tma_load(&map_a, &full_bar[s], sa, P.a.rank, c);
+        box_coords(P.b, n_tile, k_begin + it, c); tma_load(&map_b, &full_bar[s], sb, P.b.rank, c);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && n_iter > 0) {
+      bool ok = true;
+      for (int it = 0; it < n_iter && ok; ++it) {
+        const int s = it % kStages; const uint32_t ph = (uint32_t)(it / kStages) & 1u;
+        ok = mbar_wait(&full_bar[s], ph, &abort_flag, P.status, 2);
+        if (!ok) break;
+        tc_fence_after();
+        if (P.dump && it == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+          const float* src = reinterpret_cast<const float*>(stage_base);
+          for (uint32_t i = 0; i < stage_bytes / 4; ++i) P.dump[i] = src[i];
+        }
+        const uint32_t sa = smem_u32(stage_base + (size_t)s * stage_bytes), sb = sa + P.a.stage_bytes;
+        for (int k = 0; k < P.a.nk; ++k) {
+          const uint32_t aa = sa + P.a.kstep_off[k], bb = sb + P.b.kstep_off[k];
+          const uint64_t adesc = ((uint64_t)P.a.desc_hi << 32) | (uint64_t)(P.a.desc_lo | ((aa >> 4) & 0x3FFFu));
+          const uint64_t bdesc = ((uint64_t)P.b.desc_hi << 32) | (uint64_t)(P.b.desc_lo | ((bb >> 4) & 0x3FFFu));
+          tc_mma_tf32(tmem_base, adesc, bdesc, P.idesc, (it > 0 || k > 0) ? 1u : 0u);
+        }
+        tc_commit(&empty_bar[s]);       // the stage may be refilled once these MMAs have read it
+      }
+      if (ok) tc_commit(&accum_bar);    // accumulator complete
+    }
+  } else if (n_iter > 0) {
+    // ---- epilogue warps 2..5: TMEM lane quarter = warp index mod 4
+    const int q = warp & 3, row = q * 32 + lane;
+    const long long m = (long long)m_tile * 128 + row;
+    const bool ok = mbar_wait(&accum_bar, 0, &abort_flag, P.status, 3);
+    tc_fence_after();
+    if (ok) {
+      const int n0 = n_tile * P.bn;
+      float* dst = nullptr;
+      if (m < P.M) {
+        if (P.epilogue == TC_EPI_PIXEL) dst = P.out + (m / P.pix_per_img) * P.img_stride + (m % P.pix_per_img);
+        else dst = P.out + m * P.ld;
+      }
+      for (int c0 = 0; c0 < P.bn; c0 += 32) {
+        if (n0 + c0 >= P.N) break;                         // uniform across the warp
+        uint32_t r[32];
+        tc_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
+        if (dst) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int n = n0 + c0 + j;
+            if (n < P.N) {
+              float v = P.alpha * __uint_as_float(r[j]);
+              if (P.bias) v += P.bias[n];
+              float* q_ = P.epilogue == TC_EPI_PIXEL ? dst + (long long)n * P.chan_stride : dst + n;
+              if (P.atomic) atomicAdd(q_, v);
+              else if (P.accumulate) *q_ += v;
+              else *q_ = v;
+            }
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)P.bn) : "memory");
+  }
+}
+
+// ---- unfold / fold helpers for convolutions that are not 1x1 stride 1 ---------------------------------------------------
+// col[n][(c*R+r)*S+s][p] = x[n][c][ho*sh-ph+r][wo*sw-pw+s] (0 outside): the reference's `finput` (TensorDslCPU.scala:484-530).
+// ROWS: the same values written as the K-major row matrix col[(n*pix + p)][k] (for images too small to be fed M/N-major).
+template <bool ROWS>
+__global__ void unfold_kernel(const float* __restrict__ x, float* __restrict__ col, ConvDims d, int64_t total) {
+  const int pix = d.oH * d.oW, rs = d.R * d.S, ck = d.C * rs;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    int p, k, n;
+    if (ROWS) { k = (int)(i % ck); int64_t t = i / ck; p = (int)(t % pix); n = (int)(t / pix); }
+    else { p = (int)(i % pix); int64_t t = i / pix; k = (int)(t % ck); n = (int)(t / ck); }
+    int c = k / rs, r = (k % rs) / d.S, s = k % d.S;
+    int ih = (p / d.oW) * d.sh - d.ph + r, iw = (p % d.oW) * d.sw - d.pw + s;
+    col[i] = (ih >= 0 && ih < d.H && iw >= 0 && iw < d.W) ? x[(((int64_t)n * d.C + c) * d.H + ih) * d.W + iw] : 0.0f;
+  }
+}
+// [N][chan][pix] -> row matrix [N*pix][chan] (K-major operand for images smaller than one 128-byte row of pixels).
+__global__ void to_rows_kernel(const float* __restrict__ src, float* __restrict__ dst, int chan, int pix, int64_t total) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    int c = (int)(i % chan); int64_t t = i / chan; int p = (int)(t % pix); int64_t n = t / pix;
+    dst[i] = src[(n * chan + c) * pix + p];
+  }
+}
+// dx[n][c][h][w] += sum over the (r,s) taps that reach (h,w): gather form of unfoldedAcc (TensorDslCPU.scala:647-692).
+__global__ void fold_acc_kernel(const float* __restrict__ col, float* dx, ConvDims d, int64_t total) {
+  const int pix = d.oH * d.oW;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    int w = (int)(i % d.W); int64_t t = i / d.W; int h = (int)(t % d.H); t /= d.H; int c = (int)(t % d.C); int n = (int)(t / d.C);
+    float acc = 0.0f;
+    for (int r = 0; r < d.R; ++r) {
+      int hs = h + d.ph - r;
+      if (hs < 0 || hs % d.sh) continue;
+      int ho = hs / d.sh; if (ho >= d.oH) continue;
+      for (int s = 0; s < d.S; ++s) {
+        int ws = w + d.pw - s;
+        if (ws < 0 || ws % d.sw) continue;
+        int wo = ws / d.sw; if (wo >= d.oW) continue;
+        acc += col[((int64_t)n * d.C * d.R * d.S + (c * d.R + r) * d.S + s) * pix + ho * d.oW + wo];
+      }
+    }
+    dx[i] += acc;
+  }
+}
+
+// ---- host side ----------------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_tiled = nullptr;
+static float* debug_dump = nullptr;
+static bool smem_opted_in = false;
+
+static int encode_map(const TcTensorMap& m, CUtensorMap* out) {
+  if (!encode_tiled) {
+    void* fn = nullptr; cudaDriverEntryPointQueryResult qres;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+    if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || !fn) return fail(LTB_E_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    encode_tiled = (EncodeTiledFn)fn;
+  }
+  cuuint64_t dims[5], strides[4]; cuuint32_t box[5], estr[5];
+  for (int d = 0; d < m.rank; ++d) { dims[d] = m.dims[d]; box[d] = m.box[d]; estr[d] = 1; if (d > 0) strides[d - 1] = m.strides[d]; }
+  const CUtensorMapSwizzle sw = m.swizzle == TC_SW_128_32B ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B
+                                : m.swizzle == TC_SW_128 ? CU_TENSOR_MAP_SWIZZLE_128B : m.swizzle == TC_SW_64 ? CU_TENSOR_MAP_SWIZZLE_64B
+                                : m.swizzle == TC_SW_32 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_NONE;
+  CUresult r = encode_tiled(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, (cuuint32_t)m.rank, const_cast<void*>(m.base), dims, strides, box, estr,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(LTB_E_CUDA, "cuTensorMapEncodeTiled failed with code %d (rank %d, inner box %u)", (int)r, m.rank, m.box[0]);
+  return LTB_OK;
+}
+
+static void to_dev(const TcOperand& o, TcOperandDev& v) {
+  for (int d = 0; d < 5; ++d) { v.t_div[d] = o.t_div[d]; v.t_mod[d] = o.t_mod[d]; v.t_mul[d] = o.t_mul[d]; v.k_div[d] = o.k_div[d]; v.k_mod[d] = o.k_mod[d]; v.k_mul[d] = o.k_mul[d]; }
+  v.rank = o.map.rank; v.nk = o.nk; v.stage_bytes = o.stage_bytes;
+  // UMMA layout type: 0 none, 1 128-byte swizzle with 32-byte atoms (M/N-major 32-bit operands), 2 128 B, 4 64 B, 6 32 B
+  const uint32_t layout = o.map.swizzle == TC_SW_128_32B ? 1u : o.map.swizzle == TC_SW_128 ? 2u : o.map.swizzle == TC_SW_64 ? 4u : o.map.swizzle == TC_SW_32 ? 6u : 0u;
+  v.desc_lo = ((o.lbo >> 4) & 0x3FFFu) << 16;                                     // leading byte offset, bits [16,30)
+  v.desc_hi = ((o.sbo >> 4) & 0x3FFFu) | (1u << 14) | (layout << 29);             // stride byte offset [32,46), version 1 at [46,48), layout [61,64)
+  for (int i = 0; i < 8; ++i) v.kstep_off[i] = o.kstep_off[i];
+}
+
+static int launch_plan(const TcPlan& p, const char* label) {
+  CUtensorMap ma, mb;
+  int rc = encode_map(p.a.map, &ma); if (rc) return rc;
+  rc = encode_map(p.b.map, &mb); if (rc) return rc;
+  TcParams P;
+  to_dev(p.a, P.a); to_dev(p.b, P.b);
+  P.M = p.M; P.N = p.N; P.bn = p.bn; P.k_iters = p.k_iters;
+  P.k_per_split = (int)ceil_div(p.k_iters, p.splits);
+  const int splits = (int)ceil_div(p.k_iters, P.k_per_split);                     // every split has at least one iteration
+  P.epilogue = p.epilogue; P.accumulate = p.accumulate; P.atomic = splits > 1 ? 1 : 0;
+  // tf32 x tf32 -> f32: D format 1 at [4,6), A/B format 2 at [7,10)/[10,13), major bits 15/16, N>>3 at [17,23), M>>4 at [24,29)
+  P.idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)p.a.mn_major << 15) | ((uint32_t)p.b.mn_major << 16) | ((uint32_t)(p.bn >> 3) << 17) | ((128u >> 4) << 24);
+  P.out = p.out; P.bias = p.bias; P.alpha = p.alpha;
+  P.pix_per_img = p.pix_per_img ? p.pix_per_img : 1; P.img_stride = p.img_stride; P.chan_stride = p.chan_stride; P.ld = p.ld;
+  P.status = g.dev_status; P.dump = debug_dump;
+  const size_t smem = (size_t)kStages * (p.a.stage_bytes + p.b.stage_bytes) + 1024;
+  if (!smem_opted_in) {
+    LTB_CUDA(cudaFuncSetAttribute(tc_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kStages * (16384 + 32768) + 1024));
+    smem_opted_in = true;
+  }
+  const char* saved = g.label; g.label = label;
+  dim3 grid(p.m_tiles, p.n_tiles, splits);
+  LTB_LAUNCH(tc_gemm_kernel, grid, kTcThreads, smem, ma, mb, P);
+  g.label = saved;
+  return LTB_OK;
+}
+
+}  // namespace ltb
+// Diagnostics hook (not part of the public header): the next engine launches copy the first pipeline stage of CTA (0,0,0) to buf.
+extern "C" int ltb_debug_tc_dump(float* buf) { ltb::debug_dump = buf; return 0; }
+namespace ltb {
+
+int gemm_tc(const float* a, bool a_kmajor, const float* b, bool b_kmajor, float* c, bool, int M, int N, int K, float alpha, bool accumulate) {
+  TcPlan p;
+  if (!tc_plan_gemm(p, a, a_kmajor, b, b_kmajor, c, M, N, K, alpha, accumulate, g.sm_count)) return 0;
+  int rc = launch_plan(p, "tc_gemm_kernel[gemm]");
+  return rc ? rc : 1;
+}
+
+static bool is_pointwise(const ConvDims& d) { return d.R == 1 && d.S == 1 && d.sh == 1 && d.sw == 1 && d.ph == 0 && d.pw == 0; }
+static float* temp_alloc(size_t floats) {
+  size_t bytes = (floats * 4 + kGranule - 1) / kGranule * kGranule;
+  if (g.used + bytes > g.heap_bytes) return nullptr;          // no room for the staging buffer: let the FP32 path run
+  return (float*)ltb_malloc_uninit(floats * 4);
+}
+// Stages the activation operand of forward / data-grad for the engine.  `src` is [N][chan][pix] when no unfolding is needed
+// (unfold == false), else the convolution input to unfold.  Result: *op points at the operand, *rows tells its form,
+// *temp/*temp_floats describe the arena block to release afterwards (null when the tensor is used in place).
+static int stage_activation(const float* src, bool unfold, const ConvDims& d, int chan, int pix, const float** op, bool* rows, float** temp, size_t* temp_floats) {
+  *rows = tc_conv_needs_rows(pix); *temp = nullptr; *temp_floats = 0; *op = src;
+  if (!unfold && (!*rows || pix == 1)) return LTB_OK;         // [N][chan][1] already is the row matrix [N][chan]
+  const size_t n = (size_t)d.N * chan * pix;
+  float* buf = temp_alloc(n);
+  if (!buf) return 1;
+  *temp = buf; *temp_floats = n; *op = buf;
+  if (unfold) {
+    if (*rows) LTB_LAUNCH(unfold_kernel<true>, grid_for((int64_t)n, 256), 256, 0, src, buf, d, (int64_t)n);
+    else LTB_LAUNCH(unfold_kernel<false>, grid_for((int64_t)n, 256), 256, 0, src, buf, d, (int64_t)n);
+  } else {
+    LTB_LAUNCH(to_rows_kernel, grid_for((int64_t)n, 256), 256, 0, src, buf, chan, pix, (int64_t)n);
+  }
+  return LTB_OK;
+}
+
+int conv_fwd_tc(const float* x, const float* w, const float* bias, float* y, const ConvDims& d) {
+  const int ck = d.C * d.R * d.S, pix = d.oH * d.oW;
+  TcPlan p;
+  const bool rows = tc_conv_needs_rows(pix);
+  if (!tc_plan_conv_fwd(p, y /* any aligned pointer: eligibility only */, rows, w, bias, y, d.N, ck, d.K, pix, g.sm_count)) return 0;
+  const float* op; bool r2; float* temp; size_t tn;
+  int rc = stage_activation(x, !is_pointwise(d), d, ck, pix, &op, &r2, &temp, &tn);
+  if (rc) return rc < 0 ? rc : 0;
+  if (!tc_plan_conv_fwd(p, op, rows, w, bias, y, d.N, ck, d.K, pix, g.sm_count)) { if (temp) ltb_free(temp, tn * 4); return 0; }
+  rc = launch_plan(p, "tc_gemm_kernel[conv_fwd]");
+  if (temp) ltb_free(temp, tn * 4);
+  return rc ? rc : 1;
+}
+
+int conv_dgrad_tc(const float* dy, const float* w, float* dx, const ConvDims& d) {
+  const int ck = d.C * d.R * d.S, pix = d.oH * d.oW;
+  TcPlan p;
+  const bool rows = tc_conv_needs_rows(pix), direct = is_pointwise(d);
+  if (!tc_plan_conv_dgrad(p, dx, rows, w, dx, d.N, ck, d.K, pix, direct, g.sm_count)) return 0;
+  const float* op; bool r2; float* temp; size_t tn;
+  ConvDims flat = d; flat.C = d.K;                               // dy is [N][K][pix]: staged like a pointwise activation with K channels
+  int rc = stage_activation(dy, false, flat, d.K, pix, &op, &r2, &temp, &tn);
+  if (rc) return rc < 0 ? rc : 0;
+  float* col = nullptr; const size_t ncol = (size_t)d.N * ck * pix;
+  if (!direct) { col = temp_alloc(ncol); if (!col) { if (temp) ltb_free(temp, tn * 4); return 0; } }
+  bool ok = tc_plan_conv_dgrad(p, op, rows, w, direct ? dx : col, d.N, ck, d.K, pix, direct, g.sm_count);
+  rc = ok ? launch_plan(p, "tc_gemm_kernel[conv_dgrad]") : 0;
+  if (ok && !rc && !direct) {
+    const int64_t nx = (int64_t)d.N * d.C * d.H * d.W;
+    LTB_LAUNCH(fold_acc_kernel, grid_for(nx, 256), 256, 0, (const float*)col, dx, d, nx);
+  }
+  if (col) ltb_free(col, ncol * 4);
+  if (temp) ltb_free(temp, tn * 4);
+  return !ok ? 0 : (rc ? rc : 1);
+}
+
+int conv_wgrad_tc(const float* x, const float* dy, float* dw, const ConvDims& d) {
+  const int ck = d.C * d.R * d.S, pix = d.oH * d.oW;
+  TcPlan p;
+  if (!tc_plan_conv_wgrad(p, dy, dy, dw, d.N, ck, d.K, pix, g.sm_count)) return 0;
+  const float* xin = x; float* col = nullptr; const size_t n = (size_t)d.N * ck * pix;
+  if (!is_pointwise(d)) {
+    col = temp_alloc(n); if (!col) return 0;
+    LTB_LAUNCH(unfold_kernel<false>, grid_for((int64_t)n, 256), 256, 0, x, col, d, (int64_t)n);
+    xin = col;
+  }
+  tc_plan_conv_wgrad(p, xin, dy, dw, d.N, ck, d.K, pix, g.sm_count);
+  int rc = launch_plan(p, "tc_gemm_kernel[conv_wgrad]");
+  if (col) ltb_free(col, n * 4);
+  return rc ? rc : 1;
+}
+
 }  // namespace ltb

@@ -107,31 +107,31 @@ __global__ void bn_reduce_kernel(const float* __restrict__ x, const float* __res
   float k = MODE == 0 ? x[(int64_t)c * HW] : mean[c];
   float is = MODE == 0 ? 1.0f : istd[c];
   float a = 0.0f, b = 0.0f;
+  // The split's images are walked as one flat index space so that all threads stay busy when HW is small.
+  const int n_imgs = (N - s + S - 1) / S;
   if ((HW & 3) == 0) {
-    int hw4 = HW >> 2;
-    for (int n = s; n < N; n += S) {
-      const float4* px = reinterpret_cast<const float4*>(x + ((int64_t)n * C + c) * HW);
-      const float4* pd = MODE == 1 ? reinterpret_cast<const float4*>(dy + ((int64_t)n * C + c) * HW) : nullptr;
-      for (int i = threadIdx.x; i < hw4; i += blockDim.x) {
-        float4 v = px[i];
-        if (MODE == 0) {
-          float d0 = v.x - k, d1 = v.y - k, d2 = v.z - k, d3 = v.w - k;
-          a += (d0 + d1) + (d2 + d3); b += (d0 * d0 + d1 * d1) + (d2 * d2 + d3 * d3);
-        } else {
-          float4 d = pd[i];
-          a += (d.x + d.y) + (d.z + d.w);
-          b += (d.x * ((v.x - k) * is) + d.y * ((v.y - k) * is)) + (d.z * ((v.z - k) * is) + d.w * ((v.w - k) * is));
-        }
+    const int hw4 = HW >> 2;
+    const int64_t total = (int64_t)n_imgs * hw4;
+    for (int64_t t = threadIdx.x; t < total; t += blockDim.x) {
+      int n = s + (int)(t / hw4) * S, i = (int)(t % hw4);
+      const int64_t off = ((int64_t)n * C + c) * HW;
+      float4 v = reinterpret_cast<const float4*>(x + off)[i];
+      if (MODE == 0) {
+        float d0 = v.x - k, d1 = v.y - k, d2 = v.z - k, d3 = v.w - k;
+        a += (d0 + d1) + (d2 + d3); b += (d0 * d0 + d1 * d1) + (d2 * d2 + d3 * d3);
+      } else {
+        float4 d = reinterpret_cast<const float4*>(dy + off)[i];
+        a += (d.x + d.y) + (d.z + d.w);
+        b += (d.x * ((v.x - k) * is) + d.y * ((v.y - k) * is)) + (d.z * ((v.z - k) * is) + d.w * ((v.w - k) * is));
       }
     }
   } else {
-    for (int n = s; n < N; n += S) {
-      const float* px = x + ((int64_t)n * C + c) * HW;
-      const float* pd = MODE == 1 ? dy + ((int64_t)n * C + c) * HW : nullptr;
-      for (int i = threadIdx.x; i < HW; i += blockDim.x) {
-        float v = px[i] - k;
-        if (MODE == 0) { a += v; b += v * v; } else { a += pd[i]; b += pd[i] * (v * is); }
-      }
+    const int64_t total = (int64_t)n_imgs * HW;
+    for (int64_t t = threadIdx.x; t < total; t += blockDim.x) {
+      int n = s + (int)(t / HW) * S, i = (int)(t % HW);
+      const int64_t off = ((int64_t)n * C + c) * HW + i;
+      float v = x[off] - k;
+      if (MODE == 0) { a += v; b += v * v; } else { a += dy[off]; b += dy[off] * (v * is); }
     }
   }
   block_sum2(a, b);

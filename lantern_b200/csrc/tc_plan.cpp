@@ -1,0 +1,217 @@
+// Planner of the TF32 tensor-core engine: see tc_plan.h.  Pure host code.
+#include "tc_plan.h"
+
+#include <cstring>
+
+namespace ltb {
+
+namespace {
+
+constexpr int kBK = 32;          // K elements per pipeline stage (4 MMA steps of K = 8)
+constexpr int kTileM = 128;      // UMMA M with one CTA
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+int cdiv(int64_t a, int64_t b) { return (int)((a + b - 1) / b); }
+
+void clear(TcOperand& o) {
+  std::memset(&o, 0, sizeof o);
+  for (int d = 0; d < 5; ++d) {
+    o.map.dims[d] = 1; o.map.strides[d] = 0; o.map.box[d] = 1;
+    o.t_div[d] = 1; o.t_mod[d] = 1 << 30; o.t_mul[d] = 0;
+    o.k_div[d] = 1; o.k_mod[d] = 1 << 30; o.k_mul[d] = 0;
+  }
+}
+
+// Operand indexed [img][k][pix] (pix contiguous) whose M/N index is the pixel (img, pix) and whose K index is k.
+// One tile = `kTileM` pixels.  Returns the number of k-iterations through *k_iters.
+bool operand_mn_pixels(TcOperand& o, const float* base, int n_img, int kdim, int pix, int* k_iters) {
+  clear(o);
+  if (!aligned16(base) || kdim < 1 || n_img < 1) return false;
+  o.map.base = base; o.mn_major = 1; o.nk = 4; o.stage_bytes = kTileM * kBK * 4;
+  *k_iters = cdiv(kdim, kBK);
+  if (pix >= 32 && pix % 32 == 0) {
+    int cpt, ipt, tpi;
+    if (pix >= kTileM) { if (pix % kTileM) return false; cpt = kTileM / 32; ipt = 1; tpi = pix / kTileM; }
+    else { if (kTileM % pix) return false; cpt = pix / 32; ipt = kTileM / pix; tpi = 1; }
+    o.map.rank = 4; o.map.swizzle = TC_SW_128_32B;
+    o.map.dims[0] = 32; o.map.dims[1] = (uint64_t)kdim; o.map.dims[2] = (uint64_t)pix / 32; o.map.dims[3] = (uint64_t)n_img;
+    o.map.strides[1] = (uint64_t)pix * 4; o.map.strides[2] = 128; o.map.strides[3] = (uint64_t)kdim * pix * 4;
+    o.map.box[0] = 32; o.map.box[1] = kBK; o.map.box[2] = (uint32_t)cpt; o.map.box[3] = (uint32_t)ipt;
+    o.k_mul[1] = kBK;
+    o.t_div[2] = 1; o.t_mod[2] = tpi; o.t_mul[2] = cpt;          // chunk coordinate inside the image
+    o.t_div[3] = tpi; o.t_mul[3] = ipt;                          // image coordinate
+    o.lbo = kBK * 128; o.sbo = 512;                              // chunk stride; stride between the 4-row groups
+    for (int i = 0; i < 4; ++i) o.kstep_off[i] = (uint32_t)i * 1024;
+    return true;
+  }
+  if (false) {
+    const int ipt = kTileM / pix;                                // images per tile: 8 or 32
+    o.map.rank = 3; o.map.swizzle = pix == 16 ? TC_SW_64 : TC_SW_NONE;
+    o.map.dims[0] = (uint64_t)pix; o.map.dims[1] = (uint64_t)kdim; o.map.dims[2] = (uint64_t)n_img;
+    o.map.strides[1] = (uint64_t)pix * 4; o.map.strides[2] = (uint64_t)kdim * pix * 4;
+    o.map.box[0] = (uint32_t)pix; o.map.box[1] = kBK; o.map.box[2] = (uint32_t)ipt;
+    o.k_mul[1] = kBK; o.t_mul[2] = ipt;
+    const uint32_t row = (uint32_t)pix * 4;                      // bytes of one k-row of a chunk
+    if (pix == 16) { o.lbo = kBK * row; o.sbo = 8 * row; }       // swizzled: LBO = chunk stride, SBO = 8-row group stride
+    else { o.sbo = kBK * row; o.lbo = 8 * row; }                 // interleaved: SBO = chunk stride, LBO = 8-row group stride
+    for (int i = 0; i < 4; ++i) o.kstep_off[i] = (uint32_t)i * 8 * row;
+    return true;
+  }
+  return false;
+}
+
+// Row-major matrix [rows][kdim] used K-major (rows = M or N index). One tile = tile_rows rows.
+bool operand_k_rows(TcOperand& o, const float* base, int rows, int kdim, int tile_rows, int* k_iters) {
+  clear(o);
+  if (!aligned16(base) || kdim % 4 || rows < 1) return false;
+  o.map.base = base; o.mn_major = 0; o.nk = 4; o.stage_bytes = (uint32_t)tile_rows * 128;
+  o.map.rank = 2; o.map.swizzle = TC_SW_128;
+  o.map.dims[0] = (uint64_t)kdim; o.map.dims[1] = (uint64_t)rows;
+  o.map.strides[1] = (uint64_t)kdim * 4;
+  o.map.box[0] = kBK; o.map.box[1] = (uint32_t)tile_rows;
+  o.k_mul[0] = kBK; o.t_mul[1] = tile_rows;
+  o.lbo = 16; o.sbo = 1024;
+  for (int i = 0; i < 4; ++i) o.kstep_off[i] = (uint32_t)i * 32;
+  *k_iters = cdiv(kdim, kBK);
+  return true;
+}
+
+// Row-major matrix [kdim][cols] used M/N-major (cols = M or N index, contiguous). One tile = tile_cols columns.
+bool operand_mn_cols(TcOperand& o, const float* base, int kdim, int cols, int tile_cols, int* k_iters) {
+  clear(o);
+  if (!aligned16(base) || cols % 32 || kdim < 1) return false;
+  o.map.base = base; o.mn_major = 1; o.nk = 4; o.stage_bytes = (uint32_t)tile_cols * 128;
+  o.map.rank = 3; o.map.swizzle = TC_SW_128_32B;
+  o.map.dims[0] = 32; o.map.dims[1] = (uint64_t)kdim; o.map.dims[2] = (uint64_t)cols / 32;
+  o.map.strides[1] = (uint64_t)cols * 4; o.map.strides[2] = 128;
+  o.map.box[0] = 32; o.map.box[1] = kBK; o.map.box[2] = (uint32_t)tile_cols / 32;
+  o.k_mul[1] = kBK; o.t_mul[2] = tile_cols / 32;
+  o.lbo = kBK * 128; o.sbo = 512;
+  for (int i = 0; i < 4; ++i) o.kstep_off[i] = (uint32_t)i * 1024;
+  *k_iters = cdiv(kdim, kBK);
+  return true;
+}
+
+// Operand indexed [img][row][pix] used K-major with the reduction running over (img, pix). One tile = tile_rows rows.
+bool operand_k_pixels(TcOperand& o, const float* base, int n_img, int rows, int pix, int tile_rows, int* k_iters) {
+  clear(o);
+  if (!aligned16(base) || rows < 1 || n_img < 1) return false;
+  o.map.base = base; o.mn_major = 0; o.nk = 4; o.stage_bytes = (uint32_t)tile_rows * 128;
+  o.map.rank = 3;
+  o.map.dims[0] = (uint64_t)pix; o.map.dims[1] = (uint64_t)rows; o.map.dims[2] = (uint64_t)n_img;
+  o.map.strides[1] = (uint64_t)pix * 4; o.map.strides[2] = (uint64_t)rows * pix * 4;
+  o.map.box[1] = (uint32_t)tile_rows; o.t_mul[1] = tile_rows;
+  if (pix >= 32 && pix % 32 == 0) {
+    const int cpi = pix / 32;
+    o.map.swizzle = TC_SW_128; o.map.box[0] = 32; o.map.box[2] = 1;
+    o.k_div[0] = 1; o.k_mod[0] = cpi; o.k_mul[0] = 32;
+    o.k_div[2] = cpi; o.k_mul[2] = 1;
+    o.lbo = 16; o.sbo = 1024;
+    for (int i = 0; i < 4; ++i) o.kstep_off[i] = (uint32_t)i * 32;
+    *k_iters = n_img * cpi;
+    return true;
+  }
+  if (pix == 16) {            // two images per stage, each a 64-byte row: 2 MMA steps per image
+    o.map.swizzle = TC_SW_64; o.map.box[0] = 16; o.map.box[2] = 2;
+    o.k_mul[2] = 2;
+    o.lbo = 16; o.sbo = 512;
+    const uint32_t img = (uint32_t)tile_rows * 64;
+    o.kstep_off[0] = 0; o.kstep_off[1] = 32; o.kstep_off[2] = img; o.kstep_off[3] = img + 32;
+    *k_iters = cdiv(n_img, 2);
+    return true;
+  }
+  if (pix == 4) {             // eight images per stage, 16 bytes each: an MMA step spans two images
+    o.map.swizzle = TC_SW_NONE; o.map.box[0] = 4; o.map.box[2] = 8;
+    o.k_mul[2] = 8;
+    const uint32_t img = (uint32_t)tile_rows * 16;
+    o.sbo = 128; o.lbo = img;                                    // interleaved K-major: LBO = stride between the two 16-byte k-chunks
+    for (int i = 0; i < 4; ++i) o.kstep_off[i] = (uint32_t)i * 2 * img;
+    *k_iters = cdiv(n_img, 8);
+    return true;
+  }
+  return false;
+}
+
+int pick_bn(int n_extent, int m_tiles, int sm_count) {
+  const int cand[3] = {256, 128, 64};
+  for (int bn : cand) {
+    if (bn > 64 && bn > n_extent) continue;
+    if (bn == 64 || m_tiles * cdiv(n_extent, bn) >= sm_count) return bn;
+  }
+  return 64;
+}
+
+void finish(TcPlan& p, int M, int N, int k_iters, int sm_count, bool may_split) {
+  p.M = M; p.N = N; p.k_iters = k_iters;
+  p.m_tiles = cdiv(M, kTileM); p.n_tiles = cdiv(N, p.bn);
+  p.splits = 1;
+  if (may_split) {
+    int tiles = p.m_tiles * p.n_tiles;
+    int s = cdiv(2 * sm_count, tiles);
+    int mx = k_iters / 2; if (mx < 1) mx = 1;
+    if (s > mx) s = mx;
+    if (tiles >= sm_count) s = 1;
+    p.splits = s < 1 ? 1 : s;
+  }
+}
+
+}  // namespace
+
+bool tc_conv_needs_rows(int pix) { return !(pix >= 32 && pix % 32 == 0 && (pix >= kTileM ? pix % kTileM == 0 : kTileM % pix == 0)); }
+
+bool tc_plan_conv_fwd(TcPlan& p, const float* x, bool a_rows, const float* w, const float* bias, float* y, int n_img, int ck, int co, int pix, int sm_count) {
+  std::memset(&p, 0, sizeof p);
+  if (co < 16 || ck < 8 || (int64_t)n_img * pix > (1ll << 30)) return false;
+  int ka = 0, kb = 0;
+  const int M = n_img * pix;
+  if (!(a_rows ? operand_k_rows(p.a, x, M, ck, kTileM, &ka) : operand_mn_pixels(p.a, x, n_img, ck, pix, &ka))) return false;
+  p.bn = pick_bn(co, cdiv(M, kTileM), sm_count);
+  if (!operand_k_rows(p.b, w, co, ck, p.bn, &kb) || ka != kb) return false;
+  finish(p, M, co, ka, sm_count, false);
+  p.epilogue = TC_EPI_PIXEL; p.out = y; p.bias = bias; p.alpha = 1.0f; p.accumulate = 0;
+  p.pix_per_img = pix; p.img_stride = (int64_t)co * pix; p.chan_stride = pix;
+  return true;
+}
+
+bool tc_plan_conv_dgrad(TcPlan& p, const float* dy, bool a_rows, const float* w, float* dx, int n_img, int ck, int co, int pix, bool accumulate, int sm_count) {
+  std::memset(&p, 0, sizeof p);
+  if (ck < 32 || co < 8 || (int64_t)n_img * pix > (1ll << 30)) return false;
+  int ka = 0, kb = 0;
+  const int M = n_img * pix;
+  if (!(a_rows ? operand_k_rows(p.a, dy, M, co, kTileM, &ka) : operand_mn_pixels(p.a, dy, n_img, co, pix, &ka))) return false;
+  p.bn = pick_bn(ck, cdiv(M, kTileM), sm_count);
+  if (!operand_mn_cols(p.b, w, co, ck, p.bn, &kb) || ka != kb) return false;
+  finish(p, M, ck, ka, sm_count, accumulate);
+  p.epilogue = TC_EPI_PIXEL; p.out = dx; p.bias = nullptr; p.alpha = 1.0f; p.accumulate = accumulate ? 1 : 0;
+  p.pix_per_img = pix; p.img_stride = (int64_t)ck * pix; p.chan_stride = pix;
+  return true;
+}
+
+bool tc_plan_conv_wgrad(TcPlan& p, const float* x, const float* dy, float* dw, int n_img, int ck, int co, int pix, int sm_count) {
+  std::memset(&p, 0, sizeof p);
+  if (co < 16 || ck < 16) return false;
+  int ka = 0, kb = 0;
+  if (!operand_k_pixels(p.a, dy, n_img, co, pix, kTileM, &ka)) return false;
+  p.bn = pick_bn(ck, cdiv(co, kTileM), 0);            // largest tile that fits: the grid is filled by split-K
+  if (!operand_k_pixels(p.b, x, n_img, ck, pix, p.bn, &kb) || ka != kb) return false;
+  finish(p, co, ck, ka, sm_count, true);
+  p.epilogue = TC_EPI_ROWMAJOR; p.out = dw; p.bias = nullptr; p.alpha = 1.0f; p.accumulate = 1; p.ld = ck;
+  return true;
+}
+
+bool tc_plan_gemm(TcPlan& p, const float* a, bool a_kmajor, const float* b, bool b_kmajor, float* c, int M, int N, int K, float alpha,
+                  bool accumulate, int sm_count) {
+  std::memset(&p, 0, sizeof p);
+  if (M < 64 || N < 32 || K < 32 || !aligned16(c)) return false;
+  int ka = 0, kb = 0;
+  bool ok = a_kmajor ? operand_k_rows(p.a, a, M, K, kTileM, &ka) : operand_mn_cols(p.a, a, K, M, kTileM, &ka);
+  if (!ok) return false;
+  p.bn = pick_bn(N, cdiv(M, kTileM), sm_count);
+  ok = b_kmajor ? operand_k_rows(p.b, b, N, K, p.bn, &kb) : operand_mn_cols(p.b, b, K, N, p.bn, &kb);
+  if (!ok || ka != kb) return false;
+  finish(p, M, N, ka, sm_count, accumulate);
+  p.epilogue = TC_EPI_ROWMAJOR; p.out = c; p.bias = nullptr; p.alpha = alpha; p.accumulate = accumulate ? 1 : 0; p.ld = N;
+  return true;
+}
+
+}  // namespace ltb

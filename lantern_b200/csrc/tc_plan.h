@@ -1,0 +1,80 @@
+// Host-side plans for the TF32 tensor-core engine (pure C++, no CUDA: also compiled into the CPU layout test).
+//
+// The engine kernel (gemm_tc.cu) is generic: for every operand it is told how to turn (output tile, k-iteration) into
+// TMA box coordinates, how many bytes a stage holds, and the UMMA shared-memory descriptors of the MMA steps of a stage.
+// Everything that depends on the tensor layout (NCHW activations with pixels contiguous, OIHW filters, row-major
+// matrices, tiny images) is decided here and expressed in those numbers.
+//
+// Shared-memory layouts are the canonical UMMA layouts for 32-bit operands:
+//   K-major,  swizzle span X bytes : rows of X bytes (X/4 floats of K), 8-row groups SBO apart; an MMA step covers 32 B of K
+//   MN-major (32-bit operands)     : the only layout the tensor core accepts is the 128-byte swizzle with 32-byte atoms:
+//                                    chunks of 32 elements of M (or N) contiguous (128 B), one row per k, 4 k-rows per group
+//                                    (512 B), groups SBO apart, chunks LBO apart; an MMA step (K = 8) spans two groups.
+//   no swizzle (K-major only)      : 16-byte rows, 8-row groups SBO apart, the second 16-byte k-chunk LBO apart.
+// A TMA box whose inner extent is X bytes, loaded with the matching swizzle mode, lands in exactly that layout.
+// Operands whose contiguous axis is shorter than 128 bytes cannot be fed MN-major; the callers hand those in as K-major
+// row matrices instead (`a_rows`), produced by a small transposing copy.
+#pragma once
+#include <cstdint>
+
+namespace ltb {
+
+enum TcSwizzle { TC_SW_NONE = 0, TC_SW_32 = 1, TC_SW_64 = 2, TC_SW_128 = 3, TC_SW_128_32B = 4 };
+
+struct TcTensorMap {          // arguments of cuTensorMapEncodeTiled for one FP32 operand
+  const void* base;
+  int rank;
+  uint64_t dims[5];           // innermost first
+  uint64_t strides[5];        // bytes; strides[0] is implied (4) and unused
+  uint32_t box[5];
+  int swizzle;                // TcSwizzle
+};
+
+struct TcOperand {
+  TcTensorMap map;
+  // box coordinate d = ((tile / t_div[d]) % t_mod[d]) * t_mul[d] + ((kiter / k_div[d]) % k_mod[d]) * k_mul[d]
+  int t_div[5], t_mod[5], t_mul[5];
+  int k_div[5], k_mod[5], k_mul[5];
+  uint32_t stage_bytes;       // bytes one stage of this operand occupies (== bytes the TMA box delivers)
+  int mn_major;               // 0: K-major, 1: M/N-major (instruction descriptor transpose bit)
+  uint32_t lbo, sbo;          // bytes
+  int nk;                     // MMA steps (K = 8 each) per stage
+  uint32_t kstep_off[8];      // start-address offset of each step within the stage
+};
+
+enum TcEpilogue {
+  TC_EPI_PIXEL = 0,   // D row = pixel, D column = channel: out[img][chan][pix]   (conv forward / data-grad)
+  TC_EPI_ROWMAJOR = 1 // D row = row, D column contiguous:   out[row*ld + col]      (gemm, weight-grad)
+};
+
+struct TcPlan {
+  TcOperand a, b;             // a: the M-side operand (128 rows per tile), b: the N-side operand (bn columns per tile)
+  int M, N;                   // logical extents of D
+  int bn;                     // tile width: 64, 128 or 256
+  int m_tiles, n_tiles, k_iters, splits;
+  int epilogue;
+  float* out;
+  const float* bias;          // per D column, or null
+  float alpha;
+  int accumulate;             // 1: out += ..., 0: out = ...   (split-K > 1 forces atomic accumulation)
+  int64_t pix_per_img, img_stride, chan_stride;   // TC_EPI_PIXEL
+  int64_t ld;                                     // TC_EPI_ROWMAJOR
+};
+
+// "Flat" convolution view: activations X[n][k][p] with p contiguous (k = channels, or channels*kh*kw after unfolding),
+// weights W[co][k] row-major, outputs Y[n][co][p].  P is the number of pixels per image.
+//   forward : Y[n][co][p]  = sum_k  W[co][k] X[n][k][p] (+ bias[co])         D = pixels x co
+//   dgrad   : dX[n][k][p] (+)= sum_co W[co][k] dY[n][co][p]                   D = pixels x k
+//   wgrad   : dW[co][k]  += sum_{n,p} dY[n][co][p] X[n][k][p]                 D = co x k
+// Each returns false when the shape is not eligible (the caller then uses the FP32 path).
+// a_rows: the activation operand (x for forward, dy for dgrad) is given as a K-major row matrix [n_img*pix][channels]
+// instead of [n_img][channels][pix]; tc_conv_needs_rows says when that form is required.
+bool tc_conv_needs_rows(int pix);
+bool tc_plan_conv_fwd(TcPlan& p, const float* x, bool a_rows, const float* w, const float* bias, float* y, int n_img, int ck, int co, int pix, int sm_count);
+bool tc_plan_conv_dgrad(TcPlan& p, const float* dy, bool a_rows, const float* w, float* dx, int n_img, int ck, int co, int pix, bool accumulate, int sm_count);
+bool tc_plan_conv_wgrad(TcPlan& p, const float* x, const float* dy, float* dw, int n_img, int ck, int co, int pix, int sm_count);
+// C[M,N] (op)= alpha * A B; a_kmajor: A stored [M,K] (else [K,M]); b_kmajor: B stored [N,K] (else [K,N]).
+bool tc_plan_gemm(TcPlan& p, const float* a, bool a_kmajor, const float* b, bool b_kmajor, float* c, int M, int N, int K, float alpha,
+                  bool accumulate, int sm_count);
+
+}  // namespace ltb

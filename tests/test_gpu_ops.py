@@ -285,3 +285,51 @@ def test_arena_semantics_and_error_codes(gpu):
         lib.gemm(0, 0, 0, 0, 1.0, 0, 4, 4, 4)
     assert e.value.code == -2
     assert lib.kernel_launches() > 0
+
+
+# ------------------------------------------------------------------------------------------------ TF32 tensor-core engine
+@pytest.mark.parametrize("ta,tb", [(0, 0), (0, 1), (1, 0), (1, 1)])
+@pytest.mark.parametrize("M,N,K", [(128, 64, 32), (256, 128, 64), (384, 320, 96), (128, 2048, 256), (256, 100, 100), (8, 10, 2048)])
+def test_gemm_and_grad_tf32(ora, gpu, ta, tb, M, N, K):
+    """Eligible shapes run on tcgen05 (2e-3), the others fall back to the FP32 path; both must hold the TF32 tolerance."""
+    a = R(1).standard_normal((K, M) if ta else (M, K)).astype(np.float32)
+    c = R(2).standard_normal((N, K) if tb else (K, N)).astype(np.float32)
+    dc = R(3).standard_normal((M, N)).astype(np.float32)
+
+    def f(b):
+        A, C = TensorR(b.fromNumpy(a)), TensorR(b.fromNumpy(c))
+        out = b.gemm(A.x, ta, C.x, tb, 0.5)
+        b.gemm_grad(A, ta, C, tb, 0.5, TensorR(out, b.fromNumpy(dc)))
+        return {"out": out.toCPU(), "da": A.d.toCPU(), "db": C.d.toCPU()}
+    check(f, ora, gpu, rtol=TF32_RTOL)
+
+
+TC_CONVS = [  # N, C, H, W, K, R, stride, pad: the ResNet-50 / SqueezeNet layer shapes at small batch (partial tiles included)
+    (2, 64, 16, 16, 64, 1, 1, 0), (2, 64, 16, 16, 256, 1, 1, 0), (3, 256, 16, 16, 64, 1, 1, 0), (4, 128, 8, 8, 512, 1, 1, 0),
+    (5, 512, 8, 8, 128, 1, 1, 0), (9, 256, 4, 4, 1024, 1, 1, 0), (9, 1024, 4, 4, 256, 1, 1, 0), (33, 512, 2, 2, 2048, 1, 1, 0),
+    (33, 2048, 2, 2, 512, 1, 1, 0), (2, 64, 16, 16, 64, 3, 1, 1), (2, 128, 16, 16, 128, 3, 2, 1), (3, 128, 8, 8, 128, 3, 1, 1),
+    (9, 256, 8, 8, 256, 3, 2, 1), (9, 256, 4, 4, 256, 3, 1, 1), (17, 512, 4, 4, 512, 3, 2, 1), (17, 512, 2, 2, 512, 3, 1, 1),
+    (2, 256, 16, 16, 512, 1, 2, 0), (5, 512, 8, 8, 1024, 1, 2, 0), (9, 1024, 4, 4, 2048, 1, 2, 0), (4, 16, 32, 32, 64, 1, 1, 0),
+    (4, 96, 16, 16, 16, 1, 1, 0), (8, 512, 4, 4, 10, 4, 1, 0), (3, 96, 32, 32, 16, 1, 1, 0), (3, 16, 16, 16, 64, 3, 1, 1)]
+
+
+@pytest.mark.parametrize("cfg", TC_CONVS, ids=[str(c) for c in TC_CONVS])
+def test_conv_fwd_bwd_tf32(ora, gpu, cfg):
+    N, C, H, W, K, Rk, s, p = cfg
+    x0 = R(1).standard_normal((N, C, H, W)).astype(np.float32)
+    w0 = (R(2).standard_normal((K, C, Rk, Rk)) / np.sqrt(C * Rk * Rk)).astype(np.float32)
+    b0 = R(3).standard_normal(K).astype(np.float32)
+
+    def f(b):
+        x, w, bias = TensorR(b.fromNumpy(x0)), TensorR(b.fromNumpy(w0)), TensorR(b.fromNumpy(b0))
+        y, _, _ = b.conv2D_batch(x.x, w.x, bias.x, (s, s), (p, p, p, p))
+        dy = b.fromNumpy(R(4).standard_normal(y.shape).astype(np.float32))
+        # gradients accumulate: start from non-zero destinations
+        x.d, w.d = b.fromNumpy(x0 * 0.25), b.fromNumpy(w0 * 0.5)
+        b.conv2D_batch_grad(x, None, w, TensorR(y, dy), bias, (p, p), (s, s))
+        return {"y": y.toCPU(), "dx": x.d.toCPU(), "dw": w.d.toCPU(), "db": bias.d.toCPU()}
+    check(f, ora, gpu, rtol=TF32_RTOL)
+
+
+def test_tensor_core_engine_reports_no_timeouts(gpu):
+    assert gpu.lib.device_status() == 0
