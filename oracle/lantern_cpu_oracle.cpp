@@ -24,6 +24,7 @@
 // reference's shipped generated MNIST program compiled from its own source).
 #define LTB_FN(name) ora_##name
 #include "../include/lantern_b200.h"
+#include "../lantern_b200/csrc/tc_plan.h"   // eligibility rule of the product's tensor-core engine (shape arithmetic only)
 
 #include <cfloat>
 #include <cmath>
@@ -48,7 +49,29 @@ struct Ctx {
   std::string msg;
   int threads = 1;
   int64_t calls = 0;
+  int math = LTB_MATH_FP32;   // LTB_MATH_TF32: emulate the operand truncation of the product's tensor-core path
 } g;
+
+// TF32 emulation.  In LTB_MATH_TF32 mode the oracle reproduces what the product's tensor-core path computes for the
+// shapes that path accepts: both operands of the contraction reduced to TF32 (10-bit mantissa, low 13 bits dropped, as the
+// tensor core reads FP32 words), products and sums in FP32.  Shapes the engine declines are computed in plain FP32 on both
+// sides.  This turns the 2e-3 "TF32 tolerance" into a check at FP32 rounding level.  Default is plain FP32: the reference's
+// CPU backend.
+inline float tf32_trunc(float v) { uint32_t u; memcpy(&u, &v, 4); u &= 0xFFFFE000u; memcpy(&v, &u, 4); return v; }
+std::vector<float> truncated(const float* p, size_t n) { std::vector<float> v(n); for (size_t i = 0; i < n; ++i) v[i] = tf32_trunc(p[i]); return v; }
+alignas(16) float tc_dummy[4];
+bool tc_gemm_taken(bool a_kmajor, bool b_kmajor, int M, int N, int K) {
+  if (g.math != LTB_MATH_TF32) return false;
+  ltb::TcPlan p; return ltb::tc_plan_gemm(p, tc_dummy, a_kmajor, tc_dummy, b_kmajor, tc_dummy, M, N, K, 1.0f, false, 148);
+}
+// kind 0 forward, 1 data-grad, 2 weight-grad
+bool tc_conv_taken(int kind, int n_img, int ck, int co, int pix) {
+  if (g.math != LTB_MATH_TF32) return false;
+  ltb::TcPlan p; const bool rows = ltb::tc_conv_needs_rows(pix);
+  if (kind == 0) return ltb::tc_plan_conv_fwd(p, tc_dummy, rows, tc_dummy, nullptr, tc_dummy, n_img, ck, co, pix, 148);
+  if (kind == 1) return ltb::tc_plan_conv_dgrad(p, tc_dummy, rows, tc_dummy, tc_dummy, n_img, ck, co, pix, true, 148);
+  return ltb::tc_plan_conv_wgrad(p, tc_dummy, tc_dummy, tc_dummy, n_img, ck, co, pix, 148);
+}
 
 int fail(int code, const char* what) {
   g.last = code;
@@ -95,6 +118,14 @@ void sgemm(bool ta, bool tb, int M, int N, int K, float alpha, const float* A, i
     if (beta == 0.0f) for (int j = 0; j < N; ++j) c[j] = alpha * acc[j];
     else for (int j = 0; j < N; ++j) c[j] = alpha * acc[j] + beta * c[j];
   }
+}
+
+// sgemm with the TF32 emulation applied when the product would run this problem on its tensor-core engine.
+// a_kmajor / b_kmajor describe op(A) / op(B) the way the product's planner sees them: A stored [M,K], B stored [N,K].
+void sgemm_m(bool ta, bool tb, int M, int N, int K, float alpha, const float* A, int lda, const float* B, int ldb, float beta, float* C, int ldc) {
+  if (!tc_gemm_taken(!ta, tb, M, N, K)) { sgemm(ta, tb, M, N, K, alpha, A, lda, B, ldb, beta, C, ldc); return; }
+  std::vector<float> a = truncated(A, (size_t)(ta ? K : M) * lda), b = truncated(B, (size_t)(tb ? N : K) * ldb);
+  sgemm(ta, tb, M, N, K, alpha, a.data(), lda, b.data(), ldb, beta, C, ldc);
 }
 
 inline float apply_op(int op, float a, float b) {
@@ -162,7 +193,7 @@ int ora_last_error(char* buf, int len) {
 int ora_set_stream(void*) { return LTB_OK; }
 void* ora_get_stream(void) { return nullptr; }
 int ora_sync(void) { return LTB_OK; }
-int ora_set_math(int) { return LTB_OK; }
+int ora_set_math(int mode) { g.math = mode; return LTB_OK; }
 int ora_device_status(void) { return LTB_OK; }
 int64_t ora_kernel_launches(void) { return 0; }
 // Not in the shared header: number of host threads the oracle may use (1 = the reference's protocol,
@@ -234,7 +265,7 @@ int ora_mv_dot(const float* a, const float* x, float* out, int m, int k) {
 }
 // matrixMatrixDot: TensorDslCPU.scala:158-169.
 int ora_mm_dot(const float* a, const float* b, float* out, int m, int k, int n) {
-  sgemm(false, false, m, n, k, 1.0f, a, k, b, n, 0.0f, out, n); return LTB_OK;
+  sgemm_m(false, false, m, n, k, 1.0f, a, k, b, n, 0.0f, out, n); return LTB_OK;
 }
 // add_cartesian: TensorDslCPU.scala:186-196.
 int ora_add_cartesian(float* da, const float* y, const float* dout, int m, int k) {
@@ -248,17 +279,17 @@ int ora_add_composition(float* dx, const float* a, const float* dout, int m, int
 }
 // add_dotTrans1: x += y^T . output, TensorDslCPU.scala:208-215.
 int ora_add_dot_trans1(float* db, const float* a, const float* dc, int m, int k, int n) {
-  sgemm(true, false, k, n, m, 1.0f, a, k, dc, n, 1.0f, db, n); return LTB_OK;
+  sgemm_m(true, false, k, n, m, 1.0f, a, k, dc, n, 1.0f, db, n); return LTB_OK;
 }
 // add_dotTrans2: x += y . output^T, TensorDslCPU.scala:217-225.
 int ora_add_dot_trans2(float* da, const float* dc, const float* b, int m, int k, int n) {
-  sgemm(false, true, m, k, n, 1.0f, dc, n, b, n, 1.0f, da, k); return LTB_OK;
+  sgemm_m(false, true, m, k, n, 1.0f, dc, n, b, n, 1.0f, da, k); return LTB_OK;
 }
 
 // gemm: TensorDslCPU.scala:379-426 (four cblas_sgemm cases, beta 0).
 int ora_gemm(const float* a, int ta, const float* b, int tb, float alpha, float* c, int M, int N, int K) {
   REQUIRE(a && b && c && M > 0 && N > 0 && K > 0, "gemm: bad argument");
-  sgemm(ta, tb, M, N, K, alpha, a, ta ? M : K, b, tb ? K : N, 0.0f, c, N);
+  sgemm_m(ta, tb, M, N, K, alpha, a, ta ? M : K, b, tb ? K : N, 0.0f, c, N);
   return LTB_OK;
 }
 // gemm_grad: TensorDslCPU.scala:428-472 (beta 1 in all eight calls).
@@ -266,17 +297,17 @@ int ora_gemm_grad(const float* a, float* da, int ta, const float* b, float* db, 
                   int M, int N, int K) {
   REQUIRE(a && b && dc && M > 0 && N > 0 && K > 0, "gemm_grad: bad argument");
   if (!ta && !tb) {
-    if (da) sgemm(false, true, M, K, N, alpha, dc, N, b, N, 1.0f, da, K);
-    if (db) sgemm(true, false, K, N, M, alpha, a, K, dc, N, 1.0f, db, N);
+    if (da) sgemm_m(false, true, M, K, N, alpha, dc, N, b, N, 1.0f, da, K);
+    if (db) sgemm_m(true, false, K, N, M, alpha, a, K, dc, N, 1.0f, db, N);
   } else if (!ta && tb) {
-    if (da) sgemm(false, false, M, K, N, alpha, dc, N, b, K, 1.0f, da, K);
-    if (db) sgemm(true, false, N, K, M, alpha, dc, N, a, K, 1.0f, db, K);
+    if (da) sgemm_m(false, false, M, K, N, alpha, dc, N, b, K, 1.0f, da, K);
+    if (db) sgemm_m(true, false, N, K, M, alpha, dc, N, a, K, 1.0f, db, K);
   } else if (ta && !tb) {
-    if (da) sgemm(false, true, K, M, N, alpha, b, N, dc, N, 1.0f, da, M);
-    if (db) sgemm(false, false, K, N, M, alpha, a, M, dc, N, 1.0f, db, N);
+    if (da) sgemm_m(false, true, K, M, N, alpha, b, N, dc, N, 1.0f, da, M);
+    if (db) sgemm_m(false, false, K, N, M, alpha, a, M, dc, N, 1.0f, db, N);
   } else {
-    if (da) sgemm(true, true, K, M, N, alpha, b, K, dc, N, 1.0f, da, M);
-    if (db) sgemm(true, true, N, K, M, alpha, dc, N, a, M, 1.0f, db, K);
+    if (da) sgemm_m(true, true, K, M, N, alpha, b, K, dc, N, 1.0f, da, M);
+    if (db) sgemm_m(true, true, N, K, M, alpha, dc, N, a, M, 1.0f, db, K);
   }
   return LTB_OK;
 }
@@ -330,11 +361,14 @@ int ora_conv2d_fwd(const float* x, const float* w, const float* bias, float* y, 
   REQUIRE(oH > 0 && oW > 0, "conv2d_fwd: empty output");
   size_t ohw = (size_t)oH * oW;
   if (bias) ora_fill_with_bias(y, bias, N, K, (int)ohw); else memset(y, 0, sizeof(float) * N * K * ohw);
+  const bool tf = tc_conv_taken(0, N, C * R * S, K, (int)ohw);
+  std::vector<float> wt; if (tf) { wt = truncated(w, (size_t)K * C * R * S); w = wt.data(); }
   const bool par = g.threads > 1 && N > 1;
 #pragma omp parallel for if (par) num_threads(g.threads) schedule(static)
   for (int t = 0; t < N; ++t) {
     std::vector<float> fin((size_t)C * R * S * ohw);
     unfolded_copy(fin.data(), x + (size_t)t * C * H * W, S, R, sw, sh, pw, ph, C, W, H, oW, oH);
+    if (tf) for (auto& v : fin) v = tf32_trunc(v);
     int save = g.threads; // nested sgemm stays serial inside the parallel region
     (void)save;
     // sgemm body inlined serially to keep per-element summation order
@@ -361,12 +395,17 @@ int ora_conv2d_bwd(const float* x, float* dx, const float* w, float* dw, float* 
   int oH = (H + 2 * ph - R) / sh + 1, oW = (W + 2 * pw - S) / sw + 1;
   size_t ohw = (size_t)oH * oW;
   const int ckk = C * R * S;
+  const float* w_full = w;
   if (dx) {
+    const bool tf = tc_conv_taken(1, N, ckk, K, (int)ohw);
+    std::vector<float> wt, dyt;
+    const float* dy_d = dy;
+    if (tf) { wt = truncated(w, (size_t)K * ckk); w = wt.data(); dyt = truncated(dy, (size_t)N * K * ohw); dy_d = dyt.data(); }
     const bool par = g.threads > 1 && N > 1;
 #pragma omp parallel for if (par) num_threads(g.threads) schedule(static)
     for (int t = 0; t < N; ++t) {
       std::vector<float> fg((size_t)ckk * ohw);
-      const float* go = dy + (size_t)t * K * ohw;
+      const float* go = dy_d + (size_t)t * K * ohw;
       // sgemm(Trans, NoTrans, ckk, ohw, K, 1, w, ckk, go, ohw, 0, fg, ohw)
       for (int i = 0; i < ckk; ++i) {
         float* row = fg.data() + (size_t)i * ohw;
@@ -380,13 +419,16 @@ int ora_conv2d_bwd(const float* x, float* dx, const float* w, float* dw, float* 
       unfolded_acc(fg.data(), dx + (size_t)t * C * H * W, S, R, sw, sh, pw, ph, C, W, H, oW, oH);
     }
   }
+  w = w_full;
   if (dw) {
     // images are visited in order so that dW accumulates image by image as in the reference
-    std::vector<float> fin((size_t)ckk * ohw);
+    const bool tf = tc_conv_taken(2, N, ckk, K, (int)ohw);
+    std::vector<float> fin((size_t)ckk * ohw), got;
     for (int t = 0; t < N; ++t) {
       unfolded_copy(fin.data(), x + (size_t)t * C * H * W, S, R, sw, sh, pw, ph, C, W, H, oW, oH);
       const float* go = dy + (size_t)t * K * ohw;
-      sgemm(false, true, K, ckk, (int)ohw, 1.0f, go, (int)ohw, fin.data(), (int)ohw, 1.0f, dw, ckk);
+      if (tf) { for (auto& v : fin) v = tf32_trunc(v); got = truncated(go, (size_t)K * ohw); }
+      sgemm(false, true, K, ckk, (int)ohw, 1.0f, tf ? got.data() : go, (int)ohw, fin.data(), (int)ohw, 1.0f, dw, ckk);
       if (dbias)
         for (int i = 0; i < K; ++i) {
           float s = 0.0f; const float* d = go + (size_t)i * ohw;

@@ -33,6 +33,7 @@ def oracle_lib():
 def ora(oracle_lib):
     from lantern_b200.backend import Backend
     mark = oracle_lib.mark()
+    oracle_lib.set_math(0)           # plain FP32: the reference's CPU backend; TF32 tests switch the emulation on themselves
     yield Backend(oracle_lib)
     oracle_lib.reset(mark)
 
@@ -51,6 +52,7 @@ def cuda_lib():
 def gpu(cuda_lib):
     from lantern_b200.backend import Backend
     mark = cuda_lib.mark()
+    cuda_lib.set_math(1)
     yield Backend(cuda_lib)
     cuda_lib.sync()
     assert cuda_lib.device_status() == 0
