@@ -6,14 +6,15 @@
 //   warp 1      : owns the tensor memory (tcgen05.alloc / dealloc) and issues tcgen05.mma.kind::tf32 (M = 128, N = tile
 //                 width, K = 8) from one lane, four per stage, accumulating in TMEM; tcgen05.commit releases the stage
 //                 ("empty" mbarrier) and finally signals the epilogue.
-//   warps 2..5  : epilogue.  Each warp reads its 32-lane quarter of the accumulator with tcgen05.ld (32 columns at a time)
+//   warps 2..9  : epilogue.  Each warp reads its 32-lane quarter of the accumulator with tcgen05.ld (32 columns at a time)
 //                 and writes the result: pixel-major for convolutions (a warp store covers 32 consecutive pixels of one
 //                 channel: 128 contiguous bytes), row-major for gemm / weight-grad; optional bias, alpha, accumulation,
 //                 and atomic accumulation under split-K.
 // Activations stay NCHW: the pixel index is the contiguous one, so the activation operand is fed M/N-major (tcgen05 allows
 // it for tf32) straight from the tensor with a 4-D tiled tensor map; no layout conversion pass exists.
 // Every mbarrier wait is bounded: after about a second it records a code in the library's device status word and the CTA
-// runs to its normal teardown (TMEM is released on every path).
+// runs to its normal teardown (TMEM is released on every path).  The single issuing lanes of warps 0 and 1 are rejoined by
+// their warps (__syncwarp) before the block-wide barrier, which needs converged warps.
 #include <cuda.h>
 
 #include "gemm.cuh"
@@ -24,8 +25,8 @@ extern "C" int ltb_free(void* p, size_t bytes);
 
 namespace ltb {
 
-constexpr int kStages = 4;
-constexpr int kTcThreads = 192;
+constexpr int kMaxStages = 4;
+constexpr int kTcThreads = 320;                    // warp 0 TMA, warp 1 MMA, warps 2..9 epilogue
 constexpr long long kWaitCycles = 2000000000ll;    // bound of every spin wait (~1 s)
 
 struct TcOperandDev {
@@ -36,12 +37,13 @@ struct TcOperandDev {
 };
 struct TcParams {
   TcOperandDev a, b;
-  int M, N, bn, k_iters, k_per_split, epilogue, accumulate, atomic;
+  int M, N, bn, k_iters, k_per_split, epilogue, accumulate, atomic, stages;
   uint32_t idesc;
   float* out; const float* bias; float alpha;
   long long pix_per_img, img_stride, chan_stride, ld;
   int* status;
-  float* dump;                 // diagnostics: when set, CTA (0,0,0) copies its first stage (A then B) here before the first MMA
+  float* dump;                 // diagnostics buffer of CTA (0,0,0): mode 1 copies its first stage (A then B), mode 2 records cycle stamps
+  int dump_mode;
 };
 
 // ---- PTX wrappers ---------------------------------------------------------------------------------------------------
@@ -105,17 +107,67 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t* r) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-__device__ __forceinline__ void box_coords(const TcOperandDev& o, int tile, int kiter, int* c) {
+// Box coordinates of an operand: c[d] = tile part (fixed for the CTA) + ((kiter / k_div[d]) % k_mod[d]) * k_mul[d].
+// The k part is advanced incrementally with additions only: the producer is a single thread, and integer divisions or
+// branches per dimension cost it more cycles than the loads it issues.  Plans have at most one "inner" group of dimensions
+// (k_div == 1) that may wrap after `wrap` iterations, and one "outer" group (k_div == wrap) that then advances.
+struct BoxWalker {
+  int c[5], inc[5], back[5], i, wrap;
+  __device__ __forceinline__ void init(const TcOperandDev& o, int tile, int k0) {
+    wrap = 0;
 #pragma unroll
-  for (int d = 0; d < 5; ++d) c[d] = ((tile / o.t_div[d]) % o.t_mod[d]) * o.t_mul[d] + ((kiter / o.k_div[d]) % o.k_mod[d]) * o.k_mul[d];
-}
+    for (int d = 0; d < 5; ++d) if (o.k_mul[d] != 0 && o.k_div[d] > 1) wrap = o.k_div[d];
+    i = wrap ? k0 % wrap : 0;
+#pragma unroll
+    for (int d = 0; d < 5; ++d) {
+      c[d] = ((tile / o.t_div[d]) % o.t_mod[d]) * o.t_mul[d] + ((k0 / o.k_div[d]) % o.k_mod[d]) * o.k_mul[d];
+      const bool inner = o.k_mul[d] != 0 && o.k_div[d] == 1;
+      inc[d] = inner ? o.k_mul[d] : 0;
+      // on a wrap the inner dimensions return to their start and the outer ones advance
+      back[d] = inner ? -o.k_mul[d] * (wrap - 1) : ((o.k_mul[d] != 0 && o.k_div[d] > 1) ? o.k_mul[d] : 0);
+    }
+  }
+  __device__ __forceinline__ void next() {
+    if (wrap && ++i == wrap) {
+      i = 0;
+#pragma unroll
+      for (int d = 0; d < 5; ++d) c[d] += back[d];
+    } else {
+#pragma unroll
+      for (int d = 0; d < 5; ++d) c[d] += inc[d];
+    }
+  }
+};
 
 // ---- the engine -------------------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(kTcThreads, 1)
+// Epilogue store helpers: pointers advance by the column stride instead of being recomputed, and the mode (plain, bias,
+// accumulate, atomic) is decided outside the 32-element loops, so that a column costs two or three instructions.  With one
+// epilogue warp per scheduler every extra dependent instruction is exposed latency.
+template <bool FULL>
+__device__ __forceinline__ void store_columns(float* p, long long stride, const uint32_t* r, float alpha, const float* bias, int lim, int mode) {
+  if (mode == 2) {                               // split-K: atomic accumulation
+#pragma unroll
+    for (int j = 0; j < 32; ++j) { if (FULL || j < lim) atomicAdd(p, alpha * __uint_as_float(r[j])); p += stride; }
+  } else if (mode == 1) {                        // accumulate: all loads first, a load-add-store chain per element would serialise on latency
+    float old[32]; const float* q = p;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) { old[j] = (FULL || j < lim) ? *q : 0.0f; q += stride; }
+#pragma unroll
+    for (int j = 0; j < 32; ++j) { if (FULL || j < lim) *p = old[j] + alpha * __uint_as_float(r[j]); p += stride; }
+  } else if (bias) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) { if (FULL || j < lim) *p = alpha * __uint_as_float(r[j]) + bias[j]; p += stride; }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) { if (FULL || j < lim) *p = alpha * __uint_as_float(r[j]); p += stride; }
+  }
+}
+
+__global__ void __launch_bounds__(kTcThreads, 2)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ TcParams P) {
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t full_bar[kStages];
-  __shared__ __align__(8) uint64_t empty_bar[kStages];
+  __shared__ __align__(8) uint64_t full_bar[kMaxStages];
+  __shared__ __align__(8) uint64_t empty_bar[kMaxStages];
   __shared__ __align__(8) uint64_t accum_bar;
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
@@ -125,13 +177,20 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const int k_begin = blockIdx.z * P.k_per_split;
   const int k_end = min(P.k_iters, k_begin + P.k_per_split);
   const int n_iter = k_end - k_begin;
+  const int stages = P.stages;
+  // diagnostics: with a dump buffer set, CTA (0,0,0) records cycle stamps of its phases at dump[65536 + i]
+  const bool stamp = P.dump && P.dump_mode == 2 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+  const long long t_start = stamp ? clock64() : 0;
+#define LTB_STAMP(i) do { if (stamp) P.dump[65536 + (i)] = (float)(clock64() - t_start); } while (0)
 
   // stage buffers, aligned to the 1024-byte swizzle atom
   uint8_t* stage_base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const uint32_t stage_bytes = P.a.stage_bytes + P.b.stage_bytes;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_a)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_b)) : "memory");
+    for (int s = 0; s < stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
     mbar_init(&accum_bar, 1);
     abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -145,28 +204,34 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_slot;
+  if (threadIdx.x == 0) LTB_STAMP(0);        // set-up done
 
   if (warp == 0) {
     if (lane == 0 && n_iter > 0) {
+      int s = 0; uint32_t ph = 0;
+      BoxWalker wa, wb;
+      wa.init(P.a, m_tile, k_begin); wb.init(P.b, n_tile, k_begin);
       for (int it = 0; it < n_iter; ++it) {
-        const int s = it % kStages; const uint32_t ph = (uint32_t)(it / kStages) & 1u;
         if (!mbar_wait(&empty_bar[s], ph ^ 1u, &abort_flag, P.status, 1)) break;
         uint8_t* sa = stage_base + (size_t)s * stage_bytes; uint8_t* sb = sa + P.a.stage_bytes;
         mbar_expect_tx(&full_bar[s], stage_bytes);
-        int c[5];
-        box_coords(P.a, m_tile, k_begin + it, c); tma_load(&map_a, &full_bar[s], sa, P.a.rank, c);
-        box_coords(P.b, n_tile, k_begin + it, c); tma_load(&map_b, &full_bar[s], sb, P.b.rank, c);
+        if (it < 24) LTB_STAMP(40 + it);      // issue time of each of the first loads
+        tma_load(&map_a, &full_bar[s], sa, P.a.rank, wa.c); wa.next();
+        tma_load(&map_b, &full_bar[s], sb, P.b.rank, wb.c); wb.next();
+        if (++s == stages) { s = 0; ph ^= 1u; }
       }
     }
+    __syncwarp();          // the idle lanes wait here for the issuing lane: the block-wide barrier below needs converged warps
   } else if (warp == 1) {
     if (lane == 0 && n_iter > 0) {
-      bool ok = true;
-      for (int it = 0; it < n_iter && ok; ++it) {
-        const int s = it % kStages; const uint32_t ph = (uint32_t)(it / kStages) & 1u;
+      bool ok = true; int s = 0; uint32_t ph = 0;
+      for (int it = 0; it < n_iter; ++it) {
         ok = mbar_wait(&full_bar[s], ph, &abort_flag, P.status, 2);
         if (!ok) break;
+        if (it == 0) LTB_STAMP(1);           // first stage landed
+        if (it < 24) LTB_STAMP(8 + it);      // arrival of each of the first stages
         tc_fence_after();
-        if (P.dump && it == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+        if (P.dump && P.dump_mode == 1 && it == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
           const float* src = reinterpret_cast<const float*>(stage_base);
           for (uint32_t i = 0; i < stage_bytes / 4; ++i) P.dump[i] = src[i];
         }
@@ -178,45 +243,80 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           tc_mma_tf32(tmem_base, adesc, bdesc, P.idesc, (it > 0 || k > 0) ? 1u : 0u);
         }
         tc_commit(&empty_bar[s]);       // the stage may be refilled once these MMAs have read it
+        if (++s == stages) { s = 0; ph ^= 1u; }
       }
       if (ok) tc_commit(&accum_bar);    // accumulator complete
+      LTB_STAMP(2);                          // all MMAs issued
     }
+    __syncwarp();
   } else if (n_iter > 0) {
-    // ---- epilogue warps 2..5: TMEM lane quarter = warp index mod 4
-    const int q = warp & 3, row = q * 32 + lane;
-    const long long m = (long long)m_tile * 128 + row;
+    // ---- epilogue warps 2..9: TMEM lane quarter = warp index mod 4; the two warps of a quarter take alternate 32-column chunks
+    const int q = warp & 3, half = (warp - 2) >> 2;
     const bool ok = mbar_wait(&accum_bar, 0, &abort_flag, P.status, 3);
     tc_fence_after();
+    if (threadIdx.x == 64) LTB_STAMP(3);     // accumulator visible to the epilogue
     if (ok) {
       const int n0 = n_tile * P.bn;
-      float* dst = nullptr;
-      if (m < P.M) {
-        if (P.epilogue == TC_EPI_PIXEL) dst = P.out + (m / P.pix_per_img) * P.img_stride + (m % P.pix_per_img);
-        else dst = P.out + m * P.ld;
-      }
-      for (int c0 = 0; c0 < P.bn; c0 += 32) {
-        if (n0 + c0 >= P.N) break;                         // uniform across the warp
-        uint32_t r[32];
-        tc_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
-        if (dst) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int n = n0 + c0 + j;
-            if (n < P.N) {
-              float v = P.alpha * __uint_as_float(r[j]);
-              if (P.bias) v += P.bias[n];
-              float* q_ = P.epilogue == TC_EPI_PIXEL ? dst + (long long)n * P.chan_stride : dst + n;
-              if (P.atomic) atomicAdd(q_, v);
-              else if (P.accumulate) *q_ += v;
-              else *q_ = v;
-            }
+      const float alpha = P.alpha;
+      const int mode = P.atomic ? 2 : (P.accumulate ? 1 : 0);
+      const uint32_t tmem_row = tmem_base + ((uint32_t)(q * 32) << 16);
+      if (P.epilogue == TC_EPI_PIXEL) {
+        // lane = pixel, register j = channel: for a fixed j a warp covers 32 consecutive pixels (128 contiguous bytes)
+        const long long m = (long long)m_tile * 128 + q * 32 + lane;
+        const long long cs = P.chan_stride;
+        float* dst = m < P.M ? P.out + (m / P.pix_per_img) * P.img_stride + (m % P.pix_per_img) : nullptr;
+        for (int c0 = half * 32; c0 < P.bn; c0 += 64) {
+          if (n0 + c0 >= P.N) break;                         // uniform across the warp
+          uint32_t r[32];
+          tc_ld32(tmem_row + (uint32_t)c0, r);
+          if (threadIdx.x == 64 && c0 == 0) LTB_STAMP(6);    // first accumulator chunk in registers
+          if (dst) {
+            const int lim = P.N - n0 - c0;
+            const float* bias = P.bias ? P.bias + n0 + c0 : nullptr;
+            if (lim >= 32) store_columns<true>(dst + (long long)(n0 + c0) * cs, cs, r, alpha, bias, 32, mode);
+            else store_columns<false>(dst + (long long)(n0 + c0) * cs, cs, r, alpha, bias, lim, mode);
           }
+          if (threadIdx.x == 64 && c0 == 0) LTB_STAMP(7);    // first chunk's stores issued
+        }
+      } else {
+        // row-major output: transpose each 32x32 block through shared memory so that a warp writes 32 consecutive columns
+        // of one row (128 contiguous bytes) per instruction.  The staging tile lives in the pipeline stages, which are idle
+        // once the accumulator is complete (every load has landed and every MMA has read its operands).
+        float (*tile)[33] = reinterpret_cast<float (*)[33]>(stage_base + (size_t)(warp - 2) * 32 * 33 * 4);
+        const long long m0 = (long long)m_tile * 128 + q * 32;
+        const int rows = (int)min(32ll, (long long)P.M - m0);
+        const long long ld = P.ld;
+        for (int c0 = half * 32; c0 < P.bn; c0 += 64) {
+          if (n0 + c0 >= P.N) break;
+          uint32_t r[32];
+          tc_ld32(tmem_row + (uint32_t)c0, r);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) tile[lane][j] = __uint_as_float(r[j]);
+          __syncwarp();
+          const int n = n0 + c0 + lane;
+          if (n < P.N && rows > 0) {
+            uint32_t t[32];
+#pragma unroll
+            for (int rr = 0; rr < 32; ++rr) t[rr] = __float_as_uint(tile[rr][lane]);
+            // after the transpose the "columns" of store_columns are the 32 rows of this block, `ld` apart
+            const float* bias = nullptr;
+            float* p = P.out + m0 * ld + n;
+            if (P.bias && mode == 0) {
+              const float bv = P.bias[n];
+#pragma unroll
+              for (int rr = 0; rr < 32; ++rr) { if (rr < rows) *p = alpha * __uint_as_float(t[rr]) + bv; p += ld; }
+            } else if (rows == 32) store_columns<true>(p, ld, t, alpha, bias, 32, mode);
+            else store_columns<false>(p, ld, t, alpha, bias, rows, mode);
+          }
+          __syncwarp();
         }
       }
     }
   }
+  if (threadIdx.x == 64) LTB_STAMP(4);       // epilogue of warp 2 done
   tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0) LTB_STAMP(5);        // all warps done
   if (warp == 1) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)P.bn) : "memory");
@@ -225,14 +325,26 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
 // ---- unfold / fold helpers for convolutions that are not 1x1 stride 1 ---------------------------------------------------
 // col[n][(c*R+r)*S+s][p] = x[n][c][ho*sh-ph+r][wo*sw-pw+s] (0 outside): the reference's `finput` (TensorDslCPU.scala:484-530).
-// ROWS: the same values written as the K-major row matrix col[(n*pix + p)][k] (for images too small to be fed M/N-major).
-template <bool ROWS>
-__global__ void unfold_kernel(const float* __restrict__ x, float* __restrict__ col, ConvDims d, int64_t total) {
+// One thread block row per (n, k): the (c, r, s) decomposition is done once per row, the pixel loop only adds.
+__global__ void unfold_rows_kernel(const float* __restrict__ x, float* __restrict__ col, ConvDims d, int rows_per_block, int threads_per_row) {
+  const int pix = d.oH * d.oW, rs = d.R * d.S, ck = d.C * rs;
+  const int64_t row = (int64_t)blockIdx.x * rows_per_block + threadIdx.x / threads_per_row;
+  if (row >= (int64_t)d.N * ck) return;
+  const int k = (int)(row % ck); const int64_t n = row / ck;
+  const int c = k / rs, r = (k % rs) / d.S, s = k % d.S;
+  const float* src = x + (n * d.C + c) * (int64_t)d.H * d.W;
+  float* dst = col + row * pix;
+  for (int p = threadIdx.x % threads_per_row; p < pix; p += threads_per_row) {
+    const int ho = p / d.oW, wo = p - ho * d.oW;
+    const int ih = ho * d.sh - d.ph + r, iw = wo * d.sw - d.pw + s;
+    dst[p] = (ih >= 0 && ih < d.H && iw >= 0 && iw < d.W) ? src[ih * d.W + iw] : 0.0f;
+  }
+}
+// The same values written as the K-major row matrix col[(n*pix + p)][k] (for images too small to be fed M/N-major).
+__global__ void unfold_to_rows_kernel(const float* __restrict__ x, float* __restrict__ col, ConvDims d, int64_t total) {
   const int pix = d.oH * d.oW, rs = d.R * d.S, ck = d.C * rs;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-    int p, k, n;
-    if (ROWS) { k = (int)(i % ck); int64_t t = i / ck; p = (int)(t % pix); n = (int)(t / pix); }
-    else { p = (int)(i % pix); int64_t t = i / pix; k = (int)(t % ck); n = (int)(t / ck); }
+    int k = (int)(i % ck); int64_t t = i / ck; int p = (int)(t % pix); int n = (int)(t / pix);
     int c = k / rs, r = (k % rs) / d.S, s = k % d.S;
     int ih = (p / d.oW) * d.sh - d.ph + r, iw = (p % d.oW) * d.sw - d.pw + s;
     col[i] = (ih >= 0 && ih < d.H && iw >= 0 && iw < d.W) ? x[(((int64_t)n * d.C + c) * d.H + ih) * d.W + iw] : 0.0f;
@@ -246,23 +358,28 @@ __global__ void to_rows_kernel(const float* __restrict__ src, float* __restrict_
   }
 }
 // dx[n][c][h][w] += sum over the (r,s) taps that reach (h,w): gather form of unfoldedAcc (TensorDslCPU.scala:647-692).
-__global__ void fold_acc_kernel(const float* __restrict__ col, float* dx, ConvDims d, int64_t total) {
-  const int pix = d.oH * d.oW;
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-    int w = (int)(i % d.W); int64_t t = i / d.W; int h = (int)(t % d.H); t /= d.H; int c = (int)(t % d.C); int n = (int)(t / d.C);
+// One block row per (n, c) plane; the tap loops run over at most R*S entries of the unfolded gradient.
+__global__ void fold_acc_kernel(const float* __restrict__ col, float* dx, ConvDims d, int planes_per_block, int threads_per_plane) {
+  const int pix = d.oH * d.oW, hw = d.H * d.W;
+  const int64_t plane = (int64_t)blockIdx.x * planes_per_block + threadIdx.x / threads_per_plane;
+  if (plane >= (int64_t)d.N * d.C) return;
+  const float* src = col + plane * d.R * d.S * pix;          // rows (c*R + r)*S + s of image n start here
+  float* dst = dx + plane * hw;
+  for (int i = threadIdx.x % threads_per_plane; i < hw; i += threads_per_plane) {
+    const int h = i / d.W, w = i - h * d.W;
     float acc = 0.0f;
     for (int r = 0; r < d.R; ++r) {
-      int hs = h + d.ph - r;
+      const int hs = h + d.ph - r;
       if (hs < 0 || hs % d.sh) continue;
-      int ho = hs / d.sh; if (ho >= d.oH) continue;
+      const int ho = hs / d.sh; if (ho >= d.oH) continue;
       for (int s = 0; s < d.S; ++s) {
-        int ws = w + d.pw - s;
+        const int ws = w + d.pw - s;
         if (ws < 0 || ws % d.sw) continue;
-        int wo = ws / d.sw; if (wo >= d.oW) continue;
-        acc += col[((int64_t)n * d.C * d.R * d.S + (c * d.R + r) * d.S + s) * pix + ho * d.oW + wo];
+        const int wo = ws / d.sw; if (wo >= d.oW) continue;
+        acc += src[(r * d.S + s) * pix + ho * d.oW + wo];
       }
     }
-    dx[i] += acc;
+    dst[i] += acc;
   }
 }
 
@@ -271,6 +388,7 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 static EncodeTiledFn encode_tiled = nullptr;
 static float* debug_dump = nullptr;
+static int debug_dump_mode = 1;
 static bool smem_opted_in = false;
 
 static int encode_map(const TcTensorMap& m, CUtensorMap* out) {
@@ -315,10 +433,12 @@ static int launch_plan(const TcPlan& p, const char* label) {
   P.idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)p.a.mn_major << 15) | ((uint32_t)p.b.mn_major << 16) | ((uint32_t)(p.bn >> 3) << 17) | ((128u >> 4) << 24);
   P.out = p.out; P.bias = p.bias; P.alpha = p.alpha;
   P.pix_per_img = p.pix_per_img ? p.pix_per_img : 1; P.img_stride = p.img_stride; P.chan_stride = p.chan_stride; P.ld = p.ld;
-  P.status = g.dev_status; P.dump = debug_dump;
-  const size_t smem = (size_t)kStages * (p.a.stage_bytes + p.b.stage_bytes) + 1024;
+  P.status = g.dev_status; P.dump = debug_dump; P.dump_mode = debug_dump_mode;
+  // 4 stages, except 3 for 128-wide tiles so that two CTAs (2 x 97 KB) share an SM and one's epilogue overlaps the other's main loop
+  P.stages = p.bn == 128 ? 3 : kMaxStages;
+  const size_t smem = (size_t)P.stages * (p.a.stage_bytes + p.b.stage_bytes) + 1024;
   if (!smem_opted_in) {
-    LTB_CUDA(cudaFuncSetAttribute(tc_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kStages * (16384 + 32768) + 1024));
+    LTB_CUDA(cudaFuncSetAttribute(tc_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxStages * (16384 + 32768) + 1024));
     smem_opted_in = true;
   }
   const char* saved = g.label; g.label = label;
@@ -330,7 +450,7 @@ static int launch_plan(const TcPlan& p, const char* label) {
 
 }  // namespace ltb
 // Diagnostics hook (not part of the public header): the next engine launches copy the first pipeline stage of CTA (0,0,0) to buf.
-extern "C" int ltb_debug_tc_dump(float* buf) { ltb::debug_dump = buf; return 0; }
+extern "C" int ltb_debug_tc_dump(float* buf, int mode) { ltb::debug_dump = buf; ltb::debug_dump_mode = mode; return 0; }
 namespace ltb {
 
 int gemm_tc(const float* a, bool a_kmajor, const float* b, bool b_kmajor, float* c, bool, int M, int N, int K, float alpha, bool accumulate) {
@@ -340,6 +460,22 @@ int gemm_tc(const float* a, bool a_kmajor, const float* b, bool b_kmajor, float*
   return rc ? rc : 1;
 }
 
+static int launch_unfold(const float* x, float* col, const ConvDims& d) {
+  const int pix = d.oH * d.oW;
+  int tpr = 32; while (tpr < pix && tpr < 256) tpr <<= 1;      // threads per row: a power of two in [32, 256]
+  const int rpb = 256 / tpr;
+  const int64_t rows = (int64_t)d.N * d.C * d.R * d.S;
+  LTB_LAUNCH(unfold_rows_kernel, (unsigned)ceil_div(rows, rpb), 256, 0, x, col, d, rpb, tpr);
+  return LTB_OK;
+}
+static int launch_fold(const float* col, float* dx, const ConvDims& d) {
+  const int hw = d.H * d.W;
+  int tpp = 32; while (tpp < hw && tpp < 256) tpp <<= 1;
+  const int ppb = 256 / tpp;
+  const int64_t planes = (int64_t)d.N * d.C;
+  LTB_LAUNCH(fold_acc_kernel, (unsigned)ceil_div(planes, ppb), 256, 0, col, dx, d, ppb, tpp);
+  return LTB_OK;
+}
 static bool is_pointwise(const ConvDims& d) { return d.R == 1 && d.S == 1 && d.sh == 1 && d.sw == 1 && d.ph == 0 && d.pw == 0; }
 static float* temp_alloc(size_t floats) {
   size_t bytes = (floats * 4 + kGranule - 1) / kGranule * kGranule;
@@ -357,8 +493,8 @@ static int stage_activation(const float* src, bool unfold, const ConvDims& d, in
   if (!buf) return 1;
   *temp = buf; *temp_floats = n; *op = buf;
   if (unfold) {
-    if (*rows) LTB_LAUNCH(unfold_kernel<true>, grid_for((int64_t)n, 256), 256, 0, src, buf, d, (int64_t)n);
-    else LTB_LAUNCH(unfold_kernel<false>, grid_for((int64_t)n, 256), 256, 0, src, buf, d, (int64_t)n);
+    if (*rows) LTB_LAUNCH(unfold_to_rows_kernel, grid_for((int64_t)n, 256), 256, 0, src, buf, d, (int64_t)n);
+    else { int rc = launch_unfold(src, buf, d); if (rc) return rc; }
   } else {
     LTB_LAUNCH(to_rows_kernel, grid_for((int64_t)n, 256), 256, 0, src, buf, chan, pix, (int64_t)n);
   }
@@ -392,10 +528,7 @@ int conv_dgrad_tc(const float* dy, const float* w, float* dx, const ConvDims& d)
   if (!direct) { col = temp_alloc(ncol); if (!col) { if (temp) ltb_free(temp, tn * 4); return 0; } }
   bool ok = tc_plan_conv_dgrad(p, op, rows, w, direct ? dx : col, d.N, ck, d.K, pix, direct, g.sm_count);
   rc = ok ? launch_plan(p, "tc_gemm_kernel[conv_dgrad]") : 0;
-  if (ok && !rc && !direct) {
-    const int64_t nx = (int64_t)d.N * d.C * d.H * d.W;
-    LTB_LAUNCH(fold_acc_kernel, grid_for(nx, 256), 256, 0, (const float*)col, dx, d, nx);
-  }
+  if (ok && !rc && !direct) rc = launch_fold(col, dx, d);
   if (col) ltb_free(col, ncol * 4);
   if (temp) ltb_free(temp, tn * 4);
   return !ok ? 0 : (rc ? rc : 1);
@@ -408,7 +541,7 @@ int conv_wgrad_tc(const float* x, const float* dy, float* dw, const ConvDims& d)
   const float* xin = x; float* col = nullptr; const size_t n = (size_t)d.N * ck * pix;
   if (!is_pointwise(d)) {
     col = temp_alloc(n); if (!col) return 0;
-    LTB_LAUNCH(unfold_kernel<false>, grid_for((int64_t)n, 256), 256, 0, x, col, d, (int64_t)n);
+    int rc0 = launch_unfold(x, col, d); if (rc0) return rc0;
     xin = col;
   }
   tc_plan_conv_wgrad(p, xin, dy, dw, d.N, ck, d.K, pix, g.sm_count);

@@ -192,7 +192,7 @@ bool tc_plan_conv_wgrad(TcPlan& p, const float* x, const float* dy, float* dw, i
   if (co < 16 || ck < 16) return false;
   int ka = 0, kb = 0;
   if (!operand_k_pixels(p.a, dy, n_img, co, pix, kTileM, &ka)) return false;
-  p.bn = pick_bn(ck, cdiv(co, kTileM), 0);            // largest tile that fits: the grid is filled by split-K
+  p.bn = pick_bn(ck, cdiv(co, kTileM), sm_count);     // narrower tiles before more split-K: fewer atomic partial sums
   if (!operand_k_pixels(p.b, x, n_img, ck, pix, p.bn, &kb) || ka != kb) return false;
   finish(p, co, ck, ka, sm_count, true);
   p.epilogue = TC_EPI_ROWMAJOR; p.out = dw; p.bias = nullptr; p.alpha = 1.0f; p.accumulate = 1; p.ld = ck;
