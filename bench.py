@@ -83,6 +83,8 @@ class ClockSampler:
 
     def stop(self):
         if self.proc:
+            if not self.rows:
+                time.sleep(0.3)            # a very short timed region: give the sampler time for one line
             self.proc.terminate()
         sm, mx, reasons = [], [], set()
         for r in self.rows:
@@ -218,14 +220,13 @@ def main():
 
     # ---- value: device-resident batch, the recorded step replayed back to back
     model.set_resident(*pool[0])
+    sampler = ClockSampler(local); sampler.start()        # sampled from the warm-up on: all of it is under the same load
     for _ in range(args.warmup):
-        model.step_async(None if False else pool[0][0], pool[0][1], LR)
+        model.step_async(pool[0][0], pool[0][1], LR)
     lib.sync()
-    sampler = ClockSampler(local); sampler.start()
     l0 = lib.kernel_launches()
     ms = timed(lambda i: model.step_async(pool[0][0], pool[0][1], LR), args.steps)
     launches = lib.kernel_launches() - l0
-    clocks = sampler.stop()
     loss_resident = model.last_loss()
     value = BATCH * world * args.steps / (ms / 1e3)
 
@@ -241,6 +242,7 @@ def main():
     for i in range(3):
         e2e_step(i)
     ms_e2e = timed(e2e_step, args.steps)
+    clocks = sampler.stop()
     e2e = BATCH * world * args.steps / (ms_e2e / 1e3)
 
     # ---- per-kernel timing of one eagerly issued step (CUDA events on the launching stream around every launch)

@@ -117,10 +117,12 @@ struct BoxWalker {
     wrap = 0;
 #pragma unroll
     for (int d = 0; d < 5; ++d) if (o.k_mul[d] != 0 && o.k_div[d] > 1) wrap = o.k_div[d];
-    i = wrap ? k0 % wrap : 0;
+    i = (wrap && k0) ? k0 % wrap : 0;
 #pragma unroll
     for (int d = 0; d < 5; ++d) {
-      c[d] = ((tile / o.t_div[d]) % o.t_mod[d]) * o.t_mul[d] + ((k0 / o.k_div[d]) % o.k_mod[d]) * o.k_mul[d];
+      c[d] = 0;                                   // divisions only for the one or two dimensions that use them
+      if (o.t_mul[d] != 0) c[d] = ((o.t_div[d] > 1 ? tile / o.t_div[d] : tile) % o.t_mod[d]) * o.t_mul[d];
+      if (o.k_mul[d] != 0 && k0 != 0) c[d] += ((o.k_div[d] > 1 ? k0 / o.k_div[d] : k0) % o.k_mod[d]) * o.k_mul[d];
       const bool inner = o.k_mul[d] != 0 && o.k_div[d] == 1;
       inc[d] = inner ? o.k_mul[d] : 0;
       // on a wrap the inner dimensions return to their start and the outer ones advance
@@ -145,9 +147,9 @@ struct BoxWalker {
 // epilogue warp per scheduler every extra dependent instruction is exposed latency.
 template <bool FULL>
 __device__ __forceinline__ void store_columns(float* p, long long stride, const uint32_t* r, float alpha, const float* bias, int lim, int mode) {
-  if (mode == 2) {                               // split-K: atomic accumulation
+  if (mode == 2) {                               // split-K: atomic accumulation (the bias pointer is set for split 0 only)
 #pragma unroll
-    for (int j = 0; j < 32; ++j) { if (FULL || j < lim) atomicAdd(p, alpha * __uint_as_float(r[j])); p += stride; }
+    for (int j = 0; j < 32; ++j) { if (FULL || j < lim) atomicAdd(p, alpha * __uint_as_float(r[j]) + (bias ? bias[j] : 0.0f)); p += stride; }
   } else if (mode == 1) {                        // accumulate: all loads first, a load-add-store chain per element would serialise on latency
     float old[32]; const float* q = p;
 #pragma unroll
@@ -225,6 +227,13 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   } else if (warp == 1) {
     if (lane == 0 && n_iter > 0) {
       bool ok = true; int s = 0; uint32_t ph = 0;
+      // descriptor pieces that do not change: kept in registers so that an MMA costs two additions and the instruction
+      uint32_t koa[4], kob[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) { koa[k] = P.a.kstep_off[k] >> 4; kob[k] = P.b.kstep_off[k] >> 4; }
+      const uint64_t a_hi = (uint64_t)P.a.desc_hi << 32, b_hi = (uint64_t)P.b.desc_hi << 32;
+      const uint32_t a_lo = P.a.desc_lo, b_lo = P.b.desc_lo, idesc = P.idesc, a_bytes = P.a.stage_bytes;
+      const uint32_t ring = smem_u32(stage_base);
       for (int it = 0; it < n_iter; ++it) {
         ok = mbar_wait(&full_bar[s], ph, &abort_flag, P.status, 2);
         if (!ok) break;
@@ -235,12 +244,12 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           const float* src = reinterpret_cast<const float*>(stage_base);
           for (uint32_t i = 0; i < stage_bytes / 4; ++i) P.dump[i] = src[i];
         }
-        const uint32_t sa = smem_u32(stage_base + (size_t)s * stage_bytes), sb = sa + P.a.stage_bytes;
-        for (int k = 0; k < P.a.nk; ++k) {
-          const uint32_t aa = sa + P.a.kstep_off[k], bb = sb + P.b.kstep_off[k];
-          const uint64_t adesc = ((uint64_t)P.a.desc_hi << 32) | (uint64_t)(P.a.desc_lo | ((aa >> 4) & 0x3FFFu));
-          const uint64_t bdesc = ((uint64_t)P.b.desc_hi << 32) | (uint64_t)(P.b.desc_lo | ((bb >> 4) & 0x3FFFu));
-          tc_mma_tf32(tmem_base, adesc, bdesc, P.idesc, (it > 0 || k > 0) ? 1u : 0u);
+        const uint32_t sa = (ring + (uint32_t)s * stage_bytes) >> 4, sb = sa + (a_bytes >> 4);   // in 16-byte units (ring < 256 KB: 14 bits)
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const uint64_t adesc = a_hi | (uint64_t)(a_lo | ((sa + koa[k]) & 0x3FFFu));
+          const uint64_t bdesc = b_hi | (uint64_t)(b_lo | ((sb + kob[k]) & 0x3FFFu));
+          tc_mma_tf32(tmem_base, adesc, bdesc, idesc, (it > 0 || k > 0) ? 1u : 0u);
         }
         tc_commit(&empty_bar[s]);       // the stage may be refilled once these MMAs have read it
         if (++s == stages) { s = 0; ph ^= 1u; }
@@ -272,7 +281,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           if (threadIdx.x == 64 && c0 == 0) LTB_STAMP(6);    // first accumulator chunk in registers
           if (dst) {
             const int lim = P.N - n0 - c0;
-            const float* bias = P.bias ? P.bias + n0 + c0 : nullptr;
+            const float* bias = (P.bias && blockIdx.z == 0) ? P.bias + n0 + c0 : nullptr;
             if (lim >= 32) store_columns<true>(dst + (long long)(n0 + c0) * cs, cs, r, alpha, bias, 32, mode);
             else store_columns<false>(dst + (long long)(n0 + c0) * cs, cs, r, alpha, bias, lim, mode);
           }
@@ -325,19 +334,30 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
 // ---- unfold / fold helpers for convolutions that are not 1x1 stride 1 ---------------------------------------------------
 // col[n][(c*R+r)*S+s][p] = x[n][c][ho*sh-ph+r][wo*sw-pw+s] (0 outside): the reference's `finput` (TensorDslCPU.scala:484-530).
-// One thread block row per (n, k): the (c, r, s) decomposition is done once per row, the pixel loop only adds.
-__global__ void unfold_rows_kernel(const float* __restrict__ x, float* __restrict__ col, ConvDims d, int rows_per_block, int threads_per_row) {
-  const int pix = d.oH * d.oW, rs = d.R * d.S, ck = d.C * rs;
-  const int64_t row = (int64_t)blockIdx.x * rows_per_block + threadIdx.x / threads_per_row;
-  if (row >= (int64_t)d.N * ck) return;
-  const int k = (int)(row % ck); const int64_t n = row / ck;
-  const int c = k / rs, r = (k % rs) / d.S, s = k % d.S;
-  const float* src = x + (n * d.C + c) * (int64_t)d.H * d.W;
-  float* dst = col + row * pix;
-  for (int p = threadIdx.x % threads_per_row; p < pix; p += threads_per_row) {
+// A thread owns one output pixel of one input plane (n, c) and writes all R*S taps of it: the plane and pixel
+// decomposition (the only integer divisions) is paid once per R*S elements, the writes of a warp stay contiguous.
+__global__ void unfold_rows_kernel(const float* __restrict__ x, float* __restrict__ col, ConvDims d, int planes_per_block, int threads_per_plane) {
+  const int pix = d.oH * d.oW, rs = d.R * d.S;
+  const int64_t planes = (int64_t)d.N * d.C;
+  const int lane_p = threadIdx.x % threads_per_plane;
+  for (int64_t plane = (int64_t)blockIdx.x * planes_per_block + threadIdx.x / threads_per_plane; plane < planes;
+       plane += (int64_t)gridDim.x * planes_per_block) {
+  const float* src = x + plane * (int64_t)d.H * d.W;
+  float* dst = col + plane * rs * pix;                         // rows (c*R + r)*S + s of image n are consecutive
+  for (int p = lane_p; p < pix; p += threads_per_plane) {
     const int ho = p / d.oW, wo = p - ho * d.oW;
-    const int ih = ho * d.sh - d.ph + r, iw = wo * d.sw - d.pw + s;
-    dst[p] = (ih >= 0 && ih < d.H && iw >= 0 && iw < d.W) ? src[ih * d.W + iw] : 0.0f;
+    const int ih0 = ho * d.sh - d.ph, iw0 = wo * d.sw - d.pw;
+    float* q = dst + p;
+    for (int r = 0; r < d.R; ++r) {
+      const int ih = ih0 + r;
+      const bool row_ok = ih >= 0 && ih < d.H;
+      for (int s = 0; s < d.S; ++s) {
+        const int iw = iw0 + s;
+        *q = (row_ok && iw >= 0 && iw < d.W) ? src[ih * d.W + iw] : 0.0f;
+        q += pix;
+      }
+    }
+  }
   }
 }
 // The same values written as the K-major row matrix col[(n*pix + p)][k] (for images too small to be fed M/N-major).
@@ -359,27 +379,40 @@ __global__ void to_rows_kernel(const float* __restrict__ src, float* __restrict_
 }
 // dx[n][c][h][w] += sum over the (r,s) taps that reach (h,w): gather form of unfoldedAcc (TensorDslCPU.scala:647-692).
 // One block row per (n, c) plane; the tap loops run over at most R*S entries of the unfolded gradient.
+// STRIDE 1 and 2 avoid the per-tap division and remainder (0 = any stride).
+template <int STRIDE>
 __global__ void fold_acc_kernel(const float* __restrict__ col, float* dx, ConvDims d, int planes_per_block, int threads_per_plane) {
   const int pix = d.oH * d.oW, hw = d.H * d.W;
-  const int64_t plane = (int64_t)blockIdx.x * planes_per_block + threadIdx.x / threads_per_plane;
-  if (plane >= (int64_t)d.N * d.C) return;
+  const int64_t planes = (int64_t)d.N * d.C;
+  const int lane_p = threadIdx.x % threads_per_plane;
+  for (int64_t plane = (int64_t)blockIdx.x * planes_per_block + threadIdx.x / threads_per_plane; plane < planes;
+       plane += (int64_t)gridDim.x * planes_per_block) {
   const float* src = col + plane * d.R * d.S * pix;          // rows (c*R + r)*S + s of image n start here
   float* dst = dx + plane * hw;
-  for (int i = threadIdx.x % threads_per_plane; i < hw; i += threads_per_plane) {
+  for (int i = lane_p; i < hw; i += threads_per_plane) {
     const int h = i / d.W, w = i - h * d.W;
     float acc = 0.0f;
     for (int r = 0; r < d.R; ++r) {
       const int hs = h + d.ph - r;
-      if (hs < 0 || hs % d.sh) continue;
-      const int ho = hs / d.sh; if (ho >= d.oH) continue;
+      if (hs < 0) continue;
+      int ho;
+      if (STRIDE == 1) ho = hs;
+      else if (STRIDE == 2) { if (hs & 1) continue; ho = hs >> 1; }
+      else { if (hs % d.sh) continue; ho = hs / d.sh; }
+      if (ho >= d.oH) continue;
       for (int s = 0; s < d.S; ++s) {
         const int ws = w + d.pw - s;
-        if (ws < 0 || ws % d.sw) continue;
-        const int wo = ws / d.sw; if (wo >= d.oW) continue;
+        if (ws < 0) continue;
+        int wo;
+        if (STRIDE == 1) wo = ws;
+        else if (STRIDE == 2) { if (ws & 1) continue; wo = ws >> 1; }
+        else { if (ws % d.sw) continue; wo = ws / d.sw; }
+        if (wo >= d.oW) continue;
         acc += src[(r * d.S + s) * pix + ho * d.oW + wo];
       }
     }
-    dst[i] += acc;
+    if (acc != 0.0f || STRIDE == 1) dst[i] += acc;
+  }
   }
 }
 
@@ -441,6 +474,10 @@ static int launch_plan(const TcPlan& p, const char* label) {
     LTB_CUDA(cudaFuncSetAttribute(tc_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxStages * (16384 + 32768) + 1024));
     smem_opted_in = true;
   }
+  if (splits > 1 && !p.accumulate) {            // overwrite semantics under split-K: start from zero, then accumulate atomically
+    const size_t out_floats = p.epilogue == TC_EPI_PIXEL ? (size_t)ceil_div(p.M, p.pix_per_img ? p.pix_per_img : 1) * (size_t)p.img_stride : (size_t)p.M * (size_t)p.ld;
+    LTB_CUDA(cudaMemsetAsync(p.out, 0, out_floats * 4, g.stream));
+  }
   const char* saved = g.label; g.label = label;
   dim3 grid(p.m_tiles, p.n_tiles, splits);
   LTB_LAUNCH(tc_gemm_kernel, grid, kTcThreads, smem, ma, mb, P);
@@ -462,10 +499,10 @@ int gemm_tc(const float* a, bool a_kmajor, const float* b, bool b_kmajor, float*
 
 static int launch_unfold(const float* x, float* col, const ConvDims& d) {
   const int pix = d.oH * d.oW;
-  int tpr = 32; while (tpr < pix && tpr < 256) tpr <<= 1;      // threads per row: a power of two in [32, 256]
-  const int rpb = 256 / tpr;
-  const int64_t rows = (int64_t)d.N * d.C * d.R * d.S;
-  LTB_LAUNCH(unfold_rows_kernel, (unsigned)ceil_div(rows, rpb), 256, 0, x, col, d, rpb, tpr);
+  int tpp = 32; while (tpp < pix && tpp < 256) tpp <<= 1;      // threads per input plane: a power of two in [32, 256]
+  const int ppb = 256 / tpp;
+  const int64_t planes = (int64_t)d.N * d.C;
+  LTB_LAUNCH(unfold_rows_kernel, grid_for(ceil_div(planes, ppb) * 256, 256, 16), 256, 0, x, col, d, ppb, tpp);
   return LTB_OK;
 }
 static int launch_fold(const float* col, float* dx, const ConvDims& d) {
@@ -473,7 +510,10 @@ static int launch_fold(const float* col, float* dx, const ConvDims& d) {
   int tpp = 32; while (tpp < hw && tpp < 256) tpp <<= 1;
   const int ppb = 256 / tpp;
   const int64_t planes = (int64_t)d.N * d.C;
-  LTB_LAUNCH(fold_acc_kernel, (unsigned)ceil_div(planes, ppb), 256, 0, col, dx, d, ppb, tpp);
+  const unsigned grid = (unsigned)grid_for(ceil_div(planes, ppb) * 256, 256, 16);
+  if (d.sh == 1 && d.sw == 1) LTB_LAUNCH(fold_acc_kernel<1>, grid, 256, 0, col, dx, d, ppb, tpp);
+  else if (d.sh == 2 && d.sw == 2) LTB_LAUNCH(fold_acc_kernel<2>, grid, 256, 0, col, dx, d, ppb, tpp);
+  else LTB_LAUNCH(fold_acc_kernel<0>, grid, 256, 0, col, dx, d, ppb, tpp);
   return LTB_OK;
 }
 static bool is_pointwise(const ConvDims& d) { return d.R == 1 && d.S == 1 && d.sh == 1 && d.sw == 1 && d.ph == 0 && d.pw == 0; }

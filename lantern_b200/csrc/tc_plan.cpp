@@ -44,19 +44,6 @@ bool operand_mn_pixels(TcOperand& o, const float* base, int n_img, int kdim, int
     for (int i = 0; i < 4; ++i) o.kstep_off[i] = (uint32_t)i * 1024;
     return true;
   }
-  if (false) {
-    const int ipt = kTileM / pix;                                // images per tile: 8 or 32
-    o.map.rank = 3; o.map.swizzle = pix == 16 ? TC_SW_64 : TC_SW_NONE;
-    o.map.dims[0] = (uint64_t)pix; o.map.dims[1] = (uint64_t)kdim; o.map.dims[2] = (uint64_t)n_img;
-    o.map.strides[1] = (uint64_t)pix * 4; o.map.strides[2] = (uint64_t)kdim * pix * 4;
-    o.map.box[0] = (uint32_t)pix; o.map.box[1] = kBK; o.map.box[2] = (uint32_t)ipt;
-    o.k_mul[1] = kBK; o.t_mul[2] = ipt;
-    const uint32_t row = (uint32_t)pix * 4;                      // bytes of one k-row of a chunk
-    if (pix == 16) { o.lbo = kBK * row; o.sbo = 8 * row; }       // swizzled: LBO = chunk stride, SBO = 8-row group stride
-    else { o.sbo = kBK * row; o.lbo = 8 * row; }                 // interleaved: SBO = chunk stride, LBO = 8-row group stride
-    for (int i = 0; i < 4; ++i) o.kstep_off[i] = (uint32_t)i * 8 * row;
-    return true;
-  }
   return false;
 }
 
@@ -132,25 +119,21 @@ bool operand_k_pixels(TcOperand& o, const float* base, int n_img, int rows, int 
   return false;
 }
 
-int pick_bn(int n_extent, int m_tiles, int sm_count) {
-  const int cand[3] = {256, 128, 64};
-  for (int bn : cand) {
-    if (bn > 64 && bn > n_extent) continue;
-    if (bn == 64 || m_tiles * cdiv(n_extent, bn) >= sm_count) return bn;
-  }
-  return 64;
-}
+// Tile width.  The MMA-issuing thread spends a few hundred cycles per k-iteration whatever the width, so narrow tiles
+// leave the tensor core idle; 128 columns with three stages lets two CTAs share an SM (one's epilogue and issue gaps
+// overlap the other's main loop).  Parallelism for small outputs comes from split-K, not from narrower tiles.
+int pick_bn(int n_extent, int, int) { return n_extent > 64 ? 128 : 64; }
 
 void finish(TcPlan& p, int M, int N, int k_iters, int sm_count, bool may_split) {
   p.M = M; p.N = N; p.k_iters = k_iters;
   p.m_tiles = cdiv(M, kTileM); p.n_tiles = cdiv(N, p.bn);
   p.splits = 1;
   if (may_split) {
-    int tiles = p.m_tiles * p.n_tiles;
-    int s = cdiv(2 * sm_count, tiles);
-    int mx = k_iters / 2; if (mx < 1) mx = 1;
+    const int tiles = p.m_tiles * p.n_tiles;
+    int s = cdiv(2 * sm_count, tiles);                 // aim at two CTAs per SM
+    int mx = k_iters / 4; if (mx < 1) mx = 1;          // at least four k-iterations per split
     if (s > mx) s = mx;
-    if (tiles >= sm_count) s = 1;
+    if (tiles >= 2 * sm_count) s = 1;
     p.splits = s < 1 ? 1 : s;
   }
 }
@@ -167,7 +150,7 @@ bool tc_plan_conv_fwd(TcPlan& p, const float* x, bool a_rows, const float* w, co
   if (!(a_rows ? operand_k_rows(p.a, x, M, ck, kTileM, &ka) : operand_mn_pixels(p.a, x, n_img, ck, pix, &ka))) return false;
   p.bn = pick_bn(co, cdiv(M, kTileM), sm_count);
   if (!operand_k_rows(p.b, w, co, ck, p.bn, &kb) || ka != kb) return false;
-  finish(p, M, co, ka, sm_count, false);
+  finish(p, M, co, ka, sm_count, true);             // split-K for small outputs: the launcher zeroes y first
   p.epilogue = TC_EPI_PIXEL; p.out = y; p.bias = bias; p.alpha = 1.0f; p.accumulate = 0;
   p.pix_per_img = pix; p.img_stride = (int64_t)co * pix; p.chan_stride = pix;
   return true;
@@ -181,7 +164,7 @@ bool tc_plan_conv_dgrad(TcPlan& p, const float* dy, bool a_rows, const float* w,
   if (!(a_rows ? operand_k_rows(p.a, dy, M, co, kTileM, &ka) : operand_mn_pixels(p.a, dy, n_img, co, pix, &ka))) return false;
   p.bn = pick_bn(ck, cdiv(M, kTileM), sm_count);
   if (!operand_mn_cols(p.b, w, co, ck, p.bn, &kb) || ka != kb) return false;
-  finish(p, M, ck, ka, sm_count, accumulate);
+  finish(p, M, ck, ka, sm_count, true);
   p.epilogue = TC_EPI_PIXEL; p.out = dx; p.bias = nullptr; p.alpha = 1.0f; p.accumulate = accumulate ? 1 : 0;
   p.pix_per_img = pix; p.img_stride = (int64_t)ck * pix; p.chan_stride = pix;
   return true;
@@ -209,7 +192,7 @@ bool tc_plan_gemm(TcPlan& p, const float* a, bool a_kmajor, const float* b, bool
   p.bn = pick_bn(N, cdiv(M, kTileM), sm_count);
   ok = b_kmajor ? operand_k_rows(p.b, b, N, K, p.bn, &kb) : operand_mn_cols(p.b, b, K, N, p.bn, &kb);
   if (!ok || ka != kb) return false;
-  finish(p, M, N, ka, sm_count, accumulate);
+  finish(p, M, N, ka, sm_count, true);
   p.epilogue = TC_EPI_ROWMAJOR; p.out = c; p.bias = nullptr; p.alpha = alpha; p.accumulate = accumulate ? 1 : 0; p.ld = N;
   return true;
 }

@@ -66,6 +66,8 @@ static float umma_fetch(const TcOperand& o, const std::vector<float>& smem, int 
 
 static bool run_plan(const TcPlan& p, size_t out_count) {
   if (p.a.nk != p.b.nk) { printf("nk mismatch\n"); return false; }
+  // overwrite semantics under split-K: the launcher zeroes the output, then every split accumulates atomically
+  if (p.splits > 1 && !p.accumulate) for (size_t i = 0; i < out_count; ++i) p.out[i] = 0.0f;
   std::vector<float> sa, sb;
   for (int mt = 0; mt < p.m_tiles; ++mt) for (int nt = 0; nt < p.n_tiles; ++nt) for (int z = 0; z < p.splits; ++z) {
     int per = (p.k_iters + p.splits - 1) / p.splits, k0 = z * per, k1 = k0 + per < p.k_iters ? k0 + per : p.k_iters;
