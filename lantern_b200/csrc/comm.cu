@@ -7,6 +7,7 @@
 
 #include <cstring>
 
+#include "buckets.h"
 #include "common.cuh"
 
 namespace ltb {
@@ -28,8 +29,7 @@ struct Nccl {
   int rank = 0, world = 1;
   cudaStream_t comm_stream = nullptr;
   cudaEvent_t ready = nullptr;
-  static const int kBuckets = 8;
-  cudaEvent_t done[kBuckets] = {};
+  cudaEvent_t done[kMaxBuckets] = {};
 } nccl;
 
 static int load_nccl() {
@@ -110,25 +110,20 @@ int ltb_allreduce_sgd_step(float* x, float* d, float lr, int64_t n) {
   LTB_INITED(); LTB_REQUIRE(x && d && n >= 0, "ltb_allreduce_sgd_step: bad argument");
   if (nccl.world == 1) return ltb_sgd_step(x, d, lr, n);
   if (n == 0) return LTB_OK;
-  const int nb = Nccl::kBuckets;
-  int64_t per = (n / nb + 1023) / 1024 * 1024; if (per < 1024) per = 1024;
+  int64_t off[kMaxBuckets], cnt[kMaxBuckets];
+  const int used = bucket_spans(n, off, cnt);
   LTB_CUDA(cudaEventRecord(nccl.ready, g.stream));
   LTB_CUDA(cudaStreamWaitEvent(nccl.comm_stream, nccl.ready, 0));
-  int used = 0;
-  for (int b = 0; b < nb; ++b) {
-    int64_t off = (int64_t)b * per; if (off >= n) break;
-    int64_t cnt = n - off < per ? n - off : per;
-    LTB_NCCL(nccl.AllReduce(d + off, d + off, (size_t)cnt, ncclFloat, ncclSum, nccl.comm, nccl.comm_stream));
+  for (int b = 0; b < used; ++b) {
+    LTB_NCCL(nccl.AllReduce(d + off[b], d + off[b], (size_t)cnt[b], ncclFloat, ncclSum, nccl.comm, nccl.comm_stream));
     LTB_CUDA(cudaEventRecord(nccl.done[b], nccl.comm_stream));
-    used = b + 1;
   }
   float s = -1.0f * lr / (float)nccl.world;
   for (int b = 0; b < used; ++b) {
-    int64_t off = (int64_t)b * per; int64_t cnt = n - off < per ? n - off : per;
     LTB_CUDA(cudaStreamWaitEvent(g.stream, nccl.done[b], 0));
-    bool vec = aligned16(x + off) && aligned16(d + off);
-    int64_t n4 = vec ? cnt / 4 : 0;
-    LTB_LAUNCH(sgd_scaled_kernel, grid_for(cnt / 4 + 1, 256), 256, 0, x + off, d + off, s, n4, cnt);
+    float* xb = x + off[b]; float* db = d + off[b];
+    const int64_t n4 = (aligned16(xb) && aligned16(db)) ? cnt[b] / 4 : 0;
+    LTB_LAUNCH(sgd_scaled_kernel, grid_for(cnt[b] / 4 + 1, 256), 256, 0, xb, db, s, n4, cnt[b]);
   }
   return LTB_OK;
 }

@@ -25,6 +25,7 @@
 #define LTB_FN(name) ora_##name
 #include "../include/lantern_b200.h"
 #include "../lantern_b200/csrc/tc_plan.h"   // eligibility rule of the product's tensor-core engine (shape arithmetic only)
+#include "../lantern_b200/csrc/buckets.h"   // all-reduce bucket spans (host arithmetic only)
 
 #include <cfloat>
 #include <cmath>
@@ -836,14 +837,39 @@ int ora_momentum_update(float* x, float* d, float* m, float lr, float mu, float 
   return LTB_OK;
 }
 
-// ------------------------------------------------------------------ data parallelism: a single-rank communicator.
-// Multi-rank behaviour is exercised by the tests with torch.distributed (gloo) around these calls.
+// ------------------------------------------------------------------ data parallelism.
+// The communicator has no transport of its own: a test installs one (a callback that sums a host buffer over the
+// ranks in place, e.g. torch.distributed's gloo all_reduce) with ora_comm_set_transport, which is not part of the
+// shared header. The update then follows the CUDA library's: the same bucket spans, sum over ranks, x -= lr/world * d,
+// d = 0 (each rank's loss is the mean over its own shard).
+typedef int (*ora_allreduce_fn)(float* buf, int64_t n);
+static ora_allreduce_fn g_transport = nullptr;
+static int g_world = 1;
+int ora_comm_set_transport(ora_allreduce_fn fn) { g_transport = fn; return LTB_OK; }
 int ora_comm_unique_id(void* out128) { memset(out128, 0, 128); return LTB_OK; }
-int ora_comm_init(int, int world, const void*) { return world == 1 ? LTB_OK : fail(LTB_E_COMM, "oracle communicator is single-rank"); }
-int ora_comm_destroy(void) { return LTB_OK; }
-int ora_comm_world(void) { return 1; }
-int ora_allreduce_sum(float*, int64_t) { return LTB_OK; }
-int ora_allreduce_sgd_step(float* x, float* d, float lr, int64_t n) { return ora_sgd_step(x, d, lr, n); }
+int ora_comm_init(int rank, int world, const void*) {
+  if (world < 1 || rank < 0 || rank >= world) return fail(LTB_E_ARG, "ora_comm_init: bad rank/world");
+  if (world > 1 && !g_transport) return fail(LTB_E_COMM, "ora_comm_init: no transport installed for a multi-rank communicator");
+  g_world = world;
+  return LTB_OK;
+}
+int ora_comm_destroy(void) { g_world = 1; return LTB_OK; }
+int ora_comm_world(void) { return g_world; }
+int ora_allreduce_sum(float* x, int64_t n) {
+  if (g_world == 1 || n == 0) return LTB_OK;
+  return g_transport(x, n) == 0 ? LTB_OK : fail(LTB_E_COMM, "ora_allreduce_sum: transport failed");
+}
+int ora_allreduce_sgd_step(float* x, float* d, float lr, int64_t n) {
+  if (g_world == 1) return ora_sgd_step(x, d, lr, n);
+  int64_t off[ltb::kMaxBuckets], cnt[ltb::kMaxBuckets];
+  const int used = ltb::bucket_spans(n, off, cnt);
+  const float s = -1.0f * lr / (float)g_world;
+  for (int b = 0; b < used; ++b) {
+    if (g_transport(d + off[b], cnt[b]) != 0) return fail(LTB_E_COMM, "ora_allreduce_sgd_step: transport failed");
+    for (int64_t i = off[b]; i < off[b] + cnt[b]; ++i) { x[i] += d[i] * s; d[i] = 0.0f; }
+  }
+  return LTB_OK;
+}
 
 }  // extern "C"
 
