@@ -202,6 +202,12 @@ int LTB_FN(sum)(const float* x, float* out, int64_t n);            /* out[0] ow 
 int LTB_FN(sum_grad)(float* dx, const float* dout, int64_t n);     /* dx[i] += dout[0] */
 int LTB_FN(mean)(const float* x, float* out, int64_t n);
 int LTB_FN(mean_grad)(float* dx, const float* dout, int64_t n);    /* dx[i] += dout[0]/n */
+/* sum() for callers that may not allocate: same result as sum(), bit for bit, but the partial sums live in a fixed
+ * device array inside the library instead of a workspace, and the call allocates nothing (no cudaMalloc, no arena
+ * block). Has no counterpart in the reference. The first call on a device does a one-time address look-up and should
+ * come before any stream capture. Limit: n <= 2^30 elements, else LTB_E_LIMIT. One array per device: calls that
+ * overlap in time (two streams, two threads) race; calls on one stream do not. */
+int LTB_FN(sum_static_scratch)(const float* x, float* out, int64_t n);   /* out[0] ow */
 int LTB_FN(sum_dim)(const float* x, float* out, int outer, int d, int inner);         /* out[outer,inner] ow */
 int LTB_FN(sum_dim_grad)(float* dx, const float* dout, int outer, int d, int inner);  /* acc */
 

@@ -180,6 +180,44 @@ int ltb_sum_dim_grad(float* dx, const float* dout, int outer, int d, int inner) 
   return LTB_OK;
 }
 
+// ---- the full sum with its partials in a file-scope device array: nothing is allocated, at set-up or per call.
+// ltb_sum takes its partials from the workspace that ltb_init obtains with cudaMalloc. This variant is for callers
+// for whom an allocation is not acceptable at all: cudaMalloc and cudaFree synchronise the whole device, which
+// stalls every other stream of a process that serves requests while it computes, and a process that runs under a
+// memory budget fixed at start-up cannot let a library grow its footprint afterwards. No counterpart in the reference.
+//   * The first call on a device looks the array's address up (cudaGetSymbolAddress, with that device current); that
+//     is set-up work and belongs before any stream capture. Later calls only launch.
+//   * Limit: n <= kStaticSumMaxN elements; beyond it the call fails with LTB_E_LIMIT and launches nothing.
+//   * Nothing has to start at zero: stage one writes one partial per CTA into slots [0, CTAs), stage two reads exactly
+//     those slots, so stale contents of the array are never read.
+//   * The array is one per device and process: two calls in flight at once (different streams or threads) race on it.
+//     Calls on one stream are ordered and safe.
+constexpr int kStaticSumSlots = 2048;
+constexpr int64_t kStaticSumMaxN = (int64_t)1 << 30;
+constexpr int kStaticSumMaxDevices = 64;
+static __device__ __align__(256) float static_sum_scratch[kStaticSumSlots];
+static float* static_sum_ptr[kStaticSumMaxDevices] = {};
+
+int ltb_sum_static_scratch(const float* x, float* out, int64_t n) {
+  LTB_INITED(); LTB_REQUIRE(x && out && n >= 0, "ltb_sum_static_scratch: bad argument");
+  if (n > kStaticSumMaxN)
+    return fail(LTB_E_LIMIT, "ltb_sum_static_scratch: %lld elements exceed the limit of %lld", (long long)n, (long long)kStaticSumMaxN);
+  LTB_REQUIRE(g.device >= 0 && g.device < kStaticSumMaxDevices, "ltb_sum_static_scratch: device index out of range");
+  if (!static_sum_ptr[g.device]) {                        // set-up, once per device (the context's device is current)
+    float* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress((void**)&p, static_sum_scratch);
+    if (e != cudaSuccess || !p) return fail(LTB_E_CUDA, "ltb_sum_static_scratch: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+    static_sum_ptr[g.device] = p;
+  }
+  float* partial = static_sum_ptr[g.device];
+  if (n <= (1 << 16)) { LTB_LAUNCH(sum_kernel, 1, 1024, 0, x, out, n, 1.0f, false); return LTB_OK; }
+  int blocks = grid_for(n, 1024, 2);                      // the same grid as ltb_sum: the two agree bit for bit
+  if (blocks > kStaticSumSlots) blocks = kStaticSumSlots;
+  LTB_LAUNCH(sum_kernel, blocks, 1024, 0, x, partial, n, 1.0f, true);
+  LTB_LAUNCH(sum_kernel, 1, 1024, 0, (const float*)partial, out, (int64_t)blocks, 1.0f, false);
+  return LTB_OK;
+}
+
 // softmax / logSoftmax and grads: TensorDslCPU.scala:783-846.
 int ltb_softmax(const float* x, float* y, int rows, int cols) {
   LTB_INITED(); LTB_REQUIRE(x && y && rows > 0 && cols > 0, "ltb_softmax: bad argument");

@@ -749,6 +749,8 @@ int ora_nll_grad(float* dx, const float* dout, const int32_t* t, int rows, int c
 // ------------------------------------------------------------------ reductions
 // sum / mean and grads: TensorDslCPU.scala:1115-1124 (sequential float fold).
 int ora_sum(const float* x, float* out, int64_t n) { float s = 0.0f; for (int64_t i = 0; i < n; ++i) s = s + x[i]; out[0] = s; return LTB_OK; }
+// The CPU build has no workspace to avoid: the static-scratch variant is the same sequential sum.
+int ora_sum_static_scratch(const float* x, float* out, int64_t n) { return ora_sum(x, out, n); }
 int ora_sum_grad(float* dx, const float* dout, int64_t n) { for (int64_t i = 0; i < n; ++i) dx[i] = dx[i] + dout[0]; return LTB_OK; }
 int ora_mean(const float* x, float* out, int64_t n) { float s = 0.0f; for (int64_t i = 0; i < n; ++i) s = s + x[i]; out[0] = s / (float)n; return LTB_OK; }
 int ora_mean_grad(float* dx, const float* dout, int64_t n) { float g1 = dout[0] / (float)n; for (int64_t i = 0; i < n; ++i) dx[i] = dx[i] + g1; return LTB_OK; }
