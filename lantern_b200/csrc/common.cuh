@@ -36,6 +36,9 @@ struct Context {
   int sm_count = kSMs;
   bool profiling = false;             // per-launch CUDA-event timing (ltb_profile)
   const char* label = nullptr;        // optional name override for the next launches
+  cudaStream_t side = nullptr;        // second stream: the weight-gradient half of conv backward runs beside the data-gradient half
+  cudaEvent_t fork_ev = nullptr, join_ev = nullptr;
+  bool hold_workspace = false;        // while two halves are in flight their staging blocks are released together at the end
 };
 extern Context g;
 
@@ -56,6 +59,22 @@ void profile_after();
     ++::ltb::g.launches;                                                                     \
     cudaError_t e_ = cudaGetLastError();                                                     \
     if (e_ != cudaSuccess) return ::ltb::fail(LTB_E_CUDA, "launch of %s failed: %s", #kernel, cudaGetErrorString(e_)); \
+  } while (0)
+
+// The same for a launch with a thread-block cluster of `cluster` CTAs along x (grid.x must be a multiple of it).
+#define LTB_LAUNCH_CLUSTER(kernel, grid, block, cluster, ...)                                \
+  do {                                                                                       \
+    cudaLaunchConfig_t cfg_ = {};                                                            \
+    cfg_.gridDim = (grid); cfg_.blockDim = (block); cfg_.dynamicSmemBytes = 0; cfg_.stream = ::ltb::g.stream; \
+    cudaLaunchAttribute attr_[1];                                                            \
+    attr_[0].id = cudaLaunchAttributeClusterDimension;                                       \
+    attr_[0].val.clusterDim.x = (unsigned)(cluster); attr_[0].val.clusterDim.y = 1; attr_[0].val.clusterDim.z = 1; \
+    cfg_.attrs = attr_; cfg_.numAttrs = 1;                                                   \
+    if (::ltb::g.profiling) ::ltb::profile_before(::ltb::g.label ? ::ltb::g.label : #kernel); \
+    cudaError_t e_ = cudaLaunchKernelEx(&cfg_, kernel, __VA_ARGS__);                         \
+    if (::ltb::g.profiling) ::ltb::profile_after();                                          \
+    ++::ltb::g.launches;                                                                     \
+    if (e_ != cudaSuccess) return ::ltb::fail(LTB_E_CUDA, "cluster launch of %s failed: %s", #kernel, cudaGetErrorString(e_)); \
   } while (0)
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }

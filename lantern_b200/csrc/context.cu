@@ -76,6 +76,9 @@ int ltb_init(int device, size_t heap_bytes) {
   g.host_status[0] = 0;
   g.scratch_bytes = (size_t)8 << 20;
   LTB_CUDA(cudaMalloc((void**)&g.scratch, g.scratch_bytes));
+  LTB_CUDA(cudaStreamCreateWithFlags(&g.side, cudaStreamNonBlocking));
+  LTB_CUDA(cudaEventCreateWithFlags(&g.fork_ev, cudaEventDisableTiming));
+  LTB_CUDA(cudaEventCreateWithFlags(&g.join_ev, cudaEventDisableTiming));
   g.launches = 0; g.last = 0; g.msg.clear(); g.capturing = false; g.math = LTB_MATH_TF32;
   g.inited = true;
   return LTB_OK;
@@ -87,7 +90,9 @@ int ltb_shutdown(void) {
   if (!g.inited) return LTB_OK;
   ltb_comm_destroy();
   cudaStreamSynchronize(g.stream);
+  cudaStreamSynchronize(g.side);
   cudaFree(g.heap); cudaFree(g.dev_status); cudaFree(g.scratch); cudaFreeHost(g.host_status);
+  cudaStreamDestroy(g.side); cudaEventDestroy(g.fork_ev); cudaEventDestroy(g.join_ev);
   if (g.own_stream) cudaStreamDestroy(g.stream);
   g = Context();
   return LTB_OK;

@@ -80,18 +80,36 @@ int ltb_conv2d_bwd(const float* x, float* dx, const float* w, float* dw, float* 
   LTB_INITED(); ConvDims d;
   LTB_REQUIRE(x && w && dy && conv_dims(d, N, C, H, W, K, R, S, sh, sw, ph, pw), "ltb_conv2d_bwd: bad argument");
   int rc = LTB_OK;
-  if (dx) {
-    int r = g.math == LTB_MATH_TF32 ? conv_dgrad_tc(dy, w, dx, d) : 0;
-    if (r < 0) return r;
-    if (r == 0) rc = conv_dgrad_fp32(dy, w, dx, d);
-    if (rc) return rc;
+  // The two halves are independent (dx needs dy and w; dw needs dy and x). When both are asked for, the weight-gradient
+  // half is issued on the side stream and the data-gradient half on the caller's, and the caller's stream waits for both
+  // before the call returns: program order at the boundary is unchanged, and inside a recorded step the two become
+  // parallel branches of the graph. Per-launch profiling keeps them serial so that each kernel is timed alone.
+  const bool overlap = dx && dw && !g.profiling && g.side != nullptr;
+  const size_t arena_base = g.used;
+  cudaStream_t main_stream = g.stream;
+  if (overlap) {
+    LTB_CUDA(cudaEventRecord(g.fork_ev, main_stream));
+    LTB_CUDA(cudaStreamWaitEvent(g.side, g.fork_ev, 0));
+    g.hold_workspace = true;
+    g.stream = g.side;
   }
   if (dw) {
     int r = g.math == LTB_MATH_TF32 ? conv_wgrad_tc(x, dy, dw, d) : 0;
-    if (r < 0) return r;
-    if (r == 0) rc = conv_wgrad_fp32(x, dy, dw, d);
-    if (rc) return rc;
+    if (r == 0) rc = conv_wgrad_fp32(x, dy, dw, d); else if (r < 0) rc = r;
   }
+  if (overlap) g.stream = main_stream;
+  if (dx && rc == LTB_OK) {
+    int r = g.math == LTB_MATH_TF32 ? conv_dgrad_tc(dy, w, dx, d) : 0;
+    if (r == 0) rc = conv_dgrad_fp32(dy, w, dx, d); else if (r < 0) rc = r;
+  }
+  if (overlap) {                                   // join, also on the error path: nothing may stay forked
+    g.hold_workspace = false;
+    g.used = arena_base;
+    cudaError_t e1 = cudaEventRecord(g.join_ev, g.side);
+    cudaError_t e2 = cudaStreamWaitEvent(main_stream, g.join_ev, 0);
+    if (rc == LTB_OK && (e1 != cudaSuccess || e2 != cudaSuccess)) return fail(LTB_E_CUDA, "ltb_conv2d_bwd: joining the side stream failed");
+  }
+  if (rc) return rc;
   if (dbias) rc = conv_bias_grad(dy, dbias, d);
   return rc;
 }

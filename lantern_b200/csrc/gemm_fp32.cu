@@ -88,6 +88,13 @@ static int strided_gemm(const float* a, int64_t sam, int64_t sak, const float* b
   dim3 grid((M + BM - 1) / BM, (N + BN - 1) / BN, 1);
   int tiles = grid.x * grid.y;
   int splits = 1;
+  // A forward product with few output tiles and a long K (the 2048 -> 10 classifier: two tiles) would leave the machine to two
+  // CTAs; when the output is a dense matrix it is zeroed and the product accumulated from K-splits like a gradient.
+  const bool dense_c = (scn == 1 && scm == N) || (scm == 1 && scn == M);
+  if (!accumulate && K >= 1024 && tiles < g.sm_count && dense_c) {
+    LTB_CUDA(cudaMemsetAsync(c, 0, (size_t)M * N * sizeof(float), g.stream));
+    accumulate = true;
+  }
   if (accumulate && K >= 1024 && tiles < g.sm_count) { splits = (2 * g.sm_count + tiles - 1) / tiles; int mx = K / 256; if (splits > mx) splits = mx; if (splits < 1) splits = 1; }
   int kps = (int)ceil_div(ceil_div(K, splits), BKK) * BKK;
   grid.z = (unsigned)ceil_div(K, kps);

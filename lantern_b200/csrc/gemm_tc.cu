@@ -517,6 +517,9 @@ static int launch_fold(const float* col, float* dx, const ConvDims& d) {
   return LTB_OK;
 }
 static bool is_pointwise(const ConvDims& d) { return d.R == 1 && d.S == 1 && d.sh == 1 && d.sw == 1 && d.ph == 0 && d.pw == 0; }
+// Staging blocks go back to the arena (a LIFO pop, host arithmetic only) unless the caller holds them: conv backward runs
+// its two halves on two streams and pops both halves' blocks together once both are issued.
+static void temp_free(float* p, size_t floats) { if (!g.hold_workspace) temp_free(p, floats); }
 static float* temp_alloc(size_t floats) {
   size_t bytes = (floats * 4 + kGranule - 1) / kGranule * kGranule;
   if (g.used + bytes > g.heap_bytes) return nullptr;          // no room for the staging buffer: let the FP32 path run
@@ -549,9 +552,9 @@ int conv_fwd_tc(const float* x, const float* w, const float* bias, float* y, con
   const float* op; bool r2; float* temp; size_t tn;
   int rc = stage_activation(x, !is_pointwise(d), d, ck, pix, &op, &r2, &temp, &tn);
   if (rc) return rc < 0 ? rc : 0;
-  if (!tc_plan_conv_fwd(p, op, rows, w, bias, y, d.N, ck, d.K, pix, g.sm_count)) { if (temp) ltb_free(temp, tn * 4); return 0; }
+  if (!tc_plan_conv_fwd(p, op, rows, w, bias, y, d.N, ck, d.K, pix, g.sm_count)) { if (temp) temp_free(temp, tn); return 0; }
   rc = launch_plan(p, "tc_gemm_kernel[conv_fwd]");
-  if (temp) ltb_free(temp, tn * 4);
+  if (temp) temp_free(temp, tn);
   return rc ? rc : 1;
 }
 
@@ -565,12 +568,12 @@ int conv_dgrad_tc(const float* dy, const float* w, float* dx, const ConvDims& d)
   int rc = stage_activation(dy, false, flat, d.K, pix, &op, &r2, &temp, &tn);
   if (rc) return rc < 0 ? rc : 0;
   float* col = nullptr; const size_t ncol = (size_t)d.N * ck * pix;
-  if (!direct) { col = temp_alloc(ncol); if (!col) { if (temp) ltb_free(temp, tn * 4); return 0; } }
+  if (!direct) { col = temp_alloc(ncol); if (!col) { if (temp) temp_free(temp, tn); return 0; } }
   bool ok = tc_plan_conv_dgrad(p, op, rows, w, direct ? dx : col, d.N, ck, d.K, pix, direct, g.sm_count);
   rc = ok ? launch_plan(p, "tc_gemm_kernel[conv_dgrad]") : 0;
   if (ok && !rc && !direct) rc = launch_fold(col, dx, d);
-  if (col) ltb_free(col, ncol * 4);
-  if (temp) ltb_free(temp, tn * 4);
+  if (col) temp_free(col, ncol);
+  if (temp) temp_free(temp, tn);
   return !ok ? 0 : (rc ? rc : 1);
 }
 
@@ -586,7 +589,7 @@ int conv_wgrad_tc(const float* x, const float* dy, float* dw, const ConvDims& d)
   }
   tc_plan_conv_wgrad(p, xin, dy, dw, d.N, ck, d.K, pix, g.sm_count);
   int rc = launch_plan(p, "tc_gemm_kernel[conv_wgrad]");
-  if (col) ltb_free(col, n * 4);
+  if (col) temp_free(col, n);
   return rc ? rc : 1;
 }
 

@@ -5,7 +5,11 @@
 // which the reference's GPU backend does not produce at all (it returns None, TensorDslCudnn.scala:930).
 #include <cfloat>
 
+#include <cooperative_groups.h>
+
 #include "common.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace ltb {
 
@@ -213,6 +217,120 @@ __global__ void bn_inference_kernel(const float* __restrict__ x, float* __restri
   }
 }
 
+// ---- One launch per batch norm: a thread-block cluster of K CTAs owns one channel.
+// Every CTA sums its contiguous slice of the channel's (image, pixel) items, the K partial pairs are exchanged through
+// distributed shared memory, every CTA derives the same statistics from them in the same order (double), and the
+// second sweep re-reads the slice (at most a few tens of KB per CTA, still in L2) to write the result. DRAM sees the
+// compulsory traffic only: x once and y once forward (8 B per element); x, dy, dx in and dx out backward (16 B).
+// cluster.sync() is the hardware cluster barrier (all CTAs of a cluster are co-scheduled), not a spin on memory.
+struct BnClusterPlan { int K; int threads; int per_cta; };
+static BnClusterPlan bn_cluster_plan(int N, int C, int HW) {
+  const int64_t items = (int64_t)N * (HW >> 2);                   // float4 items per channel
+  int K = 1;
+  while (K < 8 && (int64_t)C * K < 2 * (int64_t)g.sm_count && items / (K * 2) >= 512) K *= 2;
+  BnClusterPlan p;
+  p.K = K; p.per_cta = (int)ceil_div(items, K);
+  int t = 64; while (t < 512 && t < p.per_cta) t <<= 1;
+  p.threads = t;
+  return p;
+}
+
+__global__ void __launch_bounds__(512) bn_fwd_cluster_kernel(const float* x, float* y, const float* __restrict__ gamma, const float* __restrict__ beta,
+                                                             float* run_mean, float* run_var, float* save_mean, float* save_istd,
+                                                             int N, int C, int HW, int per_cta, float eps, float momentum) {
+  cg::cluster_group cluster = cg::this_cluster();
+  const unsigned K = cluster.num_blocks(), r = cluster.block_rank();
+  const int c = blockIdx.x / K;
+  const int hw4 = HW >> 2;
+  const int total = N * hw4, begin = (int)r * per_cta;              // the launcher keeps N * hw4 below 2^31
+  const int end = begin + per_cta < total ? begin + per_cta : total;
+  __shared__ float part[2];
+  __shared__ float stat[2];
+  const float k = x[(int64_t)c * HW];                               // shift: a sample of the channel (see bn_reduce_kernel)
+  float a = 0.0f, b = 0.0f;
+#pragma unroll 4
+  for (int t = begin + (int)threadIdx.x; t < end; t += (int)blockDim.x) {
+    const int n = t / hw4, i = t - n * hw4;
+    const float4 v = reinterpret_cast<const float4*>(x + ((int64_t)n * C + c) * HW)[i];
+    const float d0 = v.x - k, d1 = v.y - k, d2 = v.z - k, d3 = v.w - k;
+    a += (d0 + d1) + (d2 + d3); b += (d0 * d0 + d1 * d1) + (d2 * d2 + d3 * d3);
+  }
+  block_sum2(a, b);
+  if (threadIdx.x == 0) { part[0] = a; part[1] = b; }
+  cluster.sync();
+  if (threadIdx.x == 0) {
+    double s1 = 0, s2 = 0;
+    for (unsigned q = 0; q < K; ++q) { const float* p = cluster.map_shared_rank(part, q); s1 += p[0]; s2 += p[1]; }
+    const double m = (double)N * HW;
+    const double dm = s1 / m;
+    double var = s2 / m - dm * dm;
+    if (var < 0) var = 0;
+    const float mean = (float)((double)k + dm), is = 1.0f / sqrtf((float)var + eps);
+    stat[0] = mean; stat[1] = is;
+    if (r == 0) {
+      save_mean[c] = mean; save_istd[c] = is;
+      if (run_mean) run_mean[c] = (1.0f - momentum) * run_mean[c] + momentum * mean;
+      if (run_var) run_var[c] = (1.0f - momentum) * run_var[c] + momentum * (float)(var * (m > 1 ? m / (m - 1) : 1.0));
+    }
+  }
+  cluster.sync();                // every remote read of part[] is over before a CTA may leave; stat[] is visible to the block
+  const float mu = stat[0], sc = stat[1] * gamma[c], sh = beta[c];
+#pragma unroll 4
+  for (int t = begin + (int)threadIdx.x; t < end; t += (int)blockDim.x) {
+    const int n = t / hw4, i = t - n * hw4;
+    const int64_t off = ((int64_t)n * C + c) * HW;
+    float4 v = reinterpret_cast<const float4*>(x + off)[i];
+    v.x = (v.x - mu) * sc + sh; v.y = (v.y - mu) * sc + sh; v.z = (v.z - mu) * sc + sh; v.w = (v.w - mu) * sc + sh;
+    reinterpret_cast<float4*>(y + off)[i] = v;
+  }
+}
+
+__global__ void __launch_bounds__(512) bn_bwd_cluster_kernel(const float* __restrict__ x, const float* dy, float* dx, const float* __restrict__ gamma,
+                                                             float* dgamma, float* dbeta, const float* __restrict__ mean, const float* __restrict__ istd,
+                                                             int N, int C, int HW, int per_cta) {
+  cg::cluster_group cluster = cg::this_cluster();
+  const unsigned K = cluster.num_blocks(), r = cluster.block_rank();
+  const int c = blockIdx.x / K;
+  const int hw4 = HW >> 2;
+  const int total = N * hw4, begin = (int)r * per_cta;              // the launcher keeps N * hw4 below 2^31
+  const int end = begin + per_cta < total ? begin + per_cta : total;
+  __shared__ float part[2];
+  __shared__ float stat[3];
+  const float mu = mean[c], is = istd[c];
+  float a = 0.0f, b = 0.0f;
+#pragma unroll 4
+  for (int t = begin + (int)threadIdx.x; t < end; t += (int)blockDim.x) {
+    const int n = t / hw4, i = t - n * hw4;
+    const int64_t off = ((int64_t)n * C + c) * HW;
+    const float4 v = reinterpret_cast<const float4*>(x + off)[i], d = reinterpret_cast<const float4*>(dy + off)[i];
+    a += (d.x + d.y) + (d.z + d.w);
+    b += (d.x * ((v.x - mu) * is) + d.y * ((v.y - mu) * is)) + (d.z * ((v.z - mu) * is) + d.w * ((v.w - mu) * is));
+  }
+  block_sum2(a, b);
+  if (threadIdx.x == 0) { part[0] = a; part[1] = b; }
+  cluster.sync();
+  if (threadIdx.x == 0) {
+    double s1 = 0, s2 = 0;
+    for (unsigned q = 0; q < K; ++q) { const float* p = cluster.map_shared_rank(part, q); s1 += p[0]; s2 += p[1]; }
+    const double m = (double)N * HW;
+    stat[0] = gamma[c] * is; stat[1] = (float)(s1 / m); stat[2] = (float)(s2 / m);
+    if (r == 0) { if (dbeta) dbeta[c] += (float)s1; if (dgamma) dgamma[c] += (float)s2; }
+  }
+  cluster.sync();
+  if (dx == nullptr) return;                                        // uniform over the cluster, after its last barrier
+  const float ca = stat[0], cb = stat[1], cc = stat[2];
+#pragma unroll 4
+  for (int t = begin + (int)threadIdx.x; t < end; t += (int)blockDim.x) {
+    const int n = t / hw4, i = t - n * hw4;
+    const int64_t off = ((int64_t)n * C + c) * HW;
+    const float4 v = reinterpret_cast<const float4*>(x + off)[i], d = reinterpret_cast<const float4*>(dy + off)[i];
+    float4 o = reinterpret_cast<float4*>(dx + off)[i];
+    o.x += ca * (d.x - cb - (v.x - mu) * is * cc); o.y += ca * (d.y - cb - (v.y - mu) * is * cc);
+    o.z += ca * (d.z - cb - (v.z - mu) * is * cc); o.w += ca * (d.w - cb - (v.w - mu) * is * cc);
+    reinterpret_cast<float4*>(dx + off)[i] = o;
+  }
+}
+
 static int bn_splits(int N, int C) {
   int s = (int)ceil_div(2 * (int64_t)g.sm_count, C);
   if (s > N) s = N;
@@ -271,6 +389,12 @@ int ltb_bn_train_fwd(const float* x, float* y, const float* gamma, const float* 
   LTB_REQUIRE((size_t)C * S * 2 * 4 <= g.scratch_bytes, "ltb_bn_train_fwd: too many channels");
   int64_t n = (int64_t)N * C * HW;
   bool vec = (HW & 3) == 0 && aligned16(x) && aligned16(y);
+  if (vec && (int64_t)N * (HW >> 2) < ((int64_t)1 << 30)) {      // one cluster launch: statistics and result in the same kernel
+    const BnClusterPlan p = bn_cluster_plan(N, C, HW);
+    LTB_LAUNCH_CLUSTER(bn_fwd_cluster_kernel, dim3((unsigned)C * p.K), dim3(p.threads), p.K, x, y, gamma, beta, run_mean, run_var,
+                       save_mean, save_istd, N, C, HW, p.per_cta, eps, momentum);
+    return LTB_OK;
+  }
   LTB_LAUNCH(bn_reduce_kernel<0>, dim3(C, S), 256, 0, x, nullptr, nullptr, nullptr, g.scratch, N, C, HW);
   LTB_LAUNCH(bn_fwd_finalize_kernel, (C + 127) / 128, 128, 0, x, (const float*)g.scratch, S, C, HW, (double)N * HW, eps, momentum,
              save_mean, save_istd, run_mean, run_var);
@@ -286,6 +410,12 @@ int ltb_bn_bwd(const float* x, float* dx, const float* dy, const float* gamma, f
   float* coef = g.scratch + (size_t)C * S * 2;
   int64_t n = (int64_t)N * C * HW;
   bool vec = (HW & 3) == 0 && aligned16(x) && aligned16(dy) && aligned16(dx);
+  if (vec && (int64_t)N * (HW >> 2) < ((int64_t)1 << 30)) {
+    const BnClusterPlan p = bn_cluster_plan(N, C, HW);
+    LTB_LAUNCH_CLUSTER(bn_bwd_cluster_kernel, dim3((unsigned)C * p.K), dim3(p.threads), p.K, x, dy, dx, gamma, dgamma, dbeta,
+                       save_mean, save_istd, N, C, HW, p.per_cta);
+    return LTB_OK;
+  }
   LTB_LAUNCH(bn_reduce_kernel<1>, dim3(C, S), 256, 0, x, dy, save_mean, save_istd, g.scratch, N, C, HW);
   LTB_LAUNCH(bn_bwd_finalize_kernel, (C + 127) / 128, 128, 0, (const float*)g.scratch, S, C, (double)N * HW, gamma, save_istd, dgamma, dbeta, coef);
   if (dx) LTB_LAUNCH(bn_bwd_apply_kernel, grid_for(vec ? n / 4 : n, 256), 256, 0, x, dy, dx, save_mean, save_istd, (const float*)coef, C, HW, n, vec);

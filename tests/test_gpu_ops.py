@@ -165,7 +165,8 @@ def test_avgpool(ora, gpu, cfg):
     check(f, ora, gpu)
 
 
-@pytest.mark.parametrize("cfg", [(3, 2, 3, 3), (16, 64, 16, 16), (8, 256, 4, 4), (32, 512, 2, 2), (5, 7, 3, 5), (128, 10, 1, 1)])
+@pytest.mark.parametrize("cfg", [(3, 2, 3, 3), (16, 64, 16, 16), (8, 256, 4, 4), (32, 512, 2, 2), (5, 7, 3, 5), (128, 10, 1, 1),
+                                 (128, 64, 32, 32), (64, 128, 8, 8), (128, 3, 16, 16), (7, 300, 2, 6)])
 def test_batchnorm_train_fwd_bwd(ora, gpu, cfg):
     N, C, H, W = cfg
     v = (R(1).standard_normal((N, C, H, W)) * 2 + 3).astype(np.float32)      # non-zero mean: exercises the shifted sums
