@@ -122,7 +122,7 @@ def test_training_trajectory_and_graph_replay(oracle_lib, cuda_lib):
         replay.step_async(x, y, 0.002); cuda_lib.sync(); lr_.append(replay.last_loss())
     assert cuda_lib.kernel_launches() > before
     # split-K partial sums are combined with atomics, so two runs agree to rounding, not bit for bit
-    assert le[0] == lr_[0], (le, lr_)                      # the first forward pass is bit-identical
+    assert abs(le[0] - lr_[0]) <= 2e-6 * abs(le[0]), (le, lr_)   # same forward pass; the classifier's split-K sums combine atomically
     # later steps differ by the run-to-run noise of the atomically combined split-K sums, amplified by ReLU boundary
     # flips (two eager runs differ just as much): bounds, not equality
     assert np.allclose(le, lr_, rtol=2e-2), (le, lr_)
