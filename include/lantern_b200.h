@@ -68,6 +68,12 @@ int    LTB_FN(set_stream)(void* cuda_stream);           /* adopt a caller stream
 void*  LTB_FN(get_stream)(void);
 int    LTB_FN(sync)(void);
 int    LTB_FN(set_math)(int mode);                      /* LTB_MATH_TF32 (default) or LTB_MATH_FP32 */
+/* Look-ahead fusion, off by default. When on, batch-norm forward and same-shape add are issued one call late so that an
+ * in-place ReLU of their result joins the same kernel, and an in-place ReLU gradient is held so that the batch-norm
+ * backward or add gradient that reads it applies it on the fly. Results are those of the separate calls; only the moment
+ * of the launch moves: a held operation is issued by the next call of this library whatever it is (sync, copies,
+ * get_stream and graph_end included). A host that enqueues its own work on the stream must call get_stream or sync first. */
+int    LTB_FN(set_fusion)(int on);
 int    LTB_FN(device_status)(void);                     /* 0, or LTB_E_DEVICE if a kernel's bounded wait expired */
 int64_t LTB_FN(kernel_launches)(void);                  /* kernels launched by this library so far */
 

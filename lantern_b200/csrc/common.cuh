@@ -14,6 +14,24 @@ namespace ltb {
 constexpr int kSMs = 148;             // B200: 2 dies x 74 SMs; grids are sized in multiples of this
 constexpr size_t kGranule = 256;      // arena granule (TMA wants 16 B bases/strides; 256 keeps every tensor sector-aligned)
 
+// Look-ahead fusion (ltb_set_fusion): an operation whose result the very next call may finish in the same kernel is held back
+// for one call.  BN forward or a same-shape add followed by an in-place ReLU of their result become one kernel; an in-place
+// ReLU gradient followed by BN backward or by the add's gradient reading that buffer become one kernel.  Any other call
+// first issues the held operation on its own, so results never change; only the moment of the launch does.
+enum { PEND_NONE = 0, PEND_BN_FWD = 1, PEND_ADD = 2, PEND_RELU_GRAD = 3 };
+struct Pending {
+  int kind = PEND_NONE;
+  int64_t n = 0;
+  // PEND_BN_FWD
+  const float *x = nullptr, *gamma = nullptr, *beta = nullptr;
+  float *y = nullptr, *run_mean = nullptr, *run_var = nullptr, *save_mean = nullptr, *save_istd = nullptr;
+  int N = 0, C = 0, HW = 0; float eps = 0, momentum = 0;
+  // PEND_ADD: out = a + b
+  const float *a = nullptr, *b = nullptr; float* out = nullptr;
+  // PEND_RELU_GRAD: d = relu_y > 0 ? d : 0
+  const float* relu_y = nullptr; float* d = nullptr;
+};
+
 struct Context {
   bool inited = false;
   int device = 0;
@@ -38,17 +56,26 @@ struct Context {
   const char* label = nullptr;        // optional name override for the next launches
   cudaStream_t side = nullptr;        // second stream: the weight-gradient half of conv backward runs beside the data-gradient half
   cudaEvent_t fork_ev = nullptr, join_ev = nullptr;
+  bool fusion = false;                // look-ahead fusion of BN/add with ReLU (off unless the host opts in)
+  Pending pending;
   bool hold_workspace = false;        // while two halves are in flight their staging blocks are released together at the end
 };
 extern Context g;
 
 int fail(int code, const char* fmt, ...);
+int flush_pending();                 // issues the held operation on its own (elementwise.cu)
+// issue functions shared by the entry points and the flush (pool_bn.cu / elementwise.cu)
+int bn_fwd_issue(const Pending& p, bool relu);
+int add_issue(const float* a, const float* b, float* out, int64_t n, bool relu);
+int relu_grad_issue(const float* y, float* d, int64_t n);
 void profile_before(const char* name);
 void profile_after();
 
 #define LTB_REQUIRE(cond, ...) do { if (!(cond)) return ::ltb::fail(LTB_E_ARG, __VA_ARGS__); } while (0)
 #define LTB_CUDA(call) do { cudaError_t e_ = (call); if (e_ != cudaSuccess) return ::ltb::fail(LTB_E_CUDA, "%s failed: %s (%s:%d)", #call, cudaGetErrorString(e_), __FILE__, __LINE__); } while (0)
-#define LTB_INITED() do { if (!::ltb::g.inited) return ::ltb::fail(LTB_E_STATE, "%s: library not initialised (call ltb_init)", __func__); } while (0)
+#define LTB_INITED_NOFLUSH() do { if (!::ltb::g.inited) return ::ltb::fail(LTB_E_STATE, "%s: library not initialised (call ltb_init)", __func__); } while (0)
+// Every entry point first issues an operation held back by the look-ahead fusion; the few that may complete it use _NOFLUSH.
+#define LTB_INITED() do { LTB_INITED_NOFLUSH(); if (::ltb::g.pending.kind) { int rc_ = ::ltb::flush_pending(); if (rc_) return rc_; } } while (0)
 
 // Every kernel launch of the library goes through this macro so that ltb_kernel_launches() is exact.
 #define LTB_LAUNCH(kernel, grid, block, smem, ...)                                           \

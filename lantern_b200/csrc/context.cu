@@ -88,6 +88,7 @@ int ltb_comm_destroy(void);
 
 int ltb_shutdown(void) {
   if (!g.inited) return LTB_OK;
+  if (g.pending.kind) flush_pending();
   ltb_comm_destroy();
   cudaStreamSynchronize(g.stream);
   cudaStreamSynchronize(g.side);
@@ -104,14 +105,16 @@ int ltb_set_stream(void* s) {
   g.stream = (cudaStream_t)s;
   return LTB_OK;
 }
-void* ltb_get_stream(void) { return (void*)g.stream; }
+void* ltb_get_stream(void) { if (g.inited && g.pending.kind) flush_pending(); return (void*)g.stream; }   // the caller may enqueue its own work next
 int ltb_sync(void) { LTB_INITED(); LTB_CUDA(cudaStreamSynchronize(g.stream)); return LTB_OK; }
+int ltb_set_fusion(int on) { LTB_INITED(); g.fusion = on != 0; return LTB_OK; }
 int ltb_set_math(int mode) {
   LTB_REQUIRE(mode == LTB_MATH_FP32 || mode == LTB_MATH_TF32, "ltb_set_math: unknown mode %d", mode);
   g.math = mode; return LTB_OK;
 }
 int ltb_device_status(void) {
   if (!g.inited) return LTB_OK;
+  if (g.pending.kind) flush_pending();
   if (cudaMemcpyAsync(g.host_status, g.dev_status, 4, cudaMemcpyDeviceToHost, g.stream) != cudaSuccess) return LTB_E_CUDA;
   if (cudaStreamSynchronize(g.stream) != cudaSuccess) return LTB_E_CUDA;
   return g.host_status[0] ? LTB_E_DEVICE : LTB_OK;
@@ -189,6 +192,7 @@ int ltb_graph_begin(void) {
 }
 void* ltb_graph_end(void) {
   if (!g.capturing) { fail(LTB_E_STATE, "ltb_graph_end: not recording"); return nullptr; }
+  if (g.pending.kind) flush_pending();             // a held operation belongs to the recorded step
   g.capturing = false;
   cudaGraph_t graph = nullptr;
   cudaError_t e = cudaStreamEndCapture(g.stream, &graph);

@@ -263,6 +263,44 @@ static bool make_bcast(const int* as, const int* bs, int rank, Bcast& p, int64_t
   return true;
 }
 
+// ---- look-ahead fusion: issue functions and the flush ------------------------------------------------------------
+int add_issue(const float* a, const float* b, float* out, int64_t n, bool relu) {
+  if (relu) return launch_map<2>(a, b, nullptr, out, n, [] __device__(float x, float y, float) { float v = x + y; return v < 0.0f ? 0.0f : v; });
+  return launch_map<2>(a, b, nullptr, out, n, [] __device__(float x, float y, float) { return x + y; });
+}
+int relu_grad_issue(const float* y, float* d, int64_t n) {
+  return launch_map<2>(y, d, nullptr, d, n, [] __device__(float yv, float g0, float) { return yv > 0.0f ? g0 : 0.0f; });
+}
+int flush_pending() {
+  const Pending p = g.pending;
+  g.pending.kind = PEND_NONE;
+  switch (p.kind) {
+    case PEND_BN_FWD: return bn_fwd_issue(p, false);
+    case PEND_ADD: return add_issue(p.a, p.b, p.out, p.n, false);
+    case PEND_RELU_GRAD: return relu_grad_issue(p.relu_y, p.d, p.n);
+    default: return LTB_OK;
+  }
+}
+// The held in-place ReLU gradient and the gradient of a same-shape add in one pass:
+// m = y > 0 ? d : 0;  d = m;  da += m;  db += m   (da, db nullable).  n4 float4 items, then a scalar tail from `tail`.
+__global__ void relu_add_grad_kernel(const float* __restrict__ y, float* d, float* da, float* db, int64_t n4, int64_t tail, int64_t n) {
+  const int64_t i0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = i0; i < n4; i += stride) {
+    const float4 yv = reinterpret_cast<const float4*>(y)[i];
+    float4 m = reinterpret_cast<const float4*>(d)[i];
+    m.x = yv.x > 0.0f ? m.x : 0.0f; m.y = yv.y > 0.0f ? m.y : 0.0f; m.z = yv.z > 0.0f ? m.z : 0.0f; m.w = yv.w > 0.0f ? m.w : 0.0f;
+    reinterpret_cast<float4*>(d)[i] = m;
+    if (da) { float4 v = reinterpret_cast<float4*>(da)[i]; v.x += m.x; v.y += m.y; v.z += m.z; v.w += m.w; reinterpret_cast<float4*>(da)[i] = v; }
+    if (db) { float4 v = reinterpret_cast<float4*>(db)[i]; v.x += m.x; v.y += m.y; v.z += m.z; v.w += m.w; reinterpret_cast<float4*>(db)[i] = v; }
+  }
+  for (int64_t i = tail + i0; i < n; i += stride) {
+    const float m = y[i] > 0.0f ? d[i] : 0.0f;
+    d[i] = m;
+    if (da) da[i] += m;
+    if (db) db[i] += m;
+  }
+}
+
 }  // namespace ltb
 
 using namespace ltb;
@@ -293,15 +331,29 @@ int ltb_ew_binary(int op, const float* a, const int* as, const float* b, const i
   LTB_INITED(); LTB_REQUIRE(a && b && out && op >= LTB_ADD && op <= LTB_DIV, "ltb_ew_binary: bad argument");
   Bcast p; int64_t n; bool ab, bb;
   LTB_REQUIRE(make_bcast(as, bs, rank, p, n, ab, bb), "ltb_ew_binary: shapes do not broadcast");
+  if (!ab && !bb && op == LTB_ADD) {
+    if (g.fusion && n > 0) { Pending h; h.kind = PEND_ADD; h.n = n; h.a = a; h.b = b; h.out = out; g.pending = h; return LTB_OK; }   // an in-place ReLU of out may join it
+    return add_issue(a, b, out, n, false);
+  }
   if (!ab && !bb) return launch_map<2>(a, b, nullptr, out, n, [op] __device__(float x, float y, float) { return bin_op(op, x, y); });
   LTB_LAUNCH(bcast_binary_kernel, grid_for(n, 256), 256, 0, op, a, b, out, p, n);
   return LTB_OK;
 }
 // backpropElementWiseOpWithBroadCast: TensorDslCPU.scala:246-263.
 int ltb_ew_binary_grad(int op, const float* a, float* da, const int* as, const float* b, float* db, const int* bs, const float* dout, int rank) {
-  LTB_INITED(); LTB_REQUIRE(a && b && dout && op >= LTB_ADD && op <= LTB_DIV, "ltb_ew_binary_grad: bad argument");
+  LTB_INITED_NOFLUSH(); LTB_REQUIRE(a && b && dout && op >= LTB_ADD && op <= LTB_DIV, "ltb_ew_binary_grad: bad argument");
   Bcast p; int64_t n; bool ab, bb;
   LTB_REQUIRE(make_bcast(as, bs, rank, p, n, ab, bb), "ltb_ew_binary_grad: shapes do not broadcast");
+  if (g.pending.kind == PEND_RELU_GRAD && !ab && !bb && op == LTB_ADD && g.pending.d == dout && g.pending.n == n && n > 0) {
+    // the held ReLU gradient of dout and this add's gradient in one pass (dout is rewritten with the masked values)
+    const float* y = g.pending.relu_y; float* d = g.pending.d;
+    g.pending.kind = PEND_NONE;
+    const bool vec = aligned16(y) && aligned16(d) && (!da || aligned16(da)) && (!db || aligned16(db));
+    const int64_t n4 = vec ? n / 4 : 0;
+    LTB_LAUNCH(relu_add_grad_kernel, grid_for(n4 ? n4 : n, 256), 256, 0, y, d, da, db, n4, n4 * 4, n);
+    return LTB_OK;
+  }
+  if (g.pending.kind) { int rc = flush_pending(); if (rc) return rc; }
   if (!ab && !bb && op == LTB_ADD) {   // the residual add of ResNet: da += dout, db += dout
     int rc = da ? launch_map<2>(da, dout, nullptr, da, n, [] __device__(float g0, float c, float) { return g0 + c; }) : 0;
     if (rc) return rc;
@@ -360,7 +412,13 @@ int ltb_trans_grad(float* dx, const float* dy, int rows, int cols) {
 
 // relu/tanh/sigmoid/exp/log/sqrt/square: TensorDslCPU.scala:710-781.
 int ltb_unary(int op, const float* x, float* out, int64_t n) {
-  LTB_INITED(); LTB_REQUIRE(x && out && n >= 0 && op >= LTB_RELU && op <= LTB_SQUARE, "ltb_unary: bad argument");
+  LTB_INITED_NOFLUSH(); LTB_REQUIRE(x && out && n >= 0 && op >= LTB_RELU && op <= LTB_SQUARE, "ltb_unary: bad argument");
+  if (g.pending.kind && op == LTB_RELU && x == out && g.pending.n == n) {      // in-place ReLU of the result that was just held back
+    const Pending h = g.pending;
+    if (h.kind == PEND_BN_FWD && h.y == out) { g.pending.kind = PEND_NONE; return bn_fwd_issue(h, true); }
+    if (h.kind == PEND_ADD && h.out == out) { g.pending.kind = PEND_NONE; return add_issue(h.a, h.b, h.out, h.n, true); }
+  }
+  if (g.pending.kind) { int rc = flush_pending(); if (rc) return rc; }
   return launch_map<1>(x, nullptr, nullptr, out, n, [op] __device__(float v, float, float) { return un_op(op, v); });
 }
 // *_grad.  ReLU in place: the reference's CPU backend tests the clamped value with `< 0` and so never masks
@@ -370,7 +428,8 @@ int ltb_unary_grad(int op, const float* x, float* dx, const float* y, const floa
   LTB_INITED(); LTB_REQUIRE(dx && dy && n >= 0 && op >= LTB_RELU && op <= LTB_SQUARE, "ltb_unary_grad: bad argument");
   if (op == LTB_RELU && in_place) {
     LTB_REQUIRE(y, "ltb_unary_grad: relu in place needs the result");
-    return launch_map<2>(y, dx, nullptr, dx, n, [] __device__(float yv, float g0, float) { return yv > 0.0f ? g0 : 0.0f; });
+    if (g.fusion && n > 0) { Pending h; h.kind = PEND_RELU_GRAD; h.n = n; h.relu_y = y; h.d = dx; g.pending = h; return LTB_OK; }   // BN backward or an add's gradient may absorb it
+    return relu_grad_issue(y, dx, n);
   }
   const float* xin = x ? x : y; const float* yin = y ? y : x;
   LTB_REQUIRE(xin, "ltb_unary_grad: needs x or y");

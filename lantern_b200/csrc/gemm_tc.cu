@@ -30,7 +30,8 @@ constexpr int kTcThreads = 320;                    // warp 0 TMA, warp 1 MMA, wa
 constexpr long long kWaitCycles = 2000000000ll;    // bound of every spin wait (~1 s)
 
 struct TcOperandDev {
-  int t_div[5], t_mod[5], t_mul[5], k_div[5], k_mod[5], k_mul[5];
+  int t_div[5], t_mod[5], t_mul[5], k_div[5], k_mod[5], k_mul[5], c_off[5];
+  TcWalk walk;                                // the k part as a mixed-radix counter (tc_plan.h)
   int rank, nk;
   uint32_t stage_bytes, desc_lo, desc_hi;     // descriptor without the start address
   uint32_t kstep_off[8];
@@ -41,6 +42,7 @@ struct TcParams {
   uint32_t idesc;
   float* out; const float* bias; float alpha;
   long long pix_per_img, img_stride, chan_stride, ld;
+  int col_mod, col_mul;        // row-major epilogue: D column n goes to column (n % col_mod) * col_mul + n / col_mod when col_mul != 0
   int* status;
   float* dump;                 // diagnostics buffer of CTA (0,0,0): mode 1 copies its first stage (A then B), mode 2 records cycle stamps
   int dump_mode;
@@ -107,36 +109,33 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t* r) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-// Box coordinates of an operand: c[d] = tile part (fixed for the CTA) + ((kiter / k_div[d]) % k_mod[d]) * k_mul[d].
+// Box coordinates of an operand: c[d] = c_off[d] + tile part (fixed for the CTA) + ((kiter / k_div[d]) % k_mod[d]) * k_mul[d].
 // The k part is advanced incrementally with additions only: the producer is a single thread, and integer divisions or
-// branches per dimension cost it more cycles than the loads it issues.  Plans have at most one "inner" group of dimensions
-// (k_div == 1) that may wrap after `wrap` iterations, and one "outer" group (k_div == wrap) that then advances.
+// branches per dimension cost it more cycles than the loads it issues.  The plan's TcWalk says what each level of the
+// counter adds; the common case (level 0) uses increments kept in registers.
 struct BoxWalker {
-  int c[5], inc[5], back[5], i, wrap;
+  int c[5], inc0[5], i0, i1;
   __device__ __forceinline__ void init(const TcOperandDev& o, int tile, int k0) {
-    wrap = 0;
-#pragma unroll
-    for (int d = 0; d < 5; ++d) if (o.k_mul[d] != 0 && o.k_div[d] > 1) wrap = o.k_div[d];
-    i = (wrap && k0) ? k0 % wrap : 0;
 #pragma unroll
     for (int d = 0; d < 5; ++d) {
-      c[d] = 0;                                   // divisions only for the one or two dimensions that use them
-      if (o.t_mul[d] != 0) c[d] = ((o.t_div[d] > 1 ? tile / o.t_div[d] : tile) % o.t_mod[d]) * o.t_mul[d];
+      c[d] = o.c_off[d];                          // divisions only for the one or two dimensions that use them
+      if (o.t_mul[d] != 0) c[d] += ((o.t_div[d] > 1 ? tile / o.t_div[d] : tile) % o.t_mod[d]) * o.t_mul[d];
       if (o.k_mul[d] != 0 && k0 != 0) c[d] += ((o.k_div[d] > 1 ? k0 / o.k_div[d] : k0) % o.k_mod[d]) * o.k_mul[d];
-      const bool inner = o.k_mul[d] != 0 && o.k_div[d] == 1;
-      inc[d] = inner ? o.k_mul[d] : 0;
-      // on a wrap the inner dimensions return to their start and the outer ones advance
-      back[d] = inner ? -o.k_mul[d] * (wrap - 1) : ((o.k_mul[d] != 0 && o.k_div[d] > 1) ? o.k_mul[d] : 0);
+      inc0[d] = o.walk.inc[0][d];
     }
+    i0 = k0 ? k0 % o.walk.n0 : 0;
+    i1 = k0 ? (k0 / o.walk.n0) % o.walk.n1 : 0;
   }
-  __device__ __forceinline__ void next() {
-    if (wrap && ++i == wrap) {
-      i = 0;
+  __device__ __forceinline__ void next(const TcOperandDev& o) {
+    if (++i0 != o.walk.n0) {
 #pragma unroll
-      for (int d = 0; d < 5; ++d) c[d] += back[d];
+      for (int d = 0; d < 5; ++d) c[d] += inc0[d];
     } else {
+      i0 = 0;
+      int lvl = 1;
+      if (++i1 == o.walk.n1) { i1 = 0; lvl = 2; }
 #pragma unroll
-      for (int d = 0; d < 5; ++d) c[d] += inc[d];
+      for (int d = 0; d < 5; ++d) c[d] += o.walk.inc[lvl][d];
     }
   }
 };
@@ -218,8 +217,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         uint8_t* sa = stage_base + (size_t)s * stage_bytes; uint8_t* sb = sa + P.a.stage_bytes;
         mbar_expect_tx(&full_bar[s], stage_bytes);
         if (it < 24) LTB_STAMP(40 + it);      // issue time of each of the first loads
-        tma_load(&map_a, &full_bar[s], sa, P.a.rank, wa.c); wa.next();
-        tma_load(&map_b, &full_bar[s], sb, P.b.rank, wb.c); wb.next();
+        tma_load(&map_a, &full_bar[s], sa, P.a.rank, wa.c); wa.next(P.a);
+        tma_load(&map_b, &full_bar[s], sb, P.b.rank, wb.c); wb.next(P.b);
         if (++s == stages) { s = 0; ph ^= 1u; }
       }
     }
@@ -303,13 +302,14 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           for (int j = 0; j < 32; ++j) tile[lane][j] = __uint_as_float(r[j]);
           __syncwarp();
           const int n = n0 + c0 + lane;
+          const long long col = P.col_mul ? (long long)(n % P.col_mod) * P.col_mul + n / P.col_mod : n;
           if (n < P.N && rows > 0) {
             uint32_t t[32];
 #pragma unroll
             for (int rr = 0; rr < 32; ++rr) t[rr] = __float_as_uint(tile[rr][lane]);
             // after the transpose the "columns" of store_columns are the 32 rows of this block, `ld` apart
             const float* bias = nullptr;
-            float* p = P.out + m0 * ld + n;
+            float* p = P.out + m0 * ld + col;
             if (P.bias && mode == 0) {
               const float bv = P.bias[n];
 #pragma unroll
@@ -377,6 +377,28 @@ __global__ void to_rows_kernel(const float* __restrict__ src, float* __restrict_
     dst[i] = src[(n * chan + c) * pix + p];
   }
 }
+// The same copy through a shared-memory tile of 32 channels x PT pixels (PT = min(pix, 32), pix a multiple of PT, chan a
+// multiple of 32), coalesced on both sides.  grid (pix/PT, chan/32, N), block 256.
+template <int PT>      // PT == 0: run-time tile width `pt`
+__global__ void to_rows_tiled_kernel(const float* __restrict__ src, float* __restrict__ dst, int chan, int pix, int pt_rt) {
+  __shared__ float tile[32][33];
+  const int pt = PT ? PT : pt_rt;
+  const int n = blockIdx.z, p0 = blockIdx.x * pt, c0 = blockIdx.y * 32;
+  const float* s = src + ((int64_t)n * chan + c0) * pix + p0;
+  for (int i = threadIdx.x; i < 32 * pt; i += blockDim.x) { const int c = i / pt, p = i - c * pt; tile[c][p] = s[(int64_t)c * pix + p]; }
+  __syncthreads();
+  float* d = dst + ((int64_t)n * pix + p0) * chan + c0;
+  for (int i = threadIdx.x; i < 32 * pt; i += blockDim.x) { const int p = i >> 5, c = i & 31; d[(int64_t)p * chan + c] = tile[c][p]; }
+}
+// Filters w[k][c][tap] (OIHW) as one matrix per tap: out[tap][k][c] (by_c == 0, forward) or out[tap][c][k] (data-grad).
+__global__ void permute_taps_kernel(const float* __restrict__ w, float* __restrict__ out, int K, int C, int taps, int by_c, int64_t total) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    int k, c; const int inner = by_c ? K : C, outer = by_c ? C : K;
+    const int a = (int)(i % inner); const int64_t t2 = i / inner; const int b = (int)(t2 % outer); const int t = (int)(t2 / outer);
+    if (by_c) { k = a; c = b; } else { c = a; k = b; }
+    out[i] = w[((int64_t)k * C + c) * taps + t];
+  }
+}
 // dx[n][c][h][w] += sum over the (r,s) taps that reach (h,w): gather form of unfoldedAcc (TensorDslCPU.scala:647-692).
 // One block row per (n, c) plane; the tap loops run over at most R*S entries of the unfolded gradient.
 // STRIDE 1 and 2 avoid the per-tap division and remainder (0 = any stride).
@@ -442,14 +464,19 @@ static int encode_map(const TcTensorMap& m, CUtensorMap* out) {
   return LTB_OK;
 }
 
-static void to_dev(const TcOperand& o, TcOperandDev& v) {
-  for (int d = 0; d < 5; ++d) { v.t_div[d] = o.t_div[d]; v.t_mod[d] = o.t_mod[d]; v.t_mul[d] = o.t_mul[d]; v.k_div[d] = o.k_div[d]; v.k_mod[d] = o.k_mod[d]; v.k_mul[d] = o.k_mul[d]; }
+static bool to_dev(const TcOperand& o, TcOperandDev& v) {
+  for (int d = 0; d < 5; ++d) {
+    v.t_div[d] = o.t_div[d]; v.t_mod[d] = o.t_mod[d]; v.t_mul[d] = o.t_mul[d];
+    v.k_div[d] = o.k_div[d]; v.k_mod[d] = o.k_mod[d]; v.k_mul[d] = o.k_mod[d] > 1 ? o.k_mul[d] : 0; v.c_off[d] = o.c_off[d];
+  }
+  if (!tc_walk_of(o, v.walk)) return false;
   v.rank = o.map.rank; v.nk = o.nk; v.stage_bytes = o.stage_bytes;
   // UMMA layout type: 0 none, 1 128-byte swizzle with 32-byte atoms (M/N-major 32-bit operands), 2 128 B, 4 64 B, 6 32 B
   const uint32_t layout = o.map.swizzle == TC_SW_128_32B ? 1u : o.map.swizzle == TC_SW_128 ? 2u : o.map.swizzle == TC_SW_64 ? 4u : o.map.swizzle == TC_SW_32 ? 6u : 0u;
   v.desc_lo = ((o.lbo >> 4) & 0x3FFFu) << 16;                                     // leading byte offset, bits [16,30)
   v.desc_hi = ((o.sbo >> 4) & 0x3FFFu) | (1u << 14) | (layout << 29);             // stride byte offset [32,46), version 1 at [46,48), layout [61,64)
   for (int i = 0; i < 8; ++i) v.kstep_off[i] = o.kstep_off[i];
+  return true;
 }
 
 static int launch_plan(const TcPlan& p, const char* label) {
@@ -457,7 +484,7 @@ static int launch_plan(const TcPlan& p, const char* label) {
   int rc = encode_map(p.a.map, &ma); if (rc) return rc;
   rc = encode_map(p.b.map, &mb); if (rc) return rc;
   TcParams P;
-  to_dev(p.a, P.a); to_dev(p.b, P.b);
+  if (!to_dev(p.a, P.a) || !to_dev(p.b, P.b)) return fail(LTB_E_STATE, "tensor-core plan whose k-iteration order has no incremental walk");
   P.M = p.M; P.N = p.N; P.bn = p.bn; P.k_iters = p.k_iters;
   P.k_per_split = (int)ceil_div(p.k_iters, p.splits);
   const int splits = (int)ceil_div(p.k_iters, P.k_per_split);                     // every split has at least one iteration
@@ -465,7 +492,7 @@ static int launch_plan(const TcPlan& p, const char* label) {
   // tf32 x tf32 -> f32: D format 1 at [4,6), A/B format 2 at [7,10)/[10,13), major bits 15/16, N>>3 at [17,23), M>>4 at [24,29)
   P.idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)p.a.mn_major << 15) | ((uint32_t)p.b.mn_major << 16) | ((uint32_t)(p.bn >> 3) << 17) | ((128u >> 4) << 24);
   P.out = p.out; P.bias = p.bias; P.alpha = p.alpha;
-  P.pix_per_img = p.pix_per_img ? p.pix_per_img : 1; P.img_stride = p.img_stride; P.chan_stride = p.chan_stride; P.ld = p.ld;
+  P.pix_per_img = p.pix_per_img ? p.pix_per_img : 1; P.img_stride = p.img_stride; P.chan_stride = p.chan_stride; P.ld = p.ld; P.col_mod = p.col_mod ? p.col_mod : 1; P.col_mul = p.col_mul;
   P.status = g.dev_status; P.dump = debug_dump; P.dump_mode = debug_dump_mode;
   // 4 stages, except 3 for 128-wide tiles so that two CTAs (2 x 97 KB) share an SM and one's epilogue overlaps the other's main loop
   P.stages = p.bn == 128 ? 3 : kMaxStages;
@@ -539,9 +566,84 @@ static int stage_activation(const float* src, bool unfold, const ConvDims& d, in
     if (*rows) LTB_LAUNCH(unfold_to_rows_kernel, grid_for((int64_t)n, 256), 256, 0, src, buf, d, (int64_t)n);
     else { int rc = launch_unfold(src, buf, d); if (rc) return rc; }
   } else {
-    LTB_LAUNCH(to_rows_kernel, grid_for((int64_t)n, 256), 256, 0, src, buf, chan, pix, (int64_t)n);
+    const int pt = pix < 32 ? pix : 32;
+    if (chan % 32 == 0 && pix % pt == 0 && d.N <= 65535)
+      { if (pt == 32) LTB_LAUNCH(to_rows_tiled_kernel<32>, dim3(pix / 32, chan / 32, d.N), 256, 0, src, buf, chan, pix, 32);
+        else LTB_LAUNCH(to_rows_tiled_kernel<0>, dim3(pix / pt, chan / 32, d.N), 32 * pt < 256 ? 128 : 256, 0, src, buf, chan, pix, pt); }
+    else
+      LTB_LAUNCH(to_rows_kernel, grid_for((int64_t)n, 256), 256, 0, src, buf, chan, pix, (int64_t)n);
   }
   return LTB_OK;
+}
+
+// ---- tap-loop (implicit) path for R x S convolutions with stride 1 ---------------------------------------------------------
+static bool taps_geometry(const ConvDims& d, TcConvGeom& gm) {
+  if (d.R * d.S == 1 || d.sh != 1 || d.sw != 1) return false;
+  gm.n_img = d.N; gm.C = d.C; gm.H = d.H; gm.W = d.W; gm.K = d.K; gm.R = d.R; gm.S = d.S; gm.ph = d.ph; gm.pw = d.pw; gm.oH = d.oH; gm.oW = d.oW;
+  return true;
+}
+// Channels-last copy [N][pix][chan] of a tensor [N][chan][pix] in a staging block (null when the arena has no room).
+static int channels_last(const float* src, int n_img, int chan, int pix, float** out, size_t* floats) {
+  const size_t n = (size_t)n_img * chan * pix;
+  *out = temp_alloc(n); *floats = n;
+  if (!*out) return LTB_OK;
+  const int pt = pix < 32 ? pix : 32;
+  if (chan % 32 == 0 && pix % pt == 0 && n_img <= 65535)
+    { if (pt == 32) LTB_LAUNCH(to_rows_tiled_kernel<32>, dim3(pix / 32, chan / 32, n_img), 256, 0, src, *out, chan, pix, 32);
+      else LTB_LAUNCH(to_rows_tiled_kernel<0>, dim3(pix / pt, chan / 32, n_img), 32 * pt < 256 ? 128 : 256, 0, src, *out, chan, pix, pt); }
+  else
+    LTB_LAUNCH(to_rows_kernel, grid_for((int64_t)n, 256), 256, 0, src, *out, chan, pix, (int64_t)n);
+  return LTB_OK;
+}
+static int tap_matrices(const float* w, const ConvDims& d, int by_c, float** out, size_t* floats) {
+  const size_t n = (size_t)d.K * d.C * d.R * d.S;
+  *out = temp_alloc(n); *floats = n;
+  if (!*out) return LTB_OK;
+  LTB_LAUNCH(permute_taps_kernel, grid_for((int64_t)n, 256), 256, 0, w, *out, d.K, d.C, d.R * d.S, by_c, (int64_t)n);
+  return LTB_OK;
+}
+// Each returns 1 when it took the problem, 0 when not eligible (the unfolding path then runs), negative on error.
+static int conv_fwd_taps(const float* x, const float* w, const float* bias, float* y, const ConvDims& d) {
+  TcConvGeom gm; TcPlan p;
+  if (!taps_geometry(d, gm) || !tc_plan_conv_taps_fwd(p, y, y, bias, y, gm, g.sm_count)) return 0;     // eligibility with any aligned pointers
+  float *xr = nullptr, *wt = nullptr; size_t nx = 0, nw = 0;
+  int rc = channels_last(x, d.N, d.C, d.H * d.W, &xr, &nx); if (rc) return rc;
+  if (!xr) return 0;
+  rc = tap_matrices(w, d, 0, &wt, &nw);
+  bool ok = !rc && wt && tc_plan_conv_taps_fwd(p, xr, wt, bias, y, gm, g.sm_count);
+  if (ok) rc = launch_plan(p, "tc_gemm_kernel[conv_fwd taps]");
+  if (wt) temp_free(wt, nw);
+  temp_free(xr, nx);
+  return rc ? rc : (ok ? 1 : 0);
+}
+static int conv_dgrad_taps(const float* dy, const float* w, float* dx, const ConvDims& d) {
+  TcConvGeom gm; TcPlan p;
+  if (!taps_geometry(d, gm) || !tc_plan_conv_taps_dgrad(p, dx, dx, dx, gm, true, g.sm_count)) return 0;
+  float *dyr = nullptr, *wd = nullptr; size_t ny = 0, nw = 0;
+  int rc = channels_last(dy, d.N, d.K, d.oH * d.oW, &dyr, &ny); if (rc) return rc;
+  if (!dyr) return 0;
+  rc = tap_matrices(w, d, 1, &wd, &nw);
+  bool ok = !rc && wd && tc_plan_conv_taps_dgrad(p, dyr, wd, dx, gm, true, g.sm_count);
+  if (ok) rc = launch_plan(p, "tc_gemm_kernel[conv_dgrad taps]");
+  if (wd) temp_free(wd, nw);
+  temp_free(dyr, ny);
+  return rc ? rc : (ok ? 1 : 0);
+}
+static int conv_wgrad_taps(const float* x, const float* dy, float* dw, const ConvDims& d) {
+  TcConvGeom gm; TcPlan p;
+  // The tap-loop weight-grad stores its columns (tap, c) into OIHW with a stride of R*S floats, so its split-K atomics do not
+  // coalesce; measured, it only beats unfolding once the unfolded matrix is large (64 MB and up: the 9x traffic then dominates).
+  if ((size_t)d.N * d.C * d.R * d.S * d.oH * d.oW * 4 < ((size_t)64 << 20)) return 0;
+  if (!taps_geometry(d, gm) || !tc_plan_conv_taps_wgrad(p, dw, dw, dw, gm, g.sm_count)) return 0;
+  float *dyr = nullptr, *xr = nullptr; size_t ny = 0, nx = 0;
+  int rc = channels_last(dy, d.N, d.K, d.oH * d.oW, &dyr, &ny); if (rc) return rc;
+  if (!dyr) return 0;
+  rc = channels_last(x, d.N, d.C, d.H * d.W, &xr, &nx);
+  bool ok = !rc && xr && tc_plan_conv_taps_wgrad(p, dyr, xr, dw, gm, g.sm_count);
+  if (ok) rc = launch_plan(p, "tc_gemm_kernel[conv_wgrad taps]");
+  if (xr) temp_free(xr, nx);
+  temp_free(dyr, ny);
+  return rc ? rc : (ok ? 1 : 0);
 }
 
 int conv_fwd_tc(const float* x, const float* w, const float* bias, float* y, const ConvDims& d) {
@@ -549,6 +651,7 @@ int conv_fwd_tc(const float* x, const float* w, const float* bias, float* y, con
   TcPlan p;
   const bool rows = tc_conv_needs_rows(pix);
   if (!tc_plan_conv_fwd(p, y /* any aligned pointer: eligibility only */, rows, w, bias, y, d.N, ck, d.K, pix, g.sm_count)) return 0;
+  { int t = conv_fwd_taps(x, w, bias, y, d); if (t != 0) return t; }      // the tap-loop form when the shape allows it
   const float* op; bool r2; float* temp; size_t tn;
   int rc = stage_activation(x, !is_pointwise(d), d, ck, pix, &op, &r2, &temp, &tn);
   if (rc) return rc < 0 ? rc : 0;
@@ -563,6 +666,7 @@ int conv_dgrad_tc(const float* dy, const float* w, float* dx, const ConvDims& d)
   TcPlan p;
   const bool rows = tc_conv_needs_rows(pix), direct = is_pointwise(d);
   if (!tc_plan_conv_dgrad(p, dx, rows, w, dx, d.N, ck, d.K, pix, direct, g.sm_count)) return 0;
+  { int t = conv_dgrad_taps(dy, w, dx, d); if (t != 0) return t; }
   const float* op; bool r2; float* temp; size_t tn;
   ConvDims flat = d; flat.C = d.K;                               // dy is [N][K][pix]: staged like a pointwise activation with K channels
   int rc = stage_activation(dy, false, flat, d.K, pix, &op, &r2, &temp, &tn);
@@ -581,6 +685,7 @@ int conv_wgrad_tc(const float* x, const float* dy, float* dw, const ConvDims& d)
   const int ck = d.C * d.R * d.S, pix = d.oH * d.oW;
   TcPlan p;
   if (!tc_plan_conv_wgrad(p, dy, dy, dw, d.N, ck, d.K, pix, g.sm_count)) return 0;
+  { int t = conv_wgrad_taps(x, dy, dw, d); if (t != 0) return t; }
   const float* xin = x; float* col = nullptr; const size_t n = (size_t)d.N * ck * pix;
   if (!is_pointwise(d)) {
     col = temp_alloc(n); if (!col) return 0;

@@ -230,14 +230,20 @@ static BnClusterPlan bn_cluster_plan(int N, int C, int HW) {
   while (K < 8 && (int64_t)C * K < 2 * (int64_t)g.sm_count && items / (K * 2) >= 512) K *= 2;
   BnClusterPlan p;
   p.K = K; p.per_cta = (int)ceil_div(items, K);
-  int t = 64; while (t < 512 && t < p.per_cta) t <<= 1;
+  int t = 64; while (t < 512 && t * 4 < p.per_cta) t <<= 1;    // about four float4 per thread: small slices get small CTAs, many per SM
   p.threads = t;
   return p;
 }
 
-__global__ void __launch_bounds__(512) bn_fwd_cluster_kernel(const float* x, float* y, const float* __restrict__ gamma, const float* __restrict__ beta,
+// VPT > 0: the CTA's slice is at most VPT float4 per thread and stays in registers between the two sweeps (all loads of a
+// thread are issued back to back); VPT == 0: any slice length, the second sweep re-reads it.
+constexpr int kBnVpt = 8;          // forward: x
+constexpr int kBnVptBwd = 4;       // backward keeps x, dy and dx: half the slice per thread for the same register budget
+
+template <int VPT>
+__global__ void __launch_bounds__(512, 2) bn_fwd_cluster_kernel(const float* x, float* y, const float* __restrict__ gamma, const float* __restrict__ beta,
                                                              float* run_mean, float* run_var, float* save_mean, float* save_istd,
-                                                             int N, int C, int HW, int per_cta, float eps, float momentum) {
+                                                             int N, int C, int HW, int per_cta, float eps, float momentum, int relu) {
   cg::cluster_group cluster = cg::this_cluster();
   const unsigned K = cluster.num_blocks(), r = cluster.block_rank();
   const int c = blockIdx.x / K;
@@ -248,12 +254,29 @@ __global__ void __launch_bounds__(512) bn_fwd_cluster_kernel(const float* x, flo
   __shared__ float stat[2];
   const float k = x[(int64_t)c * HW];                               // shift: a sample of the channel (see bn_reduce_kernel)
   float a = 0.0f, b = 0.0f;
+  float4 keep[VPT > 0 ? VPT : 1];
+  if (VPT > 0) {
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+      const int t = begin + j * (int)blockDim.x + (int)threadIdx.x;
+      if (t < end) { const int n = t / hw4, i = t - n * hw4; keep[j] = reinterpret_cast<const float4*>(x + ((int64_t)n * C + c) * HW)[i]; }
+    }
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+      const int t = begin + j * (int)blockDim.x + (int)threadIdx.x;
+      if (t < end) {
+        const float d0 = keep[j].x - k, d1 = keep[j].y - k, d2 = keep[j].z - k, d3 = keep[j].w - k;
+        a += (d0 + d1) + (d2 + d3); b += (d0 * d0 + d1 * d1) + (d2 * d2 + d3 * d3);
+      }
+    }
+  } else {
 #pragma unroll 4
-  for (int t = begin + (int)threadIdx.x; t < end; t += (int)blockDim.x) {
-    const int n = t / hw4, i = t - n * hw4;
-    const float4 v = reinterpret_cast<const float4*>(x + ((int64_t)n * C + c) * HW)[i];
-    const float d0 = v.x - k, d1 = v.y - k, d2 = v.z - k, d3 = v.w - k;
-    a += (d0 + d1) + (d2 + d3); b += (d0 * d0 + d1 * d1) + (d2 * d2 + d3 * d3);
+    for (int t = begin + (int)threadIdx.x; t < end; t += (int)blockDim.x) {
+      const int n = t / hw4, i = t - n * hw4;
+      const float4 v = reinterpret_cast<const float4*>(x + ((int64_t)n * C + c) * HW)[i];
+      const float d0 = v.x - k, d1 = v.y - k, d2 = v.z - k, d3 = v.w - k;
+      a += (d0 + d1) + (d2 + d3); b += (d0 * d0 + d1 * d1) + (d2 * d2 + d3 * d3);
+    }
   }
   block_sum2(a, b);
   if (threadIdx.x == 0) { part[0] = a; part[1] = b; }
@@ -275,36 +298,84 @@ __global__ void __launch_bounds__(512) bn_fwd_cluster_kernel(const float* x, flo
   }
   cluster.sync();                // every remote read of part[] is over before a CTA may leave; stat[] is visible to the block
   const float mu = stat[0], sc = stat[1] * gamma[c], sh = beta[c];
+  if (VPT > 0) {
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+      const int t = begin + j * (int)blockDim.x + (int)threadIdx.x;
+      if (t < end) {
+        const int n = t / hw4, i = t - n * hw4;
+        float4 v = keep[j];
+        v.x = (v.x - mu) * sc + sh; v.y = (v.y - mu) * sc + sh; v.z = (v.z - mu) * sc + sh; v.w = (v.w - mu) * sc + sh;
+        if (relu) { v.x = v.x < 0.0f ? 0.0f : v.x; v.y = v.y < 0.0f ? 0.0f : v.y; v.z = v.z < 0.0f ? 0.0f : v.z; v.w = v.w < 0.0f ? 0.0f : v.w; }
+        reinterpret_cast<float4*>(y + ((int64_t)n * C + c) * HW)[i] = v;
+      }
+    }
+  } else {
 #pragma unroll 4
-  for (int t = begin + (int)threadIdx.x; t < end; t += (int)blockDim.x) {
-    const int n = t / hw4, i = t - n * hw4;
-    const int64_t off = ((int64_t)n * C + c) * HW;
-    float4 v = reinterpret_cast<const float4*>(x + off)[i];
-    v.x = (v.x - mu) * sc + sh; v.y = (v.y - mu) * sc + sh; v.z = (v.z - mu) * sc + sh; v.w = (v.w - mu) * sc + sh;
-    reinterpret_cast<float4*>(y + off)[i] = v;
+    for (int t = begin + (int)threadIdx.x; t < end; t += (int)blockDim.x) {
+      const int n = t / hw4, i = t - n * hw4;
+      const int64_t off = ((int64_t)n * C + c) * HW;
+      float4 v = reinterpret_cast<const float4*>(x + off)[i];
+      v.x = (v.x - mu) * sc + sh; v.y = (v.y - mu) * sc + sh; v.z = (v.z - mu) * sc + sh; v.w = (v.w - mu) * sc + sh;
+      if (relu) { v.x = v.x < 0.0f ? 0.0f : v.x; v.y = v.y < 0.0f ? 0.0f : v.y; v.z = v.z < 0.0f ? 0.0f : v.z; v.w = v.w < 0.0f ? 0.0f : v.w; }
+      reinterpret_cast<float4*>(y + off)[i] = v;
+    }
   }
 }
 
-__global__ void __launch_bounds__(512) bn_bwd_cluster_kernel(const float* __restrict__ x, const float* dy, float* dx, const float* __restrict__ gamma,
+// mask_y != null: the ReLU gradient held back by the look-ahead fusion is applied to dy on the way in (dy = mask_y > 0 ? dy : 0)
+// and the masked values are written back, so that dy ends up as the separate ReLU-gradient kernel would have left it.
+__device__ __forceinline__ float4 relu_mask(float4 d, float4 m) {
+  d.x = m.x > 0.0f ? d.x : 0.0f; d.y = m.y > 0.0f ? d.y : 0.0f; d.z = m.z > 0.0f ? d.z : 0.0f; d.w = m.w > 0.0f ? d.w : 0.0f;
+  return d;
+}
+
+template <int VPT>
+__global__ void __launch_bounds__(512, 2) bn_bwd_cluster_kernel(const float* __restrict__ x, float* dy, float* dx, const float* __restrict__ gamma,
                                                              float* dgamma, float* dbeta, const float* __restrict__ mean, const float* __restrict__ istd,
-                                                             int N, int C, int HW, int per_cta) {
+                                                             int N, int C, int HW, int per_cta, const float* mask_y) {
   cg::cluster_group cluster = cg::this_cluster();
   const unsigned K = cluster.num_blocks(), r = cluster.block_rank();
   const int c = blockIdx.x / K;
   const int hw4 = HW >> 2;
-  const int total = N * hw4, begin = (int)r * per_cta;              // the launcher keeps N * hw4 below 2^31
+  const int total = N * hw4, begin = (int)r * per_cta;
   const int end = begin + per_cta < total ? begin + per_cta : total;
   __shared__ float part[2];
   __shared__ float stat[3];
   const float mu = mean[c], is = istd[c];
   float a = 0.0f, b = 0.0f;
+  float4 kx[VPT > 0 ? VPT : 1], kd[VPT > 0 ? VPT : 1];
+  if (VPT > 0) {
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+      const int t = begin + j * (int)blockDim.x + (int)threadIdx.x;
+      if (t < end) {
+        const int n = t / hw4, i = t - n * hw4;
+        const int64_t off = ((int64_t)n * C + c) * HW;
+        kx[j] = reinterpret_cast<const float4*>(x + off)[i]; kd[j] = reinterpret_cast<const float4*>(dy + off)[i];
+        if (mask_y) { kd[j] = relu_mask(kd[j], reinterpret_cast<const float4*>(mask_y + off)[i]); reinterpret_cast<float4*>(dy + off)[i] = kd[j]; }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+      const int t = begin + j * (int)blockDim.x + (int)threadIdx.x;
+      if (t < end) {
+        const float4 v = kx[j], d = kd[j];
+        a += (d.x + d.y) + (d.z + d.w);
+        b += (d.x * ((v.x - mu) * is) + d.y * ((v.y - mu) * is)) + (d.z * ((v.z - mu) * is) + d.w * ((v.w - mu) * is));
+      }
+    }
+  } else {
 #pragma unroll 4
-  for (int t = begin + (int)threadIdx.x; t < end; t += (int)blockDim.x) {
-    const int n = t / hw4, i = t - n * hw4;
-    const int64_t off = ((int64_t)n * C + c) * HW;
-    const float4 v = reinterpret_cast<const float4*>(x + off)[i], d = reinterpret_cast<const float4*>(dy + off)[i];
-    a += (d.x + d.y) + (d.z + d.w);
-    b += (d.x * ((v.x - mu) * is) + d.y * ((v.y - mu) * is)) + (d.z * ((v.z - mu) * is) + d.w * ((v.w - mu) * is));
+    for (int t = begin + (int)threadIdx.x; t < end; t += (int)blockDim.x) {
+      const int n = t / hw4, i = t - n * hw4;
+      const int64_t off = ((int64_t)n * C + c) * HW;
+      const float4 v = reinterpret_cast<const float4*>(x + off)[i];
+      float4 d = reinterpret_cast<const float4*>(dy + off)[i];
+      if (mask_y) { d = relu_mask(d, reinterpret_cast<const float4*>(mask_y + off)[i]); reinterpret_cast<float4*>(dy + off)[i] = d; }
+      a += (d.x + d.y) + (d.z + d.w);
+      b += (d.x * ((v.x - mu) * is) + d.y * ((v.y - mu) * is)) + (d.z * ((v.z - mu) * is) + d.w * ((v.w - mu) * is));
+    }
   }
   block_sum2(a, b);
   if (threadIdx.x == 0) { part[0] = a; part[1] = b; }
@@ -319,15 +390,36 @@ __global__ void __launch_bounds__(512) bn_bwd_cluster_kernel(const float* __rest
   cluster.sync();
   if (dx == nullptr) return;                                        // uniform over the cluster, after its last barrier
   const float ca = stat[0], cb = stat[1], cc = stat[2];
+  if (VPT > 0) {
+    float4 o[VPT > 0 ? VPT : 1];
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+      const int t = begin + j * (int)blockDim.x + (int)threadIdx.x;
+      if (t < end) { const int n = t / hw4, i = t - n * hw4; o[j] = reinterpret_cast<const float4*>(dx + ((int64_t)n * C + c) * HW)[i]; }
+    }
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+      const int t = begin + j * (int)blockDim.x + (int)threadIdx.x;
+      if (t < end) {
+        const int n = t / hw4, i = t - n * hw4;
+        const float4 v = kx[j], d = kd[j];
+        float4 w = o[j];
+        w.x += ca * (d.x - cb - (v.x - mu) * is * cc); w.y += ca * (d.y - cb - (v.y - mu) * is * cc);
+        w.z += ca * (d.z - cb - (v.z - mu) * is * cc); w.w += ca * (d.w - cb - (v.w - mu) * is * cc);
+        reinterpret_cast<float4*>(dx + ((int64_t)n * C + c) * HW)[i] = w;
+      }
+    }
+  } else {
 #pragma unroll 4
-  for (int t = begin + (int)threadIdx.x; t < end; t += (int)blockDim.x) {
-    const int n = t / hw4, i = t - n * hw4;
-    const int64_t off = ((int64_t)n * C + c) * HW;
-    const float4 v = reinterpret_cast<const float4*>(x + off)[i], d = reinterpret_cast<const float4*>(dy + off)[i];
-    float4 o = reinterpret_cast<float4*>(dx + off)[i];
-    o.x += ca * (d.x - cb - (v.x - mu) * is * cc); o.y += ca * (d.y - cb - (v.y - mu) * is * cc);
-    o.z += ca * (d.z - cb - (v.z - mu) * is * cc); o.w += ca * (d.w - cb - (v.w - mu) * is * cc);
-    reinterpret_cast<float4*>(dx + off)[i] = o;
+    for (int t = begin + (int)threadIdx.x; t < end; t += (int)blockDim.x) {
+      const int n = t / hw4, i = t - n * hw4;
+      const int64_t off = ((int64_t)n * C + c) * HW;
+      const float4 v = reinterpret_cast<const float4*>(x + off)[i], d = reinterpret_cast<const float4*>(dy + off)[i];
+      float4 o = reinterpret_cast<float4*>(dx + off)[i];
+      o.x += ca * (d.x - cb - (v.x - mu) * is * cc); o.y += ca * (d.y - cb - (v.y - mu) * is * cc);
+      o.z += ca * (d.z - cb - (v.z - mu) * is * cc); o.w += ca * (d.w - cb - (v.w - mu) * is * cc);
+      reinterpret_cast<float4*>(dx + off)[i] = o;
+    }
   }
 }
 
@@ -336,6 +428,19 @@ static int bn_splits(int N, int C) {
   if (s > N) s = N;
   if (s > 64) s = 64;
   return s < 1 ? 1 : s;
+}
+
+// Issues a BN forward described by `p` (the cluster path), optionally with the ReLU of its result.
+int bn_fwd_issue(const Pending& p, bool relu) {
+  const BnClusterPlan c = bn_cluster_plan(p.N, p.C, p.HW);
+  const int r = relu ? 1 : 0;
+  if (c.per_cta <= kBnVpt * c.threads)
+    LTB_LAUNCH_CLUSTER(bn_fwd_cluster_kernel<kBnVpt>, dim3((unsigned)p.C * c.K), dim3(c.threads), c.K, p.x, p.y, p.gamma, p.beta, p.run_mean, p.run_var,
+                       p.save_mean, p.save_istd, p.N, p.C, p.HW, c.per_cta, p.eps, p.momentum, r);
+  else
+    LTB_LAUNCH_CLUSTER(bn_fwd_cluster_kernel<0>, dim3((unsigned)p.C * c.K), dim3(c.threads), c.K, p.x, p.y, p.gamma, p.beta, p.run_mean, p.run_var,
+                       p.save_mean, p.save_istd, p.N, p.C, p.HW, c.per_cta, p.eps, p.momentum, r);
+  return LTB_OK;
 }
 
 }  // namespace ltb
@@ -390,10 +495,11 @@ int ltb_bn_train_fwd(const float* x, float* y, const float* gamma, const float* 
   int64_t n = (int64_t)N * C * HW;
   bool vec = (HW & 3) == 0 && aligned16(x) && aligned16(y);
   if (vec && (int64_t)N * (HW >> 2) < ((int64_t)1 << 30)) {      // one cluster launch: statistics and result in the same kernel
-    const BnClusterPlan p = bn_cluster_plan(N, C, HW);
-    LTB_LAUNCH_CLUSTER(bn_fwd_cluster_kernel, dim3((unsigned)C * p.K), dim3(p.threads), p.K, x, y, gamma, beta, run_mean, run_var,
-                       save_mean, save_istd, N, C, HW, p.per_cta, eps, momentum);
-    return LTB_OK;
+    Pending p;
+    p.kind = PEND_BN_FWD; p.n = n; p.x = x; p.y = y; p.gamma = gamma; p.beta = beta; p.run_mean = run_mean; p.run_var = run_var;
+    p.save_mean = save_mean; p.save_istd = save_istd; p.N = N; p.C = C; p.HW = HW; p.eps = eps; p.momentum = momentum;
+    if (g.fusion) { g.pending = p; return LTB_OK; }              // held for one call: an in-place ReLU of y may join it
+    return bn_fwd_issue(p, false);
   }
   LTB_LAUNCH(bn_reduce_kernel<0>, dim3(C, S), 256, 0, x, nullptr, nullptr, nullptr, g.scratch, N, C, HW);
   LTB_LAUNCH(bn_fwd_finalize_kernel, (C + 127) / 128, 128, 0, x, (const float*)g.scratch, S, C, HW, (double)N * HW, eps, momentum,
@@ -403,17 +509,28 @@ int ltb_bn_train_fwd(const float* x, float* y, const float* gamma, const float* 
 }
 int ltb_bn_bwd(const float* x, float* dx, const float* dy, const float* gamma, float* dgamma, float* dbeta,
                const float* save_mean, const float* save_istd, int N, int C, int HW) {
-  LTB_INITED();
+  LTB_INITED_NOFLUSH();
   LTB_REQUIRE(x && dy && gamma && save_mean && save_istd && N > 0 && C > 0 && HW > 0, "ltb_bn_bwd: bad argument");
   int S = bn_splits(N, C);
   LTB_REQUIRE((size_t)C * (S * 2 + 3) * 4 <= g.scratch_bytes, "ltb_bn_bwd: too many channels");
   float* coef = g.scratch + (size_t)C * S * 2;
   int64_t n = (int64_t)N * C * HW;
   bool vec = (HW & 3) == 0 && aligned16(x) && aligned16(dy) && aligned16(dx);
-  if (vec && (int64_t)N * (HW >> 2) < ((int64_t)1 << 30)) {
+  const bool cluster_path = vec && (int64_t)N * (HW >> 2) < ((int64_t)1 << 30);
+  // a held in-place ReLU gradient on exactly this dy is applied by the kernel itself
+  const float* mask_y = nullptr;
+  if (g.pending.kind == PEND_RELU_GRAD && cluster_path && g.pending.d == dy && g.pending.n == n && aligned16(g.pending.relu_y)) {
+    mask_y = g.pending.relu_y; g.pending.kind = PEND_NONE;
+  } else if (g.pending.kind) { int rc = flush_pending(); if (rc) return rc; }
+  if (cluster_path) {
     const BnClusterPlan p = bn_cluster_plan(N, C, HW);
-    LTB_LAUNCH_CLUSTER(bn_bwd_cluster_kernel, dim3((unsigned)C * p.K), dim3(p.threads), p.K, x, dy, dx, gamma, dgamma, dbeta,
-                       save_mean, save_istd, N, C, HW, p.per_cta);
+    float* dyw = const_cast<float*>(dy);                           // written only when the held ReLU gradient is applied to it
+    if (p.per_cta <= kBnVptBwd * p.threads)
+      LTB_LAUNCH_CLUSTER(bn_bwd_cluster_kernel<kBnVptBwd>, dim3((unsigned)C * p.K), dim3(p.threads), p.K, x, dyw, dx, gamma, dgamma, dbeta,
+                         save_mean, save_istd, N, C, HW, p.per_cta, mask_y);
+    else
+      LTB_LAUNCH_CLUSTER(bn_bwd_cluster_kernel<0>, dim3((unsigned)C * p.K), dim3(p.threads), p.K, x, dyw, dx, gamma, dgamma, dbeta,
+                         save_mean, save_istd, N, C, HW, p.per_cta, mask_y);
     return LTB_OK;
   }
   LTB_LAUNCH(bn_reduce_kernel<1>, dim3(C, S), 256, 0, x, dy, save_mean, save_istd, g.scratch, N, C, HW);

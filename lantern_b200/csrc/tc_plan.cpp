@@ -119,6 +119,94 @@ bool operand_k_pixels(TcOperand& o, const float* base, int n_img, int rows, int 
   return false;
 }
 
+// ---- operands of the tap-loop convolutions: channels-last activations act[n][h][w][ch] -------------------------------
+
+// How a run of `want` consecutive pixels (row-major over h, w, then images) is cut out of images of eh x ew pixels as
+// a box of whole rows: bw x bh x bi with bw*bh*bi == want.  blocks_per_img > 1 when an image holds several boxes.
+struct PixelBox { int bw, bh, bi, per_img; };
+bool pixel_box(int want, int eh, int ew, PixelBox& b) {
+  if (ew < 1 || eh < 1 || ew > want || want % ew) return false;
+  const int rows = want / ew;
+  b.bw = ew;
+  if (rows <= eh) { if (eh % rows) return false; b.bh = rows; b.bi = 1; b.per_img = eh / rows; }
+  else { if (rows % eh) return false; b.bh = eh; b.bi = rows / eh; b.per_img = 1; }
+  return b.bw <= 256 && b.bh <= 256 && b.bi <= 256;
+}
+
+// K-major activation window.  Rows of D = pixels (n, h, w) of a th x tw grid (the output grid for forward, the input grid
+// for data-grad); row pixel (h, w) reads act[n][h*1 + off_h + dir*r][w + off_w + dir*s][ch] at tap (r, s).  K loop:
+// kiter = (r*S + s)*chunks + chunk, 32 channels per iteration.  act has eh x ew pixels per image and `ch` channels.
+bool operand_k_window(TcOperand& o, const float* act, int n_img, int eh, int ew, int ch, int th, int tw, int R, int S, int off_h, int off_w,
+                      int dir, int* k_iters) {
+  clear(o);
+  PixelBox b;
+  if (!aligned16(act) || ch % 4 || !pixel_box(kTileM, th, tw, b)) return false;
+  const int chunks = cdiv(ch, kBK);
+  o.map.base = act; o.mn_major = 0; o.nk = 4; o.stage_bytes = kTileM * 128;
+  o.map.rank = 4; o.map.swizzle = TC_SW_128;
+  o.map.dims[0] = (uint64_t)ch; o.map.dims[1] = (uint64_t)ew; o.map.dims[2] = (uint64_t)eh; o.map.dims[3] = (uint64_t)n_img;
+  o.map.strides[1] = (uint64_t)ch * 4; o.map.strides[2] = (uint64_t)ew * ch * 4; o.map.strides[3] = (uint64_t)eh * ew * ch * 4;
+  o.map.box[0] = kBK; o.map.box[1] = (uint32_t)b.bw; o.map.box[2] = (uint32_t)b.bh; o.map.box[3] = (uint32_t)b.bi;
+  if (chunks > 1) { o.k_div[0] = 1; o.k_mod[0] = chunks; o.k_mul[0] = kBK; }
+  if (S > 1) { o.k_div[1] = chunks; o.k_mod[1] = S; o.k_mul[1] = dir; }
+  if (R > 1) { o.k_div[2] = chunks * S; o.k_mod[2] = R; o.k_mul[2] = dir; }
+  o.c_off[1] = off_w; o.c_off[2] = off_h;
+  if (b.per_img > 1) { o.t_div[2] = 1; o.t_mod[2] = b.per_img; o.t_mul[2] = b.bh; }
+  o.t_div[3] = b.per_img; o.t_mul[3] = b.bi;
+  o.lbo = 16; o.sbo = 1024;
+  for (int i = 0; i < 4; ++i) o.kstep_off[i] = (uint32_t)i * 32;
+  *k_iters = R * S * chunks;
+  return true;
+}
+
+// Per-tap weight matrices wp[tap][rows][kdim] used K-major: box (32 of kdim, tile_rows rows, 1 tap); kiter as above.
+bool operand_k_taps(TcOperand& o, const float* wp, int taps, int rows, int kdim, int tile_rows, int* k_iters) {
+  clear(o);
+  if (!aligned16(wp) || kdim % 4 || rows < 1) return false;
+  const int chunks = cdiv(kdim, kBK);
+  o.map.base = wp; o.mn_major = 0; o.nk = 4; o.stage_bytes = (uint32_t)tile_rows * 128;
+  o.map.rank = 3; o.map.swizzle = TC_SW_128;
+  o.map.dims[0] = (uint64_t)kdim; o.map.dims[1] = (uint64_t)rows; o.map.dims[2] = (uint64_t)taps;
+  o.map.strides[1] = (uint64_t)kdim * 4; o.map.strides[2] = (uint64_t)rows * kdim * 4;
+  o.map.box[0] = kBK; o.map.box[1] = (uint32_t)tile_rows; o.map.box[2] = 1;
+  if (chunks > 1) { o.k_div[0] = 1; o.k_mod[0] = chunks; o.k_mul[0] = kBK; }
+  o.k_div[2] = chunks; o.k_mul[2] = 1;
+  o.t_mul[1] = tile_rows;
+  o.lbo = 16; o.sbo = 1024;
+  for (int i = 0; i < 4; ++i) o.kstep_off[i] = (uint32_t)i * 32;
+  *k_iters = taps * chunks;
+  return true;
+}
+
+// M/N-major activation for weight-grad: the M (or N) index is the channel, the K index the pixel.  One stage = 32
+// pixels (a box of whole rows of the th x tw pixel grid the reduction runs over) x tile_ch channels, stored as
+// tile_ch/32 chunks of [32 pixels][32 channels].  The tile index selects the channel block and, when taps > 1, the tap
+// whose shift (r + off_h, s + off_w) is added to the pixel coordinates: tile = (r*S + s)*ch_blocks + block.
+bool operand_mn_window(TcOperand& o, const float* act, int n_img, int eh, int ew, int ch, int th, int tw, int tile_ch, int R, int S, int off_h, int off_w,
+                       int* k_iters) {
+  clear(o);
+  PixelBox b;
+  if (!aligned16(act) || ch % 32 || tile_ch % 32 || !pixel_box(kBK, th, tw, b)) return false;
+  const int blocks = cdiv(ch, tile_ch);
+  o.map.base = act; o.mn_major = 1; o.nk = 4; o.stage_bytes = (uint32_t)tile_ch * 128;
+  o.map.rank = 5; o.map.swizzle = TC_SW_128_32B;
+  o.map.dims[0] = 32; o.map.dims[1] = (uint64_t)ew; o.map.dims[2] = (uint64_t)eh; o.map.dims[3] = (uint64_t)n_img; o.map.dims[4] = (uint64_t)ch / 32;
+  o.map.strides[1] = (uint64_t)ch * 4; o.map.strides[2] = (uint64_t)ew * ch * 4; o.map.strides[3] = (uint64_t)eh * ew * ch * 4; o.map.strides[4] = 128;
+  o.map.box[0] = 32; o.map.box[1] = (uint32_t)b.bw; o.map.box[2] = (uint32_t)b.bh; o.map.box[3] = (uint32_t)b.bi; o.map.box[4] = (uint32_t)tile_ch / 32;
+  // reduction: pixel blocks of the th x tw grid, image after image
+  if (b.per_img > 1) { o.k_div[2] = 1; o.k_mod[2] = b.per_img; o.k_mul[2] = b.bh; }
+  o.k_div[3] = b.per_img; o.k_mul[3] = b.bi;
+  // tile: channel block, then tap
+  o.t_div[4] = 1; o.t_mod[4] = blocks; o.t_mul[4] = tile_ch / 32;
+  if (S > 1) { o.t_div[1] = blocks; o.t_mod[1] = S; o.t_mul[1] = 1; }
+  if (R > 1) { o.t_div[2] = blocks * S; o.t_mod[2] = R; o.t_mul[2] = 1; }
+  o.c_off[1] = off_w; o.c_off[2] = off_h;
+  o.lbo = kBK * 128; o.sbo = 512;
+  for (int i = 0; i < 4; ++i) o.kstep_off[i] = (uint32_t)i * 1024;
+  *k_iters = b.per_img > 1 ? n_img * b.per_img : cdiv(n_img, b.bi);
+  return true;
+}
+
 // Tile width.  The MMA-issuing thread spends a few hundred cycles per k-iteration whatever the width, so narrow tiles
 // leave the tensor core idle; 128 columns with three stages lets two CTAs share an SM (one's epilogue and issue gaps
 // overlap the other's main loop).  Parallelism for small outputs comes from split-K, not from narrower tiles.
@@ -139,6 +227,33 @@ void finish(TcPlan& p, int M, int N, int k_iters, int sm_count, bool may_split) 
 }
 
 }  // namespace
+
+bool tc_walk_of(const TcOperand& o, TcWalk& w) {
+  std::memset(&w, 0, sizeof w);
+  w.n0 = w.n1 = 1 << 30;
+  int D[5], nd = 0;
+  auto moves = [&](int d) { return o.k_mul[d] != 0 && o.k_mod[d] > 1; };     // a modulus of 1 pins the coordinate
+  for (int d = 0; d < 5; ++d) {
+    if (!moves(d)) continue;
+    bool seen = false;
+    for (int i = 0; i < nd; ++i) seen = seen || D[i] == o.k_div[d];
+    if (!seen) D[nd++] = o.k_div[d];
+  }
+  if (nd == 0) return true;
+  for (int i = 0; i < nd; ++i) for (int j = i + 1; j < nd; ++j) if (D[j] < D[i]) { int t = D[i]; D[i] = D[j]; D[j] = t; }
+  if (D[0] != 1) { if (nd == 5) return false; for (int i = nd; i > 0; --i) D[i] = D[i - 1]; D[0] = 1; ++nd; }
+  if (nd > 3) return false;
+  int n[3] = {1 << 30, 1 << 30, 1 << 30};
+  for (int j = 0; j + 1 < nd; ++j) { if (D[j + 1] % D[j]) return false; n[j] = D[j + 1] / D[j]; }
+  w.n0 = n[0]; w.n1 = n[1];
+  for (int j = 0; j < nd; ++j) for (int d = 0; d < 5; ++d) {
+    if (!moves(d)) continue;
+    int v = o.k_div[d] == D[j] ? o.k_mul[d] : 0;
+    for (int i = 0; i < j; ++i) if (o.k_div[d] == D[i]) v -= o.k_mul[d] * (n[i] - 1);
+    w.inc[j][d] = v;
+  }
+  return true;
+}
 
 bool tc_conv_needs_rows(int pix) { return !(pix >= 32 && pix % 32 == 0 && (pix >= kTileM ? pix % kTileM == 0 : kTileM % pix == 0)); }
 
@@ -179,6 +294,56 @@ bool tc_plan_conv_wgrad(TcPlan& p, const float* x, const float* dy, float* dw, i
   if (!operand_k_pixels(p.b, x, n_img, ck, pix, p.bn, &kb) || ka != kb) return false;
   finish(p, co, ck, ka, sm_count, true);
   p.epilogue = TC_EPI_ROWMAJOR; p.out = dw; p.bias = nullptr; p.alpha = 1.0f; p.accumulate = 1; p.ld = ck;
+  return true;
+}
+
+static bool taps_geometry_ok(const TcConvGeom& g) {
+  return g.n_img >= 1 && g.R * g.S > 1 && g.R <= 7 && g.S <= 7 && g.oH == g.H + 2 * g.ph - g.R + 1 && g.oW == g.W + 2 * g.pw - g.S + 1 &&
+         g.oH >= 1 && g.oW >= 1 && g.C % 32 == 0 && g.K % 32 == 0 && (int64_t)g.n_img * g.H * g.W < (1ll << 30);
+}
+
+bool tc_plan_conv_taps_fwd(TcPlan& p, const float* xr, const float* wt, const float* bias, float* y, const TcConvGeom& g, int sm_count) {
+  std::memset(&p, 0, sizeof p);
+  if (!taps_geometry_ok(g)) return false;
+  int ka = 0, kb = 0;
+  const int M = g.n_img * g.oH * g.oW;
+  // output pixel (oh, ow) reads input (oh - ph + r, ow - pw + s)
+  if (!operand_k_window(p.a, xr, g.n_img, g.H, g.W, g.C, g.oH, g.oW, g.R, g.S, -g.ph, -g.pw, +1, &ka)) return false;
+  p.bn = pick_bn(g.K, cdiv(M, kTileM), sm_count);
+  if (!operand_k_taps(p.b, wt, g.R * g.S, g.K, g.C, p.bn, &kb) || ka != kb) return false;
+  finish(p, M, g.K, ka, sm_count, true);
+  p.epilogue = TC_EPI_PIXEL; p.out = y; p.bias = bias; p.alpha = 1.0f; p.accumulate = 0;
+  p.pix_per_img = (int64_t)g.oH * g.oW; p.img_stride = (int64_t)g.K * g.oH * g.oW; p.chan_stride = (int64_t)g.oH * g.oW;
+  return true;
+}
+
+bool tc_plan_conv_taps_dgrad(TcPlan& p, const float* dyr, const float* wd, float* dx, const TcConvGeom& g, bool accumulate, int sm_count) {
+  std::memset(&p, 0, sizeof p);
+  if (!taps_geometry_ok(g)) return false;
+  int ka = 0, kb = 0;
+  const int M = g.n_img * g.H * g.W;
+  // input pixel (h, w) receives dy(h + ph - r, w + pw - s) * w[k][c][r][s]
+  if (!operand_k_window(p.a, dyr, g.n_img, g.oH, g.oW, g.K, g.H, g.W, g.R, g.S, g.ph, g.pw, -1, &ka)) return false;
+  p.bn = pick_bn(g.C, cdiv(M, kTileM), sm_count);
+  if (!operand_k_taps(p.b, wd, g.R * g.S, g.C, g.K, p.bn, &kb) || ka != kb) return false;
+  finish(p, M, g.C, ka, sm_count, true);
+  p.epilogue = TC_EPI_PIXEL; p.out = dx; p.bias = nullptr; p.alpha = 1.0f; p.accumulate = accumulate ? 1 : 0;
+  p.pix_per_img = (int64_t)g.H * g.W; p.img_stride = (int64_t)g.C * g.H * g.W; p.chan_stride = (int64_t)g.H * g.W;
+  return true;
+}
+
+bool tc_plan_conv_taps_wgrad(TcPlan& p, const float* dyr, const float* xr, float* dw, const TcConvGeom& g, int sm_count) {
+  std::memset(&p, 0, sizeof p);
+  if (!taps_geometry_ok(g) || g.C % 64) return false;
+  int ka = 0, kb = 0;
+  const int taps = g.R * g.S;
+  // dw[k][c][r][s] += sum over output pixels dy[n][k][oh][ow] * x[n][c][oh - ph + r][ow - pw + s]
+  if (!operand_mn_window(p.a, dyr, g.n_img, g.oH, g.oW, g.K, g.oH, g.oW, kTileM, 1, 1, 0, 0, &ka)) return false;
+  p.bn = g.C % 128 == 0 ? 128 : 64;
+  if (!operand_mn_window(p.b, xr, g.n_img, g.H, g.W, g.C, g.oH, g.oW, p.bn, g.R, g.S, -g.ph, -g.pw, &kb) || ka != kb) return false;
+  finish(p, g.K, taps * g.C, ka, sm_count, true);
+  p.epilogue = TC_EPI_ROWMAJOR; p.out = dw; p.bias = nullptr; p.alpha = 1.0f; p.accumulate = 1; p.ld = (int64_t)taps * g.C;
+  p.col_mod = g.C; p.col_mul = taps;
   return true;
 }
 

@@ -32,15 +32,23 @@ struct TcTensorMap {          // arguments of cuTensorMapEncodeTiled for one FP3
 
 struct TcOperand {
   TcTensorMap map;
-  // box coordinate d = ((tile / t_div[d]) % t_mod[d]) * t_mul[d] + ((kiter / k_div[d]) % k_mod[d]) * k_mul[d]
+  // box coordinate d = c_off[d] + ((tile / t_div[d]) % t_mod[d]) * t_mul[d] + ((kiter / k_div[d]) % k_mod[d]) * k_mul[d]
+  // (c_off and k_mul may be negative: the taps of a convolution window start left of / above the image, where TMA fills zeros)
   int t_div[5], t_mod[5], t_mul[5];
   int k_div[5], k_mod[5], k_mul[5];
+  int c_off[5];
   uint32_t stage_bytes;       // bytes one stage of this operand occupies (== bytes the TMA box delivers)
   int mn_major;               // 0: K-major, 1: M/N-major (instruction descriptor transpose bit)
   uint32_t lbo, sbo;          // bytes
   int nk;                     // MMA steps (K = 8 each) per stage
   uint32_t kstep_off[8];      // start-address offset of each step within the stage
 };
+
+// The k part of the coordinates as a mixed-radix counter, so that the single producer thread advances them with additions
+// only: level 0 steps n0 times, then level 1 steps once (and level 0 returns to its start), after n1 of those level 2
+// steps.  inc[j][d] is what reaching level j adds to coordinate d (returns of the lower levels included).
+struct TcWalk { int n0, n1; int inc[3][5]; };
+bool tc_walk_of(const TcOperand& o, TcWalk& w);
 
 enum TcEpilogue {
   TC_EPI_PIXEL = 0,   // D row = pixel, D column = channel: out[img][chan][pix]   (conv forward / data-grad)
@@ -59,6 +67,7 @@ struct TcPlan {
   int accumulate;             // 1: out += ..., 0: out = ...   (split-K > 1 forces atomic accumulation)
   int64_t pix_per_img, img_stride, chan_stride;   // TC_EPI_PIXEL
   int64_t ld;                                     // TC_EPI_ROWMAJOR
+  int col_mod, col_mul;                           // TC_EPI_ROWMAJOR, when col_mul != 0: D column n is stored at column (n % col_mod) * col_mul + n / col_mod
 };
 
 // "Flat" convolution view: activations X[n][k][p] with p contiguous (k = channels, or channels*kh*kw after unfolding),
@@ -73,6 +82,16 @@ bool tc_conv_needs_rows(int pix);
 bool tc_plan_conv_fwd(TcPlan& p, const float* x, bool a_rows, const float* w, const float* bias, float* y, int n_img, int ck, int co, int pix, int sm_count);
 bool tc_plan_conv_dgrad(TcPlan& p, const float* dy, bool a_rows, const float* w, float* dx, int n_img, int ck, int co, int pix, bool accumulate, int sm_count);
 bool tc_plan_conv_wgrad(TcPlan& p, const float* x, const float* dy, float* dw, int n_img, int ck, int co, int pix, int sm_count);
+// Implicit ("tap loop") forms for R x S convolutions with stride 1.  The activations are channels-last copies
+// xr[n][h][w][c] and dyr[n][oh][ow][k] (made by a transposing copy); a TMA box then is a window of whole image rows
+// with 32 channels, and the tap (r, s) only shifts the box coordinates -- the nine-fold unfolded matrix never exists.
+//   forward : rows = output pixels, K loop = (r, s, channel block); weights permuted to wt[r*S+s][k][c]
+//   dgrad   : rows = input pixels,  K loop = (r, s, k block);       weights permuted to wd[r*S+s][c][k]
+//   wgrad   : D = k x (tap, c), K loop = blocks of 32 pixels, both operands M/N-major; stored to OIHW through col_mod/col_mul
+struct TcConvGeom { int n_img, C, H, W, K, R, S, ph, pw, oH, oW; };
+bool tc_plan_conv_taps_fwd(TcPlan& p, const float* xr, const float* wt, const float* bias, float* y, const TcConvGeom& g, int sm_count);
+bool tc_plan_conv_taps_dgrad(TcPlan& p, const float* dyr, const float* wd, float* dx, const TcConvGeom& g, bool accumulate, int sm_count);
+bool tc_plan_conv_taps_wgrad(TcPlan& p, const float* dyr, const float* xr, float* dw, const TcConvGeom& g, int sm_count);
 // C[M,N] (op)= alpha * A B; a_kmajor: A stored [M,K] (else [K,M]); b_kmajor: B stored [N,K] (else [K,N]).
 bool tc_plan_gemm(TcPlan& p, const float* a, bool a_kmajor, const float* b, bool b_kmajor, float* c, int M, int N, int K, float alpha,
                   bool accumulate, int sm_count);

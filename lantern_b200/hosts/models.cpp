@@ -268,6 +268,7 @@ extern "C" {
 
 void* HOST_FN(model_create)(const char* name, int batch, int seed) {
   std::string n(name);
+  BK(set_fusion)(1);     // generated programs issue every device operation through the library: the one-call look-ahead is safe
   if (n == "mnist") return new Mnist(batch, seed);
   if (n == "resnet50") return new ResNet50(batch, seed);
   if (n == "squeezenet") return new SqueezeNet(batch, seed);

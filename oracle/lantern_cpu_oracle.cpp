@@ -194,6 +194,7 @@ int ora_last_error(char* buf, int len) {
 int ora_set_stream(void*) { return LTB_OK; }
 void* ora_get_stream(void) { return nullptr; }
 int ora_sync(void) { return LTB_OK; }
+int ora_set_fusion(int) { return LTB_OK; }   // the CPU build executes every call at once
 int ora_set_math(int mode) { g.math = mode; return LTB_OK; }
 int ora_device_status(void) { return LTB_OK; }
 int64_t ora_kernel_launches(void) { return 0; }

@@ -24,7 +24,7 @@ static uint32_t swz(uint32_t off, int mode) {
 static int span(int mode) { return (mode == TC_SW_128 || mode == TC_SW_128_32B) ? 128 : mode == TC_SW_64 ? 64 : mode == TC_SW_32 ? 32 : 16; }
 
 static void coords_of(const TcOperand& o, int tile, int kiter, int64_t* c) {
-  for (int d = 0; d < 5; ++d) c[d] = (int64_t)((tile / o.t_div[d]) % o.t_mod[d]) * o.t_mul[d] + (int64_t)((kiter / o.k_div[d]) % o.k_mod[d]) * o.k_mul[d];
+  for (int d = 0; d < 5; ++d) c[d] = (int64_t)o.c_off[d] + (int64_t)((tile / o.t_div[d]) % o.t_mod[d]) * o.t_mul[d] + (int64_t)((kiter / o.k_div[d]) % o.k_mod[d]) * o.k_mul[d];
 }
 static bool tma_load(const TcOperand& o, int tile, int kiter, std::vector<float>& smem) {
   const TcTensorMap& m = o.map;
@@ -64,8 +64,27 @@ static float umma_fetch(const TcOperand& o, const std::vector<float>& smem, int 
   return smem[off / 4];
 }
 
+// The producer's incremental walk (TcWalk) must visit the coordinates the closed formula gives, from any starting iteration.
+static bool walk_matches(const TcOperand& o, int tile, int k_iters) {
+  TcWalk w;
+  if (!tc_walk_of(o, w)) { printf("operand has no walk\n"); return false; }
+  for (int k0 = 0; k0 < k_iters; k0 += (k_iters > 7 ? k_iters / 7 : 1)) {
+    int64_t c[5]; coords_of(o, tile, k0, c);
+    int i0 = k0 % w.n0, i1 = (k0 / w.n0) % w.n1;
+    for (int it = k0; it < k_iters; ++it) {
+      int64_t want[5]; coords_of(o, tile, it, want);
+      for (int d = 0; d < 5; ++d) if (c[d] != want[d]) { printf("walk: coordinate %d at iteration %d (start %d): %lld, formula %lld\n", d, it, k0, (long long)c[d], (long long)want[d]); return false; }
+      int lvl = 0;
+      if (++i0 == w.n0) { i0 = 0; lvl = 1; if (++i1 == w.n1) { i1 = 0; lvl = 2; } }
+      for (int d = 0; d < 5; ++d) c[d] += w.inc[lvl][d];
+    }
+  }
+  return true;
+}
+
 static bool run_plan(const TcPlan& p, size_t out_count) {
   if (p.a.nk != p.b.nk) { printf("nk mismatch\n"); return false; }
+  if (!walk_matches(p.a, p.m_tiles - 1, p.k_iters) || !walk_matches(p.b, p.n_tiles - 1, p.k_iters)) return false;
   // overwrite semantics under split-K: the launcher zeroes the output, then every split accumulates atomically
   if (p.splits > 1 && !p.accumulate) for (size_t i = 0; i < out_count; ++i) p.out[i] = 0.0f;
   std::vector<float> sa, sb;
@@ -84,7 +103,8 @@ static bool run_plan(const TcPlan& p, size_t out_count) {
     for (int r = 0; r < 128; ++r) for (int c = 0; c < p.bn; ++c) {
       int64_t m = (int64_t)mt * 128 + r, n = (int64_t)nt * p.bn + c;
       if (m >= p.M || n >= p.N) continue;
-      int64_t idx = p.epilogue == TC_EPI_PIXEL ? (m / p.pix_per_img) * p.img_stride + n * p.chan_stride + (m % p.pix_per_img) : m * p.ld + n;
+      int64_t idx = p.epilogue == TC_EPI_PIXEL ? (m / p.pix_per_img) * p.img_stride + n * p.chan_stride + (m % p.pix_per_img)
+                                                : m * p.ld + (p.col_mul ? (n % p.col_mod) * p.col_mul + n / p.col_mod : n);
       if ((size_t)idx >= out_count) { printf("epilogue index out of range\n"); return false; }
       float v = p.alpha * (float)D[(size_t)r * p.bn + c] + ((p.bias && z == 0) ? p.bias[n] : 0.0f);
       if (p.accumulate || atomic) p.out[idx] += v; else p.out[idx] = v;
@@ -132,6 +152,41 @@ static int conv_case(int n_img, int ck, int co, int pix) {
   return taken;
 }
 
+// R x S convolution with stride 1 through the tap-loop plans, against a direct evaluation.
+static int taps_case(int n_img, int C, int K, int H, int W, int R, int S, int ph, int pw) {
+  const int oH = H + 2 * ph - R + 1, oW = W + 2 * pw - S + 1, taps = R * S;
+  TcConvGeom g{n_img, C, H, W, K, R, S, ph, pw, oH, oW};
+  auto x = rnd((size_t)n_img * C * H * W, 11), w = rnd((size_t)K * C * taps, 12), dy = rnd((size_t)n_img * K * oH * oW, 13), bias = rnd(K, 14);
+  std::vector<float> y((size_t)n_img * K * oH * oW, 7.0f), yr(y.size()), dx(x.size(), 0.5f), dxr(dx), dw(w.size(), -1.0f), dwr(dw);
+  auto X = [&](int n, int c, int h, int ww) -> double { return (h < 0 || h >= H || ww < 0 || ww >= W) ? 0.0 : x[(((size_t)n * C + c) * H + h) * W + ww]; };
+  for (int n = 0; n < n_img; ++n) for (int k = 0; k < K; ++k) for (int oh = 0; oh < oH; ++oh) for (int ow = 0; ow < oW; ++ow) {
+    double s = bias[k];
+    for (int c = 0; c < C; ++c) for (int r = 0; r < R; ++r) for (int q = 0; q < S; ++q) s += X(n, c, oh - ph + r, ow - pw + q) * w[(((size_t)k * C + c) * R + r) * S + q];
+    yr[(((size_t)n * K + k) * oH + oh) * oW + ow] = (float)s;
+    const double d = dy[(((size_t)n * K + k) * oH + oh) * oW + ow];
+    for (int c = 0; c < C; ++c) for (int r = 0; r < R; ++r) for (int q = 0; q < S; ++q) {
+      const int h = oh - ph + r, ww = ow - pw + q;
+      if (h < 0 || h >= H || ww < 0 || ww >= W) continue;
+      dxr[(((size_t)n * C + c) * H + h) * W + ww] += (float)(d * w[(((size_t)k * C + c) * R + r) * S + q]);
+      dwr[(((size_t)k * C + c) * R + r) * S + q] += (float)(d * x[(((size_t)n * C + c) * H + h) * W + ww]);
+    }
+  }
+  // what the library's staging kernels produce: channels-last copies and per-tap weight matrices
+  std::vector<float> xr(x.size()), dyr(dy.size()), wt(w.size()), wd(w.size());
+  for (int n = 0; n < n_img; ++n) for (int c = 0; c < C; ++c) for (int i = 0; i < H * W; ++i) xr[((size_t)n * H * W + i) * C + c] = x[((size_t)n * C + c) * H * W + i];
+  for (int n = 0; n < n_img; ++n) for (int k = 0; k < K; ++k) for (int i = 0; i < oH * oW; ++i) dyr[((size_t)n * oH * oW + i) * K + k] = dy[((size_t)n * K + k) * oH * oW + i];
+  for (int k = 0; k < K; ++k) for (int c = 0; c < C; ++c) for (int t = 0; t < taps; ++t) {
+    wt[((size_t)t * K + k) * C + c] = w[((size_t)k * C + c) * taps + t];
+    wd[((size_t)t * C + c) * K + k] = w[((size_t)k * C + c) * taps + t];
+  }
+  int taken = 0; TcPlan p;
+  if (tc_plan_conv_taps_fwd(p, xr.data(), wt.data(), bias.data(), y.data(), g, 148)) { ++taken; if (!run_plan(p, y.size()) || !close(yr, y, "taps fwd")) return -1; }
+  if (tc_plan_conv_taps_dgrad(p, dyr.data(), wd.data(), dx.data(), g, true, 148)) { ++taken; if (!run_plan(p, dx.size()) || !close(dxr, dx, "taps dgrad")) return -1; }
+  if (tc_plan_conv_taps_wgrad(p, dyr.data(), xr.data(), dw.data(), g, 148)) { ++taken; if (!run_plan(p, dw.size()) || !close(dwr, dw, "taps wgrad")) return -1; }
+  printf("taps conv n=%d C=%d K=%d %dx%d k%dx%d pad %d,%d: %d of 3 plans taken, all match\n", n_img, C, K, H, W, R, S, ph, pw, taken);
+  return taken;
+}
+
 static int gemm_case(int M, int N, int K, bool ak, bool bk, bool acc) {
   auto a = rnd((size_t)M * K, 5), b = rnd((size_t)N * K, 6);
   std::vector<float> c((size_t)M * N, 2.0f), cr(c);
@@ -151,6 +206,11 @@ int main() {
   const int convs[][4] = {{2, 64, 64, 256}, {3, 64, 256, 256}, {4, 128, 96, 64}, {5, 256, 128, 64}, {11, 256, 128, 16}, {35, 512, 64, 4}, {1, 32, 48, 1024},
                           {8, 576, 64, 256}, {2, 40, 64, 32}, {3, 64, 64, 36}, {2, 2048, 512, 4}, {9, 1024, 256, 16}, {70, 512, 32, 1}};
   for (auto& c : convs) { int r = conv_case(c[0], c[1], c[2], c[3]); if (r < 0) ++bad; else taken += r; }
+  const int taps[][9] = {{3, 64, 64, 16, 16, 3, 3, 1, 1}, {5, 128, 128, 8, 8, 3, 3, 1, 1}, {9, 64, 128, 4, 4, 3, 3, 1, 1}, {35, 64, 64, 2, 2, 3, 3, 1, 1},
+                         {1, 32, 64, 32, 32, 3, 3, 1, 1}, {2, 64, 32, 16, 16, 3, 3, 0, 0}, {2, 64, 64, 8, 8, 5, 5, 2, 2}, {3, 96, 64, 8, 8, 1, 3, 0, 1}};
+  int taps_taken = 0;
+  for (auto& c : taps) { int r = taps_case(c[0], c[1], c[2], c[3], c[4], c[5], c[6], c[7], c[8]); if (r < 0) ++bad; else { taken += r; taps_taken += r; } }
+  if (taps_taken < 14) { printf("too few tap-loop plans taken (%d)\n", taps_taken); ++bad; }
   for (int ak = 0; ak < 2; ++ak) for (int bk = 0; bk < 2; ++bk) for (int acc = 0; acc < 2; ++acc) {
     int r = gemm_case(160, 96, 72, ak, bk, acc); if (r < 0) ++bad; else taken += r;
     r = gemm_case(128, 256, 2048, ak, bk, acc); if (r < 0) ++bad; else taken += r;

@@ -112,6 +112,8 @@ def test_training_trajectory_and_graph_replay(oracle_lib, cuda_lib):
     for s in range(3):
         x, y = _batch(eager, s, "normal")
         le.append(eager.step(x, y, 0.002))
+        if s == 0:
+            eager_first = eager.slab_params()
     eager_params = eager.slab_params()
     eager.close(); cuda_lib.reset(mg_mark)
     replay = hp.model("resnet50", 4, seed=1)
@@ -120,13 +122,17 @@ def test_training_trajectory_and_graph_replay(oracle_lib, cuda_lib):
     for s in range(3):
         x, y = _batch(replay, s, "normal")
         replay.step_async(x, y, 0.002); cuda_lib.sync(); lr_.append(replay.last_loss())
+        if s == 0:
+            replay_first = replay.slab_params()
     assert cuda_lib.kernel_launches() > before
+    # one step from the same state: only the rounding of the atomically combined sums separates the two runs
+    assert_close(eager_first, replay_first, 1e-3, "parameters after the first replayed step")
     # split-K partial sums are combined with atomics, so two runs agree to rounding, not bit for bit
     assert abs(le[0] - lr_[0]) <= 2e-6 * abs(le[0]), (le, lr_)   # same forward pass; the classifier's split-K sums combine atomically
     # later steps differ by the run-to-run noise of the atomically combined split-K sums, amplified by ReLU boundary
     # flips (two eager runs differ just as much): bounds, not equality
-    assert np.allclose(le, lr_, rtol=2e-2), (le, lr_)
-    assert_close(eager_params, replay.slab_params(), 2e-2, "parameters after three replayed steps")
+    assert np.allclose(le, lr_, rtol=5e-2), (le, lr_)
+    assert_close(eager_params, replay.slab_params(), 5e-2, "parameters after three replayed steps")
     replay.close()
     cuda_lib.set_math(1)
     cuda_lib.reset(mg_mark)

@@ -5,7 +5,7 @@ import pytest
 
 from lantern_b200.backend import TensorR
 from tests.golden.reference_known_answers import CASES
-from tests.parity import FP32_RTOL, TF32_RTOL, check
+from tests.parity import FP32_RTOL, TF32_RTOL, assert_close, check
 
 pytestmark = pytest.mark.gpu
 R = lambda seed: np.random.default_rng(seed)
@@ -326,7 +326,11 @@ TC_CONVS = [  # N, C, H, W, K, R, stride, pad: the ResNet-50 / SqueezeNet layer 
     (4, 96, 16, 16, 16, 1, 1, 0), (8, 512, 4, 4, 10, 4, 1, 0), (3, 96, 32, 32, 16, 1, 1, 0), (3, 16, 16, 16, 64, 3, 1, 1),
     # SqueezeNet fire modules: channel counts that are not multiples of 32 (K tails filled with zeros by the TMA unit)
     (8, 48, 8, 8, 192, 1, 1, 0), (8, 48, 8, 8, 192, 3, 1, 1), (8, 256, 8, 8, 48, 1, 1, 0), (8, 384, 8, 8, 48, 1, 1, 0),
-    (8, 128, 16, 16, 32, 1, 1, 0), (8, 32, 16, 16, 128, 3, 1, 1), (8, 64, 4, 4, 256, 3, 1, 1), (8, 512, 4, 4, 64, 1, 1, 0)]
+    (8, 128, 16, 16, 32, 1, 1, 0), (8, 32, 16, 16, 128, 3, 1, 1), (8, 64, 4, 4, 256, 3, 1, 1), (8, 512, 4, 4, 64, 1, 1, 0),
+    # more stride-1 windows for the tap-loop plans: 32x32 images, 5x5 taps, image counts that leave partial tiles
+    (4, 64, 32, 32, 64, 3, 1, 1), (6, 64, 8, 8, 64, 5, 1, 2), (5, 128, 16, 16, 64, 3, 1, 1), (21, 64, 2, 2, 128, 3, 1, 1),
+    # large enough (unfolded matrix >= 64 MB) for the tap-loop weight-grad
+    (112, 64, 16, 16, 64, 3, 1, 1), (30, 64, 32, 32, 64, 3, 1, 1)]
 
 
 @pytest.mark.parametrize("cfg", TC_CONVS, ids=[str(c) for c in TC_CONVS])
@@ -350,3 +354,77 @@ def test_conv_fwd_bwd_tf32(ora, gpu, cfg):
 
 def test_tensor_core_engine_reports_no_timeouts(gpu):
     assert gpu.lib.device_status() == 0
+
+
+# ---------------------------------------------------------------------------------------------- look-ahead fusion
+@pytest.mark.parametrize("cfg", [(16, 64, 16, 16), (8, 256, 4, 4), (128, 64, 32, 32), (5, 7, 3, 5), (33, 512, 2, 2)])
+def test_lookahead_fusion_gives_the_results_of_separate_calls(ora, gpu, cfg):
+    """conv-net block fragment: y = relu_(bn(x)); z = relu_(y + s); backward through both. With ltb_set_fusion(1) the
+    BN+ReLU, add+ReLU, ReLU-grad+add-grad and ReLU-grad+BN-backward pairs run as single kernels; every tensor, including
+    the in-place masked gradients, must be bit-identical to the unfused run and within tolerance of the oracle."""
+    N, C, H, W = cfg
+    v = (R(1).standard_normal((N, C, H, W)) * 2 + 0.5).astype(np.float32)
+    sk = R(5).standard_normal((N, C, H, W)).astype(np.float32)
+    g0, b0 = (R(2).random(C, dtype=np.float32) + 0.5), R(3).standard_normal(C).astype(np.float32)
+    dz0 = R(4).standard_normal((N, C, H, W)).astype(np.float32)
+
+    def f(b, fusion=0):
+        b.lib.set_fusion(fusion)
+        try:
+            x, s = TensorR(b.fromNumpy(v)), TensorR(b.fromNumpy(sk))
+            scale, bias = TensorR(b.fromNumpy(g0)), TensorR(b.fromNumpy(b0))
+            rm, rv = b.fill((C,), 0.0), b.fill((C,), 1.0)
+            y, sm, si, _ = b.batchNormTraining(x.x, scale.x, bias.x, rm, rv)
+            yr = TensorR(b.relu(y, True))                                  # in place: joins the BN kernel
+            z = TensorR(b.relu(b.plus(yr.x, s.x)[0], True))                # in place: joins the add kernel
+            z.d = b.fromNumpy(dz0)
+            b.relu_grad(z, z, True)                                        # held ...
+            b.add_grad(yr, s, z)                                           # ... and absorbed by the add's gradient
+            b.relu_grad(yr, yr, True)                                      # held ...
+            b.batchNorm_grad(x, yr, scale, bias, sm, si)                   # ... and absorbed by BN backward
+            out = {"y": yr.x.toCPU(), "z": z.x.toCPU(), "dz": z.d.toCPU(), "dy": yr.d.toCPU(), "ds": s.d.toCPU(), "dx": x.d.toCPU(),
+                   "dgamma": scale.d.toCPU(), "dbeta": bias.d.toCPU(), "rm": rm.toCPU(), "rv": rv.toCPU()}
+        finally:
+            b.lib.set_fusion(0)
+        return out
+    ref = f(ora)
+    plain = f(gpu, 0)
+    fused = f(gpu, 1)
+    for k in ref:
+        assert np.array_equal(plain[k], fused[k]), k + ": fused and separate kernels differ"
+    for k in ("y", "z", "rm", "rv"):
+        assert_close(ref[k], fused[k], 2e-4, k)
+    # gradients pass through two ReLU masks: an activation within rounding of zero may fall on the other side in the two
+    # implementations and switch single elements on or off, so a handful of elements out of millions may differ
+    for k in ("dz", "dy", "ds", "dx"):
+        bad = np.abs(ref[k] - fused[k]) > 2e-4 * np.abs(ref[k]).max()
+        assert bad.mean() < 2e-5, (k, int(bad.sum()), bad.size)
+    for k in ("dgamma", "dbeta"):
+        assert_close(ref[k], fused[k], 2e-2, k)          # a flipped element is a visible part of a per-channel sum
+
+
+def test_lookahead_fusion_flushes_on_any_other_call(ora, gpu):
+    """A held operation that nothing joins is issued by the next call, whatever it is."""
+    v = R(1).standard_normal((4, 32, 8, 8)).astype(np.float32)
+    g0, b0 = np.ones(32, np.float32), np.zeros(32, np.float32)
+
+    def f(b, fusion=0):
+        b.lib.set_fusion(fusion)
+        try:
+            x = TensorR(b.fromNumpy(v))
+            rm, rv = b.fill((32,), 0.0), b.fill((32,), 1.0)
+            y, sm, si, _ = b.batchNormTraining(x.x, b.fromNumpy(g0), b.fromNumpy(b0), rm, rv)
+            y_now = y.toCPU()                                              # a copy, not a ReLU: BN must have run by now
+            t = b.tanh(y)                                                  # not a ReLU either
+            a = b.plus(y, t)[0]                                            # held add ...
+            a_sum = b.sum(a)                                               # ... flushed by a reduction that reads it
+            yd = TensorR(y, b.fromNumpy(v * 0.5))
+            b.relu_grad(yd, yd, True)                                      # held ReLU gradient ...
+            d_now = yd.d.toCPU()                                           # ... flushed by the read-back
+            out = {"y": y_now, "t": t.toCPU(), "a": a.toCPU(), "sum": a_sum.toCPU(), "d": d_now}
+        finally:
+            b.lib.set_fusion(0)
+        return out
+    ref, got = f(ora), f(gpu, 1)
+    for k in ref:
+        assert_close(ref[k], got[k], 2e-4, k)
