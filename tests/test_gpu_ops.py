@@ -330,7 +330,10 @@ TC_CONVS = [  # N, C, H, W, K, R, stride, pad: the ResNet-50 / SqueezeNet layer 
     # more stride-1 windows for the tap-loop plans: 32x32 images, 5x5 taps, image counts that leave partial tiles
     (4, 64, 32, 32, 64, 3, 1, 1), (6, 64, 8, 8, 64, 5, 1, 2), (5, 128, 16, 16, 64, 3, 1, 1), (21, 64, 2, 2, 128, 3, 1, 1),
     # large enough (unfolded matrix >= 64 MB) for the tap-loop weight-grad
-    (112, 64, 16, 16, 64, 3, 1, 1), (30, 64, 32, 32, 64, 3, 1, 1)]
+    (112, 64, 16, 16, 64, 3, 1, 1), (30, 64, 32, 32, 64, 3, 1, 1),
+    # small images whose count fills whole 128-byte rows: fed M/N-major straight from NCHW (no transposing copy)
+    (8, 256, 4, 4, 1024, 1, 1, 0), (16, 512, 2, 2, 2048, 1, 1, 0), (8, 1024, 4, 4, 256, 1, 1, 0), (40, 64, 2, 2, 64, 1, 1, 0),
+    (8, 256, 8, 8, 256, 3, 2, 1), (16, 512, 4, 4, 512, 3, 2, 1), (8, 512, 8, 8, 1024, 1, 2, 0)]
 
 
 @pytest.mark.parametrize("cfg", TC_CONVS, ids=[str(c) for c in TC_CONVS])
