@@ -18,6 +18,7 @@ _SIGS = {
     "model_slab_params": (ctypes.c_void_p, [ctypes.c_void_p]),
     "model_slab_grads": (ctypes.c_void_p, [ctypes.c_void_p]),
     "model_input_count": (ctypes.c_int64, [ctypes.c_void_p]),
+    "model_label_count": (ctypes.c_int64, [ctypes.c_void_p]),
     "model_use_graph": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int]),
     "model_set_resident": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]),
     "model_step": (ctypes.c_float, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_float, ctypes.c_int]),
@@ -54,12 +55,13 @@ class Model:
             raise ValueError("unknown model %r" % name)
         self.num_params = hp.fn["model_num_params"](self.h)
         self.input_count = hp.fn["model_input_count"](self.h)
+        self.label_count = hp.fn["model_label_count"](self.h)
         self.slab_count = hp.fn["model_slab_count"](self.h)
 
     def _arrs(self, x, y):
         x = np.ascontiguousarray(x, dtype=np.float32)
         y = np.ascontiguousarray(y, dtype=np.int32)
-        assert x.size == self.input_count and y.size == self.batch
+        assert x.size == self.input_count and y.size == self.label_count
         return x, y
 
     def step(self, x, y, lr, update=True):

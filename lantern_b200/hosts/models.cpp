@@ -34,6 +34,7 @@ struct Model {
   std::string name;
   int batch = 0;
   int in_c = 0, in_h = 0, in_w = 0;
+  int64_t label_count = 0;     // int32 targets per step (0: one per sample)
   std::vector<ParamDecl> decls;
   float* slab_x = nullptr;   // all parameter tensors, contiguous (each padded to 64 floats)
   float* slab_d = nullptr;   // their gradients, same layout
@@ -72,11 +73,12 @@ struct Model {
       else if (d.init == INIT_ONE) BK(fill)(slab_x + d.offset, 1.0f, d.count);
     }
     if (first && seed >= 0) srand((unsigned)seed);
+    if (label_count == 0) label_count = batch;
     stage_x = (float*)BK(host_alloc)((size_t)batch * in_c * in_h * in_w * 4);
-    stage_y = (int32_t*)BK(host_alloc)((size_t)batch * 4);
+    stage_y = (int32_t*)BK(host_alloc)((size_t)label_count * 4);
     loss_host = (float*)BK(host_alloc)(4);
     dev_x = alloc_value((int64_t)batch * in_c * in_h * in_w);
-    dev_y = (int32_t*)BK(malloc_uninit)((size_t)batch * 4);
+    dev_y = (int32_t*)BK(malloc_uninit)((size_t)label_count * 4);
     mark = BK(mark)();
   }
   virtual TR forward(Tape& t, const TR& x, const int32_t* y) = 0;
@@ -91,9 +93,9 @@ struct Model {
       x.x = dev_x; y = dev_y;
     } else {                  // the generated programs upload every batch: resnet50FromOnnx.scala:173-174
       x.x = alloc_value(nin);
-      y = (int32_t*)BK(malloc_uninit)((size_t)batch * 4);
+      y = (int32_t*)BK(malloc_uninit)((size_t)label_count * 4);
       BK(h2d)(x.x, stage_x, (size_t)nin * 4);
-      BK(h2d)(y, stage_y, (size_t)batch * 4);
+      BK(h2d)(y, stage_y, (size_t)label_count * 4);
     }
     TR loss = forward(tape, x, y);
     BK(fill)(loss.d, 1.0f, 1);                       // gradR_loss: y.d.setAsOne(), TD.scala:1763-1780
@@ -101,12 +103,15 @@ struct Model {
     BK(d2d)(loss_copy, loss.x, 4);
     tape.backward();
     BK(d2h_async)(loss_host, loss_copy, 4);
-    if (update) {
-      if (BK(comm_world)() > 1) BK(allreduce_sgd_step)(slab_x, slab_d, lr, slab_count);
-      else BK(sgd_step)(slab_x, slab_d, lr, slab_count);
-    }
+    if (update) apply_update(lr);
     if (tracing()) dump_trace();
     BK(reset)(mark);
+  }
+  // SGD of the CNN apps (NNModule.scala:265-287: geam x -= lr*d, then d = 0), fused with the gradient all-reduce when the
+  // communicator has more than one rank.
+  virtual void apply_update(float lr) {
+    if (BK(comm_world)() > 1) BK(allreduce_sgd_step)(slab_x, slab_d, lr, slab_count);
+    else BK(sgd_step)(slab_x, slab_d, lr, slab_count);
   }
   std::string trace_text;
   // One line per operator output, in forward order: index, element count, sum|x|, sum|d| (read back before the reset).
@@ -127,7 +132,7 @@ struct Model {
   }
   void load(const float* xh, const int32_t* yh) {
     memcpy(stage_x, xh, (size_t)batch * in_c * in_h * in_w * 4);
-    memcpy(stage_y, yh, (size_t)batch * 4);
+    memcpy(stage_y, yh, (size_t)label_count * 4);
   }
   int step_async(const float* xh, const int32_t* yh, float lr, bool update) {
     if (!resident) load(xh, yh);
@@ -174,6 +179,44 @@ struct Mnist : Model {
     TR s3 = t.dropout(t.plus_bias(t.dot(flat, P(l1w)), P(l1b)), 0.5f);
     TR out = t.plus_bias(t.dot(s3, P(l2w)), P(l2b));
     return t.sum(t.nll(t.log_softmax(out), y));
+  }
+};
+
+// ------------------------------------------------------------------------------------------------ min-char-rnn
+// Vanilla RNN of NNModule.scala:189-200 (VanillaRNNCell = Linear1D2 + tanh, Linear1D) unrolled by DynamicRNNFix
+// (NNModule.scala:240-253) as the app VanillaRNN.scala:187-291 uses it: vocabulary 80 one-hot inputs x[T][B][80],
+// hidden 100, T = 20 steps, per step  h = tanh(x_t.W1 + h.W2 + b);  o = h.Wo (+)= bo;  loss += sum(nll(logSoftmax(o), y_t));
+// Adagrad lr-as-given, clip 5.  The targets arrive as y[t][b] (the generated code gathers them per step from a
+// [b][t] host array, NNModule.scala:246-248; the order of the buffer is this host program's choice).
+struct VanillaRnn : Model {
+  static constexpr int V = 80, Hd = 100, T = 20;
+  int w1, w2, bh, wo, bo;
+  float* slab_h = nullptr;          // Adagrad accumulators, same layout as the parameter slab
+  VanillaRnn(int b, int seed) {
+    name = "rnn"; batch = b; in_c = T; in_h = 1; in_w = V; label_count = (int64_t)T * b;
+    w1 = declare({V, Hd}, INIT_RAND, 1.0f / sqrtf((float)V));   w2 = declare({Hd, Hd}, INIT_RAND, 1.0f / sqrtf((float)Hd));
+    bh = declare({Hd}, INIT_ZERO);
+    wo = declare({Hd, V}, INIT_RAND, 1.0f / sqrtf((float)Hd));  bo = declare({V}, INIT_ZERO);
+    finalize(seed);
+    slab_h = alloc_zero(slab_count);   // allocated after the mark was taken: move the mark above it
+    mark = BK(mark)();
+  }
+  TR forward(Tape& t, const TR& x, const int32_t* y) override {
+    TR h = make({batch, Hd});                          // cell.init: zeros
+    BK(fill)(h.x, 0.0f, h.count());
+    TR loss = make({1});
+    BK(fill)(loss.x, 0.0f, 1);
+    for (int s = 0; s < T; ++s) {
+      TR xt; xt.rank = 2; xt.shape[0] = batch; xt.shape[1] = V; xt.x = x.x + (int64_t)s * batch * V; xt.is_input = true;
+      TR pre = t.binary(LTB_ADD, t.binary(LTB_ADD, t.dot(xt, P(w1)), t.dot(h, P(w2))), P(bh));
+      h = t.unary(LTB_TANH, pre);
+      TR o = t.plus_bias(t.dot(h, P(wo)), P(bo));
+      loss = t.binary(LTB_ADD, loss, t.sum(t.nll(t.log_softmax(o), y + (int64_t)s * batch)));
+    }
+    return loss;
+  }
+  void apply_update(float lr) override {               // NNModule.scala:289-295 -> Backend.adagrad_update (TD.scala:377)
+    BK(adagrad_update)(slab_x, slab_d, slab_h, lr, 5.0f, 1, slab_count);
   }
 };
 
@@ -272,6 +315,7 @@ void* HOST_FN(model_create)(const char* name, int batch, int seed) {
   if (n == "mnist") return new Mnist(batch, seed);
   if (n == "resnet50") return new ResNet50(batch, seed);
   if (n == "squeezenet") return new SqueezeNet(batch, seed);
+  if (n == "rnn") return new VanillaRnn(batch, seed);
   return nullptr;
 }
 void HOST_FN(model_destroy)(void* m) {
@@ -288,6 +332,7 @@ int64_t HOST_FN(model_slab_count)(void* m) { return ((Model*)m)->slab_count; }
 float* HOST_FN(model_slab_params)(void* m) { return ((Model*)m)->slab_x; }
 float* HOST_FN(model_slab_grads)(void* m) { return ((Model*)m)->slab_d; }
 int64_t HOST_FN(model_input_count)(void* m) { Model* M = (Model*)m; return (int64_t)M->batch * M->in_c * M->in_h * M->in_w; }
+int64_t HOST_FN(model_label_count)(void* m) { return ((Model*)m)->label_count; }
 int HOST_FN(model_use_graph)(void* m, int on) { ((Model*)m)->use_graph = on != 0; return 0; }
 // Keep one batch resident in device memory; later steps read it there and upload nothing (x_host/y_host are ignored).
 int HOST_FN(model_set_resident)(void* m, const float* x_host, const int32_t* y_host) {
@@ -296,7 +341,7 @@ int HOST_FN(model_set_resident)(void* m, const float* x_host, const int32_t* y_h
   if (!x_host) { M->resident = false; return 0; }
   M->load(x_host, y_host);
   BK(h2d)(M->dev_x, M->stage_x, (size_t)M->batch * M->in_c * M->in_h * M->in_w * 4);
-  BK(h2d)(M->dev_y, M->stage_y, (size_t)M->batch * 4);
+  BK(h2d)(M->dev_y, M->stage_y, (size_t)M->label_count * 4);
   BK(sync)();
   M->resident = true;
   return 0;

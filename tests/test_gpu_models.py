@@ -136,3 +136,41 @@ def test_training_trajectory_and_graph_replay(oracle_lib, cuda_lib):
     replay.close()
     cuda_lib.set_math(1)
     cuda_lib.reset(mg_mark)
+
+
+@pytest.mark.parametrize("batch,math,rtol", [(1, 0, FP32_RTOL), (256, 0, FP32_RTOL), (256, 1, TF32_RTOL)])
+def test_vanilla_rnn_gradients_and_adagrad_trajectory(oracle_lib, cuda_lib, batch, math, rtol):
+    """min-char-rnn (vocabulary 80, hidden 100, 20 unrolled steps, batch 1 and 256): every gradient of one step, then
+    Adagrad steps (clip 5), oracle vs CUDA.  tanh is smooth, so the gradient comparison is strict."""
+    mo_mark, mg_mark = oracle_lib.mark(), cuda_lib.mark()
+    cuda_lib.set_math(math); oracle_lib.set_math(math)
+    mo, mg = _pair(oracle_lib, cuda_lib, "rnn", batch)
+    T, V = 20, 80
+    rng = np.random.default_rng(3)
+
+    def tokens(seed):
+        ids = np.random.default_rng(seed).integers(0, V, (T + 1, batch))
+        x = np.zeros((T, batch, V), np.float32)
+        x[np.arange(T)[:, None], np.arange(batch)[None, :], ids[:T]] = 1.0           # one-hot inputs
+        return x.ravel(), ids[1:].astype(np.int32).ravel()                             # targets: the next token, y[t][b]
+    x, y = tokens(11)
+    lo = mo.step(x, y, 0.0, update=False); lg = mg.step(x, y, 0.0, update=False)
+    assert abs(lo - lg) <= rtol * max(1.0, abs(lo)), (lo, lg)
+    assert lo > 0.5 * T * batch * np.log(V) * 0.5                                      # about T*B*ln(80) for untrained weights
+    for i in range(mo.num_params):
+        assert_close(mo.grad(i), mg.grad(i), rtol, "rnn grad %d" % i)
+    # Adagrad divides by sqrt(h + 1e-8): for an element whose gradient is near zero the update is about lr * g / 1e-4, so
+    # rounding differences of 1e-6 in such a gradient move the parameter by 1e-3 * lr / 1e-4 -- the bound on the
+    # parameters after an update is therefore far looser than the bound on the gradients, by construction of the optimizer.
+    x, y = tokens(20)
+    mo.step(x, y, 0.1); mg.step(x, y, 0.1)
+    assert_close(mo.slab_params(), mg.slab_params(), 3e-2, "rnn parameters after one Adagrad step")
+    assert not mg.slab_grads().any()
+    losses_o, losses_g = [], []
+    for s in range(5):
+        x, y = tokens(21 + s)
+        losses_o.append(mo.step(x, y, 0.01)); losses_g.append(mg.step(x, y, 0.01))
+    assert np.allclose(losses_o, losses_g, rtol=2e-2), (losses_o, losses_g)
+    mo.close(); mg.close()
+    cuda_lib.set_math(1); oracle_lib.set_math(0)
+    oracle_lib.reset(mo_mark); cuda_lib.reset(mg_mark)
