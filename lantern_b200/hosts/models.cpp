@@ -15,6 +15,7 @@
 #include <cstring>
 #include <memory>
 #include <string>
+#include <vector>
 
 #include "tape.hpp"
 
@@ -220,6 +221,93 @@ struct VanillaRnn : Model {
   }
 };
 
+// ------------------------------------------------------------------------------------------------ TreeLSTM (sentiment)
+// PLDI19APP/SentimentTreeLSTM.scala:67-146: Leaf (3 gates from a 300-d embedding), Node (5 gates from the two children),
+// Out (5-way classifier at every node), recursion LOOPTM over the (lch, rch) arrays from node 0, losses added up the
+// tree, Adagrad lr-as-given with the default clip 1.0 over the 22 tensors, one tree per step.
+// One quirk of the app is kept on purpose: Leaf and Node return ArrayBuffer(hidden, cell) and the caller destructures it
+// as ArrayBuffer(cell, hidden) (lines 131 and 135), so the classifier reads the cell state and the children's two states
+// reach the parent with their roles exchanged.  This program does exactly the same.
+// A step's "labels" carry the tree: y[0] = node count n <= 99, then four arrays with a stride of 99 ints: scores (0..4),
+// words (row of the embedding table), left child, right child (-1 = none; node 0 is the root).  The embedding table
+// (1000 rows x 300, N(0, 0.1), fixed seed) stands in for the GloVe file the app reads; it is data, not a parameter.
+struct TreeLstm : Model {
+  static constexpr int E = 300, Hd = 150, O = 5, MAXN = 99, VOCAB = 1000;
+  int Wi, bi, Wo, bo, Wu, bu;
+  int U0i, U1i, bbi, U00f, U01f, U10f, U11f, bbf, U0o, U1o, bbo, U0u, U1u, bbu;
+  int Why, by;
+  float* slab_h = nullptr;
+  float* table = nullptr;
+  struct State { TR loss, first, second; };   // the app's ArrayBuffer(loss, "hidden", "cell") with its exchanged roles
+
+  TreeLstm(int, int seed) {
+    name = "treelstm"; batch = 1; in_c = in_h = in_w = 1; label_count = 1 + 4 * MAXN;
+    auto W = [&](int r, int c) { return declare({r, c}, INIT_RAND, 0.01f); };
+    auto Z = [&](int n) { return declare({n}, INIT_ZERO); };
+    Wi = W(Hd, E); bi = Z(Hd); Wo = W(Hd, E); bo = Z(Hd); Wu = W(Hd, E); bu = Z(Hd);
+    U0i = W(Hd, Hd); U1i = W(Hd, Hd); bbi = Z(Hd);
+    U00f = W(Hd, Hd); U01f = W(Hd, Hd); U10f = W(Hd, Hd); U11f = W(Hd, Hd); bbf = Z(Hd);
+    U0o = W(Hd, Hd); U1o = W(Hd, Hd); bbo = Z(Hd);
+    U0u = W(Hd, Hd); U1u = W(Hd, Hd); bbu = Z(Hd);
+    Why = W(O, Hd); by = Z(O);
+    finalize(seed);
+    slab_h = alloc_zero(slab_count);
+    table = alloc_value((int64_t)VOCAB * E);
+    {
+      std::vector<float> h((size_t)VOCAB * E);
+      uint64_t st = 0x9E3779B97F4A7C15ull;              // own generator: the weights' rand() stream stays untouched
+      auto u01 = [&]() { st = st * 6364136223846793005ull + 1442695040888963407ull; return (double)((st >> 11) + 1) / 9007199254740993.0; };
+      for (size_t i = 0; i + 1 < h.size() + 1; i += 2) {
+        const double r = std::sqrt(-2.0 * std::log(u01())), a = 6.283185307179586 * u01();
+        h[i] = (float)(0.1 * r * std::cos(a)); if (i + 1 < h.size()) h[i + 1] = (float)(0.1 * r * std::sin(a));
+      }
+      BK(h2d)(table, h.data(), h.size() * 4); BK(sync)();
+    }
+    mark = BK(mark)();
+  }
+  TR gate(Tape& t, int op, int W0, const TR& a, int W1, const TR& b, int bias) {      // (W0.a plusBias W1.b plusBias bias).op
+    return t.unary(op, t.plus_bias(t.plus_bias(t.dot(P(W0), a), t.dot(P(W1), b)), P(bias)));
+  }
+  TR out(Tape& t, const TR& in, const int32_t* score) {                              // Out.apply, lines 111-118
+    TR pred = t.plus_bias(t.dot(P(Why), in), P(by));
+    return t.nll(t.log_softmax(view(pred, {1, O})), score);
+  }
+  State visit(Tape& t, const int32_t* host, const int32_t* dev, int i) {
+    const int32_t *scores = dev + 1, *words = host + 1 + MAXN, *lch = host + 1 + 2 * MAXN, *rch = host + 1 + 3 * MAXN;
+    State s;
+    if (lch[i] < 0) {                                                                // leaf, lines 72-85 and 130-133
+      TR e; e.rank = 1; e.shape[0] = E; e.x = table + (int64_t)words[i] * E; e.is_input = true;
+      TR ig = t.unary(LTB_SIGMOID, t.plus_bias(t.dot(P(Wi), e), P(bi)));
+      TR og = t.unary(LTB_SIGMOID, t.plus_bias(t.dot(P(Wo), e), P(bo)));
+      TR uv = t.unary(LTB_TANH, t.plus_bias(t.dot(P(Wu), e), P(bu)));
+      TR cell = t.binary(LTB_MUL, ig, uv);
+      TR hidden = t.binary(LTB_MUL, og, t.unary(LTB_TANH, cell));
+      // val ArrayBuffer(cell', hidden') = leaf(...): cell' = hidden, hidden' = cell
+      s.loss = out(t, /*hidden'*/ cell, scores + i);
+      s.first = /*hidden'*/ cell; s.second = /*cell'*/ hidden;
+      return s;
+    }
+    State l = visit(t, host, dev, lch[i]), r = visit(t, host, dev, rch[i]);
+    const TR &hl = l.first, &cl = l.second, &hr = r.first, &cr = r.second;           // ArrayBuffer(loss, hiddenl, celll) = l
+    TR ig = gate(t, LTB_SIGMOID, U0i, hl, U1i, hr, bbi);
+    TR fl = gate(t, LTB_SIGMOID, U00f, hl, U01f, hr, bbf);
+    TR fr = gate(t, LTB_SIGMOID, U10f, hl, U11f, hr, bbf);
+    TR og = gate(t, LTB_SIGMOID, U0o, hl, U1o, hr, bbo);
+    TR uv = gate(t, LTB_TANH, U0u, hl, U1u, hr, bbu);
+    TR cell = t.plus_bias(t.plus_bias(t.binary(LTB_MUL, ig, uv), t.binary(LTB_MUL, fl, cl)), t.binary(LTB_MUL, fr, cr));
+    TR hidden = t.binary(LTB_MUL, og, t.unary(LTB_TANH, cell));
+    s.loss = t.plus_bias(t.plus_bias(out(t, /*hidden'*/ cell, scores + i), l.loss), r.loss);
+    s.first = cell; s.second = hidden;
+    return s;
+  }
+  TR forward(Tape& t, const TR&, const int32_t* y) override {
+    const int n = stage_y[0];
+    if (n < 1 || n > MAXN) { TR z = make({1}); BK(fill)(z.x, 0.0f, 1); return z; }
+    return visit(t, stage_y, y, 0).loss;
+  }
+  void apply_update(float lr) override { BK(adagrad_update)(slab_x, slab_d, slab_h, lr, 1.0f, 1, slab_count); }
+};
+
 // ------------------------------------------------------------------------------------------------ ResNet-50 (CIFAR)
 struct ResNet50 : Model {
   struct ConvBN { int w, gamma, beta, rmean, rvar; };
@@ -316,6 +404,7 @@ void* HOST_FN(model_create)(const char* name, int batch, int seed) {
   if (n == "resnet50") return new ResNet50(batch, seed);
   if (n == "squeezenet") return new SqueezeNet(batch, seed);
   if (n == "rnn") return new VanillaRnn(batch, seed);
+  if (n == "treelstm") return new TreeLstm(batch, seed);
   return nullptr;
 }
 void HOST_FN(model_destroy)(void* m) {
@@ -333,7 +422,8 @@ float* HOST_FN(model_slab_params)(void* m) { return ((Model*)m)->slab_x; }
 float* HOST_FN(model_slab_grads)(void* m) { return ((Model*)m)->slab_d; }
 int64_t HOST_FN(model_input_count)(void* m) { Model* M = (Model*)m; return (int64_t)M->batch * M->in_c * M->in_h * M->in_w; }
 int64_t HOST_FN(model_label_count)(void* m) { return ((Model*)m)->label_count; }
-int HOST_FN(model_use_graph)(void* m, int on) { ((Model*)m)->use_graph = on != 0; return 0; }
+// A recorded step can only be replayed when every step issues the same operations: not so for one tree per step.
+int HOST_FN(model_use_graph)(void* m, int on) { Model* M = (Model*)m; M->use_graph = on != 0 && M->name != "treelstm"; return 0; }
 // Keep one batch resident in device memory; later steps read it there and upload nothing (x_host/y_host are ignored).
 int HOST_FN(model_set_resident)(void* m, const float* x_host, const int32_t* y_host) {
   Model* M = (Model*)m;

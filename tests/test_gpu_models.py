@@ -174,3 +174,55 @@ def test_vanilla_rnn_gradients_and_adagrad_trajectory(oracle_lib, cuda_lib, batc
     mo.close(); mg.close()
     cuda_lib.set_math(1); oracle_lib.set_math(0)
     oracle_lib.reset(mo_mark); cuda_lib.reset(mg_mark)
+
+
+def _random_tree(rng, leaves, vocab=1000, maxn=99):
+    """Arrays of the reference's tree file (scores, words, left child, right child; -1 = none; node 0 is the root),
+    packed the way the TreeLSTM host program takes them: [n, scores[99], words[99], lch[99], rch[99]]."""
+    scores, words, lch, rch = [], [], [], []
+
+    def build(k):
+        i = len(scores)
+        scores.append(int(rng.integers(0, 5))); words.append(-1); lch.append(-1); rch.append(-1)
+        if k == 1:
+            words[i] = int(rng.integers(0, vocab))
+        else:
+            left = int(rng.integers(1, k))
+            lch[i] = build(left); rch[i] = build(k - left)
+        return i
+    build(leaves)
+    n = len(scores)
+    y = np.full(1 + 4 * maxn, -1, np.int32)
+    y[0] = n
+    for j, arr in enumerate((scores, words, lch, rch)):
+        y[1 + j * maxn: 1 + j * maxn + n] = arr
+    return y
+
+
+def test_treelstm_gradients_and_adagrad_step(oracle_lib, cuda_lib):
+    """TreeLSTM sentiment classifier (embedding 300, hidden 150, 5 classes, one tree per step): loss and all 22 gradient
+    tensors on random binary trees of 2..12 leaves, then Adagrad (lr 0.05) steps, oracle vs CUDA (FP32 paths: the
+    150-wide matrix-vector products are not tensor-core work)."""
+    mo_mark, mg_mark = oracle_lib.mark(), cuda_lib.mark()
+    cuda_lib.set_math(0); oracle_lib.set_math(0)
+    mo, mg = _pair(oracle_lib, cuda_lib, "treelstm", 1)
+    assert mo.num_params == 22
+    rng = np.random.default_rng(17)
+    x = np.zeros(1, np.float32)
+    for leaves in (2, 3, 7, 12):
+        y = _random_tree(rng, leaves)
+        lo = mo.step(x, y, 0.0, update=False); lg = mg.step(x, y, 0.0, update=False)
+        n_nodes = 2 * leaves - 1
+        assert abs(lo - n_nodes * np.log(5.0)) < 0.05 * n_nodes                     # untrained: ln 5 per node
+        assert abs(lo - lg) <= FP32_RTOL * max(1.0, abs(lo)), (leaves, lo, lg)
+        for i in range(mo.num_params):
+            assert_close(mo.grad(i), mg.grad(i), FP32_RTOL, "treelstm grad %d (%d leaves)" % (i, leaves))
+        mo.step(x, y, 0.0); mg.step(x, y, 0.0)                                      # lr 0: only clears the gradients
+    losses_o, losses_g = [], []
+    for s in range(6):
+        y = _random_tree(rng, 2 + s)
+        losses_o.append(mo.step(x, y, 0.05)); losses_g.append(mg.step(x, y, 0.05))
+    assert np.allclose(losses_o, losses_g, rtol=2e-2), (losses_o, losses_g)
+    mo.close(); mg.close()
+    cuda_lib.set_math(1)
+    oracle_lib.reset(mo_mark); cuda_lib.reset(mg_mark)
