@@ -1,0 +1,46 @@
+"""The recursive host programs (min-char-rnn, TreeLSTM) on the CPU oracle: sanity anchors that need no GPU.
+An untrained classifier's loss is ln(classes) per prediction, and repeating one example must drive its loss down."""
+import os
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+ORA_HOSTS = os.path.join(ROOT, "oracle", "liblantern_oracle_hosts.so")
+
+
+def _model(oracle_lib, name, batch):
+    from lantern_b200.hosts import HostPrograms
+    oracle_lib.set_math(0)
+    return HostPrograms(oracle_lib, ORA_HOSTS, "orah_").model(name, batch, seed=42)
+
+
+def test_rnn_untrained_loss_and_learning(oracle_lib):
+    mark = oracle_lib.mark()
+    T, V, B = 20, 80, 3
+    m = _model(oracle_lib, "rnn", B)
+    assert m.num_params == 5 and m.label_count == T * B and m.input_count == T * B * V
+    ids = np.random.default_rng(0).integers(0, V, (T + 1, B))
+    x = np.zeros((T, B, V), np.float32)
+    x[np.arange(T)[:, None], np.arange(B)[None, :], ids[:T]] = 1.0
+    y = ids[1:].astype(np.int32).ravel()
+    first = m.step(x.ravel(), y, 0.01)
+    assert abs(first - T * B * np.log(V)) < 0.02 * T * B * np.log(V)
+    for _ in range(30):
+        last = m.step(x.ravel(), y, 0.01)
+    assert last < 0.5 * first
+    m.close(); oracle_lib.reset(mark)
+
+
+def test_treelstm_untrained_loss_and_learning(oracle_lib):
+    from tests.test_gpu_models import _random_tree
+    mark = oracle_lib.mark()
+    m = _model(oracle_lib, "treelstm", 1)
+    assert m.num_params == 22 and m.label_count == 1 + 4 * 99
+    y = _random_tree(np.random.default_rng(4), 9)
+    x = np.zeros(1, np.float32)
+    first = m.step(x, y, 0.05)
+    assert abs(first - 17 * np.log(5.0)) < 0.2
+    for _ in range(8):
+        last = m.step(x, y, 0.05)
+    assert last < 0.1 * first
+    m.close(); oracle_lib.reset(mark)
