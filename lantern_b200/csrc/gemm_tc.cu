@@ -390,6 +390,26 @@ __global__ void to_rows_tiled_kernel(const float* __restrict__ src, float* __res
   float* d = dst + ((int64_t)n * pix + p0) * chan + c0;
   for (int i = threadIdx.x; i < 32 * pt; i += blockDim.x) { const int p = i >> 5, c = i & 31; d[(int64_t)p * chan + c] = tile[c][p]; }
 }
+// Channels-last copy of dy with a zero between neighbouring pixels: up[n][2a][2b][k] = dy[n][k][a][b], 0 elsewhere
+// (up is uH x uW pixels).  The data-gradient of a stride-2 convolution is the stride-1 data-gradient of this tensor, so the
+// tap-loop plan serves it and no fold-back pass is needed.  K a multiple of 32, oW <= 32.  grid (ceil(uH/2), K/32, N), block 256.
+__global__ void to_rows_up2_kernel(const float* __restrict__ dy, float* __restrict__ up, int K, int oH, int oW, int uH, int uW) {
+  __shared__ float tile[32][33];
+  const int a = blockIdx.x, k0 = blockIdx.y * 32, n = blockIdx.z;
+  if (a < oH)
+    for (int i = threadIdx.x; i < 32 * oW; i += blockDim.x) {
+      const int k = i / oW, b = i - k * oW;
+      tile[k][b] = dy[(((int64_t)n * K + k0 + k) * oH + a) * oW + b];
+    }
+  __syncthreads();
+  for (int hu = 2 * a; hu < 2 * a + 2 && hu < uH; ++hu)
+    for (int i = threadIdx.x; i < uW * 32; i += blockDim.x) {
+      const int wu = i >> 5, k = i & 31;
+      float v = 0.0f;
+      if (hu == 2 * a && a < oH && !(wu & 1) && (wu >> 1) < oW) v = tile[k][wu >> 1];
+      up[(((int64_t)n * uH + hu) * uW + wu) * K + k0 + k] = v;
+    }
+}
 // Filters w[k][c][tap] (OIHW) as one matrix per tap: out[tap][k][c] (by_c == 0, forward) or out[tap][c][k] (data-grad).
 __global__ void permute_taps_kernel(const float* __restrict__ w, float* __restrict__ out, int K, int C, int taps, int by_c, int64_t total) {
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
@@ -532,12 +552,25 @@ static int launch_unfold(const float* x, float* col, const ConvDims& d) {
   LTB_LAUNCH(unfold_rows_kernel, grid_for(ceil_div(planes, ppb) * 256, 256, 16), 256, 0, x, col, d, ppb, tpp);
   return LTB_OK;
 }
+// 1x1 convolution with stride 2 and no padding (ResNet's downsampling branch): every gradient element goes to exactly
+// one input pixel, dx[n][c][2a][2b] += col[n][c][a][b]; a thread per element of col.
+__global__ void fold_1x1_s2_kernel(const float* __restrict__ col, float* dx, int oH, int oW, int H, int W, int64_t total) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int b = (int)(i % oW); const int64_t t = i / oW; const int a = (int)(t % oH); const int64_t plane = t / oH;
+    dx[(plane * H + 2 * a) * W + 2 * b] += col[i];
+  }
+}
 static int launch_fold(const float* col, float* dx, const ConvDims& d) {
   const int hw = d.H * d.W;
   int tpp = 32; while (tpp < hw && tpp < 256) tpp <<= 1;
   const int ppb = 256 / tpp;
   const int64_t planes = (int64_t)d.N * d.C;
   const unsigned grid = (unsigned)grid_for(ceil_div(planes, ppb) * 256, 256, 16);
+  if (d.R == 1 && d.S == 1 && d.sh == 2 && d.sw == 2 && d.ph == 0 && d.pw == 0) {
+    const int64_t total = planes * d.oH * d.oW;
+    LTB_LAUNCH(fold_1x1_s2_kernel, grid_for(total, 256), 256, 0, col, dx, d.oH, d.oW, d.H, d.W, total);
+    return LTB_OK;
+  }
   if (d.sh == 1 && d.sw == 1) LTB_LAUNCH(fold_acc_kernel<1>, grid, 256, 0, col, dx, d, ppb, tpp);
   else if (d.sh == 2 && d.sw == 2) LTB_LAUNCH(fold_acc_kernel<2>, grid, 256, 0, col, dx, d, ppb, tpp);
   else LTB_LAUNCH(fold_acc_kernel<0>, grid, 256, 0, col, dx, d, ppb, tpp);
@@ -546,7 +579,7 @@ static int launch_fold(const float* col, float* dx, const ConvDims& d) {
 static bool is_pointwise(const ConvDims& d) { return d.R == 1 && d.S == 1 && d.sh == 1 && d.sw == 1 && d.ph == 0 && d.pw == 0; }
 // Staging blocks go back to the arena (a LIFO pop, host arithmetic only) unless the caller holds them: conv backward runs
 // its two halves on two streams and pops both halves' blocks together once both are issued.
-static void temp_free(float* p, size_t floats) { if (!g.hold_workspace) temp_free(p, floats); }
+static void temp_free(float* p, size_t floats) { if (!g.hold_workspace) ltb_free(p, floats * 4); }
 static float* temp_alloc(size_t floats) {
   size_t bytes = (floats * 4 + kGranule - 1) / kGranule * kGranule;
   if (g.used + bytes > g.heap_bytes) return nullptr;          // no room for the staging buffer: let the FP32 path run
@@ -629,6 +662,26 @@ static int conv_dgrad_taps(const float* dy, const float* w, float* dx, const Con
   temp_free(dyr, ny);
   return rc ? rc : (ok ? 1 : 0);
 }
+// Stride 2 (both directions): dx is the stride-1 data-gradient of dy with zeros inserted (to_rows_up2_kernel).
+static int conv_dgrad_taps_up2(const float* dy, const float* w, float* dx, const ConvDims& d) {
+  if (d.sh != 2 || d.sw != 2 || d.R * d.S == 1 || d.K % 32 || d.oW > 32 || d.N > 65535) return 0;   // 1x1: the unfolded form with its one-to-one fold is cheaper
+  TcConvGeom gm; TcPlan p;
+  gm.n_img = d.N; gm.C = d.C; gm.H = d.H; gm.W = d.W; gm.K = d.K; gm.R = d.R; gm.S = d.S; gm.ph = d.ph; gm.pw = d.pw;
+  gm.oH = d.H + 2 * d.ph - d.R + 1; gm.oW = d.W + 2 * d.pw - d.S + 1;              // the stride-1 output grid
+  if (gm.oH < 1 || gm.oW < 1 || 2 * (d.oH - 1) >= gm.oH || 2 * (d.oW - 1) >= gm.oW) return 0;
+  if (!tc_plan_conv_taps_dgrad(p, dx, dx, dx, gm, true, g.sm_count)) return 0;
+  const size_t nu = (size_t)d.N * gm.oH * gm.oW * d.K;
+  float* up = temp_alloc(nu);
+  if (!up) return 0;
+  LTB_LAUNCH(to_rows_up2_kernel, dim3((gm.oH + 1) / 2, d.K / 32, d.N), 256, 0, dy, up, d.K, d.oH, d.oW, gm.oH, gm.oW);
+  float* wd = nullptr; size_t nw = 0;
+  int rc = tap_matrices(w, d, 1, &wd, &nw);
+  bool ok = !rc && wd && tc_plan_conv_taps_dgrad(p, up, wd, dx, gm, true, g.sm_count);
+  if (ok) rc = launch_plan(p, "tc_gemm_kernel[conv_dgrad taps up2]");
+  if (wd) temp_free(wd, nw);
+  temp_free(up, nu);
+  return rc ? rc : (ok ? 1 : 0);
+}
 static int conv_wgrad_taps(const float* x, const float* dy, float* dw, const ConvDims& d) {
   TcConvGeom gm; TcPlan p;
   // The tap-loop weight-grad stores its columns (tap, c) into OIHW with a stride of R*S floats, so its split-K atomics do not
@@ -667,6 +720,7 @@ int conv_dgrad_tc(const float* dy, const float* w, float* dx, const ConvDims& d)
   const bool rows = tc_conv_needs_rows(pix), direct = is_pointwise(d);
   if (!tc_plan_conv_dgrad(p, dx, rows, w, dx, d.N, ck, d.K, pix, direct, g.sm_count)) return 0;
   { int t = conv_dgrad_taps(dy, w, dx, d); if (t != 0) return t; }
+  { int t = conv_dgrad_taps_up2(dy, w, dx, d); if (t != 0) return t; }
   const float* op; bool r2; float* temp; size_t tn;
   ConvDims flat = d; flat.C = d.K;                               // dy is [N][K][pix]: staged like a pointwise activation with K channels
   int rc = stage_activation(dy, false, flat, d.K, pix, &op, &r2, &temp, &tn);
