@@ -115,16 +115,27 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t* r) {
 // counter adds; the common case (level 0) uses increments kept in registers.
 struct BoxWalker {
   int c[5], inc0[5], i0, i1;
-  __device__ __forceinline__ void init(const TcOperandDev& o, int tile, int k0) {
+  // Start coordinates of both operands, computed by the lanes of one warp in parallel (lane d: coordinate d of A, lane
+  // 8 + d: coordinate d of B, lanes 5/6 and 13/14: the counter positions) and handed to lane 0.  Done by a single thread
+  // the ten pairs of integer division and remainder cost about 3000 cycles per CTA (measured), as long as a short main loop.
+  __device__ static __forceinline__ void init_pair(BoxWalker& wa, BoxWalker& wb, const TcOperandDev& a, const TcOperandDev& b,
+                                                   int m_tile, int n_tile, int k0, int lane) {
+    const bool second = (lane & 8) != 0;
+    const TcOperandDev& o = second ? b : a;
+    const int tile = second ? n_tile : m_tile, d = lane & 7;
+    int v = 0;
+    if (lane < 16 && d < 5) {
+      v = o.c_off[d];
+      if (o.t_mul[d] != 0) v += ((o.t_div[d] > 1 ? tile / o.t_div[d] : tile) % o.t_mod[d]) * o.t_mul[d];
+      if (o.k_mul[d] != 0 && k0 != 0) v += ((o.k_div[d] > 1 ? k0 / o.k_div[d] : k0) % o.k_mod[d]) * o.k_mul[d];
+    } else if (lane < 16 && d == 5) v = k0 ? k0 % o.walk.n0 : 0;
+    else if (lane < 16 && d == 6) v = k0 ? (k0 / o.walk.n0) % o.walk.n1 : 0;
 #pragma unroll
-    for (int d = 0; d < 5; ++d) {
-      c[d] = o.c_off[d];                          // divisions only for the one or two dimensions that use them
-      if (o.t_mul[d] != 0) c[d] += ((o.t_div[d] > 1 ? tile / o.t_div[d] : tile) % o.t_mod[d]) * o.t_mul[d];
-      if (o.k_mul[d] != 0 && k0 != 0) c[d] += ((o.k_div[d] > 1 ? k0 / o.k_div[d] : k0) % o.k_mod[d]) * o.k_mul[d];
-      inc0[d] = o.walk.inc[0][d];
-    }
-    i0 = k0 ? k0 % o.walk.n0 : 0;
-    i1 = k0 ? (k0 / o.walk.n0) % o.walk.n1 : 0;
+    for (int j = 0; j < 5; ++j) { wa.c[j] = __shfl_sync(0xffffffffu, v, j); wb.c[j] = __shfl_sync(0xffffffffu, v, 8 + j); }
+    wa.i0 = __shfl_sync(0xffffffffu, v, 5); wa.i1 = __shfl_sync(0xffffffffu, v, 6);
+    wb.i0 = __shfl_sync(0xffffffffu, v, 13); wb.i1 = __shfl_sync(0xffffffffu, v, 14);
+#pragma unroll
+    for (int j = 0; j < 5; ++j) { wa.inc0[j] = a.walk.inc[0][j]; wb.inc0[j] = b.walk.inc[0][j]; }
   }
   __device__ __forceinline__ void next(const TcOperandDev& o) {
     if (++i0 != o.walk.n0) {
@@ -208,12 +219,13 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   if (threadIdx.x == 0) LTB_STAMP(0);        // set-up done
 
   if (warp == 0) {
+    BoxWalker wa, wb;
+    BoxWalker::init_pair(wa, wb, P.a, P.b, m_tile, n_tile, k_begin, lane);
     if (lane == 0 && n_iter > 0) {
       int s = 0; uint32_t ph = 0;
-      BoxWalker wa, wb;
-      wa.init(P.a, m_tile, k_begin); wb.init(P.b, n_tile, k_begin);
       for (int it = 0; it < n_iter; ++it) {
-        if (!mbar_wait(&empty_bar[s], ph ^ 1u, &abort_flag, P.status, 1)) break;
+        // the first `stages` fills find the ring empty: no wait, no barrier round trip
+        if (it >= stages && !mbar_wait(&empty_bar[s], ph ^ 1u, &abort_flag, P.status, 1)) break;
         uint8_t* sa = stage_base + (size_t)s * stage_bytes; uint8_t* sb = sa + P.a.stage_bytes;
         mbar_expect_tx(&full_bar[s], stage_bytes);
         if (it < 24) LTB_STAMP(40 + it);      // issue time of each of the first loads
