@@ -246,6 +246,9 @@ int LTB_FN(comm_init)(int rank, int world, const void* id128);
 int LTB_FN(comm_destroy)(void);
 int LTB_FN(comm_world)(void);
 int LTB_FN(allreduce_sum)(float* x, int64_t n);
+/* Starts, while backward is still running, the sum of a gradient range that is already final; the allreduce_sgd_step
+ * that follows over a span containing it only waits for that sum. No-op with one rank. */
+int LTB_FN(allreduce_begin)(float* d, int64_t n);
 int LTB_FN(allreduce_sgd_step)(float* x, float* d, float lr, int64_t n);
 
 #ifdef __cplusplus

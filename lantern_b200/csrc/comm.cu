@@ -30,6 +30,10 @@ struct Nccl {
   cudaStream_t comm_stream = nullptr;
   cudaEvent_t ready = nullptr;
   cudaEvent_t done[kMaxBuckets] = {};
+  // gradient ranges whose all-reduce was started early (ltb_allreduce_begin), in the order they were started
+  static const int kMaxEarly = 16;
+  struct Early { float* ptr; int64_t n; cudaEvent_t done; } early[kMaxEarly] = {};
+  int n_early = 0;
 } nccl;
 
 static int load_nccl() {
@@ -84,6 +88,8 @@ int ltb_comm_init(int rank, int world, const void* id128) {
   LTB_CUDA(cudaStreamCreateWithFlags(&nccl.comm_stream, cudaStreamNonBlocking));
   LTB_CUDA(cudaEventCreateWithFlags(&nccl.ready, cudaEventDisableTiming));
   for (auto& e : nccl.done) LTB_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+  for (auto& e : nccl.early) LTB_CUDA(cudaEventCreateWithFlags(&e.done, cudaEventDisableTiming));
+  nccl.n_early = 0;
   return LTB_OK;
 }
 int ltb_comm_destroy(void) {
@@ -91,7 +97,9 @@ int ltb_comm_destroy(void) {
     nccl.CommDestroy(nccl.comm); nccl.comm = nullptr;
     cudaStreamDestroy(nccl.comm_stream); cudaEventDestroy(nccl.ready);
     for (auto& e : nccl.done) cudaEventDestroy(e);
+    for (auto& e : nccl.early) cudaEventDestroy(e.done);
   }
+  nccl.n_early = 0;
   nccl.world = 1; nccl.rank = 0;
   return LTB_OK;
 }
@@ -103,29 +111,71 @@ int ltb_allreduce_sum(float* x, int64_t n) {
   LTB_NCCL(nccl.AllReduce(x, x, (size_t)n, ncclFloat, ncclSum, nccl.comm, g.stream));
   return LTB_OK;
 }
-// Gradient all-reduce fused with the update: the slab is cut into buckets; bucket i is reduced on the communication
-// stream while the update kernel of bucket i-1 runs on the compute stream, so only the first reduction and the last
-// update are exposed.  Each rank's loss is the mean over its own shard, hence the 1/world factor.
+// Starts the sum of a gradient range whose values are final while the rest of the backward pass is still running: the
+// range is reduced in place on the communication stream, after everything issued so far on the compute stream.  The
+// following ltb_allreduce_sgd_step over a span that contains the range does not reduce it again.  With one rank: no-op.
+int ltb_allreduce_begin(float* d, int64_t n) {
+  LTB_INITED(); LTB_REQUIRE(d && n >= 0, "ltb_allreduce_begin: bad argument");
+  if (nccl.world == 1 || n == 0) return LTB_OK;
+  if (nccl.n_early == Nccl::kMaxEarly) return LTB_OK;              // no slot left: the range is simply reduced at the step
+  Nccl::Early& e = nccl.early[nccl.n_early];
+  LTB_CUDA(cudaEventRecord(nccl.ready, g.stream));
+  LTB_CUDA(cudaStreamWaitEvent(nccl.comm_stream, nccl.ready, 0));
+  LTB_NCCL(nccl.AllReduce(d, d, (size_t)n, ncclFloat, ncclSum, nccl.comm, nccl.comm_stream));
+  LTB_CUDA(cudaEventRecord(e.done, nccl.comm_stream));
+  e.ptr = d; e.n = n; ++nccl.n_early;
+  return LTB_OK;
+}
+// Gradient all-reduce fused with the update.  Ranges started early are only waited for; what is left of the span is cut
+// into buckets, bucket i being reduced on the communication stream while the update kernel of bucket i-1 runs on the
+// compute stream, so only the first reduction and the last update are exposed.  Each rank's loss is the mean over its own
+// shard, hence the 1/world factor.
+static int update_range(float* x, float* d, int64_t off, int64_t cnt, float s) {
+  float* xb = x + off; float* db = d + off;
+  const int64_t n4 = (aligned16(xb) && aligned16(db)) ? cnt / 4 : 0;
+  LTB_LAUNCH(sgd_scaled_kernel, grid_for(cnt / 4 + 1, 256), 256, 0, xb, db, s, n4, cnt);
+  return LTB_OK;
+}
 int ltb_allreduce_sgd_step(float* x, float* d, float lr, int64_t n) {
   LTB_INITED(); LTB_REQUIRE(x && d && n >= 0, "ltb_allreduce_sgd_step: bad argument");
   if (nccl.world == 1) return ltb_sgd_step(x, d, lr, n);
   if (n == 0) return LTB_OK;
-  int64_t off[kMaxBuckets], cnt[kMaxBuckets];
-  const int used = bucket_spans(n, off, cnt);
+  const float s = -1.0f * lr / (float)nccl.world;
+  // early ranges inside [d, d + n), sorted by address; the gaps between them are what is still to be reduced
+  int order[Nccl::kMaxEarly], ne = 0;
+  for (int i = 0; i < nccl.n_early; ++i) {
+    const Nccl::Early& e = nccl.early[i];
+    if (e.ptr >= d && e.ptr + e.n <= d + n) order[ne++] = i;
+    else return fail(LTB_E_ARG, "ltb_allreduce_sgd_step: a range given to ltb_allreduce_begin lies outside this span");
+  }
+  for (int i = 1; i < ne; ++i) for (int j = i; j > 0 && nccl.early[order[j]].ptr < nccl.early[order[j - 1]].ptr; --j) { int t = order[j]; order[j] = order[j - 1]; order[j - 1] = t; }
   LTB_CUDA(cudaEventRecord(nccl.ready, g.stream));
   LTB_CUDA(cudaStreamWaitEvent(nccl.comm_stream, nccl.ready, 0));
-  for (int b = 0; b < used; ++b) {
-    LTB_NCCL(nccl.AllReduce(d + off[b], d + off[b], (size_t)cnt[b], ncclFloat, ncclSum, nccl.comm, nccl.comm_stream));
-    LTB_CUDA(cudaEventRecord(nccl.done[b], nccl.comm_stream));
+  int64_t cursor = 0; int rc = LTB_OK;
+  for (int k = 0; k <= ne && rc == LTB_OK; ++k) {
+    const int64_t gap_end = k < ne ? (int64_t)(nccl.early[order[k]].ptr - d) : n;
+    if (gap_end < cursor) return fail(LTB_E_ARG, "ltb_allreduce_sgd_step: overlapping early ranges");
+    if (gap_end > cursor) {                                        // a gap: reduce it now, bucket by bucket
+      int64_t off[kMaxBuckets], cnt[kMaxBuckets];
+      const int used = bucket_spans(gap_end - cursor, off, cnt);
+      for (int b = 0; b < used; ++b) {
+        LTB_NCCL(nccl.AllReduce(d + cursor + off[b], d + cursor + off[b], (size_t)cnt[b], ncclFloat, ncclSum, nccl.comm, nccl.comm_stream));
+        LTB_CUDA(cudaEventRecord(nccl.done[b], nccl.comm_stream));
+      }
+      for (int b = 0; b < used && rc == LTB_OK; ++b) {
+        LTB_CUDA(cudaStreamWaitEvent(g.stream, nccl.done[b], 0));
+        rc = update_range(x, d, cursor + off[b], cnt[b], s);
+      }
+    }
+    if (k < ne && rc == LTB_OK) {                                  // an early range: its sum is on its way or done
+      const Nccl::Early& e = nccl.early[order[k]];
+      LTB_CUDA(cudaStreamWaitEvent(g.stream, e.done, 0));
+      rc = update_range(x, d, (int64_t)(e.ptr - d), e.n, s);
+      cursor = (int64_t)(e.ptr - d) + e.n;
+    }
   }
-  float s = -1.0f * lr / (float)nccl.world;
-  for (int b = 0; b < used; ++b) {
-    LTB_CUDA(cudaStreamWaitEvent(g.stream, nccl.done[b], 0));
-    float* xb = x + off[b]; float* db = d + off[b];
-    const int64_t n4 = (aligned16(xb) && aligned16(db)) ? cnt[b] / 4 : 0;
-    LTB_LAUNCH(sgd_scaled_kernel, grid_for(cnt[b] / 4 + 1, 256), 256, 0, xb, db, s, n4, cnt[b]);
-  }
-  return LTB_OK;
+  nccl.n_early = 0;
+  return rc;
 }
 
 }  // extern "C"

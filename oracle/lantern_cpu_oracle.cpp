@@ -862,18 +862,36 @@ int ora_allreduce_sum(float* x, int64_t n) {
   if (g_world == 1 || n == 0) return LTB_OK;
   return g_transport(x, n) == 0 ? LTB_OK : fail(LTB_E_COMM, "ora_allreduce_sum: transport failed");
 }
-int ora_allreduce_sgd_step(float* x, float* d, float lr, int64_t n) {
-  if (g_world == 1) return ora_sgd_step(x, d, lr, n);
-  int64_t off[ltb::kMaxBuckets], cnt[ltb::kMaxBuckets];
-  const int used = ltb::bucket_spans(n, off, cnt);
-  const float s = -1.0f * lr / (float)g_world;
-  for (int b = 0; b < used; ++b) {
-    if (g_transport(d + off[b], cnt[b]) != 0) return fail(LTB_E_COMM, "ora_allreduce_sgd_step: transport failed");
-    for (int64_t i = off[b]; i < off[b] + cnt[b]; ++i) { x[i] += d[i] * s; d[i] = 0.0f; }
-  }
+// Early ranges: summed at once (the transport is synchronous) and remembered, so that the step does not sum them twice.
+static struct { float* ptr; int64_t n; } g_early[16];
+static int g_n_early = 0;
+int ora_allreduce_begin(float* d, int64_t n) {
+  if (g_world == 1 || n == 0 || g_n_early == 16) return LTB_OK;
+  if (g_transport(d, n) != 0) return fail(LTB_E_COMM, "ora_allreduce_begin: transport failed");
+  g_early[g_n_early].ptr = d; g_early[g_n_early].n = n; ++g_n_early;
   return LTB_OK;
 }
-
+int ora_allreduce_sgd_step(float* x, float* d, float lr, int64_t n) {
+  if (g_world == 1) return ora_sgd_step(x, d, lr, n);
+  const float s = -1.0f * lr / (float)g_world;
+  std::vector<char> done((size_t)n, 0);
+  for (int e = 0; e < g_n_early; ++e) {
+    if (g_early[e].ptr < d || g_early[e].ptr + g_early[e].n > d + n) return fail(LTB_E_ARG, "ora_allreduce_sgd_step: early range outside the span");
+    for (int64_t i = g_early[e].ptr - d; i < (g_early[e].ptr - d) + g_early[e].n; ++i) done[(size_t)i] = 1;
+  }
+  g_n_early = 0;
+  int64_t i = 0;
+  while (i < n) {                                   // maximal runs that still need the sum, cut into the library's bucket spans
+    if (done[(size_t)i]) { ++i; continue; }
+    int64_t j = i; while (j < n && !done[(size_t)j]) ++j;
+    int64_t off[ltb::kMaxBuckets], cnt[ltb::kMaxBuckets];
+    const int used = ltb::bucket_spans(j - i, off, cnt);
+    for (int b = 0; b < used; ++b) if (g_transport(d + i + off[b], cnt[b]) != 0) return fail(LTB_E_COMM, "ora_allreduce_sgd_step: transport failed");
+    i = j;
+  }
+  for (int64_t k = 0; k < n; ++k) { x[k] += d[k] * s; d[k] = 0.0f; }
+  return LTB_OK;
+}
 }  // extern "C"
 
 // ------------------------------------------------------------------ staging / replay: plain host equivalents.
