@@ -82,9 +82,91 @@ struct MatStore {
   }
 };
 
+// ---- skinny products: one extent of 16 or less (a 10-way classifier and its gradients) -----------------------------------
+// The 64 x 64 tiles above leave such products to one or two CTAs walking a long K; these three kernels give every output
+// (or every output column) its own thread or warp instead.
+// N <= 16, A and B both contiguous along k: a block of four warps per row m, each warp a quarter of K, lanes stride over k.
+template <bool ACC>
+__global__ void skinny_n_kernel(const float* __restrict__ a, int64_t sam, const float* __restrict__ b, int64_t sbn, float* c, int64_t scm, int64_t scn,
+                                int N, int K, float alpha) {
+  __shared__ float part[4][16];
+  const int m = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int k0 = (int)((int64_t)K * warp / 4), k1 = (int)((int64_t)K * (warp + 1) / 4);
+  float acc[16];
+#pragma unroll
+  for (int n = 0; n < 16; ++n) acc[n] = 0.0f;
+  const float* ar = a + (int64_t)m * sam;
+  for (int k = k0 + lane; k < k1; k += 32) {
+    const float av = ar[k];
+#pragma unroll
+    for (int n = 0; n < 16; ++n) if (n < N) acc[n] += av * b[(int64_t)n * sbn + k];
+  }
+#pragma unroll
+  for (int n = 0; n < 16; ++n) {
+    float v = acc[n];
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    if (lane == 0) part[warp][n] = v;
+  }
+  __syncthreads();
+  if (threadIdx.x < N) {
+    const int n = threadIdx.x;
+    const float v = alpha * ((part[0][n] + part[1][n]) + (part[2][n] + part[3][n]));
+    float* q = c + (int64_t)m * scm + (int64_t)n * scn;
+    *q = ACC ? *q + v : v;
+  }
+}
+// K <= 16: a thread per output element.
+template <bool ACC>
+__global__ void skinny_k_kernel(const float* __restrict__ a, int64_t sam, int64_t sak, const float* __restrict__ b, int64_t sbk, int64_t sbn,
+                                float* c, int64_t scm, int64_t scn, int M, int N, int K, float alpha) {
+  const int64_t total = (int64_t)M * N;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int n = (int)(i % N); const int64_t m = i / N;
+    float v = 0.0f;
+    for (int k = 0; k < K; ++k) v += a[m * sam + k * sak] * b[k * sbk + n * sbn];
+    float* q = c + m * scm + n * scn;
+    *q = ACC ? *q + alpha * v : alpha * v;
+  }
+}
+// M <= 16: a thread per output column n, all rows in registers; B is read once, coalesced when contiguous along n.
+template <bool ACC>
+__global__ void skinny_m_kernel(const float* __restrict__ a, int64_t sam, int64_t sak, const float* __restrict__ b, int64_t sbk, int64_t sbn,
+                                float* c, int64_t scm, int64_t scn, int M, int N, int K, float alpha) {
+  const int n = blockIdx.x * blockDim.x + threadIdx.x;
+  if (n >= N) return;
+  float acc[16];
+#pragma unroll
+  for (int m = 0; m < 16; ++m) acc[m] = 0.0f;
+  for (int k = 0; k < K; ++k) {
+    const float bv = b[(int64_t)k * sbk + (int64_t)n * sbn];
+#pragma unroll
+    for (int m = 0; m < 16; ++m) if (m < M) acc[m] += a[(int64_t)m * sam + (int64_t)k * sak] * bv;
+  }
+#pragma unroll
+  for (int m = 0; m < 16; ++m) if (m < M) { float* q = c + (int64_t)m * scm + (int64_t)n * scn; *q = ACC ? *q + alpha * acc[m] : alpha * acc[m]; }
+}
+static int skinny_gemm(const float* a, int64_t sam, int64_t sak, const float* b, int64_t sbk, int64_t sbn, float* c, int64_t scm, int64_t scn,
+                       int M, int N, int K, float alpha, bool accumulate, bool* taken) {
+  *taken = true;
+  if (N <= 16 && sak == 1 && sbk == 1 && K >= 128 && M <= 65535) {
+    if (accumulate) LTB_LAUNCH(skinny_n_kernel<true>, M, 128, 0, a, sam, b, sbn, c, scm, scn, N, K, alpha);
+    else LTB_LAUNCH(skinny_n_kernel<false>, M, 128, 0, a, sam, b, sbn, c, scm, scn, N, K, alpha);
+  } else if (K <= 16) {
+    const unsigned grid = (unsigned)grid_for((int64_t)M * N, 256);
+    if (accumulate) LTB_LAUNCH(skinny_k_kernel<true>, grid, 256, 0, a, sam, sak, b, sbk, sbn, c, scm, scn, M, N, K, alpha);
+    else LTB_LAUNCH(skinny_k_kernel<false>, grid, 256, 0, a, sam, sak, b, sbk, sbn, c, scm, scn, M, N, K, alpha);
+  } else if (M <= 16 && N >= 256 && K <= 4096) {
+    const unsigned grid = (unsigned)ceil_div(N, 128);
+    if (accumulate) LTB_LAUNCH(skinny_m_kernel<true>, grid, 128, 0, a, sam, sak, b, sbk, sbn, c, scm, scn, M, N, K, alpha);
+    else LTB_LAUNCH(skinny_m_kernel<false>, grid, 128, 0, a, sam, sak, b, sbk, sbn, c, scm, scn, M, N, K, alpha);
+  } else *taken = false;
+  return LTB_OK;
+}
+
 // C[M,N] (op)= alpha * A B with arbitrary strides; accumulate selects += (gradients) over = (forward).
 static int strided_gemm(const float* a, int64_t sam, int64_t sak, const float* b, int64_t sbk, int64_t sbn, float* c, int64_t scm,
                         int64_t scn, int M, int N, int K, float alpha, bool accumulate) {
+  { bool taken = false; int rc = skinny_gemm(a, sam, sak, b, sbk, sbn, c, scm, scn, M, N, K, alpha, accumulate, &taken); if (rc || taken) return rc; }
   dim3 grid((M + BM - 1) / BM, (N + BN - 1) / BN, 1);
   int tiles = grid.x * grid.y;
   int splits = 1;

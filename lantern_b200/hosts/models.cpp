@@ -200,10 +200,11 @@ struct Mnist : Model {
 // Adagrad lr-as-given, clip 5.  The targets arrive as y[t][b] (the generated code gathers them per step from a
 // [b][t] host array, NNModule.scala:246-248; the order of the buffer is this host program's choice).
 struct VanillaRnn : Model {
-  static constexpr int V = 80, Hd = 100, T = 20;
+  static constexpr int T = 20;
+  const int V, Hd;                  // 80 / 100 for the benchmark configuration; 26 / 50 in the reference's shipped generated program
   int w1, w2, bh, wo, bo;
   float* slab_h = nullptr;          // Adagrad accumulators, same layout as the parameter slab
-  VanillaRnn(int b, int seed) {
+  VanillaRnn(int b, int seed, int vocab, int hidden) : V(vocab), Hd(hidden) {
     name = "rnn"; batch = b; in_c = T; in_h = 1; in_w = V; label_count = (int64_t)T * b;
     w1 = declare({V, Hd}, INIT_RAND, 1.0f / sqrtf((float)V));   w2 = declare({Hd, Hd}, INIT_RAND, 1.0f / sqrtf((float)Hd));
     bh = declare({Hd}, INIT_ZERO);
@@ -420,7 +421,8 @@ void* HOST_FN(model_create)(const char* name, int batch, int seed) {
   if (n == "mnist") return new Mnist(batch, seed);
   if (n == "resnet50") return new ResNet50(batch, seed);
   if (n == "squeezenet") return new SqueezeNet(batch, seed);
-  if (n == "rnn") return new VanillaRnn(batch, seed);
+  if (n == "rnn") return new VanillaRnn(batch, seed, 80, 100);
+  if (n == "rnn_26_50") return new VanillaRnn(batch, seed, 26, 50);     // sizes of src/out/NIPS18evaluation/evaluationRNN/Lantern.cpp
   if (n == "treelstm") return new TreeLstm(batch, seed);
   return nullptr;
 }
