@@ -19,6 +19,7 @@ _SIGS = {
     "model_slab_grads": (ctypes.c_void_p, [ctypes.c_void_p]),
     "model_input_count": (ctypes.c_int64, [ctypes.c_void_p]),
     "model_label_count": (ctypes.c_int64, [ctypes.c_void_p]),
+    "model_set_table": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int]),
     "model_use_graph": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int]),
     "model_set_resident": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]),
     "model_step": (ctypes.c_float, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_float, ctypes.c_int]),
@@ -95,6 +96,13 @@ class Model:
             p = line.split()
             rows.append((int(p[0]), int(p[1]), p[2], float(p[3]), float(p[4])) + tuple(float(v) for v in p[5:]))
         return rows
+
+    def set_table(self, table):
+        """TreeLSTM: replace the embedding table by `table` (rows x 300 float32)."""
+        t = np.ascontiguousarray(table, dtype=np.float32)
+        rc = self.hp.fn["model_set_table"](self.h, t.ctypes.data, t.shape[0])
+        if rc:
+            raise ValueError("model_set_table failed: %d" % rc)
 
     def use_graph(self, on=True):
         self.hp.fn["model_use_graph"](self.h, int(on))

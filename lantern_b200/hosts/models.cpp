@@ -250,8 +250,12 @@ struct TreeLstm : Model {
   float* slab_h = nullptr;
   float* table = nullptr;
   struct State { TR loss, first, second; };   // the app's ArrayBuffer(loss, "hidden", "cell") with its exchanged roles
+  // pldi19 == false: the earlier NIPS18App/SentimentTreeLSTM.scala:118-170, whose generated program ships under
+  // src/out/NIPS18evaluation/evaluationTreeLSTM/Lantern/Lantern.cpp: the same cell without the exchanged roles, and a
+  // hand-written Adagrad loop without gradient clipping.
+  const bool pldi19;
 
-  TreeLstm(int, int seed) {
+  TreeLstm(int, int seed, bool pldi19_variant) : pldi19(pldi19_variant) {
     name = "treelstm"; batch = 1; in_c = in_h = in_w = 1; label_count = 1 + 4 * MAXN;
     auto W = [&](int r, int c) { return declare({r, c}, INIT_RAND, 0.01f); };
     auto Z = [&](int n) { return declare({n}, INIT_ZERO); };
@@ -293,6 +297,7 @@ struct TreeLstm : Model {
       TR uv = t.unary(LTB_TANH, t.plus_bias(t.dot(P(Wu), e), P(bu)));
       TR cell = t.binary(LTB_MUL, ig, uv);
       TR hidden = t.binary(LTB_MUL, og, t.unary(LTB_TANH, cell));
+      if (!pldi19) { s.loss = out(t, hidden, scores + i); s.first = hidden; s.second = cell; return s; }
       // val ArrayBuffer(cell', hidden') = leaf(...): cell' = hidden, hidden' = cell
       s.loss = out(t, /*hidden'*/ cell, scores + i);
       s.first = /*hidden'*/ cell; s.second = /*cell'*/ hidden;
@@ -307,6 +312,11 @@ struct TreeLstm : Model {
     TR uv = gate(t, LTB_TANH, U0u, hl, U1u, hr, bbu);
     TR cell = t.plus_bias(t.plus_bias(t.binary(LTB_MUL, ig, uv), t.binary(LTB_MUL, fl, cl)), t.binary(LTB_MUL, fr, cr));
     TR hidden = t.binary(LTB_MUL, og, t.unary(LTB_TANH, cell));
+    if (!pldi19) {        // loss = lossl + lossr + nll, NIPS18App/SentimentTreeLSTM.scala:158
+      s.loss = t.binary(LTB_ADD, t.binary(LTB_ADD, l.loss, r.loss), out(t, hidden, scores + i));
+      s.first = hidden; s.second = cell;
+      return s;
+    }
     s.loss = t.plus_bias(t.plus_bias(out(t, /*hidden'*/ cell, scores + i), l.loss), r.loss);
     s.first = cell; s.second = hidden;
     return s;
@@ -316,7 +326,13 @@ struct TreeLstm : Model {
     if (n < 1 || n > MAXN) { TR z = make({1}); BK(fill)(z.x, 0.0f, 1); return z; }
     return visit(t, stage_y, y, 0).loss;
   }
-  void apply_update(float lr) override { BK(adagrad_update)(slab_x, slab_d, slab_h, lr, 1.0f, 1, slab_count); }
+  void apply_update(float lr) override { BK(adagrad_update)(slab_x, slab_d, slab_h, lr, pldi19 ? 1.0f : 3.0e38f, 1, slab_count); }
+  // Replaces the embedding table (rows x 300 floats, rows <= VOCAB) by the caller's.
+  int set_table(const float* host, int rows) {
+    if (rows < 1 || rows > VOCAB) return LTB_E_ARG;
+    int rc = BK(h2d)(table, host, (size_t)rows * E * 4);
+    return rc ? rc : BK(sync)();
+  }
 };
 
 // ------------------------------------------------------------------------------------------------ ResNet-50 (CIFAR)
@@ -423,7 +439,8 @@ void* HOST_FN(model_create)(const char* name, int batch, int seed) {
   if (n == "squeezenet") return new SqueezeNet(batch, seed);
   if (n == "rnn") return new VanillaRnn(batch, seed, 80, 100);
   if (n == "rnn_26_50") return new VanillaRnn(batch, seed, 26, 50);     // sizes of src/out/NIPS18evaluation/evaluationRNN/Lantern.cpp
-  if (n == "treelstm") return new TreeLstm(batch, seed);
+  if (n == "treelstm") return new TreeLstm(batch, seed, true);
+  if (n == "treelstm_nips18") return new TreeLstm(batch, seed, false);
   return nullptr;
 }
 void HOST_FN(model_destroy)(void* m) {
@@ -440,6 +457,11 @@ int64_t HOST_FN(model_slab_count)(void* m) { return ((Model*)m)->slab_count; }
 float* HOST_FN(model_slab_params)(void* m) { return ((Model*)m)->slab_x; }
 float* HOST_FN(model_slab_grads)(void* m) { return ((Model*)m)->slab_d; }
 int64_t HOST_FN(model_input_count)(void* m) { Model* M = (Model*)m; return (int64_t)M->batch * M->in_c * M->in_h * M->in_w; }
+// TreeLSTM only: load the embedding table (rows x 300) the leaves read.
+int HOST_FN(model_set_table)(void* m, const float* host, int rows) {
+  TreeLstm* T = dynamic_cast<TreeLstm*>((Model*)m);
+  return T ? T->set_table(host, rows) : LTB_E_ARG;
+}
 int64_t HOST_FN(model_label_count)(void* m) { return ((Model*)m)->label_count; }
 // A recorded step can only be replayed when every step issues the same operations: not so for one tree per step.
 int HOST_FN(model_use_graph)(void* m, int on) { Model* M = (Model*)m; M->use_graph = on != 0 && M->name != "treelstm"; return 0; }

@@ -199,13 +199,14 @@ def _random_tree(rng, leaves, vocab=1000, maxn=99):
     return y
 
 
-def test_treelstm_gradients_and_adagrad_step(oracle_lib, cuda_lib):
+@pytest.mark.parametrize("variant", ["treelstm", "treelstm_nips18"])
+def test_treelstm_gradients_and_adagrad_step(oracle_lib, cuda_lib, variant):
     """TreeLSTM sentiment classifier (embedding 300, hidden 150, 5 classes, one tree per step): loss and all 22 gradient
     tensors on random binary trees of 2..12 leaves, then Adagrad (lr 0.05) steps, oracle vs CUDA (FP32 paths: the
     150-wide matrix-vector products are not tensor-core work)."""
     mo_mark, mg_mark = oracle_lib.mark(), cuda_lib.mark()
     cuda_lib.set_math(0); oracle_lib.set_math(0)
-    mo, mg = _pair(oracle_lib, cuda_lib, "treelstm", 1)
+    mo, mg = _pair(oracle_lib, cuda_lib, variant, 1)      # PLDI19 app (exchanged roles, clip 1) / NIPS18 app (plain cell, no clip)
     assert mo.num_params == 22
     rng = np.random.default_rng(17)
     x = np.zeros(1, np.float32)

@@ -97,3 +97,53 @@ def test_rnn_loss_trajectory_matches_generated_program(oracle_lib, tmp_path):
     assert np.allclose(got[:2], want[:2], rtol=2e-5), list(zip(got[:2], want[:2]))
     assert np.allclose(got, want, rtol=5e-3, atol=1e-4), list(zip(got, want))
     assert got[-1] < 1e-3 * got[0]
+
+
+REF_TREE_BIN = os.path.join(ROOT, "oracle", "_ref", "treelstm_cpu")
+
+
+@pytest.mark.skipif(not os.path.exists(REF_TREE_BIN), reason="oracle/_ref not built (reference checkout absent at build time)")
+def test_treelstm_loss_trajectory_matches_generated_program(oracle_lib, tmp_path):
+    """The reference's shipped generated TreeLSTM sentiment program (src/out/NIPS18evaluation/evaluationTreeLSTM/Lantern/
+    Lantern.cpp: embedding 300, hidden 150, 5 classes, one tree per step, hand-written Adagrad lr 0.05 without clipping,
+    6 epochs) against the `treelstm_nips18` host program on the oracle, on synthetic files in the program's own formats
+    (`small_glove.txt`: row count, then 300 floats per row; `array_tree.txt`: tree count, then per tree the node count
+    and four rows scores / words / left child / right child). Same rand() stream (seed 1: the program never calls
+    srand). Pins matrix-vector dot, sigmoid, tanh, elementwise product, the recursion and Adagrad of the oracle."""
+    from lantern_b200.hosts import HostPrograms
+    from tests.test_gpu_models import _random_tree
+    rng = np.random.default_rng(77)
+    vocab, n_trees = 60, 24
+    emb = np.float32(rng.normal(0.0, 0.1, (vocab, 300)))
+    with open(tmp_path / "small_glove.txt", "w") as f:
+        f.write("%d\n" % vocab)
+        for row in emb:
+            f.write(" ".join("%.9g" % v for v in row) + "\n")
+    trees = [_random_tree(rng, int(rng.integers(2, 9)), vocab=vocab) for _ in range(n_trees)]
+    with open(tmp_path / "array_tree.txt", "w") as f:
+        f.write("%d\n" % n_trees)
+        for y in trees:
+            n = int(y[0])
+            f.write("%d\n" % n)
+            for j in range(4):
+                f.write(" ".join(str(int(v)) for v in y[1 + j * 99: 1 + j * 99 + n]) + "\n")
+    out = subprocess.run([REF_TREE_BIN, "result.txt"], cwd=tmp_path, check=True, capture_output=True, text=True, timeout=900).stdout
+    ref = [float(line.split("average_loss ")[1].split(",")[0]) for line in out.split("\n") if line.startswith("epoc ")]
+    assert len(ref) == 6
+
+    mark = oracle_lib.mark()
+    oracle_lib.set_math(0)
+    model = HostPrograms(oracle_lib, ORA_HOSTS, "orah_").model("treelstm_nips18", 1, seed=1)
+    model.set_table(emb)
+    x = np.zeros(1, np.float32)
+    ours = []
+    for epoch in range(6):
+        avg = np.float32(0)
+        for n, y in enumerate(trees):                              # average_loss = average_loss * n / (n + 1) + loss / (n + 1)
+            loss = np.float32(model.step(x, y, 0.05))
+            avg = np.float32(avg * np.float32(n) / np.float32(n + 1) + loss / np.float32(n + 1))
+        ours.append(float(avg))
+    model.close()
+    oracle_lib.reset(mark)
+    assert np.allclose(ours, ref, rtol=2e-4), list(zip(ours, ref))
+    assert ours[-1] < ours[0]
