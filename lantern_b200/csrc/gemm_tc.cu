@@ -10,8 +10,12 @@
 //                 and writes the result: pixel-major for convolutions (a warp store covers 32 consecutive pixels of one
 //                 channel: 128 contiguous bytes), row-major for gemm / weight-grad; optional bias, alpha, accumulation,
 //                 and atomic accumulation under split-K.
-// Activations stay NCHW: the pixel index is the contiguous one, so the activation operand is fed M/N-major (tcgen05 allows
-// it for tf32) straight from the tensor with a 4-D tiled tensor map; no layout conversion pass exists.
+// Activations are NCHW at the boundary.  For 1x1 convolutions on images of 32 pixels or more the pixel index is the
+// contiguous one and the activation operand is fed M/N-major (tcgen05 allows it for tf32) straight from the tensor with a
+// 4-D tiled tensor map.  R x S convolutions with stride 1 run in tap-loop form from a channels-last copy (one transposing
+// pass, see to_rows_tiled_kernel): a TMA box is then a window of whole image rows whose coordinates the tap shifts, and
+// zero fill outside the image is the padding.  Smaller images, strided forward convolutions and weight-grads of R x S
+// filters are staged as row matrices or unfolded matrices by the helper kernels at the end of this file.
 // Every mbarrier wait is bounded: after about a second it records a code in the library's device status word and the CTA
 // runs to its normal teardown (TMEM is released on every path).  The single issuing lanes of warps 0 and 1 are rejoined by
 // their warps (__syncwarp) before the block-wide barrier, which needs converged warps.

@@ -431,3 +431,28 @@ def test_lookahead_fusion_flushes_on_any_other_call(ora, gpu):
     ref, got = f(ora), f(gpu, 1)
     for k in ref:
         assert_close(ref[k], got[k], 2e-4, k)
+
+
+@pytest.mark.parametrize("n", [0, 1, 3, 5, 1027, 65537])
+def test_empty_ragged_and_misaligned_vectors(ora, gpu, n):
+    """Element counts that are zero, smaller than a float4 or not a multiple of four, on buffers that start one float past
+    a 16-byte boundary (the vectorised kernels must fall back to their scalar forms), through the streaming operators."""
+    v = (R(1).standard_normal(n + 1) * 2).astype(np.float32)
+    d0 = R(2).standard_normal(n + 1).astype(np.float32)
+
+    def f(b):
+        full, dfull = b.fromNumpy(v), b.fromNumpy(d0)
+        x, d = full.offset(1, (n,)), dfull.offset(1, (n,))               # misaligned views of n elements
+        out = {}
+        if n:
+            out["relu"] = b.relu(x).toCPU(); out["tanh"] = b.tanh(x).toCPU()
+            out["scaled"] = b.mul(x, 0.5).toCPU()
+            out["sum"] = b.sum(x).toCPU()
+        t = TensorR(x, d)
+        b.lib.unary_grad(0, x.ptr, d.ptr, x.ptr, d.ptr, n, 1)               # in-place ReLU gradient
+        b.lib.sgd_step(x.ptr, d.ptr, 0.1, n)
+        b.lib.clip(x.ptr, 1.5, n)
+        b.lib.fill(d.ptr, 2.0, n)
+        out["x"], out["d"], out["guard_x"], out["guard_d"] = full.toCPU()[1:], dfull.toCPU()[1:], full.toCPU()[:1], dfull.toCPU()[:1]
+        return out
+    check(f, ora, gpu)
