@@ -165,11 +165,15 @@ __device__ __forceinline__ void store_columns(float* p, long long stride, const 
 #pragma unroll
     for (int j = 0; j < 32; ++j) { if (FULL || j < lim) atomicAdd(p, alpha * __uint_as_float(r[j]) + (bias ? bias[j] : 0.0f)); p += stride; }
   } else if (mode == 1) {                        // accumulate: all loads first, a load-add-store chain per element would serialise on latency
-    float old[32]; const float* q = p;
+    // sixteen at a time: thirty-two loads in flight next to the thirty-two accumulator registers spill
 #pragma unroll
-    for (int j = 0; j < 32; ++j) { old[j] = (FULL || j < lim) ? *q : 0.0f; q += stride; }
+    for (int h = 0; h < 32; h += 16) {
+      float old[16]; const float* q = p;
 #pragma unroll
-    for (int j = 0; j < 32; ++j) { if (FULL || j < lim) *p = old[j] + alpha * __uint_as_float(r[j]); p += stride; }
+      for (int j = 0; j < 16; ++j) { old[j] = (FULL || h + j < lim) ? *q : 0.0f; q += stride; }
+#pragma unroll
+      for (int j = 0; j < 16; ++j) { if (FULL || h + j < lim) *p = old[j] + alpha * __uint_as_float(r[h + j]); p += stride; }
+    }
   } else if (bias) {
 #pragma unroll
     for (int j = 0; j < 32; ++j) { if (FULL || j < lim) *p = alpha * __uint_as_float(r[j]) + bias[j]; p += stride; }
