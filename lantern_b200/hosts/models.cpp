@@ -47,6 +47,7 @@ struct Model {
   void* graph = nullptr;
   bool use_graph = false;
   float graph_lr = 0.f;
+  size_t zero_bytes = 0;       // bytes of zero-initialised gradient buffers the last step asked for (0: not known yet)
   bool early_reduce = false;   // this step runs data-parallel with an update: finished gradient ranges are summed during backward
   bool resident = false;       // read the batch from dev_x/dev_y instead of uploading it
   float* dev_x = nullptr; int32_t* dev_y = nullptr;
@@ -88,6 +89,7 @@ struct Model {
   // One training step's device work, in the order of the generated programs.
   void enqueue(float lr, bool update) {
     Tape tape;
+    zero_pool_begin(zero_bytes);
     int64_t nin = (int64_t)batch * in_c * in_h * in_w;
     TR x; x.rank = 4; x.shape[0] = batch; x.shape[1] = in_c; x.shape[2] = in_h; x.shape[3] = in_w; x.is_input = true;
     int32_t* y;
@@ -108,6 +110,7 @@ struct Model {
     BK(d2h_async)(loss_host, loss_copy, 4);
     if (update) apply_update(lr);
     if (tracing()) dump_trace();
+    zero_bytes = zero_pool_end();
     BK(reset)(mark);
   }
   // Data parallelism: pushed on the tape at a point of the forward pass, this fires in the backward pass once every layer
@@ -147,7 +150,7 @@ struct Model {
   }
   int step_async(const float* xh, const int32_t* yh, float lr, bool update) {
     if (!resident) load(xh, yh);
-    if (use_graph && update) {
+    if (use_graph && update && zero_bytes > 0) {        // the first step runs eagerly: it measures the gradient pool
       if (graph && graph_lr != lr) { BK(graph_destroy)(graph); graph = nullptr; }
       if (!graph) {
         int rc = BK(graph_begin)(); if (rc) return rc;

@@ -32,7 +32,25 @@ struct TR {
 };
 
 inline float* alloc_value(int64_t n) { return (float*)BK(malloc_uninit)((size_t)n * 4); }
-inline float* alloc_zero(int64_t n) { return (float*)BK(malloc)((size_t)n * 4); }
+// Gradient buffers of one step are carved out of ONE zero-filled block taken at the start of the step (the reference
+// zeroes its whole arena span once per step, DslAPI.scala:475-484: one bulk fill instead of one small fill per tensor, each
+// of which is a node of its own in the recorded step).  The block's size is what the previous step of the same program
+// asked for; a request that does not fit (first step, data-dependent programs) is served by the library's zeroing malloc.
+struct ZeroPool { char* base = nullptr; size_t cap = 0, used = 0, asked = 0; };
+inline ZeroPool& zero_pool() { static ZeroPool p; return p; }
+inline void zero_pool_begin(size_t bytes) {
+  ZeroPool& p = zero_pool();
+  p.base = bytes ? (char*)BK(malloc)(bytes) : nullptr;
+  p.cap = p.base ? bytes : 0; p.used = 0; p.asked = 0;
+}
+inline size_t zero_pool_end() { ZeroPool& p = zero_pool(); size_t a = p.asked; p.base = nullptr; p.cap = p.used = 0; return a; }
+inline float* alloc_zero(int64_t n) {
+  ZeroPool& p = zero_pool();
+  const size_t bytes = ((size_t)n * 4 + 255) / 256 * 256;
+  p.asked += bytes;
+  if (p.used + bytes <= p.cap) { float* r = (float*)(p.base + p.used); p.used += bytes; return r; }
+  return (float*)BK(malloc)((size_t)n * 4);
+}
 
 // Debug trace: when on, every tensor an operator allocates is remembered so that a step can be dumped
 // (per-tensor checksums of value and gradient) and two libraries compared operator by operator.
