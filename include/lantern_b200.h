@@ -98,6 +98,14 @@ int LTB_FN(d2d)(void* dst, const void* src, size_t bytes);   /* copyFloatArray, 
 void* LTB_FN(host_alloc)(size_t bytes);
 int   LTB_FN(host_free)(void* p);
 int   LTB_FN(d2h_async)(void* dst_pinned, const void* src, size_t bytes);
+/* Stream markers (no counterpart in the reference, whose generated programs block on every transfer,
+ * GPUOps.scala:63-65): marker_record notes the current end of the library's stream in one of 16 slots, marker_wait
+ * blocks the calling thread until the work issued before that record has finished (returns at once for a slot
+ * never recorded).  They let a host program keep two steps in flight -- refill a pinned staging buffer, or read a
+ * loss written by d2h_async, as soon as the step that used it is done -- instead of draining the stream with
+ * ltb_sync after every step.  Not allowed while recording a step. */
+int   LTB_FN(marker_record)(int slot);
+int   LTB_FN(marker_wait)(int slot);
 
 /* Whole-step replay. Shapes are static and the bump arena hands out the same addresses every iteration after
  * ltb_reset, so one training step can be recorded once and replayed: graph_begin starts recording the calls

@@ -58,7 +58,7 @@ def build_all(force=False, verbose=False):
     if force or jobs or _newer(LIB, objs):
         _run([NVCC, "-shared", "-o", LIB] + objs + ["-ldl", "-lpthread"])
     hsrc = os.path.join(HERE, "hosts", "models.cpp")
-    hdeps = [hsrc, os.path.join(HERE, "hosts", "tape.hpp"), LIB] + headers[-1:]
+    hdeps = [hsrc, os.path.join(HERE, "hosts", "tape.hpp"), os.path.join(HERE, "hosts", "loader.hpp"), LIB] + headers[-1:]
     if force or _newer(HOSTS, hdeps):
         _run(["g++", "-std=c++17", "-O2", "-fPIC", "-shared", "-o", HOSTS, hsrc, "-L" + HERE, "-llantern_b200",
               "-Wl,-rpath,$ORIGIN"])

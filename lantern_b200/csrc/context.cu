@@ -86,6 +86,10 @@ int ltb_init(int device, size_t heap_bytes) {
 
 int ltb_comm_destroy(void);
 
+// Stream markers (ltb_marker_record / ltb_marker_wait): one event per slot, created on first use.
+static cudaEvent_t marker_ev[16];
+static bool marker_set[16];
+
 int ltb_shutdown(void) {
   if (!g.inited) return LTB_OK;
   if (g.pending.kind) flush_pending();
@@ -94,6 +98,7 @@ int ltb_shutdown(void) {
   cudaStreamSynchronize(g.side);
   cudaFree(g.heap); cudaFree(g.dev_status); cudaFree(g.scratch); cudaFreeHost(g.host_status);
   cudaStreamDestroy(g.side); cudaEventDestroy(g.fork_ev); cudaEventDestroy(g.join_ev);
+  for (int i = 0; i < 16; ++i) { if (marker_ev[i]) cudaEventDestroy(marker_ev[i]); marker_ev[i] = nullptr; marker_set[i] = false; }
   if (g.own_stream) cudaStreamDestroy(g.stream);
   g = Context();
   return LTB_OK;
@@ -180,6 +185,19 @@ int ltb_host_free(void* p) { if (p) LTB_CUDA(cudaFreeHost(p)); return LTB_OK; }
 int ltb_d2h_async(void* dst, const void* src, size_t bytes) {
   LTB_INITED(); LTB_REQUIRE(dst && src, "ltb_d2h_async: null pointer");
   if (bytes) LTB_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, g.stream));
+  return LTB_OK;
+}
+int ltb_marker_record(int slot) {
+  LTB_INITED(); LTB_REQUIRE(slot >= 0 && slot < 16, "ltb_marker_record: slot %d out of range", slot);
+  LTB_REQUIRE(!g.capturing, "ltb_marker_record: not allowed while recording a step");
+  if (!marker_ev[slot]) LTB_CUDA(cudaEventCreateWithFlags(&marker_ev[slot], cudaEventDisableTiming));
+  LTB_CUDA(cudaEventRecord(marker_ev[slot], g.stream));
+  marker_set[slot] = true;
+  return LTB_OK;
+}
+int ltb_marker_wait(int slot) {
+  LTB_INITED_NOFLUSH(); LTB_REQUIRE(slot >= 0 && slot < 16, "ltb_marker_wait: slot %d out of range", slot);
+  if (marker_set[slot]) LTB_CUDA(cudaEventSynchronize(marker_ev[slot]));
   return LTB_OK;
 }
 

@@ -25,6 +25,17 @@ _SIGS = {
     "model_step": (ctypes.c_float, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_float, ctypes.c_int]),
     "model_step_async": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_float]),
     "model_last_loss": (ctypes.c_float, [ctypes.c_void_p]),
+    "model_submit": (ctypes.c_int64, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_float]),
+    "model_collect": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int64, ctypes.POINTER(ctypes.c_float)]),
+    "model_train_epoch": (ctypes.c_int64, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_float, ctypes.c_void_p, ctypes.c_int64]),
+    "model_save_params": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_char_p]),
+    "model_load_params": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_char_p]),
+    "loader_open_floats": (ctypes.c_void_p, [ctypes.c_char_p, ctypes.c_char_p, ctypes.c_int64, ctypes.c_float, ctypes.c_float]),
+    "loader_open_cifar": (ctypes.c_void_p, [ctypes.c_char_p, ctypes.c_int64]),
+    "loader_error": (ctypes.c_char_p, [ctypes.c_void_p]),
+    "loader_length": (ctypes.c_int64, [ctypes.c_void_p]),
+    "loader_fill": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p]),
+    "loader_close": (None, [ctypes.c_void_p]),
     "model_trace": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_char_p, ctypes.c_int]),
 }
 
@@ -46,6 +57,37 @@ class HostPrograms:
 
     def model(self, name, batch, seed=42):
         return Model(self, name, batch, seed)
+
+    def float_loader(self, data_path, target_path, floats_per_sample, mean=0.0, std=1.0):
+        """`<name>_train.bin` (raw float32) + `<name>_train_target.bin` (raw int32), samples used as (x - mean) / std."""
+        return Loader(self, self.fn["loader_open_floats"](os.fsencode(data_path), os.fsencode(target_path), floats_per_sample, mean, std), floats_per_sample)
+
+    def cifar_loader(self, path, bytes_per_sample=3072):
+        """CIFAR binary records: one label byte + `bytes_per_sample` pixel bytes; x = byte / 255."""
+        return Loader(self, self.fn["loader_open_cifar"](os.fsencode(path), bytes_per_sample), bytes_per_sample)
+
+
+class Loader:
+    def __init__(self, hp, handle, sample_count):
+        self.hp, self.h, self.sample_count = hp, handle, sample_count
+        err = hp.fn["loader_error"](handle).decode()
+        if err:
+            hp.fn["loader_close"](handle)
+            self.h = None
+            raise OSError(err)
+        self.length = hp.fn["loader_length"](handle)
+
+    def batch(self, index, batch):
+        x = np.empty(batch * self.sample_count, dtype=np.float32)
+        y = np.empty(batch, dtype=np.int32)
+        if self.hp.fn["loader_fill"](self.h, index, batch, x.ctypes.data, y.ctypes.data):
+            raise IndexError("batch %d of %d samples is outside the file" % (index, batch))
+        return x, y
+
+    def close(self):
+        if self.h:
+            self.hp.fn["loader_close"](self.h)
+            self.h = None
 
 
 class Model:
@@ -74,6 +116,41 @@ class Model:
         rc = self.hp.fn["model_step_async"](self.h, x.ctypes.data, y.ctypes.data, lr)
         if rc:
             raise RuntimeError("model_step_async failed: %d %s" % (rc, self.lib.error_message()))
+
+    def submit(self, x, y, lr):
+        """Queue one training step on host arrays and return its number without waiting (two steps stay in flight)."""
+        x, y = self._arrs(x, y)
+        k = self.hp.fn["model_submit"](self.h, x.ctypes.data, y.ctypes.data, lr)
+        if k < 0:
+            raise RuntimeError("model_submit failed: %s" % self.lib.error_message())
+        return k
+
+    def collect(self, step):
+        """Wait for step `step` (one of the last two submitted) and return its loss."""
+        out = ctypes.c_float()
+        rc = self.hp.fn["model_collect"](self.h, step, ctypes.byref(out))
+        if rc:
+            raise RuntimeError("model_collect(%d) failed: %d %s" % (step, rc, self.lib.error_message()))
+        return float(out.value)
+
+    def train_epoch(self, loader, lr, max_batches=0):
+        """One pass over `loader` with two steps in flight; returns the per-batch losses."""
+        n = loader.length // self.batch
+        if max_batches > 0:
+            n = min(n, max_batches)
+        losses = np.zeros(max(n, 1), dtype=np.float32)
+        rc = self.hp.fn["model_train_epoch"](self.h, loader.h, lr, losses.ctypes.data, max_batches)
+        if rc < 0:
+            raise RuntimeError("model_train_epoch failed: %d %s" % (rc, self.lib.error_message()))
+        return losses[:rc]
+
+    def save_params(self, path):
+        if self.hp.fn["model_save_params"](self.h, os.fsencode(path)):
+            raise OSError("cannot write %s" % path)
+
+    def load_params(self, path):
+        if self.hp.fn["model_load_params"](self.h, os.fsencode(path)):
+            raise ValueError("%s is not a parameter file of this model" % path)
 
     def last_loss(self):
         return float(self.hp.fn["model_last_loss"](self.h))

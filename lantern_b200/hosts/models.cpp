@@ -17,6 +17,7 @@
 #include <string>
 #include <vector>
 
+#include "loader.hpp"
 #include "tape.hpp"
 
 #ifndef HOST_FN
@@ -51,6 +52,11 @@ struct Model {
   bool early_reduce = false;   // this step runs data-parallel with an update: finished gradient ranges are summed during backward
   bool resident = false;       // read the batch from dev_x/dev_y instead of uploading it
   float* dev_x = nullptr; int32_t* dev_y = nullptr;
+  float* dev_loss = nullptr;   // the loss of the last step, kept outside the arena span that the step resets
+  // Two steps in flight (submit / collect): staging pair p = step & 1; marker p = its upload done, marker 2 + p = its step done.
+  bool feeding = false;
+  int64_t submitted = 0;
+  float* feed_x[2] = {nullptr, nullptr}; int32_t* feed_y[2] = {nullptr, nullptr}; float* feed_loss = nullptr;
 
   int declare(std::initializer_list<int> shape, int init, float scale = 0.f) {
     ParamDecl d; d.shape.assign(shape.begin(), shape.end()); d.init = init; d.scale = scale;
@@ -82,6 +88,7 @@ struct Model {
     loss_host = (float*)BK(host_alloc)(4);
     dev_x = alloc_value((int64_t)batch * in_c * in_h * in_w);
     dev_y = (int32_t*)BK(malloc_uninit)((size_t)label_count * 4);
+    dev_loss = alloc_value(1);
     mark = BK(mark)();
   }
   virtual TR forward(Tape& t, const TR& x, const int32_t* y) = 0;
@@ -104,10 +111,9 @@ struct Model {
     early_reduce = update && BK(comm_world)() > 1;
     TR loss = forward(tape, x, y);
     BK(fill)(loss.d, 1.0f, 1);                       // gradR_loss: y.d.setAsOne(), TD.scala:1763-1780
-    float* loss_copy = alloc_value(1);
-    BK(d2d)(loss_copy, loss.x, 4);
+    BK(d2d)(dev_loss, loss.x, 4);
     tape.backward();
-    BK(d2h_async)(loss_host, loss_copy, 4);
+    BK(d2h_async)(loss_host, dev_loss, 4);
     if (update) apply_update(lr);
     if (tracing()) dump_trace();
     zero_bytes = zero_pool_end();
@@ -149,7 +155,7 @@ struct Model {
     memcpy(stage_y, yh, (size_t)label_count * 4);
   }
   int step_async(const float* xh, const int32_t* yh, float lr, bool update) {
-    if (!resident) load(xh, yh);
+    if (!resident && xh) load(xh, yh);
     if (use_graph && update && zero_bytes > 0) {        // the first step runs eagerly: it measures the gradient pool
       if (graph && graph_lr != lr) { BK(graph_destroy)(graph); graph = nullptr; }
       if (!graph) {
@@ -167,6 +173,49 @@ struct Model {
     step_async(xh, yh, lr, update);
     BK(sync)();
     return *loss_host;
+  }
+  // Training with two steps in flight.  The generated programs upload a batch, run the step and block on the loss copy
+  // (resnet50FromOnnx.scala:173-186), so the device idles while the host prepares the next batch.  submit() copies the
+  // batch into one of two pinned staging pairs, queues the upload, the step (reading the batch at its fixed device
+  // address, so the recorded step is the same every time) and a 4-byte loss copy, and returns; collect(k) waits for
+  // step k alone.  The staging pair of step k is refilled by step k + 2, after its upload marker has fired.
+  void feed_mode(bool on) {
+    if (feeding == on) return;
+    if (graph) { BK(graph_destroy)(graph); graph = nullptr; }      // the recorded step reads the batch from another place
+    if (on && !feed_loss) {
+      const size_t xb = (size_t)batch * in_c * in_h * in_w * 4;
+      for (int p = 0; p < 2; ++p) { feed_x[p] = (float*)BK(host_alloc)(xb); feed_y[p] = (int32_t*)BK(host_alloc)((size_t)label_count * 4); }
+      feed_loss = (float*)BK(host_alloc)(8);
+    }
+    if (on) BK(sync)();
+    feeding = resident = on;
+  }
+  // Staging pair for the next submit, free to be written (a loader decodes a batch straight into it).
+  int feed_slot(float** x, int32_t** y) {
+    feed_mode(true);
+    const int p = (int)(submitted & 1);
+    if (submitted >= 2) { int rc = BK(marker_wait)(p); if (rc) return rc; }
+    *x = feed_x[p]; *y = feed_y[p];
+    return 0;
+  }
+  // xh == nullptr: the caller has filled the pair returned by feed_slot.
+  int64_t submit(const float* xh, const int32_t* yh, float lr) {
+    float* sx; int32_t* sy;
+    if (feed_slot(&sx, &sy)) return -1;
+    const int p = (int)(submitted & 1);
+    const size_t xb = (size_t)batch * in_c * in_h * in_w * 4;
+    if (xh) { memcpy(sx, xh, xb); memcpy(sy, yh, (size_t)label_count * 4); }
+    if (BK(h2d)(dev_x, sx, xb) || BK(h2d)(dev_y, sy, (size_t)label_count * 4) || BK(marker_record)(p)) return -1;
+    if (step_async(nullptr, nullptr, lr, true)) return -1;
+    if (BK(d2h_async)(feed_loss + p, dev_loss, 4) || BK(marker_record)(2 + p)) return -1;
+    return submitted++;
+  }
+  int collect(int64_t k, float* loss) {
+    if (k < 0 || k >= submitted || k + 2 < submitted) return LTB_E_ARG;     // only the last two steps keep their loss
+    const int p = (int)(k & 1);
+    int rc = BK(marker_wait)(2 + p); if (rc) return rc;
+    *loss = feed_loss[p];
+    return 0;
   }
 };
 
@@ -450,6 +499,8 @@ void HOST_FN(model_destroy)(void* m) {
   Model* M = (Model*)m;
   if (M->graph) BK(graph_destroy)(M->graph);
   BK(host_free)(M->stage_x); BK(host_free)(M->stage_y); BK(host_free)(M->loss_host);
+  for (int p = 0; p < 2; ++p) { BK(host_free)(M->feed_x[p]); BK(host_free)(M->feed_y[p]); }
+  BK(host_free)(M->feed_loss);
   delete M;
 }
 int HOST_FN(model_num_params)(void* m) { return (int)((Model*)m)->decls.size(); }
@@ -471,6 +522,7 @@ int HOST_FN(model_use_graph)(void* m, int on) { Model* M = (Model*)m; M->use_gra
 // Keep one batch resident in device memory; later steps read it there and upload nothing (x_host/y_host are ignored).
 int HOST_FN(model_set_resident)(void* m, const float* x_host, const int32_t* y_host) {
   Model* M = (Model*)m;
+  M->feed_mode(false);
   if (M->graph) { BK(graph_destroy)(M->graph); M->graph = nullptr; }
   if (!x_host) { M->resident = false; return 0; }
   M->load(x_host, y_host);
@@ -482,13 +534,85 @@ int HOST_FN(model_set_resident)(void* m, const float* x_host, const int32_t* y_h
 }
 // Blocking step: returns the loss of this batch. update=0 leaves the parameter gradients in place for inspection.
 float HOST_FN(model_step)(void* m, const float* x_host, const int32_t* y_host, float lr, int update) {
-  return ((Model*)m)->step(x_host, y_host, lr, update != 0);
+  Model* M = (Model*)m;
+  if (M->feeding) M->feed_mode(false);
+  return M->step(x_host, y_host, lr, update != 0);
 }
 // Non-blocking step: the loss is available from model_last_loss after the library's sync.
 int HOST_FN(model_step_async)(void* m, const float* x_host, const int32_t* y_host, float lr) {
-  return ((Model*)m)->step_async(x_host, y_host, lr, true);
+  Model* M = (Model*)m;
+  if (M->feeding) M->feed_mode(false);
+  return M->step_async(x_host, y_host, lr, true);
 }
+// Two steps in flight: submit returns the step's number (or -1) without waiting; collect(k) waits for step k and gives its
+// loss.  Only the last two submitted steps can be collected.
+int64_t HOST_FN(model_submit)(void* m, const float* x_host, const int32_t* y_host, float lr) { return ((Model*)m)->submit(x_host, y_host, lr); }
+int HOST_FN(model_collect)(void* m, int64_t step, float* loss) { return ((Model*)m)->collect(step, loss); }
 float HOST_FN(model_last_loss)(void* m) { return *((Model*)m)->loss_host; }
+
+// ---- data and parameter files in the reference's formats (loader.hpp)
+void* HOST_FN(loader_open_floats)(const char* data_path, const char* target_path, int64_t floats_per_sample, float mean, float stdev) {
+  Loader* L = new Loader;
+  L->open_floats(data_path, target_path, floats_per_sample, mean, stdev);
+  return L;                                      // a loader that failed to open has length 0 and a message (loader_error)
+}
+void* HOST_FN(loader_open_cifar)(const char* path, int64_t bytes_per_sample) {
+  Loader* L = new Loader;
+  L->open_cifar(path, bytes_per_sample);
+  return L;
+}
+const char* HOST_FN(loader_error)(void* l) { return ((Loader*)l)->error.c_str(); }
+int64_t HOST_FN(loader_length)(void* l) { Loader* L = (Loader*)l; return L->error.empty() ? L->length : 0; }
+int HOST_FN(loader_fill)(void* l, int64_t index, int batch, float* x, int32_t* y) {
+  Loader* L = (Loader*)l;
+  return L->error.empty() && L->fill(index, batch, x, y) ? 0 : LTB_E_ARG;
+}
+void HOST_FN(loader_close)(void* l) { Loader* L = (Loader*)l; L->close(); delete L; }
+// One pass over the loader's batches (at most max_batches when positive) with two steps in flight: batch i + 1 is decoded
+// into pinned staging while the device runs step i.  losses (nullable) receives one value per batch.  Returns the number
+// of steps, or a negative error code.
+int64_t HOST_FN(model_train_epoch)(void* m, void* l, float lr, float* losses, int64_t max_batches) {
+  Model* M = (Model*)m; Loader* L = (Loader*)l;
+  if (!L->error.empty() || L->sample_count != (int64_t)M->in_c * M->in_h * M->in_w || M->label_count != M->batch) return LTB_E_ARG;
+  int64_t n = L->batches(M->batch);
+  if (max_batches > 0 && max_batches < n) n = max_batches;
+  int64_t prev = -1;
+  for (int64_t i = 0; i < n; ++i) {
+    float* sx; int32_t* sy; float loss;
+    if (M->feed_slot(&sx, &sy) || !L->fill(i, M->batch, sx, sy)) return LTB_E_STATE;
+    const int64_t k = M->submit(nullptr, nullptr, lr);
+    if (k < 0) return LTB_E_CUDA;
+    if (prev >= 0) { if (M->collect(prev, &loss)) return LTB_E_CUDA; if (losses) losses[i - 1] = loss; }
+    prev = k;
+  }
+  if (prev >= 0) { float loss; if (M->collect(prev, &loss)) return LTB_E_CUDA; if (losses) losses[n - 1] = loss; }
+  return n;
+}
+// Parameter file: every tensor's floats back to back, unpadded, in declaration order (ONNXLib.scala:157-185).
+int HOST_FN(model_save_params)(void* m, const char* path) {
+  Model* M = (Model*)m;
+  std::vector<float> slab((size_t)M->slab_count);
+  if (BK(d2h)(slab.data(), M->slab_x, slab.size() * 4)) return LTB_E_CUDA;
+  FILE* f = fopen(path, "wb");
+  if (!f) return LTB_E_ARG;
+  bool ok = true;
+  for (const ParamDecl& d : M->decls) ok = ok && fwrite(slab.data() + d.offset, 4, (size_t)d.count, f) == (size_t)d.count;
+  return fclose(f) == 0 && ok ? 0 : LTB_E_STATE;
+}
+int HOST_FN(model_load_params)(void* m, const char* path) {
+  Model* M = (Model*)m;
+  MappedFile f;
+  if (!f.open(path)) return LTB_E_ARG;
+  int64_t total = 0;
+  for (const ParamDecl& d : M->decls) total += d.count;
+  if ((int64_t)(f.bytes / 4) != total || f.bytes % 4) { f.close(); return LTB_E_ARG; }      // not this model's file
+  std::vector<float> slab((size_t)M->slab_count, 0.0f);
+  const float* src = (const float*)f.data;
+  for (const ParamDecl& d : M->decls) { memcpy(slab.data() + d.offset, src, (size_t)d.count * 4); src += d.count; }
+  f.close();
+  if (BK(sync)() || BK(h2d)(M->slab_x, slab.data(), slab.size() * 4) || BK(sync)()) return LTB_E_CUDA;
+  return 0;
+}
 // Debug: run one step without update and write per-operator checksums (see Model::dump_trace) into buf.
 int HOST_FN(model_trace)(void* m, const float* x_host, const int32_t* y_host, char* buf, int len) {
   Model* M = (Model*)m;

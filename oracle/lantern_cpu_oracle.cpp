@@ -899,6 +899,8 @@ extern "C" {
 void* ora_host_alloc(size_t bytes) { return malloc(bytes); }
 int ora_host_free(void* p) { free(p); return LTB_OK; }
 int ora_d2h_async(void* d, const void* s, size_t n) { memcpy(d, s, n); return LTB_OK; }
+int ora_marker_record(int) { return LTB_OK; }      // the CPU oracle runs every call to completion
+int ora_marker_wait(int) { return LTB_OK; }
 int ora_graph_begin(void) { return fail(LTB_E_ARG, "the CPU oracle does not record steps"); }
 void* ora_graph_end(void) { return nullptr; }
 int ora_graph_launch(void*) { return fail(LTB_E_ARG, "the CPU oracle does not record steps"); }
