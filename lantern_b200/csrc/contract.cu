@@ -23,6 +23,11 @@ bool conv_dims(ConvDims& d, int N, int C, int H, int W, int K, int R, int S, int
   return (int64_t)N * d.oH * d.oW < (1ll << 31) && (int64_t)N * H * W < (1ll << 31) && (int64_t)C * R * S < (1ll << 31);
 }
 
+// A convolution whose filter covers the whole unpadded image has one output pixel per image and is a plain matrix
+// product over (channel, row, column): y[N][K] = x[N][CHW] w[K][CHW]^T (the last layer of the reference's SqueezeNet, a 4x4
+// filter on 4x4 maps).  The gemm paths split a long reduction over the machine; the convolution paths would give it to one tile.
+bool covers_image(const ConvDims& d) { return d.R == d.H && d.S == d.W && d.ph == 0 && d.pw == 0 && d.oH == 1 && d.oW == 1; }
+
 }  // namespace
 
 extern "C" {
@@ -71,6 +76,10 @@ int ltb_conv2d_fwd(const float* x, const float* w, const float* bias, float* y, 
                    int sh, int sw, int ph, int pw) {
   LTB_INITED(); ConvDims d;
   LTB_REQUIRE(x && w && y && conv_dims(d, N, C, H, W, K, R, S, sh, sw, ph, pw), "ltb_conv2d_fwd: bad argument");
+  if (covers_image(d) && d.R * d.S > 1) {
+    if (bias) { int rc = ltb_fill_with_bias(y, bias, N, K, 1); if (rc) return rc; }
+    return gemm_any(x, false, w, true, y, N, K, C * R * S, 1.0f, bias != nullptr);
+  }
   if (g.math == LTB_MATH_TF32) { int r = conv_fwd_tc(x, w, bias, y, d); if (r != 0) return r < 0 ? r : LTB_OK; }
   return conv_fwd_fp32(x, w, bias, y, d);
 }
@@ -80,6 +89,13 @@ int ltb_conv2d_bwd(const float* x, float* dx, const float* w, float* dw, float* 
   LTB_INITED(); ConvDims d;
   LTB_REQUIRE(x && w && dy && conv_dims(d, N, C, H, W, K, R, S, sh, sw, ph, pw), "ltb_conv2d_bwd: bad argument");
   int rc = LTB_OK;
+  if (covers_image(d) && d.R * d.S > 1) {
+    const int crs = C * R * S;
+    if (dw) rc = gemm_any(dy, true, x, false, dw, K, crs, N, 1.0f, true);           // dw[K][CHW] += dy^T x
+    if (!rc && dx) rc = gemm_any(dy, false, w, false, dx, N, crs, K, 1.0f, true);   // dx[N][CHW] += dy w
+    if (!rc && dbias) rc = conv_bias_grad(dy, dbias, d);
+    return rc;
+  }
   // The two halves are independent (dx needs dy and w; dw needs dy and x). When both are asked for, the weight-gradient
   // half is issued on the side stream and the data-gradient half on the caller's, and the caller's stream waits for both
   // before the call returns: program order at the boundary is unchanged, and inside a recorded step the two become

@@ -85,13 +85,15 @@ struct MatStore {
 // ---- skinny products: one extent of 16 or less (a 10-way classifier and its gradients) -----------------------------------
 // The 64 x 64 tiles above leave such products to one or two CTAs walking a long K; these three kernels give every output
 // (or every output column) its own thread or warp instead.
-// N <= 16, A and B both contiguous along k: a block of four warps per row m, each warp a quarter of K, lanes stride over k.
+// N <= 16, A and B both contiguous along k: a block of four warps per (row m, K split), each warp a quarter of the split,
+// lanes stride over k.  With more than one split (a long K and few rows) the partial results are added atomically.
 template <bool ACC>
 __global__ void skinny_n_kernel(const float* __restrict__ a, int64_t sam, const float* __restrict__ b, int64_t sbn, float* c, int64_t scm, int64_t scn,
                                 int N, int K, float alpha) {
   __shared__ float part[4][16];
   const int m = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int k0 = (int)((int64_t)K * warp / 4), k1 = (int)((int64_t)K * (warp + 1) / 4);
+  const int quarter = blockIdx.y * 4 + warp, quarters = gridDim.y * 4;
+  const int k0 = (int)((int64_t)K * quarter / quarters), k1 = (int)((int64_t)K * (quarter + 1) / quarters);
   float acc[16];
 #pragma unroll
   for (int n = 0; n < 16; ++n) acc[n] = 0.0f;
@@ -112,7 +114,7 @@ __global__ void skinny_n_kernel(const float* __restrict__ a, int64_t sam, const 
     const int n = threadIdx.x;
     const float v = alpha * ((part[0][n] + part[1][n]) + (part[2][n] + part[3][n]));
     float* q = c + (int64_t)m * scm + (int64_t)n * scn;
-    *q = ACC ? *q + v : v;
+    if (gridDim.y > 1) atomicAdd(q, v); else *q = ACC ? *q + v : v;
   }
 }
 // K <= 16: a thread per output element.
@@ -149,8 +151,16 @@ static int skinny_gemm(const float* a, int64_t sam, int64_t sak, const float* b,
                        int M, int N, int K, float alpha, bool accumulate, bool* taken) {
   *taken = true;
   if (N <= 16 && sak == 1 && sbk == 1 && K >= 128 && M <= 65535) {
-    if (accumulate) LTB_LAUNCH(skinny_n_kernel<true>, M, 128, 0, a, sam, b, sbn, c, scm, scn, N, K, alpha);
-    else LTB_LAUNCH(skinny_n_kernel<false>, M, 128, 0, a, sam, b, sbn, c, scm, scn, N, K, alpha);
+    // a lane walks its share of K one dependent step at a time: few rows with a long K are split over more blocks
+    int ks = (int)ceil_div(2 * g.sm_count, M);
+    if (ks > K / 512) ks = K / 512;
+    if (ks < 1) ks = 1;
+    if (ks > 1 && !accumulate) {                     // the splits add atomically: start from zero (dense outputs only)
+      if (scn == 1 && scm == N) { LTB_CUDA(cudaMemsetAsync(c, 0, (size_t)M * N * sizeof(float), g.stream)); accumulate = true; }
+      else ks = 1;
+    }
+    if (accumulate) LTB_LAUNCH(skinny_n_kernel<true>, dim3(M, ks), 128, 0, a, sam, b, sbn, c, scm, scn, N, K, alpha);
+    else LTB_LAUNCH(skinny_n_kernel<false>, dim3(M, ks), 128, 0, a, sam, b, sbn, c, scm, scn, N, K, alpha);
   } else if (K <= 16) {
     const unsigned grid = (unsigned)grid_for((int64_t)M * N, 256);
     if (accumulate) LTB_LAUNCH(skinny_k_kernel<true>, grid, 256, 0, a, sam, sak, b, sbk, sbn, c, scm, scn, M, N, K, alpha);
@@ -250,13 +260,20 @@ struct ConvWgradB {
   }
 };
 
-// dbias[co] += sum over n, ho, wo of dy (TensorDslCPU.scala:607-617): one block per channel.
-__global__ void conv_bias_grad_kernel(const float* __restrict__ dy, float* dbias, int N, int K, int hw) {
-  int co = blockIdx.x;
+// dbias[co] += sum over n, ho, wo of dy (TensorDslCPU.scala:607-617).  grid (channel, image split): with one block per
+// channel a 16-channel squeeze layer would read its 4 MB gradient with 16 blocks; the splits each add their partial sum
+// atomically.  VEC: hw is a multiple of 4 and dy is 16-byte aligned.
+template <bool VEC>
+__global__ void conv_bias_grad_kernel(const float* __restrict__ dy, float* dbias, int N, int K, int hw, int img_per_split) {
+  const int co = blockIdx.x;
+  const int n0 = blockIdx.y * img_per_split, n1 = min(N, n0 + img_per_split);
   float s = 0.0f;
-  for (int n = 0; n < N; ++n) {
-    const float* p = dy + ((int64_t)n * K + co) * hw;
-    for (int i = threadIdx.x; i < hw; i += blockDim.x) s += p[i];
+  const int per = VEC ? hw / 4 : hw;                       // the threads run over (image, element) pairs: small maps keep every lane busy
+  for (int j = threadIdx.x; j < (n1 - n0) * per; j += blockDim.x) {
+    const int n = j / per, i = j - n * per;
+    const float* p = dy + ((int64_t)(n0 + n) * K + co) * hw;
+    if (VEC) { const float4 v = reinterpret_cast<const float4*>(p)[i]; s += (v.x + v.y) + (v.z + v.w); }
+    else s += p[i];
   }
   __shared__ float sh[32];
   for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
@@ -265,7 +282,7 @@ __global__ void conv_bias_grad_kernel(const float* __restrict__ dy, float* dbias
   if (threadIdx.x < 32) {
     s = threadIdx.x < (blockDim.x >> 5) ? sh[threadIdx.x] : 0.0f;
     for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-    if (threadIdx.x == 0) dbias[co] += s;
+    if (threadIdx.x == 0) { if (gridDim.y == 1) dbias[co] += s; else atomicAdd(dbias + co, s); }
   }
 }
 
@@ -295,7 +312,16 @@ int conv_wgrad_fp32(const float* x, const float* dy, float* dw, const ConvDims& 
   return LTB_OK;
 }
 int conv_bias_grad(const float* dy, float* dbias, const ConvDims& d) {
-  LTB_LAUNCH(conv_bias_grad_kernel, d.K, 256, 0, dy, dbias, d.N, d.K, d.oH * d.oW);
+  const int hw = d.oH * d.oW;
+  int splits = (int)ceil_div(2 * g.sm_count, d.K);                      // about two blocks per SM in all
+  if (splits > d.N) splits = d.N;
+  if ((int64_t)d.N * hw < 4096) splits = 1;                              // a few KB per channel: one block reads it at once
+  const int ips = (int)ceil_div(d.N, splits);
+  splits = (int)ceil_div(d.N, ips);
+  const int threads = 256;
+  const bool vec = hw % 4 == 0 && (reinterpret_cast<uintptr_t>(dy) & 15) == 0;
+  if (vec) LTB_LAUNCH(conv_bias_grad_kernel<true>, dim3(d.K, splits), threads, 0, dy, dbias, d.N, d.K, hw, ips);
+  else LTB_LAUNCH(conv_bias_grad_kernel<false>, dim3(d.K, splits), threads, 0, dy, dbias, d.N, d.K, hw, ips);
   return LTB_OK;
 }
 

@@ -443,6 +443,14 @@ __global__ void permute_taps_kernel(const float* __restrict__ w, float* __restri
     out[i] = w[((int64_t)k * C + c) * taps + t];
   }
 }
+// Filter matrix w[rows][cols] copied with its rows padded by zeros to ld floats (the engine's tensor maps want a row length
+// of 4 floats for K-major and 32 floats for N-major operands; 3x3 filters over 3 or 16 channels have 27 or 144).
+__global__ void pad_rows_kernel(const float* __restrict__ w, float* __restrict__ out, int cols, int ld, int64_t total) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int c = (int)(i % ld); const int64_t r = i / ld;
+    out[i] = c < cols ? w[r * cols + c] : 0.0f;
+  }
+}
 // dx[n][c][h][w] += sum over the (r,s) taps that reach (h,w): gather form of unfoldedAcc (TensorDslCPU.scala:647-692).
 // One block row per (n, c) plane; the tap loops run over at most R*S entries of the unfolded gradient.
 // STRIDE 1 and 2 avoid the per-tap division and remainder (0 = any stride).
@@ -674,6 +682,19 @@ static int tap_matrices(const float* w, const ConvDims& d, int by_c, float** out
   LTB_LAUNCH(permute_taps_kernel, grid_for((int64_t)n, 256), 256, 0, w, *out, d.K, d.C, d.R * d.S, by_c, (int64_t)n);
   return LTB_OK;
 }
+// w[rows][cols] with rows of ld floats: the tensor itself when ld == cols, else a zero-padded copy in a staging block
+// (*out stays null when the arena has no room for it).
+static int padded_filter(const float* w, int rows, int cols, int ld, const float** out, float** temp, size_t* floats) {
+  *temp = nullptr; *floats = 0; *out = w;
+  if (ld == cols) return LTB_OK;
+  const size_t n = (size_t)rows * ld;
+  float* buf = temp_alloc(n);
+  *out = buf;
+  if (!buf) return LTB_OK;
+  *temp = buf; *floats = n;
+  LTB_LAUNCH(pad_rows_kernel, grid_for((int64_t)n, 256), 256, 0, w, buf, cols, ld, (int64_t)n);
+  return LTB_OK;
+}
 // Each returns 1 when it took the problem, 0 when not eligible (the unfolding path then runs), negative on error.
 static int conv_fwd_taps(const float* x, const float* w, const float* bias, float* y, const ConvDims& d) {
   TcConvGeom gm; TcPlan p;
@@ -742,22 +763,27 @@ int conv_fwd_tc(const float* x, const float* w, const float* bias, float* y, con
   const int ck = d.C * d.R * d.S, pix = d.oH * d.oW;
   TcPlan p;
   const bool rows = tc_conv_needs_rows(pix);
-  if (!tc_plan_conv_fwd(p, y /* any aligned pointer: eligibility only */, rows, w, bias, y, d.N, ck, d.K, pix, g.sm_count)) return 0;
+  const int ldw = (ck + 3) / 4 * 4;                                        // K-major filter rows must be a multiple of 16 bytes
+  if (!tc_plan_conv_fwd(p, y /* any aligned pointer: eligibility only */, rows, y, ldw, bias, y, d.N, ck, d.K, pix, g.sm_count)) return 0;
   { int t = conv_fwd_taps(x, w, bias, y, d); if (t != 0) return t; }      // the tap-loop form when the shape allows it
   const float* op; bool r2; float* temp; size_t tn;
   int rc = stage_activation(x, !is_pointwise(d), d, ck, pix, &op, &r2, &temp, &tn);
   if (rc) return rc < 0 ? rc : 0;
-  if (!tc_plan_conv_fwd(p, op, rows, w, bias, y, d.N, ck, d.K, pix, g.sm_count)) { if (temp) temp_free(temp, tn); return 0; }
-  rc = launch_plan(p, "tc_gemm_kernel[conv_fwd]");
+  float* wtemp; size_t wn; const float* wp;
+  rc = padded_filter(w, d.K, ck, ldw, &wp, &wtemp, &wn);
+  const bool ok = !rc && wp && tc_plan_conv_fwd(p, op, rows, wp, ldw, bias, y, d.N, ck, d.K, pix, g.sm_count);
+  if (ok) rc = launch_plan(p, "tc_gemm_kernel[conv_fwd]");
+  if (wtemp) temp_free(wtemp, wn);
   if (temp) temp_free(temp, tn);
-  return rc ? rc : 1;
+  return rc ? rc : (ok ? 1 : 0);
 }
 
 int conv_dgrad_tc(const float* dy, const float* w, float* dx, const ConvDims& d) {
   const int ck = d.C * d.R * d.S, pix = d.oH * d.oW;
   TcPlan p;
   const bool rows = tc_conv_needs_rows(pix), direct = is_pointwise(d);
-  if (!tc_plan_conv_dgrad(p, dx, rows, w, dx, d.N, ck, d.K, pix, direct, g.sm_count)) return 0;
+  const int ldw = (ck + 31) / 32 * 32;                                     // N-major filter rows must be whole 128-byte chunks
+  if (!tc_plan_conv_dgrad(p, dx, rows, dx, ldw, dx, d.N, ck, d.K, pix, direct, g.sm_count)) return 0;
   { int t = conv_dgrad_taps(dy, w, dx, d); if (t != 0) return t; }
   { int t = conv_dgrad_taps_up2(dy, w, dx, d); if (t != 0) return t; }
   const float* op; bool r2; float* temp; size_t tn;
@@ -766,12 +792,15 @@ int conv_dgrad_tc(const float* dy, const float* w, float* dx, const ConvDims& d)
   if (rc) return rc < 0 ? rc : 0;
   float* col = nullptr; const size_t ncol = (size_t)d.N * ck * pix;
   if (!direct) { col = temp_alloc(ncol); if (!col) { if (temp) temp_free(temp, tn); return 0; } }
-  bool ok = tc_plan_conv_dgrad(p, op, rows, w, direct ? dx : col, d.N, ck, d.K, pix, direct, g.sm_count);
-  rc = ok ? launch_plan(p, "tc_gemm_kernel[conv_dgrad]") : 0;
+  float* wtemp; size_t wn; const float* wp;
+  rc = padded_filter(w, d.K, ck, ldw, &wp, &wtemp, &wn);
+  bool ok = !rc && wp && tc_plan_conv_dgrad(p, op, rows, wp, ldw, direct ? dx : col, d.N, ck, d.K, pix, direct, g.sm_count);
+  if (ok) rc = launch_plan(p, "tc_gemm_kernel[conv_dgrad]");
   if (ok && !rc && !direct) rc = launch_fold(col, dx, d);
+  if (wtemp) temp_free(wtemp, wn);
   if (col) temp_free(col, ncol);
   if (temp) temp_free(temp, tn);
-  return !ok ? 0 : (rc ? rc : 1);
+  return rc ? rc : (ok ? 1 : 0);
 }
 
 int conv_wgrad_tc(const float* x, const float* dy, float* dw, const ConvDims& d) {

@@ -260,28 +260,28 @@ bool tc_walk_of(const TcOperand& o, TcWalk& w) {
 
 bool tc_conv_needs_rows(int pix) { return !(pix >= 32 && pix % 32 == 0 && (pix >= kTileM ? pix % kTileM == 0 : kTileM % pix == 0)); }
 
-bool tc_plan_conv_fwd(TcPlan& p, const float* x, bool a_rows, const float* w, const float* bias, float* y, int n_img, int ck, int co, int pix, int sm_count) {
+bool tc_plan_conv_fwd(TcPlan& p, const float* x, bool a_rows, const float* w, int ldw, const float* bias, float* y, int n_img, int ck, int co, int pix, int sm_count) {
   std::memset(&p, 0, sizeof p);
-  if (co < 16 || ck < 8 || (int64_t)n_img * pix > (1ll << 30)) return false;
+  if (co < 8 || ck < 8 || ldw < ck || (a_rows && ldw != ck) || (int64_t)n_img * pix > (1ll << 30)) return false;
   int ka = 0, kb = 0;
   const int M = n_img * pix;
   if (!(a_rows ? operand_k_rows(p.a, x, M, ck, kTileM, &ka) : operand_mn_pixels(p.a, x, n_img, ck, pix, &ka))) return false;
   p.bn = pick_bn(co, cdiv(M, kTileM), sm_count);
-  if (!operand_k_rows(p.b, w, co, ck, p.bn, &kb) || ka != kb) return false;
+  if (!operand_k_rows(p.b, w, co, ldw, p.bn, &kb) || ka != kb) return false;      // columns ck..ldw of w are zero padding
   finish(p, M, co, ka, sm_count, true);             // split-K for small outputs: the launcher zeroes y first
   p.epilogue = TC_EPI_PIXEL; p.out = y; p.bias = bias; p.alpha = 1.0f; p.accumulate = 0;
   p.pix_per_img = pix; p.img_stride = (int64_t)co * pix; p.chan_stride = pix;
   return true;
 }
 
-bool tc_plan_conv_dgrad(TcPlan& p, const float* dy, bool a_rows, const float* w, float* dx, int n_img, int ck, int co, int pix, bool accumulate, int sm_count) {
+bool tc_plan_conv_dgrad(TcPlan& p, const float* dy, bool a_rows, const float* w, int ldw, float* dx, int n_img, int ck, int co, int pix, bool accumulate, int sm_count) {
   std::memset(&p, 0, sizeof p);
-  if (ck < 32 || co < 8 || (int64_t)n_img * pix > (1ll << 30)) return false;
+  if (ck < 8 || co < 8 || ldw < ck || (int64_t)n_img * pix > (1ll << 30)) return false;
   int ka = 0, kb = 0;
   const int M = n_img * pix;
   if (!(a_rows ? operand_k_rows(p.a, dy, M, co, kTileM, &ka) : operand_mn_pixels(p.a, dy, n_img, co, pix, &ka))) return false;
   p.bn = pick_bn(ck, cdiv(M, kTileM), sm_count);
-  if (!operand_mn_cols(p.b, w, co, ck, p.bn, &kb) || ka != kb) return false;
+  if (!operand_mn_cols(p.b, w, co, ldw, p.bn, &kb) || ka != kb) return false;      // w is stored with ldw (a multiple of 32) columns
   finish(p, M, ck, ka, sm_count, true);
   p.epilogue = TC_EPI_PIXEL; p.out = dx; p.bias = nullptr; p.alpha = 1.0f; p.accumulate = accumulate ? 1 : 0;
   p.pix_per_img = pix; p.img_stride = (int64_t)ck * pix; p.chan_stride = pix;
@@ -290,7 +290,7 @@ bool tc_plan_conv_dgrad(TcPlan& p, const float* dy, bool a_rows, const float* w,
 
 bool tc_plan_conv_wgrad(TcPlan& p, const float* x, const float* dy, float* dw, int n_img, int ck, int co, int pix, int sm_count) {
   std::memset(&p, 0, sizeof p);
-  if (co < 16 || ck < 16) return false;
+  if (co < 8 || ck < 16) return false;
   int ka = 0, kb = 0;
   if (!operand_k_pixels(p.a, dy, n_img, co, pix, kTileM, &ka)) return false;
   p.bn = pick_bn(ck, cdiv(co, kTileM), sm_count);     // narrower tiles before more split-K: fewer atomic partial sums

@@ -71,7 +71,8 @@ struct TcPlan {
 };
 
 // "Flat" convolution view: activations X[n][k][p] with p contiguous (k = channels, or channels*kh*kw after unfolding),
-// weights W[co][k] row-major, outputs Y[n][co][p].  P is the number of pixels per image.
+// weights W[co][k] row-major with ldw >= k floats per row (zeros beyond k: the caller pads a copy when the engine needs a
+// wider row -- forward: ldw a multiple of 4, dgrad: a multiple of 32), outputs Y[n][co][p].  P is the number of pixels per image.
 //   forward : Y[n][co][p]  = sum_k  W[co][k] X[n][k][p] (+ bias[co])         D = pixels x co
 //   dgrad   : dX[n][k][p] (+)= sum_co W[co][k] dY[n][co][p]                   D = pixels x k
 //   wgrad   : dW[co][k]  += sum_{n,p} dY[n][co][p] X[n][k][p]                 D = co x k
@@ -79,8 +80,8 @@ struct TcPlan {
 // a_rows: the activation operand (x for forward, dy for dgrad) is given as a K-major row matrix [n_img*pix][channels]
 // instead of [n_img][channels][pix]; tc_conv_needs_rows says when that form is required.
 bool tc_conv_needs_rows(int pix);
-bool tc_plan_conv_fwd(TcPlan& p, const float* x, bool a_rows, const float* w, const float* bias, float* y, int n_img, int ck, int co, int pix, int sm_count);
-bool tc_plan_conv_dgrad(TcPlan& p, const float* dy, bool a_rows, const float* w, float* dx, int n_img, int ck, int co, int pix, bool accumulate, int sm_count);
+bool tc_plan_conv_fwd(TcPlan& p, const float* x, bool a_rows, const float* w, int ldw, const float* bias, float* y, int n_img, int ck, int co, int pix, int sm_count);
+bool tc_plan_conv_dgrad(TcPlan& p, const float* dy, bool a_rows, const float* w, int ldw, float* dx, int n_img, int ck, int co, int pix, bool accumulate, int sm_count);
 bool tc_plan_conv_wgrad(TcPlan& p, const float* x, const float* dy, float* dw, int n_img, int ck, int co, int pix, int sm_count);
 // Implicit ("tap loop") forms for R x S convolutions with stride 1.  The activations are channels-last copies
 // xr[n][h][w][c] and dyr[n][oh][ow][k] (made by a transposing copy); a TMA box then is a window of whole image rows

@@ -518,7 +518,8 @@ int HOST_FN(model_set_table)(void* m, const float* host, int rows) {
 }
 int64_t HOST_FN(model_label_count)(void* m) { return ((Model*)m)->label_count; }
 // A recorded step can only be replayed when every step issues the same operations: not so for one tree per step.
-int HOST_FN(model_use_graph)(void* m, int on) { Model* M = (Model*)m; M->use_graph = on != 0 && M->name != "treelstm"; return 0; }
+// Nor when a step touches the host: the MNIST program draws its dropout mask from rand() every step.
+int HOST_FN(model_use_graph)(void* m, int on) { Model* M = (Model*)m; M->use_graph = on != 0 && M->name != "treelstm" && M->name != "mnist"; return 0; }
 // Keep one batch resident in device memory; later steps read it there and upload nothing (x_host/y_host are ignored).
 int HOST_FN(model_set_resident)(void* m, const float* x_host, const int32_t* y_host) {
   Model* M = (Model*)m;

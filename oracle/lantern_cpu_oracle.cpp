@@ -65,12 +65,19 @@ bool tc_gemm_taken(bool a_kmajor, bool b_kmajor, int M, int N, int K) {
   if (g.math != LTB_MATH_TF32) return false;
   ltb::TcPlan p; return ltb::tc_plan_gemm(p, tc_dummy, a_kmajor, tc_dummy, b_kmajor, tc_dummy, M, N, K, 1.0f, false, 148);
 }
-// kind 0 forward, 1 data-grad, 2 weight-grad
-bool tc_conv_taken(int kind, int n_img, int ck, int co, int pix) {
+// kind 0 forward, 1 data-grad, 2 weight-grad.  full_image: the filter covers the whole unpadded image (one output pixel),
+// which the product computes as a matrix product over (channel, row, column).
+bool tc_conv_taken(int kind, int n_img, int ck, int co, int pix, bool full_image) {
   if (g.math != LTB_MATH_TF32) return false;
+  if (full_image) {
+    if (kind == 0) return tc_gemm_taken(true, true, n_img, co, ck);       // y[N][K] = x[N][CHW] w[K][CHW]^T
+    if (kind == 1) return tc_gemm_taken(true, false, n_img, ck, co);      // dx[N][CHW] += dy[N][K] w[K][CHW]
+    return tc_gemm_taken(false, false, co, ck, n_img);                    // dw[K][CHW] += dy^T[K][N] x[N][CHW]
+  }
   ltb::TcPlan p; const bool rows = ltb::tc_conv_needs_rows(pix);
-  if (kind == 0) return ltb::tc_plan_conv_fwd(p, tc_dummy, rows, tc_dummy, nullptr, tc_dummy, n_img, ck, co, pix, 148);
-  if (kind == 1) return ltb::tc_plan_conv_dgrad(p, tc_dummy, rows, tc_dummy, tc_dummy, n_img, ck, co, pix, true, 148);
+  // the product pads filter rows to 4 floats (forward) or 32 (data-grad) in a staging copy when they are not
+  if (kind == 0) return ltb::tc_plan_conv_fwd(p, tc_dummy, rows, tc_dummy, (ck + 3) / 4 * 4, nullptr, tc_dummy, n_img, ck, co, pix, 148);
+  if (kind == 1) return ltb::tc_plan_conv_dgrad(p, tc_dummy, rows, tc_dummy, (ck + 31) / 32 * 32, tc_dummy, n_img, ck, co, pix, true, 148);
   return ltb::tc_plan_conv_wgrad(p, tc_dummy, tc_dummy, tc_dummy, n_img, ck, co, pix, 148);
 }
 
@@ -363,7 +370,8 @@ int ora_conv2d_fwd(const float* x, const float* w, const float* bias, float* y, 
   REQUIRE(oH > 0 && oW > 0, "conv2d_fwd: empty output");
   size_t ohw = (size_t)oH * oW;
   if (bias) ora_fill_with_bias(y, bias, N, K, (int)ohw); else memset(y, 0, sizeof(float) * N * K * ohw);
-  const bool tf = tc_conv_taken(0, N, C * R * S, K, (int)ohw);
+  const bool full_image = R == H && S == W && ph == 0 && pw == 0 && R * S > 1;
+  const bool tf = tc_conv_taken(0, N, C * R * S, K, (int)ohw, full_image);
   std::vector<float> wt; if (tf) { wt = truncated(w, (size_t)K * C * R * S); w = wt.data(); }
   const bool par = g.threads > 1 && N > 1;
 #pragma omp parallel for if (par) num_threads(g.threads) schedule(static)
@@ -397,9 +405,10 @@ int ora_conv2d_bwd(const float* x, float* dx, const float* w, float* dw, float* 
   int oH = (H + 2 * ph - R) / sh + 1, oW = (W + 2 * pw - S) / sw + 1;
   size_t ohw = (size_t)oH * oW;
   const int ckk = C * R * S;
+  const bool full_image = R == H && S == W && ph == 0 && pw == 0 && R * S > 1;
   const float* w_full = w;
   if (dx) {
-    const bool tf = tc_conv_taken(1, N, ckk, K, (int)ohw);
+    const bool tf = tc_conv_taken(1, N, ckk, K, (int)ohw, full_image);
     std::vector<float> wt, dyt;
     const float* dy_d = dy;
     if (tf) { wt = truncated(w, (size_t)K * ckk); w = wt.data(); dyt = truncated(dy, (size_t)N * K * ohw); dy_d = dyt.data(); }
@@ -424,7 +433,7 @@ int ora_conv2d_bwd(const float* x, float* dx, const float* w, float* dw, float* 
   w = w_full;
   if (dw) {
     // images are visited in order so that dW accumulates image by image as in the reference
-    const bool tf = tc_conv_taken(2, N, ckk, K, (int)ohw);
+    const bool tf = tc_conv_taken(2, N, ckk, K, (int)ohw, full_image);
     std::vector<float> fin((size_t)ckk * ohw), got;
     for (int t = 0; t < N; ++t) {
       unfolded_copy(fin.data(), x + (size_t)t * C * H * W, S, R, sw, sh, pw, ph, C, W, H, oW, oH);

@@ -145,8 +145,12 @@ static int conv_case(int n_img, int ck, int co, int pix) {
       for (int c = 0; c < co; ++c) dyt[((size_t)n * pix + q) * co + c] = dy[((size_t)n * co + c) * pix + q];
     }
   }
-  if (tc_plan_conv_fwd(p, rows ? xt.data() : x.data(), rows, w.data(), bias.data(), y.data(), n_img, ck, co, pix, 148)) { ++taken; if (!run_plan(p, y.size()) || !close(yr, y, "fwd")) return -1; }
-  if (tc_plan_conv_dgrad(p, rows ? dyt.data() : dy.data(), rows, w.data(), dx.data(), n_img, ck, co, pix, true, 148)) { ++taken; if (!run_plan(p, dx.size()) || !close(dxr, dx, "dgrad")) return -1; }
+  // filter rows padded with zeros the way the library stages them: to 4 floats for forward, to 32 for data-grad
+  auto padded = [&](int ld) { std::vector<float> o((size_t)co * ld, 0.0f); for (int c = 0; c < co; ++c) for (int k = 0; k < ck; ++k) o[(size_t)c * ld + k] = w[(size_t)c * ck + k]; return o; };
+  const int ld4 = (ck + 3) / 4 * 4, ld32 = (ck + 31) / 32 * 32;
+  const std::vector<float> w4 = padded(ld4), w32 = padded(ld32);
+  if (tc_plan_conv_fwd(p, rows ? xt.data() : x.data(), rows, w4.data(), ld4, bias.data(), y.data(), n_img, ck, co, pix, 148)) { ++taken; if (!run_plan(p, y.size()) || !close(yr, y, "fwd")) return -1; }
+  if (tc_plan_conv_dgrad(p, rows ? dyt.data() : dy.data(), rows, w32.data(), ld32, dx.data(), n_img, ck, co, pix, true, 148)) { ++taken; if (!run_plan(p, dx.size()) || !close(dxr, dx, "dgrad")) return -1; }
   if (tc_plan_conv_wgrad(p, x.data(), dy.data(), dw.data(), n_img, ck, co, pix, 148)) { ++taken; if (!run_plan(p, dw.size()) || !close(dwr, dw, "wgrad")) return -1; }
   printf("conv n=%d ck=%d co=%d pix=%d: %d of 3 plans taken, all match\n", n_img, ck, co, pix, taken);
   return taken;
@@ -204,7 +208,9 @@ static int gemm_case(int M, int N, int K, bool ak, bool bk, bool acc) {
 int main() {
   int bad = 0, taken = 0;
   const int convs[][4] = {{2, 64, 64, 256}, {3, 64, 256, 256}, {4, 128, 96, 64}, {5, 256, 128, 64}, {11, 256, 128, 16}, {35, 512, 64, 4}, {1, 32, 48, 1024},
-                          {8, 576, 64, 256}, {2, 40, 64, 32}, {3, 64, 64, 36}, {2, 2048, 512, 4}, {9, 1024, 256, 16}, {70, 512, 32, 1}};
+                          {8, 576, 64, 256}, {2, 40, 64, 32}, {3, 64, 64, 36}, {2, 2048, 512, 4}, {9, 1024, 256, 16}, {70, 512, 32, 1},
+                          // filter rows that need padding (3x3 over 3, 16 and 48 channels; 1x1 over 16 and 48) and few output channels
+                          {2, 27, 96, 1024}, {3, 144, 64, 256}, {4, 16, 64, 256}, {2, 48, 192, 64}, {2, 432, 192, 64}, {3, 128, 12, 64}, {5, 48, 192, 16}};
   for (auto& c : convs) { int r = conv_case(c[0], c[1], c[2], c[3]); if (r < 0) ++bad; else taken += r; }
   const int taps[][9] = {{3, 64, 64, 16, 16, 3, 3, 1, 1}, {5, 128, 128, 8, 8, 3, 3, 1, 1}, {9, 64, 128, 4, 4, 3, 3, 1, 1}, {35, 64, 64, 2, 2, 3, 3, 1, 1},
                          {1, 32, 64, 32, 32, 3, 3, 1, 1}, {2, 64, 32, 16, 16, 3, 3, 0, 0}, {2, 64, 64, 8, 8, 5, 5, 2, 2}, {3, 96, 64, 8, 8, 1, 3, 0, 1},

@@ -166,7 +166,9 @@ def test_avgpool(ora, gpu, cfg):
 
 
 @pytest.mark.parametrize("cfg", [(3, 2, 3, 3), (16, 64, 16, 16), (8, 256, 4, 4), (32, 512, 2, 2), (5, 7, 3, 5), (128, 10, 1, 1),
-                                 (128, 64, 32, 32), (64, 128, 8, 8), (128, 3, 16, 16), (7, 300, 2, 6)])
+                                 (128, 64, 32, 32), (64, 128, 8, 8), (128, 3, 16, 16), (7, 300, 2, 6),
+                                 # several channels per CTA (no cluster): row widths 64 / 128 / 512, an idle last row, 12-byte rows
+                                 (128, 2048, 2, 2), (128, 1024, 4, 4), (128, 512, 8, 8), (5, 301, 2, 2), (96, 330, 4, 4)])
 def test_batchnorm_train_fwd_bwd(ora, gpu, cfg):
     N, C, H, W = cfg
     v = (R(1).standard_normal((N, C, H, W)) * 2 + 3).astype(np.float32)      # non-zero mean: exercises the shifted sums
@@ -333,7 +335,11 @@ TC_CONVS = [  # N, C, H, W, K, R, stride, pad: the ResNet-50 / SqueezeNet layer 
     (112, 64, 16, 16, 64, 3, 1, 1), (30, 64, 32, 32, 64, 3, 1, 1),
     # small images whose count fills whole 128-byte rows: fed M/N-major straight from NCHW (no transposing copy)
     (8, 256, 4, 4, 1024, 1, 1, 0), (16, 512, 2, 2, 2048, 1, 1, 0), (8, 1024, 4, 4, 256, 1, 1, 0), (40, 64, 2, 2, 64, 1, 1, 0),
-    (8, 256, 8, 8, 256, 3, 2, 1), (16, 512, 4, 4, 512, 3, 2, 1), (8, 512, 8, 8, 1024, 1, 2, 0)]
+    (8, 256, 8, 8, 256, 3, 2, 1), (16, 512, 4, 4, 512, 3, 2, 1), (8, 512, 8, 8, 1024, 1, 2, 0),
+    # filter rows that the engine needs padded (3x3 over 3 / 16 / 48 channels, 1x1 over 16 / 48), the stems of ResNet-50 and
+    # SqueezeNet, and a filter that covers the whole image (SqueezeNet's classifier: a matrix product)
+    (4, 3, 32, 32, 64, 3, 1, 1), (3, 3, 32, 32, 96, 3, 1, 1), (4, 16, 16, 16, 64, 1, 1, 0), (5, 48, 8, 8, 192, 3, 1, 1),
+    (64, 512, 4, 4, 10, 4, 1, 0), (6, 16, 16, 16, 64, 3, 1, 1), (7, 20, 8, 8, 40, 1, 1, 0)]
 
 
 @pytest.mark.parametrize("cfg", TC_CONVS, ids=[str(c) for c in TC_CONVS])
