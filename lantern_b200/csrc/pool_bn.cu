@@ -577,7 +577,7 @@ int bn_fwd_issue(const Pending& p, bool relu) {
   const BnClusterPlan c = bn_cluster_plan(p.N, p.C, p.HW);
   const int r = relu ? 1 : 0;
   BnPackedPlan pk;
-  if (c.K == 1 && bn_packed_plan(p.N, p.C, p.HW, kBnVpt, pk)) {
+  if ((c.K == 1 || p.C >= 96) && bn_packed_plan(p.N, p.C, p.HW, kBnVpt, pk)) {
     LTB_LAUNCH(bn_fwd_packed_kernel<kBnVpt>, (unsigned)ceil_div(p.C, pk.G), dim3(pk.T, pk.G), 0, p.x, p.y, p.gamma, p.beta, p.run_mean, p.run_var,
                p.save_mean, p.save_istd, p.N, p.C, p.HW, p.eps, p.momentum, r);
     return LTB_OK;
@@ -674,7 +674,7 @@ int ltb_bn_bwd(const float* x, float* dx, const float* dy, const float* gamma, f
     const BnClusterPlan p = bn_cluster_plan(N, C, HW);
     float* dyw = const_cast<float*>(dy);                           // written only when the held ReLU gradient is applied to it
     BnPackedPlan pk;
-    if (p.K == 1 && bn_packed_plan(N, C, HW, kBnVptBwd, pk)) {
+    if ((p.K == 1 || C >= 96) && bn_packed_plan(N, C, HW, kBnVptBwd, pk)) {
       LTB_LAUNCH(bn_bwd_packed_kernel<kBnVptBwd>, (unsigned)ceil_div(C, pk.G), dim3(pk.T, pk.G), 0, x, dyw, dx, gamma, dgamma, dbeta,
                  save_mean, save_istd, N, C, HW, mask_y);
       return LTB_OK;
