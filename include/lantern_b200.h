@@ -107,6 +107,22 @@ int   LTB_FN(d2h_async)(void* dst_pinned, const void* src, size_t bytes);
 int   LTB_FN(marker_record)(int slot);
 int   LTB_FN(marker_wait)(int slot);
 
+/* Branch regions (no counterpart in the reference, whose generated programs issue everything on one stream): two runs of
+ * calls that do not depend on each other -- the shortcut convolution of a residual block and its main path, the two
+ * expand convolutions of a fire module -- may overlap on the device.
+ *   ltb_branch_mark()   remembers the current point of the stream (both runs may read what was issued before it);
+ *   ltb_branch_begin()  the calls that follow are issued on a second stream that starts from the marked point;
+ *   ltb_branch_end()    back to the first stream;
+ *   ltb_branch_join()   the first stream waits for the branch: from here on its results may be used.
+ * Calls issued between mark and begin belong to the first run.  The caller guarantees that the branch and the calls issued
+ * on the first stream between mark and join touch no common buffer other than read-only inputs (gradients ACCUMULATE into
+ * their destinations, so two runs that end in the same gradient buffer must be separated by the join).  One region at a
+ * time; not nested.  Staging memory taken inside a region is returned by the next ltb_reset, not at the end of its call. */
+int   LTB_FN(branch_mark)(void);
+int   LTB_FN(branch_begin)(void);
+int   LTB_FN(branch_end)(void);
+int   LTB_FN(branch_join)(void);
+
 /* Whole-step replay. Shapes are static and the bump arena hands out the same addresses every iteration after
  * ltb_reset, so one training step can be recorded once and replayed: graph_begin starts recording the calls
  * that follow on the library's stream, graph_end returns a handle, graph_launch replays it.  Calls that

@@ -59,6 +59,13 @@ struct Context {
   bool fusion = false;                // look-ahead fusion of BN/add with ReLU (off unless the host opts in)
   Pending pending;
   bool hold_workspace = false;        // while two halves are in flight their staging blocks are released together at the end
+  // Branch region (ltb_branch_mark .. ltb_branch_join): a run of calls issued on a third stream beside the caller's.
+  cudaStream_t branch = nullptr, trunk = nullptr;
+  cudaEvent_t mark_ev = nullptr, branch_done_ev = nullptr;
+  bool branch_marked = false, in_branch = false, branch_ended = false;
+  // Private workspace of the calling side: while a branch region is open the two streams each get one half.
+  float* cur_scratch() const { return in_branch ? scratch + (scratch_bytes / 2) / sizeof(float) : scratch; }
+  size_t cur_scratch_bytes() const { return branch_marked ? scratch_bytes / 2 : scratch_bytes; }
 };
 extern Context g;
 

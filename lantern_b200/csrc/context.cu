@@ -79,6 +79,9 @@ int ltb_init(int device, size_t heap_bytes) {
   LTB_CUDA(cudaStreamCreateWithFlags(&g.side, cudaStreamNonBlocking));
   LTB_CUDA(cudaEventCreateWithFlags(&g.fork_ev, cudaEventDisableTiming));
   LTB_CUDA(cudaEventCreateWithFlags(&g.join_ev, cudaEventDisableTiming));
+  LTB_CUDA(cudaStreamCreateWithFlags(&g.branch, cudaStreamNonBlocking));
+  LTB_CUDA(cudaEventCreateWithFlags(&g.mark_ev, cudaEventDisableTiming));
+  LTB_CUDA(cudaEventCreateWithFlags(&g.branch_done_ev, cudaEventDisableTiming));
   g.launches = 0; g.last = 0; g.msg.clear(); g.capturing = false; g.math = LTB_MATH_TF32;
   g.inited = true;
   return LTB_OK;
@@ -96,6 +99,8 @@ int ltb_shutdown(void) {
   ltb_comm_destroy();
   cudaStreamSynchronize(g.stream);
   cudaStreamSynchronize(g.side);
+  cudaStreamSynchronize(g.branch);
+  cudaStreamDestroy(g.branch); cudaEventDestroy(g.mark_ev); cudaEventDestroy(g.branch_done_ev);
   cudaFree(g.heap); cudaFree(g.dev_status); cudaFree(g.scratch); cudaFreeHost(g.host_status);
   cudaStreamDestroy(g.side); cudaEventDestroy(g.fork_ev); cudaEventDestroy(g.join_ev);
   for (int i = 0; i < 16; ++i) { if (marker_ev[i]) cudaEventDestroy(marker_ev[i]); marker_ev[i] = nullptr; marker_set[i] = false; }
@@ -153,6 +158,7 @@ int ltb_reset(void* mark) {
   LTB_INITED();
   char* m = (char*)mark;
   LTB_REQUIRE(m >= g.heap && m <= g.heap + g.used, "ltb_reset: mark outside the used span");
+  LTB_REQUIRE(!g.branch_marked, "ltb_reset: a branch region is open (ltb_branch_join missing)");
   g.used = (size_t)(m - g.heap);   // zeroing happens when a block is handed out again by ltb_malloc
   return LTB_OK;
 }
@@ -198,6 +204,44 @@ int ltb_marker_record(int slot) {
 int ltb_marker_wait(int slot) {
   LTB_INITED_NOFLUSH(); LTB_REQUIRE(slot >= 0 && slot < 16, "ltb_marker_wait: slot %d out of range", slot);
   if (marker_set[slot]) LTB_CUDA(cudaEventSynchronize(marker_ev[slot]));
+  return LTB_OK;
+}
+
+// ------------------------------------------------------------------ branch regions
+// mark: remember this point of the caller's stream.  begin: the calls that follow run on the branch stream, which starts
+// from the marked point.  end: back to the caller's stream.  join: the caller's stream waits for the branch.  Between mark
+// and join staging blocks are not handed back (a block released by one side could be overwritten by the other side's next
+// call while a kernel still reads it); they return with the next ltb_reset.  While the launch profiler is on the four
+// calls do nothing, so that every kernel is timed alone.
+int ltb_branch_mark(void) {
+  LTB_INITED();
+  if (g.profiling) return LTB_OK;
+  LTB_REQUIRE(!g.branch_marked, "ltb_branch_mark: a branch region is already open");
+  LTB_CUDA(cudaEventRecord(g.mark_ev, g.stream));
+  g.branch_marked = true; g.branch_ended = false;
+  return LTB_OK;
+}
+int ltb_branch_begin(void) {
+  LTB_INITED();
+  if (g.profiling && !g.branch_marked) return LTB_OK;
+  LTB_REQUIRE(g.branch_marked && !g.in_branch && !g.branch_ended, "ltb_branch_begin: needs ltb_branch_mark first, once per region");
+  LTB_CUDA(cudaStreamWaitEvent(g.branch, g.mark_ev, 0));
+  g.trunk = g.stream; g.stream = g.branch; g.in_branch = true;
+  return LTB_OK;
+}
+int ltb_branch_end(void) {
+  LTB_INITED();
+  if (!g.in_branch) { LTB_REQUIRE(g.profiling, "ltb_branch_end: no branch is running"); return LTB_OK; }
+  LTB_CUDA(cudaEventRecord(g.branch_done_ev, g.branch));
+  g.stream = g.trunk; g.in_branch = false; g.branch_ended = true;
+  return LTB_OK;
+}
+int ltb_branch_join(void) {
+  LTB_INITED();
+  if (!g.branch_marked) { LTB_REQUIRE(g.profiling, "ltb_branch_join: no branch region is open"); return LTB_OK; }
+  LTB_REQUIRE(!g.in_branch, "ltb_branch_join: the branch has not ended");
+  if (g.branch_ended) LTB_CUDA(cudaStreamWaitEvent(g.stream, g.branch_done_ev, 0));
+  g.branch_marked = g.branch_ended = false;
   return LTB_OK;
 }
 

@@ -120,7 +120,7 @@ int ltb_conv2d_bwd(const float* x, float* dx, const float* w, float* dw, float* 
   }
   if (overlap) {                                   // join, also on the error path: nothing may stay forked
     g.hold_workspace = false;
-    g.used = arena_base;
+    if (!g.branch_marked) g.used = arena_base;
     cudaError_t e1 = cudaEventRecord(g.join_ev, g.side);
     cudaError_t e2 = cudaStreamWaitEvent(main_stream, g.join_ev, 0);
     if (rc == LTB_OK && (e1 != cudaSuccess || e2 != cudaSuccess)) return fail(LTB_E_CUDA, "ltb_conv2d_bwd: joining the side stream failed");

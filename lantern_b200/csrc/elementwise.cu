@@ -503,15 +503,15 @@ int ltb_sgd_step(float* x, float* d, float lr, int64_t n) {
 int ltb_sgd_step_multi(float* const* xs, float* const* ds, const int64_t* sizes, int nt, float lr) {
   LTB_INITED(); LTB_REQUIRE(xs && ds && sizes && nt >= 0, "ltb_sgd_step_multi: bad argument");
   if (!nt) return LTB_OK;
-  LTB_REQUIRE((size_t)nt * sizeof(SgdChunk) <= g.scratch_bytes, "ltb_sgd_step_multi: too many tensors");
+  LTB_REQUIRE((size_t)nt * sizeof(SgdChunk) <= g.cur_scratch_bytes(), "ltb_sgd_step_multi: too many tensors");
   LTB_REQUIRE(!g.capturing, "ltb_sgd_step_multi: uploads its tensor list; use ltb_sgd_step on a slab while recording");
   std::vector<SgdChunk> h(nt);
   int64_t mx = 0;
   for (int i = 0; i < nt; ++i) { h[i] = {xs[i], ds[i], sizes[i]}; if (sizes[i] > mx) mx = sizes[i]; }
-  LTB_CUDA(cudaMemcpyAsync(g.scratch, h.data(), nt * sizeof(SgdChunk), cudaMemcpyHostToDevice, g.stream));
+  LTB_CUDA(cudaMemcpyAsync(g.cur_scratch(), h.data(), nt * sizeof(SgdChunk), cudaMemcpyHostToDevice, g.stream));
   LTB_CUDA(cudaStreamSynchronize(g.stream));
   int gx = (int)(ceil_div(mx, 256) < 64 ? ceil_div(mx, 256) : 64);
-  LTB_LAUNCH(sgd_multi_kernel, dim3(gx < 1 ? 1 : gx, nt), 256, 0, (const SgdChunk*)g.scratch, lr);
+  LTB_LAUNCH(sgd_multi_kernel, dim3(gx < 1 ? 1 : gx, nt), 256, 0, (const SgdChunk*)g.cur_scratch(), lr);
   return LTB_OK;
 }
 int ltb_adagrad_update(float* x, float* d, float* h, float lr, float clip, int descent, int64_t n) {

@@ -626,7 +626,8 @@ static int launch_fold(const float* col, float* dx, const ConvDims& d) {
 static bool is_pointwise(const ConvDims& d) { return d.R == 1 && d.S == 1 && d.sh == 1 && d.sw == 1 && d.ph == 0 && d.pw == 0; }
 // Staging blocks go back to the arena (a LIFO pop, host arithmetic only) unless the caller holds them: conv backward runs
 // its two halves on two streams and pops both halves' blocks together once both are issued.
-static void temp_free(float* p, size_t floats) { if (!g.hold_workspace) ltb_free(p, floats * 4); }
+// Nor inside a branch region (ltb_branch_mark .. ltb_branch_join): the other stream's next call would reuse the block.
+static void temp_free(float* p, size_t floats) { if (!g.hold_workspace && !g.branch_marked) ltb_free(p, floats * 4); }
 static float* temp_alloc(size_t floats) {
   size_t bytes = (floats * 4 + kGranule - 1) / kGranule * kGranule;
   if (g.used + bytes > g.heap_bytes) return nullptr;          // no room for the staging buffer: let the FP32 path run

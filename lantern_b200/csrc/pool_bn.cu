@@ -639,7 +639,7 @@ int ltb_bn_train_fwd(const float* x, float* y, const float* gamma, const float* 
   LTB_INITED();
   LTB_REQUIRE(x && y && gamma && beta && save_mean && save_istd && N > 0 && C > 0 && HW > 0, "ltb_bn_train_fwd: bad argument");
   int S = bn_splits(N, C);
-  LTB_REQUIRE((size_t)C * S * 2 * 4 <= g.scratch_bytes, "ltb_bn_train_fwd: too many channels");
+  LTB_REQUIRE((size_t)C * S * 2 * 4 <= g.cur_scratch_bytes(), "ltb_bn_train_fwd: too many channels");
   int64_t n = (int64_t)N * C * HW;
   bool vec = (HW & 3) == 0 && aligned16(x) && aligned16(y);
   if (vec && (int64_t)N * (HW >> 2) < ((int64_t)1 << 30)) {      // one cluster launch: statistics and result in the same kernel
@@ -649,8 +649,8 @@ int ltb_bn_train_fwd(const float* x, float* y, const float* gamma, const float* 
     if (g.fusion) { g.pending = p; return LTB_OK; }              // held for one call: an in-place ReLU of y may join it
     return bn_fwd_issue(p, false);
   }
-  LTB_LAUNCH(bn_reduce_kernel<0>, dim3(C, S), 256, 0, x, nullptr, nullptr, nullptr, g.scratch, N, C, HW);
-  LTB_LAUNCH(bn_fwd_finalize_kernel, (C + 127) / 128, 128, 0, x, (const float*)g.scratch, S, C, HW, (double)N * HW, eps, momentum,
+  LTB_LAUNCH(bn_reduce_kernel<0>, dim3(C, S), 256, 0, x, nullptr, nullptr, nullptr, g.cur_scratch(), N, C, HW);
+  LTB_LAUNCH(bn_fwd_finalize_kernel, (C + 127) / 128, 128, 0, x, (const float*)g.cur_scratch(), S, C, HW, (double)N * HW, eps, momentum,
              save_mean, save_istd, run_mean, run_var);
   LTB_LAUNCH(bn_apply_kernel, grid_for(vec ? n / 4 : n, 256), 256, 0, x, y, (const float*)save_mean, (const float*)save_istd, gamma, beta, C, HW, n, vec);
   return LTB_OK;
@@ -660,8 +660,8 @@ int ltb_bn_bwd(const float* x, float* dx, const float* dy, const float* gamma, f
   LTB_INITED_NOFLUSH();
   LTB_REQUIRE(x && dy && gamma && save_mean && save_istd && N > 0 && C > 0 && HW > 0, "ltb_bn_bwd: bad argument");
   int S = bn_splits(N, C);
-  LTB_REQUIRE((size_t)C * (S * 2 + 3) * 4 <= g.scratch_bytes, "ltb_bn_bwd: too many channels");
-  float* coef = g.scratch + (size_t)C * S * 2;
+  LTB_REQUIRE((size_t)C * (S * 2 + 3) * 4 <= g.cur_scratch_bytes(), "ltb_bn_bwd: too many channels");
+  float* coef = g.cur_scratch() + (size_t)C * S * 2;
   int64_t n = (int64_t)N * C * HW;
   bool vec = (HW & 3) == 0 && aligned16(x) && aligned16(dy) && aligned16(dx);
   const bool cluster_path = vec && (int64_t)N * (HW >> 2) < ((int64_t)1 << 30);
@@ -687,8 +687,8 @@ int ltb_bn_bwd(const float* x, float* dx, const float* dy, const float* gamma, f
                          save_mean, save_istd, N, C, HW, p.per_cta, mask_y);
     return LTB_OK;
   }
-  LTB_LAUNCH(bn_reduce_kernel<1>, dim3(C, S), 256, 0, x, dy, save_mean, save_istd, g.scratch, N, C, HW);
-  LTB_LAUNCH(bn_bwd_finalize_kernel, (C + 127) / 128, 128, 0, (const float*)g.scratch, S, C, (double)N * HW, gamma, save_istd, dgamma, dbeta, coef);
+  LTB_LAUNCH(bn_reduce_kernel<1>, dim3(C, S), 256, 0, x, dy, save_mean, save_istd, g.cur_scratch(), N, C, HW);
+  LTB_LAUNCH(bn_bwd_finalize_kernel, (C + 127) / 128, 128, 0, (const float*)g.cur_scratch(), S, C, (double)N * HW, gamma, save_istd, dgamma, dbeta, coef);
   if (dx) LTB_LAUNCH(bn_bwd_apply_kernel, grid_for(vec ? n / 4 : n, 256), 256, 0, x, dy, dx, save_mean, save_istd, (const float*)coef, C, HW, n, vec);
   return LTB_OK;
 }

@@ -143,8 +143,8 @@ __global__ void axpy_from_scalar_kernel(float* dx, const float* __restrict__ y, 
 static int full_sum(const float* x, float* out, int64_t n, float scale) {
   if (n <= (1 << 16)) { LTB_LAUNCH(sum_kernel, 1, 1024, 0, x, out, n, scale, false); return LTB_OK; }
   int blocks = grid_for(n, 1024, 2);
-  LTB_LAUNCH(sum_kernel, blocks, 1024, 0, x, g.scratch, n, 1.0f, true);
-  LTB_LAUNCH(sum_kernel, 1, 1024, 0, (const float*)g.scratch, out, (int64_t)blocks, scale, false);
+  LTB_LAUNCH(sum_kernel, blocks, 1024, 0, x, g.cur_scratch(), n, 1.0f, true);
+  LTB_LAUNCH(sum_kernel, 1, 1024, 0, (const float*)g.cur_scratch(), out, (int64_t)blocks, scale, false);
   return LTB_OK;
 }
 

@@ -21,6 +21,7 @@ _SIGS = {
     "model_label_count": (ctypes.c_int64, [ctypes.c_void_p]),
     "model_set_table": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int]),
     "model_use_graph": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int]),
+    "model_use_branches": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int]),
     "model_set_resident": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]),
     "model_step": (ctypes.c_float, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_float, ctypes.c_int]),
     "model_step_async": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_float]),
@@ -180,6 +181,10 @@ class Model:
         rc = self.hp.fn["model_set_table"](self.h, t.ctypes.data, t.shape[0])
         if rc:
             raise ValueError("model_set_table failed: %d" % rc)
+
+    def use_branches(self, on=True):
+        """Issue independent runs of calls (shortcut convolutions) as branch regions (default) or all in program order."""
+        self.hp.fn["model_use_branches"](self.h, int(on))
 
     def use_graph(self, on=True):
         self.hp.fn["model_use_graph"](self.h, int(on))

@@ -50,6 +50,7 @@ struct Model {
   float graph_lr = 0.f;
   size_t zero_bytes = 0;       // bytes of zero-initialised gradient buffers the last step asked for (0: not known yet)
   bool early_reduce = false;   // this step runs data-parallel with an update: finished gradient ranges are summed during backward
+  bool branches = true;        // independent runs of calls (shortcut convolutions) are issued as branch regions
   bool resident = false;       // read the batch from dev_x/dev_y instead of uploading it
   float* dev_x = nullptr; int32_t* dev_y = nullptr;
   float* dev_loss = nullptr;   // the loss of the last step, kept outside the arena span that the step resets
@@ -428,10 +429,23 @@ struct ResNet50 : Model {
       const Block& bl = blocks[bi];
       for (int k = 0; k < 3; ++k)
         if (bi == stage_start[k]) reduce_when_final(t, bl.a.w, k == 2 ? slab_count : decls[blocks[stage_start[k + 1]].a.w].offset);
-      TR o = cbn(t, h, bl.a, 1, 0, true);
+      // A block with a shortcut convolution has two runs of calls that meet only at the sum: the shortcut (conv + BN) is
+      // issued as a branch beside the three conv + BN of the main path.  Backward replays the tape in reverse, so every
+      // marker pushes its counterpart: the shortcut's gradients run as a branch from the sum's gradient on, and are joined
+      // before the gradient of the block's first convolution, which accumulates into the same input gradient.
+      const bool fork = bl.has_down && branches;
+      if (fork) BK(branch_mark)();
+      TR o = t.conv(h, P(bl.a.w), nullptr, 1, 0);
+      if (fork) t.push([] { BK(branch_join)(); });
+      o = t.relu(t.batch_norm(o, P(bl.a.gamma), P(bl.a.beta), P(bl.a.rmean).x, P(bl.a.rvar).x), true);
       o = cbn(t, o, bl.b, bl.stride, 1, true);
       o = cbn(t, o, bl.c, 1, 0, false);
-      TR res = bl.has_down ? cbn(t, h, bl.down, bl.stride, 0, false) : h;
+      TR res = h;
+      if (bl.has_down) {
+        if (fork) { BK(branch_begin)(); t.push([] { BK(branch_end)(); }); }
+        res = cbn(t, h, bl.down, bl.stride, 0, false);
+        if (fork) { BK(branch_end)(); t.push([] { BK(branch_begin)(); }); BK(branch_join)(); t.push([] { BK(branch_mark)(); }); }
+      }
       h = t.relu(t.binary(LTB_ADD, o, res), true);
     }
     TR p = t.avg_pool(h, 2, 1);
@@ -517,6 +531,12 @@ int HOST_FN(model_set_table)(void* m, const float* host, int rows) {
   return T ? T->set_table(host, rows) : LTB_E_ARG;
 }
 int64_t HOST_FN(model_label_count)(void* m) { return ((Model*)m)->label_count; }
+// Issue independent runs of calls as branch regions (default) or everything in program order on one stream.
+int HOST_FN(model_use_branches)(void* m, int on) {
+  Model* M = (Model*)m;
+  if (M->graph) { BK(graph_destroy)(M->graph); M->graph = nullptr; }
+  M->branches = on != 0; return 0;
+}
 // A recorded step can only be replayed when every step issues the same operations: not so for one tree per step.
 // Nor when a step touches the host: the MNIST program draws its dropout mask from rand() every step.
 int HOST_FN(model_use_graph)(void* m, int on) { Model* M = (Model*)m; M->use_graph = on != 0 && M->name != "treelstm" && M->name != "mnist"; return 0; }

@@ -908,6 +908,10 @@ extern "C" {
 void* ora_host_alloc(size_t bytes) { return malloc(bytes); }
 int ora_host_free(void* p) { free(p); return LTB_OK; }
 int ora_d2h_async(void* d, const void* s, size_t n) { memcpy(d, s, n); return LTB_OK; }
+int ora_branch_mark(void) { return LTB_OK; }        // one thread of control: a branch simply runs where it is issued
+int ora_branch_begin(void) { return LTB_OK; }
+int ora_branch_end(void) { return LTB_OK; }
+int ora_branch_join(void) { return LTB_OK; }
 int ora_marker_record(int) { return LTB_OK; }      // the CPU oracle runs every call to completion
 int ora_marker_wait(int) { return LTB_OK; }
 int ora_graph_begin(void) { return fail(LTB_E_ARG, "the CPU oracle does not record steps"); }

@@ -462,3 +462,105 @@ def test_empty_ragged_and_misaligned_vectors(ora, gpu, n):
         out["x"], out["d"], out["guard_x"], out["guard_d"] = full.toCPU()[1:], dfull.toCPU()[1:], full.toCPU()[:1], dfull.toCPU()[:1]
         return out
     check(f, ora, gpu)
+
+
+# ---------------------------------------------------------------------------------------------- branch regions
+@pytest.mark.parametrize("replay", [False, True])
+def test_branch_region_gives_the_results_of_program_order(gpu, replay):
+    """A residual block's two paths (conv + BN + ReLU + 3x3 conv on one, 1x1 conv + BN on the other, then the sum) and their
+    gradients, issued once in program order and once with the shortcut as a branch region on a second stream, eagerly and
+    from a recorded step: every tensor bit-identical except the weight gradients, whose split-K partial sums are added
+    atomically in any order (compared at 1e-5 of their largest element), and the arena back at its mark afterwards."""
+    N, C, H, K = 128, 64, 16, 64
+    x0 = R(1).standard_normal((N, C, H, H)).astype(np.float32)
+    w10 = (R(2).standard_normal((K, C, 1, 1)) / 8).astype(np.float32)
+    w20 = (R(3).standard_normal((K, K, 3, 3)) / 24).astype(np.float32)
+    wd0 = (R(4).standard_normal((K, C, 1, 1)) / 8).astype(np.float32)
+    dz0 = R(5).standard_normal((N, K, H, H)).astype(np.float32)
+    b, lib = gpu, gpu.lib
+
+    def run(branch):
+        mark = lib.mark()
+        x = TensorR(b.fromNumpy(x0)); x.d = b.fill(x0.shape, 0.0)
+        w1, w2, wd = TensorR(b.fromNumpy(w10)), TensorR(b.fromNumpy(w20)), TensorR(b.fromNumpy(wd0))
+        for w in (w1, w2, wd):
+            w.d = b.fill(w.x.shape, 0.0)
+        g, be = TensorR(b.fill((K,), 1.0)), TensorR(b.fill((K,), 0.0))
+        gd, bd = TensorR(b.fill((K,), 1.0)), TensorR(b.fill((K,), 0.0))
+        for t in (g, be, gd, bd):
+            t.d = b.fill((K,), 0.0)
+        rm, rv, rmd, rvd = b.fill((K,), 0.0), b.fill((K,), 1.0), b.fill((K,), 0.0), b.fill((K,), 1.0)
+        dz = b.fromNumpy(dz0)
+        lib.sync()
+        inner = lib.mark()
+        out = {}
+
+        def step():
+            if branch: lib.branch_mark()
+            a, _, _ = b.conv2D_batch(x.x, w1.x, None, (1, 1), (0, 0, 0, 0))
+            an, sm, si, _ = b.batchNormTraining(a, g.x, be.x, rm, rv)
+            ar = TensorR(b.relu(an, True)); ar.d = b.fill(an.shape, 0.0)
+            m, _, _ = b.conv2D_batch(ar.x, w2.x, None, (1, 1), (1, 1, 1, 1))
+            if branch: lib.branch_begin()
+            s, _, _ = b.conv2D_batch(x.x, wd.x, None, (1, 1), (0, 0, 0, 0))
+            sn, smd, sid, _ = b.batchNormTraining(s, gd.x, bd.x, rmd, rvd)
+            if branch: lib.branch_end(); lib.branch_join()
+            z, _, _ = b.plus(m, sn)
+            # backward: the sum's gradient reaches both paths; the shortcut's gradients run as a branch and are joined before
+            # the first convolution's gradient, which accumulates into the same x.d
+            mr, snr, sr, ac = TensorR(m, dz), TensorR(sn, dz), TensorR(s), TensorR(a)
+            sr.d, ac.d = b.fill(s.shape, 0.0), b.fill(a.shape, 0.0)
+            if branch: lib.branch_mark(); lib.branch_begin()
+            b.batchNorm_grad(sr, snr, gd, bd, smd, sid)
+            b.conv2D_batch_grad(x, None, wd, sr, None, (0, 0), (1, 1))
+            if branch: lib.branch_end()
+            b.conv2D_batch_grad(ar, None, w2, mr, None, (1, 1), (1, 1))
+            b.relu_grad(ar, ar, True)
+            b.batchNorm_grad(ac, ar, g, be, sm, si)
+            if branch: lib.branch_join()
+            b.conv2D_batch_grad(x, None, w1, ac, None, (0, 0), (1, 1))
+            out["z"] = z
+        if replay:
+            assert lib.graph_begin() == 0
+            step()
+            graph = lib.graph_end()
+            assert graph
+            lib.graph_launch(graph); lib.sync(); lib.graph_destroy(graph)
+        else:
+            step()
+        res = {"z": out["z"].toCPU(), "dx": x.d.toCPU(), "dw1": w1.d.toCPU(), "dw2": w2.d.toCPU(), "dwd": wd.d.toCPU(),
+               "dg": g.d.toCPU(), "dgd": gd.d.toCPU(), "rm": rm.toCPU(), "rvd": rvd.toCPU()}
+        lib.reset(inner)
+        assert lib.mark() == inner          # staging blocks held during the regions went back with the reset
+        lib.reset(mark)
+        return res
+    lib.set_fusion(1)
+    try:
+        plain, forked = run(False), run(True)
+    finally:
+        lib.set_fusion(0)
+    for k in plain:
+        assert np.isfinite(plain[k]).all() and np.abs(plain[k]).max() > 0, k
+        if k.startswith("dw"):
+            assert np.abs(plain[k] - forked[k]).max() <= 1e-5 * np.abs(plain[k]).max(), k
+        else:
+            assert np.array_equal(plain[k], forked[k]), k + ": branch region and program order differ"
+
+
+def test_branch_region_misuse_is_reported(gpu):
+    from lantern_b200._ffi import LanternError
+    lib = gpu.lib
+    with pytest.raises(LanternError):
+        lib.branch_begin()                          # no mark
+    with pytest.raises(LanternError):
+        lib.branch_join()                           # no region
+    lib.branch_mark()
+    with pytest.raises(LanternError):
+        lib.branch_mark()                           # one region at a time
+    lib.branch_begin()
+    with pytest.raises(LanternError):
+        lib.branch_join()                           # the branch has not ended
+    lib.branch_end()
+    with pytest.raises(LanternError):
+        lib.branch_begin()                          # one branch per region
+    lib.branch_join()
