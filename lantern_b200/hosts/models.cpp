@@ -48,7 +48,7 @@ struct Model {
   void* graph = nullptr;
   bool use_graph = false;
   float graph_lr = 0.f;
-  size_t zero_bytes = 0;       // bytes of zero-initialised gradient buffers the last step asked for (0: not known yet)
+  size_t zero_bytes = 0;       // bytes of zero-initialised gradient buffers the largest step so far asked for (0: not known yet)
   bool early_reduce = false;   // this step runs data-parallel with an update: finished gradient ranges are summed during backward
   bool branches = true;        // independent runs of calls (shortcut convolutions) are issued as branch regions
   bool resident = false;       // read the batch from dev_x/dev_y instead of uploading it
@@ -117,7 +117,7 @@ struct Model {
     BK(d2h_async)(loss_host, dev_loss, 4);
     if (update) apply_update(lr);
     if (tracing()) dump_trace();
-    zero_bytes = zero_pool_end();
+    { const size_t asked = zero_pool_end(); if (asked > zero_bytes) zero_bytes = asked; }   // the largest step so far: a smaller tree leaves part of the block unused
     BK(reset)(mark);
   }
   // Data parallelism: pushed on the tape at a point of the forward pass, this fires in the backward pass once every layer
