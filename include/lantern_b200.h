@@ -107,6 +107,20 @@ int   LTB_FN(d2h_async)(void* dst_pinned, const void* src, size_t bytes);
 int   LTB_FN(marker_record)(int slot);
 int   LTB_FN(marker_wait)(int slot);
 
+/* Fused affine map with activation on vectors, for the recursive models (one LSTM gate per call instead of five).  The
+ * Backend trait has no such method; the reference fuses the same expression for its CPU backend only (Tensor.linearTanh /
+ * linear2Tanh, TensorDifferentiation.scala:947-990).
+ *   affine_act:      out[r] = act(sum_j W0[r][j] a[j] (+ sum_j W1[r][j] b[j]) + bias[r])
+ *                    W0 [rows x cols0], W1 [rows x cols1] row-major; W1 and b may both be NULL; act = LTB_SIGMOID, LTB_TANH or
+ *                    -1 (none).
+ *   affine_act_grad: dpre = dout * act'(out); dbias += dpre; dW0 += dpre a^T; da += W0^T dpre; likewise dW1, db.
+ *                    da / db may be NULL (a leaf input).  Everything accumulates, as the separate gradients do
+ *                    (TensorDslCPU.scala:186-225, 748-766). */
+int LTB_FN(affine_act)(const float* W0, const float* a, int cols0, const float* W1, const float* b, int cols1, const float* bias,
+                       int act, float* out, int rows);
+int LTB_FN(affine_act_grad)(const float* W0, float* dW0, const float* a, float* da, int cols0, const float* W1, float* dW1,
+                            const float* b, float* db, int cols1, float* dbias, int act, const float* out, const float* dout, int rows);
+
 /* Branch regions (no counterpart in the reference, whose generated programs issue everything on one stream): two runs of
  * calls that do not depend on each other -- the shortcut convolution of a residual block and its main path, the two
  * expand convolutions of a fire module -- may overlap on the device.

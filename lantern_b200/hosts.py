@@ -22,6 +22,7 @@ _SIGS = {
     "model_set_table": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int]),
     "model_use_graph": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int]),
     "model_use_branches": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int]),
+    "model_use_fused_cells": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int]),
     "model_set_resident": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]),
     "model_step": (ctypes.c_float, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_float, ctypes.c_int]),
     "model_step_async": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_float]),
@@ -181,6 +182,10 @@ class Model:
         rc = self.hp.fn["model_set_table"](self.h, t.ctypes.data, t.shape[0])
         if rc:
             raise ValueError("model_set_table failed: %d" % rc)
+
+    def use_fused_cells(self, on=True):
+        """Recursive models: one fused call per gate (default) or one call per operator, as the reference stages them."""
+        self.hp.fn["model_use_fused_cells"](self.h, int(on))
 
     def use_branches(self, on=True):
         """Issue independent runs of calls (shortcut convolutions) as branch regions (default) or all in program order."""

@@ -51,6 +51,7 @@ struct Model {
   size_t zero_bytes = 0;       // bytes of zero-initialised gradient buffers the largest step so far asked for (0: not known yet)
   bool early_reduce = false;   // this step runs data-parallel with an update: finished gradient ranges are summed during backward
   bool branches = true;        // independent runs of calls (shortcut convolutions) are issued as branch regions
+  bool fused_cells = true;     // recursive models: one call per gate (ltb_affine_act) instead of one per operator
   bool resident = false;       // read the batch from dev_x/dev_y instead of uploading it
   float* dev_x = nullptr; int32_t* dev_y = nullptr;
   float* dev_loss = nullptr;   // the loss of the last step, kept outside the arena span that the step resets
@@ -333,11 +334,18 @@ struct TreeLstm : Model {
     }
     mark = BK(mark)();
   }
+  // With fused cells (the default) a gate is one call forward and one backward (ltb_affine_act) instead of the five and
+  // about eight small kernels of the operator-by-operator form, which is kept for comparison (model_use_fused_cells).
   TR gate(Tape& t, int op, int W0, const TR& a, int W1, const TR& b, int bias) {      // (W0.a plusBias W1.b plusBias bias).op
+    if (fused_cells) { TR w1 = P(W1); return t.affine_act(op, P(W0), a, &w1, &b, P(bias)); }
     return t.unary(op, t.plus_bias(t.plus_bias(t.dot(P(W0), a), t.dot(P(W1), b)), P(bias)));
   }
+  TR leaf_gate(Tape& t, int op, int W, const TR& e, int bias) {                       // (W.e plusBias bias).op
+    if (fused_cells) return t.affine_act(op, P(W), e, nullptr, nullptr, P(bias));
+    return t.unary(op, t.plus_bias(t.dot(P(W), e), P(bias)));
+  }
   TR out(Tape& t, const TR& in, const int32_t* score) {                              // Out.apply, lines 111-118
-    TR pred = t.plus_bias(t.dot(P(Why), in), P(by));
+    TR pred = fused_cells ? t.affine_act(-1, P(Why), in, nullptr, nullptr, P(by)) : t.plus_bias(t.dot(P(Why), in), P(by));
     return t.nll(t.log_softmax(view(pred, {1, O})), score);
   }
   State visit(Tape& t, const int32_t* host, const int32_t* dev, int i) {
@@ -345,9 +353,9 @@ struct TreeLstm : Model {
     State s;
     if (lch[i] < 0) {                                                                // leaf, lines 72-85 and 130-133
       TR e; e.rank = 1; e.shape[0] = E; e.x = table + (int64_t)words[i] * E; e.is_input = true;
-      TR ig = t.unary(LTB_SIGMOID, t.plus_bias(t.dot(P(Wi), e), P(bi)));
-      TR og = t.unary(LTB_SIGMOID, t.plus_bias(t.dot(P(Wo), e), P(bo)));
-      TR uv = t.unary(LTB_TANH, t.plus_bias(t.dot(P(Wu), e), P(bu)));
+      TR ig = leaf_gate(t, LTB_SIGMOID, Wi, e, bi);
+      TR og = leaf_gate(t, LTB_SIGMOID, Wo, e, bo);
+      TR uv = leaf_gate(t, LTB_TANH, Wu, e, bu);
       TR cell = t.binary(LTB_MUL, ig, uv);
       TR hidden = t.binary(LTB_MUL, og, t.unary(LTB_TANH, cell));
       if (!pldi19) { s.loss = out(t, hidden, scores + i); s.first = hidden; s.second = cell; return s; }
@@ -531,6 +539,8 @@ int HOST_FN(model_set_table)(void* m, const float* host, int rows) {
   return T ? T->set_table(host, rows) : LTB_E_ARG;
 }
 int64_t HOST_FN(model_label_count)(void* m) { return ((Model*)m)->label_count; }
+// Recursive models: gates as single fused calls (default) or operator by operator, as the reference stages them.
+int HOST_FN(model_use_fused_cells)(void* m, int on) { ((Model*)m)->fused_cells = on != 0; return 0; }
 // Issue independent runs of calls as branch regions (default) or everything in program order on one stream.
 int HOST_FN(model_use_branches)(void* m, int on) {
   Model* M = (Model*)m;

@@ -155,6 +155,18 @@ struct Tape {
     return main;
   }
   // dot (2,2) and (2,1), TD.scala:1220-1226
+  // act(W0.a (+ W1.b) + bias) in one call and one gradient call (an LSTM gate); b == nullptr: one product only.
+  // Equivalent to unary(act, plus_bias(plus_bias(dot(W0, a), dot(W1, b)), bias)); act == -1: no activation.
+  TR affine_act(int act, const TR& W0, const TR& a, const TR* W1, const TR* b, const TR& bias) {
+    const int rows = W0.shape[0], c0 = W0.shape[1], c1 = W1 ? W1->shape[1] : 0;
+    TR y = make({rows});
+    const float *w1x = W1 ? W1->x : nullptr, *bx = b ? b->x : nullptr;
+    float *w1d = W1 ? W1->d : nullptr, *bd = (b && !b->is_input) ? b->d : nullptr;
+    BK(affine_act)(W0.x, a.x, c0, w1x, bx, c1, bias.x, act, y.x, rows);
+    float* ad = a.is_input ? nullptr : a.d;
+    push([=] { BK(affine_act_grad)(W0.x, W0.d, a.x, ad, c0, w1x, w1d, bx, bd, c1, bias.d, act, y.x, y.d, rows); });
+    return y;
+  }
   TR dot(const TR& a, const TR& b) {
     if (b.rank == 2) {
       int m = a.shape[0], k = a.shape[1], n = b.shape[1];

@@ -272,6 +272,36 @@ int ora_mv_dot(const float* a, const float* x, float* out, int m, int k) {
   for (int i = 0; i < m; ++i) { float s = 0.0f; for (int j = 0; j < k; ++j) s += a[(size_t)i * k + j] * x[j]; out[i] = s; }
   return LTB_OK;
 }
+// Fused affine map with activation: the composition of matrixVectorDot (TensorDslCPU.scala:148-156), the broadcasting
+// adds and tanh / sigmoid (748-766) that the unfused programs issue, sums in the same sequential float order per product.
+int ora_affine_act(const float* W0, const float* a, int cols0, const float* W1, const float* b, int cols1, const float* bias,
+                   int act, float* out, int rows) {
+  REQUIRE(W0 && a && bias && out && rows > 0 && cols0 > 0 && (W1 == nullptr) == (b == nullptr), "affine_act: bad argument");
+  REQUIRE(act == -1 || act == LTB_TANH || act == LTB_SIGMOID, "affine_act: activation must be tanh, sigmoid or -1");
+  for (int r = 0; r < rows; ++r) {
+    float s0 = 0.0f, s1 = 0.0f;
+    for (int j = 0; j < cols0; ++j) s0 += W0[(size_t)r * cols0 + j] * a[j];
+    if (W1) for (int j = 0; j < cols1; ++j) s1 += W1[(size_t)r * cols1 + j] * b[j];
+    float v = (s0 + s1) + bias[r];
+    if (act == LTB_TANH) v = (float)tanh((double)v); else if (act == LTB_SIGMOID) v = 1.0f / ((float)exp((double)(-1.0f * v)) + 1.0f);
+    out[r] = v;
+  }
+  return LTB_OK;
+}
+int ora_affine_act_grad(const float* W0, float* dW0, const float* a, float* da, int cols0, const float* W1, float* dW1,
+                        const float* b, float* db, int cols1, float* dbias, int act, const float* out, const float* dout, int rows) {
+  REQUIRE(W0 && dW0 && a && dbias && out && dout && rows > 0 && cols0 > 0, "affine_act_grad: bad argument");
+  REQUIRE((W1 == nullptr) == (b == nullptr) && (W1 == nullptr) == (dW1 == nullptr), "affine_act_grad: W1, dW1 and b go together");
+  for (int r = 0; r < rows; ++r) {
+    const float y = out[r];
+    float dpre = dout[r];
+    if (act == LTB_TANH) dpre *= 1.0f - y * y; else if (act == LTB_SIGMOID) dpre *= (1.0f - y) * y;
+    dbias[r] += dpre;
+    for (int j = 0; j < cols0; ++j) { dW0[(size_t)r * cols0 + j] += dpre * a[j]; if (da) da[j] += W0[(size_t)r * cols0 + j] * dpre; }
+    if (W1) for (int j = 0; j < cols1; ++j) { dW1[(size_t)r * cols1 + j] += dpre * b[j]; if (db) db[j] += W1[(size_t)r * cols1 + j] * dpre; }
+  }
+  return LTB_OK;
+}
 // matrixMatrixDot: TensorDslCPU.scala:158-169.
 int ora_mm_dot(const float* a, const float* b, float* out, int m, int k, int n) {
   sgemm_m(false, false, m, n, k, 1.0f, a, k, b, n, 0.0f, out, n); return LTB_OK;

@@ -564,3 +564,27 @@ def test_branch_region_misuse_is_reported(gpu):
     with pytest.raises(LanternError):
         lib.branch_begin()                          # one branch per region
     lib.branch_join()
+
+
+# ---------------------------------------------------------------------------------------------- fused gate
+@pytest.mark.parametrize("cfg", [(150, 150, 150, 2), (150, 300, 0, 1), (5, 150, 0, -1), (33, 70, 9, 2), (1, 1, 1, 1)])
+def test_affine_act_and_gradient(ora, gpu, cfg):
+    """out = act(W0.a + W1.b + bias) and its accumulating gradient against the oracle: the TreeLSTM gate sizes (two 150x150
+    products; one 150x300 product of a leaf, whose input has no gradient; the 5-way output layer without activation)."""
+    rows, c0, c1, act = cfg
+    W00, a0 = R(1).standard_normal((rows, c0)).astype(np.float32) / np.sqrt(c0), R(2).standard_normal(c0).astype(np.float32)
+    W10, b0 = R(3).standard_normal((rows, max(c1, 1))).astype(np.float32) / np.sqrt(max(c1, 1)), R(4).standard_normal(max(c1, 1)).astype(np.float32)
+    bias0, dout0 = R(5).standard_normal(rows).astype(np.float32), R(6).standard_normal(rows).astype(np.float32)
+
+    def f(b):
+        lib = b.lib
+        W0, a, W1, bb, bias, dout = (b.fromNumpy(v) for v in (W00, a0, W10, b0, bias0, dout0))
+        dW0, da, dW1, db, dbias = (b.fromNumpy(v * 0.5) for v in (W00, a0, W10, b0, bias0))      # accumulate onto non-zero values
+        out = b.fill((rows,), 0.0)
+        two = c1 > 0
+        leaf = c0 == 300                                                # the leaf's embedding is an input: no gradient for it
+        lib.affine_act(W0, a, c0, W1 if two else 0, bb if two else 0, c1, bias, act, out, rows)
+        lib.affine_act_grad(W0, dW0, a, 0 if leaf else da, c0, W1 if two else 0, dW1 if two else 0, bb if two else 0, db if two else 0, c1,
+                            dbias, act, out, dout, rows)
+        return {"out": out.toCPU(), "dW0": dW0.toCPU(), "da": da.toCPU(), "dW1": dW1.toCPU(), "db": db.toCPU(), "dbias": dbias.toCPU()}
+    check(f, ora, gpu)

@@ -44,3 +44,22 @@ def test_treelstm_untrained_loss_and_learning(oracle_lib):
         last = m.step(x, y, 0.05)
     assert last < 0.1 * first
     m.close(); oracle_lib.reset(mark)
+
+
+def test_treelstm_fused_gates_equal_operator_by_operator(oracle_lib):
+    """One fused call per gate (affine_act) against the reference's operator-by-operator form on the oracle: same loss and
+    the same 22 gradients up to the order of two float additions per gate."""
+    from tests.test_gpu_models import _random_tree
+    mark = oracle_lib.mark()
+    y = _random_tree(np.random.default_rng(11), 7)
+    x = np.zeros(1, np.float32)
+    res = []
+    for fused in (True, False):
+        m = _model(oracle_lib, "treelstm", 1)
+        m.use_fused_cells(fused)
+        loss = m.step(x, y, 0.0, update=False)
+        res.append((loss, [m.grad(i) for i in range(m.num_params)]))
+        m.close(); oracle_lib.reset(mark)
+    assert abs(res[0][0] - res[1][0]) <= 1e-6 * abs(res[1][0])
+    for a, b in zip(res[0][1], res[1][1]):
+        assert np.abs(a - b).max() <= 1e-5 * max(np.abs(b).max(), 1e-12)
