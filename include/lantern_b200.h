@@ -121,6 +121,17 @@ int LTB_FN(affine_act)(const float* W0, const float* a, int cols0, const float* 
 int LTB_FN(affine_act_grad)(const float* W0, float* dW0, const float* a, float* da, int cols0, const float* W1, float* dW1,
                             const float* b, float* db, int cols1, float* dbias, int act, const float* out, const float* dout, int rows);
 
+/* The elementwise part of a (tree) LSTM cell in one call, and its gradient in one call (no Backend counterpart; the
+ * expression is NIPS18App/SentimentTreeLSTM.scala:150-156 = PLDI19APP/SentimentTreeLSTM.scala:136-141):
+ *   c = i*u (+ fl*cl + fr*cr when fl is not NULL: an inner node);  tc = tanh(c);  h = o*tc       (tc is kept for the gradient)
+ *   lstm_cell_grad: dct = dc + dh*o*(1 - tc^2); do += dh*tc; di += dct*u; du += dct*i; dfl += dct*cl; dcl += dct*fl;
+ *                   dfr += dct*cr; dcr += dct*fr.  fl, cl, fr, cr and their gradients are all NULL for a leaf. */
+int LTB_FN(lstm_cell)(const float* i, const float* u, const float* fl, const float* cl, const float* fr, const float* cr,
+                      const float* o, float* c, float* tc, float* h, int n);
+int LTB_FN(lstm_cell_grad)(const float* i, float* di, const float* u, float* du, const float* fl, float* dfl, const float* cl, float* dcl,
+                           const float* fr, float* dfr, const float* cr, float* dcr, const float* o, float* d_o,
+                           const float* tc, const float* dc, const float* dh, int n);
+
 /* Branch regions (no counterpart in the reference, whose generated programs issue everything on one stream): two runs of
  * calls that do not depend on each other -- the shortcut convolution of a residual block and its main path, the two
  * expand convolutions of a fire module -- may overlap on the device.

@@ -297,6 +297,49 @@ __global__ void affine_act_grad_kernel(const float* __restrict__ W0, float* dW0,
 }
 }  // namespace ltb
 extern "C" {
+}  // extern "C"
+namespace ltb {
+__global__ void lstm_cell_kernel(const float* __restrict__ i, const float* __restrict__ u, const float* __restrict__ fl, const float* __restrict__ cl,
+                                 const float* __restrict__ fr, const float* __restrict__ cr, const float* __restrict__ o, float* c, float* tc, float* h, int n) {
+  const int k = blockIdx.x * blockDim.x + threadIdx.x;
+  if (k >= n) return;
+  float v = i[k] * u[k];
+  if (fl) { v = v + fl[k] * cl[k]; v = v + fr[k] * cr[k]; }
+  const float t = tanhf(v);
+  c[k] = v; tc[k] = t; h[k] = o[k] * t;
+}
+__global__ void lstm_cell_grad_kernel(const float* __restrict__ i, float* di, const float* __restrict__ u, float* du, const float* __restrict__ fl, float* dfl,
+                                      const float* __restrict__ cl, float* dcl, const float* __restrict__ fr, float* dfr, const float* __restrict__ cr, float* dcr,
+                                      const float* __restrict__ o, float* d_o, const float* __restrict__ tc, const float* __restrict__ dc,
+                                      const float* __restrict__ dh, int n) {
+  const int k = blockIdx.x * blockDim.x + threadIdx.x;
+  if (k >= n) return;
+  const float t = tc[k], g = dh[k];
+  d_o[k] += g * t;
+  const float dct = dc[k] + (g * o[k]) * (1.0f - t * t);
+  di[k] += dct * u[k]; du[k] += dct * i[k];
+  if (fl) { dfl[k] += dct * cl[k]; dcl[k] += dct * fl[k]; dfr[k] += dct * cr[k]; dcr[k] += dct * fr[k]; }
+}
+}  // namespace ltb
+extern "C" {
+int ltb_lstm_cell(const float* i, const float* u, const float* fl, const float* cl, const float* fr, const float* cr,
+                  const float* o, float* c, float* tc, float* h, int n) {
+  LTB_INITED();
+  LTB_REQUIRE(i && u && o && c && tc && h && n > 0, "ltb_lstm_cell: bad argument");
+  LTB_REQUIRE((fl && cl && fr && cr) || (!fl && !cl && !fr && !cr), "ltb_lstm_cell: the four child operands go together");
+  LTB_LAUNCH(lstm_cell_kernel, (unsigned)ceil_div(n, 128), 128, 0, i, u, fl, cl, fr, cr, o, c, tc, h, n);
+  return LTB_OK;
+}
+int ltb_lstm_cell_grad(const float* i, float* di, const float* u, float* du, const float* fl, float* dfl, const float* cl, float* dcl,
+                       const float* fr, float* dfr, const float* cr, float* dcr, const float* o, float* d_o,
+                       const float* tc, const float* dc, const float* dh, int n) {
+  LTB_INITED();
+  LTB_REQUIRE(i && di && u && du && o && d_o && tc && dc && dh && n > 0, "ltb_lstm_cell_grad: bad argument");
+  LTB_REQUIRE((fl && dfl && cl && dcl && fr && dfr && cr && dcr) || (!fl && !dfl && !cl && !dcl && !fr && !dfr && !cr && !dcr),
+              "ltb_lstm_cell_grad: the child operands and their gradients go together");
+  LTB_LAUNCH(lstm_cell_grad_kernel, (unsigned)ceil_div(n, 128), 128, 0, i, di, u, du, fl, dfl, cl, dcl, fr, dfr, cr, dcr, o, d_o, tc, dc, dh, n);
+  return LTB_OK;
+}
 int ltb_affine_act(const float* W0, const float* a, int cols0, const float* W1, const float* b, int cols1, const float* bias,
                    int act, float* out, int rows) {
   LTB_INITED();

@@ -356,8 +356,9 @@ struct TreeLstm : Model {
       TR ig = leaf_gate(t, LTB_SIGMOID, Wi, e, bi);
       TR og = leaf_gate(t, LTB_SIGMOID, Wo, e, bo);
       TR uv = leaf_gate(t, LTB_TANH, Wu, e, bu);
-      TR cell = t.binary(LTB_MUL, ig, uv);
-      TR hidden = t.binary(LTB_MUL, og, t.unary(LTB_TANH, cell));
+      TR cell, hidden;
+      if (fused_cells) t.lstm_cell(ig, uv, nullptr, nullptr, nullptr, nullptr, og, &cell, &hidden);
+      else { cell = t.binary(LTB_MUL, ig, uv); hidden = t.binary(LTB_MUL, og, t.unary(LTB_TANH, cell)); }
       if (!pldi19) { s.loss = out(t, hidden, scores + i); s.first = hidden; s.second = cell; return s; }
       // val ArrayBuffer(cell', hidden') = leaf(...): cell' = hidden, hidden' = cell
       s.loss = out(t, /*hidden'*/ cell, scores + i);
@@ -371,8 +372,12 @@ struct TreeLstm : Model {
     TR fr = gate(t, LTB_SIGMOID, U10f, hl, U11f, hr, bbf);
     TR og = gate(t, LTB_SIGMOID, U0o, hl, U1o, hr, bbo);
     TR uv = gate(t, LTB_TANH, U0u, hl, U1u, hr, bbu);
-    TR cell = t.plus_bias(t.plus_bias(t.binary(LTB_MUL, ig, uv), t.binary(LTB_MUL, fl, cl)), t.binary(LTB_MUL, fr, cr));
-    TR hidden = t.binary(LTB_MUL, og, t.unary(LTB_TANH, cell));
+    TR cell, hidden;
+    if (fused_cells) t.lstm_cell(ig, uv, &fl, &cl, &fr, &cr, og, &cell, &hidden);
+    else {
+      cell = t.plus_bias(t.plus_bias(t.binary(LTB_MUL, ig, uv), t.binary(LTB_MUL, fl, cl)), t.binary(LTB_MUL, fr, cr));
+      hidden = t.binary(LTB_MUL, og, t.unary(LTB_TANH, cell));
+    }
     if (!pldi19) {        // loss = lossl + lossr + nll, NIPS18App/SentimentTreeLSTM.scala:158
       s.loss = t.binary(LTB_ADD, t.binary(LTB_ADD, l.loss, r.loss), out(t, hidden, scores + i));
       s.first = hidden; s.second = cell;

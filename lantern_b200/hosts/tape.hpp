@@ -167,6 +167,17 @@ struct Tape {
     push([=] { BK(affine_act_grad)(W0.x, W0.d, a.x, ad, c0, w1x, w1d, bx, bd, c1, bias.d, act, y.x, y.d, rows); });
     return y;
   }
+  // cell = i*u (+ fl*cl + fr*cr), hidden = o*tanh(cell) in one call and one gradient call; the child operands are null for a leaf.
+  void lstm_cell(const TR& i, const TR& u, const TR* fl, const TR* cl, const TR* fr, const TR* cr, const TR& o, TR* cell, TR* hidden) {
+    const int n = (int)i.count();
+    TR c = make({n}), h = make({n});
+    float* tc = alloc_value(n);
+    const float *flx = fl ? fl->x : nullptr, *clx = cl ? cl->x : nullptr, *frx = fr ? fr->x : nullptr, *crx = cr ? cr->x : nullptr;
+    float *fld = fl ? fl->d : nullptr, *cld = cl ? cl->d : nullptr, *frd = fr ? fr->d : nullptr, *crd = cr ? cr->d : nullptr;
+    BK(lstm_cell)(i.x, u.x, flx, clx, frx, crx, o.x, c.x, tc, h.x, n);
+    push([=] { BK(lstm_cell_grad)(i.x, i.d, u.x, u.d, flx, fld, clx, cld, frx, frd, crx, crd, o.x, o.d, tc, c.d, h.d, n); });
+    *cell = c; *hidden = h;
+  }
   TR dot(const TR& a, const TR& b) {
     if (b.rank == 2) {
       int m = a.shape[0], k = a.shape[1], n = b.shape[1];

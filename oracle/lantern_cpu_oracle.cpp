@@ -302,6 +302,35 @@ int ora_affine_act_grad(const float* W0, float* dW0, const float* a, float* da, 
   }
   return LTB_OK;
 }
+// The elementwise part of an LSTM cell: the products, in-place sums and tanh the unfused programs issue
+// (TensorDslCPU.scala:227-374 elementwise, 748-758 tanh), in the same order of float operations.
+int ora_lstm_cell(const float* i, const float* u, const float* fl, const float* cl, const float* fr, const float* cr,
+                  const float* o, float* c, float* tc, float* h, int n) {
+  REQUIRE(i && u && o && c && tc && h && n > 0, "lstm_cell: bad argument");
+  REQUIRE((fl && cl && fr && cr) || (!fl && !cl && !fr && !cr), "lstm_cell: the four child operands go together");
+  for (int k = 0; k < n; ++k) {
+    float v = i[k] * u[k];
+    if (fl) { v = v + fl[k] * cl[k]; v = v + fr[k] * cr[k]; }
+    const float t = (float)tanh((double)v);
+    c[k] = v; tc[k] = t; h[k] = o[k] * t;
+  }
+  return LTB_OK;
+}
+int ora_lstm_cell_grad(const float* i, float* di, const float* u, float* du, const float* fl, float* dfl, const float* cl, float* dcl,
+                       const float* fr, float* dfr, const float* cr, float* dcr, const float* o, float* d_o,
+                       const float* tc, const float* dc, const float* dh, int n) {
+  REQUIRE(i && di && u && du && o && d_o && tc && dc && dh && n > 0, "lstm_cell_grad: bad argument");
+  REQUIRE((fl && dfl && cl && dcl && fr && dfr && cr && dcr) || (!fl && !dfl && !cl && !dcl && !fr && !dfr && !cr && !dcr),
+          "lstm_cell_grad: the child operands and their gradients go together");
+  for (int k = 0; k < n; ++k) {
+    const float t = tc[k], g = dh[k];
+    d_o[k] += g * t;
+    const float dct = dc[k] + (g * o[k]) * (1.0f - t * t);
+    di[k] += dct * u[k]; du[k] += dct * i[k];
+    if (fl) { dfl[k] += dct * cl[k]; dcl[k] += dct * fl[k]; dfr[k] += dct * cr[k]; dcr[k] += dct * fr[k]; }
+  }
+  return LTB_OK;
+}
 // matrixMatrixDot: TensorDslCPU.scala:158-169.
 int ora_mm_dot(const float* a, const float* b, float* out, int m, int k, int n) {
   sgemm_m(false, false, m, n, k, 1.0f, a, k, b, n, 0.0f, out, n); return LTB_OK;

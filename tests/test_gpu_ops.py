@@ -588,3 +588,25 @@ def test_affine_act_and_gradient(ora, gpu, cfg):
                             dbias, act, out, dout, rows)
         return {"out": out.toCPU(), "dW0": dW0.toCPU(), "da": da.toCPU(), "dW1": dW1.toCPU(), "db": db.toCPU(), "dbias": dbias.toCPU()}
     check(f, ora, gpu)
+
+
+@pytest.mark.parametrize("inner", [True, False])
+def test_lstm_cell_and_gradient(ora, gpu, inner):
+    """cell = i*u (+ fl*cl + fr*cr), hidden = o*tanh(cell) and the accumulating gradient, inner node and leaf, against the oracle."""
+    n = 150
+    v = {k: R(10 + j).standard_normal(n).astype(np.float32) for j, k in enumerate(["i", "u", "fl", "cl", "fr", "cr", "o", "dc", "dh"])}
+
+    def f(b):
+        lib = b.lib
+        t = {k: b.fromNumpy(a) for k, a in v.items()}
+        d = {k: b.fromNumpy(v[k] * 0.25) for k in ["i", "u", "fl", "cl", "fr", "cr", "o"]}          # accumulate onto non-zero values
+        c, tc, h = b.fill((n,), 0.0), b.fill((n,), 0.0), b.fill((n,), 0.0)
+        kids = [t[k] if inner else 0 for k in ("fl", "cl", "fr", "cr")]
+        lib.lstm_cell(t["i"], t["u"], kids[0], kids[1], kids[2], kids[3], t["o"], c, tc, h, n)
+        g = lambda k: d[k] if inner else 0
+        lib.lstm_cell_grad(t["i"], d["i"], t["u"], d["u"], kids[0], g("fl"), kids[1], g("cl"), kids[2], g("fr"), kids[3], g("cr"),
+                           t["o"], d["o"], tc, t["dc"], t["dh"], n)
+        out = {"c": c.toCPU(), "tc": tc.toCPU(), "h": h.toCPU()}
+        out.update({"d" + k: d[k].toCPU() for k in d})
+        return out
+    check(f, ora, gpu)
