@@ -121,6 +121,17 @@ int LTB_FN(affine_act)(const float* W0, const float* a, int cols0, const float* 
 int LTB_FN(affine_act_grad)(const float* W0, float* dW0, const float* a, float* da, int cols0, const float* W1, float* dW1,
                             const float* b, float* db, int cols1, float* dbias, int act, const float* out, const float* dout, int rows);
 
+/* The batched form, for a recurrent cell over a minibatch (weights stored [in, out] as the reference's Linear1D does,
+ * NNModule.scala:112-117; the cell is tanh(x W0 + h W1 + bias), NNModule.scala:189-200):
+ *   affine_act_rows:      out[b][j] = act(sum_c x0[b][c] W0[c][j] (+ sum_c x1[b][c] W1[c][j]) + bias[j]),  b < batch, j < width
+ *   affine_act_rows_grad: dpre = dout * act'(out); dbias += column sums of dpre; dW0 += x0^T dpre; dx0 += dpre W0^T; likewise
+ *                         dW1, dx1.  dx0 / dx1 may be NULL (an input); x1, W1, dW1 go together and may be NULL. */
+int LTB_FN(affine_act_rows)(const float* x0, const float* W0, int cols0, const float* x1, const float* W1, int cols1, const float* bias,
+                            int act, float* out, int batch, int width);
+int LTB_FN(affine_act_rows_grad)(const float* x0, float* dx0, const float* W0, float* dW0, int cols0, const float* x1, float* dx1,
+                                 const float* W1, float* dW1, int cols1, float* dbias, int act, const float* out, const float* dout,
+                                 int batch, int width);
+
 /* The elementwise part of a (tree) LSTM cell in one call, and its gradient in one call (no Backend counterpart; the
  * expression is NIPS18App/SentimentTreeLSTM.scala:150-156 = PLDI19APP/SentimentTreeLSTM.scala:136-141):
  *   c = i*u (+ fl*cl + fr*cr when fl is not NULL: an inner node);  tc = tanh(c);  h = o*tc       (tc is kept for the gradient)

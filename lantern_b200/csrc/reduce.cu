@@ -340,6 +340,92 @@ int ltb_lstm_cell_grad(const float* i, float* di, const float* u, float* du, con
   LTB_LAUNCH(lstm_cell_grad_kernel, (unsigned)ceil_div(n, 128), 128, 0, i, di, u, du, fl, dfl, cl, dcl, fr, dfr, cr, dcr, o, d_o, tc, dc, dh, n);
   return LTB_OK;
 }
+}  // extern "C"
+namespace ltb {
+__device__ __forceinline__ float act_fwd(int act, float v) { return act == LTB_TANH ? tanhf(v) : act == LTB_SIGMOID ? 1.0f / (expf(-v) + 1.0f) : v; }
+__device__ __forceinline__ float act_slope(int act, float y) { return act == LTB_TANH ? 1.0f - y * y : act == LTB_SIGMOID ? (1.0f - y) * y : 1.0f; }
+// A thread per output (b, j): the lanes of a warp share b (x is a broadcast) and read consecutive j of a weight row.
+__global__ void affine_act_rows_kernel(const float* __restrict__ x0, const float* __restrict__ W0, int cols0, const float* __restrict__ x1,
+                                       const float* __restrict__ W1, int cols1, const float* __restrict__ bias, int act, float* out, int batch, int width) {
+  const int j = blockIdx.x * blockDim.x + threadIdx.x, b = blockIdx.y;
+  if (j >= width) return;
+  float s0 = 0.0f, s1 = 0.0f;
+  const float* xr = x0 + (int64_t)b * cols0;
+#pragma unroll 4
+  for (int c = 0; c < cols0; ++c) s0 += xr[c] * W0[(int64_t)c * width + j];
+  if (W1) {
+    xr = x1 + (int64_t)b * cols1;
+#pragma unroll 4
+    for (int c = 0; c < cols1; ++c) s1 += xr[c] * W1[(int64_t)c * width + j];
+  }
+  out[(int64_t)b * width + j] = act_fwd(act, (s0 + s1) + bias[j]);
+}
+// The whole gradient in one launch, two kinds of blocks.  blockIdx.y < cols0 + cols1 + 1: row c of [dW0; dW1; dbias], a
+// thread per column j walks the batch (dpre is recomputed from out and dout: two coalesced loads, nothing stored).
+// The blocks after those: input gradients, a thread per (b, c) walks j.
+__global__ void affine_act_rows_grad_kernel(const float* __restrict__ x0, float* dx0, const float* __restrict__ W0, float* dW0, int cols0,
+                                            const float* __restrict__ x1, float* dx1, const float* __restrict__ W1, float* dW1, int cols1,
+                                            float* dbias, int act, const float* __restrict__ out, const float* __restrict__ dout, int batch, int width) {
+  const int wrows = cols0 + cols1 + 1;
+  if ((int)blockIdx.y < wrows) {
+    const int j = blockIdx.x * blockDim.x + threadIdx.x, c = blockIdx.y;
+    if (j >= width) return;
+    const float* xs; int ld, cc; float* dst;
+    if (c < cols0) { xs = x0; ld = cols0; cc = c; dst = dW0 + (int64_t)c * width + j; }
+    else if (c < cols0 + cols1) { xs = x1; ld = cols1; cc = c - cols0; dst = dW1 + (int64_t)(c - cols0) * width + j; }
+    else { xs = nullptr; ld = 0; cc = 0; dst = dbias + j; }
+    float s = 0.0f;
+#pragma unroll 4
+    for (int b = 0; b < batch; ++b) {
+      const float dpre = dout[(int64_t)b * width + j] * act_slope(act, out[(int64_t)b * width + j]);
+      s += xs ? xs[(int64_t)b * ld + cc] * dpre : dpre;
+    }
+    *dst += s;
+  } else {
+    // input gradients: flat index over dx0 (batch x cols0, when wanted) then dx1 (batch x cols1, when wanted)
+    const int64_t n0 = dx0 ? (int64_t)batch * cols0 : 0, n1 = dx1 ? (int64_t)batch * cols1 : 0;
+    const int64_t t = ((int64_t)(blockIdx.y - wrows) * gridDim.x + blockIdx.x) * blockDim.x + threadIdx.x;
+    if (t >= n0 + n1) return;
+    const bool first = t < n0;
+    const int64_t u = first ? t : t - n0;
+    const int ld = first ? cols0 : cols1;
+    const int b = (int)(u / ld), c = (int)(u - (int64_t)b * ld);
+    const float* w = (first ? W0 : W1) + (int64_t)c * width;
+    const float* o = out + (int64_t)b * width; const float* d = dout + (int64_t)b * width;
+    float s = 0.0f;
+#pragma unroll 4
+    for (int j = 0; j < width; ++j) s += d[j] * act_slope(act, o[j]) * w[j];
+    (first ? dx0 : dx1)[u] += s;
+  }
+}
+}  // namespace ltb
+extern "C" {
+int ltb_affine_act_rows(const float* x0, const float* W0, int cols0, const float* x1, const float* W1, int cols1, const float* bias,
+                        int act, float* out, int batch, int width) {
+  LTB_INITED();
+  LTB_REQUIRE(x0 && W0 && bias && out && cols0 > 0 && batch > 0 && batch <= 65535 && width > 0 && (x1 == nullptr) == (W1 == nullptr) && (!W1 || cols1 > 0),
+              "ltb_affine_act_rows: bad argument");
+  LTB_REQUIRE(act == -1 || act == LTB_TANH || act == LTB_SIGMOID, "ltb_affine_act_rows: activation must be tanh, sigmoid or -1");
+  LTB_LAUNCH(affine_act_rows_kernel, dim3((unsigned)ceil_div(width, 128), batch), 128, 0, x0, W0, cols0, x1, W1, W1 ? cols1 : 0, bias, act, out, batch, width);
+  return LTB_OK;
+}
+int ltb_affine_act_rows_grad(const float* x0, float* dx0, const float* W0, float* dW0, int cols0, const float* x1, float* dx1,
+                             const float* W1, float* dW1, int cols1, float* dbias, int act, const float* out, const float* dout,
+                             int batch, int width) {
+  LTB_INITED();
+  LTB_REQUIRE(x0 && W0 && dW0 && dbias && out && dout && cols0 > 0 && batch > 0 && width > 0, "ltb_affine_act_rows_grad: bad argument");
+  LTB_REQUIRE((x1 == nullptr) == (W1 == nullptr) && (W1 == nullptr) == (dW1 == nullptr) && (!W1 || cols1 > 0) && (W1 || !dx1),
+              "ltb_affine_act_rows_grad: x1, W1 and dW1 go together");
+  LTB_REQUIRE(act == -1 || act == LTB_TANH || act == LTB_SIGMOID, "ltb_affine_act_rows_grad: activation must be tanh, sigmoid or -1");
+  const int c1 = W1 ? cols1 : 0;
+  const unsigned gx = (unsigned)ceil_div(width, 128);
+  const int64_t inputs = (dx0 ? (int64_t)batch * cols0 : 0) + (dx1 ? (int64_t)batch * c1 : 0);
+  const int64_t extra = ceil_div(inputs, (int64_t)gx * 128);
+  LTB_REQUIRE(cols0 + c1 + 1 + extra <= 65535, "ltb_affine_act_rows_grad: too large for one launch");
+  LTB_LAUNCH(affine_act_rows_grad_kernel, dim3(gx, (unsigned)(cols0 + c1 + 1 + extra)), 128, 0, x0, dx0, W0, dW0, cols0, x1, dx1, W1, dW1, c1,
+             dbias, act, out, dout, batch, width);
+  return LTB_OK;
+}
 int ltb_affine_act(const float* W0, const float* a, int cols0, const float* W1, const float* b, int cols1, const float* bias,
                    int act, float* out, int rows) {
   LTB_INITED();

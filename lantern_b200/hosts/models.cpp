@@ -274,9 +274,16 @@ struct VanillaRnn : Model {
     BK(fill)(loss.x, 0.0f, 1);
     for (int s = 0; s < T; ++s) {
       TR xt; xt.rank = 2; xt.shape[0] = batch; xt.shape[1] = V; xt.x = x.x + (int64_t)s * batch * V; xt.is_input = true;
-      TR pre = t.binary(LTB_ADD, t.binary(LTB_ADD, t.dot(xt, P(w1)), t.dot(h, P(w2))), P(bh));
-      h = t.unary(LTB_TANH, pre);
-      TR o = t.plus_bias(t.dot(h, P(wo)), P(bo));
+      TR o;
+      if (fused_cells) {       // the cell and the output layer as one call each (ltb_affine_act_rows)
+        TR w2t = P(w2);
+        h = t.affine_act_rows(LTB_TANH, xt, P(w1), &h, &w2t, P(bh));
+        o = t.affine_act_rows(-1, h, P(wo), nullptr, nullptr, P(bo));
+      } else {
+        TR pre = t.binary(LTB_ADD, t.binary(LTB_ADD, t.dot(xt, P(w1)), t.dot(h, P(w2))), P(bh));
+        h = t.unary(LTB_TANH, pre);
+        o = t.plus_bias(t.dot(h, P(wo)), P(bo));
+      }
       loss = t.binary(LTB_ADD, loss, t.sum(t.nll(t.log_softmax(o), y + (int64_t)s * batch)));
     }
     return loss;

@@ -167,6 +167,17 @@ struct Tape {
     push([=] { BK(affine_act_grad)(W0.x, W0.d, a.x, ad, c0, w1x, w1d, bx, bd, c1, bias.d, act, y.x, y.d, rows); });
     return y;
   }
+  // Batched: act(x0 W0 (+ x1 W1) + bias) over the rows of x0 / x1, weights stored [in, out]; one call forward, one backward.
+  TR affine_act_rows(int act, const TR& x0, const TR& W0, const TR* x1, const TR* W1, const TR& bias) {
+    const int batch = x0.shape[0], c0 = x0.shape[1], width = W0.shape[1], c1 = x1 ? x1->shape[1] : 0;
+    TR y = make({batch, width});
+    const float *x1x = x1 ? x1->x : nullptr, *w1x = W1 ? W1->x : nullptr;
+    float *x1d = (x1 && !x1->is_input) ? x1->d : nullptr, *w1d = W1 ? W1->d : nullptr;
+    float* x0d = x0.is_input ? nullptr : x0.d;
+    BK(affine_act_rows)(x0.x, W0.x, c0, x1x, w1x, c1, bias.x, act, y.x, batch, width);
+    push([=] { BK(affine_act_rows_grad)(x0.x, x0d, W0.x, W0.d, c0, x1x, x1d, w1x, w1d, c1, bias.d, act, y.x, y.d, batch, width); });
+    return y;
+  }
   // cell = i*u (+ fl*cl + fr*cr), hidden = o*tanh(cell) in one call and one gradient call; the child operands are null for a leaf.
   void lstm_cell(const TR& i, const TR& u, const TR* fl, const TR* cl, const TR* fr, const TR* cr, const TR& o, TR* cell, TR* hidden) {
     const int n = (int)i.count();

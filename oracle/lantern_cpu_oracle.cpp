@@ -302,6 +302,48 @@ int ora_affine_act_grad(const float* W0, float* dW0, const float* a, float* da, 
   }
   return LTB_OK;
 }
+// Batched form: matrixMatrixDot (TensorDslCPU.scala:158-169) with the broadcasting adds and the activation; every sum runs
+// sequentially over its index in float, as the cblas restatement above does.
+int ora_affine_act_rows(const float* x0, const float* W0, int cols0, const float* x1, const float* W1, int cols1, const float* bias,
+                        int act, float* out, int batch, int width) {
+  REQUIRE(x0 && W0 && bias && out && cols0 > 0 && batch > 0 && width > 0 && (x1 == nullptr) == (W1 == nullptr), "affine_act_rows: bad argument");
+  REQUIRE(act == -1 || act == LTB_TANH || act == LTB_SIGMOID, "affine_act_rows: activation must be tanh, sigmoid or -1");
+  for (int b = 0; b < batch; ++b) for (int j = 0; j < width; ++j) {
+    float s0 = 0.0f, s1 = 0.0f;
+    for (int c = 0; c < cols0; ++c) s0 += x0[(size_t)b * cols0 + c] * W0[(size_t)c * width + j];
+    if (W1) for (int c = 0; c < cols1; ++c) s1 += x1[(size_t)b * cols1 + c] * W1[(size_t)c * width + j];
+    float v = (s0 + s1) + bias[j];
+    if (act == LTB_TANH) v = (float)tanh((double)v); else if (act == LTB_SIGMOID) v = 1.0f / ((float)exp((double)(-1.0f * v)) + 1.0f);
+    out[(size_t)b * width + j] = v;
+  }
+  return LTB_OK;
+}
+int ora_affine_act_rows_grad(const float* x0, float* dx0, const float* W0, float* dW0, int cols0, const float* x1, float* dx1,
+                             const float* W1, float* dW1, int cols1, float* dbias, int act, const float* out, const float* dout,
+                             int batch, int width) {
+  REQUIRE(x0 && W0 && dW0 && dbias && out && dout && cols0 > 0 && batch > 0 && width > 0, "affine_act_rows_grad: bad argument");
+  REQUIRE((x1 == nullptr) == (W1 == nullptr) && (W1 == nullptr) == (dW1 == nullptr) && (W1 || !dx1), "affine_act_rows_grad: x1, W1 and dW1 go together");
+  std::vector<float> dpre((size_t)batch * width);
+  for (size_t k = 0; k < dpre.size(); ++k) {
+    const float y = out[k];
+    dpre[k] = dout[k] * (act == LTB_TANH ? 1.0f - y * y : act == LTB_SIGMOID ? (1.0f - y) * y : 1.0f);
+  }
+  for (int j = 0; j < width; ++j) { float s = 0.0f; for (int b = 0; b < batch; ++b) s += dpre[(size_t)b * width + j]; dbias[j] += s; }
+  for (int pass = 0; pass < 2; ++pass) {
+    const float* x = pass ? x1 : x0; const float* W = pass ? W1 : W0; float* dW = pass ? dW1 : dW0; float* dx = pass ? dx1 : dx0;
+    const int cols = pass ? cols1 : cols0;
+    if (!W) continue;
+    for (int c = 0; c < cols; ++c) for (int j = 0; j < width; ++j) {
+      float s = 0.0f; for (int b = 0; b < batch; ++b) s += x[(size_t)b * cols + c] * dpre[(size_t)b * width + j];
+      dW[(size_t)c * width + j] += s;
+    }
+    if (dx) for (int b = 0; b < batch; ++b) for (int c = 0; c < cols; ++c) {
+      float s = 0.0f; for (int j = 0; j < width; ++j) s += dpre[(size_t)b * width + j] * W[(size_t)c * width + j];
+      dx[(size_t)b * cols + c] += s;
+    }
+  }
+  return LTB_OK;
+}
 // The elementwise part of an LSTM cell: the products, in-place sums and tanh the unfused programs issue
 // (TensorDslCPU.scala:227-374 elementwise, 748-758 tanh), in the same order of float operations.
 int ora_lstm_cell(const float* i, const float* u, const float* fl, const float* cl, const float* fr, const float* cr,

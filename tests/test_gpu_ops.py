@@ -610,3 +610,28 @@ def test_lstm_cell_and_gradient(ora, gpu, inner):
         out.update({"d" + k: d[k].toCPU() for k in d})
         return out
     check(f, ora, gpu)
+
+
+@pytest.mark.parametrize("cfg", [(256, 80, 100, 100, 1), (1, 80, 100, 100, 1), (20, 26, 50, 50, 2), (256, 100, 0, 80, -1), (7, 5, 3, 130, 1)])
+def test_affine_act_rows_and_gradient(ora, gpu, cfg):
+    """out = act(x0 W0 + x1 W1 + bias) over a minibatch and its accumulating gradient against the oracle: the min-char-rnn
+    cell (one-hot input without gradient) and its output layer (no activation, one product), at batch 1, 20 and 256."""
+    batch, c0, c1, width, act = cfg
+    x00 = R(1).standard_normal((batch, c0)).astype(np.float32)
+    W00 = (R(2).standard_normal((c0, width)) / np.sqrt(c0)).astype(np.float32)
+    x10 = R(3).standard_normal((batch, max(c1, 1))).astype(np.float32)
+    W10 = (R(4).standard_normal((max(c1, 1), width)) / np.sqrt(max(c1, 1))).astype(np.float32)
+    bias0, dout0 = R(5).standard_normal(width).astype(np.float32), R(6).standard_normal((batch, width)).astype(np.float32)
+
+    def f(b):
+        lib = b.lib
+        x0, W0, x1, W1, bias, dout = (b.fromNumpy(v) for v in (x00, W00, x10, W10, bias0, dout0))
+        dx0, dW0, dx1, dW1, dbias = (b.fromNumpy(v * 0.5) for v in (x00, W00, x10, W10, bias0))
+        out = b.fill((batch, width), 0.0)
+        two = c1 > 0
+        onehot = c0 in (80, 26)                                         # the RNN's input: no gradient wanted
+        lib.affine_act_rows(x0, W0, c0, x1 if two else 0, W1 if two else 0, c1, bias, act, out, batch, width)
+        lib.affine_act_rows_grad(x0, 0 if onehot else dx0, W0, dW0, c0, x1 if two else 0, dx1 if two else 0, W1 if two else 0, dW1 if two else 0, c1,
+                                 dbias, act, out, dout, batch, width)
+        return {"out": out.toCPU(), "dx0": dx0.toCPU(), "dW0": dW0.toCPU(), "dx1": dx1.toCPU(), "dW1": dW1.toCPU(), "dbias": dbias.toCPU()}
+    check(f, ora, gpu)

@@ -63,3 +63,23 @@ def test_treelstm_fused_gates_equal_operator_by_operator(oracle_lib):
     assert abs(res[0][0] - res[1][0]) <= 1e-6 * abs(res[1][0])
     for a, b in zip(res[0][1], res[1][1]):
         assert np.abs(a - b).max() <= 1e-5 * max(np.abs(b).max(), 1e-12)
+
+
+def test_rnn_fused_cell_equals_operator_by_operator(oracle_lib):
+    """The recurrent cell and the output layer as one fused call each (affine_act_rows) against the operator-by-operator form."""
+    mark = oracle_lib.mark()
+    T, V, B = 20, 80, 3
+    ids = np.random.default_rng(5).integers(0, V, (T + 1, B))
+    x = np.zeros((T, B, V), np.float32)
+    x[np.arange(T)[:, None], np.arange(B)[None, :], ids[:T]] = 1.0
+    y = ids[1:].astype(np.int32).ravel()
+    res = []
+    for fused in (True, False):
+        m = _model(oracle_lib, "rnn", B)
+        m.use_fused_cells(fused)
+        loss = m.step(x.ravel(), y, 0.0, update=False)
+        res.append((loss, [m.grad(i) for i in range(m.num_params)]))
+        m.close(); oracle_lib.reset(mark)
+    assert abs(res[0][0] - res[1][0]) <= 1e-6 * abs(res[1][0])
+    for a, b in zip(res[0][1], res[1][1]):
+        assert np.abs(a - b).max() <= 2e-5 * max(np.abs(b).max(), 1e-12)
