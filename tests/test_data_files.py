@@ -184,3 +184,22 @@ def test_epoch_from_cifar_file_matches_oracle(cuda_lib, oracle_lib, tmp_path):
         assert gpu.device_status() == 0
     finally:
         gpu.set_math(1); gpu.reset(mark_g); oracle_lib.reset(mark_o)
+
+
+def test_empty_and_short_files(oracle_lib, tmp_path):
+    """An empty data file has no samples and an epoch over it runs no step; a file shorter than one batch likewise."""
+    hp = _programs(oracle_lib, True)
+    oracle_lib.set_math(0)
+    (tmp_path / "empty.bin").write_bytes(b"")
+    ld = hp.cifar_loader(tmp_path / "empty.bin")
+    assert ld.length == 0
+    with pytest.raises(IndexError):
+        ld.batch(0, 1)
+    mark = oracle_lib.mark()
+    m = hp.model("squeezenet", 4, seed=42)
+    assert len(m.train_epoch(ld, 0.005)) == 0
+    ld.close()
+    _cifar_file(tmp_path / "three.bin", 3, np.random.default_rng(9))
+    ld = hp.cifar_loader(tmp_path / "three.bin")
+    assert ld.length == 3 and len(m.train_epoch(ld, 0.005)) == 0          # three samples do not fill a batch of four
+    ld.close(); m.close(); oracle_lib.reset(mark)
