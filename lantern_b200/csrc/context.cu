@@ -28,12 +28,14 @@ int fail(int code, const char* fmt, ...) {
 struct ProfRec { const char* name; cudaEvent_t a, b; };
 static std::vector<ProfRec> prof_recs;
 void profile_before(const char* name) {
+  if (prof_recs.size() >= ((size_t)1 << 20)) { g.profiling = false; return; }     // a forgotten ltb_profile(1): stop recording, keep what is there
   ProfRec r; r.name = name;
   cudaEventCreate(&r.a); cudaEventCreate(&r.b);
   cudaEventRecord(r.a, g.stream);
   prof_recs.push_back(r);
 }
 void profile_after() { cudaEventRecord(prof_recs.back().b, g.stream); }
+static void profile_clear() { for (auto& r : prof_recs) { cudaEventDestroy(r.a); cudaEventDestroy(r.b); } prof_recs.clear(); }
 
 struct Graph { cudaGraphExec_t exec; cudaGraph_t graph; int64_t launches; };
 
@@ -51,8 +53,28 @@ int ltb_last_error(char* buf, int len) {
   return g.last;
 }
 
-int ltb_init(int device, size_t heap_bytes) {
-  if (g.inited) return fail(LTB_E_STATE, "ltb_init: already initialised");
+// Everything ltb_init obtained, in any state of completion (also the way out of a failed ltb_init).
+static void release_all() {
+  if (g.stream) cudaStreamSynchronize(g.stream);
+  if (g.side) cudaStreamSynchronize(g.side);
+  if (g.branch) cudaStreamSynchronize(g.branch);
+  if (g.branch) cudaStreamDestroy(g.branch);
+  if (g.mark_ev) cudaEventDestroy(g.mark_ev);
+  if (g.branch_done_ev) cudaEventDestroy(g.branch_done_ev);
+  if (g.heap) cudaFree(g.heap);
+  if (g.dev_status) cudaFree(g.dev_status);
+  if (g.scratch) cudaFree(g.scratch);
+  if (g.host_status) cudaFreeHost(g.host_status);
+  if (g.side) cudaStreamDestroy(g.side);
+  if (g.fork_ev) cudaEventDestroy(g.fork_ev);
+  if (g.join_ev) cudaEventDestroy(g.join_ev);
+  if (g.own_stream && g.stream) cudaStreamDestroy(g.stream);
+  const int fatal = g.fatal, last = g.last; const std::string msg = g.msg;
+  g = Context();
+  g.fatal = fatal; g.last = last; g.msg = msg;          // the error mode and the last message outlive the context
+}
+
+static int init_steps(int device, size_t heap_bytes) {
   int count = 0;
   cudaError_t e = cudaGetDeviceCount(&count);
   if (e != cudaSuccess || count == 0)
@@ -83,11 +105,21 @@ int ltb_init(int device, size_t heap_bytes) {
   LTB_CUDA(cudaEventCreateWithFlags(&g.mark_ev, cudaEventDisableTiming));
   LTB_CUDA(cudaEventCreateWithFlags(&g.branch_done_ev, cudaEventDisableTiming));
   g.launches = 0; g.last = 0; g.msg.clear(); g.capturing = false; g.math = LTB_MATH_TF32;
+  return LTB_OK;
+}
+
+int ltb_init(int device, size_t heap_bytes) {
+  if (g.inited) return fail(LTB_E_STATE, "ltb_init: already initialised");
+  const int rc = init_steps(device, heap_bytes);
+  if (rc) { release_all(); return rc; }        // non-fatal mode: a step that failed leaves nothing behind
   g.inited = true;
   return LTB_OK;
 }
 
 int ltb_comm_destroy(void);
+}
+namespace ltb { void static_sum_forget(); }
+extern "C" {
 
 // Stream markers (ltb_marker_record / ltb_marker_wait): one event per slot, created on first use.
 static cudaEvent_t marker_ev[16];
@@ -97,15 +129,10 @@ int ltb_shutdown(void) {
   if (!g.inited) return LTB_OK;
   if (g.pending.kind) flush_pending();
   ltb_comm_destroy();
-  cudaStreamSynchronize(g.stream);
-  cudaStreamSynchronize(g.side);
-  cudaStreamSynchronize(g.branch);
-  cudaStreamDestroy(g.branch); cudaEventDestroy(g.mark_ev); cudaEventDestroy(g.branch_done_ev);
-  cudaFree(g.heap); cudaFree(g.dev_status); cudaFree(g.scratch); cudaFreeHost(g.host_status);
-  cudaStreamDestroy(g.side); cudaEventDestroy(g.fork_ev); cudaEventDestroy(g.join_ev);
+  static_sum_forget();
+  profile_clear();
   for (int i = 0; i < 16; ++i) { if (marker_ev[i]) cudaEventDestroy(marker_ev[i]); marker_ev[i] = nullptr; marker_set[i] = false; }
-  if (g.own_stream) cudaStreamDestroy(g.stream);
-  g = Context();
+  release_all();
   return LTB_OK;
 }
 
@@ -248,6 +275,8 @@ int ltb_branch_join(void) {
 // ------------------------------------------------------------------ whole-step replay
 int ltb_graph_begin(void) {
   LTB_INITED(); LTB_REQUIRE(!g.capturing, "ltb_graph_begin: already recording");
+  LTB_REQUIRE(!g.profiling, "ltb_graph_begin: the launch profiler is on (its event pairs cannot be recorded into a step)");
+  LTB_REQUIRE(!g.branch_marked && !g.in_branch, "ltb_graph_begin: a branch region is open (ltb_branch_join missing)");
   LTB_CUDA(cudaStreamBeginCapture(g.stream, cudaStreamCaptureModeThreadLocal));
   g.capturing = true; g.capture_launch_base = g.launches;
   return LTB_OK;
@@ -285,7 +314,7 @@ int ltb_graph_destroy(void* graph) {
 // ltb_profile(0) stops.  ltb_profile_report writes one line per kernel name: "name<TAB>launches<TAB>total_ms".
 int ltb_profile(int on) {
   LTB_INITED(); LTB_REQUIRE(!g.capturing, "ltb_profile: not while recording a step");
-  if (on) { for (auto& r : prof_recs) { cudaEventDestroy(r.a); cudaEventDestroy(r.b); } prof_recs.clear(); }
+  if (on) profile_clear();          // a new measurement starts; the records of the last one stay readable until then
   g.profiling = on != 0;
   return LTB_OK;
 }
@@ -304,7 +333,6 @@ int ltb_profile_report(char* buf, int len) {
   strncpy(buf, out.c_str(), len - 1); buf[len - 1] = 0;
   return (int)out.size() < len ? LTB_OK : LTB_E_LIMIT;
 }
-int ltb_set_label(const char* label) { g.label = label; return LTB_OK; }
 
 // ------------------------------------------------------------------ host-RNG initialisation
 // randinit on the reference's GPU backends draws on the CPU and uploads (TensorDslCublas.scala:154-155);

@@ -48,8 +48,6 @@ struct TcParams {
   long long pix_per_img, img_stride, chan_stride, ld;
   int col_mod, col_mul;        // row-major epilogue: D column n goes to column (n % col_mod) * col_mul + n / col_mod when col_mul != 0
   int* status;
-  float* dump;                 // diagnostics buffer of CTA (0,0,0): mode 1 copies its first stage (A then B), mode 2 records cycle stamps
-  int dump_mode;
 };
 
 // ---- PTX wrappers ---------------------------------------------------------------------------------------------------
@@ -202,10 +200,6 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const int k_end = min(P.k_iters, k_begin + P.k_per_split);
   const int n_iter = k_end - k_begin;
   const int stages = P.stages;
-  // diagnostics: with a dump buffer set, CTA (0,0,0) records cycle stamps of its phases at dump[65536 + i]
-  const bool stamp = P.dump && P.dump_mode == 2 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
-  const long long t_start = stamp ? clock64() : 0;
-#define LTB_STAMP(i) do { if (stamp) P.dump[65536 + (i)] = (float)(clock64() - t_start); } while (0)
 
   // stage buffers, aligned to the 1024-byte swizzle atom
   uint8_t* stage_base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -228,7 +222,6 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_slot;
-  if (threadIdx.x == 0) LTB_STAMP(0);        // set-up done
 
   if (warp == 0) {
     BoxWalker wa, wb;
@@ -240,7 +233,6 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (it >= stages && !mbar_wait(&empty_bar[s], ph ^ 1u, &abort_flag, P.status, 1)) break;
         uint8_t* sa = stage_base + (size_t)s * stage_bytes; uint8_t* sb = sa + P.a.stage_bytes;
         mbar_expect_tx(&full_bar[s], stage_bytes);
-        if (it < 24) LTB_STAMP(40 + it);      // issue time of each of the first loads
         tma_load(&map_a, &full_bar[s], sa, P.a.rank, wa.c); wa.next(P.a);
         tma_load(&map_b, &full_bar[s], sb, P.b.rank, wb.c); wb.next(P.b);
         if (++s == stages) { s = 0; ph ^= 1u; }
@@ -260,13 +252,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       for (int it = 0; it < n_iter; ++it) {
         ok = mbar_wait(&full_bar[s], ph, &abort_flag, P.status, 2);
         if (!ok) break;
-        if (it == 0) LTB_STAMP(1);           // first stage landed
-        if (it < 24) LTB_STAMP(8 + it);      // arrival of each of the first stages
         tc_fence_after();
-        if (P.dump && P.dump_mode == 1 && it == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
-          const float* src = reinterpret_cast<const float*>(stage_base);
-          for (uint32_t i = 0; i < stage_bytes / 4; ++i) P.dump[i] = src[i];
-        }
         const uint32_t sa = (ring + (uint32_t)s * stage_bytes) >> 4, sb = sa + (a_bytes >> 4);   // in 16-byte units (ring < 256 KB: 14 bits)
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
@@ -278,7 +264,6 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (++s == stages) { s = 0; ph ^= 1u; }
       }
       if (ok) tc_commit(&accum_bar);    // accumulator complete
-      LTB_STAMP(2);                          // all MMAs issued
     }
     __syncwarp();
   } else if (n_iter > 0) {
@@ -286,7 +271,6 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int q = warp & 3, half = (warp - 2) >> 2;
     const bool ok = mbar_wait(&accum_bar, 0, &abort_flag, P.status, 3);
     tc_fence_after();
-    if (threadIdx.x == 64) LTB_STAMP(3);     // accumulator visible to the epilogue
     if (ok) {
       const int n0 = n_tile * P.bn;
       const float alpha = P.alpha;
@@ -301,14 +285,12 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           if (n0 + c0 >= P.N) break;                         // uniform across the warp
           uint32_t r[32];
           tc_ld32(tmem_row + (uint32_t)c0, r);
-          if (threadIdx.x == 64 && c0 == 0) LTB_STAMP(6);    // first accumulator chunk in registers
           if (dst) {
             const int lim = P.N - n0 - c0;
             const float* bias = (P.bias && blockIdx.z == 0) ? P.bias + n0 + c0 : nullptr;
             if (lim >= 32) store_columns<true>(dst + (long long)(n0 + c0) * cs, cs, r, alpha, bias, 32, mode);
             else store_columns<false>(dst + (long long)(n0 + c0) * cs, cs, r, alpha, bias, lim, mode);
           }
-          if (threadIdx.x == 64 && c0 == 0) LTB_STAMP(7);    // first chunk's stores issued
         }
       } else {
         // row-major output: transpose each 32x32 block through shared memory so that a warp writes 32 consecutive columns
@@ -346,10 +328,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       }
     }
   }
-  if (threadIdx.x == 64) LTB_STAMP(4);       // epilogue of warp 2 done
   tc_fence_before();
   __syncthreads();
-  if (threadIdx.x == 0) LTB_STAMP(5);        // all warps done
   if (warp == 1) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)P.bn) : "memory");
@@ -494,8 +474,6 @@ __global__ void fold_acc_kernel(const float* __restrict__ col, float* dx, ConvDi
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 static EncodeTiledFn encode_tiled = nullptr;
-static float* debug_dump = nullptr;
-static int debug_dump_mode = 1;
 static bool smem_opted_in = false;
 
 static int encode_map(const TcTensorMap& m, CUtensorMap* out) {
@@ -545,7 +523,7 @@ static int launch_plan(const TcPlan& p, const char* label) {
   P.idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)p.a.mn_major << 15) | ((uint32_t)p.b.mn_major << 16) | ((uint32_t)(p.bn >> 3) << 17) | ((128u >> 4) << 24);
   P.out = p.out; P.bias = p.bias; P.alpha = p.alpha;
   P.pix_per_img = p.pix_per_img ? p.pix_per_img : 1; P.img_stride = p.img_stride; P.chan_stride = p.chan_stride; P.ld = p.ld; P.col_mod = p.col_mod ? p.col_mod : 1; P.col_mul = p.col_mul;
-  P.status = g.dev_status; P.dump = debug_dump; P.dump_mode = debug_dump_mode;
+  P.status = g.dev_status;
   // 4 stages, except 3 for 128-wide tiles so that two CTAs (2 x 97 KB) share an SM and one's epilogue overlaps the other's main loop
   P.stages = p.bn == 128 ? 3 : kMaxStages;
   const size_t smem = (size_t)P.stages * (p.a.stage_bytes + p.b.stage_bytes) + 1024;
@@ -578,11 +556,6 @@ static int launch_plan(const TcPlan& p, const char* label) {
   g.label = saved;
   return LTB_OK;
 }
-
-}  // namespace ltb
-// Diagnostics hook (not part of the public header): the next engine launches copy the first pipeline stage of CTA (0,0,0) to buf.
-extern "C" int ltb_debug_tc_dump(float* buf, int mode) { ltb::debug_dump = buf; ltb::debug_dump_mode = mode; return 0; }
-namespace ltb {
 
 int gemm_tc(const float* a, bool a_kmajor, const float* b, bool b_kmajor, float* c, bool, int M, int N, int K, float alpha, bool accumulate) {
   TcPlan p;
@@ -815,7 +788,8 @@ int conv_wgrad_tc(const float* x, const float* dy, float* dw, const ConvDims& d)
     int rc0 = launch_unfold(x, col, d); if (rc0) return rc0;
     xin = col;
   }
-  tc_plan_conv_wgrad(p, xin, dy, dw, d.N, ck, d.K, pix, g.sm_count);
+  // the probe above used dy in place of x: the caller's x may still be declined (a view that is not 16-byte aligned)
+  if (!tc_plan_conv_wgrad(p, xin, dy, dw, d.N, ck, d.K, pix, g.sm_count)) { if (col) temp_free(col, n); return 0; }
   int rc = launch_plan(p, "tc_gemm_kernel[conv_wgrad]");
   if (col) temp_free(col, n);
   return rc ? rc : 1;

@@ -197,15 +197,25 @@ constexpr int64_t kStaticSumMaxN = (int64_t)1 << 30;
 constexpr int kStaticSumMaxDevices = 64;
 static __device__ __align__(256) float static_sum_scratch[kStaticSumSlots];
 static float* static_sum_ptr[kStaticSumMaxDevices] = {};
+}  // extern "C"
+namespace ltb { void static_sum_forget() { for (auto& p : static_sum_ptr) p = nullptr; } }   // ltb_shutdown: a later context looks the address up again
+extern "C" {
 
 int ltb_sum_static_scratch(const float* x, float* out, int64_t n) {
   LTB_INITED(); LTB_REQUIRE(x && out && n >= 0, "ltb_sum_static_scratch: bad argument");
   if (n > kStaticSumMaxN)
     return fail(LTB_E_LIMIT, "ltb_sum_static_scratch: %lld elements exceed the limit of %lld", (long long)n, (long long)kStaticSumMaxN);
   LTB_REQUIRE(g.device >= 0 && g.device < kStaticSumMaxDevices, "ltb_sum_static_scratch: device index out of range");
-  if (!static_sum_ptr[g.device]) {                        // set-up, once per device (the context's device is current)
+  if (!static_sum_ptr[g.device]) {                        // set-up, once per device
+    // A symbol's address belongs to the device that is current in the calling thread, which need not be the context's
+    // (another thread of the host may have selected a different GPU): select ours for the look-up and put the caller's back.
+    LTB_REQUIRE(!g.capturing, "ltb_sum_static_scratch: the first call on a device does its set-up and must come before a step is recorded");
+    int prev = -1;
+    LTB_CUDA(cudaGetDevice(&prev));
+    if (prev != g.device) LTB_CUDA(cudaSetDevice(g.device));
     float* p = nullptr;
     cudaError_t e = cudaGetSymbolAddress((void**)&p, static_sum_scratch);
+    if (prev != g.device) cudaSetDevice(prev);
     if (e != cudaSuccess || !p) return fail(LTB_E_CUDA, "ltb_sum_static_scratch: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
     static_sum_ptr[g.device] = p;
   }

@@ -464,6 +464,54 @@ def test_empty_ragged_and_misaligned_vectors(ora, gpu, n):
     check(f, ora, gpu)
 
 
+def test_sgd_step_over_a_list_of_tensors(ora, gpu):
+    """ltb_sgd_step_multi: one launch over a list of parameter tensors of ragged sizes (an empty one and misaligned ones
+    among them) gives what ltb_sgd_step gives tensor by tensor: x -= lr * d, d = 0."""
+    import ctypes
+    sizes = [1, 7, 0, 64, 1023, 4096, 100003, 5]
+    xs0 = [R(10 + i).standard_normal(n + 1).astype(np.float32) for i, n in enumerate(sizes)]
+    ds0 = [R(50 + i).standard_normal(n + 1).astype(np.float32) for i, n in enumerate(sizes)]
+
+    def f(b):
+        xf = [b.fromNumpy(a) for a in xs0]; df = [b.fromNumpy(a) for a in ds0]
+        off = [i % 2 for i in range(len(sizes))]                               # every other tensor starts one float past a 16-byte boundary
+        xp = (ctypes.c_void_p * len(sizes))(*[t.ptr + 4 * o for t, o in zip(xf, off)])
+        dp = (ctypes.c_void_p * len(sizes))(*[t.ptr + 4 * o for t, o in zip(df, off)])
+        sz = (ctypes.c_int64 * len(sizes))(*sizes)
+        b.lib.sgd_step_multi(ctypes.addressof(xp), ctypes.addressof(dp), ctypes.addressof(sz), len(sizes), 0.25)
+        out = {}
+        for i, (t, d) in enumerate(zip(xf, df)):
+            out["x%d" % i], out["d%d" % i] = t.toCPU(), d.toCPU()
+        return out
+    a = f(ora)
+    check(f, ora, gpu)
+    for i, (n, o) in enumerate(zip(sizes, [i % 2 for i in range(len(sizes))])):   # and against the formula itself; elements outside the spans untouched
+        want = xs0[i].copy(); want[o:o + n] -= np.float32(0.25) * ds0[i][o:o + n]
+        assert np.allclose(a["x%d" % i], want, rtol=1e-6, atol=1e-7)
+        dz = ds0[i].copy(); dz[o:o + n] = 0
+        assert np.array_equal(a["d%d" % i], dz)
+
+
+def test_pointwise_weight_grad_with_a_misaligned_input_view(ora, gpu):
+    """A 1x1 convolution whose x is a view one float past a 16-byte boundary: the tensor-core weight-gradient plan must
+    decline it (TMA needs 16-byte bases) and the FP32 path take over, not a half-built plan reach the launch."""
+    N, C, H, K = 4, 64, 8, 64
+    xv = R(1).standard_normal(N * C * H * H + 1).astype(np.float32)
+    w0 = (R(2).standard_normal((K, C, 1, 1)) / 8).astype(np.float32)
+    dy0 = R(3).standard_normal((N, K, H, H)).astype(np.float32)
+
+    def f(b, math=1):
+        b.lib.set_math(math)
+        x = b.fromNumpy(xv).offset(1, (N, C, H, H))
+        w = TensorR(b.fromNumpy(w0)); dy = b.fromNumpy(dy0)
+        dx = b.zeros(N, C, H, H)
+        b.lib.conv2d_bwd(x.ptr, dx.ptr, w.x.ptr, w.d.ptr, 0, dy.ptr, N, C, H, H, K, 1, 1, 1, 1, 0, 0)
+        return {"dw": w.d.toCPU(), "dx": dx.toCPU()}
+    got, ref = f(gpu, 1), f(ora, 0)
+    assert_close(ref["dw"], got["dw"], FP32_RTOL, "dw (declined by the engine: FP32 path)")
+    assert_close(ref["dx"], got["dx"], TF32_RTOL, "dx (dy and w are aligned: tensor-core path)")
+
+
 # ---------------------------------------------------------------------------------------------- branch regions
 @pytest.mark.parametrize("replay", [False, True])
 def test_branch_region_gives_the_results_of_program_order(gpu, replay):

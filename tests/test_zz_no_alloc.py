@@ -21,13 +21,17 @@ def test_static_scratch_sum_equals_sum_twice_in_a_row(cuda_lib):
     lib = cuda_lib
     mark = lib.mark()
     try:
+        import torch
         rng = np.random.default_rng(5)
+        torch.cuda.mem_get_info(0)                                  # the first query may itself set something up: not counted
         for n in (1, 1000, 65536, 65537, 1 << 20, (1 << 24) + 13):
             a = rng.standard_normal(n).astype(np.float32)
             x = _upload(lib, a)
             want, got = lib.malloc(256), lib.malloc(256)
             lib.sum(x, want, n)
             used = lib.arena_used()
+            lib.sync()
+            free_before = torch.cuda.mem_get_info(0)[0]             # cudaMemGetInfo: what the driver still has to give on this device
             for call in range(2):                                   # two calls in a row: the second reuses the scratch as the first left it
                 lib.fill(got, -7.0, 1)
                 lib.sum_static_scratch(x, got, n)
@@ -35,6 +39,7 @@ def test_static_scratch_sum_equals_sum_twice_in_a_row(cuda_lib):
                 assert _read1(lib, got) == _read1(lib, want), (n, call)
                 assert abs(float(_read1(lib, got)) - float(a.astype(np.float64).sum())) <= 1e-4 * max(1.0, np.abs(a).sum())
             assert lib.arena_used() == used                         # no arena block taken either
+            assert torch.cuda.mem_get_info(0)[0] == free_before     # and nothing obtained from the driver: the device's free memory is unchanged
         assert lib.device_status() == 0
     finally:
         lib.reset(mark)
