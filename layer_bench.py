@@ -1,6 +1,6 @@
 """Per-layer timing of the ResNet-50 (CIFAR shape) convolutions through the C ABI.
 
-    python -m lantern_b200.layer_bench [--batch 128] [--reps 10] [--math tf32|fp32]
+    python layer_bench.py [--batch 128] [--reps 10] [--math tf32|fp32]
 
 For every distinct convolution shape of the network it times forward, data-grad and weight-grad separately with the
 library's launch profiler (CUDA events around every kernel on the launching stream), flushing the L2 cache between calls,
@@ -14,14 +14,11 @@ import sys
 
 import numpy as np
 
-sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
 
 def distinct_convs():
-    import importlib.util
-    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    spec = importlib.util.spec_from_file_location("bench", os.path.join(root, "bench.py"))
-    mod = importlib.util.module_from_spec(spec); spec.loader.exec_module(mod)
+    import bench as mod                  # the workload arithmetic lives beside this file
     counts = {}
     for c in mod.resnet50_convs():
         counts[c] = counts.get(c, 0) + 1

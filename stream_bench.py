@@ -1,6 +1,6 @@
 """Timing of the memory-bound operators at the ResNet-50 (CIFAR shape) sizes, against the HBM roofline.
 
-    python -m lantern_b200.stream_bench [--batch 128] [--reps 10] [--no-flush] [--json out.json]
+    python stream_bench.py [--batch 128] [--reps 10] [--no-flush] [--json out.json]
 
 Every operator is called through the C ABI on tensors of the sizes the training step uses and timed with the
 library's launch profiler (CUDA events around every kernel on the launching stream). Between calls a 256 MB buffer
@@ -21,14 +21,11 @@ import sys
 
 import numpy as np
 
-sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
 def shapes(batch):
     """(C, H) of every conv output (batch-norm input) and of every residual sum of ResNet-50, with multiplicities."""
-    import importlib.util
-    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    spec = importlib.util.spec_from_file_location("bench", os.path.join(root, "bench.py"))
-    mod = importlib.util.module_from_spec(spec); spec.loader.exec_module(mod)
+    import bench as mod                  # the workload arithmetic lives beside this file
     bn, add = {}, {}
     for (ci, co, k, s, p, h) in mod.resnet50_convs():
         ho = (h + 2 * p - k) // s + 1
