@@ -75,6 +75,16 @@ int    LTB_FN(set_math)(int mode);                      /* LTB_MATH_TF32 (defaul
  * get_stream and graph_end included). A host that enqueues its own work on the stream must call get_stream or sync first. */
 int    LTB_FN(set_fusion)(int on);
 int    LTB_FN(device_status)(void);                     /* 0, or LTB_E_DEVICE if a kernel's bounded wait expired */
+/* Failure detection on the device (no counterpart in the reference, whose kernels never wait on anything). Every spin wait
+ * inside a kernel of this library (on a TMA or tensor-core completion barrier) gives up after a limit, records a code in
+ * a status word that device_status reads, and lets the kernel run to its normal end, so the context stays usable.
+ *   set_wait_limit:         the limit in SM clock ticks (default 2e9, about a second);
+ *   clear_device_status:    back to 0 (stream-ordered);
+ *   selftest_bounded_wait:  launches one warp that waits, through the same wait routine, on a barrier at which nothing
+ *                           ever arrives: after `cycles` ticks device_status reports LTB_E_DEVICE. Nothing faults or hangs. */
+int    LTB_FN(set_wait_limit)(int64_t cycles);
+int    LTB_FN(clear_device_status)(void);
+int    LTB_FN(selftest_bounded_wait)(int64_t cycles);
 int64_t LTB_FN(kernel_launches)(void);                  /* kernels launched by this library so far */
 
 /* ---------------------------------------------------------------- arena
@@ -305,6 +315,11 @@ int LTB_FN(comm_unique_id)(void* out128);
 int LTB_FN(comm_init)(int rank, int world, const void* id128);
 int LTB_FN(comm_destroy)(void);
 int LTB_FN(comm_world)(void);
+/* Failure detection between ranks: while a communicator exists, every host-side wait on the library's stream (sync, d2h,
+ * marker_wait) polls NCCL's asynchronous error state and gives up after this many milliseconds (default 60000; 0 = wait for
+ * ever). On an error or a timeout the communicator is aborted, the call returns LTB_E_COMM, and later collectives are
+ * refused with LTB_E_COMM until comm_destroy / comm_init. */
+int LTB_FN(comm_set_timeout_ms)(int64_t ms);
 int LTB_FN(allreduce_sum)(float* x, int64_t n);
 /* Starts, while backward is still running, the sum of a gradient range that is already final; the allreduce_sgd_step
  * that follows over a span containing it only waits for that sum. No-op with one rank. */

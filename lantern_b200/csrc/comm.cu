@@ -8,6 +8,7 @@
 #include <cstring>
 
 #include "buckets.h"
+#include "comm_wait.h"
 #include "common.cuh"
 
 namespace ltb {
@@ -25,7 +26,11 @@ struct Nccl {
   int (*CommDestroy)(ncclComm_t) = nullptr;
   int (*AllReduce)(const void*, void*, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
   const char* (*GetErrorString)(int) = nullptr;
+  int (*CommGetAsyncError)(ncclComm_t, int*) = nullptr;     // failure detection: polled while the host waits for a step
+  int (*CommAbort)(ncclComm_t) = nullptr;
   ncclComm_t comm = nullptr;
+  bool broken = false;               // the communicator was aborted after a failure or a timeout: collectives are refused from then on
+  int64_t timeout_ms = 60000;        // how long the host waits for a stream that carries collectives (ltb_comm_set_timeout_ms)
   int rank = 0, world = 1;
   cudaStream_t comm_stream = nullptr;
   cudaEvent_t ready = nullptr;
@@ -44,6 +49,7 @@ static int load_nccl() {
 #define LTB_SYM(field, name) do { *(void**)(&nccl.field) = dlsym(nccl.handle, name); if (!nccl.field) return fail(LTB_E_COMM, "libnccl lacks %s", name); } while (0)
   LTB_SYM(GetUniqueId, "ncclGetUniqueId"); LTB_SYM(CommInitRank, "ncclCommInitRank"); LTB_SYM(CommDestroy, "ncclCommDestroy");
   LTB_SYM(AllReduce, "ncclAllReduce"); LTB_SYM(GetErrorString, "ncclGetErrorString");
+  LTB_SYM(CommGetAsyncError, "ncclCommGetAsyncError"); LTB_SYM(CommAbort, "ncclCommAbort");
 #undef LTB_SYM
   return LTB_OK;
 }
@@ -59,6 +65,41 @@ __global__ void sgd_scaled_kernel(float* x, float* d, float neg_lr_over_world, i
     reinterpret_cast<float4*>(x)[j] = xv; reinterpret_cast<float4*>(d)[j] = z;
   }
   for (int64_t j = n4 * 4 + i; j < n; j += stride) { x[j] += d[j] * neg_lr_over_world; d[j] = 0.0f; }
+}
+
+// ---- failure detection ---------------------------------------------------------------------------------------------------
+// A rank that leaves (a crash, an exception in its host program) makes its peers' next collective wait for ever, and a plain
+// cudaStreamSynchronize behind it never returns.  Whenever the host blocks on the library's stream while a communicator
+// exists (ltb_sync, ltb_d2h, ltb_marker_wait) it therefore polls instead: the stream or event, NCCL's asynchronous error
+// state, and a deadline.  On an error or when the deadline passes the communicator is aborted (which ends its kernels on
+// the device, so the stream drains), further collectives are refused, and the call returns LTB_E_COMM.
+static int comm_failed(const char* what, int why) {
+  if (nccl.comm && nccl.CommAbort) nccl.CommAbort(nccl.comm);
+  nccl.comm = nullptr; nccl.broken = true;
+  // the aborted kernels end promptly; give the streams a moment to drain so that the context stays usable
+  bounded_wait([] { return cudaStreamQuery(g.stream) != cudaErrorNotReady; }, [] { return false; }, 5000);
+  if (nccl.comm_stream) bounded_wait([] { return cudaStreamQuery(nccl.comm_stream) != cudaErrorNotReady; }, [] { return false; }, 5000);
+  return fail(LTB_E_COMM, "%s: %s; the communicator was aborted", what,
+              why == WAIT_TIMEOUT ? "a collective did not finish within the communicator's timeout (a rank has left?)" : "NCCL reported an asynchronous error");
+}
+static bool comm_async_error() {
+  int e = ncclSuccess;
+  return nccl.comm && nccl.CommGetAsyncError && (nccl.CommGetAsyncError(nccl.comm, &e) != ncclSuccess || e != ncclSuccess);
+}
+bool comm_active() { return nccl.comm != nullptr; }
+int comm_wait_stream(cudaStream_t s, const char* what) {
+  cudaError_t last = cudaSuccess;
+  const int r = bounded_wait([&] { last = cudaStreamQuery(s); return last != cudaErrorNotReady; }, comm_async_error, nccl.timeout_ms);
+  if (r != WAIT_DONE) return comm_failed(what, r);
+  if (last != cudaSuccess) return fail(LTB_E_CUDA, "%s: %s", what, cudaGetErrorString(last));
+  return LTB_OK;
+}
+int comm_wait_event(cudaEvent_t ev, const char* what) {
+  cudaError_t last = cudaSuccess;
+  const int r = bounded_wait([&] { last = cudaEventQuery(ev); return last != cudaErrorNotReady; }, comm_async_error, nccl.timeout_ms);
+  if (r != WAIT_DONE) return comm_failed(what, r);
+  if (last != cudaSuccess) return fail(LTB_E_CUDA, "%s: %s", what, cudaGetErrorString(last));
+  return LTB_OK;
 }
 
 }  // namespace ltb
@@ -99,15 +140,23 @@ int ltb_comm_destroy(void) {
     for (auto& e : nccl.done) cudaEventDestroy(e);
     for (auto& e : nccl.early) cudaEventDestroy(e.done);
   }
+  else if (nccl.broken && nccl.comm_stream) {        // aborted earlier: the communicator is gone, its stream and events are not
+    cudaStreamDestroy(nccl.comm_stream); cudaEventDestroy(nccl.ready);
+    for (auto& e : nccl.done) cudaEventDestroy(e);
+    for (auto& e : nccl.early) cudaEventDestroy(e.done);
+  }
+  nccl.comm_stream = nullptr; nccl.broken = false;
   nccl.n_early = 0;
   nccl.world = 1; nccl.rank = 0;
   return LTB_OK;
 }
 int ltb_comm_world(void) { return nccl.world; }
+int ltb_comm_set_timeout_ms(int64_t ms) { nccl.timeout_ms = ms; return LTB_OK; }
 
 int ltb_allreduce_sum(float* x, int64_t n) {
   LTB_INITED(); LTB_REQUIRE(x && n >= 0, "ltb_allreduce_sum: bad argument");
   if (nccl.world == 1 || n == 0) return LTB_OK;
+  if (nccl.broken) return fail(LTB_E_COMM, "ltb_allreduce_sum: the communicator was aborted");
   LTB_NCCL(nccl.AllReduce(x, x, (size_t)n, ncclFloat, ncclSum, nccl.comm, g.stream));
   return LTB_OK;
 }
@@ -117,6 +166,7 @@ int ltb_allreduce_sum(float* x, int64_t n) {
 int ltb_allreduce_begin(float* d, int64_t n) {
   LTB_INITED(); LTB_REQUIRE(d && n >= 0, "ltb_allreduce_begin: bad argument");
   if (nccl.world == 1 || n == 0) return LTB_OK;
+  if (nccl.broken) return fail(LTB_E_COMM, "ltb_allreduce_begin: the communicator was aborted");
   if (nccl.n_early == Nccl::kMaxEarly) return LTB_OK;              // no slot left: the range is simply reduced at the step
   Nccl::Early& e = nccl.early[nccl.n_early];
   LTB_CUDA(cudaEventRecord(nccl.ready, g.stream));
@@ -140,6 +190,7 @@ int ltb_allreduce_sgd_step(float* x, float* d, float lr, int64_t n) {
   LTB_INITED(); LTB_REQUIRE(x && d && n >= 0, "ltb_allreduce_sgd_step: bad argument");
   if (nccl.world == 1) return ltb_sgd_step(x, d, lr, n);
   if (n == 0) return LTB_OK;
+  if (nccl.broken) return fail(LTB_E_COMM, "ltb_allreduce_sgd_step: the communicator was aborted");
   const float s = -1.0f * lr / (float)nccl.world;
   // early ranges inside [d, d + n), sorted by address; the gaps between them are what is still to be reduced
   int order[Nccl::kMaxEarly], ne = 0;

@@ -49,6 +49,7 @@ struct Context {
   int64_t capture_launch_base = 0;
   int* dev_status = nullptr;          // device word set by kernels whose bounded waits run out
   int* host_status = nullptr;         // pinned mirror
+  int64_t wait_limit_cycles = 2000000000ll;   // bound of every device-side spin wait (about a second; ltb_set_wait_limit)
   float* scratch = nullptr;           // private workspace for multi-stage reductions
   size_t scratch_bytes = 0;
   int sm_count = kSMs;
@@ -75,6 +76,10 @@ int flush_pending();                 // issues the held operation on its own (el
 int bn_fwd_issue(const Pending& p, bool relu);
 int add_issue(const float* a, const float* b, float* out, int64_t n, bool relu);
 int relu_grad_issue(const float* y, float* d, int64_t n);
+// Host waits while a communicator exists: bounded, with NCCL's asynchronous error state polled (comm.cu).
+bool comm_active();
+int comm_wait_stream(cudaStream_t s, const char* what);
+int comm_wait_event(cudaEvent_t ev, const char* what);
 void profile_before(const char* name);
 void profile_after();
 

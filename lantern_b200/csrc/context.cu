@@ -143,7 +143,13 @@ int ltb_set_stream(void* s) {
   return LTB_OK;
 }
 void* ltb_get_stream(void) { if (g.inited && g.pending.kind) flush_pending(); return (void*)g.stream; }   // the caller may enqueue its own work next
-int ltb_sync(void) { LTB_INITED(); LTB_CUDA(cudaStreamSynchronize(g.stream)); return LTB_OK; }
+// With a communicator the wait is bounded and watches for a failed collective (comm.cu: comm_wait_stream).
+static int stream_wait(const char* what) {
+  if (comm_active()) return comm_wait_stream(g.stream, what);
+  LTB_CUDA(cudaStreamSynchronize(g.stream));
+  return LTB_OK;
+}
+int ltb_sync(void) { LTB_INITED(); return stream_wait("ltb_sync"); }
 int ltb_set_fusion(int on) { LTB_INITED(); g.fusion = on != 0; return LTB_OK; }
 int ltb_set_math(int mode) {
   LTB_REQUIRE(mode == LTB_MATH_FP32 || mode == LTB_MATH_TF32, "ltb_set_math: unknown mode %d", mode);
@@ -155,6 +161,11 @@ int ltb_device_status(void) {
   if (cudaMemcpyAsync(g.host_status, g.dev_status, 4, cudaMemcpyDeviceToHost, g.stream) != cudaSuccess) return LTB_E_CUDA;
   if (cudaStreamSynchronize(g.stream) != cudaSuccess) return LTB_E_CUDA;
   return g.host_status[0] ? LTB_E_DEVICE : LTB_OK;
+}
+int ltb_clear_device_status(void) {
+  LTB_INITED();
+  LTB_CUDA(cudaMemsetAsync(g.dev_status, 0, 4, g.stream));
+  return LTB_OK;
 }
 int64_t ltb_kernel_launches(void) { return g.launches; }
 
@@ -201,8 +212,7 @@ int ltb_d2h(void* dst, const void* src, size_t bytes) {
   LTB_INITED(); LTB_REQUIRE(dst && src, "ltb_d2h: null pointer");
   LTB_REQUIRE(!g.capturing, "ltb_d2h: blocking read-back while recording a step");
   if (bytes) LTB_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, g.stream));
-  LTB_CUDA(cudaStreamSynchronize(g.stream));
-  return LTB_OK;
+  return stream_wait("ltb_d2h");
 }
 int ltb_d2d(void* dst, const void* src, size_t bytes) {
   LTB_INITED(); LTB_REQUIRE(dst && src, "ltb_d2d: null pointer");
@@ -230,7 +240,10 @@ int ltb_marker_record(int slot) {
 }
 int ltb_marker_wait(int slot) {
   LTB_INITED_NOFLUSH(); LTB_REQUIRE(slot >= 0 && slot < 16, "ltb_marker_wait: slot %d out of range", slot);
-  if (marker_set[slot]) LTB_CUDA(cudaEventSynchronize(marker_ev[slot]));
+  if (marker_set[slot]) {
+    if (comm_active()) return comm_wait_event(marker_ev[slot], "ltb_marker_wait");
+    LTB_CUDA(cudaEventSynchronize(marker_ev[slot]));
+  }
   return LTB_OK;
 }
 

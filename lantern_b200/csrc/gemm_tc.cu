@@ -31,7 +31,6 @@ namespace ltb {
 
 constexpr int kMaxStages = 4;
 constexpr int kTcThreads = 320;                    // warp 0 TMA, warp 1 MMA, warps 2..9 epilogue
-constexpr long long kWaitCycles = 2000000000ll;    // bound of every spin wait (~1 s)
 
 struct TcOperandDev {
   int t_div[5], t_mod[5], t_mul[5], k_div[5], k_mod[5], k_mul[5], c_off[5];
@@ -48,6 +47,7 @@ struct TcParams {
   long long pix_per_img, img_stride, chan_stride, ld;
   int col_mod, col_mul;        // row-major epilogue: D column n goes to column (n % col_mod) * col_mul + n / col_mod when col_mul != 0
   int* status;
+  long long wait_cycles;       // bound of every spin wait, in clock64 ticks (the context's limit, ~1 s by default)
 };
 
 // ---- PTX wrappers ---------------------------------------------------------------------------------------------------
@@ -65,12 +65,12 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait: false when it gave up (the code is recorded, the shared abort flag raised).
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int code, long long limit) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   while (!mbar_try_wait(bar, parity)) {
     if (*abort_flag) return false;
-    if (clock64() - t0 > kWaitCycles) { *abort_flag = 1; atomicExch(status, code); return false; }
+    if (clock64() - t0 > limit) { *abort_flag = 1; atomicExch(status, code); return false; }
   }
   return true;
 }
@@ -230,7 +230,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       int s = 0; uint32_t ph = 0;
       for (int it = 0; it < n_iter; ++it) {
         // the first `stages` fills find the ring empty: no wait, no barrier round trip
-        if (it >= stages && !mbar_wait(&empty_bar[s], ph ^ 1u, &abort_flag, P.status, 1)) break;
+        if (it >= stages && !mbar_wait(&empty_bar[s], ph ^ 1u, &abort_flag, P.status, 1, P.wait_cycles)) break;
         uint8_t* sa = stage_base + (size_t)s * stage_bytes; uint8_t* sb = sa + P.a.stage_bytes;
         mbar_expect_tx(&full_bar[s], stage_bytes);
         tma_load(&map_a, &full_bar[s], sa, P.a.rank, wa.c); wa.next(P.a);
@@ -250,7 +250,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const uint32_t a_lo = P.a.desc_lo, b_lo = P.b.desc_lo, idesc = P.idesc, a_bytes = P.a.stage_bytes;
       const uint32_t ring = smem_u32(stage_base);
       for (int it = 0; it < n_iter; ++it) {
-        ok = mbar_wait(&full_bar[s], ph, &abort_flag, P.status, 2);
+        ok = mbar_wait(&full_bar[s], ph, &abort_flag, P.status, 2, P.wait_cycles);
         if (!ok) break;
         tc_fence_after();
         const uint32_t sa = (ring + (uint32_t)s * stage_bytes) >> 4, sb = sa + (a_bytes >> 4);   // in 16-byte units (ring < 256 KB: 14 bits)
@@ -269,7 +269,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   } else if (n_iter > 0) {
     // ---- epilogue warps 2..9: TMEM lane quarter = warp index mod 4; the two warps of a quarter take alternate 32-column chunks
     const int q = warp & 3, half = (warp - 2) >> 2;
-    const bool ok = mbar_wait(&accum_bar, 0, &abort_flag, P.status, 3);
+    const bool ok = mbar_wait(&accum_bar, 0, &abort_flag, P.status, 3, P.wait_cycles);
     tc_fence_after();
     if (ok) {
       const int n0 = n_tile * P.bn;
@@ -523,7 +523,7 @@ static int launch_plan(const TcPlan& p, const char* label) {
   P.idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)p.a.mn_major << 15) | ((uint32_t)p.b.mn_major << 16) | ((uint32_t)(p.bn >> 3) << 17) | ((128u >> 4) << 24);
   P.out = p.out; P.bias = p.bias; P.alpha = p.alpha;
   P.pix_per_img = p.pix_per_img ? p.pix_per_img : 1; P.img_stride = p.img_stride; P.chan_stride = p.chan_stride; P.ld = p.ld; P.col_mod = p.col_mod ? p.col_mod : 1; P.col_mul = p.col_mul;
-  P.status = g.dev_status;
+  P.status = g.dev_status; P.wait_cycles = g.wait_limit_cycles;
   // 4 stages, except 3 for 128-wide tiles so that two CTAs (2 x 97 KB) share an SM and one's epilogue overlaps the other's main loop
   P.stages = p.bn == 128 ? 3 : kMaxStages;
   const size_t smem = (size_t)P.stages * (p.a.stage_bytes + p.b.stage_bytes) + 1024;
@@ -556,6 +556,32 @@ static int launch_plan(const TcPlan& p, const char* label) {
   g.label = saved;
   return LTB_OK;
 }
+
+// Self-test of the bounded wait: one warp waits, through the engine's own mbar_wait, on a barrier at which nothing ever
+// arrives.  No copy is in flight and no tensor memory is held, so when the limit runs out the kernel simply records code 9
+// in the status word and returns; the context stays usable.
+__global__ void wait_selftest_kernel(int* status, long long limit) {
+  __shared__ __align__(8) uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) { mbar_init(&bar, 1); abort_flag = 0; asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+  __syncthreads();
+  if (threadIdx.x == 0) mbar_wait(&bar, 0, &abort_flag, status, 9, limit);
+  __syncthreads();
+}
+
+}  // namespace ltb
+extern "C" {
+int ltb_set_wait_limit(int64_t cycles) {
+  LTB_INITED(); LTB_REQUIRE(cycles > 0, "ltb_set_wait_limit: the limit must be positive");
+  ltb::g.wait_limit_cycles = cycles; return LTB_OK;
+}
+int ltb_selftest_bounded_wait(int64_t cycles) {
+  LTB_INITED(); LTB_REQUIRE(cycles > 0 && cycles <= 4000000000ll, "ltb_selftest_bounded_wait: limit out of range (1 .. 4e9 cycles)");
+  LTB_LAUNCH(ltb::wait_selftest_kernel, 1, 32, 0, ltb::g.dev_status, (long long)cycles);
+  return LTB_OK;
+}
+}
+namespace ltb {
 
 int gemm_tc(const float* a, bool a_kmajor, const float* b, bool b_kmajor, float* c, bool, int M, int N, int K, float alpha, bool accumulate) {
   TcPlan p;

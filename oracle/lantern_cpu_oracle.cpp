@@ -24,15 +24,19 @@
 // reference's shipped generated MNIST program compiled from its own source).
 #define LTB_FN(name) ora_##name
 #include "../include/lantern_b200.h"
+#include "../lantern_b200/csrc/comm_wait.h"   // the product's bounded host wait (policy shared with the CPU communicator below)
 #include "../lantern_b200/csrc/tc_plan.h"   // eligibility rule of the product's tensor-core engine (shape arithmetic only)
 #include "../lantern_b200/csrc/buckets.h"   // all-reduce bucket spans (host arithmetic only)
 
+#include <atomic>
 #include <cfloat>
 #include <cmath>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <memory>
 #include <string>
+#include <thread>
 #include <vector>
 #ifdef _OPENMP
 #include <omp.h>
@@ -204,6 +208,10 @@ int ora_sync(void) { return LTB_OK; }
 int ora_set_fusion(int) { return LTB_OK; }   // the CPU build executes every call at once
 int ora_set_math(int mode) { g.math = mode; return LTB_OK; }
 int ora_device_status(void) { return LTB_OK; }
+// The device-side bounded waits have no CPU counterpart: there is nothing to wait for.
+int ora_set_wait_limit(int64_t) { return LTB_OK; }
+int ora_clear_device_status(void) { return LTB_OK; }
+int ora_selftest_bounded_wait(int64_t) { return LTB_OK; }
 int64_t ora_kernel_launches(void) { return 0; }
 // Not in the shared header: number of host threads the oracle may use (1 = the reference's protocol,
 // OPENBLAS_NUM_THREADS=1 in src/out/NIPS18evaluation/run_exp.sh:12).
@@ -958,26 +966,46 @@ int ora_momentum_update(float* x, float* d, float* m, float lr, float mu, float 
 typedef int (*ora_allreduce_fn)(float* buf, int64_t n);
 static ora_allreduce_fn g_transport = nullptr;
 static int g_world = 1;
+// Failure detection, as in the CUDA library (csrc/comm.cu): a sum is waited for through the same bounded_wait
+// (csrc/comm_wait.h) with the communicator's timeout; a transport error or a timeout marks the communicator broken, the call
+// returns LTB_E_COMM and later collectives are refused until comm_destroy.  The transport runs on a helper thread so that
+// the wait can give up on it (a rank that has left makes a blocking transport wait for as long as its own timeout).
+static int64_t g_timeout_ms = 60000;
+static bool g_broken = false;
+struct TransportCall { std::atomic<int> state{0}; int rc = 0; };      // 0 running, 1 finished
+static int transport_sum(float* buf, int64_t n, const char* who) {
+  if (g_broken) return fail(LTB_E_COMM, (std::string(who) + ": the communicator was aborted").c_str());
+  auto call = std::make_shared<TransportCall>();
+  const ora_allreduce_fn fn = g_transport;
+  std::thread([call, fn, buf, n] { call->rc = fn(buf, n); call->state.store(1); }).detach();
+  const int r = ltb::bounded_wait([&] { return call->state.load() == 1 && call->rc == 0; },
+                                  [&] { return call->state.load() == 1 && call->rc != 0; }, g_timeout_ms);
+  if (r == ltb::WAIT_DONE) return LTB_OK;
+  g_broken = true;
+  return fail(LTB_E_COMM, (std::string(who) + (r == ltb::WAIT_TIMEOUT ? ": a collective did not finish within the communicator's timeout (a rank has left?)"
+                                                                      : ": the transport reported an error") + "; the communicator was aborted").c_str());
+}
 int ora_comm_set_transport(ora_allreduce_fn fn) { g_transport = fn; return LTB_OK; }
+int ora_comm_set_timeout_ms(int64_t ms) { g_timeout_ms = ms; return LTB_OK; }
 int ora_comm_unique_id(void* out128) { memset(out128, 0, 128); return LTB_OK; }
 int ora_comm_init(int rank, int world, const void*) {
   if (world < 1 || rank < 0 || rank >= world) return fail(LTB_E_ARG, "ora_comm_init: bad rank/world");
   if (world > 1 && !g_transport) return fail(LTB_E_COMM, "ora_comm_init: no transport installed for a multi-rank communicator");
-  g_world = world;
+  g_world = world; g_broken = false;
   return LTB_OK;
 }
-int ora_comm_destroy(void) { g_world = 1; return LTB_OK; }
+int ora_comm_destroy(void) { g_world = 1; g_broken = false; return LTB_OK; }
 int ora_comm_world(void) { return g_world; }
 int ora_allreduce_sum(float* x, int64_t n) {
   if (g_world == 1 || n == 0) return LTB_OK;
-  return g_transport(x, n) == 0 ? LTB_OK : fail(LTB_E_COMM, "ora_allreduce_sum: transport failed");
+  return transport_sum(x, n, "ora_allreduce_sum");
 }
 // Early ranges: summed at once (the transport is synchronous) and remembered, so that the step does not sum them twice.
 static struct { float* ptr; int64_t n; } g_early[16];
 static int g_n_early = 0;
 int ora_allreduce_begin(float* d, int64_t n) {
   if (g_world == 1 || n == 0 || g_n_early == 16) return LTB_OK;
-  if (g_transport(d, n) != 0) return fail(LTB_E_COMM, "ora_allreduce_begin: transport failed");
+  { const int rc = transport_sum(d, n, "ora_allreduce_begin"); if (rc) return rc; }
   g_early[g_n_early].ptr = d; g_early[g_n_early].n = n; ++g_n_early;
   return LTB_OK;
 }
@@ -996,7 +1024,7 @@ int ora_allreduce_sgd_step(float* x, float* d, float lr, int64_t n) {
     int64_t j = i; while (j < n && !done[(size_t)j]) ++j;
     int64_t off[ltb::kMaxBuckets], cnt[ltb::kMaxBuckets];
     const int used = ltb::bucket_spans(j - i, off, cnt);
-    for (int b = 0; b < used; ++b) if (g_transport(d + i + off[b], cnt[b]) != 0) return fail(LTB_E_COMM, "ora_allreduce_sgd_step: transport failed");
+    for (int b = 0; b < used; ++b) { const int rc = transport_sum(d + i + off[b], cnt[b], "ora_allreduce_sgd_step"); if (rc) return rc; }
     i = j;
   }
   for (int64_t k = 0; k < n; ++k) { x[k] += d[k] * s; d[k] = 0.0f; }

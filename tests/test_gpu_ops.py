@@ -365,6 +365,31 @@ def test_tensor_core_engine_reports_no_timeouts(gpu):
     assert gpu.lib.device_status() == 0
 
 
+def test_a_device_wait_that_runs_out_is_reported_and_the_context_stays_usable(ora, gpu):
+    """Failure detection on the device without a fault: one warp waits, through the engine's own bounded wait, on a barrier
+    at which nothing ever arrives (no copy in flight, no tensor memory held).  After the limit the kernel records a code and
+    returns; the host reads LTB_E_DEVICE, clears it, and the next tensor-core launch works as before."""
+    lib = gpu.lib
+    assert lib.device_status() == 0
+    lib.selftest_bounded_wait(200000)                    # about 0.1 ms of SM clock
+    lib.sync()
+    assert lib.device_status() == -6                     # LTB_E_DEVICE
+    assert lib.device_status() == -6                     # sticky until cleared
+    lib.clear_device_status()
+    assert lib.device_status() == 0
+    lib.set_wait_limit(3000000000)                       # the engine's own limit is a run-time value
+    try:
+        a = R(1).standard_normal((256, 64)).astype(np.float32); c = R(2).standard_normal((64, 128)).astype(np.float32)
+
+        def f(b, math=1):
+            b.lib.set_math(math)
+            return {"out": b.gemm(b.fromNumpy(a), 0, b.fromNumpy(c), 0, 1.0).toCPU()}
+        _tf32_check(f, ora, gpu)
+    finally:
+        lib.set_wait_limit(2000000000)
+    assert lib.device_status() == 0
+
+
 # ---------------------------------------------------------------------------------------------- look-ahead fusion
 @pytest.mark.parametrize("cfg", [(16, 64, 16, 16), (8, 256, 4, 4), (128, 64, 32, 32), (5, 7, 3, 5), (33, 512, 2, 2)])
 def test_lookahead_fusion_gives_the_results_of_separate_calls(ora, gpu, cfg):
