@@ -27,6 +27,7 @@ _SIGS = {
     "model_step": (ctypes.c_float, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_float, ctypes.c_int]),
     "model_step_async": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_float]),
     "model_last_loss": (ctypes.c_float, [ctypes.c_void_p]),
+    "model_logits": (ctypes.c_int64, [ctypes.c_void_p, ctypes.c_void_p]),
     "model_submit": (ctypes.c_int64, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_float]),
     "model_collect": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int64, ctypes.POINTER(ctypes.c_float)]),
     "model_train_epoch": (ctypes.c_int64, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_float, ctypes.c_void_p, ctypes.c_int64]),
@@ -157,6 +158,14 @@ class Model:
     def last_loss(self):
         return float(self.hp.fn["model_last_loss"](self.h))
 
+    def logits(self):
+        """The classifier's output of the last step as [batch, classes] (CNN programs); predictions are its arg-max per row."""
+        out = np.empty(self.batch * 10, dtype=np.float32)
+        n = self.hp.fn["model_logits"](self.h, out.ctypes.data)
+        if n != out.size:
+            raise ValueError("this program keeps no classifier output")
+        return out.reshape(self.batch, 10)
+
     def set_resident(self, x=None, y=None):
         """Keep one batch in device memory (steps then upload nothing); None switches back to per-step uploads."""
         if x is None:
@@ -166,15 +175,29 @@ class Model:
         self.hp.fn["model_set_resident"](self.h, x.ctypes.data, y.ctypes.data)
 
     def trace(self, x, y):
-        """Debug: per-operator (index, count, shape, sum|x|, sum|d|) rows of one step without update."""
+        """Debug: one row per operator output of one step without update, in forward order: (index, count, shape, sum|x|,
+        sum|d|, non-zeros of x, of d, smallest non-zero |x|, sum x^2, sum d^2, eight signed sums of x, eight of d)."""
         x, y = self._arrs(x, y)
-        buf = ctypes.create_string_buffer(1 << 20)
-        self.hp.fn["model_trace"](self.h, x.ctypes.data, y.ctypes.data, buf, 1 << 20)
+        buf = ctypes.create_string_buffer(1 << 22)
+        self.hp.fn["model_trace"](self.h, x.ctypes.data, y.ctypes.data, buf, 1 << 22)
         rows = []
         for line in buf.value.decode().strip().split("\n"):
             p = line.split()
             rows.append((int(p[0]), int(p[1]), p[2], float(p[3]), float(p[4])) + tuple(float(v) for v in p[5:]))
         return rows
+
+    @staticmethod
+    def trace_distance(rows_a, rows_b):
+        """Per operator output, the estimated relative L2 distance of value and gradient between two traces of the same
+        program (from the signed sums: the mean of their squared differences estimates |a - b|^2): [(index, shape, ex, ed)]."""
+        out = []
+        for a, b in zip(rows_a, rows_b):
+            assert a[:3] == b[:3], (a[:3], b[:3])
+            xa, xb, da, db = np.array(a[10:18]), np.array(b[10:18]), np.array(a[18:26]), np.array(b[18:26])
+            ex = float(np.sqrt(np.mean((xa - xb) ** 2) / max(a[8], 1e-300)))
+            ed = float(np.sqrt(np.mean((da - db) ** 2) / max(a[9], 1e-300))) if a[9] > 0 else 0.0
+            out.append((a[0], a[2], ex, ed))
+        return out
 
     def set_table(self, table):
         """TreeLSTM: replace the embedding table by `table` (rows x 300 float32)."""

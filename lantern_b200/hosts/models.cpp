@@ -55,6 +55,9 @@ struct Model {
   bool resident = false;       // read the batch from dev_x/dev_y instead of uploading it
   float* dev_x = nullptr; int32_t* dev_y = nullptr;
   float* dev_loss = nullptr;   // the loss of the last step, kept outside the arena span that the step resets
+  // The classifier's output of the last step (CNN programs: batch x classes), copied out of the arena span that the step
+  // resets so that predictions (arg-max per row) can be read afterwards.
+  float* dev_logits = nullptr; int64_t logit_count = 0; TR last_logits;
   // Two steps in flight (submit / collect): staging pair p = step & 1; marker p = its upload done, marker 2 + p = its step done.
   bool feeding = false;
   int64_t submitted = 0;
@@ -91,6 +94,7 @@ struct Model {
     dev_x = alloc_value((int64_t)batch * in_c * in_h * in_w);
     dev_y = (int32_t*)BK(malloc_uninit)((size_t)label_count * 4);
     dev_loss = alloc_value(1);
+    if (logit_count > 0) dev_logits = alloc_value(logit_count);
     mark = BK(mark)();
   }
   virtual TR forward(Tape& t, const TR& x, const int32_t* y) = 0;
@@ -111,7 +115,9 @@ struct Model {
       BK(h2d)(y, stage_y, (size_t)label_count * 4);
     }
     early_reduce = update && BK(comm_world)() > 1;
+    last_logits = TR();
     TR loss = forward(tape, x, y);
+    if (dev_logits && last_logits.x && last_logits.count() == logit_count) BK(d2d)(dev_logits, last_logits.x, (size_t)logit_count * 4);
     BK(fill)(loss.d, 1.0f, 1);                       // gradR_loss: y.d.setAsOne(), TD.scala:1763-1780
     BK(d2d)(dev_loss, loss.x, 4);
     tape.backward();
@@ -136,18 +142,35 @@ struct Model {
     else BK(sgd_step)(slab_x, slab_d, lr, slab_count);
   }
   std::string trace_text;
-  // One line per operator output, in forward order: index, element count, sum|x|, sum|d| (read back before the reset).
+  // One line per operator output, in forward order (read back before the reset): index, element count, shape, sum|x|,
+  // sum|d|, non-zero counts, smallest non-zero |x|, then sum x^2, sum d^2 and eight signed sums of x and of d.  A signed sum
+  // is sum_i s_k(i) v_i with s_k(i) = +-1 from a fixed hash of (i, k): for two tensors a, b the mean over k of
+  // (S_k(a) - S_k(b))^2 estimates |a - b|^2, so two libraries can be compared tensor by tensor from these few numbers.
   void dump_trace() {
     trace_text.clear();
     std::vector<float> h;
     int idx = 0;
     for (const TR& t : trace_list()) {
       int64_t n = t.count(); h.resize((size_t)n);
-      double ax = 0, ad = 0, minx = 1e30; long long nzx = 0, nzd = 0;
+      double ax = 0, ad = 0, minx = 1e30, x2 = 0, d2 = 0, px[8] = {0}, pd[8] = {0}; long long nzx = 0, nzd = 0;
+      auto signs = [](int64_t i) { uint64_t z = (uint64_t)i + 0x9E3779B97F4A7C15ull; z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull; z = (z ^ (z >> 27)) * 0x94D049BB133111EBull; return z ^ (z >> 31); };
       BK(d2h)(h.data(), t.x, (size_t)n * 4);
-      for (int64_t i = 0; i < n; ++i) { double v = std::fabs((double)h[i]); ax += v; if (v != 0) { ++nzx; if (v < minx) minx = v; } }
-      if (t.d) { BK(d2h)(h.data(), t.d, (size_t)n * 4); for (int64_t i = 0; i < n; ++i) { ad += std::fabs((double)h[i]); nzd += h[i] != 0; } }
-      char line[200]; snprintf(line, sizeof line, "%d %lld [%d,%d,%d,%d] %.9e %.9e %lld %lld %.3e\n", idx++, (long long)n, t.shape[0], t.shape[1], t.shape[2], t.shape[3], ax, ad, nzx, nzd, minx);
+      for (int64_t i = 0; i < n; ++i) {
+        const double v = h[i], a = std::fabs(v); ax += a; x2 += v * v; if (a != 0) { ++nzx; if (a < minx) minx = a; }
+        const uint64_t s = signs(i); for (int k = 0; k < 8; ++k) px[k] += ((s >> k) & 1) ? v : -v;
+      }
+      if (t.d) {
+        BK(d2h)(h.data(), t.d, (size_t)n * 4);
+        for (int64_t i = 0; i < n; ++i) {
+          const double v = h[i]; ad += std::fabs(v); d2 += v * v; nzd += h[i] != 0;
+          const uint64_t s = signs(i); for (int k = 0; k < 8; ++k) pd[k] += ((s >> (8 + k)) & 1) ? v : -v;
+        }
+      }
+      char line[1024];
+      int w = snprintf(line, sizeof line, "%d %lld [%d,%d,%d,%d] %.9e %.9e %lld %lld %.3e %.9e %.9e", idx++, (long long)n, t.shape[0], t.shape[1], t.shape[2], t.shape[3], ax, ad, nzx, nzd, minx, x2, d2);
+      for (int k = 0; k < 8; ++k) w += snprintf(line + w, sizeof line - w, " %.9e", px[k]);
+      for (int k = 0; k < 8; ++k) w += snprintf(line + w, sizeof line - w, " %.9e", pd[k]);
+      snprintf(line + w, sizeof line - w, "\n");
       trace_text += line;
     }
     trace_list().clear();
@@ -225,7 +248,7 @@ struct Model {
 struct Mnist : Model {
   int c1w, c1b, c2w, c2b, l1w, l1b, l2w, l2b;
   Mnist(int b, int seed) {
-    name = "mnist"; batch = b; in_c = 1; in_h = in_w = 28;
+    name = "mnist"; batch = b; in_c = 1; in_h = in_w = 28; logit_count = (int64_t)b * 10;
     // Conv2D: uniform(+-sqrt(6/fan_in)) == (rand-0.5)*2*sqrt(6/fan_in), bias 0 (NNModule.scala:128-146);
     // Linear1D: (rand-0.5)/sqrt(in), weight stored [in,out] (NNModule.scala:112-117).
     c1w = declare({10, 1, 5, 5}, INIT_RAND, 2.0f * sqrtf(6.0f / 25.0f));  c1b = declare({10}, INIT_ZERO);
@@ -243,6 +266,7 @@ struct Mnist : Model {
     TR flat = view(s25, {batch, 320});
     TR s3 = t.dropout(t.plus_bias(t.dot(flat, P(l1w)), P(l1b)), 0.5f);
     TR out = t.plus_bias(t.dot(s3, P(l2w)), P(l2b));
+    last_logits = out;
     return t.sum(t.nll(t.log_softmax(out), y));
   }
 };
@@ -422,12 +446,15 @@ struct ResNet50 : Model {
     cb.rmean = declare({cout}, INIT_ZERO); cb.rvar = declare({cout}, INIT_ONE);
     return cb;
   }
-  ResNet50(int b, int seed) {
-    name = "resnet50"; batch = b; in_c = 3; in_h = in_w = 32;
+  // max_blocks < 16 gives a prefix of the network (stem, max pool, the first max_blocks bottleneck blocks) closed by an
+  // average pool over the whole remaining map and the classifier: shallow enough for its TF32 gradients to be compared
+  // tightly, made of exactly the layer types and the issue order of the full program.
+  ResNet50(int b, int seed, int max_blocks = 16) {
+    name = max_blocks < 16 ? "resnet50_prefix" : "resnet50"; batch = b; in_c = 3; in_h = in_w = 32; logit_count = (int64_t)b * 10;
     stem = conv_bn(3, 64, 3);
     int inplanes = 64; const int layers[4] = {3, 4, 6, 3}; const int planes[4] = {64, 128, 256, 512};
     for (int s = 0; s < 4; ++s)
-      for (int i = 0; i < layers[s]; ++i) {
+      for (int i = 0; i < layers[s] && (int)blocks.size() < max_blocks; ++i) {
         Block bl; bl.stride = (i == 0 && s > 0) ? 2 : 1;
         bl.a = conv_bn(inplanes, planes[s], 1); bl.b = conv_bn(planes[s], planes[s], 3); bl.c = conv_bn(planes[s], planes[s] * 4, 1);
         bl.has_down = (i == 0);
@@ -435,7 +462,7 @@ struct ResNet50 : Model {
         inplanes = planes[s] * 4;
         blocks.push_back(bl);
       }
-    fcw = declare({10, 2048}, INIT_RAND, 1.0f / sqrtf(2048.0f)); fcb = declare({10}, INIT_ZERO);
+    fcw = declare({10, inplanes}, INIT_RAND, 1.0f / sqrtf((float)inplanes)); fcb = declare({10}, INIT_ZERO);
     finalize(seed);
   }
   TR cbn(Tape& t, const TR& x, const ConvBN& p, int stride, int pad, bool relu) {
@@ -447,7 +474,7 @@ struct ResNet50 : Model {
     const size_t stage_start[3] = {3, 7, 13};            // first block of stages 2, 3, 4: the slab above each is final when backward gets there
     for (size_t bi = 0; bi < blocks.size(); ++bi) {       // Bottleneck.forward, resnet50.py:72-93
       const Block& bl = blocks[bi];
-      for (int k = 0; k < 3; ++k)
+      for (int k = 0; k < 3 && blocks.size() == 16; ++k)
         if (bi == stage_start[k]) reduce_when_final(t, bl.a.w, k == 2 ? slab_count : decls[blocks[stage_start[k + 1]].a.w].offset);
       // A block with a shortcut convolution has two runs of calls that meet only at the sum: the shortcut (conv + BN) is
       // issued as a branch beside the three conv + BN of the main path.  Backward replays the tape in reverse, so every
@@ -468,9 +495,10 @@ struct ResNet50 : Model {
       }
       h = t.relu(t.binary(LTB_ADD, o, res), true);
     }
-    TR p = t.avg_pool(h, 2, 1);
-    TR flat = view(p, {batch, 2048});
+    TR p = t.avg_pool(h, h.shape[2], 1);                                         // 2x2 on the full network's last map
+    TR flat = view(p, {batch, h.shape[1]});
     TR logits = t.plus_bias(t.gemm(flat, false, P(fcw), true, 1.0f), P(fcb));   // ONNX Gemm, ONNXLib.scala:956-974
+    last_logits = logits;
     return t.mean(t.nll(t.log_softmax(logits), y));                              // resnet50FromOnnx.scala:153-156
   }
 };
@@ -484,7 +512,7 @@ struct SqueezeNet : Model {
     Conv c; c.w = declare({cout, cin, k, k}, INIT_RAND, 2.0f * sqrtf(6.0f / (float)(cin * k * k))); c.b = declare({cout}, INIT_ZERO); return c;
   }
   SqueezeNet(int b, int seed) {
-    name = "squeezenet"; batch = b; in_c = 3; in_h = in_w = 32;
+    name = "squeezenet"; batch = b; in_c = 3; in_h = in_w = 32; logit_count = (int64_t)b * 10;
     first = conv(3, 96, 3);
     const int cfg[8][4] = {{96, 16, 64, 64}, {128, 16, 64, 64}, {128, 32, 128, 128}, {256, 32, 128, 128},
                            {256, 48, 192, 192}, {384, 48, 192, 192}, {384, 64, 256, 256}, {512, 64, 256, 256}};
@@ -509,6 +537,7 @@ struct SqueezeNet : Model {
     h = fire(t, h, fires[7]);
     TR lb = P(last.b);
     TR logits = view(t.conv(h, P(last.w), &lb, 1, 0), {batch, 10});
+    last_logits = logits;
     return t.mean(t.nll(t.log_softmax(logits), y));
   }
 };
@@ -522,6 +551,7 @@ void* HOST_FN(model_create)(const char* name, int batch, int seed) {
   BK(set_fusion)(1);     // generated programs issue every device operation through the library: the one-call look-ahead is safe
   if (n == "mnist") return new Mnist(batch, seed);
   if (n == "resnet50") return new ResNet50(batch, seed);
+  if (n == "resnet50_prefix") return new ResNet50(batch, seed, 1);        // stem + the first bottleneck block + classifier
   if (n == "squeezenet") return new SqueezeNet(batch, seed);
   if (n == "rnn") return new VanillaRnn(batch, seed, 80, 100);
   if (n == "rnn_26_50") return new VanillaRnn(batch, seed, 26, 50);     // sizes of src/out/NIPS18evaluation/evaluationRNN/Lantern.cpp
@@ -592,6 +622,12 @@ int HOST_FN(model_step_async)(void* m, const float* x_host, const int32_t* y_hos
 int64_t HOST_FN(model_submit)(void* m, const float* x_host, const int32_t* y_host, float lr) { return ((Model*)m)->submit(x_host, y_host, lr); }
 int HOST_FN(model_collect)(void* m, int64_t step, float* loss) { return ((Model*)m)->collect(step, loss); }
 float HOST_FN(model_last_loss)(void* m) { return *((Model*)m)->loss_host; }
+// The classifier's output of the last step (batch x classes floats); returns the number of floats, 0 for programs without one.
+int64_t HOST_FN(model_logits)(void* m, float* host_out) {
+  Model* M = (Model*)m;
+  if (!M->dev_logits || BK(d2h)(host_out, M->dev_logits, (size_t)M->logit_count * 4)) return 0;
+  return M->logit_count;
+}
 
 // ---- data and parameter files in the reference's formats (loader.hpp)
 void* HOST_FN(loader_open_floats)(const char* data_path, const char* target_path, int64_t floats_per_sample, float mean, float stdev) {

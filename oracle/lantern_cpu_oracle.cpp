@@ -28,6 +28,7 @@
 #include "../lantern_b200/csrc/tc_plan.h"   // eligibility rule of the product's tensor-core engine (shape arithmetic only)
 #include "../lantern_b200/csrc/buckets.h"   // all-reduce bucket spans (host arithmetic only)
 
+#include <algorithm>
 #include <atomic>
 #include <cfloat>
 #include <cmath>
@@ -39,6 +40,7 @@
 #include <thread>
 #include <vector>
 #ifdef _OPENMP
+#include <immintrin.h>
 #include <omp.h>
 #endif
 
@@ -94,10 +96,58 @@ int fail(int code, const char* what) {
   }
   return code;
 }
+// Wall-clock time per entry point (ora_profile / ora_profile_report): where a CPU step spends its time.
+struct ProfEntry { const char* name; double seconds; long long calls; };
+static ProfEntry g_prof[160]; static int g_prof_n = 0; static bool g_prof_on = false;
+struct ProfScope {
+  const char* name; double t0; bool on;
+  explicit ProfScope(const char* n) : name(n), t0(0), on(g_prof_on) { if (on) t0 = omp_get_wtime(); }
+  ~ProfScope() {
+    if (!on) return;
+    const double dt = omp_get_wtime() - t0;
+    for (int i = 0; i < g_prof_n; ++i) if (g_prof[i].name == name) { g_prof[i].seconds += dt; ++g_prof[i].calls; return; }
+    if (g_prof_n < 160) g_prof[g_prof_n++] = ProfEntry{name, dt, 1};
+  }
+};
 #define REQUIRE(cond, what) do { if (!(cond)) return fail(LTB_E_ARG, what); } while (0)
 
 const size_t kGranule = 256;
 size_t round_up(size_t b) { return (b + kGranule - 1) / kGranule * kGranule; }
+
+// S[i][j] = sum over k = 0 .. K-1, in that order, of A(i,k) * B[k][j], every element a float sum of its own (fused multiply-add,
+// which is what the compiler makes of `acc += a * b` in the plain loops as well).  A(i,k) = A[i*ais + k*aks]; B is row-major
+// with ldb floats per row; S is row-major with lds floats per row and is overwritten.  A register tile of 4 rows x 16 columns
+// keeps the partial sums out of memory; the order of the additions per element is that of the plain loop, so results are
+// the same bit for bit.  `threads` > 1 spreads the row blocks over that many threads.
+void gemm_seq(int M, int N, int K, const float* A, size_t ais, size_t aks, const float* B, size_t ldb, float* S, size_t lds, int threads) {
+  const int row_blocks = (M + 3) / 4;
+#pragma omp parallel for if (threads > 1 && row_blocks > 1) num_threads(threads) schedule(static)
+  for (int ib = 0; ib < row_blocks; ++ib) {
+    const int i0 = ib * 4, rows = std::min(4, M - i0);
+    int j0 = 0;
+    for (; j0 + 16 <= N; j0 += 16) {
+      __m256 acc[4][2];
+      for (int r = 0; r < 4; ++r) { acc[r][0] = _mm256_setzero_ps(); acc[r][1] = _mm256_setzero_ps(); }
+      const float* a0 = A + (size_t)i0 * ais;
+      for (int k = 0; k < K; ++k) {
+        const float* b = B + (size_t)k * ldb + j0;
+        const __m256 b0 = _mm256_loadu_ps(b), b1 = _mm256_loadu_ps(b + 8);
+        for (int r = 0; r < rows; ++r) {
+          const __m256 a = _mm256_set1_ps(a0[(size_t)r * ais + (size_t)k * aks]);
+          acc[r][0] = _mm256_fmadd_ps(a, b0, acc[r][0]); acc[r][1] = _mm256_fmadd_ps(a, b1, acc[r][1]);
+        }
+      }
+      for (int r = 0; r < rows; ++r) { _mm256_storeu_ps(S + (size_t)(i0 + r) * lds + j0, acc[r][0]); _mm256_storeu_ps(S + (size_t)(i0 + r) * lds + j0 + 8, acc[r][1]); }
+    }
+    for (; j0 < N; ++j0)                                   // the ragged columns, one at a time
+      for (int r = 0; r < rows; ++r) {
+        float acc = 0.0f;
+        const float* a = A + (size_t)(i0 + r) * ais;
+        for (int k = 0; k < K; ++k) acc = __builtin_fmaf(a[(size_t)k * aks], B[(size_t)k * ldb + j0], acc);
+        S[(size_t)(i0 + r) * lds + j0] = acc;
+      }
+  }
+}
 
 // Plain row-major sgemm with the cblas contract: C = alpha*op(A)*op(B) + beta*C.
 // Summation over k is sequential in float for every output element.
@@ -156,6 +206,7 @@ void shadow_strides(const int* shape, int rank, int64_t* st) {
 }
 int64_t prod(const int* s, int rank) { int64_t p = 1; for (int i = 0; i < rank; ++i) p *= s[i]; return p; }
 
+bool same_shape(const int* a, const int* b, int rank) { for (int i = 0; i < rank; ++i) if (a[i] != b[i]) return false; return true; }
 bool bcast_shape(const int* a, const int* b, int rank, int* r) {
   if (rank < 1 || rank > 8) return false;
   for (int i = 0; i < rank; ++i) {
@@ -202,20 +253,20 @@ int ora_last_error(char* buf, int len) {
   if (buf && len > 0) { strncpy(buf, g.msg.c_str(), len - 1); buf[len - 1] = 0; }
   return g.last;
 }
-int ora_set_stream(void*) { return LTB_OK; }
+int ora_set_stream(void*) { ProfScope prof_scope_("ora_set_stream"); return LTB_OK; }
 void* ora_get_stream(void) { return nullptr; }
-int ora_sync(void) { return LTB_OK; }
-int ora_set_fusion(int) { return LTB_OK; }   // the CPU build executes every call at once
-int ora_set_math(int mode) { g.math = mode; return LTB_OK; }
+int ora_sync(void) { ProfScope prof_scope_("ora_sync"); return LTB_OK; }
+int ora_set_fusion(int) { ProfScope prof_scope_("ora_set_fusion"); return LTB_OK; }   // the CPU build executes every call at once
+int ora_set_math(int mode) { ProfScope prof_scope_("ora_set_math"); g.math = mode; return LTB_OK; }
 int ora_device_status(void) { return LTB_OK; }
 // The device-side bounded waits have no CPU counterpart: there is nothing to wait for.
-int ora_set_wait_limit(int64_t) { return LTB_OK; }
-int ora_clear_device_status(void) { return LTB_OK; }
-int ora_selftest_bounded_wait(int64_t) { return LTB_OK; }
+int ora_set_wait_limit(int64_t) { ProfScope prof_scope_("ora_set_wait_limit"); return LTB_OK; }
+int ora_clear_device_status(void) { ProfScope prof_scope_("ora_clear_device_status"); return LTB_OK; }
+int ora_selftest_bounded_wait(int64_t) { ProfScope prof_scope_("ora_selftest_bounded_wait"); return LTB_OK; }
 int64_t ora_kernel_launches(void) { return 0; }
 // Not in the shared header: number of host threads the oracle may use (1 = the reference's protocol,
 // OPENBLAS_NUM_THREADS=1 in src/out/NIPS18evaluation/run_exp.sh:12).
-int ora_set_threads(int n) { g.threads = n < 1 ? 1 : n; return LTB_OK; }
+int ora_set_threads(int n) { ProfScope prof_scope_("ora_set_threads"); g.threads = n < 1 ? 1 : n; return LTB_OK; }
 
 void* ora_malloc(size_t bytes) {
   if (!g.inited) { fail(LTB_E_STATE, "ora_malloc: not initialised"); return nullptr; }
@@ -225,65 +276,65 @@ void* ora_malloc(size_t bytes) {
   return p;  // zero: calloc at start, memset on reset/free
 }
 void* ora_malloc_uninit(size_t bytes) { return ora_malloc(bytes); }
-int ora_free(void* p, size_t bytes) {
+int ora_free(void* p, size_t bytes) { ProfScope prof_scope_("ora_free");
   size_t b = round_up(bytes);
   if (!p || b > g.used || (char*)p != g.heap + g.used - b) return fail(LTB_E_ARG, "ora_free: not the newest block");
   memset(p, 0, b); g.used -= b; return LTB_OK;
 }
 void* ora_mark(void) { return g.heap + g.used; }
-int ora_reset(void* mark) {
+int ora_reset(void* mark) { ProfScope prof_scope_("ora_reset");
   char* m = (char*)mark;
   if (m < g.heap || m > g.heap + g.used) return fail(LTB_E_ARG, "ora_reset: mark outside the used span");
   memset(m, 0, g.heap + g.used - m); g.used = m - g.heap; return LTB_OK;
 }
 size_t ora_arena_used(void) { return g.used; }
-int ora_h2d(void* d, const void* s, size_t n) { memcpy(d, s, n); return LTB_OK; }
-int ora_d2h(void* d, const void* s, size_t n) { memcpy(d, s, n); return LTB_OK; }
-int ora_d2d(void* d, const void* s, size_t n) { memmove(d, s, n); return LTB_OK; }
+int ora_h2d(void* d, const void* s, size_t n) { ProfScope prof_scope_("ora_h2d"); memcpy(d, s, n); return LTB_OK; }
+int ora_d2h(void* d, const void* s, size_t n) { ProfScope prof_scope_("ora_d2h"); memcpy(d, s, n); return LTB_OK; }
+int ora_d2d(void* d, const void* s, size_t n) { ProfScope prof_scope_("ora_d2d"); memmove(d, s, n); return LTB_OK; }
 
 // ------------------------------------------------------------------ fill / init
 // fill, fillInPlace: TensorDslCPU.scala:30-35, 65-67.
-int ora_fill(float* x, float v, int64_t n) { for (int64_t i = 0; i < n; ++i) x[i] = v; return LTB_OK; }
+int ora_fill(float* x, float v, int64_t n) { ProfScope prof_scope_("ora_fill"); for (int64_t i = 0; i < n; ++i) x[i] = v; return LTB_OK; }
 // fillWithBias: TensorDslCPU.scala:41-61.
-int ora_fill_with_bias(float* out, const float* bias, int outer, int c, int inner) {
+int ora_fill_with_bias(float* out, const float* bias, int outer, int c, int inner) { ProfScope prof_scope_("ora_fill_with_bias");
   REQUIRE(out && bias && outer >= 0 && c >= 0 && inner >= 0, "fill_with_bias: bad argument");
   size_t off = 0;
   for (int h = 0; h < outer; ++h) for (int cd = 0; cd < c; ++cd) for (int l = 0; l < inner; ++l) out[off++] = bias[cd];
   return LTB_OK;
 }
 // randinit: TensorDslCPU.scala:101-110 with Random.rand() = (float)rand()/RAND_MAX (TD.scala:1018-1026).
-int ora_randinit(float* x, int64_t n, float scale, int seed) {
+int ora_randinit(float* x, int64_t n, float scale, int seed) { ProfScope prof_scope_("ora_randinit");
   if (seed >= 0) srand((unsigned)seed);
   for (int64_t i = 0; i < n; ++i) x[i] = ((float)rand() / RAND_MAX - 0.5f) * scale;
   return LTB_OK;
 }
 // clipAt: TensorDslCPU.scala:113-119.
-int ora_clip(float* x, float bound, int64_t n) {
+int ora_clip(float* x, float bound, int64_t n) { ProfScope prof_scope_("ora_clip");
   for (int64_t i = 0; i < n; ++i) { float t = x[i]; if (t > bound) x[i] = bound; if (t < -1.0f * bound) x[i] = -1.0f * bound; }
   return LTB_OK;
 }
 
 // ------------------------------------------------------------------ dot family
 // vectorVectorDot: TensorDslCPU.scala:135-144.
-int ora_vv_dot(const float* x, const float* y, float* out, int n) {
+int ora_vv_dot(const float* x, const float* y, float* out, int n) { ProfScope prof_scope_("ora_vv_dot");
   float v = 0.0f; for (int i = 0; i < n; ++i) v += x[i] * y[i]; out[0] = v; return LTB_OK;
 }
 // dot_grad case (1,1): addMul(output.d.data(0), other), TensorDslCPU.scala:173-175, TD.scala:766-773.
-int ora_vv_dot_grad(float* dx, float* dy, const float* x, const float* y, const float* dout, int n) {
+int ora_vv_dot_grad(float* dx, float* dy, const float* x, const float* y, const float* dout, int n) { ProfScope prof_scope_("ora_vv_dot_grad");
   float a = dout[0];
   if (dx) for (int i = 0; i < n; ++i) dx[i] = dx[i] + a * y[i];
   if (dy) for (int i = 0; i < n; ++i) dy[i] = dy[i] + a * x[i];
   return LTB_OK;
 }
 // matrixVectorDot: cblas_sgemv NoTrans beta 0, TensorDslCPU.scala:146-156.
-int ora_mv_dot(const float* a, const float* x, float* out, int m, int k) {
+int ora_mv_dot(const float* a, const float* x, float* out, int m, int k) { ProfScope prof_scope_("ora_mv_dot");
   for (int i = 0; i < m; ++i) { float s = 0.0f; for (int j = 0; j < k; ++j) s += a[(size_t)i * k + j] * x[j]; out[i] = s; }
   return LTB_OK;
 }
 // Fused affine map with activation: the composition of matrixVectorDot (TensorDslCPU.scala:148-156), the broadcasting
 // adds and tanh / sigmoid (748-766) that the unfused programs issue, sums in the same sequential float order per product.
 int ora_affine_act(const float* W0, const float* a, int cols0, const float* W1, const float* b, int cols1, const float* bias,
-                   int act, float* out, int rows) {
+                   int act, float* out, int rows) { ProfScope prof_scope_("ora_affine_act");
   REQUIRE(W0 && a && bias && out && rows > 0 && cols0 > 0 && (W1 == nullptr) == (b == nullptr), "affine_act: bad argument");
   REQUIRE(act == -1 || act == LTB_TANH || act == LTB_SIGMOID, "affine_act: activation must be tanh, sigmoid or -1");
   for (int r = 0; r < rows; ++r) {
@@ -297,7 +348,7 @@ int ora_affine_act(const float* W0, const float* a, int cols0, const float* W1, 
   return LTB_OK;
 }
 int ora_affine_act_grad(const float* W0, float* dW0, const float* a, float* da, int cols0, const float* W1, float* dW1,
-                        const float* b, float* db, int cols1, float* dbias, int act, const float* out, const float* dout, int rows) {
+                        const float* b, float* db, int cols1, float* dbias, int act, const float* out, const float* dout, int rows) { ProfScope prof_scope_("ora_affine_act_grad");
   REQUIRE(W0 && dW0 && a && dbias && out && dout && rows > 0 && cols0 > 0, "affine_act_grad: bad argument");
   REQUIRE((W1 == nullptr) == (b == nullptr) && (W1 == nullptr) == (dW1 == nullptr), "affine_act_grad: W1, dW1 and b go together");
   for (int r = 0; r < rows; ++r) {
@@ -313,7 +364,7 @@ int ora_affine_act_grad(const float* W0, float* dW0, const float* a, float* da, 
 // Batched form: matrixMatrixDot (TensorDslCPU.scala:158-169) with the broadcasting adds and the activation; every sum runs
 // sequentially over its index in float, as the cblas restatement above does.
 int ora_affine_act_rows(const float* x0, const float* W0, int cols0, const float* x1, const float* W1, int cols1, const float* bias,
-                        int act, float* out, int batch, int width) {
+                        int act, float* out, int batch, int width) { ProfScope prof_scope_("ora_affine_act_rows");
   REQUIRE(x0 && W0 && bias && out && cols0 > 0 && batch > 0 && width > 0 && (x1 == nullptr) == (W1 == nullptr), "affine_act_rows: bad argument");
   REQUIRE(act == -1 || act == LTB_TANH || act == LTB_SIGMOID, "affine_act_rows: activation must be tanh, sigmoid or -1");
   for (int b = 0; b < batch; ++b) for (int j = 0; j < width; ++j) {
@@ -328,7 +379,7 @@ int ora_affine_act_rows(const float* x0, const float* W0, int cols0, const float
 }
 int ora_affine_act_rows_grad(const float* x0, float* dx0, const float* W0, float* dW0, int cols0, const float* x1, float* dx1,
                              const float* W1, float* dW1, int cols1, float* dbias, int act, const float* out, const float* dout,
-                             int batch, int width) {
+                             int batch, int width) { ProfScope prof_scope_("ora_affine_act_rows_grad");
   REQUIRE(x0 && W0 && dW0 && dbias && out && dout && cols0 > 0 && batch > 0 && width > 0, "affine_act_rows_grad: bad argument");
   REQUIRE((x1 == nullptr) == (W1 == nullptr) && (W1 == nullptr) == (dW1 == nullptr) && (W1 || !dx1), "affine_act_rows_grad: x1, W1 and dW1 go together");
   std::vector<float> dpre((size_t)batch * width);
@@ -355,7 +406,7 @@ int ora_affine_act_rows_grad(const float* x0, float* dx0, const float* W0, float
 // The elementwise part of an LSTM cell: the products, in-place sums and tanh the unfused programs issue
 // (TensorDslCPU.scala:227-374 elementwise, 748-758 tanh), in the same order of float operations.
 int ora_lstm_cell(const float* i, const float* u, const float* fl, const float* cl, const float* fr, const float* cr,
-                  const float* o, float* c, float* tc, float* h, int n) {
+                  const float* o, float* c, float* tc, float* h, int n) { ProfScope prof_scope_("ora_lstm_cell");
   REQUIRE(i && u && o && c && tc && h && n > 0, "lstm_cell: bad argument");
   REQUIRE((fl && cl && fr && cr) || (!fl && !cl && !fr && !cr), "lstm_cell: the four child operands go together");
   for (int k = 0; k < n; ++k) {
@@ -368,7 +419,7 @@ int ora_lstm_cell(const float* i, const float* u, const float* fl, const float* 
 }
 int ora_lstm_cell_grad(const float* i, float* di, const float* u, float* du, const float* fl, float* dfl, const float* cl, float* dcl,
                        const float* fr, float* dfr, const float* cr, float* dcr, const float* o, float* d_o,
-                       const float* tc, const float* dc, const float* dh, int n) {
+                       const float* tc, const float* dc, const float* dh, int n) { ProfScope prof_scope_("ora_lstm_cell_grad");
   REQUIRE(i && di && u && du && o && d_o && tc && dc && dh && n > 0, "lstm_cell_grad: bad argument");
   REQUIRE((fl && dfl && cl && dcl && fr && dfr && cr && dcr) || (!fl && !dfl && !cl && !dcl && !fr && !dfr && !cr && !dcr),
           "lstm_cell_grad: the child operands and their gradients go together");
@@ -382,37 +433,37 @@ int ora_lstm_cell_grad(const float* i, float* di, const float* u, float* du, con
   return LTB_OK;
 }
 // matrixMatrixDot: TensorDslCPU.scala:158-169.
-int ora_mm_dot(const float* a, const float* b, float* out, int m, int k, int n) {
+int ora_mm_dot(const float* a, const float* b, float* out, int m, int k, int n) { ProfScope prof_scope_("ora_mm_dot");
   sgemm_m(false, false, m, n, k, 1.0f, a, k, b, n, 0.0f, out, n); return LTB_OK;
 }
 // add_cartesian: TensorDslCPU.scala:186-196.
-int ora_add_cartesian(float* da, const float* y, const float* dout, int m, int k) {
+int ora_add_cartesian(float* da, const float* y, const float* dout, int m, int k) { ProfScope prof_scope_("ora_add_cartesian");
   for (int i = 0; i < m; ++i) for (int j = 0; j < k; ++j) da[(size_t)i * k + j] = da[(size_t)i * k + j] + y[j] * dout[i];
   return LTB_OK;
 }
 // add_composition: cblas_sgemv Trans beta 1, TensorDslCPU.scala:198-206.
-int ora_add_composition(float* dx, const float* a, const float* dout, int m, int k) {
+int ora_add_composition(float* dx, const float* a, const float* dout, int m, int k) { ProfScope prof_scope_("ora_add_composition");
   for (int j = 0; j < k; ++j) { float s = 0.0f; for (int i = 0; i < m; ++i) s += a[(size_t)i * k + j] * dout[i]; dx[j] += s; }
   return LTB_OK;
 }
 // add_dotTrans1: x += y^T . output, TensorDslCPU.scala:208-215.
-int ora_add_dot_trans1(float* db, const float* a, const float* dc, int m, int k, int n) {
+int ora_add_dot_trans1(float* db, const float* a, const float* dc, int m, int k, int n) { ProfScope prof_scope_("ora_add_dot_trans1");
   sgemm_m(true, false, k, n, m, 1.0f, a, k, dc, n, 1.0f, db, n); return LTB_OK;
 }
 // add_dotTrans2: x += y . output^T, TensorDslCPU.scala:217-225.
-int ora_add_dot_trans2(float* da, const float* dc, const float* b, int m, int k, int n) {
+int ora_add_dot_trans2(float* da, const float* dc, const float* b, int m, int k, int n) { ProfScope prof_scope_("ora_add_dot_trans2");
   sgemm_m(false, true, m, k, n, 1.0f, dc, n, b, n, 1.0f, da, k); return LTB_OK;
 }
 
 // gemm: TensorDslCPU.scala:379-426 (four cblas_sgemm cases, beta 0).
-int ora_gemm(const float* a, int ta, const float* b, int tb, float alpha, float* c, int M, int N, int K) {
+int ora_gemm(const float* a, int ta, const float* b, int tb, float alpha, float* c, int M, int N, int K) { ProfScope prof_scope_("ora_gemm");
   REQUIRE(a && b && c && M > 0 && N > 0 && K > 0, "gemm: bad argument");
   sgemm_m(ta, tb, M, N, K, alpha, a, ta ? M : K, b, tb ? K : N, 0.0f, c, N);
   return LTB_OK;
 }
 // gemm_grad: TensorDslCPU.scala:428-472 (beta 1 in all eight calls).
 int ora_gemm_grad(const float* a, float* da, int ta, const float* b, float* db, int tb, float alpha, const float* dc,
-                  int M, int N, int K) {
+                  int M, int N, int K) { ProfScope prof_scope_("ora_gemm_grad");
   REQUIRE(a && b && dc && M > 0 && N > 0 && K > 0, "gemm_grad: bad argument");
   if (!ta && !tb) {
     if (da) sgemm_m(false, true, M, K, N, alpha, dc, N, b, N, 1.0f, da, K);
@@ -473,7 +524,7 @@ void unfolded_acc(const float* finput, float* input, int kW, int kH, int dW, int
 // conv2D_batch: TensorDslCPU.scala:532-571. Output pre-filled with the bias (or zero), then per image
 // im2col + sgemm(Cout x HoWo x CinKhKw, beta 1).
 int ora_conv2d_fwd(const float* x, const float* w, const float* bias, float* y, int N, int C, int H, int W, int K, int R,
-                   int S, int sh, int sw, int ph, int pw) {
+                   int S, int sh, int sw, int ph, int pw) { ProfScope prof_scope_("ora_conv2d_fwd");
   REQUIRE(x && w && y && N > 0 && C > 0 && K > 0 && R > 0 && S > 0 && sh > 0 && sw > 0 && ph >= 0 && pw >= 0, "conv2d_fwd: bad argument");
   int oH = (H + 2 * ph - R) / sh + 1, oW = (W + 2 * pw - S) / sw + 1;
   REQUIRE(oH > 0 && oW > 0, "conv2d_fwd: empty output");
@@ -482,26 +533,34 @@ int ora_conv2d_fwd(const float* x, const float* w, const float* bias, float* y, 
   const bool full_image = R == H && S == W && ph == 0 && pw == 0 && R * S > 1;
   const bool tf = tc_conv_taken(0, N, C * R * S, K, (int)ohw, full_image);
   std::vector<float> wt; if (tf) { wt = truncated(w, (size_t)K * C * R * S); w = wt.data(); }
-  const bool par = g.threads > 1 && N > 1;
+  // Images are independent, so they run in parallel; images whose output map is small (fewer than 64 pixels) are taken
+  // several at a time with their unfolded columns side by side, so that the innermost loop stays long.  Every output
+  // element is still its own float sum over k = 0 .. C*R*S - 1 in order, added to the bias: the grouping changes no value.
+  const int G = ohw >= 64 ? 1 : (int)std::min<size_t>((size_t)N, (64 + ohw - 1) / ohw);
+  const int groups = (N + G - 1) / G;
+  const bool par = g.threads > 1 && groups > 1;
 #pragma omp parallel for if (par) num_threads(g.threads) schedule(static)
-  for (int t = 0; t < N; ++t) {
-    std::vector<float> fin((size_t)C * R * S * ohw);
-    unfolded_copy(fin.data(), x + (size_t)t * C * H * W, S, R, sw, sh, pw, ph, C, W, H, oW, oH);
-    if (tf) for (auto& v : fin) v = tf32_trunc(v);
-    int save = g.threads; // nested sgemm stays serial inside the parallel region
-    (void)save;
-    // sgemm body inlined serially to keep per-element summation order
-    const int dim1 = K, dim2 = C * R * S, dim3 = (int)ohw;
-    float* out = y + (size_t)t * K * ohw;
-    for (int i = 0; i < dim1; ++i) {
-      std::vector<float> acc(dim3, 0.0f);
-      for (int k = 0; k < dim2; ++k) {
-        float a = w[(size_t)i * dim2 + k];
-        const float* b = fin.data() + (size_t)k * dim3;
-        for (int j = 0; j < dim3; ++j) acc[j] += a * b[j];
+  for (int gi = 0; gi < groups; ++gi) {
+    const int t0 = gi * G, gn = std::min(G, N - t0);
+    const int dim1 = K, dim2 = C * R * S, dim3 = (int)ohw, cols = gn * dim3;
+    std::vector<float> fin((size_t)dim2 * cols), one(gn > 1 ? (size_t)dim2 * dim3 : 0), acc(cols);
+    for (int u = 0; u < gn; ++u) {
+      const float* img = x + (size_t)(t0 + u) * C * H * W;
+      if (gn == 1) unfolded_copy(fin.data(), img, S, R, sw, sh, pw, ph, C, W, H, oW, oH);
+      else {
+        unfolded_copy(one.data(), img, S, R, sw, sh, pw, ph, C, W, H, oW, oH);
+        for (int k = 0; k < dim2; ++k) memcpy(fin.data() + (size_t)k * cols + (size_t)u * dim3, one.data() + (size_t)k * dim3, sizeof(float) * dim3);
       }
-      for (int j = 0; j < dim3; ++j) out[(size_t)i * dim3 + j] = acc[j] + out[(size_t)i * dim3 + j];
     }
+    if (tf) for (auto& v : fin) v = tf32_trunc(v);
+    acc.resize((size_t)dim1 * cols);
+    gemm_seq(dim1, cols, dim2, w, (size_t)dim2, 1, fin.data(), (size_t)cols, acc.data(), (size_t)cols, 1);
+    for (int i = 0; i < dim1; ++i)
+      for (int u = 0; u < gn; ++u) {
+        float* out = y + ((size_t)(t0 + u) * K + i) * ohw;
+        const float* a = acc.data() + (size_t)i * cols + (size_t)u * dim3;
+        for (int j = 0; j < dim3; ++j) out[j] = a[j] + out[j];
+      }
   }
   return LTB_OK;
 }
@@ -509,7 +568,7 @@ int ora_conv2d_fwd(const float* x, const float* w, const float* bias, float* y, 
 // conv2D_batch_grad: TensorDslCPU.scala:575-645. ConvGradInput (per image W^T.dY into the unfolded buffer, then
 // unfoldedAcc into dX) and ConvGradParam (per image dY.finput^T accumulated into dW, row sums into dbias).
 int ora_conv2d_bwd(const float* x, float* dx, const float* w, float* dw, float* dbias, const float* dy, int N, int C, int H,
-                   int W, int K, int R, int S, int sh, int sw, int ph, int pw) {
+                   int W, int K, int R, int S, int sh, int sw, int ph, int pw) { ProfScope prof_scope_("ora_conv2d_bwd");
   REQUIRE(x && w && dy && N > 0 && C > 0 && K > 0 && R > 0 && S > 0 && sh > 0 && sw > 0, "conv2d_bwd: bad argument");
   int oH = (H + 2 * ph - R) / sh + 1, oW = (W + 2 * pw - S) / sw + 1;
   size_t ohw = (size_t)oH * oW;
@@ -521,41 +580,102 @@ int ora_conv2d_bwd(const float* x, float* dx, const float* w, float* dw, float* 
     std::vector<float> wt, dyt;
     const float* dy_d = dy;
     if (tf) { wt = truncated(w, (size_t)K * ckk); w = wt.data(); dyt = truncated(dy, (size_t)N * K * ohw); dy_d = dyt.data(); }
-    const bool par = g.threads > 1 && N > 1;
+    // as in forward: images in parallel, small maps several at a time; each element of the unfolded gradient is its own
+    // sequential sum over the K output channels
+    const int G = ohw >= 64 ? 1 : (int)std::min<size_t>((size_t)N, (64 + ohw - 1) / ohw);
+    const int groups = (N + G - 1) / G;
+    const bool par = g.threads > 1 && groups > 1;
 #pragma omp parallel for if (par) num_threads(g.threads) schedule(static)
-    for (int t = 0; t < N; ++t) {
-      std::vector<float> fg((size_t)ckk * ohw);
-      const float* go = dy_d + (size_t)t * K * ohw;
-      // sgemm(Trans, NoTrans, ckk, ohw, K, 1, w, ckk, go, ohw, 0, fg, ohw)
-      for (int i = 0; i < ckk; ++i) {
-        float* row = fg.data() + (size_t)i * ohw;
-        for (size_t j = 0; j < ohw; ++j) row[j] = 0.0f;
-        for (int k = 0; k < K; ++k) {
-          float a = w[(size_t)k * ckk + i];
-          const float* b = go + (size_t)k * ohw;
-          for (size_t j = 0; j < ohw; ++j) row[j] += a * b[j];
-        }
+    for (int gi = 0; gi < groups; ++gi) {
+      const int t0 = gi * G, gn = std::min(G, N - t0);
+      const size_t cols = (size_t)gn * ohw;
+      std::vector<float> fg((size_t)ckk * cols), gog(gn > 1 ? (size_t)K * cols : 0), one(gn > 1 ? (size_t)ckk * ohw : 0);
+      const float* go = dy_d + (size_t)t0 * K * ohw;                  // [K][ohw] of the one image, or the group side by side
+      if (gn > 1) {
+        for (int u = 0; u < gn; ++u) for (int k = 0; k < K; ++k)
+          memcpy(gog.data() + (size_t)k * cols + (size_t)u * ohw, dy_d + ((size_t)(t0 + u) * K + k) * ohw, sizeof(float) * ohw);
+        go = gog.data();
       }
-      unfolded_acc(fg.data(), dx + (size_t)t * C * H * W, S, R, sw, sh, pw, ph, C, W, H, oW, oH);
+      // sgemm(Trans, NoTrans, ckk, ohw, K, 1, w, ckk, go, ohw, 0, fg, ohw)
+      gemm_seq(ckk, (int)cols, K, w, 1, (size_t)ckk, go, cols, fg.data(), cols, 1);
+      for (int u = 0; u < gn; ++u) {
+        const float* src = fg.data();
+        if (gn > 1) {
+          for (int i = 0; i < ckk; ++i) memcpy(one.data() + (size_t)i * ohw, fg.data() + (size_t)i * cols + (size_t)u * ohw, sizeof(float) * ohw);
+          src = one.data();
+        }
+        unfolded_acc(src, dx + (size_t)(t0 + u) * C * H * W, S, R, sw, sh, pw, ph, C, W, H, oW, oH);
+      }
     }
   }
   w = w_full;
   if (dw) {
-    // images are visited in order so that dW accumulates image by image as in the reference
+    // ConvGradParam, TensorDslCPU.scala:589-620: per image, sgemm(NoTrans, Trans, K, ckk, ohw, 1, dY_t, ohw, finput_t, ohw, 1, dW, ckk),
+    // i.e. every dW element gets, image after image in order, a float sum over the pixels p = 0 .. ohw - 1 added to it.
+    // The elements are independent of one another, so the work is spread over tiles of dW (4 rows x 16 columns kept in
+    // registers across the whole image loop) instead of over images; per element the order of the additions is the reference's.
+    // The unfolded inputs of all images are made first, in parallel, transposed to [pixel][filter row].
     const bool tf = tc_conv_taken(2, N, ckk, K, (int)ohw, full_image);
-    std::vector<float> fin((size_t)ckk * ohw), got;
+    std::vector<float> finT((size_t)N * ohw * ckk), dyt;
+    const bool par = g.threads > 1;
+#pragma omp parallel for if (par && N > 1) num_threads(g.threads) schedule(static)
     for (int t = 0; t < N; ++t) {
+      std::vector<float> fin((size_t)ckk * ohw);
       unfolded_copy(fin.data(), x + (size_t)t * C * H * W, S, R, sw, sh, pw, ph, C, W, H, oW, oH);
-      const float* go = dy + (size_t)t * K * ohw;
-      if (tf) { for (auto& v : fin) v = tf32_trunc(v); got = truncated(go, (size_t)K * ohw); }
-      sgemm(false, true, K, ckk, (int)ohw, 1.0f, tf ? got.data() : go, (int)ohw, fin.data(), (int)ohw, 1.0f, dw, ckk);
-      if (dbias)
-        for (int i = 0; i < K; ++i) {
-          float s = 0.0f; const float* d = go + (size_t)i * ohw;
-          for (size_t k = 0; k < ohw; ++k) s += d[k];
-          dbias[i] += 1.0f * s;
-        }
+      float* ft = finT.data() + (size_t)t * ohw * ckk;
+      for (int c = 0; c < ckk; ++c) for (size_t q = 0; q < ohw; ++q) ft[q * ckk + c] = tf ? tf32_trunc(fin[(size_t)c * ohw + q]) : fin[(size_t)c * ohw + q];
     }
+    const float* gt = dy;
+    if (tf) { dyt = truncated(dy, (size_t)N * K * ohw); gt = dyt.data(); }
+    const int row_blocks = (K + 3) / 4, col_blocks = (ckk + 15) / 16;
+    // images in runs whose 16-column slice of the unfolded inputs fits a core's cache (dW goes back to memory between runs;
+    // the order of the additions per element stays image by image)
+    const int run = (int)std::max<size_t>(1, std::min<size_t>((size_t)N, 4096 / ohw));
+    for (int tb0 = 0; tb0 < N; tb0 += run) {
+    const int tb1 = std::min(N, tb0 + run);
+#pragma omp parallel for if (par) num_threads(g.threads) schedule(static) collapse(2)
+    for (int jb = 0; jb < col_blocks; ++jb)           // column block outermost: its slice of the unfolded inputs stays in cache across the row blocks
+      for (int ib = 0; ib < row_blocks; ++ib) {
+        const int i0 = ib * 4, rows = std::min(4, K - i0), j0 = jb * 16, cols = std::min(16, ckk - j0);
+        if (cols == 16) {
+          __m256 d[4][2];
+          for (int r = 0; r < rows; ++r) { d[r][0] = _mm256_loadu_ps(dw + (size_t)(i0 + r) * ckk + j0); d[r][1] = _mm256_loadu_ps(dw + (size_t)(i0 + r) * ckk + j0 + 8); }
+          for (int t = tb0; t < tb1; ++t) {
+            const float* a0 = gt + ((size_t)t * K + i0) * ohw;
+            const float* bt = finT.data() + (size_t)t * ohw * ckk + j0;
+            __m256 acc[4][2];
+            for (int r = 0; r < 4; ++r) { acc[r][0] = _mm256_setzero_ps(); acc[r][1] = _mm256_setzero_ps(); }
+            for (size_t q = 0; q < ohw; ++q) {
+              const __m256 b0 = _mm256_loadu_ps(bt + q * ckk), b1 = _mm256_loadu_ps(bt + q * ckk + 8);
+              for (int r = 0; r < rows; ++r) {
+                const __m256 a = _mm256_set1_ps(a0[(size_t)r * ohw + q]);
+                acc[r][0] = _mm256_fmadd_ps(a, b0, acc[r][0]); acc[r][1] = _mm256_fmadd_ps(a, b1, acc[r][1]);
+              }
+            }
+            for (int r = 0; r < rows; ++r) { d[r][0] = _mm256_add_ps(acc[r][0], d[r][0]); d[r][1] = _mm256_add_ps(acc[r][1], d[r][1]); }
+          }
+          for (int r = 0; r < rows; ++r) { _mm256_storeu_ps(dw + (size_t)(i0 + r) * ckk + j0, d[r][0]); _mm256_storeu_ps(dw + (size_t)(i0 + r) * ckk + j0 + 8, d[r][1]); }
+        } else {
+          for (int r = 0; r < rows; ++r) for (int c = 0; c < cols; ++c) {
+            float dv = dw[(size_t)(i0 + r) * ckk + j0 + c];
+            for (int t = tb0; t < tb1; ++t) {
+              const float* a = gt + ((size_t)t * K + i0 + r) * ohw;
+              const float* bt = finT.data() + (size_t)t * ohw * ckk + j0 + c;
+              float acc = 0.0f;
+              for (size_t q = 0; q < ohw; ++q) acc = __builtin_fmaf(a[q], bt[q * ckk], acc);
+              dv = acc + dv;
+            }
+            dw[(size_t)(i0 + r) * ckk + j0 + c] = dv;
+          }
+        }
+      }
+    }
+    if (dbias)
+      for (int t = 0; t < N; ++t) for (int i = 0; i < K; ++i) {
+        float s = 0.0f; const float* d = dy + ((size_t)t * K + i) * ohw;
+        for (size_t k = 0; k < ohw; ++k) s += d[k];
+        dbias[i] += 1.0f * s;
+      }
   } else if (dbias) {
     for (int t = 0; t < N; ++t) for (int i = 0; i < K; ++i) {
       float s = 0.0f; const float* d = dy + ((size_t)t * K + i) * ohw;
@@ -568,7 +688,7 @@ int ora_conv2d_bwd(const float* x, float* dx, const float* w, float* dw, float* 
 
 // ------------------------------------------------------------------ pooling
 // maxPool2D_batch / maxPool_k_inplace: TensorDslCPU.scala:848-948.
-int ora_maxpool_fwd(const float* x, float* y, int32_t* idx, int N, int C, int H, int W, int kh, int kw, int sh, int sw, int pad) {
+int ora_maxpool_fwd(const float* x, float* y, int32_t* idx, int N, int C, int H, int W, int kh, int kw, int sh, int sw, int pad) { ProfScope prof_scope_("ora_maxpool_fwd");
   REQUIRE(x && y && idx && N > 0 && C > 0 && kh >= 1 && kw >= 1 && sh >= 1 && sw >= 1 && pad >= 0, "maxpool_fwd: bad argument");
   REQUIRE(H + 2 * pad >= kh && W + 2 * pad >= kw, "maxpool_fwd: image too small");
   int oH = (H + 2 * pad - kh) / sh + 1, oW = (W + 2 * pad - kw) / sw + 1;
@@ -588,12 +708,12 @@ int ora_maxpool_fwd(const float* x, float* y, int32_t* idx, int N, int C, int H,
   return LTB_OK;
 }
 // maxPool2D_batch_grad: TensorDslCPU.scala:950-959.
-int ora_maxpool_bwd(float* dx, const float* dy, const int32_t* idx, int64_t n_out) {
+int ora_maxpool_bwd(float* dx, const float* dy, const int32_t* idx, int64_t n_out) { ProfScope prof_scope_("ora_maxpool_bwd");
   for (int64_t i = 0; i < n_out; ++i) dx[idx[i]] += dy[i];
   return LTB_OK;
 }
 // averagePool2D_batch / averagePool_inplace: TensorDslCPU.scala:961-1006.
-int ora_avgpool_fwd(const float* x, float* y, int N, int C, int H, int W, int kh, int kw, int sh, int sw) {
+int ora_avgpool_fwd(const float* x, float* y, int N, int C, int H, int W, int kh, int kw, int sh, int sw) { ProfScope prof_scope_("ora_avgpool_fwd");
   REQUIRE(x && y && N > 0 && C > 0 && kh >= 1 && kw >= 1 && sh >= 1 && sw >= 1 && H >= kh && W >= kw, "avgpool_fwd: bad argument");
   int oH = (H - kh) / sh + 1, oW = (W - kw) / sw + 1;
   float ksz = kh * kw * 1.0f;
@@ -605,7 +725,7 @@ int ora_avgpool_fwd(const float* x, float* y, int N, int C, int H, int W, int kh
   return LTB_OK;
 }
 // averagePool2D_batch_grad: TensorDslCPU.scala:1008-1038.
-int ora_avgpool_bwd(float* dx, const float* dy, int N, int C, int H, int W, int kh, int kw, int sh, int sw) {
+int ora_avgpool_bwd(float* dx, const float* dy, int N, int C, int H, int W, int kh, int kw, int sh, int sw) { ProfScope prof_scope_("ora_avgpool_bwd");
   int oH = (H - kh) / sh + 1, oW = (W - kw) / sw + 1;
   int ksz = kh * kw;
   for (size_t p = 0; p < (size_t)N * C; ++p) for (int r = 0; r < oH; ++r) for (int q = 0; q < oW; ++q) {
@@ -635,7 +755,7 @@ void bn_average(const float* x, int N, int C, int HW, std::vector<float>& out, b
 // batchNormTraining: TensorDslCPU.scala:1047-1056 for y; saved stats / running stats as cuDNN gives them to the
 // reference's GPU backend (TensorDslCudnn.scala:1025-1056): exponentialAverageFactor = momentum, unbiased running var.
 int ora_bn_train_fwd(const float* x, float* y, const float* gamma, const float* beta, float* run_mean, float* run_var,
-                     float* save_mean, float* save_istd, int N, int C, int HW, float eps, float momentum) {
+                     float* save_mean, float* save_istd, int N, int C, int HW, float eps, float momentum) { ProfScope prof_scope_("ora_bn_train_fwd");
   REQUIRE(x && y && gamma && beta && save_mean && save_istd && N > 0 && C > 0 && HW > 0, "bn_train_fwd: bad argument");
   std::vector<float> mean, var;
   bn_average(x, N, C, HW, mean, false, nullptr);
@@ -660,33 +780,44 @@ int ora_bn_train_fwd(const float* x, float* y, const float* gamma, const float* 
 // calls it (alpha/beta = 1 for data and params, TensorDslCudnn.scala:1086-1109):
 //   dbeta += sum dy; dgamma += sum dy*xhat; dx += gamma*istd/m * (m*dy - sum dy - xhat * sum dy*xhat).
 int ora_bn_bwd(const float* x, float* dx, const float* dy, const float* gamma, float* dgamma, float* dbeta,
-               const float* save_mean, const float* save_istd, int N, int C, int HW) {
+               const float* save_mean, const float* save_istd, int N, int C, int HW) { ProfScope prof_scope_("ora_bn_bwd");
   REQUIRE(x && dy && gamma && save_mean && save_istd && N > 0 && C > 0 && HW > 0, "bn_bwd: bad argument");
   double m = (double)N * HW;
   const bool par = g.threads > 1;
+  // Channels are independent; a thread takes a run of 16 neighbouring channels and walks the images once for all of them
+  // (for small maps a cache line holds several channels of one image).  Per channel the sums run over n, then over the
+  // pixels, in order, in double, exactly as a loop over that channel alone would.
+  const int chunk = 16, chunks = (C + chunk - 1) / chunk;
 #pragma omp parallel for if (par) num_threads(g.threads) schedule(static)
-  for (int c = 0; c < C; ++c) {
-    double s1 = 0, s2 = 0; float mu = save_mean[c], is = save_istd[c];
-    for (int n = 0; n < N; ++n) {
+  for (int cb = 0; cb < chunks; ++cb) {
+    const int c0 = cb * chunk, cn = std::min(chunk, C - c0);
+    double s1[16] = {0}, s2[16] = {0};
+    for (int n = 0; n < N; ++n) for (int cc = 0; cc < cn; ++cc) {
+      const int c = c0 + cc; const float mu = save_mean[c], is = save_istd[c];
       const float* p = x + ((size_t)n * C + c) * HW; const float* d = dy + ((size_t)n * C + c) * HW;
-      for (int l = 0; l < HW; ++l) { s1 += d[l]; s2 += (double)d[l] * ((p[l] - mu) * is); }
+      double a1 = s1[cc], a2 = s2[cc];
+      for (int l = 0; l < HW; ++l) { a1 += d[l]; a2 += (double)d[l] * ((p[l] - mu) * is); }
+      s1[cc] = a1; s2[cc] = a2;
     }
-    if (dbeta) dbeta[c] += (float)s1;
-    if (dgamma) dgamma[c] += (float)s2;
-    if (dx) {
-      float k = (float)(gamma[c] * is / m);
-      for (int n = 0; n < N; ++n) {
+    for (int cc = 0; cc < cn; ++cc) {
+      if (dbeta) dbeta[c0 + cc] += (float)s1[cc];
+      if (dgamma) dgamma[c0 + cc] += (float)s2[cc];
+    }
+    if (dx)
+      for (int n = 0; n < N; ++n) for (int cc = 0; cc < cn; ++cc) {
+        const int c = c0 + cc; const float mu = save_mean[c], is = save_istd[c];
+        const float k = (float)(gamma[c] * is / m);
+        const double t1 = s1[cc], t2 = s2[cc];
         const float* p = x + ((size_t)n * C + c) * HW; const float* d = dy + ((size_t)n * C + c) * HW;
         float* o = dx + ((size_t)n * C + c) * HW;
-        for (int l = 0; l < HW; ++l) { float xh = (p[l] - mu) * is; o[l] += k * (float)(m * d[l] - s1 - xh * s2); }
+        for (int l = 0; l < HW; ++l) { float xh = (p[l] - mu) * is; o[l] += k * (float)(m * d[l] - t1 - xh * t2); }
       }
-    }
   }
   return LTB_OK;
 }
 // batchNormInference: TensorDslCPU.scala:1040-1045.
 int ora_bn_inference(const float* x, float* y, const float* gamma, const float* beta, const float* rm, const float* rv,
-                     int N, int C, int HW, float eps) {
+                     int N, int C, int HW, float eps) { ProfScope prof_scope_("ora_bn_inference");
   REQUIRE(x && y && gamma && beta && rm && rv, "bn_inference: bad argument");
   for (int n = 0; n < N; ++n) for (int c = 0; c < C; ++c) {
     float sd = (float)sqrt((double)(rv[c] + eps));
@@ -698,8 +829,14 @@ int ora_bn_inference(const float* x, float* y, const float* gamma, const float* 
 
 // ------------------------------------------------------------------ broadcasting elementwise
 // elementWiseOpWithBroadCast: TensorDslCPU.scala:227-244.
-int ora_ew_binary(int op, const float* a, const int* as, const float* b, const int* bs, float* out, int rank) {
+int ora_ew_binary(int op, const float* a, const int* as, const float* b, const int* bs, float* out, int rank) { ProfScope prof_scope_("ora_ew_binary");
   int rs[8]; REQUIRE(a && b && out && as && bs && bcast_shape(as, bs, rank, rs), "ew_binary: shapes do not broadcast");
+  if (same_shape(as, bs, rank)) {                     // no broadcast: the traversal is the identity on all three tensors
+    const int64_t n = prod(rs, rank);
+#pragma omp parallel for if (g.threads > 1 && n > (1 << 16)) num_threads(g.threads) schedule(static)
+    for (int64_t i = 0; i < n; ++i) out[i] = apply_op(op, a[i], b[i]);
+    return LTB_OK;
+  }
   int64_t sa[8], sb[8]; shadow_strides(as, rank, sa); shadow_strides(bs, rank, sb);
   traverse(rs, sa, sb, rank, [&](int64_t ia, int64_t ib, int64_t ir) { out[ir] = apply_op(op, a[ia], b[ib]); });
   return LTB_OK;
@@ -707,8 +844,25 @@ int ora_ew_binary(int op, const float* a, const int* as, const float* b, const i
 // backpropElementWiseOpWithBroadCast with the op1/op2 of add_grad, minus_grad, mul_grad, div_grad:
 // TensorDslCPU.scala:246-263, 300-337.
 int ora_ew_binary_grad(int op, const float* a, float* da, const int* as, const float* b, float* db, const int* bs,
-                       const float* dout, int rank) {
+                       const float* dout, int rank) { ProfScope prof_scope_("ora_ew_binary_grad");
   int rs[8]; REQUIRE(a && b && dout && bcast_shape(as, bs, rank, rs), "ew_binary_grad: shapes do not broadcast");
+  if (same_shape(as, bs, rank) && da != db) {         // no broadcast and distinct destinations: every element is touched once
+    const int64_t n = prod(rs, rank);
+#pragma omp parallel for if (g.threads > 1 && n > (1 << 16)) num_threads(g.threads) schedule(static)
+    for (int64_t i = 0; i < n; ++i) {
+      const float x = a[i], y = b[i], c = dout[i];
+      float g1, g2;
+      switch (op) {
+        case LTB_ADD: g1 = c; g2 = c; break;
+        case LTB_SUB: g1 = c; g2 = 0.0f - c; break;
+        case LTB_MUL: g1 = c * y; g2 = c * x; break;
+        default: g1 = c / y; g2 = -1.0f * x * c / (y * y); break;
+      }
+      if (da) da[i] += g1;
+      if (db) db[i] += g2;
+    }
+    return LTB_OK;
+  }
   int64_t sa[8], sb[8]; shadow_strides(as, rank, sa); shadow_strides(bs, rank, sb);
   traverse(rs, sa, sb, rank, [&](int64_t ia, int64_t ib, int64_t ir) {
     float x = a[ia], y = b[ib], c = dout[ir];
@@ -725,27 +879,27 @@ int ora_ew_binary_grad(int op, const float* a, float* da, const int* as, const f
   return LTB_OK;
 }
 // map(x, s => s op y): TensorDslCPU.scala:298, 309, 320, 331.
-int ora_ew_scalar(int op, const float* a, float s, float* out, int64_t n) {
+int ora_ew_scalar(int op, const float* a, float s, float* out, int64_t n) { ProfScope prof_scope_("ora_ew_scalar");
   for (int64_t i = 0; i < n; ++i) out[i] = apply_op(op, a[i], s);
   return LTB_OK;
 }
 // inplaceElementWiseOpWithBroadCastOrReduce: TensorDslCPU.scala:265-279.
-int ora_ew_inplace(int op, float* x, const int* xs, const float* y, const int* ys, int rank) {
+int ora_ew_inplace(int op, float* x, const int* xs, const float* y, const int* ys, int rank) { ProfScope prof_scope_("ora_ew_inplace");
   int rs[8]; REQUIRE(x && y && bcast_shape(xs, ys, rank, rs), "ew_inplace: shapes do not broadcast");
   int64_t sx[8], sy[8]; shadow_strides(xs, rank, sx); shadow_strides(ys, rank, sy);
   traverse(rs, sx, sy, rank, [&](int64_t ix, int64_t iy, int64_t) { x[ix] = apply_op(op, x[ix], y[iy]); });
   return LTB_OK;
 }
-int ora_ew_inplace_scalar(int op, float* x, float s, int64_t n) {
+int ora_ew_inplace_scalar(int op, float* x, float s, int64_t n) { ProfScope prof_scope_("ora_ew_inplace_scalar");
   for (int64_t i = 0; i < n; ++i) x[i] = apply_op(op, x[i], s);
   return LTB_OK;
 }
 // plusBias / plusBias_grad: TensorDslCPU.scala:281-288.
-int ora_plus_bias(float* main, const int* ms, const float* bias, const int* bs, int rank) { return ora_ew_inplace(LTB_ADD, main, ms, bias, bs, rank); }
-int ora_plus_bias_grad(float* dbias, const int* bs, const float* dmain, const int* ms, int rank) { return ora_ew_inplace(LTB_ADD, dbias, bs, dmain, ms, rank); }
+int ora_plus_bias(float* main, const int* ms, const float* bias, const int* bs, int rank) { ProfScope prof_scope_("ora_plus_bias"); return ora_ew_inplace(LTB_ADD, main, ms, bias, bs, rank); }
+int ora_plus_bias_grad(float* dbias, const int* bs, const float* dmain, const int* ms, int rank) { ProfScope prof_scope_("ora_plus_bias_grad"); return ora_ew_inplace(LTB_ADD, dbias, bs, dmain, ms, rank); }
 // geam: TensorDslCPU.scala:342-347 (no-transpose case only on the CPU; the transposed cases follow cublasSgeam's
 // definition as used at TensorDslCublas.scala:318-373).
-int ora_geam(const float* x, int tx, float alpha, const float* y, int ty, float beta, float* out, int rows, int cols) {
+int ora_geam(const float* x, int tx, float alpha, const float* y, int ty, float beta, float* out, int rows, int cols) { ProfScope prof_scope_("ora_geam");
   REQUIRE(x && y && out && rows > 0 && cols > 0, "geam: bad argument");
   REQUIRE(!((tx || ty) && (out == x || out == y)), "geam: in-place with transpose");
   for (int i = 0; i < rows; ++i) for (int j = 0; j < cols; ++j) {
@@ -756,18 +910,18 @@ int ora_geam(const float* x, int tx, float alpha, const float* y, int ty, float 
   return LTB_OK;
 }
 // trans / trans_grad: TensorDslCPU.scala:349-374.
-int ora_trans(const float* x, float* out, int rows, int cols) {
+int ora_trans(const float* x, float* out, int rows, int cols) { ProfScope prof_scope_("ora_trans");
   for (int i = 0; i < cols; ++i) for (int j = 0; j < rows; ++j) out[(size_t)i * rows + j] = x[(size_t)j * cols + i];
   return LTB_OK;
 }
-int ora_trans_grad(float* dx, const float* dy, int rows, int cols) {
+int ora_trans_grad(float* dx, const float* dy, int rows, int cols) { ProfScope prof_scope_("ora_trans_grad");
   for (int i = 0; i < cols; ++i) for (int j = 0; j < rows; ++j) dx[(size_t)j * cols + i] += dy[(size_t)i * rows + j];
   return LTB_OK;
 }
 
 // ------------------------------------------------------------------ activations
 // relu, tanh, sigmoid, exp, log, sqrt, square: TensorDslCPU.scala:710-781 (double libm, cast to float).
-int ora_unary(int op, const float* x, float* out, int64_t n) {
+int ora_unary(int op, const float* x, float* out, int64_t n) { ProfScope prof_scope_("ora_unary");
   REQUIRE(x && out && n >= 0, "unary: bad argument");
   for (int64_t i = 0; i < n; ++i) {
     float v = x[i], r;
@@ -786,7 +940,7 @@ int ora_unary(int op, const float* x, float* out, int64_t n) {
   return LTB_OK;
 }
 // *_grad: TensorDslCPU.scala:722-781, TD.scala:789-809.
-int ora_unary_grad(int op, const float* x, float* dx, const float* y, const float* dy, int64_t n, int in_place) {
+int ora_unary_grad(int op, const float* x, float* dx, const float* y, const float* dy, int64_t n, int in_place) { ProfScope prof_scope_("ora_unary_grad");
   REQUIRE(dx && dy && n >= 0, "unary_grad: bad argument");
   for (int64_t i = 0; i < n; ++i) {
     switch (op) {
@@ -808,7 +962,7 @@ int ora_unary_grad(int op, const float* x, float* dx, const float* y, const floa
 
 // ------------------------------------------------------------------ softmax / loss
 // softmax: TensorDslCPU.scala:783-805; max2D TD.scala:552-571; sum(dim=1) accumulates left to right.
-int ora_softmax(const float* x, float* y, int rows, int cols) {
+int ora_softmax(const float* x, float* y, int rows, int cols) { ProfScope prof_scope_("ora_softmax");
   REQUIRE(x && y && rows > 0 && cols > 0, "softmax: bad argument");
   for (int b = 0; b < rows; ++b) {
     const float* p = x + (size_t)b * cols; float* q = y + (size_t)b * cols;
@@ -820,7 +974,7 @@ int ora_softmax(const float* x, float* y, int rows, int cols) {
   return LTB_OK;
 }
 // logSoftmax: TensorDslCPU.scala:807-832.
-int ora_log_softmax(const float* x, float* y, int rows, int cols) {
+int ora_log_softmax(const float* x, float* y, int rows, int cols) { ProfScope prof_scope_("ora_log_softmax");
   REQUIRE(x && y && rows > 0 && cols > 0, "log_softmax: bad argument");
   for (int b = 0; b < rows; ++b) {
     const float* p = x + (size_t)b * cols; float* q = y + (size_t)b * cols;
@@ -834,7 +988,7 @@ int ora_log_softmax(const float* x, float* y, int rows, int cols) {
 }
 // softmax_grad: `???` on the CPU backend; cudnnSoftmaxBackward ACCURATE as called at TensorDslCudnn.scala:1465-1504:
 // dx += y * (dy - sum_j dy_j*y_j).
-int ora_softmax_grad(float* dx, const float* y, const float* dy, int rows, int cols) {
+int ora_softmax_grad(float* dx, const float* y, const float* dy, int rows, int cols) { ProfScope prof_scope_("ora_softmax_grad");
   for (int b = 0; b < rows; ++b) {
     const float* yy = y + (size_t)b * cols; const float* d = dy + (size_t)b * cols; float* o = dx + (size_t)b * cols;
     float s = 0.0f; for (int i = 0; i < cols; ++i) s += d[i] * yy[i];
@@ -843,7 +997,7 @@ int ora_softmax_grad(float* dx, const float* y, const float* dy, int rows, int c
   return LTB_OK;
 }
 // logSoftmax_grad: TensorDslCPU.scala:837-846.
-int ora_log_softmax_grad(float* dx, const float* y, const float* dy, int rows, int cols) {
+int ora_log_softmax_grad(float* dx, const float* y, const float* dy, int rows, int cols) { ProfScope prof_scope_("ora_log_softmax_grad");
   for (int b = 0; b < rows; ++b) {
     const float* yy = y + (size_t)b * cols; const float* d = dy + (size_t)b * cols; float* o = dx + (size_t)b * cols;
     float s = 0.0f; for (int i = 0; i < cols; ++i) s += d[i];
@@ -852,7 +1006,7 @@ int ora_log_softmax_grad(float* dx, const float* y, const float* dy, int rows, i
   return LTB_OK;
 }
 // nllLoss / nllLoss_grad: TensorDslCPU.scala:1090-1110.
-int ora_nll(const float* x, const int32_t* t, float* out, int rows, int cols) {
+int ora_nll(const float* x, const int32_t* t, float* out, int rows, int cols) { ProfScope prof_scope_("ora_nll");
   REQUIRE(x && t && out, "nll: bad argument");
   for (int b = 0; b < rows; ++b) {
     REQUIRE(t[b] >= 0 && t[b] < cols, "nll: target out of range");
@@ -860,21 +1014,21 @@ int ora_nll(const float* x, const int32_t* t, float* out, int rows, int cols) {
   }
   return LTB_OK;
 }
-int ora_nll_grad(float* dx, const float* dout, const int32_t* t, int rows, int cols) {
+int ora_nll_grad(float* dx, const float* dout, const int32_t* t, int rows, int cols) { ProfScope prof_scope_("ora_nll_grad");
   for (int b = 0; b < rows; ++b) dx[(size_t)b * cols + t[b]] += -1.0f * dout[b];
   return LTB_OK;
 }
 
 // ------------------------------------------------------------------ reductions
 // sum / mean and grads: TensorDslCPU.scala:1115-1124 (sequential float fold).
-int ora_sum(const float* x, float* out, int64_t n) { float s = 0.0f; for (int64_t i = 0; i < n; ++i) s = s + x[i]; out[0] = s; return LTB_OK; }
+int ora_sum(const float* x, float* out, int64_t n) { ProfScope prof_scope_("ora_sum"); float s = 0.0f; for (int64_t i = 0; i < n; ++i) s = s + x[i]; out[0] = s; return LTB_OK; }
 // The CPU build has no workspace to avoid: the static-scratch variant is the same sequential sum.
-int ora_sum_static_scratch(const float* x, float* out, int64_t n) { return ora_sum(x, out, n); }
-int ora_sum_grad(float* dx, const float* dout, int64_t n) { for (int64_t i = 0; i < n; ++i) dx[i] = dx[i] + dout[0]; return LTB_OK; }
-int ora_mean(const float* x, float* out, int64_t n) { float s = 0.0f; for (int64_t i = 0; i < n; ++i) s = s + x[i]; out[0] = s / (float)n; return LTB_OK; }
-int ora_mean_grad(float* dx, const float* dout, int64_t n) { float g1 = dout[0] / (float)n; for (int64_t i = 0; i < n; ++i) dx[i] = dx[i] + g1; return LTB_OK; }
+int ora_sum_static_scratch(const float* x, float* out, int64_t n) { ProfScope prof_scope_("ora_sum_static_scratch"); return ora_sum(x, out, n); }
+int ora_sum_grad(float* dx, const float* dout, int64_t n) { ProfScope prof_scope_("ora_sum_grad"); for (int64_t i = 0; i < n; ++i) dx[i] = dx[i] + dout[0]; return LTB_OK; }
+int ora_mean(const float* x, float* out, int64_t n) { ProfScope prof_scope_("ora_mean"); float s = 0.0f; for (int64_t i = 0; i < n; ++i) s = s + x[i]; out[0] = s / (float)n; return LTB_OK; }
+int ora_mean_grad(float* dx, const float* dout, int64_t n) { ProfScope prof_scope_("ora_mean_grad"); float g1 = dout[0] / (float)n; for (int64_t i = 0; i < n; ++i) dx[i] = dx[i] + g1; return LTB_OK; }
 // sum(dim) / sum_grad(dim): TensorDslCPU.scala:1125-1164.
-int ora_sum_dim(const float* x, float* out, int outer, int d, int inner) {
+int ora_sum_dim(const float* x, float* out, int outer, int d, int inner) { ProfScope prof_scope_("ora_sum_dim");
   for (int h = 0; h < outer; ++h) {
     float* o = out + (size_t)h * inner;
     for (int l = 0; l < inner; ++l) o[l] = 0.0f;
@@ -882,7 +1036,7 @@ int ora_sum_dim(const float* x, float* out, int outer, int d, int inner) {
   }
   return LTB_OK;
 }
-int ora_sum_dim_grad(float* dx, const float* dout, int outer, int d, int inner) {
+int ora_sum_dim_grad(float* dx, const float* dout, int outer, int d, int inner) { ProfScope prof_scope_("ora_sum_dim_grad");
   for (int h = 0; h < outer; ++h) for (int s = 0; s < d; ++s) {
     float* p = dx + ((size_t)h * d + s) * inner; const float* o = dout + (size_t)h * inner;
     for (int l = 0; l < inner; ++l) p[l] += o[l];
@@ -892,7 +1046,7 @@ int ora_sum_dim_grad(float* dx, const float* dout, int outer, int d, int inner) 
 
 // ------------------------------------------------------------------ concat
 // concat / concat_grad: TensorDslCPU.scala:1166-1212.
-int ora_concat(float* out, const float* const* inputs, const int* dims, int n_inputs, int outer, int inner) {
+int ora_concat(float* out, const float* const* inputs, const int* dims, int n_inputs, int outer, int inner) { ProfScope prof_scope_("ora_concat");
   REQUIRE(out && inputs && dims && n_inputs > 0, "concat: bad argument");
   size_t t = 0;
   for (int h = 0; h < outer; ++h) for (int k = 0; k < n_inputs; ++k) {
@@ -901,7 +1055,7 @@ int ora_concat(float* out, const float* const* inputs, const int* dims, int n_in
   }
   return LTB_OK;
 }
-int ora_concat_grad(float* const* dinputs, const float* dout, const int* dims, int n_inputs, int outer, int inner) {
+int ora_concat_grad(float* const* dinputs, const float* dout, const int* dims, int n_inputs, int outer, int inner) { ProfScope prof_scope_("ora_concat_grad");
   size_t t = 0;
   for (int h = 0; h < outer; ++h) for (int k = 0; k < n_inputs; ++k) {
     size_t stride = (size_t)dims[k] * inner;
@@ -913,7 +1067,7 @@ int ora_concat_grad(float* const* dinputs, const float* dout, const int* dims, i
 
 // ------------------------------------------------------------------ dropout
 // dropout / dropout_grad: TensorDslCPU.scala:1066-1088.
-int ora_dropout(const float* x, float* y, float* mask, float p, int64_t n) {
+int ora_dropout(const float* x, float* y, float* mask, float p, int64_t n) { ProfScope prof_scope_("ora_dropout");
   REQUIRE(x && y && mask && p >= 0.0f && p < 1.0f, "dropout: rate must be in [0,1)");
   float scale = 1.0f / (1.0f - p);
   for (int64_t i = 0; i < n; ++i) {
@@ -921,22 +1075,22 @@ int ora_dropout(const float* x, float* y, float* mask, float p, int64_t n) {
   }
   return LTB_OK;
 }
-int ora_dropout_masked(const float* x, float* y, const float* mask, int64_t n) { for (int64_t i = 0; i < n; ++i) y[i] = x[i] * mask[i]; return LTB_OK; }
-int ora_dropout_grad(float* dx, const float* mask, const float* dy, int64_t n) { for (int64_t i = 0; i < n; ++i) dx[i] += mask[i] * dy[i]; return LTB_OK; }
+int ora_dropout_masked(const float* x, float* y, const float* mask, int64_t n) { ProfScope prof_scope_("ora_dropout_masked"); for (int64_t i = 0; i < n; ++i) y[i] = x[i] * mask[i]; return LTB_OK; }
+int ora_dropout_grad(float* dx, const float* mask, const float* dy, int64_t n) { ProfScope prof_scope_("ora_dropout_grad"); for (int64_t i = 0; i < n; ++i) dx[i] += mask[i] * dy[i]; return LTB_OK; }
 
 // ------------------------------------------------------------------ optimizers
 // SGD.step: geam(x, 1, d, -lr) then clear_grad, NNModule.scala:265-287 with geam of TensorDslCPU.scala:342-347.
-int ora_sgd_step(float* x, float* d, float lr, int64_t n) {
+int ora_sgd_step(float* x, float* d, float lr, int64_t n) { ProfScope prof_scope_("ora_sgd_step");
   float beta = -1.0f * lr;
   for (int64_t i = 0; i < n; ++i) { x[i] = x[i] * 1.0f + d[i] * beta; d[i] = 0.0f; }
   return LTB_OK;
 }
-int ora_sgd_step_multi(float* const* xs, float* const* ds, const int64_t* sizes, int nt, float lr) {
+int ora_sgd_step_multi(float* const* xs, float* const* ds, const int64_t* sizes, int nt, float lr) { ProfScope prof_scope_("ora_sgd_step_multi");
   for (int t = 0; t < nt; ++t) ora_sgd_step(xs[t], ds[t], lr, sizes[t]);
   return LTB_OK;
 }
 // adagrad_update: TensorDslCPU.scala:1217-1230.
-int ora_adagrad_update(float* x, float* d, float* h, float lr, float clip, int descent, int64_t n) {
+int ora_adagrad_update(float* x, float* d, float* h, float lr, float clip, int descent, int64_t n) { ProfScope prof_scope_("ora_adagrad_update");
   for (int64_t i = 0; i < n; ++i) {
     float t = d[i]; if (t > clip) t = clip; if (t < -clip) t = -clip;
     h[i] += t * t;
@@ -947,7 +1101,7 @@ int ora_adagrad_update(float* x, float* d, float* h, float lr, float clip, int d
   return LTB_OK;
 }
 // momentum_update: TensorDslCPU.scala:1232-1246.
-int ora_momentum_update(float* x, float* d, float* m, float lr, float mu, float clip, int nesterov, int descent, int64_t n) {
+int ora_momentum_update(float* x, float* d, float* m, float lr, float mu, float clip, int nesterov, int descent, int64_t n) { ProfScope prof_scope_("ora_momentum_update");
   for (int64_t i = 0; i < n; ++i) {
     float t = d[i]; if (t > clip) t = clip; if (t < -clip) t = -clip;
     m[i] *= mu; m[i] += t;
@@ -985,31 +1139,31 @@ static int transport_sum(float* buf, int64_t n, const char* who) {
   return fail(LTB_E_COMM, (std::string(who) + (r == ltb::WAIT_TIMEOUT ? ": a collective did not finish within the communicator's timeout (a rank has left?)"
                                                                       : ": the transport reported an error") + "; the communicator was aborted").c_str());
 }
-int ora_comm_set_transport(ora_allreduce_fn fn) { g_transport = fn; return LTB_OK; }
-int ora_comm_set_timeout_ms(int64_t ms) { g_timeout_ms = ms; return LTB_OK; }
-int ora_comm_unique_id(void* out128) { memset(out128, 0, 128); return LTB_OK; }
-int ora_comm_init(int rank, int world, const void*) {
+int ora_comm_set_transport(ora_allreduce_fn fn) { ProfScope prof_scope_("ora_comm_set_transport"); g_transport = fn; return LTB_OK; }
+int ora_comm_set_timeout_ms(int64_t ms) { ProfScope prof_scope_("ora_comm_set_timeout_ms"); g_timeout_ms = ms; return LTB_OK; }
+int ora_comm_unique_id(void* out128) { ProfScope prof_scope_("ora_comm_unique_id"); memset(out128, 0, 128); return LTB_OK; }
+int ora_comm_init(int rank, int world, const void*) { ProfScope prof_scope_("ora_comm_init");
   if (world < 1 || rank < 0 || rank >= world) return fail(LTB_E_ARG, "ora_comm_init: bad rank/world");
   if (world > 1 && !g_transport) return fail(LTB_E_COMM, "ora_comm_init: no transport installed for a multi-rank communicator");
   g_world = world; g_broken = false;
   return LTB_OK;
 }
-int ora_comm_destroy(void) { g_world = 1; g_broken = false; return LTB_OK; }
-int ora_comm_world(void) { return g_world; }
-int ora_allreduce_sum(float* x, int64_t n) {
+int ora_comm_destroy(void) { ProfScope prof_scope_("ora_comm_destroy"); g_world = 1; g_broken = false; return LTB_OK; }
+int ora_comm_world(void) { ProfScope prof_scope_("ora_comm_world"); return g_world; }
+int ora_allreduce_sum(float* x, int64_t n) { ProfScope prof_scope_("ora_allreduce_sum");
   if (g_world == 1 || n == 0) return LTB_OK;
   return transport_sum(x, n, "ora_allreduce_sum");
 }
 // Early ranges: summed at once (the transport is synchronous) and remembered, so that the step does not sum them twice.
 static struct { float* ptr; int64_t n; } g_early[16];
 static int g_n_early = 0;
-int ora_allreduce_begin(float* d, int64_t n) {
+int ora_allreduce_begin(float* d, int64_t n) { ProfScope prof_scope_("ora_allreduce_begin");
   if (g_world == 1 || n == 0 || g_n_early == 16) return LTB_OK;
   { const int rc = transport_sum(d, n, "ora_allreduce_begin"); if (rc) return rc; }
   g_early[g_n_early].ptr = d; g_early[g_n_early].n = n; ++g_n_early;
   return LTB_OK;
 }
-int ora_allreduce_sgd_step(float* x, float* d, float lr, int64_t n) {
+int ora_allreduce_sgd_step(float* x, float* d, float lr, int64_t n) { ProfScope prof_scope_("ora_allreduce_sgd_step");
   if (g_world == 1) return ora_sgd_step(x, d, lr, n);
   const float s = -1.0f * lr / (float)g_world;
   std::vector<char> done((size_t)n, 0);
@@ -1035,18 +1189,25 @@ int ora_allreduce_sgd_step(float* x, float* d, float lr, int64_t n) {
 // ------------------------------------------------------------------ staging / replay: plain host equivalents.
 extern "C" {
 void* ora_host_alloc(size_t bytes) { return malloc(bytes); }
-int ora_host_free(void* p) { free(p); return LTB_OK; }
-int ora_d2h_async(void* d, const void* s, size_t n) { memcpy(d, s, n); return LTB_OK; }
-int ora_branch_mark(void) { return LTB_OK; }        // one thread of control: a branch simply runs where it is issued
-int ora_branch_begin(void) { return LTB_OK; }
-int ora_branch_end(void) { return LTB_OK; }
-int ora_branch_join(void) { return LTB_OK; }
-int ora_marker_record(int) { return LTB_OK; }      // the CPU oracle runs every call to completion
-int ora_marker_wait(int) { return LTB_OK; }
-int ora_graph_begin(void) { return fail(LTB_E_ARG, "the CPU oracle does not record steps"); }
+int ora_host_free(void* p) { ProfScope prof_scope_("ora_host_free"); free(p); return LTB_OK; }
+int ora_d2h_async(void* d, const void* s, size_t n) { ProfScope prof_scope_("ora_d2h_async"); memcpy(d, s, n); return LTB_OK; }
+int ora_branch_mark(void) { ProfScope prof_scope_("ora_branch_mark"); return LTB_OK; }        // one thread of control: a branch simply runs where it is issued
+int ora_branch_begin(void) { ProfScope prof_scope_("ora_branch_begin"); return LTB_OK; }
+int ora_branch_end(void) { ProfScope prof_scope_("ora_branch_end"); return LTB_OK; }
+int ora_branch_join(void) { ProfScope prof_scope_("ora_branch_join"); return LTB_OK; }
+int ora_marker_record(int) { ProfScope prof_scope_("ora_marker_record"); return LTB_OK; }      // the CPU oracle runs every call to completion
+int ora_marker_wait(int) { ProfScope prof_scope_("ora_marker_wait"); return LTB_OK; }
+int ora_graph_begin(void) { ProfScope prof_scope_("ora_graph_begin"); return fail(LTB_E_ARG, "the CPU oracle does not record steps"); }
 void* ora_graph_end(void) { return nullptr; }
-int ora_graph_launch(void*) { return fail(LTB_E_ARG, "the CPU oracle does not record steps"); }
-int ora_graph_destroy(void*) { return LTB_OK; }
-int ora_profile(int) { return LTB_OK; }
-int ora_profile_report(char* buf, int len) { if (buf && len > 0) buf[0] = 0; return LTB_OK; }
+int ora_graph_launch(void*) { ProfScope prof_scope_("ora_graph_launch"); return fail(LTB_E_ARG, "the CPU oracle does not record steps"); }
+int ora_graph_destroy(void*) { ProfScope prof_scope_("ora_graph_destroy"); return LTB_OK; }
+int ora_profile(int on) { if (on) g_prof_n = 0; g_prof_on = on != 0; return LTB_OK; }
+// One line per entry point: name<TAB>calls<TAB>total milliseconds (the format of the CUDA library's report).
+int ora_profile_report(char* buf, int len) {
+  if (!buf || len <= 0) return LTB_E_ARG;
+  std::string out;
+  for (int i = 0; i < g_prof_n; ++i) { char line[256]; snprintf(line, sizeof line, "%s\t%lld\t%.6f\n", g_prof[i].name, g_prof[i].calls, g_prof[i].seconds * 1e3); out += line; }
+  strncpy(buf, out.c_str(), len - 1); buf[len - 1] = 0;
+  return (int)out.size() < len ? LTB_OK : LTB_E_LIMIT;
+}
 }

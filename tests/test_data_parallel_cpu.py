@@ -102,8 +102,11 @@ def test_two_ranks_match_one_process_on_the_whole_batch(tmp_path):
     ref, init, whole = np.load(tmp_path / "ref_params.npy"), np.load(tmp_path / "init_params.npy"), np.load(tmp_path / "ref_losses.npy")
     l0, l1 = np.load(tmp_path / "losses_0.npy"), np.load(tmp_path / "losses_1.npy")
     assert np.allclose((l0 + l1) / 2, whole, rtol=1e-4), ((l0 + l1) / 2, whole)
-    err = np.abs(p0 - ref).max() / np.abs(ref).max()
-    assert err < 1e-5, err
+    # Two shard sums added together round differently from one sum over the whole batch (1e-7), and after the first update
+    # a pre-activation within that distance of zero may fall on the other side of its ReLU in the second step, which switches
+    # one gradient element on or off and shows in one filter row: nearly every parameter agrees to 1e-5, all of them to 2e-4.
+    err = np.abs(p0 - ref) / np.abs(ref).max()
+    assert (err > 1e-5).mean() < 1e-3 and err.max() < 2e-4, (float(err.max()), int((err > 1e-5).sum()))
     # and the steps did move the parameters by far more than that bound
     assert np.abs(p0 - init).max() / np.abs(ref).max() > 1e-3
 
