@@ -4,6 +4,7 @@
     python bench.py --gpus 1 --steps 20 --warmup 5
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P bench.py --gpus N ...
     python bench.py --impl reference ...        # the CPU path (oracle port of the reference's CPU backend) on the host cores
+    --blocks R                                  # the K-step block is timed R times and the median block reported (default: >= 20, ~2 s)
 
 One step = upload of one synthetic batch (128 x 3 x 32 x 32 per GPU, N(0,1), labels uniform 0..9) -> forward ->
 backward -> loss read-back -> SGD (lr 0.1) over every parameter tensor, issued by the host program in
@@ -61,6 +62,40 @@ def step_flops(batch):
     return fwd + fc, total + 3 * fc
 
 
+def hbm_bound_bytes(batch):
+    """Compulsory bytes of one training step for each class of HBM-bound kernel, keyed by a substring of the kernel's name:
+    every distinct input read once, every output written once, one more read of a destination that is accumulated into,
+    4 B per element.  With the look-ahead fusion on, the classes are the fused kernels the step really launches:
+      bn_fwd*        batch-norm forward (+ ReLU in the same pass)          x, y                          8 B / element
+      bn_bwd*        batch-norm backward; where an in-place ReLU gradient joined it the kernel also reads the ReLU output
+                     and writes the masked gradient back                  x, dy, dx r/w (+ y, dy w)     16 (24) B / element
+      relu_add_grad  ReLU gradient + residual-add gradient                y, d r/w, da r/w, db r/w      28 B / element
+      map_vec4       residual add + ReLU                                  a, b, out                     12 B / element
+      maxpool_*      2x2 max pool forward (x, y, idx) and backward        6 and 10 B / input element
+      sgd_*          x -= lr d; d = 0                                     16 B / parameter"""
+    el = {"bn": [], "add": []}
+    for (ci, co, k, s, p, h) in resnet50_convs():
+        ho = (h + 2 * p - k) // s + 1
+        el["bn"].append(batch * co * ho * ho)
+    bn_all = float(sum(el["bn"]))
+    relu_bn = 0.0                                   # BN outputs followed by an in-place ReLU: the stem, and conv1/conv2 of every block
+    convs = resnet50_convs()
+    i = 1
+    relu_bn += el["bn"][0]
+    for s_, (planes, nblk) in enumerate(((64, 3), (128, 4), (256, 6), (512, 3))):
+        for b_ in range(nblk):
+            relu_bn += el["bn"][i] + el["bn"][i + 1]
+            i += 4 if b_ == 0 else 3
+    adds = sum(batch * c * h * h * n for (c, h, n) in ((256, 16, 3), (512, 8, 4), (1024, 4, 6), (2048, 2, 3)))
+    pool_in = batch * 64 * 32 * 32
+    params = 23520842
+    return {"bn_fwd": 8.0 * bn_all, "bn_bwd": 16.0 * bn_all + 8.0 * relu_bn, "relu_add_grad": 28.0 * adds, "map_vec4": 12.0 * adds,
+            "maxpool_fwd": 6.0 * pool_in, "maxpool_bwd": 10.0 * pool_in, "sgd": 16.0 * params}
+
+
+STAGING_KERNELS = ("to_rows", "unfold", "permute_taps", "fold_", "pad_rows", "filter_forms", "channels_last")
+
+
 # --------------------------------------------------------------------------------------------- clocks
 class ClockSampler:
     Q = "index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown," \
@@ -109,12 +144,15 @@ def measured_peaks():
 
 
 # --------------------------------------------------------------------------------------------- CPU legs
+CPU_BLAS = "none: the port's own register-tiled AVX2/FMA loops (4 x 16 tile, sequential sum over k per element) under OpenMP"
+
+
 def cpu_steps(batch, steps, warmup, threads):
     """Time the CPU port (oracle/) of the same host program: `steps` training steps of `batch` samples."""
     from lantern_b200._ffi import BoundLibrary
     from lantern_b200.hosts import HostPrograms
     ora = BoundLibrary(os.path.join(ROOT, "oracle", "liblantern_oracle.so"), "ora_")
-    ora.init(0, 8 << 30)
+    ora.init(0, 12 << 30)
     ora.cdll.ora_set_threads(threads)
     m = HostPrograms(ora, os.path.join(ROOT, "oracle", "liblantern_oracle_hosts.so"), "orah_").model("resnet50", batch, seed=42)
     rng = np.random.default_rng(1)
@@ -131,23 +169,25 @@ def cpu_steps(batch, steps, warmup, threads):
 
 
 def reference_arm(args, rank):
+    """The reference's CPU path for this step on the host cores.  Its own CPU backend cannot train ResNet-50 (batchNorm_grad
+    is unimplemented there) and its generator needs a JVM, so what is timed is the CPU port of that backend (oracle/)
+    running the same host program on the FULL 128-sample batch with every host thread; the number of steps is cut so that
+    the run ends within a few minutes."""
     if rank != 0:
         return
     threads = os.cpu_count() or 1
-    sample = 8                                      # samples per step: a bounded slice of the 128-sample batch
-    probe = cpu_steps(sample, 1, 1, threads)        # also warms the page cache / allocator
-    steps = args.steps
-    if probe * (steps + args.warmup) > 240:         # keep the whole run within a few minutes
-        steps = max(1, int(240 / probe) - args.warmup)
-    sec = cpu_steps(sample, steps, args.warmup, threads)
-    v = sample / sec
-    line = {"impl": "reference", "metric": METRIC, "value": v, "unit": "samples/s", "n_gpus": args.gpus, "steps": steps, "warmup": args.warmup,
+    probe = cpu_steps(BATCH, 1, 1, threads)         # one warm-up + one step: also sizes the run
+    steps = max(1, min(args.steps, int(200 / max(probe, 1e-3))))
+    warm = 1 if probe * (steps + args.warmup) > 200 else args.warmup
+    sec = cpu_steps(BATCH, steps, warm, threads)
+    v = BATCH / sec
+    line = {"impl": "reference", "metric": METRIC, "value": v, "unit": "samples/s", "n_gpus": args.gpus, "steps": steps, "warmup": warm,
             "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": "resnet50_cifar_train_step_sgd_lr0.1", "batch_per_gpu": BATCH, "sample_per_step": sample,
+            "config": {"workload": "resnet50_cifar_train_step_sgd_lr0.1", "batch_per_gpu": BATCH, "global_batch": BATCH, "sample_per_step": BATCH,
                        "note": "the reference's CPU backend cannot train ResNet-50 (batchNorm_grad is unimplemented) and its Scala generator "
                                "needs a JVM; this arm times the CPU port of that backend (oracle/) running the same host program"},
-            "cpu_baseline": {"value": v, "unit": "samples/s", "cores": threads, "kind": "port",
-                             "sample": "%d steps of %d samples (slice of the 128-sample batch), all host threads" % (steps, sample)},
+            "cpu_baseline": {"value": v, "unit": "samples/s", "cores": threads, "kind": "port", "blas": CPU_BLAS,
+                             "sample": "%d steps of the full %d-sample batch after %d warm-up, all host threads" % (steps, BATCH, warm)},
             "e2e": {"value": v, "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
     print(json.dumps(line), flush=True)
 
@@ -161,6 +201,7 @@ def main():
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--math", default="tf32", choices=["tf32", "fp32"])
+    ap.add_argument("--blocks", type=int, default=0, help="timed blocks of --steps steps each; the median block is reported (0: enough for about 2 s)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0")); local = int(os.environ.get("LOCAL_RANK", "0")); world = int(os.environ.get("WORLD_SIZE", "1"))
     args.warmup = max(3, args.warmup)
@@ -204,6 +245,7 @@ def main():
         torch.cuda.synchronize()
 
     def timed(fn, steps):
+        """One block: exactly `steps` steps between barrier + synchronize, CUDA events on the launching stream, max over ranks."""
         barrier()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         with torch.cuda.stream(stream):
@@ -218,6 +260,16 @@ def main():
             t = torch.tensor([ms], device="cuda"); dist.all_reduce(t, op=dist.ReduceOp.MAX); ms = float(t.item())
         return ms
 
+    def timed_blocks(make_fn, steps, first_ms=None):
+        """Repeats the K-step block (20 blocks or more, until about 2 s are covered) and returns (median, all blocks): one block
+        of 20 steps lasts under 0.1 s, too short to compare two boxes."""
+        first = timed(make_fn(), steps) if first_ms is None else first_ms
+        n = args.blocks if args.blocks > 0 else int(min(200, max(20, 2000.0 / max(first, 1e-3))))
+        if world > 1:                               # every rank must run the same number of blocks
+            t = torch.tensor([n], device="cuda"); dist.all_reduce(t, op=dist.ReduceOp.MAX); n = int(t.item())
+        blocks = [first] + [timed(make_fn(), steps) for _ in range(n - 1)]
+        return float(np.median(blocks)), blocks
+
     # ---- value: device-resident batch, the recorded step replayed back to back
     model.set_resident(*pool[0])
     sampler = ClockSampler(local); sampler.start()        # sampled from the warm-up on: all of it is under the same load
@@ -225,10 +277,13 @@ def main():
         model.step_async(pool[0][0], pool[0][1], LR)
     lib.sync()
     l0 = lib.kernel_launches()
-    ms = timed(lambda i: model.step_async(pool[0][0], pool[0][1], LR), args.steps)
-    launches = lib.kernel_launches() - l0
+    ms, blocks = timed_blocks(lambda: (lambda i: model.step_async(pool[0][0], pool[0][1], LR)), args.steps)
+    launches = (lib.kernel_launches() - l0) // len(blocks)
     loss_resident = model.last_loss()
     value = BATCH * world * args.steps / (ms / 1e3)
+    exposed = ctypes.c_float(0.0)
+    if world > 1:
+        lib.comm_exposed_ms(ctypes.addressof(exposed))
 
     # ---- e2e: host buffers in, loss out, every step (upload + read-back inside the timed region)
     model.set_resident(None)
@@ -250,9 +305,19 @@ def main():
         return fn
     for i in range(3):
         e2e_loop(1)(0)
-    ms_e2e = timed(e2e_loop(args.steps), args.steps)
+    ms_e2e, blocks_e2e = timed_blocks(lambda: e2e_loop(args.steps), args.steps)
     clocks = sampler.stop()
     e2e = BATCH * world * args.steps / (ms_e2e / 1e3)
+
+    # ---- replicas: after all those updates every rank must hold the same parameters, bit for bit
+    replicas_identical = None
+    if world > 1:
+        lib.sync()
+        p = model.slab_params()
+        chk = torch.tensor([float(p.astype(np.float64).sum()), float(np.abs(p).astype(np.float64).sum())], dtype=torch.float64, device="cuda")
+        lo, hi = chk.clone(), chk.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN); dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        replicas_identical = bool(torch.equal(lo, hi))
 
     # ---- per-kernel timing of one eagerly issued step (CUDA events on the launching stream around every launch)
     model.use_graph(False)
@@ -277,30 +342,59 @@ def main():
         total_ms = sum(t for _, t in kern.values())
         contraction = {k: v for k, v in kern.items() if "gemm" in k}
         c_ms = sum(t for _, t in contraction.values()); c_n = sum(c for c, _ in contraction.values())
+        staging = {k: v for k, v in kern.items() if any(tag in k for tag in STAGING_KERNELS)}
+        s_ms = sum(t for _, t in staging.values()); s_n = sum(c for c, _ in staging.values())
         top = max(kern.items(), key=lambda kv: kv[1][1]) if kern else ("none", (0, 0.0))
         tf32_peak = peaks["bf16_tflops_sustained"] / 2.0
+        # The dominant kernel's DRAM traffic comes from its ncu capture (profiles/tc_gemm_taps_conv64x64_3x3_batch512.md: a
+        # batch-512 layer, because a batch-128 layer sits inside the 126 MB L2; traffic grows in proportion to the batch):
+        # 33.8 MB read + 33.6 MB written per launch at batch 512 for 33.55 + 0.15 MB of operands and 33.55 MB of output.
+        traffic_b512, algo_b512 = 33.8e6 + 33.6e6, (512 * 64 * 256 + 9 * 64 * 64 + 512 * 64 * 256) * 4.0
         roofline = {"bound": "tensor", "kernel": "contraction engine (all conv fwd/dgrad/wgrad and gemm launches of one step)",
                     "achieved": flops / (c_ms / 1e3) / 1e12 if c_ms else None, "peak": tf32_peak, "unit": "TFLOP/s",
-                    "frac": (flops / (c_ms / 1e3) / 1e12 / tf32_peak) if c_ms else None, "traffic": None,
+                    "frac": (flops / (c_ms / 1e3) / 1e12 / tf32_peak) if c_ms else None,
+                    "traffic": traffic_b512 * BATCH / 512.0, "algorithmic_bytes": algo_b512 * BATCH / 512.0,
+                    "traffic_note": "DRAM bytes per launch of the 3x3 64->64 16x16 forward convolution, ncu capture at batch 512 scaled to batch %d" % BATCH,
                     "peak_source": "%s bf16 sustained / 2 (TF32 rate is half the bf16 rate)" % peaks["source"],
                     "launches_per_step": c_n, "ms_per_step": c_ms, "share_of_step_kernel_time": c_ms / total_ms if total_ms else None,
+                    "frac_with_staging": (flops / ((c_ms + s_ms) / 1e3) / 1e12 / tf32_peak) if c_ms else None,
+                    "whole_step_frac": value / world * (flops / BATCH) / 1e12 / tf32_peak,
                     "top_kernel": top[0][:80], "top_kernel_ms": top[1][1]}
+        # HBM side: the streaming kernels of the same eagerly issued step, compulsory bytes over event-timed duration
+        want = hbm_bound_bytes(BATCH)
+        h_bytes = h_ms = 0.0; per_class = {}
+        for tag, nbytes in want.items():
+            t = sum(v[1] for k, v in kern.items() if tag in k)
+            if t > 0:
+                h_bytes += nbytes; h_ms += t
+                per_class[tag] = {"ms": round(t, 4), "GB/s": round(nbytes / (t / 1e3) / 1e9, 1), "frac": round(nbytes / (t / 1e3) / 1e9 / peaks["hbm_gbs"], 3)}
+        roofline_hbm = {"bound": "hbm", "kernel": "streaming kernels of one step (batch norm, ReLU/add fusions, pooling, SGD)",
+                        "achieved": h_bytes / (h_ms / 1e3) / 1e9 if h_ms else None, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                        "frac": (h_bytes / (h_ms / 1e3) / 1e9 / peaks["hbm_gbs"]) if h_ms else None,
+                        "frac_of_nominal_8TBs": (h_bytes / (h_ms / 1e3) / 1e9 / 8000.0) if h_ms else None,
+                        "bytes_per_step": h_bytes, "ms_per_step": h_ms, "peak_source": peaks["source"] + " copy bandwidth", "classes": per_class}
         line = {"metric": METRIC, "value": value, "unit": "samples/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
                 "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
                 "dtype": args.math if args.math == "tf32" else "f32", "data": "synthetic",
                 "config": {"workload": "resnet50_cifar_train_step_sgd_lr0.1", "batch_per_gpu": BATCH, "global_batch": BATCH * world,
                            "parallelism": "dp%d" % world, "replay": "cuda_graph", "l2": "per-step working set (~3 GB of activations and gradients) exceeds the 126 MB L2",
                            "step_gflop": flops / 1e9},
-                "e2e": {"value": e2e, "unit": "samples/s", "ms_per_step": ms_e2e / args.steps, "h2d_bytes_per_step": BATCH * 3072 * 4 + BATCH * 4, "d2h_bytes_per_step": 4},
-                "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline, "device_status": status,
+                "timing": {"blocks": len(blocks), "steps_per_block": args.steps, "block_ms_median": ms, "block_ms_min": min(blocks), "block_ms_max": max(blocks),
+                           "timed_region_s": sum(blocks) / 1e3, "note": "value and ms_per_step are the median block of exactly `steps` steps"},
+                "e2e": {"value": e2e, "unit": "samples/s", "ms_per_step": ms_e2e / args.steps, "h2d_bytes_per_step": BATCH * 3072 * 4 + BATCH * 4, "d2h_bytes_per_step": 4,
+                        "blocks": len(blocks_e2e)},
+                "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline, "roofline_hbm": roofline_hbm,
+                "staging_ms_per_step": s_ms, "staging_launches_per_step": s_n, "device_status": status,
                 "loss": {"resident_last": loss_resident, "e2e_first": losses[3] if len(losses) > 3 else None, "e2e_last": losses[-1]},
                 "kernels_ms_per_step": {k[:60]: round(v[1], 4) for k, v in sorted(kern.items(), key=lambda kv: -kv[1][1])[:12]}}
+        if world > 1:
+            line["exposed_comm_ms"] = float(exposed.value)
+            line["replicas_identical"] = replicas_identical
         if world == 1 and not args.no_cpu_baseline:
             threads = os.cpu_count() or 1
-            sample = 8
-            sec = cpu_steps(sample, 3, 1, threads)
-            line["cpu_baseline"] = {"value": sample / sec, "unit": "samples/s", "cores": threads, "kind": "port",
-                                    "sample": "3 steps of %d samples (slice of the 128-sample batch) after 1 warm-up, all host threads" % sample}
+            sec = cpu_steps(BATCH, 2, 1, threads)
+            line["cpu_baseline"] = {"value": BATCH / sec, "unit": "samples/s", "cores": threads, "kind": "port", "blas": CPU_BLAS, "same_config": True,
+                                    "sample": "2 steps of the full %d-sample batch after 1 warm-up, all host threads" % BATCH}
         print(json.dumps(line), flush=True)
     model.close()
     lib.shutdown()

@@ -320,6 +320,10 @@ int LTB_FN(comm_world)(void);
  * ever). On an error or a timeout the communicator is aborted, the call returns LTB_E_COMM, and later collectives are
  * refused with LTB_E_COMM until comm_destroy / comm_init. */
 int LTB_FN(comm_set_timeout_ms)(int64_t ms);
+/* Measurement: milliseconds between the end of backward on the compute stream and the start of the update kernel of the
+ * last allreduce_sgd_step that followed allreduce_begin calls (the part of the exchange that backward did not hide);
+ * 0 with one rank. Waits for that step to finish. */
+int LTB_FN(comm_exposed_ms)(float* out_ms);
 int LTB_FN(allreduce_sum)(float* x, int64_t n);
 /* Starts, while backward is still running, the sum of a gradient range that is already final; the allreduce_sgd_step
  * that follows over a span containing it only waits for that sum. No-op with one rank. */

@@ -39,6 +39,9 @@ struct Nccl {
   static const int kMaxEarly = 16;
   struct Early { float* ptr; int64_t n; cudaEvent_t done; } early[kMaxEarly] = {};
   int n_early = 0;
+  // measurement: the end of backward on the compute stream and the start of the update kernel, as timed events
+  cudaEvent_t t_backward_end = nullptr, t_update_start = nullptr;
+  bool timed = false;
 } nccl;
 
 static int load_nccl() {
@@ -131,6 +134,7 @@ int ltb_comm_init(int rank, int world, const void* id128) {
   for (auto& e : nccl.done) LTB_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
   for (auto& e : nccl.early) LTB_CUDA(cudaEventCreateWithFlags(&e.done, cudaEventDisableTiming));
   nccl.n_early = 0;
+  LTB_CUDA(cudaEventCreate(&nccl.t_backward_end)); LTB_CUDA(cudaEventCreate(&nccl.t_update_start)); nccl.timed = false;
   return LTB_OK;
 }
 int ltb_comm_destroy(void) {
@@ -145,13 +149,24 @@ int ltb_comm_destroy(void) {
     for (auto& e : nccl.done) cudaEventDestroy(e);
     for (auto& e : nccl.early) cudaEventDestroy(e.done);
   }
-  nccl.comm_stream = nullptr; nccl.broken = false;
+  if (nccl.t_backward_end) { cudaEventDestroy(nccl.t_backward_end); cudaEventDestroy(nccl.t_update_start); nccl.t_backward_end = nccl.t_update_start = nullptr; }
+  nccl.comm_stream = nullptr; nccl.broken = false; nccl.timed = false;
   nccl.n_early = 0;
   nccl.world = 1; nccl.rank = 0;
   return LTB_OK;
 }
 int ltb_comm_world(void) { return nccl.world; }
 int ltb_comm_set_timeout_ms(int64_t ms) { nccl.timeout_ms = ms; return LTB_OK; }
+// The part of the gradient exchange that the last data-parallel step could not hide: the time from the end of backward on
+// the compute stream to the start of the update kernel, which waits for every sum.  Blocks until that step has finished.
+int ltb_comm_exposed_ms(float* out_ms) {
+  LTB_INITED(); LTB_REQUIRE(out_ms, "ltb_comm_exposed_ms: null pointer");
+  *out_ms = 0.0f;
+  if (nccl.world == 1 || !nccl.timed) return LTB_OK;
+  int rc = comm_wait_stream(g.stream, "ltb_comm_exposed_ms"); if (rc) return rc;
+  LTB_CUDA(cudaEventElapsedTime(out_ms, nccl.t_backward_end, nccl.t_update_start));
+  return LTB_OK;
+}
 
 int ltb_allreduce_sum(float* x, int64_t n) {
   LTB_INITED(); LTB_REQUIRE(x && n >= 0, "ltb_allreduce_sum: bad argument");
@@ -200,6 +215,10 @@ int ltb_allreduce_sgd_step(float* x, float* d, float lr, int64_t n) {
     else return fail(LTB_E_ARG, "ltb_allreduce_sgd_step: a range given to ltb_allreduce_begin lies outside this span");
   }
   for (int i = 1; i < ne; ++i) for (int j = i; j > 0 && nccl.early[order[j]].ptr < nccl.early[order[j - 1]].ptr; --j) { int t = order[j]; order[j] = order[j - 1]; order[j - 1] = t; }
+  // Inside a recorded step an ordinary event record is only a dependency; the external form makes a node that really
+  // records the event at every replay, so that ltb_comm_exposed_ms can read the last step's span.
+  const unsigned rec = g.capturing ? cudaEventRecordExternal : cudaEventRecordDefault;
+  LTB_CUDA(cudaEventRecordWithFlags(nccl.t_backward_end, g.stream, rec));
   LTB_CUDA(cudaEventRecord(nccl.ready, g.stream));
   LTB_CUDA(cudaStreamWaitEvent(nccl.comm_stream, nccl.ready, 0));
   int64_t cursor = 0; int rc = LTB_OK;
@@ -229,6 +248,7 @@ int ltb_allreduce_sgd_step(float* x, float* d, float lr, int64_t n) {
     // everything on the communication stream so far (early ranges and gaps, in issue order) precedes this event
     LTB_CUDA(cudaEventRecord(nccl.done[0], nccl.comm_stream));
     LTB_CUDA(cudaStreamWaitEvent(g.stream, nccl.done[0], 0));
+    LTB_CUDA(cudaEventRecordWithFlags(nccl.t_update_start, g.stream, rec)); nccl.timed = true;
     rc = update_range(x, d, 0, n, s);
   }
   nccl.n_early = 0;

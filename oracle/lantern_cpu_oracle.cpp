@@ -1140,6 +1140,7 @@ static int transport_sum(float* buf, int64_t n, const char* who) {
                                                                       : ": the transport reported an error") + "; the communicator was aborted").c_str());
 }
 int ora_comm_set_transport(ora_allreduce_fn fn) { ProfScope prof_scope_("ora_comm_set_transport"); g_transport = fn; return LTB_OK; }
+int ora_comm_exposed_ms(float* out_ms) { if (out_ms) *out_ms = 0.0f; return LTB_OK; }   // the CPU transport is synchronous: nothing overlaps
 int ora_comm_set_timeout_ms(int64_t ms) { ProfScope prof_scope_("ora_comm_set_timeout_ms"); g_timeout_ms = ms; return LTB_OK; }
 int ora_comm_unique_id(void* out128) { ProfScope prof_scope_("ora_comm_unique_id"); memset(out128, 0, 128); return LTB_OK; }
 int ora_comm_init(int rank, int world, const void*) { ProfScope prof_scope_("ora_comm_init");
