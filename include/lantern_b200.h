@@ -74,6 +74,23 @@ int    LTB_FN(set_math)(int mode);                      /* LTB_MATH_TF32 (defaul
  * of the launch moves: a held operation is issued by the next call of this library whatever it is (sync, copies,
  * get_stream and graph_end included). A host that enqueues its own work on the stream must call get_stream or sync first. */
 int    LTB_FN(set_fusion)(int on);
+/* Filter cache, off by default (no counterpart in the reference, where cuDNN reads OIHW filters as they are). The tensor-core
+ * engine reads the filter of an R x S convolution as one matrix per tap; forward and data-grad each need their own form, and
+ * without the cache both are rebuilt at every call. With it on they are kept, keyed by the filter's address and shape, and
+ * rebuilt once after the parameters changed. The library notes a change by itself in every entry point through which a
+ * generated program writes parameters: the optimizer steps (sgd_step*, adagrad_update, momentum_update, allreduce_*), h2d,
+ * d2d, fill*, randinit, clip, geam, the in-place elementwise forms, and a replayed step. A host that writes a filter by
+ * any other route (as the output of another operator, or with its own kernel) must call params_changed afterwards. */
+/* Deterministic mode, off by default (the counterpart of choosing cuDNN's deterministic algorithms, which the reference does
+ * not do: it takes whatever cudnnFind*Algorithm ranks first, TensorDslCudnn.scala:515-624). A contraction whose output has few
+ * tiles is split over its reduction dimension. By default the splits add their partial results into the output atomically,
+ * in whatever order they finish, so the last bits of such a sum can differ from run to run. With this mode on, up to eight
+ * splits form a thread-block cluster that adds its tiles up in a fixed order through shared memory, and larger splits go
+ * through slabs of partial results summed in a fixed order by one more launch: a step of the tensor-core path then gives
+ * the same bits on every run, at about a third more time in the contraction kernels. */
+int    LTB_FN(set_deterministic)(int on);
+int    LTB_FN(set_filter_cache)(int on);
+int    LTB_FN(params_changed)(void);
 int    LTB_FN(device_status)(void);                     /* 0, or LTB_E_DEVICE if a kernel's bounded wait expired */
 /* Failure detection on the device (no counterpart in the reference, whose kernels never wait on anything). Every spin wait
  * inside a kernel of this library (on a TMA or tensor-core completion barrier) gives up after a limit, records a code in

@@ -68,9 +68,12 @@ trait TensorDslB200 extends TensorDslCublas {
     // ---- lifetime, arena, initialisation (TensorDifferentiation.scala:139-179) ---------------------------------------
     // ltb_set_fusion(1): every device operation of a staged program goes through this library, so its one-call look-ahead
     // (batch norm or add joined by the in-place ReLU that follows, and the mirror image in backward) is safe.
+    // ltb_set_filter_cache(1): a staged program writes its filters only through the optimizer, transfer and fill entry
+    // points, which is what the cache of per-tap filter forms relies on.
     override def setup(): Unit = {
       ltb("init", 0, "HEAP_SIZE")
       ltb("set_fusion", 1)
+      ltb("set_filter_cache", 1)
     }
     override def cleanup(): Unit = ltb("shutdown")
 

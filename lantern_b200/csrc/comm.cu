@@ -169,7 +169,7 @@ int ltb_comm_exposed_ms(float* out_ms) {
 }
 
 int ltb_allreduce_sum(float* x, int64_t n) {
-  LTB_INITED(); LTB_REQUIRE(x && n >= 0, "ltb_allreduce_sum: bad argument");
+  LTB_INITED(); filter_cache_note_write(x, (size_t)(n > 0 ? n : 0) * 4); LTB_REQUIRE(x && n >= 0, "ltb_allreduce_sum: bad argument");
   if (nccl.world == 1 || n == 0) return LTB_OK;
   if (nccl.broken) return fail(LTB_E_COMM, "ltb_allreduce_sum: the communicator was aborted");
   LTB_NCCL(nccl.AllReduce(x, x, (size_t)n, ncclFloat, ncclSum, nccl.comm, g.stream));
@@ -202,7 +202,7 @@ static int update_range(float* x, float* d, int64_t off, int64_t cnt, float s) {
   return LTB_OK;
 }
 int ltb_allreduce_sgd_step(float* x, float* d, float lr, int64_t n) {
-  LTB_INITED(); LTB_REQUIRE(x && d && n >= 0, "ltb_allreduce_sgd_step: bad argument");
+  LTB_INITED(); filter_cache_note_write(x, (size_t)(n > 0 ? n : 0) * 4); LTB_REQUIRE(x && d && n >= 0, "ltb_allreduce_sgd_step: bad argument");
   if (nccl.world == 1) return ltb_sgd_step(x, d, lr, n);
   if (n == 0) return LTB_OK;
   if (nccl.broken) return fail(LTB_E_COMM, "ltb_allreduce_sgd_step: the communicator was aborted");

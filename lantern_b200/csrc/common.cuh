@@ -40,6 +40,8 @@ struct Context {
   char* heap = nullptr;
   size_t heap_bytes = 0;
   size_t used = 0;
+  size_t top_used = 0;                // bytes taken from the far end of the arena for blocks that live until ltb_reset (step_alloc)
+  bool keep_off = false;              // the two ends met once: nothing is kept at the far end any more
   int fatal = 1;
   int last = 0;
   std::string msg;
@@ -57,6 +59,8 @@ struct Context {
   const char* label = nullptr;        // optional name override for the next launches
   cudaStream_t side = nullptr;        // second stream: the weight-gradient half of conv backward runs beside the data-gradient half
   cudaEvent_t fork_ev = nullptr, join_ev = nullptr;
+  bool deterministic = false;         // split-K sums in a fixed order (clusters, slabs) instead of atomics (ltb_set_deterministic)
+  bool filter_cache = false;          // per-tap filter forms kept across calls (ltb_set_filter_cache)
   bool fusion = false;                // look-ahead fusion of BN/add with ReLU (off unless the host opts in)
   Pending pending;
   bool hold_workspace = false;        // while two halves are in flight their staging blocks are released together at the end
@@ -77,6 +81,13 @@ int bn_fwd_issue(const Pending& p, bool relu);
 int add_issue(const float* a, const float* b, float* out, int64_t n, bool relu);
 int relu_grad_issue(const float* y, float* d, int64_t n);
 // Host waits while a communicator exists: bounded, with NCCL's asynchronous error state polled (comm.cu).
+void filter_cache_clear();           // gemm_tc.cu
+void cl_cache_clear();               // gemm_tc.cu: kept channels-last copies (they live in step_alloc blocks)
+void cl_cache_drop_from(const void* p);
+// A block from the far end of the arena that stays until ltb_reset; nullptr when the two ends would meet (context.cu).
+void* step_alloc(size_t bytes);
+// A call is about to write [p, p + bytes): cached filter forms whose source overlaps it are stale (p == nullptr: all of them).
+void filter_cache_note_write(const void* p, size_t bytes);
 bool comm_active();
 int comm_wait_stream(cudaStream_t s, const char* what);
 int comm_wait_event(cudaEvent_t ev, const char* what);

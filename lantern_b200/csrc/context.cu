@@ -131,6 +131,8 @@ int ltb_shutdown(void) {
   ltb_comm_destroy();
   static_sum_forget();
   profile_clear();
+  cudaStreamSynchronize(g.stream); cudaStreamSynchronize(g.side); cudaStreamSynchronize(g.branch);
+  filter_cache_clear(); cl_cache_clear();
   for (int i = 0; i < 16; ++i) { if (marker_ev[i]) cudaEventDestroy(marker_ev[i]); marker_ev[i] = nullptr; marker_set[i] = false; }
   release_all();
   return LTB_OK;
@@ -151,6 +153,13 @@ static int stream_wait(const char* what) {
 }
 int ltb_sync(void) { LTB_INITED(); return stream_wait("ltb_sync"); }
 int ltb_set_fusion(int on) { LTB_INITED(); g.fusion = on != 0; return LTB_OK; }
+int ltb_set_filter_cache(int on) {
+  LTB_INITED(); LTB_REQUIRE(!g.capturing, "ltb_set_filter_cache: not while recording a step");
+  if (!on && g.filter_cache) { cudaStreamSynchronize(g.stream); cudaStreamSynchronize(g.side); cudaStreamSynchronize(g.branch); filter_cache_clear(); }
+  g.filter_cache = on != 0; return LTB_OK;
+}
+int ltb_set_deterministic(int on) { LTB_INITED(); LTB_REQUIRE(!g.capturing, "ltb_set_deterministic: not while recording a step"); g.deterministic = on != 0; return LTB_OK; }
+int ltb_params_changed(void) { LTB_INITED(); filter_cache_note_write(nullptr, 0); return LTB_OK; }
 int ltb_set_math(int mode) {
   LTB_REQUIRE(mode == LTB_MATH_FP32 || mode == LTB_MATH_TF32, "ltb_set_math: unknown mode %d", mode);
   g.math = mode; return LTB_OK;
@@ -173,7 +182,13 @@ int64_t ltb_kernel_launches(void) { return g.launches; }
 static void* arena_alloc(size_t bytes, bool zero) {
   if (!g.inited) { fail(LTB_E_STATE, "ltb_malloc: library not initialised"); return nullptr; }
   size_t b = round_up(bytes ? bytes : 1);
-  if (g.used + b > g.heap_bytes) {
+  if (g.used + b + g.top_used > g.heap_bytes && g.top_used && !g.capturing) {
+    // The far end's kept copies are a convenience and yield to a real allocation: wait for their readers, drop them, and keep
+    // nothing from now on (this arena is too tight for them).  Not possible while a step is being recorded: that is an overflow.
+    cudaStreamSynchronize(g.stream); cudaStreamSynchronize(g.side); cudaStreamSynchronize(g.branch);
+    cl_cache_clear(); g.top_used = 0; g.keep_off = true;
+  }
+  if (g.used + b + g.top_used > g.heap_bytes) {
     fail(LTB_E_OOM, "ltb_malloc: arena exhausted (%zu used + %zu requested > %zu)", g.used, b, g.heap_bytes);
     return nullptr;
   }
@@ -182,6 +197,17 @@ static void* arena_alloc(size_t bytes, bool zero) {
   if (zero && cudaMemsetAsync(p, 0, b, g.stream) != cudaSuccess) { fail(LTB_E_CUDA, "ltb_malloc: memset failed"); return nullptr; }
   return p;
 }
+}  // extern "C"
+namespace ltb {
+void* step_alloc(size_t bytes) {
+  if (!g.inited || g.keep_off) return nullptr;
+  const size_t b = round_up(bytes ? bytes : 1);
+  if (g.used + g.top_used + b + ((size_t)256 << 20) > g.heap_bytes) return nullptr;     // leave the near end room to grow
+  g.top_used += b;
+  return g.heap + g.heap_bytes - g.top_used;
+}
+}  // namespace ltb
+extern "C" {
 void* ltb_malloc(size_t bytes) { return arena_alloc(bytes, true); }
 void* ltb_malloc_uninit(size_t bytes) { return arena_alloc(bytes, false); }
 int ltb_free(void* p, size_t bytes) {
@@ -189,6 +215,7 @@ int ltb_free(void* p, size_t bytes) {
   size_t b = round_up(bytes ? bytes : 1);
   LTB_REQUIRE(p && b <= g.used && (char*)p == g.heap + g.used - b, "ltb_free: not the newest block (LIFO arena)");
   g.used -= b;
+  cl_cache_drop_from(p);
   return LTB_OK;
 }
 void* ltb_mark(void) { return g.heap + g.used; }
@@ -198,13 +225,14 @@ int ltb_reset(void* mark) {
   LTB_REQUIRE(m >= g.heap && m <= g.heap + g.used, "ltb_reset: mark outside the used span");
   LTB_REQUIRE(!g.branch_marked, "ltb_reset: a branch region is open (ltb_branch_join missing)");
   g.used = (size_t)(m - g.heap);   // zeroing happens when a block is handed out again by ltb_malloc
+  g.top_used = 0; cl_cache_clear();  // the step's kept copies go with it
   return LTB_OK;
 }
 size_t ltb_arena_used(void) { return g.used; }
 
 // ------------------------------------------------------------------ transfers (GPUOps.scala:51-95)
 int ltb_h2d(void* dst, const void* src, size_t bytes) {
-  LTB_INITED(); LTB_REQUIRE(dst && src, "ltb_h2d: null pointer");
+  LTB_INITED(); filter_cache_note_write(dst, bytes); LTB_REQUIRE(dst && src, "ltb_h2d: null pointer");
   if (bytes) LTB_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, g.stream));
   return LTB_OK;
 }
@@ -215,7 +243,7 @@ int ltb_d2h(void* dst, const void* src, size_t bytes) {
   return stream_wait("ltb_d2h");
 }
 int ltb_d2d(void* dst, const void* src, size_t bytes) {
-  LTB_INITED(); LTB_REQUIRE(dst && src, "ltb_d2d: null pointer");
+  LTB_INITED(); filter_cache_note_write(dst, bytes); LTB_REQUIRE(dst && src, "ltb_d2d: null pointer");
   if (bytes) LTB_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, g.stream));
   return LTB_OK;
 }
@@ -309,7 +337,7 @@ void* ltb_graph_end(void) {
   return G;
 }
 int ltb_graph_launch(void* graph) {
-  LTB_INITED(); LTB_REQUIRE(graph, "ltb_graph_launch: null graph");
+  LTB_INITED(); filter_cache_note_write(nullptr, 0); LTB_REQUIRE(graph, "ltb_graph_launch: null graph");
   Graph* G = (Graph*)graph;
   LTB_CUDA(cudaGraphLaunch(G->exec, g.stream));
   g.launches += G->launches;
@@ -351,7 +379,7 @@ int ltb_profile_report(char* buf, int len) {
 // randinit on the reference's GPU backends draws on the CPU and uploads (TensorDslCublas.scala:154-155);
 // the stream is glibc rand(), consumed in element order (TensorDslCPU.scala:101-110).
 int ltb_randinit(float* x, int64_t n, float scale, int seed) {
-  LTB_INITED(); LTB_REQUIRE(x && n >= 0, "ltb_randinit: bad argument");
+  LTB_INITED(); filter_cache_note_write(x, (size_t)(n > 0 ? n : 0) * 4); LTB_REQUIRE(x && n >= 0, "ltb_randinit: bad argument");
   LTB_REQUIRE(!g.capturing, "ltb_randinit: host RNG while recording a step");
   if (seed >= 0) srand((unsigned)seed);
   std::vector<float> h((size_t)n);

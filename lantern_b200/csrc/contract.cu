@@ -100,6 +100,7 @@ int ltb_conv2d_bwd(const float* x, float* dx, const float* w, float* dw, float* 
   // half is issued on the side stream and the data-gradient half on the caller's, and the caller's stream waits for both
   // before the call returns: program order at the boundary is unchanged, and inside a recorded step the two become
   // parallel branches of the graph. Per-launch profiling keeps them serial so that each kernel is timed alone.
+  if (g.math == LTB_MATH_TF32) { rc = conv_bwd_prestage(dy, d, dx && dw); if (rc) return rc; }
   const bool overlap = dx && dw && !g.profiling && g.side != nullptr;
   const size_t arena_base = g.used;
   cudaStream_t main_stream = g.stream;

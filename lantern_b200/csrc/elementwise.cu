@@ -309,20 +309,20 @@ extern "C" {
 
 // fill / fillInPlace: TensorDslCPU.scala:30-35, 65-67.
 int ltb_fill(float* x, float v, int64_t n) {
-  LTB_INITED(); LTB_REQUIRE(x && n >= 0, "ltb_fill: bad argument");
+  LTB_INITED(); filter_cache_note_write(x, (size_t)(n > 0 ? n : 0) * 4); LTB_REQUIRE(x && n >= 0, "ltb_fill: bad argument");
   if (n) LTB_LAUNCH(fill_kernel, grid_for(n, 256), 256, 0, x, v, n);
   return LTB_OK;
 }
 // fillWithBias: TensorDslCPU.scala:41-61.
 int ltb_fill_with_bias(float* out, const float* bias, int outer, int c, int inner) {
-  LTB_INITED(); LTB_REQUIRE(out && bias && outer >= 0 && c > 0 && inner > 0, "ltb_fill_with_bias: bad argument");
+  LTB_INITED(); filter_cache_note_write(out, (size_t)outer * c * inner * 4); LTB_REQUIRE(out && bias && outer >= 0 && c > 0 && inner > 0, "ltb_fill_with_bias: bad argument");
   int64_t n = (int64_t)outer * c * inner;
   if (n) LTB_LAUNCH(fill_bias_kernel, grid_for(n, 256), 256, 0, out, bias, c, (int64_t)inner, n);
   return LTB_OK;
 }
 // clipAt: TensorDslCPU.scala:113-119.
 int ltb_clip(float* x, float bound, int64_t n) {
-  LTB_INITED(); LTB_REQUIRE(x && n >= 0, "ltb_clip: bad argument");
+  LTB_INITED(); filter_cache_note_write(x, (size_t)(n > 0 ? n : 0) * 4); LTB_REQUIRE(x && n >= 0, "ltb_clip: bad argument");
   return launch_map<1>(x, nullptr, nullptr, x, n, [bound] __device__(float v, float, float) { return v > bound ? bound : (v < -bound ? -bound : v); });
 }
 
@@ -365,14 +365,14 @@ int ltb_ew_binary_grad(int op, const float* a, float* da, const int* as, const f
 }
 // map(x, s => s op y): TensorDslCPU.scala:298-331.
 int ltb_ew_scalar(int op, const float* a, float s, float* out, int64_t n) {
-  LTB_INITED(); LTB_REQUIRE(a && out && n >= 0 && op >= LTB_ADD && op <= LTB_DIV, "ltb_ew_scalar: bad argument");
+  LTB_INITED(); filter_cache_note_write(out, (size_t)(n > 0 ? n : 0) * 4); LTB_REQUIRE(a && out && n >= 0 && op >= LTB_ADD && op <= LTB_DIV, "ltb_ew_scalar: bad argument");
   return launch_map<1>(a, nullptr, nullptr, out, n, [op, s] __device__(float x, float, float) { return bin_op(op, x, s); });
 }
 int ltb_ew_inplace_scalar(int op, float* x, float s, int64_t n) { return ltb_ew_scalar(op, x, s, x, n); }
 
 // inplaceElementWiseOpWithBroadCastOrReduce: TensorDslCPU.scala:265-279.
 int ltb_ew_inplace(int op, float* x, const int* xs, const float* y, const int* ys, int rank) {
-  LTB_INITED(); LTB_REQUIRE(x && y && op >= LTB_ADD && op <= LTB_DIV, "ltb_ew_inplace: bad argument");
+  LTB_INITED(); { size_t cnt_ = 1; for (int i_ = 0; i_ < rank && i_ < 8 && xs; ++i_) cnt_ *= (size_t)(xs[i_] > 0 ? xs[i_] : 1); filter_cache_note_write(x, cnt_ * 4); } LTB_REQUIRE(x && y && op >= LTB_ADD && op <= LTB_DIV, "ltb_ew_inplace: bad argument");
   Bcast p; int64_t n; bool xb, yb;
   LTB_REQUIRE(make_bcast(xs, ys, rank, p, n, xb, yb), "ltb_ew_inplace: shapes do not broadcast");
   if (!xb && !yb) return launch_map<2>(x, y, nullptr, x, n, [op] __device__(float u, float v, float) { return bin_op(op, u, v); });
@@ -390,7 +390,7 @@ int ltb_plus_bias_grad(float* dbias, const int* bs, const float* dmain, const in
 
 // geam: TensorDslCPU.scala:342-347 / cublasSgeam at TensorDslCublas.scala:318-373.
 int ltb_geam(const float* x, int tx, float alpha, const float* y, int ty, float beta, float* out, int rows, int cols) {
-  LTB_INITED(); LTB_REQUIRE(x && y && out && rows > 0 && cols > 0, "ltb_geam: bad argument");
+  LTB_INITED(); filter_cache_note_write(out, (size_t)rows * cols * 4); LTB_REQUIRE(x && y && out && rows > 0 && cols > 0, "ltb_geam: bad argument");
   LTB_REQUIRE(!((tx || ty) && (out == x || out == y)), "ltb_geam: in-place with transpose");
   int64_t n = (int64_t)rows * cols;
   if (!tx && !ty) return launch_map<2>(x, y, nullptr, out, n, [alpha, beta] __device__(float u, float v, float) { return u * alpha + v * beta; });
@@ -491,7 +491,7 @@ int ltb_concat_grad(float* const* dinputs, const float* dout, const int* dims, i
 
 // SGD.step: NNModule.scala:265-287.
 int ltb_sgd_step(float* x, float* d, float lr, int64_t n) {
-  LTB_INITED(); LTB_REQUIRE(x && d && n >= 0, "ltb_sgd_step: bad argument");
+  LTB_INITED(); filter_cache_note_write(x, (size_t)(n > 0 ? n : 0) * 4); LTB_REQUIRE(x && d && n >= 0, "ltb_sgd_step: bad argument");
   if (!n) return LTB_OK;
   float neg_lr = -1.0f * lr;
   int64_t n4 = (aligned16(x) && aligned16(d)) ? n / 4 : 0;
@@ -501,7 +501,7 @@ int ltb_sgd_step(float* x, float* d, float lr, int64_t n) {
 }
 // One launch for a whole list of parameter tensors (the reference issues 2 launches per tensor, 267 tensors for ResNet-50).
 int ltb_sgd_step_multi(float* const* xs, float* const* ds, const int64_t* sizes, int nt, float lr) {
-  LTB_INITED(); LTB_REQUIRE(xs && ds && sizes && nt >= 0, "ltb_sgd_step_multi: bad argument");
+  LTB_INITED(); filter_cache_note_write(nullptr, 0); LTB_REQUIRE(xs && ds && sizes && nt >= 0, "ltb_sgd_step_multi: bad argument");
   if (!nt) return LTB_OK;
   LTB_REQUIRE((size_t)nt * sizeof(SgdChunk) <= g.cur_scratch_bytes(), "ltb_sgd_step_multi: too many tensors");
   LTB_REQUIRE(!g.capturing, "ltb_sgd_step_multi: uploads its tensor list; use ltb_sgd_step on a slab while recording");
@@ -515,12 +515,12 @@ int ltb_sgd_step_multi(float* const* xs, float* const* ds, const int64_t* sizes,
   return LTB_OK;
 }
 int ltb_adagrad_update(float* x, float* d, float* h, float lr, float clip, int descent, int64_t n) {
-  LTB_INITED(); LTB_REQUIRE(x && d && h && n >= 0, "ltb_adagrad_update: bad argument");
+  LTB_INITED(); filter_cache_note_write(x, (size_t)(n > 0 ? n : 0) * 4); LTB_REQUIRE(x && d && h && n >= 0, "ltb_adagrad_update: bad argument");
   if (n) LTB_LAUNCH(adagrad_kernel, grid_for(n, 256), 256, 0, x, d, h, lr, clip, descent, n);
   return LTB_OK;
 }
 int ltb_momentum_update(float* x, float* d, float* m, float lr, float mu, float clip, int nesterov, int descent, int64_t n) {
-  LTB_INITED(); LTB_REQUIRE(x && d && m && n >= 0, "ltb_momentum_update: bad argument");
+  LTB_INITED(); filter_cache_note_write(x, (size_t)(n > 0 ? n : 0) * 4); LTB_REQUIRE(x && d && m && n >= 0, "ltb_momentum_update: bad argument");
   if (n) LTB_LAUNCH(momentum_kernel, grid_for(n, 256), 256, 0, x, d, m, lr, mu, clip, nesterov, descent, n);
   return LTB_OK;
 }

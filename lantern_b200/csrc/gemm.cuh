@@ -21,5 +21,7 @@ int gemm_tc(const float* a, bool a_kmajor, const float* b, bool b_kmajor, float*
 int conv_fwd_tc(const float* x, const float* w, const float* bias, float* y, const ConvDims& d);
 int conv_dgrad_tc(const float* dy, const float* w, float* dx, const ConvDims& d);
 int conv_wgrad_tc(const float* x, const float* dy, float* dw, const ConvDims& d);
+// Before the two halves of a convolution's backward call are issued: stages what both will read (one channels-last copy of dy).
+int conv_bwd_prestage(const float* dy, const ConvDims& d, bool both_halves);
 
 }  // namespace ltb

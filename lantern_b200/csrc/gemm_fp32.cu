@@ -136,7 +136,7 @@ __global__ void skinny_k_kernel(const float* __restrict__ a, int64_t sam, int64_
 // sixteen blocks walking all of K).
 template <bool ACC>
 __global__ void skinny_m_kernel(const float* __restrict__ a, int64_t sam, int64_t sak, const float* __restrict__ b, int64_t sbk, int64_t sbn,
-                                float* c, int64_t scm, int64_t scn, int M, int N, int K, float alpha) {
+                                float* c, int64_t scm, int64_t scn, int M, int N, int K, float alpha, float* part) {
   const int n = blockIdx.x * blockDim.x + threadIdx.x;
   if (n >= N) return;
   const int k0 = (int)((int64_t)K * blockIdx.y / gridDim.y), k1 = (int)((int64_t)K * (blockIdx.y + 1) / gridDim.y);
@@ -152,21 +152,28 @@ __global__ void skinny_m_kernel(const float* __restrict__ a, int64_t sam, int64_
 #pragma unroll
   for (int m = 0; m < 16; ++m) if (m < M) {
     float* q = c + (int64_t)m * scm + (int64_t)n * scn;
-    if (gridDim.y > 1) atomicAdd(q, alpha * acc[m]); else *q = ACC ? *q + alpha * acc[m] : alpha * acc[m];
+    if (part) part[((int64_t)blockIdx.y * M + m) * N + n] = acc[m];              // K was split: this block's share goes to its own slab
+    else *q = ACC ? *q + alpha * acc[m] : alpha * acc[m];
+  }
+}
+// c[m][n] (+)= alpha * (part[0][m][n] + part[1][m][n] + ...), in that order: the second half of skinny_m_kernel when K is split.
+template <bool ACC>
+__global__ void skinny_sum_kernel(const float* __restrict__ part, int slabs, float* c, int64_t scm, int64_t scn, int M, int N, float alpha) {
+  const int64_t total = (int64_t)M * N;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    float v = 0.0f;
+    for (int z = 0; z < slabs; ++z) v += part[(int64_t)z * total + i];
+    float* q = c + (i / N) * scm + (i % N) * scn;
+    *q = ACC ? *q + alpha * v : alpha * v;
   }
 }
 static int skinny_gemm(const float* a, int64_t sam, int64_t sak, const float* b, int64_t sbk, int64_t sbn, float* c, int64_t scm, int64_t scn,
                        int M, int N, int K, float alpha, bool accumulate, bool* taken) {
   *taken = true;
   if (N <= 16 && sak == 1 && sbk == 1 && K >= 128 && M <= 65535) {
-    // a lane walks its share of K one dependent step at a time: few rows with a long K are split over more blocks
-    int ks = (int)ceil_div(2 * g.sm_count, M);
-    if (ks > K / 512) ks = K / 512;
-    if (ks < 1) ks = 1;
-    if (ks > 1 && !accumulate) {                     // the splits add atomically: start from zero (dense outputs only)
-      if (scn == 1 && scm == N) { LTB_CUDA(cudaMemsetAsync(c, 0, (size_t)M * N * sizeof(float), g.stream)); accumulate = true; }
-      else ks = 1;
-    }
+    // one block per row, its four warps share K and are added in a fixed order: the same bits on every run (splitting K over
+    // more blocks would need atomics, whose order changes from run to run)
+    const int ks = 1;
     if (accumulate) LTB_LAUNCH(skinny_n_kernel<true>, dim3(M, ks), 128, 0, a, sam, b, sbn, c, scm, scn, N, K, alpha);
     else LTB_LAUNCH(skinny_n_kernel<false>, dim3(M, ks), 128, 0, a, sam, b, sbn, c, scm, scn, N, K, alpha);
   } else if (K <= 16) {
@@ -175,11 +182,21 @@ static int skinny_gemm(const float* a, int64_t sam, int64_t sak, const float* b,
     else LTB_LAUNCH(skinny_k_kernel<false>, grid, 256, 0, a, sam, sak, b, sbk, sbn, c, scm, scn, M, N, K, alpha);
   } else if (M <= 16 && N >= 256 && K <= 4096) {
     const unsigned gx = (unsigned)ceil_div(N, 128);
-    int ks = accumulate ? (int)ceil_div(2 * g.sm_count, (int64_t)gx) : 1;          // splits add atomically: accumulating calls only
+    // a lane's loop over k is a chain of dependent steps: a long K is split over blockIdx.y, every split writes its share
+    // into a slab of the library's workspace and a second small launch adds the slabs in order (no atomics: same bits every run)
+    int ks = (int)ceil_div(2 * g.sm_count, (int64_t)gx);
     if (ks > K / 8) ks = K / 8;
+    const size_t room = g.cur_scratch_bytes() / ((size_t)M * N * sizeof(float));
+    if ((size_t)ks > room) ks = (int)room;
     if (ks < 1) ks = 1;
-    if (accumulate) LTB_LAUNCH(skinny_m_kernel<true>, dim3(gx, ks), 128, 0, a, sam, sak, b, sbk, sbn, c, scm, scn, M, N, K, alpha);
-    else LTB_LAUNCH(skinny_m_kernel<false>, dim3(gx, ks), 128, 0, a, sam, sak, b, sbk, sbn, c, scm, scn, M, N, K, alpha);
+    float* part = ks > 1 ? g.cur_scratch() : nullptr;
+    if (accumulate) LTB_LAUNCH(skinny_m_kernel<true>, dim3(gx, ks), 128, 0, a, sam, sak, b, sbk, sbn, c, scm, scn, M, N, K, alpha, part);
+    else LTB_LAUNCH(skinny_m_kernel<false>, dim3(gx, ks), 128, 0, a, sam, sak, b, sbk, sbn, c, scm, scn, M, N, K, alpha, part);
+    if (part) {
+      const unsigned gr = (unsigned)grid_for((int64_t)M * N, 256);
+      if (accumulate) LTB_LAUNCH(skinny_sum_kernel<true>, gr, 256, 0, (const float*)part, ks, c, scm, scn, M, N, alpha);
+      else LTB_LAUNCH(skinny_sum_kernel<false>, gr, 256, 0, (const float*)part, ks, c, scm, scn, M, N, alpha);
+    }
   } else *taken = false;
   return LTB_OK;
 }

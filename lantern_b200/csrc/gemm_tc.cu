@@ -19,17 +19,24 @@
 // Every mbarrier wait is bounded: after about a second it records a code in the library's device status word and the CTA
 // runs to its normal teardown (TMEM is released on every path).  The single issuing lanes of warps 0 and 1 are rejoined by
 // their warps (__syncwarp) before the block-wide barrier, which needs converged warps.
+#include <cooperative_groups.h>
 #include <cuda.h>
+
+#include <vector>
 
 #include "gemm.cuh"
 #include "tc_plan.h"
 
 extern "C" void* ltb_malloc_uninit(size_t bytes);
+namespace ltb { void* step_alloc(size_t bytes); }
 extern "C" int ltb_free(void* p, size_t bytes);
+
+namespace cg = cooperative_groups;
 
 namespace ltb {
 
 constexpr int kMaxStages = 4;
+constexpr int kPartPitch = 129;                    // floats per column of a CTA's partial tile in shared memory (odd: reads along either axis are conflict-free)
 constexpr int kTcThreads = 320;                    // warp 0 TMA, warp 1 MMA, warps 2..9 epilogue
 
 struct TcOperandDev {
@@ -44,8 +51,14 @@ struct TcParams {
   int M, N, bn, k_iters, k_per_split, epilogue, accumulate, atomic, stages;
   uint32_t idesc;
   float* out; const float* bias; float alpha;
+  long long split_stride;      // floats between the result slabs of consecutive clusters of splits (see launch_plan)
+  int cluster_z;               // splits whose partial results are summed inside the kernel: a thread-block cluster of this many CTAs along z
   long long pix_per_img, img_stride, chan_stride, ld;
   int col_mod, col_mul;        // row-major epilogue: D column n goes to column (n % col_mod) * col_mul + n / col_mod when col_mul != 0
+  // Gather mode (gather_src != null): the A operand is not loaded by TMA but collected by the epilogue warps, which are idle
+  // during the main loop, straight from an activation tensor src[img][chan][pix] with pix = 4 or 16 (images too small for a
+  // 128-byte run of pixels), transposing it on the way into the K-major rows the tensor core reads.
+  const float* gather_src; int g_pix, g_chan, g_imgs;
   int* status;
   long long wait_cycles;       // bound of every spin wait, in clock64 ticks (the context's limit, ~1 s by default)
 };
@@ -159,7 +172,7 @@ struct BoxWalker {
 // epilogue warp per scheduler every extra dependent instruction is exposed latency.
 template <bool FULL>
 __device__ __forceinline__ void store_columns(float* p, long long stride, const uint32_t* r, float alpha, const float* bias, int lim, int mode) {
-  if (mode == 2) {                               // split-K: atomic accumulation (the bias pointer is set for split 0 only)
+  if (mode == 2) {                               // split-K, default mode: atomic accumulation (the bias pointer is set for split 0 only)
 #pragma unroll
     for (int j = 0; j < 32; ++j) { if (FULL || j < lim) atomicAdd(p, alpha * __uint_as_float(r[j]) + (bias ? bias[j] : 0.0f)); p += stride; }
   } else if (mode == 1) {                        // accumulate: all loads first, a load-add-store chain per element would serialise on latency
@@ -200,19 +213,40 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const int k_end = min(P.k_iters, k_begin + P.k_per_split);
   const int n_iter = k_end - k_begin;
   const int stages = P.stages;
+  const bool gather = P.gather_src != nullptr;
 
   // stage buffers, aligned to the 1024-byte swizzle atom
   uint8_t* stage_base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const uint32_t stage_bytes = P.a.stage_bytes + P.b.stage_bytes;
 
-  if (threadIdx.x == 0) {
-    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_a)) : "memory");
-    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_b)) : "memory");
-    for (int s = 0; s < stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-    mbar_init(&accum_bar, 1);
-    abort_flag = 0;
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  // Set-up.  The producer warp initialises the barriers and, without waiting for anybody, issues the loads that fill the
+  // (empty) ring: the copies are in flight while warp 1 allocates tensor memory and the block meets at the barrier below.
+  // Before that barrier nobody but the producer's issuing lane touches an mbarrier.
+  BoxWalker wa, wb;
+  int issued = 0;
+  if (warp == 0) {
+    if (lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_a)) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_b)) : "memory");
+      // a stage is full when the TMA bytes have landed (one arrival with the byte count) and, in gather mode, the eight
+      // gathering warps have stored their rows (one arrival each)
+      for (int s = 0; s < stages; ++s) { mbar_init(&full_bar[s], P.gather_src ? 9 : 1); mbar_init(&empty_bar[s], 1); }
+      mbar_init(&accum_bar, 1);
+      abort_flag = 0;
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    BoxWalker::init_pair(wa, wb, P.a, P.b, m_tile, n_tile, k_begin, lane);
+    if (lane == 0) {
+      const int first = n_iter < stages ? n_iter : stages;
+      for (; issued < first; ++issued) {
+        uint8_t* sa = stage_base + (size_t)issued * stage_bytes; uint8_t* sb = sa + P.a.stage_bytes;
+        mbar_expect_tx(&full_bar[issued], gather ? P.b.stage_bytes : stage_bytes);
+        if (!gather) { tma_load(&map_a, &full_bar[issued], sa, P.a.rank, wa.c); wa.next(P.a); }
+        tma_load(&map_b, &full_bar[issued], sb, P.b.rank, wb.c); wb.next(P.b);
+      }
+    }
+    __syncwarp();
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"((uint32_t)P.bn) : "memory");
@@ -224,16 +258,13 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const uint32_t tmem_base = tmem_slot;
 
   if (warp == 0) {
-    BoxWalker wa, wb;
-    BoxWalker::init_pair(wa, wb, P.a, P.b, m_tile, n_tile, k_begin, lane);
-    if (lane == 0 && n_iter > 0) {
-      int s = 0; uint32_t ph = 0;
-      for (int it = 0; it < n_iter; ++it) {
-        // the first `stages` fills find the ring empty: no wait, no barrier round trip
-        if (it >= stages && !mbar_wait(&empty_bar[s], ph ^ 1u, &abort_flag, P.status, 1, P.wait_cycles)) break;
+    if (lane == 0 && n_iter > issued) {
+      int s = 0; uint32_t ph = 1u;          // more iterations than stages: the ring was filled once, stage 0 is reused next, in its second round
+      for (int it = issued; it < n_iter; ++it) {
+        if (!mbar_wait(&empty_bar[s], ph ^ 1u, &abort_flag, P.status, 1, P.wait_cycles)) break;
         uint8_t* sa = stage_base + (size_t)s * stage_bytes; uint8_t* sb = sa + P.a.stage_bytes;
-        mbar_expect_tx(&full_bar[s], stage_bytes);
-        tma_load(&map_a, &full_bar[s], sa, P.a.rank, wa.c); wa.next(P.a);
+        mbar_expect_tx(&full_bar[s], gather ? P.b.stage_bytes : stage_bytes);
+        if (!gather) { tma_load(&map_a, &full_bar[s], sa, P.a.rank, wa.c); wa.next(P.a); }
         tma_load(&map_b, &full_bar[s], sb, P.b.rank, wb.c); wb.next(P.b);
         if (++s == stages) { s = 0; ph ^= 1u; }
       }
@@ -267,7 +298,55 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
     __syncwarp();
   } else if (n_iter > 0) {
-    // ---- epilogue warps 2..9: TMEM lane quarter = warp index mod 4; the two warps of a quarter take alternate 32-column chunks
+    // ---- warps 2..9.  In gather mode they first feed the A operand: warp g owns rows 16 g .. 16 g + 15 of the tile (one image
+    // of 16 pixels, or four images of 4), lane = channel within the 32-channel block of the k-iteration.  A lane reads its
+    // channel's 16 pixels (64 contiguous bytes, or four runs of 16) and stores them down its column of the tile: for a fixed
+    // pixel the 32 lanes write one whole 128-byte row (128-byte swizzle: 16-byte chunk j of row r sits at chunk j ^ (r & 7)),
+    // so the stores are free of bank conflicts.  The loads of the next two k-iterations are issued before this one is stored.
+    if (gather) {
+      const int gw = warp - 2, pix = P.g_pix, chan = P.g_chan;
+      const long long row0 = (long long)m_tile * 128 + gw * 16;                   // first tile row of this warp, as a pixel index
+      const long long img0 = row0 / pix;                                          // its image (pix 16) or first of four (pix 4)
+      const int runs = 16 / pix;                                                  // 1 run of 16 floats or 4 runs of 4
+      const uint32_t col = (uint32_t)(lane >> 2), sub = (uint32_t)(lane & 3) << 2;
+      float4 cur[4], nxt[4], nx2[4];                                             // the loads of two k-iterations are in flight while one is stored
+      auto fetch = [&](int it, float4* v) {
+        const int c = (k_begin + it) * 32 + lane;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const long long img = runs == 1 ? img0 : img0 + j;
+          const bool ok = c < chan && img < P.g_imgs;
+          const float4* src = reinterpret_cast<const float4*>(P.gather_src + (img * chan + c) * pix) + (runs == 1 ? j : 0);
+          v[j] = ok ? __ldg(src) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+      };
+      fetch(0, cur);
+      if (n_iter > 1) fetch(1, nxt);
+      int s = 0; uint32_t ph = 0;
+      for (int it = 0; it < n_iter; ++it) {
+        if (it + 2 < n_iter) fetch(it + 2, nx2);
+        bool ok = true;
+        if (it >= stages) { if (lane == 0) ok = mbar_wait(&empty_bar[s], ph ^ 1u, &abort_flag, P.status, 4, P.wait_cycles); ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0; }
+        if (!ok) break;
+        uint8_t* sa = stage_base + (size_t)s * stage_bytes + (size_t)gw * 16 * 128;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float e[4] = {cur[j].x, cur[j].y, cur[j].z, cur[j].w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const uint32_t r = (uint32_t)(j * 4 + i);                            // row within this warp's sixteen (gw * 16 is a multiple of 8: r & 7 is the swizzle phase)
+            *reinterpret_cast<float*>(sa + r * 128 + (((col ^ (r & 7u)) << 4) | sub)) = e[i];
+          }
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");             // the tensor core reads shared memory through the async proxy
+        __syncwarp();
+        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&full_bar[s])) : "memory");
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { cur[j] = nxt[j]; nxt[j] = nx2[j]; }
+        if (++s == stages) { s = 0; ph ^= 1u; }
+      }
+    }
+    // ---- epilogue: TMEM lane quarter = warp index mod 4; the two warps of a quarter take alternate 32-column chunks
     const int q = warp & 3, half = (warp - 2) >> 2;
     const bool ok = mbar_wait(&accum_bar, 0, &abort_flag, P.status, 3, P.wait_cycles);
     tc_fence_after();
@@ -276,18 +355,32 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const float alpha = P.alpha;
       constexpr int mode = MODE;
       const uint32_t tmem_row = tmem_base + ((uint32_t)(q * 32) << 16);
-      if (EPI == TC_EPI_PIXEL) {
+      float* const out_base = P.out + (long long)(blockIdx.z / P.cluster_z) * P.split_stride;   // a cluster of splits writes its own slab of partial results
+      if (P.cluster_z > 1) {
+        // Split-K inside a cluster: the accumulator goes to this CTA's shared memory (the pipeline stages are idle by now);
+        // the cluster then adds the tiles up (below, after the block has met).  The tile is laid out so that the reads of
+        // that sum run along contiguous addresses (reads from another SM's shared memory are slow when scattered):
+        // part[column][row] for the pixel-major epilogue, part[row][column] for the row-major one, odd pitches.
+        float* part = reinterpret_cast<float*>(stage_base);
+        const int row = q * 32 + lane, rp = P.bn + 1;
+        for (int c0 = half * 32; c0 < P.bn; c0 += 64) {
+          uint32_t r[32];
+          tc_ld32(tmem_row + (uint32_t)c0, r);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) part[EPI == TC_EPI_PIXEL ? (c0 + j) * kPartPitch + row : row * rp + c0 + j] = __uint_as_float(r[j]);
+        }
+      } else if (EPI == TC_EPI_PIXEL) {
         // lane = pixel, register j = channel: for a fixed j a warp covers 32 consecutive pixels (128 contiguous bytes)
         const long long m = (long long)m_tile * 128 + q * 32 + lane;
         const long long cs = P.chan_stride;
-        float* dst = m < P.M ? P.out + (m / P.pix_per_img) * P.img_stride + (m % P.pix_per_img) : nullptr;
+        float* dst = m < P.M ? out_base + (m / P.pix_per_img) * P.img_stride + (m % P.pix_per_img) : nullptr;
         for (int c0 = half * 32; c0 < P.bn; c0 += 64) {
           if (n0 + c0 >= P.N) break;                         // uniform across the warp
           uint32_t r[32];
           tc_ld32(tmem_row + (uint32_t)c0, r);
           if (dst) {
             const int lim = P.N - n0 - c0;
-            const float* bias = (P.bias && blockIdx.z == 0) ? P.bias + n0 + c0 : nullptr;
+            const float* bias = (P.bias && (!P.atomic || blockIdx.z == 0)) ? P.bias + n0 + c0 : nullptr;
             if (lim >= 32) store_columns<true>(dst + (long long)(n0 + c0) * cs, cs, r, alpha, bias, 32, mode);
             else store_columns<false>(dst + (long long)(n0 + c0) * cs, cs, r, alpha, bias, lim, mode);
           }
@@ -315,7 +408,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             for (int rr = 0; rr < 32; ++rr) t[rr] = __float_as_uint(tile[rr][lane]);
             // after the transpose the "columns" of store_columns are the 32 rows of this block, `ld` apart
             const float* bias = nullptr;
-            float* p = P.out + m0 * ld + col;
+            float* p = out_base + m0 * ld + col;
             if (P.bias && mode == 0) {
               const float bv = P.bias[n];
 #pragma unroll
@@ -328,8 +421,85 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       }
     }
   }
+  if (P.cluster_z > 1 && n_iter <= 0 && warp >= 2) {
+    // a split without k-iterations (the split count was rounded up to the cluster size) contributes zeros
+    float* part = reinterpret_cast<float*>(stage_base);
+    const int part_floats = EPI == TC_EPI_PIXEL ? P.bn * kPartPitch : 128 * (P.bn + 1);
+    for (int i = threadIdx.x - 64; i < part_floats; i += kTcThreads - 64) part[i] = 0.0f;
+  }
   tc_fence_before();
   __syncthreads();
+  if (P.cluster_z > 1) {
+    // ---- the cluster sums its partial tiles in a fixed order.  The hardware cluster barrier is safe to wait at: the CTAs
+    // of a cluster are scheduled together.  CTA number zr of the cluster owns a slice of the tile -- columns for the
+    // pixel-major epilogue, rows for the row-major one, so that its global stores coalesce -- reads that slice from the
+    // shared memory of every CTA of the cluster, rank 0 first, and writes the result the way the epilogue would.
+    cg::cluster_group cluster = cg::this_cluster();
+    cluster.sync();
+    if (warp >= 2 && !abort_flag) {
+      const int cz = P.cluster_z, zr = (int)cluster.block_rank();
+      float* part = reinterpret_cast<float*>(stage_base);
+      const float* remote[8];
+#pragma unroll
+      for (int z = 0; z < 8; ++z) remote[z] = z < cz ? cluster.map_shared_rank(part, z) : part;
+      const int t = threadIdx.x - 64;                                  // 0 .. 255
+      const int n0 = n_tile * P.bn;
+      float* const out_base = P.out + (long long)(blockIdx.z / cz) * P.split_stride;
+      const float alpha = P.alpha;
+      // Eight outputs at a time per thread: their partial tiles are read and, when the destination is accumulated into, its
+      // old values loaded, all before the first store (a load-add-store chain per element would pay the memory latency
+      // once per element).
+      const bool acc = MODE == 1;
+      if (EPI == TC_EPI_PIXEL) {
+        const int cpc = (P.bn + cz - 1) / cz, c_lo = zr * cpc + (t >> 7), c_hi = min(min(P.bn, zr * cpc + cpc), P.N - n0);
+        const int row = t & 127;
+        const long long m = (long long)m_tile * 128 + row;
+        if (m < P.M) {
+          float* dst = out_base + (m / P.pix_per_img) * P.img_stride + (m % P.pix_per_img) + (long long)n0 * P.chan_stride;
+          for (int cb = c_lo; cb < c_hi; cb += 16) {                   // this thread's columns cb, cb + 2, ..., cb + 14
+            float v[8], old[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+              const int c = cb + 2 * u; v[u] = 0.0f; old[u] = 0.0f;
+              if (c < c_hi) {
+#pragma unroll
+                for (int z = 0; z < 8; ++z) if (z < cz) v[u] += remote[z][c * kPartPitch + row];
+                if (acc) old[u] = dst[(long long)c * P.chan_stride];
+              }
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+              const int c = cb + 2 * u;
+              if (c < c_hi) dst[(long long)c * P.chan_stride] = old[u] + alpha * v[u] + (P.bias ? P.bias[n0 + c] : 0.0f);
+            }
+          }
+        }
+      } else {
+        // rows of the slice go round the eight warps, a lane takes every 32nd column: a warp's stores cover 128 contiguous bytes
+        const int rpc = (128 + cz - 1) / cz, r_lo = zr * rpc, r_hi = min(min(128, r_lo + rpc), (int)min(128ll, (long long)P.M - (long long)m_tile * 128));
+        const int w = t >> 5, cchunks = P.bn >> 5, cshift = cchunks == 4 ? 2 : cchunks == 2 ? 1 : 0;
+        const int n_rows = r_hi - r_lo - w > 0 ? (r_hi - r_lo - w + 7) / 8 : 0, items = n_rows << cshift;
+        for (int ib = 0; ib < items; ib += 8) {
+          float v[8], old[8]; float* o[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const int i = ib + u; v[u] = 0.0f; old[u] = 0.0f; o[u] = nullptr;
+            const int row = r_lo + w + 8 * (i >> cshift), c = ((i & (cchunks - 1)) << 5) + lane, n = n0 + c;
+            if (i < items && n < P.N) {
+#pragma unroll
+              for (int z = 0; z < 8; ++z) if (z < cz) v[u] += remote[z][row * (P.bn + 1) + c];
+              const long long col = P.col_mul ? (long long)(n % P.col_mod) * P.col_mul + n / P.col_mod : n;
+              o[u] = out_base + ((long long)m_tile * 128 + row) * P.ld + col;
+              if (acc) old[u] = *o[u];
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < 8; ++u) if (o[u]) *o[u] = old[u] + alpha * v[u];
+        }
+      }
+    }
+    cluster.sync();                // no CTA leaves while its shared memory may still be read
+  }
   if (warp == 1) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)P.bn) : "memory");
@@ -423,6 +593,15 @@ __global__ void permute_taps_kernel(const float* __restrict__ w, float* __restri
     out[i] = w[((int64_t)k * C + c) * taps + t];
   }
 }
+// Both per-tap forms in one launch: fwd[tap][k][c] and dgrad[tap][c][k] (the filter cache refreshes a filter once per step).
+__global__ void filter_forms_kernel(const float* __restrict__ w, float* __restrict__ fwd, float* __restrict__ dgrad, int K, int C, int taps, int64_t total) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    { const int c = (int)(i % C); const int64_t t2 = i / C; const int k = (int)(t2 % K); const int t = (int)(t2 / K);
+      fwd[i] = w[((int64_t)k * C + c) * taps + t]; }
+    { const int k = (int)(i % K); const int64_t t2 = i / K; const int c = (int)(t2 % C); const int t = (int)(t2 / C);
+      dgrad[i] = w[((int64_t)k * C + c) * taps + t]; }
+  }
+}
 // Filter matrix w[rows][cols] copied with its rows padded by zeros to ld floats (the engine's tensor maps want a row length
 // of 4 floats for K-major and 32 floats for N-major operands; 3x3 filters over 3 or 16 channels have 27 or 144).
 __global__ void pad_rows_kernel(const float* __restrict__ w, float* __restrict__ out, int cols, int ld, int64_t total) {
@@ -470,6 +649,41 @@ __global__ void fold_acc_kernel(const float* __restrict__ col, float* dx, ConvDi
   }
 }
 
+// ---- split-K beyond one cluster: the slabs of partial results are summed in a fixed order -----------------------------------
+// out[i] (+)= alpha * sum over the slabs of ws[slab][i] (+ bias of i's channel).  A CTA owns 128 consecutive outputs (32
+// float4 per warp row); its eight warps each add every eighth slab, in order, and warp 0 adds the eight partial sums, in
+// order: the association is fixed, so the result has the same bits on every run (sums combined by atomics do not).  The
+// slabs have the layout of the output itself.  chan_div / chan_mod locate the bias entry: channel = (i / chan_div) % chan_mod.
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ ws, int slabs, long long slab, float* out, long long n, float alpha, int accumulate,
+                                                            const float* __restrict__ bias, long long chan_div, int chan_mod, int vec) {
+  __shared__ float4 partial[8][32];
+  const int lane = threadIdx.x & 31, zl = threadIdx.x >> 5;
+  const long long base = ((long long)blockIdx.x * 32 + lane) * 4;                  // this lane's four outputs
+  float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (base < n) {
+    for (int z = zl; z < slabs; z += 8) {
+      const float* p = ws + (long long)z * slab + base;
+      float4 b;
+      if (vec) b = *reinterpret_cast<const float4*>(p);
+      else { b.x = p[0]; b.y = base + 1 < n ? p[1] : 0.f; b.z = base + 2 < n ? p[2] : 0.f; b.w = base + 3 < n ? p[3] : 0.f; }
+      a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+    }
+  }
+  partial[zl][lane] = a;
+  __syncthreads();
+  if (zl != 0 || base >= n) return;
+#pragma unroll
+  for (int z = 1; z < 8; ++z) { const float4 b = partial[z][lane]; a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w; }
+  const float v[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const long long i = base + e;
+    if (i >= n) break;
+    const float bv = bias ? bias[(i / chan_div) % chan_mod] : 0.0f;
+    out[i] = (accumulate ? out[i] : 0.0f) + alpha * v[e] + bv;
+  }
+}
+
 // ---- host side ----------------------------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -509,6 +723,9 @@ static bool to_dev(const TcOperand& o, TcOperandDev& v) {
   return true;
 }
 
+static void temp_free(float* p, size_t floats);
+static float* temp_alloc(size_t floats);
+
 static int launch_plan(const TcPlan& p, const char* label) {
   CUtensorMap ma, mb;
   int rc = encode_map(p.a.map, &ma); if (rc) return rc;
@@ -516,44 +733,77 @@ static int launch_plan(const TcPlan& p, const char* label) {
   TcParams P;
   if (!to_dev(p.a, P.a) || !to_dev(p.b, P.b)) return fail(LTB_E_STATE, "tensor-core plan whose k-iteration order has no incremental walk");
   P.M = p.M; P.N = p.N; P.bn = p.bn; P.k_iters = p.k_iters;
-  P.k_per_split = (int)ceil_div(p.k_iters, p.splits);
-  const int splits = (int)ceil_div(p.k_iters, P.k_per_split);                     // every split has at least one iteration
-  P.epilogue = p.epilogue; P.accumulate = p.accumulate; P.atomic = splits > 1 ? 1 : 0;
+  // Split-K: up to eight splits of a tile form a thread-block cluster and add their partial tiles up inside the kernel
+  // (through distributed shared memory, in a fixed order).  More than eight splits: every cluster of eight writes a slab of
+  // partial results (a staging block with the layout of the output) and one more launch adds the slabs up, again in a fixed
+  // order, and applies alpha, bias and accumulation.  No atomics, no zero fill, the same bits on every run.
+  // That is the deterministic mode (ltb_set_deterministic): measured, it costs the contraction kernels about a third more
+  // time (cluster barriers, partial tiles through shared memory).  By default the splits add their tiles into the output
+  // atomically, as cuDNN's default algorithms do: faster, and the last bits of a sum depend on the order of arrival.
+  int splits = p.splits < 1 ? 1 : p.splits, cz = 1, nslabs = 1;
+  const bool atomic = splits > 1 && !g.deterministic;
+  if (splits > 1 && !atomic) {
+    cz = splits <= 2 ? 2 : splits <= 4 ? 4 : 8;
+    nslabs = (int)ceil_div(splits, cz);
+  }
+  const size_t out_floats = p.epilogue == TC_EPI_PIXEL ? (size_t)ceil_div(p.M, p.pix_per_img ? p.pix_per_img : 1) * (size_t)p.img_stride : (size_t)p.M * (size_t)p.ld;
+  float* ws = nullptr;
+  if (nslabs > 1) {
+    ws = temp_alloc((size_t)nslabs * out_floats);
+    if (!ws) nslabs = 1;                                                           // no room for the slabs: one cluster per tile
+  }
+  if (!atomic) splits = nslabs * cz;
+  P.k_per_split = (int)ceil_div(p.k_iters, splits);                                // a split may end up without iterations: it contributes zeros
+  if (atomic) splits = (int)ceil_div(p.k_iters, P.k_per_split);                    // atomic mode: only splits that have work
+  P.cluster_z = cz;
+  P.epilogue = p.epilogue; P.accumulate = ws ? 0 : p.accumulate; P.atomic = atomic ? 1 : 0;
+  if (atomic && !p.accumulate) LTB_CUDA(cudaMemsetAsync(p.out, 0, out_floats * 4, g.stream));     // overwrite semantics: start from zero, then add
   // tf32 x tf32 -> f32: D format 1 at [4,6), A/B format 2 at [7,10)/[10,13), major bits 15/16, N>>3 at [17,23), M>>4 at [24,29)
   P.idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)p.a.mn_major << 15) | ((uint32_t)p.b.mn_major << 16) | ((uint32_t)(p.bn >> 3) << 17) | ((128u >> 4) << 24);
-  P.out = p.out; P.bias = p.bias; P.alpha = p.alpha;
+  P.out = ws ? ws : p.out; P.bias = ws ? nullptr : p.bias; P.alpha = ws ? 1.0f : p.alpha; P.split_stride = ws ? (long long)out_floats : 0;
   P.pix_per_img = p.pix_per_img ? p.pix_per_img : 1; P.img_stride = p.img_stride; P.chan_stride = p.chan_stride; P.ld = p.ld; P.col_mod = p.col_mod ? p.col_mod : 1; P.col_mul = p.col_mul;
+  P.gather_src = p.gather_src; P.g_pix = p.g_pix; P.g_chan = p.g_chan; P.g_imgs = p.g_imgs;
   P.status = g.dev_status; P.wait_cycles = g.wait_limit_cycles;
   // 4 stages, except 3 for 128-wide tiles so that two CTAs (2 x 97 KB) share an SM and one's epilogue overlaps the other's main loop
   P.stages = p.bn == 128 ? 3 : kMaxStages;
   const size_t smem = (size_t)P.stages * (p.a.stage_bytes + p.b.stage_bytes) + 1024;
+  if (cz > 1 && (size_t)128 * (p.bn + 1) * 4 > smem - 1024) return fail(LTB_E_STATE, "tensor-core plan whose partial tile does not fit the pipeline stages");
   if (!smem_opted_in) {
     const int max_smem = kMaxStages * (16384 + 32768) + 1024;
     LTB_CUDA(cudaFuncSetAttribute(tc_gemm_kernel<0, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
     LTB_CUDA(cudaFuncSetAttribute(tc_gemm_kernel<0, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
-    LTB_CUDA(cudaFuncSetAttribute(tc_gemm_kernel<0, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
     LTB_CUDA(cudaFuncSetAttribute(tc_gemm_kernel<1, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
     LTB_CUDA(cudaFuncSetAttribute(tc_gemm_kernel<1, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
+    LTB_CUDA(cudaFuncSetAttribute(tc_gemm_kernel<0, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
     LTB_CUDA(cudaFuncSetAttribute(tc_gemm_kernel<1, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
     smem_opted_in = true;
   }
-  if (splits > 1 && !p.accumulate) {            // overwrite semantics under split-K: start from zero, then accumulate atomically
-    const size_t out_floats = p.epilogue == TC_EPI_PIXEL ? (size_t)ceil_div(p.M, p.pix_per_img ? p.pix_per_img : 1) * (size_t)p.img_stride : (size_t)p.M * (size_t)p.ld;
-    LTB_CUDA(cudaMemsetAsync(p.out, 0, out_floats * 4, g.stream));
+  const int mode = atomic ? 2 : (P.accumulate ? 1 : 0);
+  void (*kernel)(const CUtensorMap, const CUtensorMap, const TcParams) =
+      p.epilogue == TC_EPI_PIXEL ? (mode == 2 ? tc_gemm_kernel<TC_EPI_PIXEL, 2> : mode == 1 ? tc_gemm_kernel<TC_EPI_PIXEL, 1> : tc_gemm_kernel<TC_EPI_PIXEL, 0>)
+                                 : (mode == 2 ? tc_gemm_kernel<TC_EPI_ROWMAJOR, 2> : mode == 1 ? tc_gemm_kernel<TC_EPI_ROWMAJOR, 1> : tc_gemm_kernel<TC_EPI_ROWMAJOR, 0>);
+  {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(p.m_tiles, p.n_tiles, splits); cfg.blockDim = dim3(kTcThreads); cfg.dynamicSmemBytes = smem; cfg.stream = g.stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = (unsigned)cz;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    if (g.profiling) profile_before(label);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, ma, mb, P);
+    if (g.profiling) profile_after();
+    ++g.launches;
+    if (e != cudaSuccess) return fail(LTB_E_CUDA, "launch of the tensor-core engine failed: %s (grid %d x %d x %d, cluster %d)", cudaGetErrorString(e), p.m_tiles, p.n_tiles, splits, cz);
   }
-  const char* saved = g.label; g.label = label;
-  dim3 grid(p.m_tiles, p.n_tiles, splits);
-  const int mode = P.atomic ? 2 : (P.accumulate ? 1 : 0);
-  if (p.epilogue == TC_EPI_PIXEL) {
-    if (mode == 0) LTB_LAUNCH((tc_gemm_kernel<TC_EPI_PIXEL, 0>), grid, kTcThreads, smem, ma, mb, P);
-    else if (mode == 1) LTB_LAUNCH((tc_gemm_kernel<TC_EPI_PIXEL, 1>), grid, kTcThreads, smem, ma, mb, P);
-    else LTB_LAUNCH((tc_gemm_kernel<TC_EPI_PIXEL, 2>), grid, kTcThreads, smem, ma, mb, P);
-  } else {
-    if (mode == 0) LTB_LAUNCH((tc_gemm_kernel<TC_EPI_ROWMAJOR, 0>), grid, kTcThreads, smem, ma, mb, P);
-    else if (mode == 1) LTB_LAUNCH((tc_gemm_kernel<TC_EPI_ROWMAJOR, 1>), grid, kTcThreads, smem, ma, mb, P);
-    else LTB_LAUNCH((tc_gemm_kernel<TC_EPI_ROWMAJOR, 2>), grid, kTcThreads, smem, ma, mb, P);
+  if (ws) {
+    const bool pixel = p.epilogue == TC_EPI_PIXEL;
+    const long long chan_div = pixel ? (long long)(p.pix_per_img ? p.pix_per_img : 1) : 1;
+    const int chan_mod = pixel ? p.N : (int)(p.ld > 0 ? p.ld : 1);
+    const int vec = aligned16(ws) && out_floats % 4 == 0 ? 1 : 0;
+    const unsigned grid_r = (unsigned)ceil_div((int64_t)out_floats, 128);
+    LTB_LAUNCH(splitk_reduce_kernel, grid_r, 256, 0, (const float*)ws, nslabs, (long long)out_floats, p.out, (long long)out_floats, p.alpha, p.accumulate, p.bias, chan_div, chan_mod, vec);
+    temp_free(ws, (size_t)nslabs * out_floats);
   }
-  g.label = saved;
   return LTB_OK;
 }
 
@@ -629,7 +879,7 @@ static bool is_pointwise(const ConvDims& d) { return d.R == 1 && d.S == 1 && d.s
 static void temp_free(float* p, size_t floats) { if (!g.hold_workspace && !g.branch_marked) ltb_free(p, floats * 4); }
 static float* temp_alloc(size_t floats) {
   size_t bytes = (floats * 4 + kGranule - 1) / kGranule * kGranule;
-  if (g.used + bytes > g.heap_bytes) return nullptr;          // no room for the staging buffer: let the FP32 path run
+  if (g.used + bytes + g.top_used > g.heap_bytes) return nullptr;   // no room for the staging buffer: let the FP32 path run
   return (float*)ltb_malloc_uninit(floats * 4);
 }
 // Stages the activation operand of forward / data-grad for the engine.  `src` is [N][chan][pix] when no unfolding is needed
@@ -662,21 +912,104 @@ static bool taps_geometry(const ConvDims& d, TcConvGeom& gm) {
   gm.n_img = d.N; gm.C = d.C; gm.H = d.H; gm.W = d.W; gm.K = d.K; gm.R = d.R; gm.S = d.S; gm.ph = d.ph; gm.pw = d.pw; gm.oH = d.oH; gm.oW = d.oW;
   return true;
 }
-// Channels-last copy [N][pix][chan] of a tensor [N][chan][pix] in a staging block (null when the arena has no room).
-static int channels_last(const float* src, int n_img, int chan, int pix, float** out, size_t* floats) {
+// ---- channels-last copies of activations ---------------------------------------------------------------------------------------
+// The tap-loop convolutions read act[n][h][w][c].  Without the operand cache (ltb_set_filter_cache) every call makes its own
+// copy in a staging block and gives it back.  With it, a copy made by a forward convolution, or of dy at the start of a
+// convolution's backward call, is kept in a block taken from the far end of the arena (those blocks live until ltb_reset)
+// and found again by address and shape: the weight-gradient of that convolution reads the forward copy of x, and data-grad
+// and weight-grad share one copy of dy.  A copy is dropped when one of the entry points that report their writes
+// (filter_cache_note_write) touches its source, when ltb_free releases the source, and at ltb_reset.
+struct ClCopy { const float* src; int n_img, chan, pix; float* cl; };
+static std::vector<ClCopy> cl_cache;
+void cl_cache_clear() { cl_cache.clear(); }
+void cl_cache_drop_from(const void* p) {                   // ltb_free: everything at or above p is gone
+  for (size_t i = 0; i < cl_cache.size();) { if ((const void*)cl_cache[i].src >= p) { cl_cache[i] = cl_cache.back(); cl_cache.pop_back(); } else ++i; }
+}
+static float* cl_lookup(const float* src, int n_img, int chan, int pix) {
+  for (auto& e : cl_cache) if (e.src == src && e.n_img == n_img && e.chan == chan && e.pix == pix) return e.cl;
+  return nullptr;
+}
+static int channels_last_into(const float* src, int n_img, int chan, int pix, float* out) {
   const size_t n = (size_t)n_img * chan * pix;
-  *out = temp_alloc(n); *floats = n;
-  if (!*out) return LTB_OK;
   const int pt = pix < 32 ? pix : 32;
   if (chan % 32 == 0 && pix % pt == 0 && n_img <= 65535)
-    { if (pt == 32) LTB_LAUNCH(to_rows_tiled_kernel<32>, dim3(pix / 32, chan / 32, n_img), 256, 0, src, *out, chan, pix, 32);
-      else LTB_LAUNCH(to_rows_tiled_kernel<0>, dim3(pix / pt, chan / 32, n_img), 32 * pt < 256 ? 128 : 256, 0, src, *out, chan, pix, pt); }
+    { if (pt == 32) LTB_LAUNCH(to_rows_tiled_kernel<32>, dim3(pix / 32, chan / 32, n_img), 256, 0, src, out, chan, pix, 32);
+      else LTB_LAUNCH(to_rows_tiled_kernel<0>, dim3(pix / pt, chan / 32, n_img), 32 * pt < 256 ? 128 : 256, 0, src, out, chan, pix, pt); }
   else
-    LTB_LAUNCH(to_rows_kernel, grid_for((int64_t)n, 256), 256, 0, src, *out, chan, pix, (int64_t)n);
+    LTB_LAUNCH(to_rows_kernel, grid_for((int64_t)n, 256), 256, 0, src, out, chan, pix, (int64_t)n);
   return LTB_OK;
 }
+// Channels-last copy [N][pix][chan] of a tensor [N][chan][pix].  keep: put it where it outlives the call and remember it (when
+// the cache is on and the arena has room); otherwise a staging block of *floats floats to give back (*floats == 0: kept).
+// *out stays null when there is no room at all.
+static int channels_last(const float* src, int n_img, int chan, int pix, float** out, size_t* floats, bool keep = false) {
+  const size_t n = (size_t)n_img * chan * pix;
+  *floats = 0; *out = nullptr;
+  if (keep && g.filter_cache) {
+    if (float* kept = (float*)step_alloc(n * 4)) {
+      int rc = channels_last_into(src, n_img, chan, pix, kept); if (rc) return rc;
+      for (size_t i = 0; i < cl_cache.size(); ++i) if (cl_cache[i].src == src) { cl_cache[i] = cl_cache.back(); cl_cache.pop_back(); break; }
+      cl_cache.push_back(ClCopy{src, n_img, chan, pix, kept});
+      *out = kept;
+      return LTB_OK;
+    }
+  }
+  *out = temp_alloc(n); *floats = n;
+  if (!*out) return LTB_OK;
+  return channels_last_into(src, n_img, chan, pix, *out);
+}
+// ---- filter cache (ltb_set_filter_cache) ------------------------------------------------------------------------------------
+// The per-tap forms of a filter are needed twice per step (forward and data-grad) and change once per step (the optimizer).
+// With the cache on they live in private device memory, keyed by the filter's address and shape, and are refreshed by ONE
+// launch at the first use after a write that overlaps the filter (filter_cache_note_write, called by the optimizer, transfer,
+// fill and in-place entry points with their destination; a replayed step and ltb_params_changed mark every filter).  A filter first seen while a step is being recorded takes
+// the uncached path (no allocation inside a capture).
+struct FilterForms { const float* w; int K, C, taps; float *fwd, *dgrad; bool stale; };
+static std::vector<FilterForms> filter_cache;
+static size_t filter_cache_bytes = 0;
+void filter_cache_clear() {
+  for (auto& e : filter_cache) { cudaFree(e.fwd); cudaFree(e.dgrad); }
+  filter_cache.clear(); filter_cache_bytes = 0;
+}
+void filter_cache_note_write(const void* p, size_t bytes) {
+  for (size_t i = 0; i < cl_cache.size();) {
+    const char* sl = (const char*)cl_cache[i].src; const char* sh = sl + (size_t)cl_cache[i].n_img * cl_cache[i].chan * cl_cache[i].pix * 4;
+    if (!p || ((const char*)p < sh && sl < (const char*)p + bytes)) { cl_cache[i] = cl_cache.back(); cl_cache.pop_back(); } else ++i;
+  }
+  if (filter_cache.empty()) return;
+  const char* lo = (const char*)p; const char* hi = lo + bytes;
+  for (auto& e : filter_cache) {
+    const char* wl = (const char*)e.w; const char* wh = wl + (size_t)e.K * e.C * e.taps * 4;
+    if (!p || (lo < wh && wl < hi)) e.stale = true;
+  }
+}
+static FilterForms* filter_cache_entry(const float* w, const ConvDims& d) {
+  const int taps = d.R * d.S;
+  for (auto& e : filter_cache) if (e.w == w && e.K == d.K && e.C == d.C && e.taps == taps) return &e;
+  if (g.capturing) return nullptr;
+  const size_t bytes = (size_t)d.K * d.C * taps * 4;
+  if (filter_cache_bytes + 2 * bytes > ((size_t)2 << 30)) { cudaStreamSynchronize(g.stream); cudaStreamSynchronize(g.side); cudaStreamSynchronize(g.branch); filter_cache_clear(); }
+  FilterForms e{w, d.K, d.C, taps, nullptr, nullptr, true};
+  if (cudaMalloc((void**)&e.fwd, bytes) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+  if (cudaMalloc((void**)&e.dgrad, bytes) != cudaSuccess) { cudaGetLastError(); cudaFree(e.fwd); return nullptr; }
+  filter_cache_bytes += 2 * bytes;
+  filter_cache.push_back(e);
+  return &filter_cache.back();
+}
+// The per-tap matrices of w: out[tap][k][c] (by_c == 0, forward) or out[tap][c][k] (data-grad).  *floats is the size of the
+// staging block to give back afterwards, 0 when the matrices live in the cache.
 static int tap_matrices(const float* w, const ConvDims& d, int by_c, float** out, size_t* floats) {
   const size_t n = (size_t)d.K * d.C * d.R * d.S;
+  if (g.filter_cache) {
+    if (FilterForms* e = filter_cache_entry(w, d)) {
+      if (e->stale) {
+        LTB_LAUNCH(filter_forms_kernel, grid_for((int64_t)n, 256), 256, 0, w, e->fwd, e->dgrad, d.K, d.C, d.R * d.S, (int64_t)n);
+        e->stale = false;
+      }
+      *out = by_c ? e->dgrad : e->fwd; *floats = 0;
+      return LTB_OK;
+    }
+  }
   *out = temp_alloc(n); *floats = n;
   if (!*out) return LTB_OK;
   LTB_LAUNCH(permute_taps_kernel, grid_for((int64_t)n, 256), 256, 0, w, *out, d.K, d.C, d.R * d.S, by_c, (int64_t)n);
@@ -700,26 +1033,26 @@ static int conv_fwd_taps(const float* x, const float* w, const float* bias, floa
   TcConvGeom gm; TcPlan p;
   if (!taps_geometry(d, gm) || !tc_plan_conv_taps_fwd(p, y, y, bias, y, gm, g.sm_count)) return 0;     // eligibility with any aligned pointers
   float *xr = nullptr, *wt = nullptr; size_t nx = 0, nw = 0;
-  int rc = channels_last(x, d.N, d.C, d.H * d.W, &xr, &nx); if (rc) return rc;
+  int rc = channels_last(x, d.N, d.C, d.H * d.W, &xr, &nx, /*keep=*/true); if (rc) return rc;     // the weight-gradient of this convolution reads it again
   if (!xr) return 0;
   rc = tap_matrices(w, d, 0, &wt, &nw);
   bool ok = !rc && wt && tc_plan_conv_taps_fwd(p, xr, wt, bias, y, gm, g.sm_count);
   if (ok) rc = launch_plan(p, "tc_gemm_kernel[conv_fwd taps]");
-  if (wt) temp_free(wt, nw);
-  temp_free(xr, nx);
+  if (wt && nw) temp_free(wt, nw);
+  if (nx) temp_free(xr, nx);
   return rc ? rc : (ok ? 1 : 0);
 }
 static int conv_dgrad_taps(const float* dy, const float* w, float* dx, const ConvDims& d) {
   TcConvGeom gm; TcPlan p;
   if (!taps_geometry(d, gm) || !tc_plan_conv_taps_dgrad(p, dx, dx, dx, gm, true, g.sm_count)) return 0;
-  float *dyr = nullptr, *wd = nullptr; size_t ny = 0, nw = 0;
-  int rc = channels_last(dy, d.N, d.K, d.oH * d.oW, &dyr, &ny); if (rc) return rc;
+  float *dyr = cl_lookup(dy, d.N, d.K, d.oH * d.oW), *wd = nullptr; size_t ny = 0, nw = 0;
+  int rc = dyr ? LTB_OK : channels_last(dy, d.N, d.K, d.oH * d.oW, &dyr, &ny); if (rc) return rc;
   if (!dyr) return 0;
   rc = tap_matrices(w, d, 1, &wd, &nw);
   bool ok = !rc && wd && tc_plan_conv_taps_dgrad(p, dyr, wd, dx, gm, true, g.sm_count);
   if (ok) rc = launch_plan(p, "tc_gemm_kernel[conv_dgrad taps]");
-  if (wd) temp_free(wd, nw);
-  temp_free(dyr, ny);
+  if (wd && nw) temp_free(wd, nw);
+  if (ny) temp_free(dyr, ny);
   return rc ? rc : (ok ? 1 : 0);
 }
 // Stride 2 (both directions): dx is the stride-1 data-gradient of dy with zeros inserted (to_rows_up2_kernel).
@@ -738,25 +1071,36 @@ static int conv_dgrad_taps_up2(const float* dy, const float* w, float* dx, const
   int rc = tap_matrices(w, d, 1, &wd, &nw);
   bool ok = !rc && wd && tc_plan_conv_taps_dgrad(p, up, wd, dx, gm, true, g.sm_count);
   if (ok) rc = launch_plan(p, "tc_gemm_kernel[conv_dgrad taps up2]");
-  if (wd) temp_free(wd, nw);
+  if (wd && nw) temp_free(wd, nw);
   temp_free(up, nu);
   return rc ? rc : (ok ? 1 : 0);
 }
 static int conv_wgrad_taps(const float* x, const float* dy, float* dw, const ConvDims& d) {
   TcConvGeom gm; TcPlan p;
-  // The tap-loop weight-grad stores its columns (tap, c) into OIHW with a stride of R*S floats, so its split-K atomics do not
-  // coalesce; measured, it only beats unfolding once the unfolded matrix is large (64 MB and up: the 9x traffic then dominates).
-  if ((size_t)d.N * d.C * d.R * d.S * d.oH * d.oW * 4 < ((size_t)64 << 20)) return 0;
   if (!taps_geometry(d, gm) || !tc_plan_conv_taps_wgrad(p, dw, dw, dw, gm, g.sm_count)) return 0;
-  float *dyr = nullptr, *xr = nullptr; size_t ny = 0, nx = 0;
-  int rc = channels_last(dy, d.N, d.K, d.oH * d.oW, &dyr, &ny); if (rc) return rc;
+  float *dyr = cl_lookup(dy, d.N, d.K, d.oH * d.oW), *xr = cl_lookup(x, d.N, d.C, d.H * d.W); size_t ny = 0, nx = 0;
+  // Both operands are read channels-last.  With the copies already there (x from this convolution's forward call, dy shared
+  // with the data-grad) the tap loop reads each of them once; having to make both first only pays once the unfolded
+  // matrix, nine times the size of x, would be large.
+  if ((!dyr || !xr) && (size_t)d.N * d.C * d.R * d.S * d.oH * d.oW * 4 < ((size_t)64 << 20)) return 0;
+  int rc = dyr ? LTB_OK : channels_last(dy, d.N, d.K, d.oH * d.oW, &dyr, &ny); if (rc) return rc;
   if (!dyr) return 0;
-  rc = channels_last(x, d.N, d.C, d.H * d.W, &xr, &nx);
+  if (!xr) rc = channels_last(x, d.N, d.C, d.H * d.W, &xr, &nx);
   bool ok = !rc && xr && tc_plan_conv_taps_wgrad(p, dyr, xr, dw, gm, g.sm_count);
   if (ok) rc = launch_plan(p, "tc_gemm_kernel[conv_wgrad taps]");
-  if (xr) temp_free(xr, nx);
-  temp_free(dyr, ny);
+  if (xr && nx) temp_free(xr, nx);
+  if (ny) temp_free(dyr, ny);
   return rc ? rc : (ok ? 1 : 0);
+}
+// Start of a convolution's backward call, before its two halves part onto two streams: one channels-last copy of dy for both.
+int conv_bwd_prestage(const float* dy, const ConvDims& d, bool both_halves) {
+  TcConvGeom gm;
+  if (!g.filter_cache || !both_halves || !taps_geometry(d, gm) || d.C % 64 || d.K % 32) return LTB_OK;
+  if (cl_lookup(dy, d.N, d.K, d.oH * d.oW)) return LTB_OK;
+  float* dyr; size_t ny;
+  int rc = channels_last(dy, d.N, d.K, d.oH * d.oW, &dyr, &ny, /*keep=*/true);
+  if (!rc && dyr && ny) temp_free(dyr, ny);                 // no room to keep it: each half makes its own, as before
+  return rc;
 }
 
 int conv_fwd_tc(const float* x, const float* w, const float* bias, float* y, const ConvDims& d) {
@@ -766,13 +1110,16 @@ int conv_fwd_tc(const float* x, const float* w, const float* bias, float* y, con
   const int ldw = (ck + 3) / 4 * 4;                                        // K-major filter rows must be a multiple of 16 bytes
   if (!tc_plan_conv_fwd(p, y /* any aligned pointer: eligibility only */, rows, y, ldw, bias, y, d.N, ck, d.K, pix, g.sm_count)) return 0;
   { int t = conv_fwd_taps(x, w, bias, y, d); if (t != 0) return t; }      // the tap-loop form when the shape allows it
-  const float* op; bool r2; float* temp; size_t tn;
-  int rc = stage_activation(x, !is_pointwise(d), d, ck, pix, &op, &r2, &temp, &tn);
+  // Small images (4 or 16 pixels) of a 1x1 convolution: the kernel collects the activation itself (no row copy first).
+  const bool gathered = rows && is_pointwise(d) && pix > 1 && tc_gather_possible(x, ck, pix);
+  const float* op = x; bool r2; float* temp = nullptr; size_t tn = 0;
+  int rc = gathered ? LTB_OK : stage_activation(x, !is_pointwise(d), d, ck, pix, &op, &r2, &temp, &tn);
   if (rc) return rc < 0 ? rc : 0;
   float* wtemp; size_t wn; const float* wp;
   rc = padded_filter(w, d.K, ck, ldw, &wp, &wtemp, &wn);
   const bool ok = !rc && wp && tc_plan_conv_fwd(p, op, rows, wp, ldw, bias, y, d.N, ck, d.K, pix, g.sm_count);
-  if (ok) rc = launch_plan(p, "tc_gemm_kernel[conv_fwd]");
+  if (ok && gathered) tc_plan_gather(p, x, d.N, ck, pix);
+  if (ok) rc = launch_plan(p, gathered ? "tc_gemm_kernel[conv_fwd gather]" : "tc_gemm_kernel[conv_fwd]");
   if (wtemp) temp_free(wtemp, wn);
   if (temp) temp_free(temp, tn);
   return rc ? rc : (ok ? 1 : 0);
@@ -786,16 +1133,18 @@ int conv_dgrad_tc(const float* dy, const float* w, float* dx, const ConvDims& d)
   if (!tc_plan_conv_dgrad(p, dx, rows, dx, ldw, dx, d.N, ck, d.K, pix, direct, g.sm_count)) return 0;
   { int t = conv_dgrad_taps(dy, w, dx, d); if (t != 0) return t; }
   { int t = conv_dgrad_taps_up2(dy, w, dx, d); if (t != 0) return t; }
-  const float* op; bool r2; float* temp; size_t tn;
+  const bool gathered = rows && pix > 1 && tc_gather_possible(dy, d.K, pix);    // dy of a small map: collected by the kernel itself
+  const float* op = dy; bool r2; float* temp = nullptr; size_t tn = 0;
   ConvDims flat = d; flat.C = d.K;                               // dy is [N][K][pix]: staged like a pointwise activation with K channels
-  int rc = stage_activation(dy, false, flat, d.K, pix, &op, &r2, &temp, &tn);
+  int rc = gathered ? LTB_OK : stage_activation(dy, false, flat, d.K, pix, &op, &r2, &temp, &tn);
   if (rc) return rc < 0 ? rc : 0;
   float* col = nullptr; const size_t ncol = (size_t)d.N * ck * pix;
   if (!direct) { col = temp_alloc(ncol); if (!col) { if (temp) temp_free(temp, tn); return 0; } }
   float* wtemp; size_t wn; const float* wp;
   rc = padded_filter(w, d.K, ck, ldw, &wp, &wtemp, &wn);
   bool ok = !rc && wp && tc_plan_conv_dgrad(p, op, rows, wp, ldw, direct ? dx : col, d.N, ck, d.K, pix, direct, g.sm_count);
-  if (ok) rc = launch_plan(p, "tc_gemm_kernel[conv_dgrad]");
+  if (ok && gathered) tc_plan_gather(p, dy, d.N, d.K, pix);
+  if (ok) rc = launch_plan(p, gathered ? "tc_gemm_kernel[conv_dgrad gather]" : "tc_gemm_kernel[conv_dgrad]");
   if (ok && !rc && !direct) rc = launch_fold(col, dx, d);
   if (wtemp) temp_free(wtemp, wn);
   if (col) temp_free(col, ncol);

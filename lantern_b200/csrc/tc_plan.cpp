@@ -260,6 +260,9 @@ bool tc_walk_of(const TcOperand& o, TcWalk& w) {
 
 bool tc_conv_needs_rows(int pix) { return !(pix >= 32 && pix % 32 == 0 && (pix >= kTileM ? pix % kTileM == 0 : kTileM % pix == 0)); }
 
+bool tc_gather_possible(const float* src, int chan, int pix) { return aligned16(src) && (pix == 4 || pix == 16) && chan % 4 == 0 && chan >= 8; }
+void tc_plan_gather(TcPlan& p, const float* src, int n_img, int chan, int pix) { p.gather_src = src; p.g_pix = pix; p.g_chan = chan; p.g_imgs = n_img; }
+
 bool tc_plan_conv_fwd(TcPlan& p, const float* x, bool a_rows, const float* w, int ldw, const float* bias, float* y, int n_img, int ck, int co, int pix, int sm_count) {
   std::memset(&p, 0, sizeof p);
   if (co < 8 || ck < 8 || ldw < ck || (a_rows && ldw != ck) || (int64_t)n_img * pix > (1ll << 30)) return false;

@@ -68,6 +68,11 @@ struct TcPlan {
   int64_t pix_per_img, img_stride, chan_stride;   // TC_EPI_PIXEL
   int64_t ld;                                     // TC_EPI_ROWMAJOR
   int col_mod, col_mul;                           // TC_EPI_ROWMAJOR, when col_mul != 0: D column n is stored at column (n % col_mod) * col_mul + n / col_mod
+  // Gather mode (tc_plan_gather): operand a keeps its K-major row descriptors but is not loaded by TMA; the kernel's
+  // epilogue warps collect it from gather_src[img][chan][pix] (pix = 4 or 16), warp g filling rows 16 g .. 16 g + 15 of
+  // the tile, lane = channel within the 32-channel block, 128-byte swizzle.
+  const float* gather_src;
+  int g_pix, g_chan, g_imgs;
 };
 
 // "Flat" convolution view: activations X[n][k][p] with p contiguous (k = channels, or channels*kh*kw after unfolding),
@@ -80,6 +85,10 @@ struct TcPlan {
 // a_rows: the activation operand (x for forward, dy for dgrad) is given as a K-major row matrix [n_img*pix][channels]
 // instead of [n_img][channels][pix]; tc_conv_needs_rows says when that form is required.
 bool tc_conv_needs_rows(int pix);
+// Whether an activation [n_img][chan][pix] that needs the row form can be gathered by the kernel itself instead of being
+// copied into a row matrix first; tc_plan_gather switches a plan made with a_rows = true (x = src as base) to that mode.
+bool tc_gather_possible(const float* src, int chan, int pix);
+void tc_plan_gather(TcPlan& p, const float* src, int n_img, int chan, int pix);
 bool tc_plan_conv_fwd(TcPlan& p, const float* x, bool a_rows, const float* w, int ldw, const float* bias, float* y, int n_img, int ck, int co, int pix, int sm_count);
 bool tc_plan_conv_dgrad(TcPlan& p, const float* dy, bool a_rows, const float* w, int ldw, float* dx, int n_img, int ck, int co, int pix, bool accumulate, int sm_count);
 bool tc_plan_conv_wgrad(TcPlan& p, const float* x, const float* dy, float* dw, int n_img, int ck, int co, int pix, int sm_count);

@@ -549,6 +549,7 @@ extern "C" {
 void* HOST_FN(model_create)(const char* name, int batch, int seed) {
   std::string n(name);
   BK(set_fusion)(1);     // generated programs issue every device operation through the library: the one-call look-ahead is safe
+  BK(set_filter_cache)(1);   // and they write parameters only through the optimizer, transfer and fill entry points
   if (n == "mnist") return new Mnist(batch, seed);
   if (n == "resnet50") return new ResNet50(batch, seed);
   if (n == "resnet50_prefix") return new ResNet50(batch, seed, 1);        // stem + the first bottleneck block + classifier

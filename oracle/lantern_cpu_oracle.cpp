@@ -256,6 +256,9 @@ int ora_last_error(char* buf, int len) {
 int ora_set_stream(void*) { ProfScope prof_scope_("ora_set_stream"); return LTB_OK; }
 void* ora_get_stream(void) { return nullptr; }
 int ora_sync(void) { ProfScope prof_scope_("ora_sync"); return LTB_OK; }
+int ora_set_deterministic(int) { return LTB_OK; }   // the CPU build always sums in program order
+int ora_set_filter_cache(int) { return LTB_OK; }    // the CPU build reads OIHW filters as they are
+int ora_params_changed(void) { return LTB_OK; }
 int ora_set_fusion(int) { ProfScope prof_scope_("ora_set_fusion"); return LTB_OK; }   // the CPU build executes every call at once
 int ora_set_math(int mode) { ProfScope prof_scope_("ora_set_math"); g.math = mode; return LTB_OK; }
 int ora_device_status(void) { return LTB_OK; }

@@ -24,7 +24,7 @@ def oracle_lib():
     from lantern_b200._ffi import BoundLibrary
     _build_oracle()
     lib = BoundLibrary(ORACLE_SO, "ora_")
-    lib.init(0, 768 << 20)
+    lib.init(0, 10 << 30)            # untouched pages cost nothing; a ResNet-50 step at batch 128 needs about 4 GiB
     yield lib
     lib.shutdown()
 
@@ -43,7 +43,7 @@ def cuda_lib():
     """The CUDA product library on device 0; absent library or device is an error, never a skip."""
     import lantern_b200
     lib = lantern_b200.load()
-    lib.init(0, 6 << 30)
+    lib.init(0, 16 << 30)            # of the 180 GB: the batch-128 steps with their staging blocks need about 6 GiB
     yield lib
     lib.shutdown()
 

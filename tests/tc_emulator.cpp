@@ -6,6 +6,7 @@
 // (start offset, LBO, SBO, swizzle, major-ness), and (3) the epilogue's output indexing.  The result of the emulated
 // engine is compared with a direct evaluation of the convolution / GEMM.  This pins coordinates, strides, descriptors
 // and tile/split arithmetic without a GPU; it does not prove that the hardware follows the emulated conventions.
+#include <algorithm>
 #include <cmath>
 #include <cstdio>
 #include <cstdlib>
@@ -48,6 +49,26 @@ static bool tma_load(const TcOperand& o, int tile, int kiter, std::vector<float>
   }
   return true;
 }
+// What the kernel's gathering warps store for operand a of a plan in gather mode (gemm_tc.cu): warp g, lane l, run j, element
+// i write row 16 g + 4 j + i, channel l of the 32-channel block, at 16-byte chunk (l >> 2) ^ (row & 7) of the 128-byte row.
+static bool gather_load(const TcPlan& p, int tile, int kiter, std::vector<float>& smem) {
+  if (p.a.stage_bytes != 128 * 128 || p.a.mn_major || p.a.map.swizzle != TC_SW_128) { printf("gather mode needs a K-major 128-byte-swizzled operand\n"); return false; }
+  smem.assign(p.a.stage_bytes / 4, 0.0f);
+  const int pix = p.g_pix, chan = p.g_chan, runs = 16 / pix;
+  for (int gw = 0; gw < 8; ++gw) for (int lane = 0; lane < 32; ++lane) {
+    const int64_t row0 = (int64_t)tile * 128 + gw * 16, img0 = row0 / pix;
+    const int c = kiter * 32 + lane;
+    for (int j = 0; j < 4; ++j) for (int i = 0; i < 4; ++i) {
+      const int64_t img = runs == 1 ? img0 : img0 + j;
+      const int q = runs == 1 ? j * 4 + i : i;
+      const float v = (c < chan && img < p.g_imgs) ? p.gather_src[(img * chan + c) * pix + q] : 0.0f;
+      const uint32_t r = (uint32_t)(j * 4 + i);
+      const uint32_t off = (uint32_t)gw * 16 * 128 + r * 128 + (((((uint32_t)lane >> 2) ^ (r & 7u)) << 4) | (((uint32_t)lane & 3u) << 2));
+      smem[off / 4] = v;
+    }
+  }
+  return true;
+}
 // Element (r, kk) of MMA step `ks`: r = row (M or N index within the tile), kk in [0,8).
 static float umma_fetch(const TcOperand& o, const std::vector<float>& smem, int ks, int r, int kk) {
   const int X = span(o.map.swizzle); uint32_t off = o.kstep_off[ks];
@@ -85,7 +106,7 @@ static bool walk_matches(const TcOperand& o, int tile, int k_iters) {
 static bool run_plan(const TcPlan& p, size_t out_count) {
   if (p.a.nk != p.b.nk) { printf("nk mismatch\n"); return false; }
   if (!walk_matches(p.a, p.m_tiles - 1, p.k_iters) || !walk_matches(p.b, p.n_tiles - 1, p.k_iters)) return false;
-  // overwrite semantics under split-K: the launcher zeroes the output, then every split accumulates atomically
+  // overwrite semantics under split-K: the partial results of the splits are summed and then stored; emulated by zeroing first
   if (p.splits > 1 && !p.accumulate) for (size_t i = 0; i < out_count; ++i) p.out[i] = 0.0f;
   std::vector<float> sa, sb;
   for (int mt = 0; mt < p.m_tiles; ++mt) for (int nt = 0; nt < p.n_tiles; ++nt) for (int z = 0; z < p.splits; ++z) {
@@ -93,7 +114,7 @@ static bool run_plan(const TcPlan& p, size_t out_count) {
     if (k0 >= k1) continue;
     std::vector<double> D((size_t)128 * p.bn, 0.0);
     for (int it = k0; it < k1; ++it) {
-      if (!tma_load(p.a, mt, it, sa) || !tma_load(p.b, nt, it, sb)) return false;
+      if (!(p.gather_src ? gather_load(p, mt, it, sa) : tma_load(p.a, mt, it, sa)) || !tma_load(p.b, nt, it, sb)) return false;
       for (int ks = 0; ks < p.a.nk; ++ks) for (int r = 0; r < 128; ++r) for (int c = 0; c < p.bn; ++c) {
         double s = 0; for (int kk = 0; kk < 8; ++kk) s += (double)umma_fetch(p.a, sa, ks, r, kk) * umma_fetch(p.b, sb, ks, c, kk);
         D[(size_t)r * p.bn + c] += s;
@@ -151,6 +172,14 @@ static int conv_case(int n_img, int ck, int co, int pix) {
   const std::vector<float> w4 = padded(ld4), w32 = padded(ld32);
   if (tc_plan_conv_fwd(p, rows ? xt.data() : x.data(), rows, w4.data(), ld4, bias.data(), y.data(), n_img, ck, co, pix, 148)) { ++taken; if (!run_plan(p, y.size()) || !close(yr, y, "fwd")) return -1; }
   if (tc_plan_conv_dgrad(p, rows ? dyt.data() : dy.data(), rows, w32.data(), ld32, dx.data(), n_img, ck, co, pix, true, 148)) { ++taken; if (!run_plan(p, dx.size()) || !close(dxr, dx, "dgrad")) return -1; }
+  // the same two contractions with the kernel gathering the activation itself (small images: 4 or 16 pixels)
+  if (rows && tc_gather_possible(x.data(), ck, pix) && tc_gather_possible(dy.data(), co, pix)) {
+    std::fill(y.begin(), y.end(), 7.0f); std::fill(dx.begin(), dx.end(), 0.5f);
+    if (tc_plan_conv_fwd(p, x.data(), true, w4.data(), ld4, bias.data(), y.data(), n_img, ck, co, pix, 148)) {
+      tc_plan_gather(p, x.data(), n_img, ck, pix); ++taken; if (!run_plan(p, y.size()) || !close(yr, y, "fwd (gather)")) return -1; }
+    if (tc_plan_conv_dgrad(p, dy.data(), true, w32.data(), ld32, dx.data(), n_img, ck, co, pix, true, 148)) {
+      tc_plan_gather(p, dy.data(), n_img, co, pix); ++taken; if (!run_plan(p, dx.size()) || !close(dxr, dx, "dgrad (gather)")) return -1; }
+  }
   if (tc_plan_conv_wgrad(p, x.data(), dy.data(), dw.data(), n_img, ck, co, pix, 148)) { ++taken; if (!run_plan(p, dw.size()) || !close(dwr, dw, "wgrad")) return -1; }
   printf("conv n=%d ck=%d co=%d pix=%d: %d of 3 plans taken, all match\n", n_img, ck, co, pix, taken);
   return taken;

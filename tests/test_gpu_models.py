@@ -138,6 +138,34 @@ def test_training_trajectory_and_graph_replay(oracle_lib, cuda_lib):
     cuda_lib.reset(mg_mark)
 
 
+def test_deterministic_mode_replays_bit_for_bit(cuda_lib):
+    """ltb_set_deterministic(1), tensor-core math: three ResNet-50 training steps issued call by call and the same three
+    replayed from a recorded step end in the same parameters and losses, bit for bit (split-K sums are combined in a fixed
+    order; streams, branch regions and the look-ahead fusion move launches, not bits)."""
+    from lantern_b200.hosts import HostPrograms
+    lib = cuda_lib
+    mark = lib.mark()
+    lib.set_math(1); lib.set_deterministic(1)
+    try:
+        hp = HostPrograms(lib)
+        runs = []
+        for replay in (False, True, True):
+            m = hp.model("resnet50", 8, seed=1)
+            m.use_graph(replay)
+            losses = []
+            for s in range(3):
+                x, y = _batch(m, s, "normal")
+                m.step_async(x, y, 0.002); lib.sync(); losses.append(m.last_loss())
+            runs.append((losses, m.slab_params()))
+            m.close(); lib.reset(mark)
+        for losses, params in runs[1:]:
+            assert losses == runs[0][0], (losses, runs[0][0])
+            assert np.array_equal(params, runs[0][1])
+    finally:
+        lib.set_deterministic(0)
+        lib.reset(mark)
+
+
 @pytest.mark.parametrize("batch,math,rtol", [(1, 0, FP32_RTOL), (256, 0, FP32_RTOL), (256, 1, TF32_RTOL)])
 def test_vanilla_rnn_gradients_and_adagrad_trajectory(oracle_lib, cuda_lib, batch, math, rtol):
     """min-char-rnn (vocabulary 80, hidden 100, 20 unrolled steps, batch 1 and 256): every gradient of one step, then
