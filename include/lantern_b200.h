@@ -170,6 +170,68 @@ int LTB_FN(lstm_cell_grad)(const float* i, float* di, const float* u, float* du,
                            const float* fr, float* dfr, const float* cr, float* dcr, const float* o, float* d_o,
                            const float* tc, const float* dc, const float* dh, int n);
 
+/* A whole unrolled sequence of the vanilla recurrent network in one call (no Backend counterpart: the reference stages the
+ * cell of NNModule.scala:189-200 operator by operator and unrolls it, DynamicRNNFix, NNModule.scala:240-253; the loss is
+ * sum over the steps of sum(nllLoss(logSoftmax(o_t), y_t)), as the generated min-char-rnn programs compute it).
+ *   x [T][B][V] inputs, y [T][B] classes, h0 [B][H] or NULL (zeros); Wxh [V][H], Whh [H][H], bh [H], Who [H][V], bo [V].
+ *   rnn_seq_fwd: h[t] = tanh(x[t] Wxh + h[t-1] Whh + bh); logp[t] = logSoftmax(h[t] Who + bo); loss[0] = -sum logp[t][b][y[t][b]].
+ *                h [T][B][H] and logp [T][B][V] are kept for the gradient.
+ *   rnn_seq_bwd: ACCUMULATES the gradient of dloss[0] * loss into dWxh, dWhh, dbh, dWho, dbo (inputs and h0 get none).
+ * The weights must fit one SM's shared memory (LTB_E_LIMIT otherwise: use the per-step calls); the first call must come
+ * before a step is recorded. */
+int LTB_FN(rnn_seq_fwd)(const float* x, const int32_t* y, const float* h0, const float* Wxh, const float* Whh, const float* bh,
+                        const float* Who, const float* bo, float* h, float* logp, float* loss, int T, int B, int V, int H);
+int LTB_FN(rnn_seq_bwd)(const float* x, const int32_t* y, const float* h0, const float* Whh, const float* Who, const float* h,
+                        const float* logp, const float* dloss, float* dWxh, float* dWhh, float* dbh, float* dWho, float* dbo,
+                        int T, int B, int V, int H);
+
+/* One node of the binary tree LSTM in one call forward and one call backward (no Backend counterpart: the reference stages a
+ * node operator by operator, PLDI19APP/SentimentTreeLSTM.scala:67-146 = NIPS18App/SentimentTreeLSTM.scala:118-170).
+ * Gate slots: 0 input gate i, 1 forget gate of the left child fl, 2 forget gate of the right child fr, 3 output gate o
+ * (all sigmoid), 4 update u (tanh).  A leaf uses slots 0, 3, 4 over ONE input (the embedding row); an inner node all five
+ * over TWO inputs (the children's first state vector):  gate[g] = act(W[g][0] in[0] (+ W[g][1] in[1]) + bias[g]).
+ *   c = i*u (+ fl*cl + fr*cr);  tc = tanh(c);  h = o*tc;
+ *   logp = logSoftmax(Why (classify_cell ? c : h) + by);  loss[0] = -logp[score[0]] (+ loss_l[0] + loss_r[0]).
+ * tree_node_bwd reads the gradients that arrived in dc, dh, dloss and ACCUMULATES into dW, dbias, din, dcl, dcr, dWhy, dby,
+ * dloss_l, dloss_r (any of din, dcl, dcr, dloss_l, dloss_r may be NULL: an input, a leaf). */
+typedef struct ltb_tree_node {
+  int hidden;                 /* length of every gate, of c and of h */
+  int in_len;                 /* length of the gate inputs: the embedding for a leaf, hidden for an inner node */
+  int classes;                /* rows of the classifier, at most 32 */
+  int inner;                  /* 0: leaf, 1: inner node */
+  int classify_cell;          /* the classifier reads c (the exchanged roles of the PLDI19 application) instead of h */
+  const float* in[2];         /* gate inputs (in[1] NULL for a leaf) */
+  float* din[2];
+  const float* W[5][2];       /* [hidden][in_len] each; unused slots NULL */
+  float* dW[5][2];
+  const float* bias[5];       /* [hidden]; slots 1 and 2 may name the same vector */
+  float* dbias[5];
+  const float* cl;            /* the children's second state vector (inner node) */
+  const float* cr;
+  float* dcl;
+  float* dcr;
+  const float* Why;           /* classifier [classes][hidden] */
+  const float* by;
+  float* dWhy;
+  float* dby;
+  const int32_t* score;       /* the node's class, in device memory */
+  const float* loss_l;        /* the children's accumulated losses (inner node) */
+  const float* loss_r;
+  float* dloss_l;
+  float* dloss_r;
+  float* gates;               /* out: [5][hidden] activations, kept for the gradient */
+  float* c;                   /* out: [hidden] each */
+  float* tc;
+  float* h;
+  float* logp;                /* out: [classes] */
+  float* loss;                /* out: [1] */
+  const float* dc;            /* gradients arriving from the parent and from the root's loss */
+  const float* dh;
+  const float* dloss;
+} ltb_tree_node;
+int LTB_FN(tree_node_fwd)(const ltb_tree_node* node);
+int LTB_FN(tree_node_bwd)(const ltb_tree_node* node);
+
 /* Branch regions (no counterpart in the reference, whose generated programs issue everything on one stream): two runs of
  * calls that do not depend on each other -- the shortcut convolution of a residual block and its main path, the two
  * expand convolutions of a fire module -- may overlap on the device.

@@ -7,7 +7,7 @@ trait method by method.  There is no CPU fallback: if the CUDA library is missin
 """
 import os
 
-from ._ffi import BoundLibrary, LanternError, parse_header  # noqa: F401
+from ._ffi import BoundLibrary, LanternError, parse_header, parse_struct  # noqa: F401
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "liblantern_b200.so")

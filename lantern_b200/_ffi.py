@@ -45,6 +45,27 @@ def parse_header(path=HEADER):
     return out
 
 
+def parse_struct(name, path=HEADER):
+    """ctypes.Structure mirroring `typedef struct <name> { ... } <name>;` of the header: int fields, and pointers (arrays of
+    pointers) that cross as raw addresses."""
+    text = open(path).read()
+    text = re.sub(r"/\*.*?\*/", " ", text, flags=re.S)
+    m = re.search(r"typedef\s+struct\s+%s\s*\{(.*?)\}\s*%s\s*;" % (name, name), text, flags=re.S)
+    if not m:
+        raise ValueError("no struct %s in the header" % name)
+    fields = []
+    for decl in m.group(1).split(";"):
+        decl = decl.strip()
+        if not decl:
+            continue
+        mm = re.match(r"(.*?)(\w+)((?:\[\d+\])*)$", decl)
+        ctype = _ctype(mm.group(1))
+        for dim in reversed(re.findall(r"\[(\d+)\]", mm.group(3))):
+            ctype = ctype * int(dim)
+        fields.append((mm.group(2), ctype))
+    return type(name, (ctypes.Structure,), {"_fields_": fields})
+
+
 class LanternError(RuntimeError):
     def __init__(self, code, msg):
         super().__init__("lantern backend error %d: %s" % (code, msg))

@@ -59,6 +59,8 @@ struct Context {
   const char* label = nullptr;        // optional name override for the next launches
   cudaStream_t side = nullptr;        // second stream: the weight-gradient half of conv backward runs beside the data-gradient half
   cudaEvent_t fork_ev = nullptr, join_ev = nullptr;
+  unsigned tune = 0;                  // LTB_TUNE (environment, read by ltb_init): switches single optimisations off for A/B measurements:
+                                      // 1 no in-kernel gather, 2 no tap-loop weight-grad from kept copies, 4 no kept copies, 8 no early first loads
   bool deterministic = false;         // split-K sums in a fixed order (clusters, slabs) instead of atomics (ltb_set_deterministic)
   bool filter_cache = false;          // per-tap filter forms kept across calls (ltb_set_filter_cache)
   bool fusion = false;                // look-ahead fusion of BN/add with ReLU (off unless the host opts in)

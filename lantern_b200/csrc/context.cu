@@ -105,6 +105,7 @@ static int init_steps(int device, size_t heap_bytes) {
   LTB_CUDA(cudaEventCreateWithFlags(&g.mark_ev, cudaEventDisableTiming));
   LTB_CUDA(cudaEventCreateWithFlags(&g.branch_done_ev, cudaEventDisableTiming));
   g.launches = 0; g.last = 0; g.msg.clear(); g.capturing = false; g.math = LTB_MATH_TF32;
+  if (const char* t = getenv("LTB_TUNE")) g.tune = (unsigned)strtoul(t, nullptr, 0);
   return LTB_OK;
 }
 

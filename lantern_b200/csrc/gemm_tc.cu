@@ -52,6 +52,7 @@ struct TcParams {
   uint32_t idesc;
   float* out; const float* bias; float alpha;
   long long split_stride;      // floats between the result slabs of consecutive clusters of splits (see launch_plan)
+  int early_loads;             // the producer fills the ring before the set-up barrier (0: after it)
   int cluster_z;               // splits whose partial results are summed inside the kernel: a thread-block cluster of this many CTAs along z
   long long pix_per_img, img_stride, chan_stride, ld;
   int col_mod, col_mul;        // row-major epilogue: D column n goes to column (n % col_mod) * col_mul + n / col_mod when col_mul != 0
@@ -238,7 +239,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
     BoxWalker::init_pair(wa, wb, P.a, P.b, m_tile, n_tile, k_begin, lane);
     if (lane == 0) {
-      const int first = n_iter < stages ? n_iter : stages;
+      const int first = !P.early_loads ? 0 : n_iter < stages ? n_iter : stages;
       for (; issued < first; ++issued) {
         uint8_t* sa = stage_base + (size_t)issued * stage_bytes; uint8_t* sb = sa + P.a.stage_bytes;
         mbar_expect_tx(&full_bar[issued], gather ? P.b.stage_bytes : stage_bytes);
@@ -259,9 +260,11 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
   if (warp == 0) {
     if (lane == 0 && n_iter > issued) {
-      int s = 0; uint32_t ph = 1u;          // more iterations than stages: the ring was filled once, stage 0 is reused next, in its second round
+      // after a ring filled before the barrier, stage 0 is reused next, in its second round; the first `stages` fills find
+      // the ring empty and wait for nobody
+      int s = issued == stages ? 0 : issued; uint32_t ph = issued == stages ? 1u : 0u;
       for (int it = issued; it < n_iter; ++it) {
-        if (!mbar_wait(&empty_bar[s], ph ^ 1u, &abort_flag, P.status, 1, P.wait_cycles)) break;
+        if (it >= stages && !mbar_wait(&empty_bar[s], ph ^ 1u, &abort_flag, P.status, 1, P.wait_cycles)) break;
         uint8_t* sa = stage_base + (size_t)s * stage_bytes; uint8_t* sb = sa + P.a.stage_bytes;
         mbar_expect_tx(&full_bar[s], gather ? P.b.stage_bytes : stage_bytes);
         if (!gather) { tma_load(&map_a, &full_bar[s], sa, P.a.rank, wa.c); wa.next(P.a); }
@@ -755,7 +758,7 @@ static int launch_plan(const TcPlan& p, const char* label) {
   if (!atomic) splits = nslabs * cz;
   P.k_per_split = (int)ceil_div(p.k_iters, splits);                                // a split may end up without iterations: it contributes zeros
   if (atomic) splits = (int)ceil_div(p.k_iters, P.k_per_split);                    // atomic mode: only splits that have work
-  P.cluster_z = cz;
+  P.cluster_z = cz; P.early_loads = (g.tune & 8) ? 0 : 1;
   P.epilogue = p.epilogue; P.accumulate = ws ? 0 : p.accumulate; P.atomic = atomic ? 1 : 0;
   if (atomic && !p.accumulate) LTB_CUDA(cudaMemsetAsync(p.out, 0, out_floats * 4, g.stream));     // overwrite semantics: start from zero, then add
   // tf32 x tf32 -> f32: D format 1 at [4,6), A/B format 2 at [7,10)/[10,13), major bits 15/16, N>>3 at [17,23), M>>4 at [24,29)
@@ -945,7 +948,7 @@ static int channels_last_into(const float* src, int n_img, int chan, int pix, fl
 static int channels_last(const float* src, int n_img, int chan, int pix, float** out, size_t* floats, bool keep = false) {
   const size_t n = (size_t)n_img * chan * pix;
   *floats = 0; *out = nullptr;
-  if (keep && g.filter_cache) {
+  if (keep && g.filter_cache && !(g.tune & 4)) {
     if (float* kept = (float*)step_alloc(n * 4)) {
       int rc = channels_last_into(src, n_img, chan, pix, kept); if (rc) return rc;
       for (size_t i = 0; i < cl_cache.size(); ++i) if (cl_cache[i].src == src) { cl_cache[i] = cl_cache.back(); cl_cache.pop_back(); break; }
@@ -1082,7 +1085,7 @@ static int conv_wgrad_taps(const float* x, const float* dy, float* dw, const Con
   // Both operands are read channels-last.  With the copies already there (x from this convolution's forward call, dy shared
   // with the data-grad) the tap loop reads each of them once; having to make both first only pays once the unfolded
   // matrix, nine times the size of x, would be large.
-  if ((!dyr || !xr) && (size_t)d.N * d.C * d.R * d.S * d.oH * d.oW * 4 < ((size_t)64 << 20)) return 0;
+  if ((!dyr || !xr || (g.tune & 2)) && (size_t)d.N * d.C * d.R * d.S * d.oH * d.oW * 4 < ((size_t)64 << 20)) return 0;
   int rc = dyr ? LTB_OK : channels_last(dy, d.N, d.K, d.oH * d.oW, &dyr, &ny); if (rc) return rc;
   if (!dyr) return 0;
   if (!xr) rc = channels_last(x, d.N, d.C, d.H * d.W, &xr, &nx);
@@ -1111,7 +1114,7 @@ int conv_fwd_tc(const float* x, const float* w, const float* bias, float* y, con
   if (!tc_plan_conv_fwd(p, y /* any aligned pointer: eligibility only */, rows, y, ldw, bias, y, d.N, ck, d.K, pix, g.sm_count)) return 0;
   { int t = conv_fwd_taps(x, w, bias, y, d); if (t != 0) return t; }      // the tap-loop form when the shape allows it
   // Small images (4 or 16 pixels) of a 1x1 convolution: the kernel collects the activation itself (no row copy first).
-  const bool gathered = rows && is_pointwise(d) && pix > 1 && tc_gather_possible(x, ck, pix);
+  const bool gathered = rows && is_pointwise(d) && pix > 1 && !(g.tune & 1) && tc_gather_possible(x, ck, pix);
   const float* op = x; bool r2; float* temp = nullptr; size_t tn = 0;
   int rc = gathered ? LTB_OK : stage_activation(x, !is_pointwise(d), d, ck, pix, &op, &r2, &temp, &tn);
   if (rc) return rc < 0 ? rc : 0;
@@ -1133,7 +1136,7 @@ int conv_dgrad_tc(const float* dy, const float* w, float* dx, const ConvDims& d)
   if (!tc_plan_conv_dgrad(p, dx, rows, dx, ldw, dx, d.N, ck, d.K, pix, direct, g.sm_count)) return 0;
   { int t = conv_dgrad_taps(dy, w, dx, d); if (t != 0) return t; }
   { int t = conv_dgrad_taps_up2(dy, w, dx, d); if (t != 0) return t; }
-  const bool gathered = rows && pix > 1 && tc_gather_possible(dy, d.K, pix);    // dy of a small map: collected by the kernel itself
+  const bool gathered = rows && pix > 1 && !(g.tune & 1) && tc_gather_possible(dy, d.K, pix);    // dy of a small map: collected by the kernel itself
   const float* op = dy; bool r2; float* temp = nullptr; size_t tn = 0;
   ConvDims flat = d; flat.C = d.K;                               // dy is [N][K][pix]: staged like a pointwise activation with K channels
   int rc = gathered ? LTB_OK : stage_activation(dy, false, flat, d.K, pix, &op, &r2, &temp, &tn);

@@ -52,6 +52,7 @@ struct Model {
   bool early_reduce = false;   // this step runs data-parallel with an update: finished gradient ranges are summed during backward
   bool branches = true;        // independent runs of calls (shortcut convolutions) are issued as branch regions
   bool fused_cells = true;     // recursive models: one call per gate (ltb_affine_act) instead of one per operator
+  bool whole_sequence = true;  // with fused cells: the vanilla RNN's whole unrolled sequence (ltb_rnn_seq_fwd) and a whole tree node (ltb_tree_node_fwd) in one call
   bool resident = false;       // read the batch from dev_x/dev_y instead of uploading it
   float* dev_x = nullptr; int32_t* dev_y = nullptr;
   float* dev_loss = nullptr;   // the loss of the last step, kept outside the arena span that the step resets
@@ -292,6 +293,8 @@ struct VanillaRnn : Model {
     mark = BK(mark)();
   }
   TR forward(Tape& t, const TR& x, const int32_t* y) override {
+    if (fused_cells && whole_sequence)                 // all T steps in one call (ltb_rnn_seq_fwd / _bwd): 4 launches per sequence
+      return t.rnn_sequence(x, y, P(w1), P(w2), P(bh), P(wo), P(bo), T, batch);
     TR h = make({batch, Hd});                          // cell.init: zeros
     BK(fill)(h.x, 0.0f, h.count());
     TR loss = make({1});
@@ -382,6 +385,24 @@ struct TreeLstm : Model {
   State visit(Tape& t, const int32_t* host, const int32_t* dev, int i) {
     const int32_t *scores = dev + 1, *words = host + 1 + MAXN, *lch = host + 1 + 2 * MAXN, *rch = host + 1 + 3 * MAXN;
     State s;
+    if (fused_cells && whole_sequence) {               // the whole node in one call forward and one backward (ltb_tree_node_fwd / _bwd)
+      TR none, W[5][2], bias[5];
+      Tape::NodeOut o;
+      if (lch[i] < 0) {
+        TR e; e.rank = 1; e.shape[0] = E; e.x = table + (int64_t)words[i] * E; e.is_input = true;
+        W[0][0] = P(Wi); W[3][0] = P(Wo); W[4][0] = P(Wu); bias[0] = P(bi); bias[3] = P(bo); bias[4] = P(bu);
+        o = t.tree_node(false, pldi19, e, nullptr, W, bias, nullptr, nullptr, P(Why), P(by), scores + i, nullptr, nullptr);
+      } else {
+        State l = visit(t, host, dev, lch[i]), r = visit(t, host, dev, rch[i]);
+        W[0][0] = P(U0i); W[0][1] = P(U1i); W[1][0] = P(U00f); W[1][1] = P(U01f); W[2][0] = P(U10f); W[2][1] = P(U11f);
+        W[3][0] = P(U0o); W[3][1] = P(U1o); W[4][0] = P(U0u); W[4][1] = P(U1u);
+        bias[0] = P(bbi); bias[1] = P(bbf); bias[2] = P(bbf); bias[3] = P(bbo); bias[4] = P(bbu);
+        o = t.tree_node(true, pldi19, l.first, &r.first, W, bias, &l.second, &r.second, P(Why), P(by), scores + i, &l.loss, &r.loss);
+      }
+      s.loss = o.loss;
+      s.first = pldi19 ? o.cell : o.hidden; s.second = pldi19 ? o.hidden : o.cell;   // the PLDI19 application's exchanged roles
+      return s;
+    }
     if (lch[i] < 0) {                                                                // leaf, lines 72-85 and 130-133
       TR e; e.rank = 1; e.shape[0] = E; e.x = table + (int64_t)words[i] * E; e.is_input = true;
       TR ig = leaf_gate(t, LTB_SIGMOID, Wi, e, bi);
@@ -583,7 +604,12 @@ int HOST_FN(model_set_table)(void* m, const float* host, int rows) {
 }
 int64_t HOST_FN(model_label_count)(void* m) { return ((Model*)m)->label_count; }
 // Recursive models: gates as single fused calls (default) or operator by operator, as the reference stages them.
-int HOST_FN(model_use_fused_cells)(void* m, int on) { ((Model*)m)->fused_cells = on != 0; return 0; }
+// on: 0 operator by operator, 1 one call per gate / cell, 2 (default) in addition the vanilla RNN's whole sequence in one call.
+int HOST_FN(model_use_fused_cells)(void* m, int on) {
+  Model* M = (Model*)m;
+  if (M->graph) { BK(graph_destroy)(M->graph); M->graph = nullptr; }
+  M->fused_cells = on != 0; M->whole_sequence = on >= 2; return 0;
+}
 // Issue independent runs of calls as branch regions (default) or everything in program order on one stream.
 int HOST_FN(model_use_branches)(void* m, int on) {
   Model* M = (Model*)m;

@@ -189,6 +189,49 @@ struct Tape {
     push([=] { BK(lstm_cell_grad)(i.x, i.d, u.x, u.d, flx, fld, clx, cld, frx, frd, crx, crd, o.x, o.d, tc, c.d, h.d, n); });
     *cell = c; *hidden = h;
   }
+  // The whole unrolled vanilla RNN (cell, output layer, logSoftmax + NLL summed over steps and batch) as ONE forward call and
+  // one backward call: x [T][B][V], targets y [T][B], weights stored [in, out]; the initial hidden state is zero.
+  TR rnn_sequence(const TR& x, const int32_t* y, const TR& Wxh, const TR& Whh, const TR& bh, const TR& Who, const TR& bo, int T, int B) {
+    const int V = Wxh.shape[0], H = Wxh.shape[1];
+    TR loss = make({1});
+    float* h = alloc_value((int64_t)T * B * H); float* logp = alloc_value((int64_t)T * B * V);
+    BK(rnn_seq_fwd)(x.x, y, nullptr, Wxh.x, Whh.x, bh.x, Who.x, bo.x, h, logp, loss.x, T, B, V, H);
+    push([=] { BK(rnn_seq_bwd)(x.x, y, nullptr, Whh.x, Who.x, h, logp, loss.d, Wxh.d, Whh.d, bh.d, Who.d, bo.d, T, B, V, H); });
+    return loss;
+  }
+  // One node of the binary tree LSTM as ONE forward call and one backward call (ltb_tree_node_fwd / _bwd).  W and bias are
+  // indexed by gate slot (i, fl, fr, o, u; a leaf leaves fl and fr empty and has one input); in0 / in1 are the children's first
+  // state vector (or the embedding row), cl / cr their second one; the node's loss is nll + loss_l + loss_r.
+  struct NodeOut { TR loss, cell, hidden; };
+  NodeOut tree_node(bool inner, bool classify_cell, const TR& in0, const TR* in1, const TR (&W)[5][2], const TR (&bias)[5], const TR* cl, const TR* cr,
+                    const TR& Why, const TR& by, const int32_t* score, const TR* loss_l, const TR* loss_r) {
+    const int Hd = Why.shape[1], K = Why.shape[0], L = (int)in0.count();
+    const int64_t pitch = ((int64_t)Hd + 63) / 64 * 64;
+    float* vals = alloc_value(8 * pitch + 64);                     // gates [5], c, tc, h, then logp and the loss
+    float* grads = alloc_zero(2 * pitch + 64);                     // dc, dh, dloss
+    ltb_tree_node n = {};
+    n.hidden = Hd; n.in_len = L; n.classes = K; n.inner = inner ? 1 : 0; n.classify_cell = classify_cell ? 1 : 0;
+    n.in[0] = in0.x; n.din[0] = in0.is_input ? nullptr : in0.d;
+    if (inner) { n.in[1] = in1->x; n.din[1] = in1->is_input ? nullptr : in1->d; n.cl = cl->x; n.cr = cr->x; n.dcl = cl->d; n.dcr = cr->d; }
+    for (int g = 0; g < 5; ++g) {
+      if (!inner && (g == 1 || g == 2)) continue;
+      for (int k = 0; k < (inner ? 2 : 1); ++k) { n.W[g][k] = W[g][k].x; n.dW[g][k] = W[g][k].d; }
+      n.bias[g] = bias[g].x; n.dbias[g] = bias[g].d;
+    }
+    n.Why = Why.x; n.by = by.x; n.dWhy = Why.d; n.dby = by.d; n.score = score;
+    if (loss_l) { n.loss_l = loss_l->x; n.dloss_l = loss_l->d; }
+    if (loss_r) { n.loss_r = loss_r->x; n.dloss_r = loss_r->d; }
+    n.gates = vals; n.c = vals + 5 * pitch; n.tc = vals + 6 * pitch; n.h = vals + 7 * pitch; n.logp = vals + 8 * pitch; n.loss = vals + 8 * pitch + 32;
+    n.dc = grads; n.dh = grads + pitch; n.dloss = grads + 2 * pitch;
+    BK(tree_node_fwd)(&n);
+    push([=] { BK(tree_node_bwd)(&n); });
+    NodeOut out;
+    out.cell.rank = out.hidden.rank = out.loss.rank = 1;
+    out.cell.shape[0] = out.hidden.shape[0] = Hd; out.loss.shape[0] = 1;
+    out.cell.x = n.c; out.cell.d = grads; out.hidden.x = n.h; out.hidden.d = grads + pitch; out.loss.x = n.loss; out.loss.d = grads + 2 * pitch;
+    traced(out.cell); traced(out.hidden); traced(out.loss);
+    return out;
+  }
   TR dot(const TR& a, const TR& b) {
     if (b.rank == 2) {
       int m = a.shape[0], k = a.shape[1], n = b.shape[1];

@@ -1190,6 +1190,134 @@ int ora_allreduce_sgd_step(float* x, float* d, float lr, int64_t n) { ProfScope 
 }
 }  // extern "C"
 
+// ------------------------------------------------------------------ a whole unrolled sequence of the vanilla RNN
+// The operator sequence the reference stages for T steps (NNModule.scala:189-200, 240-253), issued through this file's own
+// entry points: two matrix products, two broadcasting adds and tanh for the cell; product and plusBias for the output layer;
+// logSoftmax, nllLoss and sum for the step's loss, added to the running total.  Backward replays the gradient calls of
+// those operators in reverse order.  What the CUDA library's single-launch sequence kernels are checked against.  Those kernels
+// are FP32 CUDA-core code in every math mode (a 100-wide product per row is no tensor-core work), so the operand truncation
+// of the TF32 mode is switched off for the duration of the call.
+namespace { struct Fp32Scope { int saved; Fp32Scope() : saved(g.math) { g.math = LTB_MATH_FP32; } ~Fp32Scope() { g.math = saved; } }; }
+extern "C" {
+int ora_rnn_seq_fwd(const float* x, const int32_t* y, const float* h0, const float* Wxh, const float* Whh, const float* bh, const float* Who,
+                    const float* bo, float* h, float* logp, float* loss, int T, int B, int V, int H) { ProfScope prof_scope_("ora_rnn_seq_fwd");
+  REQUIRE(x && y && Wxh && Whh && bh && Who && bo && h && logp && loss && T > 0 && B > 0 && V > 0 && H > 0, "rnn_seq_fwd: bad argument");
+  Fp32Scope fp32_only;
+  std::vector<float> zero((size_t)B * H, 0.0f), p1((size_t)B * H), p2((size_t)B * H), pre((size_t)B * H), pre2((size_t)B * H), o((size_t)B * V), nl(B);
+  const int sbh[2] = {B, H}, sh1[2] = {1, H}, sbv[2] = {B, V}, sv1[2] = {1, V};
+  float total = 0.0f, st = 0.0f;
+  for (int t = 0; t < T; ++t) {
+    const float* hp = t ? h + (size_t)(t - 1) * B * H : (h0 ? h0 : zero.data());
+    float* ht = h + (size_t)t * B * H;
+    ora_mm_dot(x + (size_t)t * B * V, Wxh, p1.data(), B, V, H);
+    ora_mm_dot(hp, Whh, p2.data(), B, H, H);
+    ora_ew_binary(LTB_ADD, p1.data(), sbh, p2.data(), sbh, pre.data(), 2);
+    ora_ew_binary(LTB_ADD, pre.data(), sbh, bh, sh1, pre2.data(), 2);
+    ora_unary(LTB_TANH, pre2.data(), ht, (int64_t)B * H);
+    ora_mm_dot(ht, Who, o.data(), B, H, V);
+    ora_plus_bias(o.data(), sbv, bo, sv1, 2);
+    ora_log_softmax(o.data(), logp + (size_t)t * B * V, B, V);
+    ora_nll(logp + (size_t)t * B * V, y + (size_t)t * B, nl.data(), B, V);
+    ora_sum(nl.data(), &st, B);
+    total = total + st;
+  }
+  loss[0] = total;
+  return LTB_OK;
+}
+int ora_rnn_seq_bwd(const float* x, const int32_t* y, const float* h0, const float* Whh, const float* Who, const float* h, const float* logp,
+                    const float* dloss, float* dWxh, float* dWhh, float* dbh, float* dWho, float* dbo, int T, int B, int V, int H) { ProfScope prof_scope_("ora_rnn_seq_bwd");
+  REQUIRE(x && y && Whh && Who && h && logp && dloss && dWxh && dWhh && dbh && dWho && dbo && T > 0 && B > 0 && V > 0 && H > 0, "rnn_seq_bwd: bad argument");
+  Fp32Scope fp32_only;
+  std::vector<float> zero((size_t)B * H, 0.0f), dh((size_t)B * H, 0.0f), dhp((size_t)B * H), dpre((size_t)B * H), dlogp((size_t)B * V), dob((size_t)B * V), dnl(B);
+  const int sbh[2] = {B, H}, sh1[2] = {1, H}, sbv[2] = {B, V}, sv1[2] = {1, V};
+  for (int t = T - 1; t >= 0; --t) {
+    const float* hp = t ? h + (size_t)(t - 1) * B * H : (h0 ? h0 : zero.data());
+    const float* ht = h + (size_t)t * B * H;
+    std::fill(dnl.begin(), dnl.end(), 0.0f); std::fill(dlogp.begin(), dlogp.end(), 0.0f); std::fill(dob.begin(), dob.end(), 0.0f);
+    std::fill(dpre.begin(), dpre.end(), 0.0f); std::fill(dhp.begin(), dhp.end(), 0.0f);
+    ora_sum_grad(dnl.data(), dloss, B);                                            // loss = loss + sum(nll): both operands get dloss
+    ora_nll_grad(dlogp.data(), dnl.data(), y + (size_t)t * B, B, V);
+    ora_log_softmax_grad(dob.data(), logp + (size_t)t * B * V, dlogp.data(), B, V);
+    ora_plus_bias_grad(dbo, sv1, dob.data(), sbv, 2);
+    ora_add_dot_trans2(dh.data(), dob.data(), Who, B, H, V);                          // dh += do Who^T (on top of what step t + 1 sent)
+    ora_add_dot_trans1(dWho, ht, dob.data(), B, H, V);                                // dWho += h^T do
+    ora_unary_grad(LTB_TANH, ht, dpre.data(), ht, dh.data(), (int64_t)B * H, 0);      // dpre += dh (1 - h^2)
+    ora_ew_inplace(LTB_ADD, dbh, sh1, dpre.data(), sbh, 2);                           // the bias's share of the broadcasting add
+    ora_add_dot_trans1(dWxh, x + (size_t)t * B * V, dpre.data(), B, V, H);
+    ora_add_dot_trans1(dWhh, hp, dpre.data(), B, H, H);
+    ora_add_dot_trans2(dhp.data(), dpre.data(), Whh, B, H, H);                        // for step t - 1
+    dh = dhp;
+  }
+  return LTB_OK;
+}
+}  // extern "C"
+
+// One node of the binary tree LSTM (PLDI19APP/SentimentTreeLSTM.scala:67-146, NIPS18App/SentimentTreeLSTM.scala:118-170) as
+// the sequence of this file's entry points that the gate-by-gate host program issues: one affine_act per gate, lstm_cell, the
+// classifier, logSoftmax, nllLoss, the two additions of the children's losses; backward replays their gradient calls in
+// reverse order with the gates' gradient vectors as locals.  What the CUDA library's one-launch node kernels are checked against.
+extern "C" {
+static const int kSlotAct[5] = {LTB_SIGMOID, LTB_SIGMOID, LTB_SIGMOID, LTB_SIGMOID, LTB_TANH};
+static bool tree_node_ok(const ltb_tree_node* n) {
+  if (!n || n->hidden <= 0 || n->hidden > 512 || n->in_len <= 0 || n->classes <= 0 || n->classes > 32) return false;
+  if (!n->in[0] || (n->inner && (!n->in[1] || !n->cl || !n->cr)) || !n->Why || !n->by || !n->score || !n->gates || !n->c || !n->tc || !n->h || !n->logp || !n->loss) return false;
+  for (int slot = 0; slot < 5; ++slot) {
+    if (!n->inner && (slot == 1 || slot == 2)) continue;
+    if (!n->W[slot][0] || !n->bias[slot] || (n->inner && !n->W[slot][1])) return false;
+  }
+  return true;
+}
+int ora_tree_node_fwd(const ltb_tree_node* n) { ProfScope prof_scope_("ora_tree_node_fwd");
+  REQUIRE(tree_node_ok(n), "tree_node_fwd: bad argument");
+  const int Hd = n->hidden, L = n->in_len, K = n->classes;
+  for (int slot = 0; slot < 5; ++slot) {
+    if (!n->inner && (slot == 1 || slot == 2)) continue;
+    ora_affine_act(n->W[slot][0], n->in[0], L, n->inner ? n->W[slot][1] : nullptr, n->inner ? n->in[1] : nullptr, n->inner ? L : 0, n->bias[slot], kSlotAct[slot],
+                   n->gates + (size_t)slot * Hd, Hd);
+  }
+  float* g = n->gates;
+  if (n->inner) ora_lstm_cell(g, g + 4 * Hd, g + Hd, n->cl, g + 2 * Hd, n->cr, g + 3 * Hd, n->c, n->tc, n->h, Hd);
+  else ora_lstm_cell(g, g + 4 * Hd, nullptr, nullptr, nullptr, nullptr, g + 3 * Hd, n->c, n->tc, n->h, Hd);
+  std::vector<float> pred(K); float nl = 0.0f;
+  ora_affine_act(n->Why, n->classify_cell ? n->c : n->h, Hd, nullptr, nullptr, 0, n->by, -1, pred.data(), K);
+  ora_log_softmax(pred.data(), n->logp, 1, K);
+  ora_nll(n->logp, n->score, &nl, 1, K);
+  if (n->loss_l) nl = nl + n->loss_l[0];
+  if (n->loss_r) nl = nl + n->loss_r[0];
+  n->loss[0] = nl;
+  return LTB_OK;
+}
+int ora_tree_node_bwd(const ltb_tree_node* n) { ProfScope prof_scope_("ora_tree_node_bwd");
+  REQUIRE(tree_node_ok(n) && n->dc && n->dh && n->dloss && n->dWhy && n->dby, "tree_node_bwd: bad argument");
+  const int Hd = n->hidden, L = n->in_len, K = n->classes;
+  const float dl = n->dloss[0];
+  if (n->dloss_l) n->dloss_l[0] += dl;
+  if (n->dloss_r) n->dloss_r[0] += dl;
+  std::vector<float> dlogp(K, 0.0f), dpred(K, 0.0f), pred(K, 0.0f), dc(n->dc, n->dc + Hd), dh(n->dh, n->dh + Hd), dg((size_t)5 * Hd, 0.0f), dchild((size_t)2 * Hd, 0.0f);
+  ora_nll_grad(dlogp.data(), &dl, n->score, 1, K);
+  ora_log_softmax_grad(dpred.data(), n->logp, dlogp.data(), 1, K);
+  ora_affine_act_grad(n->Why, n->dWhy, n->classify_cell ? n->c : n->h, n->classify_cell ? dc.data() : dh.data(), Hd, nullptr, nullptr, nullptr, nullptr, 0,
+                      n->dby, -1, pred.data(), dpred.data(), K);
+  float* g = n->gates;
+  if (n->inner) {
+    float* dcl = n->dcl ? n->dcl : dchild.data(); float* dcr = n->dcr ? n->dcr : dchild.data() + Hd;
+    ora_lstm_cell_grad(g, dg.data(), g + 4 * Hd, dg.data() + 4 * Hd, g + Hd, dg.data() + Hd, n->cl, dcl, g + 2 * Hd, dg.data() + 2 * Hd, n->cr, dcr,
+                       g + 3 * Hd, dg.data() + 3 * Hd, n->tc, dc.data(), dh.data(), Hd);
+  } else {
+    ora_lstm_cell_grad(g, dg.data(), g + 4 * Hd, dg.data() + 4 * Hd, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr,
+                       g + 3 * Hd, dg.data() + 3 * Hd, n->tc, dc.data(), dh.data(), Hd);
+  }
+  for (int slot = 4; slot >= 0; --slot) {
+    if (!n->inner && (slot == 1 || slot == 2)) continue;
+    REQUIRE(n->dW[slot][0] && n->dbias[slot] && (!n->inner || n->dW[slot][1]), "tree_node_bwd: missing gate gradient");
+    ora_affine_act_grad(n->W[slot][0], n->dW[slot][0], n->in[0], n->din[0], L, n->inner ? n->W[slot][1] : nullptr, n->inner ? n->dW[slot][1] : nullptr,
+                        n->inner ? n->in[1] : nullptr, n->inner ? n->din[1] : nullptr, n->inner ? L : 0, n->dbias[slot], kSlotAct[slot],
+                        g + (size_t)slot * Hd, dg.data() + (size_t)slot * Hd, Hd);
+  }
+  return LTB_OK;
+}
+}  // extern "C"
+
 // ------------------------------------------------------------------ staging / replay: plain host equivalents.
 extern "C" {
 void* ora_host_alloc(size_t bytes) { return malloc(bytes); }

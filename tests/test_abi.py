@@ -53,3 +53,21 @@ def test_product_sources_never_reference_the_oracle():
                         bad.append(os.path.join(dp, f))
     # the header documents the oracle prefix in a comment; nothing else may mention it
     assert [b for b in bad if not b.endswith("lantern_b200.h")] == []
+
+
+def test_ctypes_mirror_of_the_tree_node_struct_has_the_c_layout(tmp_path):
+    """`parse_struct` builds the ctypes mirror of `ltb_tree_node` from the header text; a C program compiled against the same
+    header must report the same size and the same offset for every field."""
+    import ctypes
+    import subprocess
+    from lantern_b200 import parse_struct
+    node = parse_struct("ltb_tree_node")
+    names = [n for n, _ in node._fields_]
+    src = tmp_path / "layout.c"
+    src.write_text('#include <stdio.h>\n#include <stddef.h>\n#include "lantern_b200.h"\nint main(void) {\n  printf("%zu\\n", sizeof(ltb_tree_node));\n'
+                   + "".join('  printf("%%zu\\n", offsetof(ltb_tree_node, %s));\n' % n for n in names) + "  return 0;\n}\n")
+    exe = tmp_path / "layout"
+    subprocess.check_call(["gcc", "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe)])
+    got = [int(v) for v in subprocess.check_output([str(exe)]).split()]
+    assert got[0] == ctypes.sizeof(node)
+    assert got[1:] == [getattr(node, n).offset for n in names]

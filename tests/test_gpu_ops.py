@@ -537,6 +537,94 @@ def test_pointwise_weight_grad_with_a_misaligned_input_view(ora, gpu):
     assert_close(ref["dx"], got["dx"], TF32_RTOL, "dx (dy and w are aligned: tensor-core path)")
 
 
+@pytest.mark.parametrize("T,B,V,H", [(20, 256, 80, 100), (20, 1, 80, 100), (7, 37, 26, 50), (3, 300, 33, 17)])
+def test_rnn_whole_sequence_kernels(ora, gpu, T, B, V, H):
+    """ltb_rnn_seq_fwd / ltb_rnn_seq_bwd (every step of the unrolled vanilla RNN inside one launch, the rows of the batch dealt
+    out to CTAs) against the oracle issuing the reference's operator sequence: hidden states, log-probabilities, loss, and the
+    five gradients accumulated onto non-zero destinations.  Twice in a row: the launch leaves its completion counter at zero."""
+    rng = R(9)
+    ids = rng.integers(0, V, (T + 1, B))
+    x0 = (rng.standard_normal((T, B, V)) * 0.1).astype(np.float32)
+    x0[np.arange(T)[:, None], np.arange(B)[None, :], ids[:T]] += 1.0                       # near one-hot, every entry live
+    y0 = ids[1:].astype(np.int32)
+    W = {"xh": (rng.standard_normal((V, H)) / np.sqrt(V)).astype(np.float32), "hh": (rng.standard_normal((H, H)) / np.sqrt(H)).astype(np.float32),
+         "bh": (rng.standard_normal(H) * 0.1).astype(np.float32), "ho": (rng.standard_normal((H, V)) / np.sqrt(H)).astype(np.float32),
+         "bo": (rng.standard_normal(V) * 0.1).astype(np.float32)}
+
+    def f(b):
+        b.lib.set_math(0)
+        x, y = b.fromNumpy(x0), b.fromNumpy(y0)
+        w = {k: TensorR(b.fromNumpy(v), b.fromNumpy(v * 0.5)) for k, v in W.items()}
+        out = {}
+        for rep in range(2):
+            h, logp, loss = b.empty(T, B, H), b.empty(T, B, V), b.empty(1)
+            b.lib.rnn_seq_fwd(x.ptr, y.ptr, 0, w["xh"].x.ptr, w["hh"].x.ptr, w["bh"].x.ptr, w["ho"].x.ptr, w["bo"].x.ptr, h.ptr, logp.ptr, loss.ptr, T, B, V, H)
+            dloss = b.fill((1,), 0.5)
+            b.lib.rnn_seq_bwd(x.ptr, y.ptr, 0, w["hh"].x.ptr, w["ho"].x.ptr, h.ptr, logp.ptr, dloss.ptr,
+                              w["xh"].d.ptr, w["hh"].d.ptr, w["bh"].d.ptr, w["ho"].d.ptr, w["bo"].d.ptr, T, B, V, H)
+            out["h%d" % rep], out["logp%d" % rep], out["loss%d" % rep] = h.toCPU(), logp.toCPU(), loss.toCPU()
+        for k in w:
+            out["d" + k] = w[k].d.toCPU()
+        return out
+    check(f, ora, gpu)
+
+
+@pytest.mark.parametrize("inner,classify_cell,Hd,L", [(1, 1, 150, 150), (1, 0, 150, 150), (0, 1, 150, 300), (0, 0, 150, 300), (1, 0, 40, 40)])
+def test_tree_node_and_gradient(ora, gpu, inner, classify_cell, Hd, L):
+    """ltb_tree_node_fwd / ltb_tree_node_bwd (a whole tree-LSTM node per launch) against the oracle issuing the gate-by-gate
+    operator sequence: gates, cell, hidden, log-probabilities and loss; then every gradient accumulated onto non-zero
+    destinations -- an inner node (five gates over two inputs, the two forget gates sharing one bias) and a leaf (three
+    gates over the embedding, no input gradient), with the classifier on the cell and on the hidden vector.  Twice in a row:
+    the forward launch leaves its completion counter at zero."""
+    import ctypes
+    from lantern_b200 import parse_struct
+    Node = parse_struct("ltb_tree_node")
+    K = 5
+    rng = R(21)
+    v = lambda *shape, scale=1.0: (rng.standard_normal(shape) * scale).astype(np.float32)
+    slots = (0, 1, 2, 3, 4) if inner else (0, 3, 4)
+    data = {"in0": v(L, scale=0.5), "in1": v(L, scale=0.5), "cl": v(Hd), "cr": v(Hd), "Why": v(K, Hd, scale=0.1), "by": v(K, scale=0.1),
+            "dc": v(Hd), "dh": v(Hd), "dloss": np.array([0.75], np.float32), "loss_l": np.array([1.25], np.float32), "loss_r": np.array([2.5], np.float32)}
+    for g in slots:
+        data["W%d0" % g] = v(Hd, L, scale=1.0 / np.sqrt(L)); data["W%d1" % g] = v(Hd, L, scale=1.0 / np.sqrt(L))
+    data["b0"], data["b12"], data["b3"], data["b4"] = v(Hd, scale=0.1), v(Hd, scale=0.1), v(Hd, scale=0.1), v(Hd, scale=0.1)
+    bias_of = {0: "b0", 1: "b12", 2: "b12", 3: "b3", 4: "b4"}
+    grads = ["in0", "in1", "cl", "cr", "Why", "by", "loss_l", "loss_r", "b0", "b12", "b3", "b4"] + ["W%d%d" % (g, k) for g in slots for k in (0, 1)]
+
+    def f(b):
+        t = {k: b.fromNumpy(a) for k, a in data.items()}
+        d = {k: b.fromNumpy(data[k] * 0.25) for k in grads}                           # accumulate onto non-zero values
+        score = b.fromNumpy(np.array([3], np.int32))
+        out = {}
+        for rep in range(2):
+            gates, c, tc, h, logp, loss = b.fill((5, Hd), 0.0), b.fill((Hd,), 0.0), b.fill((Hd,), 0.0), b.fill((Hd,), 0.0), b.fill((K,), 0.0), b.fill((1,), 0.0)
+            n = Node()
+            n.hidden, n.in_len, n.classes, n.inner, n.classify_cell = Hd, L, K, inner, classify_cell
+            getattr(n, "in")[0] = t["in0"].ptr
+            if inner:
+                getattr(n, "in")[1] = t["in1"].ptr
+                n.din[0], n.din[1] = d["in0"].ptr, d["in1"].ptr
+                n.cl, n.cr, n.dcl, n.dcr = t["cl"].ptr, t["cr"].ptr, d["cl"].ptr, d["cr"].ptr
+                n.loss_l, n.loss_r, n.dloss_l, n.dloss_r = t["loss_l"].ptr, t["loss_r"].ptr, d["loss_l"].ptr, d["loss_r"].ptr
+            for g in slots:
+                for k in ((0, 1) if inner else (0,)):
+                    n.W[g][k], n.dW[g][k] = t["W%d%d" % (g, k)].ptr, d["W%d%d" % (g, k)].ptr
+                n.bias[g], n.dbias[g] = t[bias_of[g]].ptr, d[bias_of[g]].ptr
+            n.Why, n.by, n.dWhy, n.dby, n.score = t["Why"].ptr, t["by"].ptr, d["Why"].ptr, d["by"].ptr, score.ptr
+            n.gates, n.c, n.tc, n.h, n.logp, n.loss = gates.ptr, c.ptr, tc.ptr, h.ptr, logp.ptr, loss.ptr
+            n.dc, n.dh, n.dloss = t["dc"].ptr, t["dh"].ptr, t["dloss"].ptr
+            b.lib.tree_node_fwd(ctypes.addressof(n))
+            b.lib.tree_node_bwd(ctypes.addressof(n))
+            g_all = gates.toCPU()
+            out["gates%d" % rep] = g_all if inner else g_all[[0, 3, 4]]
+            out["c%d" % rep], out["h%d" % rep], out["logp%d" % rep], out["loss%d" % rep] = c.toCPU(), h.toCPU(), logp.toCPU(), loss.toCPU()
+        used = [k for k in grads if inner or k not in ("in0", "in1", "cl", "cr", "loss_l", "loss_r", "b12") and not k.endswith("1")]
+        for k in used:
+            out["d" + k] = d[k].toCPU()
+        return out
+    check(f, ora, gpu)
+
+
 # ---------------------------------------------------------------------------------------------- branch regions
 @pytest.mark.parametrize("replay", [False, True])
 def test_branch_region_gives_the_results_of_program_order(gpu, replay):

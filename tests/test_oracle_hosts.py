@@ -3,6 +3,7 @@ An untrained classifier's loss is ln(classes) per prediction, and repeating one 
 import os
 
 import numpy as np
+import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 ORA_HOSTS = os.path.join(ROOT, "oracle", "liblantern_oracle_hosts.so")
@@ -65,6 +66,28 @@ def test_treelstm_fused_gates_equal_operator_by_operator(oracle_lib):
         assert np.abs(a - b).max() <= 1e-5 * max(np.abs(b).max(), 1e-12)
 
 
+@pytest.mark.parametrize("variant", ["treelstm", "treelstm_nips18"])
+def test_treelstm_node_call_equals_operator_by_operator(oracle_lib, variant):
+    """A whole tree node as one forward and one backward call (tree_node_fwd / tree_node_bwd) against the reference's
+    operator-by-operator form, on the oracle, whose node entry points issue that operator sequence: same loss and the same 22
+    gradients up to the order of a few float additions (both applications: exchanged roles with clipping, plain cell)."""
+    from tests.test_gpu_models import _random_tree
+    mark = oracle_lib.mark()
+    x = np.zeros(1, np.float32)
+    for leaves in (1, 2, 9):
+        y = _random_tree(np.random.default_rng(12 + leaves), leaves)
+        res = []
+        for level in (2, 0):
+            m = _model(oracle_lib, variant, 1)
+            m.use_fused_cells(level)
+            loss = m.step(x, y, 0.0, update=False)
+            res.append((loss, [m.grad(i) for i in range(m.num_params)]))
+            m.close(); oracle_lib.reset(mark)
+        assert abs(res[0][0] - res[1][0]) <= 1e-6 * abs(res[1][0]), (leaves, res[0][0], res[1][0])
+        for i, (a, b) in enumerate(zip(res[0][1], res[1][1])):
+            assert np.abs(a - b).max() <= 1e-5 * max(np.abs(b).max(), 1e-12), (leaves, i)
+
+
 def test_rnn_fused_cell_equals_operator_by_operator(oracle_lib):
     """The recurrent cell and the output layer as one fused call each (affine_act_rows) against the operator-by-operator form."""
     mark = oracle_lib.mark()
@@ -77,6 +100,28 @@ def test_rnn_fused_cell_equals_operator_by_operator(oracle_lib):
     for fused in (True, False):
         m = _model(oracle_lib, "rnn", B)
         m.use_fused_cells(fused)
+        loss = m.step(x.ravel(), y, 0.0, update=False)
+        res.append((loss, [m.grad(i) for i in range(m.num_params)]))
+        m.close(); oracle_lib.reset(mark)
+    assert abs(res[0][0] - res[1][0]) <= 1e-6 * abs(res[1][0])
+    for a, b in zip(res[0][1], res[1][1]):
+        assert np.abs(a - b).max() <= 2e-5 * max(np.abs(b).max(), 1e-12)
+
+
+def test_rnn_whole_sequence_call_equals_operator_by_operator(oracle_lib):
+    """The whole unrolled sequence as one forward and one backward call (rnn_seq_fwd / rnn_seq_bwd) against the
+    operator-by-operator form, on the oracle, whose sequence entry points issue that very operator sequence: loss and the five
+    gradients agree to the last bits of a few reordered float additions."""
+    mark = oracle_lib.mark()
+    T, V, B = 20, 80, 5
+    ids = np.random.default_rng(6).integers(0, V, (T + 1, B))
+    x = np.zeros((T, B, V), np.float32)
+    x[np.arange(T)[:, None], np.arange(B)[None, :], ids[:T]] = 1.0
+    y = ids[1:].astype(np.int32).ravel()
+    res = []
+    for level in (2, 0):
+        m = _model(oracle_lib, "rnn", B)
+        m.use_fused_cells(level)
         loss = m.step(x.ravel(), y, 0.0, update=False)
         res.append((loss, [m.grad(i) for i in range(m.num_params)]))
         m.close(); oracle_lib.reset(mark)
