@@ -219,7 +219,7 @@ def test_predictions_are_bit_exact(libs, math):
         libc.srand(9 + s); mg.step(x, y, 0.0005)
         zo, zg = mo.logits(), mg.logits()
         assert np.array_equal(zo.argmax(1), zg.argmax(1)), "step %d: predictions differ" % s
-        assert_close(zo, zg, FP32_RTOL, "logits")
+        assert_close(zo, zg, FP32_RTOL if math == 0 else 1e-3, "logits")    # TF32: five updates carry the 1e-4 of one step forward (measured up to 1.6e-4)
     mo.close(); mg.close()
 
 
