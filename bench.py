@@ -309,11 +309,12 @@ def main():
     clocks = sampler.stop()
     e2e = BATCH * world * args.steps / (ms_e2e / 1e3)
 
-    # ---- replicas: after all those updates every rank must hold the same parameters, bit for bit
+    # ---- replicas: after all those updates every rank must hold the same trained parameters, bit for bit (batch-norm running
+    #      statistics are each replica's own: the reference has no cross-replica batch norm)
     replicas_identical = None
     if world > 1:
         lib.sync()
-        p = model.slab_params()
+        p = model.trained_params()
         chk = torch.tensor([float(p.astype(np.float64).sum()), float(np.abs(p).astype(np.float64).sum())], dtype=torch.float64, device="cuda")
         lo, hi = chk.clone(), chk.clone()
         dist.all_reduce(lo, op=dist.ReduceOp.MIN); dist.all_reduce(hi, op=dist.ReduceOp.MAX)

@@ -12,6 +12,7 @@ _SIGS = {
     "model_destroy": (None, [ctypes.c_void_p]),
     "model_num_params": (ctypes.c_int, [ctypes.c_void_p]),
     "model_param_count": (ctypes.c_int64, [ctypes.c_void_p, ctypes.c_int]),
+    "model_param_is_state": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int]),
     "model_param_ptr": (ctypes.c_void_p, [ctypes.c_void_p, ctypes.c_int]),
     "model_grad_ptr": (ctypes.c_void_p, [ctypes.c_void_p, ctypes.c_int]),
     "model_slab_count": (ctypes.c_int64, [ctypes.c_void_p]),
@@ -228,6 +229,14 @@ class Model:
 
     def grad(self, i):
         return self._read(self.hp.fn["model_grad_ptr"](self.h, i), self.hp.fn["model_param_count"](self.h, i))
+
+    def param_is_state(self, i):
+        """True for a batch-norm running statistic: updated by each replica from its own batches, never trained or all-reduced."""
+        return bool(self.hp.fn["model_param_is_state"](self.h, i))
+
+    def trained_params(self):
+        """Every trained parameter tensor (the running statistics left out), concatenated."""
+        return np.concatenate([self.param(i) for i in range(self.num_params) if not self.param_is_state(i)])
 
     def slab_params(self):
         return self._read(self.hp.fn["model_slab_params"](self.h), self.slab_count)

@@ -28,7 +28,7 @@ using namespace lantern_host;
 
 namespace {
 
-struct ParamDecl { std::vector<int> shape; int init; float scale; int64_t count; int64_t offset; };
+struct ParamDecl { std::vector<int> shape; int init; float scale; int64_t count; int64_t offset; bool state = false; };   // state: a running statistic, not trained (no gradient, not all-reduced)
 enum { INIT_ZERO = 0, INIT_RAND = 1, INIT_ONE = 2 };
 
 struct Model {
@@ -458,13 +458,13 @@ struct ResNet50 : Model {
   struct ConvBN { int w, gamma, beta, rmean, rvar; };
   struct Block { ConvBN a, b, c, down; bool has_down; int stride; };
   ConvBN stem; std::vector<Block> blocks; int fcw, fcb;
-  std::vector<int> running;   // indices of running-stat tensors (their gradient stays zero)
 
   ConvBN conv_bn(int cin, int cout, int k) {
     ConvBN cb;
     cb.w = declare({cout, cin, k, k}, INIT_RAND, 2.0f * sqrtf(6.0f / (float)(cin * k * k)));
     cb.gamma = declare({cout}, INIT_ONE); cb.beta = declare({cout}, INIT_ZERO);
     cb.rmean = declare({cout}, INIT_ZERO); cb.rvar = declare({cout}, INIT_ONE);
+    decls[cb.rmean].state = decls[cb.rvar].state = true;   // each replica keeps the running statistics of its own batches
     return cb;
   }
   // max_blocks < 16 gives a prefix of the network (stem, max pool, the first max_blocks bottleneck blocks) closed by an
@@ -591,6 +591,7 @@ void HOST_FN(model_destroy)(void* m) {
 }
 int HOST_FN(model_num_params)(void* m) { return (int)((Model*)m)->decls.size(); }
 int64_t HOST_FN(model_param_count)(void* m, int i) { return ((Model*)m)->decls[i].count; }
+int HOST_FN(model_param_is_state)(void* m, int i) { return ((Model*)m)->decls[i].state ? 1 : 0; }   // 1: a batch-norm running statistic
 float* HOST_FN(model_param_ptr)(void* m, int i) { Model* M = (Model*)m; return M->slab_x + M->decls[i].offset; }
 float* HOST_FN(model_grad_ptr)(void* m, int i) { Model* M = (Model*)m; return M->slab_d + M->decls[i].offset; }
 int64_t HOST_FN(model_slab_count)(void* m) { return ((Model*)m)->slab_count; }

@@ -34,14 +34,14 @@ def _data(world):
     return x, y
 
 
-def _gpu_worker(rank, world, out_dir, graph):
+def _gpu_worker(rank, world, out_dir, graph, name="squeezenet", math=0):
     os.environ["NCCL_NVLS_ENABLE"] = "0"        # plain peer transport: nothing stays bound to a multicast object if a rank dies
     import lantern_b200
     from lantern_b200.hosts import HostPrograms
     lib = lantern_b200.load()
     lib.init(rank, 2 << 30)
-    lib.set_math(0)
-    id_path = os.path.join(out_dir, "nccl_id_%d.bin" % int(graph))
+    lib.set_math(math)
+    id_path = os.path.join(out_dir, "nccl_id_%s_%d.bin" % (name, int(graph)))
     buf = ctypes.create_string_buffer(128)
     if rank == 0:
         lib.comm_unique_id(buf)
@@ -57,7 +57,7 @@ def _gpu_worker(rank, world, out_dir, graph):
         buf = ctypes.create_string_buffer(open(id_path, "rb").read(), 128)
     lib.comm_init(rank, world, buf)
     assert lib.comm_world() == world
-    m = HostPrograms(lib).model("squeezenet", SHARD, seed=42)
+    m = HostPrograms(lib).model(name, SHARD, seed=42)
     m.use_graph(bool(graph))
     x, y = _data(world)
     losses = [m.step(x[s, rank * SHARD:(rank + 1) * SHARD].ravel(), y[s, rank * SHARD:(rank + 1) * SHARD], LR) for s in range(STEPS)]
@@ -65,6 +65,8 @@ def _gpu_worker(rank, world, out_dir, graph):
     assert lib.device_status() == 0
     tag = "g%d_r%d" % (int(graph), rank)
     np.save(os.path.join(out_dir, "params_%s.npy" % tag), m.slab_params())
+    np.save(os.path.join(out_dir, "trained_%s.npy" % tag), m.trained_params())
+    np.save(os.path.join(out_dir, "state_%s.npy" % tag), np.concatenate([m.param(i) for i in range(m.num_params) if m.param_is_state(i)] + [np.zeros(0, np.float32)]))
     np.save(os.path.join(out_dir, "grads_%s.npy" % tag), m.slab_grads())
     np.save(os.path.join(out_dir, "losses_%s.npy" % tag), np.array(losses, np.float64))
     m.close(); lib.comm_destroy(); lib.shutdown()
@@ -101,3 +103,22 @@ def test_two_gpus_match_the_oracle_on_the_whole_batch(tmp_path):
         assert np.allclose((l0 + l1) / 2, ref_losses, rtol=1e-4), ((l0 + l1) / 2, ref_losses)
         err = np.abs(p0 - ref).max() / np.abs(ref).max()
         assert err < 5e-4, (graph, err)        # three steps of FP32 rounding in different summation orders (measured 1.6e-4)
+
+
+@pytest.mark.gpu
+@pytest.mark.timeout(900)
+def test_two_gpus_keep_trained_parameters_identical_with_batch_norm(tmp_path):
+    """A program with batch norm (stem + first bottleneck block of ResNet-50) on the tensor-core path, three data-parallel
+    steps, eager and replayed: the trained parameters of the two ranks stay bit-identical (local gradients are summed by
+    atomics in any order, but both ranks apply the same all-reduced sum), while the running statistics are each replica's
+    own (different shards: they differ), as in the reference, which has no cross-replica batch norm."""
+    if _device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    for graph in (0, 1):
+        mp.spawn(_gpu_worker, args=(2, str(tmp_path), graph, "resnet50_prefix", 1), nprocs=2, join=True)
+        t0, t1 = np.load(tmp_path / ("trained_g%d_r0.npy" % graph)), np.load(tmp_path / ("trained_g%d_r1.npy" % graph))
+        assert t0.size > 70000 and np.array_equal(t0, t1), "trained parameters diverged (graph=%d)" % graph
+        s0, s1 = np.load(tmp_path / ("state_g%d_r0.npy" % graph)), np.load(tmp_path / ("state_g%d_r1.npy" % graph))
+        assert s0.size == 2 * (64 + 64 + 64 + 256 + 256) and not np.array_equal(s0, s1)
+        assert not np.load(tmp_path / ("grads_g%d_r0.npy" % graph)).any()
