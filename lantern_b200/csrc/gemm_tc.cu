@@ -596,13 +596,21 @@ __global__ void permute_taps_kernel(const float* __restrict__ w, float* __restri
     out[i] = w[((int64_t)k * C + c) * taps + t];
   }
 }
-// Both per-tap forms in one launch: fwd[tap][k][c] and dgrad[tap][c][k] (the filter cache refreshes a filter once per step).
-__global__ void filter_forms_kernel(const float* __restrict__ w, float* __restrict__ fwd, float* __restrict__ dgrad, int K, int C, int taps, int64_t total) {
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-    { const int c = (int)(i % C); const int64_t t2 = i / C; const int k = (int)(t2 % K); const int t = (int)(t2 / K);
-      fwd[i] = w[((int64_t)k * C + c) * taps + t]; }
-    { const int k = (int)(i % K); const int64_t t2 = i / K; const int c = (int)(t2 % C); const int t = (int)(t2 / C);
-      dgrad[i] = w[((int64_t)k * C + c) * taps + t]; }
+// Both per-tap forms, fwd[tap][k][c] and dgrad[tap][c][k], of several filters in one launch (every filter the optimizer has just written: one launch per step instead of one
+// per 3x3 layer).  Jobs are laid end to end over one flat index; a thread finds its job by a short scan.
+struct FormJob { const float* w; float* fwd; float* dgrad; int K, C, taps; long long begin; };
+constexpr int kFormJobs = 24;
+struct FormJobs { FormJob j[kFormJobs]; int n; long long total; };
+__global__ void filter_forms_multi_kernel(const FormJobs J) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < J.total; i += (long long)gridDim.x * blockDim.x) {
+    int q = 0;
+    while (q + 1 < J.n && i >= J.j[q + 1].begin) ++q;
+    const FormJob& f = J.j[q];
+    const long long l = i - f.begin;
+    { const int c = (int)(l % f.C); const long long t2 = l / f.C; const int k = (int)(t2 % f.K); const int t = (int)(t2 / f.K);
+      f.fwd[l] = f.w[((long long)k * f.C + c) * f.taps + t]; }
+    { const int k = (int)(l % f.K); const long long t2 = l / f.K; const int c = (int)(t2 % f.C); const int t = (int)(t2 / f.C);
+      f.dgrad[l] = f.w[((long long)k * f.C + c) * f.taps + t]; }
   }
 }
 // Filter matrix w[rows][cols] copied with its rows padded by zeros to ld floats (the engine's tensor maps want a row length
@@ -843,6 +851,31 @@ int gemm_tc(const float* a, bool a_kmajor, const float* b, bool b_kmajor, float*
   return rc ? rc : 1;
 }
 
+// ---- channels-last copies of activations ---------------------------------------------------------------------------------------
+// The tap-loop convolutions read act[n][h][w][c].  Without the operand cache (ltb_set_filter_cache) every call makes its own
+// copy in a staging block and gives it back.  With it, a copy made by a forward convolution, or of dy at the start of a
+// convolution's backward call, is kept in a block taken from the far end of the arena (those blocks live until ltb_reset)
+// and found again by address and shape: the weight-gradient of that convolution reads the forward copy of x, and data-grad
+// and weight-grad share one copy of dy.  A copy is dropped when one of the entry points that report their writes
+// (filter_cache_note_write) touches its source, when ltb_free releases the source, and at ltb_reset.
+struct ClCopy { const float* src; int n_img, chan, pix; float* cl; int geom; };   // geom 0: channels-last copy; else the key of an unfolded matrix (unfold_key)
+static std::vector<ClCopy> cl_cache;
+void cl_cache_clear() { cl_cache.clear(); }
+void cl_cache_drop_from(const void* p) {                   // ltb_free: everything at or above p is gone
+  for (size_t i = 0; i < cl_cache.size();) { if ((const void*)cl_cache[i].src >= p) { cl_cache[i] = cl_cache.back(); cl_cache.pop_back(); } else ++i; }
+}
+static float* cl_lookup(const float* src, int n_img, int chan, int pix) {
+  for (auto& e : cl_cache) if (e.src == src && e.n_img == n_img && e.chan == chan && e.pix == pix && e.geom == 0) return e.cl;
+  return nullptr;
+}
+// The unfolded matrix col[n][(c, r, s)][p] of a convolution input (the forward pass of a strided or 3-channel convolution
+// makes it, the weight gradient of the same convolution reads it again): kept and found like the channels-last copies.
+static int unfold_key(const ConvDims& d) { return 1 + ((((((d.R * 8 + d.S) * 4 + d.sh) * 4 + d.sw) * 8 + d.ph) * 8 + d.pw) * 64 + d.W % 64); }
+static float* unfold_lookup(const float* src, const ConvDims& d) {
+  const int ck = d.C * d.R * d.S, pix = d.oH * d.oW, key = unfold_key(d);
+  for (auto& e : cl_cache) if (e.src == src && e.n_img == d.N && e.chan == ck && e.pix == pix && e.geom == key) return e.cl;
+  return nullptr;
+}
 static int launch_unfold(const float* x, float* col, const ConvDims& d) {
   const int pix = d.oH * d.oW;
   int tpp = 32; while (tpp < pix && tpp < 256) tpp <<= 1;      // threads per input plane: a power of two in [32, 256]
@@ -892,6 +925,14 @@ static int stage_activation(const float* src, bool unfold, const ConvDims& d, in
   *rows = tc_conv_needs_rows(pix); *temp = nullptr; *temp_floats = 0; *op = src;
   if (!unfold && (!*rows || pix == 1)) return LTB_OK;         // [N][chan][1] already is the row matrix [N][chan]
   const size_t n = (size_t)d.N * chan * pix;
+  if (unfold && !*rows && g.filter_cache && !(g.tune & 4)) {         // keep it for the weight gradient of the same convolution
+    if (float* kept = (float*)step_alloc(n * 4)) {
+      int rc = launch_unfold(src, kept, d); if (rc) return rc;
+      cl_cache.push_back(ClCopy{src, d.N, chan, pix, kept, unfold_key(d)});
+      *op = kept;
+      return LTB_OK;
+    }
+  }
   float* buf = temp_alloc(n);
   if (!buf) return 1;
   *temp = buf; *temp_floats = n; *op = buf;
@@ -915,23 +956,6 @@ static bool taps_geometry(const ConvDims& d, TcConvGeom& gm) {
   gm.n_img = d.N; gm.C = d.C; gm.H = d.H; gm.W = d.W; gm.K = d.K; gm.R = d.R; gm.S = d.S; gm.ph = d.ph; gm.pw = d.pw; gm.oH = d.oH; gm.oW = d.oW;
   return true;
 }
-// ---- channels-last copies of activations ---------------------------------------------------------------------------------------
-// The tap-loop convolutions read act[n][h][w][c].  Without the operand cache (ltb_set_filter_cache) every call makes its own
-// copy in a staging block and gives it back.  With it, a copy made by a forward convolution, or of dy at the start of a
-// convolution's backward call, is kept in a block taken from the far end of the arena (those blocks live until ltb_reset)
-// and found again by address and shape: the weight-gradient of that convolution reads the forward copy of x, and data-grad
-// and weight-grad share one copy of dy.  A copy is dropped when one of the entry points that report their writes
-// (filter_cache_note_write) touches its source, when ltb_free releases the source, and at ltb_reset.
-struct ClCopy { const float* src; int n_img, chan, pix; float* cl; };
-static std::vector<ClCopy> cl_cache;
-void cl_cache_clear() { cl_cache.clear(); }
-void cl_cache_drop_from(const void* p) {                   // ltb_free: everything at or above p is gone
-  for (size_t i = 0; i < cl_cache.size();) { if ((const void*)cl_cache[i].src >= p) { cl_cache[i] = cl_cache.back(); cl_cache.pop_back(); } else ++i; }
-}
-static float* cl_lookup(const float* src, int n_img, int chan, int pix) {
-  for (auto& e : cl_cache) if (e.src == src && e.n_img == n_img && e.chan == chan && e.pix == pix) return e.cl;
-  return nullptr;
-}
 static int channels_last_into(const float* src, int n_img, int chan, int pix, float* out) {
   const size_t n = (size_t)n_img * chan * pix;
   const int pt = pix < 32 ? pix : 32;
@@ -951,8 +975,8 @@ static int channels_last(const float* src, int n_img, int chan, int pix, float**
   if (keep && g.filter_cache && !(g.tune & 4)) {
     if (float* kept = (float*)step_alloc(n * 4)) {
       int rc = channels_last_into(src, n_img, chan, pix, kept); if (rc) return rc;
-      for (size_t i = 0; i < cl_cache.size(); ++i) if (cl_cache[i].src == src) { cl_cache[i] = cl_cache.back(); cl_cache.pop_back(); break; }
-      cl_cache.push_back(ClCopy{src, n_img, chan, pix, kept});
+      for (size_t i = 0; i < cl_cache.size(); ++i) if (cl_cache[i].src == src && cl_cache[i].geom == 0) { cl_cache[i] = cl_cache.back(); cl_cache.pop_back(); break; }
+      cl_cache.push_back(ClCopy{src, n_img, chan, pix, kept, 0});
       *out = kept;
       return LTB_OK;
     }
@@ -963,8 +987,8 @@ static int channels_last(const float* src, int n_img, int chan, int pix, float**
 }
 // ---- filter cache (ltb_set_filter_cache) ------------------------------------------------------------------------------------
 // The per-tap forms of a filter are needed twice per step (forward and data-grad) and change once per step (the optimizer).
-// With the cache on they live in private device memory, keyed by the filter's address and shape, and are refreshed by ONE
-// launch at the first use after a write that overlaps the filter (filter_cache_note_write, called by the optimizer, transfer,
+// With the cache on they live in private device memory, keyed by the filter's address and shape, and are refreshed -- all
+// stale filters together, in ONE launch -- at the first use after a write that overlaps a filter (filter_cache_note_write, called by the optimizer, transfer,
 // fill and in-place entry points with their destination; a replayed step and ltb_params_changed mark every filter).  A filter first seen while a step is being recorded takes
 // the uncached path (no allocation inside a capture).
 struct FilterForms { const float* w; int K, C, taps; float *fwd, *dgrad; bool stale; };
@@ -1006,8 +1030,23 @@ static int tap_matrices(const float* w, const ConvDims& d, int by_c, float** out
   if (g.filter_cache) {
     if (FilterForms* e = filter_cache_entry(w, d)) {
       if (e->stale) {
-        LTB_LAUNCH(filter_forms_kernel, grid_for((int64_t)n, 256), 256, 0, w, e->fwd, e->dgrad, d.K, d.C, d.R * d.S, (int64_t)n);
-        e->stale = false;
+        // every stale filter at once: after an optimizer step all of them are, and their values are final until the next write
+        // (which marks them again), so the forms of the layers still to come are made here too
+        FormJobs jobs; jobs.n = 0; jobs.total = 0;
+        auto flush = [&]() -> int {
+          if (jobs.n == 0) return LTB_OK;
+          LTB_LAUNCH(filter_forms_multi_kernel, grid_for((int64_t)jobs.total, 256), 256, 0, jobs);
+          jobs.n = 0; jobs.total = 0;
+          return LTB_OK;
+        };
+        for (auto& o : filter_cache) {
+          if (!o.stale) continue;
+          if (jobs.n == kFormJobs) { int rc = flush(); if (rc) return rc; }
+          jobs.j[jobs.n++] = FormJob{o.w, o.fwd, o.dgrad, o.K, o.C, o.taps, jobs.total};
+          jobs.total += (long long)o.K * o.C * o.taps;
+          o.stale = false;
+        }
+        int rc = flush(); if (rc) return rc;
       }
       *out = by_c ? e->dgrad : e->fwd; *floats = 0;
       return LTB_OK;
@@ -1162,9 +1201,12 @@ int conv_wgrad_tc(const float* x, const float* dy, float* dw, const ConvDims& d)
   { int t = conv_wgrad_taps(x, dy, dw, d); if (t != 0) return t; }
   const float* xin = x; float* col = nullptr; const size_t n = (size_t)d.N * ck * pix;
   if (!is_pointwise(d)) {
-    col = temp_alloc(n); if (!col) return 0;
-    int rc0 = launch_unfold(x, col, d); if (rc0) return rc0;
-    xin = col;
+    if (float* kept = unfold_lookup(x, d)) xin = kept;               // forward left its unfolded matrix behind
+    else {
+      col = temp_alloc(n); if (!col) return 0;
+      int rc0 = launch_unfold(x, col, d); if (rc0) return rc0;
+      xin = col;
+    }
   }
   // the probe above used dy in place of x: the caller's x may still be declined (a view that is not 16-byte aligned)
   if (!tc_plan_conv_wgrad(p, xin, dy, dw, d.N, ck, d.K, pix, g.sm_count)) { if (col) temp_free(col, n); return 0; }
