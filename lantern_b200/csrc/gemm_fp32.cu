@@ -85,19 +85,21 @@ struct MatStore {
 // ---- skinny products: one extent of 16 or less (a 10-way classifier and its gradients) -----------------------------------
 // The 64 x 64 tiles above leave such products to one or two CTAs walking a long K; these three kernels give every output
 // (or every output column) its own thread or warp instead.
-// N <= 16, A and B both contiguous along k: a block of four warps per (row m, K split), each warp a quarter of the split,
-// lanes stride over k.  With more than one split (a long K and few rows) the partial results are added atomically.
+// N <= 16, A and B both contiguous along k: a block of sixteen warps per row m, each warp a sixteenth of K, lanes stride over
+// k (at K = 2048 a lane makes four independent iterations: the loads of a row are all in flight at once).  The warps' sums are
+// added in warp order by one thread per column: the same bits on every run.
+constexpr int kSkinnyNWarps = 16;
 template <bool ACC>
-__global__ void skinny_n_kernel(const float* __restrict__ a, int64_t sam, const float* __restrict__ b, int64_t sbn, float* c, int64_t scm, int64_t scn,
-                                int N, int K, float alpha) {
-  __shared__ float part[4][16];
+__global__ void __launch_bounds__(kSkinnyNWarps * 32) skinny_n_kernel(const float* __restrict__ a, int64_t sam, const float* __restrict__ b, int64_t sbn, float* c,
+                                                                      int64_t scm, int64_t scn, int N, int K, float alpha) {
+  __shared__ float part[kSkinnyNWarps][16];
   const int m = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int quarter = blockIdx.y * 4 + warp, quarters = gridDim.y * 4;
-  const int k0 = (int)((int64_t)K * quarter / quarters), k1 = (int)((int64_t)K * (quarter + 1) / quarters);
+  const int k0 = (int)((int64_t)K * warp / kSkinnyNWarps), k1 = (int)((int64_t)K * (warp + 1) / kSkinnyNWarps);
   float acc[16];
 #pragma unroll
   for (int n = 0; n < 16; ++n) acc[n] = 0.0f;
   const float* ar = a + (int64_t)m * sam;
+#pragma unroll 4
   for (int k = k0 + lane; k < k1; k += 32) {
     const float av = ar[k];
 #pragma unroll
@@ -112,9 +114,12 @@ __global__ void skinny_n_kernel(const float* __restrict__ a, int64_t sam, const 
   __syncthreads();
   if (threadIdx.x < N) {
     const int n = threadIdx.x;
-    const float v = alpha * ((part[0][n] + part[1][n]) + (part[2][n] + part[3][n]));
+    float v = 0.0f;
+#pragma unroll
+    for (int w = 0; w < kSkinnyNWarps; ++w) v += part[w][n];
+    v *= alpha;
     float* q = c + (int64_t)m * scm + (int64_t)n * scn;
-    if (gridDim.y > 1) atomicAdd(q, v); else *q = ACC ? *q + v : v;
+    *q = ACC ? *q + v : v;
   }
 }
 // K <= 16: a thread per output element.
@@ -130,30 +135,41 @@ __global__ void skinny_k_kernel(const float* __restrict__ a, int64_t sam, int64_
     *q = ACC ? *q + alpha * v : alpha * v;
   }
 }
-// M <= 16: a thread per output column n (and K split blockIdx.y), all rows in registers; B is read once, coalesced when
-// contiguous along n.  A lane's loop over k is a chain of dependent-latency steps, so a long K is split over blockIdx.y and
-// the partial columns are added atomically (the classifier's weight gradient, 10 x 2048 over a batch of 128, took 89 us as
-// sixteen blocks walking all of K).
+// M <= 16: a block is 32 output columns x 8 slices of K (blockIdx.y splits K further when it is long); a thread keeps all
+// rows of its column in registers over its slice, B is read once, coalesced when contiguous along n.  The slices of a block
+// are added in slice order through shared memory (a lane's loop over k is a chain of dependent steps: the classifier's weight
+// gradient, 10 x 2048 over a batch of 128, took 89 us as sixteen blocks walking all of K, 19 us as sixteen slabs and a second
+// launch).  With blockIdx.y > 1 a block's sum goes to its own slab and skinny_sum_kernel adds the slabs in order.
+constexpr int kSkinnyMSlices = 8;
 template <bool ACC>
-__global__ void skinny_m_kernel(const float* __restrict__ a, int64_t sam, int64_t sak, const float* __restrict__ b, int64_t sbk, int64_t sbn,
-                                float* c, int64_t scm, int64_t scn, int M, int N, int K, float alpha, float* part) {
-  const int n = blockIdx.x * blockDim.x + threadIdx.x;
-  if (n >= N) return;
-  const int k0 = (int)((int64_t)K * blockIdx.y / gridDim.y), k1 = (int)((int64_t)K * (blockIdx.y + 1) / gridDim.y);
+__global__ void __launch_bounds__(32 * kSkinnyMSlices) skinny_m_kernel(const float* __restrict__ a, int64_t sam, int64_t sak, const float* __restrict__ b, int64_t sbk,
+                                                                       int64_t sbn, float* c, int64_t scm, int64_t scn, int M, int N, int K, float alpha, float* part) {
+  __shared__ float sums[kSkinnyMSlices][16][33];
+  const int n = blockIdx.x * 32 + threadIdx.x, slice = threadIdx.y;
+  const int q0 = (int)((int64_t)K * blockIdx.y / gridDim.y), q1 = (int)((int64_t)K * (blockIdx.y + 1) / gridDim.y);
+  const int k0 = q0 + (int)((int64_t)(q1 - q0) * slice / kSkinnyMSlices), k1 = q0 + (int)((int64_t)(q1 - q0) * (slice + 1) / kSkinnyMSlices);
   float acc[16];
 #pragma unroll
   for (int m = 0; m < 16; ++m) acc[m] = 0.0f;
+  if (n < N) {
 #pragma unroll 4
-  for (int k = k0; k < k1; ++k) {
-    const float bv = b[(int64_t)k * sbk + (int64_t)n * sbn];
+    for (int k = k0; k < k1; ++k) {
+      const float bv = b[(int64_t)k * sbk + (int64_t)n * sbn];
 #pragma unroll
-    for (int m = 0; m < 16; ++m) if (m < M) acc[m] += a[(int64_t)m * sam + (int64_t)k * sak] * bv;
+      for (int m = 0; m < 16; ++m) if (m < M) acc[m] += a[(int64_t)m * sam + (int64_t)k * sak] * bv;
+    }
   }
 #pragma unroll
-  for (int m = 0; m < 16; ++m) if (m < M) {
+  for (int m = 0; m < 16; ++m) sums[slice][m][threadIdx.x] = acc[m];
+  __syncthreads();
+  if (n >= N) return;
+  for (int m = slice; m < M; m += kSkinnyMSlices) {                              // the rows are dealt out to the slices' threads
+    float v = 0.0f;
+#pragma unroll
+    for (int z = 0; z < kSkinnyMSlices; ++z) v += sums[z][m][threadIdx.x];
     float* q = c + (int64_t)m * scm + (int64_t)n * scn;
-    if (part) part[((int64_t)blockIdx.y * M + m) * N + n] = acc[m];              // K was split: this block's share goes to its own slab
-    else *q = ACC ? *q + alpha * acc[m] : alpha * acc[m];
+    if (part) part[((int64_t)blockIdx.y * M + m) * N + n] = v;                   // K was split over blocks too: this block's share goes to its own slab
+    else *q = ACC ? *q + alpha * v : alpha * v;
   }
 }
 // c[m][n] (+)= alpha * (part[0][m][n] + part[1][m][n] + ...), in that order: the second half of skinny_m_kernel when K is split.
@@ -171,27 +187,26 @@ static int skinny_gemm(const float* a, int64_t sam, int64_t sak, const float* b,
                        int M, int N, int K, float alpha, bool accumulate, bool* taken) {
   *taken = true;
   if (N <= 16 && sak == 1 && sbk == 1 && K >= 128 && M <= 65535) {
-    // one block per row, its four warps share K and are added in a fixed order: the same bits on every run (splitting K over
+    // one block per row, its warps share K and are added in a fixed order: the same bits on every run (splitting K over
     // more blocks would need atomics, whose order changes from run to run)
-    const int ks = 1;
-    if (accumulate) LTB_LAUNCH(skinny_n_kernel<true>, dim3(M, ks), 128, 0, a, sam, b, sbn, c, scm, scn, N, K, alpha);
-    else LTB_LAUNCH(skinny_n_kernel<false>, dim3(M, ks), 128, 0, a, sam, b, sbn, c, scm, scn, N, K, alpha);
+    if (accumulate) LTB_LAUNCH(skinny_n_kernel<true>, dim3(M), kSkinnyNWarps * 32, 0, a, sam, b, sbn, c, scm, scn, N, K, alpha);
+    else LTB_LAUNCH(skinny_n_kernel<false>, dim3(M), kSkinnyNWarps * 32, 0, a, sam, b, sbn, c, scm, scn, N, K, alpha);
   } else if (K <= 16) {
     const unsigned grid = (unsigned)grid_for((int64_t)M * N, 256);
     if (accumulate) LTB_LAUNCH(skinny_k_kernel<true>, grid, 256, 0, a, sam, sak, b, sbk, sbn, c, scm, scn, M, N, K, alpha);
     else LTB_LAUNCH(skinny_k_kernel<false>, grid, 256, 0, a, sam, sak, b, sbk, sbn, c, scm, scn, M, N, K, alpha);
   } else if (M <= 16 && N >= 256 && K <= 4096) {
-    const unsigned gx = (unsigned)ceil_div(N, 128);
-    // a lane's loop over k is a chain of dependent steps: a long K is split over blockIdx.y, every split writes its share
-    // into a slab of the library's workspace and a second small launch adds the slabs in order (no atomics: same bits every run)
-    int ks = (int)ceil_div(2 * g.sm_count, (int64_t)gx);
-    if (ks > K / 8) ks = K / 8;
+    const unsigned gx = (unsigned)ceil_div(N, 32);
+    // a thread's loop over k is a chain of dependent steps: beyond 64 steps per in-block slice K is also split over blockIdx.y,
+    // every such split writes its share into a slab of the library's workspace and a second small launch adds the slabs in
+    // order (no atomics: same bits every run)
+    int ks = (int)ceil_div(K, 64 * kSkinnyMSlices);
     const size_t room = g.cur_scratch_bytes() / ((size_t)M * N * sizeof(float));
     if ((size_t)ks > room) ks = (int)room;
     if (ks < 1) ks = 1;
     float* part = ks > 1 ? g.cur_scratch() : nullptr;
-    if (accumulate) LTB_LAUNCH(skinny_m_kernel<true>, dim3(gx, ks), 128, 0, a, sam, sak, b, sbk, sbn, c, scm, scn, M, N, K, alpha, part);
-    else LTB_LAUNCH(skinny_m_kernel<false>, dim3(gx, ks), 128, 0, a, sam, sak, b, sbk, sbn, c, scm, scn, M, N, K, alpha, part);
+    if (accumulate) LTB_LAUNCH(skinny_m_kernel<true>, dim3(gx, ks), dim3(32, kSkinnyMSlices), 0, a, sam, sak, b, sbk, sbn, c, scm, scn, M, N, K, alpha, part);
+    else LTB_LAUNCH(skinny_m_kernel<false>, dim3(gx, ks), dim3(32, kSkinnyMSlices), 0, a, sam, sak, b, sbk, sbn, c, scm, scn, M, N, K, alpha, part);
     if (part) {
       const unsigned gr = (unsigned)grid_for((int64_t)M * N, 256);
       if (accumulate) LTB_LAUNCH(skinny_sum_kernel<true>, gr, 256, 0, (const float*)part, ks, c, scm, scn, M, N, alpha);

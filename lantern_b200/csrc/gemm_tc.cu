@@ -547,6 +547,33 @@ __global__ void unfold_to_rows_kernel(const float* __restrict__ x, float* __rest
     col[i] = (ih >= 0 && ih < d.H && iw >= 0 && iw < d.W) ? x[(((int64_t)n * d.C + c) * d.H + ih) * d.W + iw] : 0.0f;
   }
 }
+// The same matrix made by tiles: a CTA takes 32 input channels of one image through shared memory (their planes are one
+// contiguous run of x) and writes, for every output pixel, the run of 32 x R*S consecutive floats that those channels own in
+// the pixel's row.  For input planes of at most 256 pixels (the strided layers of the last stages: element by element the
+// copy of 19 MB took 41 us).
+constexpr int kUnfoldTilePix = 256;
+__global__ void __launch_bounds__(256) unfold_to_rows_tiled_kernel(const float* __restrict__ x, float* __restrict__ col, ConvDims d) {
+  __shared__ float plane[32][kUnfoldTilePix + 1];
+  const int n = blockIdx.y, c0 = blockIdx.x * 32, cn = min(32, d.C - c0);
+  const int hw = d.H * d.W, pix = d.oH * d.oW, rs = d.R * d.S, ck = d.C * rs;
+  const float* src = x + ((int64_t)n * d.C + c0) * hw;
+  for (int i = threadIdx.x; i < cn * hw; i += 256) { const int cc = i / hw; plane[cc][i - cc * hw] = src[i]; }
+  __syncthreads();
+  // a thread owns (channel, tap) and walks the output pixels; when the 32 channels have fewer than 256 (channel, tap) pairs
+  // (a 1x1 convolution) the block's threads also share the pixels
+  const int per = cn * rs, lanes = per < 256 ? per : 256, ppar = 256 / lanes;
+  const int pl = threadIdx.x / lanes, il = threadIdx.x - pl * lanes;
+  if (pl >= ppar) return;
+  for (int i2 = il; i2 < per; i2 += lanes) {
+    const int cc = i2 / rs, t = i2 - cc * rs, r = t / d.S, sx = t - r * d.S;
+    float* dst = col + (int64_t)n * pix * ck + (int64_t)c0 * rs + i2;
+    for (int p = pl; p < pix; p += ppar) {
+      const int ho = p / d.oW, wo = p - ho * d.oW;
+      const int ih = ho * d.sh - d.ph + r, iw = wo * d.sw - d.pw + sx;
+      dst[(int64_t)p * ck] = (ih >= 0 && ih < d.H && iw >= 0 && iw < d.W) ? plane[cc][ih * d.W + iw] : 0.0f;
+    }
+  }
+}
 // [N][chan][pix] -> row matrix [N*pix][chan] (K-major operand for images smaller than one 128-byte row of pixels).
 __global__ void to_rows_kernel(const float* __restrict__ src, float* __restrict__ dst, int chan, int pix, int64_t total) {
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
@@ -596,21 +623,46 @@ __global__ void permute_taps_kernel(const float* __restrict__ w, float* __restri
     out[i] = w[((int64_t)k * C + c) * taps + t];
   }
 }
-// Both per-tap forms, fwd[tap][k][c] and dgrad[tap][c][k], of several filters in one launch (every filter the optimizer has just written: one launch per step instead of one
-// per 3x3 layer).  Jobs are laid end to end over one flat index; a thread finds its job by a short scan.
-struct FormJob { const float* w; float* fwd; float* dgrad; int K, C, taps; long long begin; };
+// Both per-tap forms, fwd[tap][k][c] and dgrad[tap][c][k], of several filters in one launch (every filter the optimizer has
+// just written: one launch per step instead of one per 3x3 layer).  A CTA takes a tile of 32 output channels x 32 input
+// channels x all taps of one filter through shared memory: the 32 x (32 taps) floats of a tile are contiguous runs of w, and
+// both forms leave as runs of 32 consecutive floats (read element by element, w's stride of `taps` floats between
+// neighbouring channels made this copy of 45 MB take 137 us).  Jobs are laid end to end over the tile index.
+struct FormJob { const float* w; float* fwd; float* dgrad; int K, C, taps; int begin; };    // begin: first tile of this job
 constexpr int kFormJobs = 24;
-struct FormJobs { FormJob j[kFormJobs]; int n; long long total; };
-__global__ void filter_forms_multi_kernel(const FormJobs J) {
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < J.total; i += (long long)gridDim.x * blockDim.x) {
-    int q = 0;
-    while (q + 1 < J.n && i >= J.j[q + 1].begin) ++q;
-    const FormJob& f = J.j[q];
-    const long long l = i - f.begin;
-    { const int c = (int)(l % f.C); const long long t2 = l / f.C; const int k = (int)(t2 % f.K); const int t = (int)(t2 / f.K);
-      f.fwd[l] = f.w[((long long)k * f.C + c) * f.taps + t]; }
-    { const int k = (int)(l % f.K); const long long t2 = l / f.K; const int c = (int)(t2 % f.C); const int t = (int)(t2 / f.C);
-      f.dgrad[l] = f.w[((long long)k * f.C + c) * f.taps + t]; }
+struct FormJobs { FormJob j[kFormJobs]; int n; int total; };
+constexpr int kFormTaps = 9;                                   // filters with more taps go element by element inside their tile
+__global__ void __launch_bounds__(256) filter_forms_multi_kernel(const FormJobs J) {
+  __shared__ float tile[32][32 * kFormTaps + 1];
+  int q = 0;
+  while (q + 1 < J.n && (int)blockIdx.x >= J.j[q + 1].begin) ++q;
+  const FormJob& f = J.j[q];
+  const int K = f.K, C = f.C, taps = f.taps;
+  const int ctiles = (C + 31) / 32, id = (int)blockIdx.x - f.begin;
+  const int k0 = (id / ctiles) * 32, c0 = (id % ctiles) * 32;
+  const int kn = min(32, K - k0), cn = min(32, C - c0);
+  if (taps > kFormTaps) {
+    for (int i = threadIdx.x; i < kn * cn * taps; i += 256) {
+      const int t = i % taps, cc = (i / taps) % cn, kk = i / (taps * cn);
+      const float v = f.w[((long long)(k0 + kk) * C + c0 + cc) * taps + t];
+      f.fwd[((long long)t * K + k0 + kk) * C + c0 + cc] = v;
+      f.dgrad[((long long)t * C + c0 + cc) * K + k0 + kk] = v;
+    }
+    return;
+  }
+  const int run = cn * taps;                                   // floats of one output channel's row inside the tile
+  for (int i = threadIdx.x; i < kn * run; i += 256) {
+    const int kk = i / run, r = i - kk * run;
+    tile[kk][r] = f.w[((long long)(k0 + kk) * C + c0) * taps + r];
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < taps * kn * cn; i += 256) {    // fwd[t][k][c]: consecutive threads, consecutive c
+    const int cc = i % cn, kk = (i / cn) % kn, t = i / (cn * kn);
+    f.fwd[((long long)t * K + k0 + kk) * C + c0 + cc] = tile[kk][cc * taps + t];
+  }
+  for (int i = threadIdx.x; i < taps * cn * kn; i += 256) {    // dgrad[t][c][k]: consecutive threads, consecutive k
+    const int kk = i % kn, cc = (i / kn) % cn, t = i / (kn * cn);
+    f.dgrad[((long long)t * C + c0 + cc) * K + k0 + kk] = tile[kk][cc * taps + t];
   }
 }
 // Filter matrix w[rows][cols] copied with its rows padded by zeros to ld floats (the engine's tensor maps want a row length
@@ -937,7 +989,8 @@ static int stage_activation(const float* src, bool unfold, const ConvDims& d, in
   if (!buf) return 1;
   *temp = buf; *temp_floats = n; *op = buf;
   if (unfold) {
-    if (*rows) LTB_LAUNCH(unfold_to_rows_kernel, grid_for((int64_t)n, 256), 256, 0, src, buf, d, (int64_t)n);
+    if (*rows && d.H * d.W <= kUnfoldTilePix && d.N <= 65535) LTB_LAUNCH(unfold_to_rows_tiled_kernel, dim3((unsigned)ceil_div(d.C, 32), (unsigned)d.N), 256, 0, src, buf, d);
+    else if (*rows) LTB_LAUNCH(unfold_to_rows_kernel, grid_for((int64_t)n, 256), 256, 0, src, buf, d, (int64_t)n);
     else { int rc = launch_unfold(src, buf, d); if (rc) return rc; }
   } else {
     const int pt = pix < 32 ? pix : 32;
@@ -1035,7 +1088,7 @@ static int tap_matrices(const float* w, const ConvDims& d, int by_c, float** out
         FormJobs jobs; jobs.n = 0; jobs.total = 0;
         auto flush = [&]() -> int {
           if (jobs.n == 0) return LTB_OK;
-          LTB_LAUNCH(filter_forms_multi_kernel, grid_for((int64_t)jobs.total, 256), 256, 0, jobs);
+          LTB_LAUNCH(filter_forms_multi_kernel, (unsigned)jobs.total, 256, 0, jobs);
           jobs.n = 0; jobs.total = 0;
           return LTB_OK;
         };
@@ -1043,7 +1096,7 @@ static int tap_matrices(const float* w, const ConvDims& d, int by_c, float** out
           if (!o.stale) continue;
           if (jobs.n == kFormJobs) { int rc = flush(); if (rc) return rc; }
           jobs.j[jobs.n++] = FormJob{o.w, o.fwd, o.dgrad, o.K, o.C, o.taps, jobs.total};
-          jobs.total += (long long)o.K * o.C * o.taps;
+          jobs.total += (int)(ceil_div(o.K, 32) * ceil_div(o.C, 32));
           o.stale = false;
         }
         int rc = flush(); if (rc) return rc;
@@ -1153,14 +1206,25 @@ int conv_fwd_tc(const float* x, const float* w, const float* bias, float* y, con
   if (!tc_plan_conv_fwd(p, y /* any aligned pointer: eligibility only */, rows, y, ldw, bias, y, d.N, ck, d.K, pix, g.sm_count)) return 0;
   { int t = conv_fwd_taps(x, w, bias, y, d); if (t != 0) return t; }      // the tap-loop form when the shape allows it
   // Small images (4 or 16 pixels) of a 1x1 convolution: the kernel collects the activation itself (no row copy first).
-  const bool gathered = rows && is_pointwise(d) && pix > 1 && !(g.tune & 1) && tc_gather_possible(x, ck, pix);
-  const float* op = x; bool r2; float* temp = nullptr; size_t tn = 0;
-  int rc = gathered ? LTB_OK : stage_activation(x, !is_pointwise(d), d, ck, pix, &op, &r2, &temp, &tn);
+  bool gathered = rows && is_pointwise(d) && pix > 1 && !(g.tune & 1) && tc_gather_possible(x, ck, pix);
+  const float* op = x; const float* gsrc = x; bool r2; float* temp = nullptr; size_t tn = 0;
+  int rc = LTB_OK;
+  // Small images of a strided or 3x3 convolution: unfold into col[n][(c, r, s)][p] -- the layout the weight gradient of this
+  // convolution reads, so the matrix is kept for it -- and let the kernel collect its rows from there like those of a 1x1.
+  if (!gathered && rows && !is_pointwise(d) && pix > 1 && !(g.tune & 1) && g.filter_cache && !(g.tune & 4) && tc_gather_possible(y, ck, pix)) {
+    float* kept = unfold_lookup(x, d);
+    if (!kept && (kept = (float*)step_alloc((size_t)d.N * ck * pix * 4)) != nullptr) {
+      rc = launch_unfold(x, kept, d); if (rc) return rc;
+      cl_cache.push_back(ClCopy{x, d.N, ck, pix, kept, unfold_key(d)});
+    }
+    if (kept) { gathered = true; op = gsrc = kept; }
+  }
+  if (!gathered) rc = stage_activation(x, !is_pointwise(d), d, ck, pix, &op, &r2, &temp, &tn);
   if (rc) return rc < 0 ? rc : 0;
   float* wtemp; size_t wn; const float* wp;
   rc = padded_filter(w, d.K, ck, ldw, &wp, &wtemp, &wn);
   const bool ok = !rc && wp && tc_plan_conv_fwd(p, op, rows, wp, ldw, bias, y, d.N, ck, d.K, pix, g.sm_count);
-  if (ok && gathered) tc_plan_gather(p, x, d.N, ck, pix);
+  if (ok && gathered) tc_plan_gather(p, gsrc, d.N, ck, pix);
   if (ok) rc = launch_plan(p, gathered ? "tc_gemm_kernel[conv_fwd gather]" : "tc_gemm_kernel[conv_fwd]");
   if (wtemp) temp_free(wtemp, wn);
   if (temp) temp_free(temp, tn);
