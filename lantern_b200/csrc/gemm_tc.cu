@@ -930,7 +930,7 @@ static float* unfold_lookup(const float* src, const ConvDims& d) {
 }
 static int launch_unfold(const float* x, float* col, const ConvDims& d) {
   const int pix = d.oH * d.oW;
-  int tpp = 32; while (tpp < pix && tpp < 256) tpp <<= 1;      // threads per input plane: a power of two in [32, 256]
+  int tpp = 4; while (tpp < pix && tpp < 256) tpp <<= 1;       // threads per input plane: a power of two in [4, 256] (4 x 4 and 2 x 2 outputs leave no lane idle)
   const int ppb = 256 / tpp;
   const int64_t planes = (int64_t)d.N * d.C;
   LTB_LAUNCH(unfold_rows_kernel, grid_for(ceil_div(planes, ppb) * 256, 256, 16), 256, 0, x, col, d, ppb, tpp);
