@@ -651,18 +651,20 @@ __global__ void __launch_bounds__(256) filter_forms_multi_kernel(const FormJobs 
     return;
   }
   const int run = cn * taps;                                   // floats of one output channel's row inside the tile
-  for (int i = threadIdx.x; i < kn * run; i += 256) {
-    const int kk = i / run, r = i - kk * run;
-    tile[kk][r] = f.w[((long long)(k0 + kk) * C + c0) * taps + r];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int kk = warp; kk < kn; kk += 8) {                      // a warp per row of the tile: no index arithmetic per element
+    const float* src = f.w + ((long long)(k0 + kk) * C + c0) * taps;
+    for (int r = lane; r < run; r += 32) tile[kk][r] = src[r];
   }
   __syncthreads();
-  for (int i = threadIdx.x; i < taps * kn * cn; i += 256) {    // fwd[t][k][c]: consecutive threads, consecutive c
-    const int cc = i % cn, kk = (i / cn) % kn, t = i / (cn * kn);
-    f.fwd[((long long)t * K + k0 + kk) * C + c0 + cc] = tile[kk][cc * taps + t];
+  // both forms leave as rows of up to 32 consecutive floats, a warp per row: fwd[t][k][c0 ..] and dgrad[t][c][k0 ..]
+  for (int row = warp; row < taps * kn; row += 8) {
+    const int t = row / kn, kk = row - t * kn;
+    if (lane < cn) f.fwd[((long long)t * K + k0 + kk) * C + c0 + lane] = tile[kk][lane * taps + t];
   }
-  for (int i = threadIdx.x; i < taps * cn * kn; i += 256) {    // dgrad[t][c][k]: consecutive threads, consecutive k
-    const int kk = i % kn, cc = (i / kn) % cn, t = i / (kn * cn);
-    f.dgrad[((long long)t * C + c0 + cc) * K + k0 + kk] = tile[kk][cc * taps + t];
+  for (int row = warp; row < taps * cn; row += 8) {
+    const int t = row / cn, cc = row - t * cn;
+    if (lane < kn) f.dgrad[((long long)t * C + c0 + cc) * K + k0 + lane] = tile[lane][cc * taps + t];
   }
 }
 // Filter matrix w[rows][cols] copied with its rows padded by zeros to ld floats (the engine's tensor maps want a row length
