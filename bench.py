@@ -70,6 +70,9 @@ def hbm_bound_bytes(batch):
       bn_bwd*        batch-norm backward; where an in-place ReLU gradient joined it the kernel also reads the ReLU output
                      and writes the masked gradient back                  x, dy, dx r/w (+ y, dy w)     16 (24) B / element
       relu_add_grad  ReLU gradient + residual-add gradient                y, d r/w, da r/w, db r/w      28 B / element
+                     Gradient buffers of 2^20 elements and more are not zero-filled but written by the first operator that
+                     would add into them (ltb_grad_unset: the host program's default), so for those tensors dx, da and db
+                     are written only: 12 (20) and 20 B / element.
       map_vec4       residual add + ReLU                                  a, b, out                     12 B / element
       maxpool_*      2x2 max pool forward (x, y, idx) and backward        6 and 10 B / input element
       sgd_*          x -= lr d; d = 0                                     16 B / parameter"""
@@ -78,6 +81,8 @@ def hbm_bound_bytes(batch):
         ho = (h + 2 * p - k) // s + 1
         el["bn"].append(batch * co * ho * ho)
     bn_all = float(sum(el["bn"]))
+    big = lambda n: n >= (1 << 20)                  # the host program's threshold for a deferred zero fill
+    bn_bwd_bytes = float(sum((12.0 if big(n) else 16.0) * n for n in el["bn"]))
     relu_bn = 0.0                                   # BN outputs followed by an in-place ReLU: the stem, and conv1/conv2 of every block
     convs = resnet50_convs()
     i = 1
@@ -86,10 +91,12 @@ def hbm_bound_bytes(batch):
         for b_ in range(nblk):
             relu_bn += el["bn"][i] + el["bn"][i + 1]
             i += 4 if b_ == 0 else 3
-    adds = sum(batch * c * h * h * n for (c, h, n) in ((256, 16, 3), (512, 8, 4), (1024, 4, 6), (2048, 2, 3)))
+    add_shapes = ((256, 16, 3), (512, 8, 4), (1024, 4, 6), (2048, 2, 3))
+    adds = sum(batch * c * h * h * n for (c, h, n) in add_shapes)
+    add_grad_bytes = float(sum((20.0 if big(batch * c * h * h) else 28.0) * batch * c * h * h * n for (c, h, n) in add_shapes))
     pool_in = batch * 64 * 32 * 32
     params = 23520842
-    return {"bn_fwd": 8.0 * bn_all, "bn_bwd": 16.0 * bn_all + 8.0 * relu_bn, "relu_add_grad": 28.0 * adds, "map_vec4": 12.0 * adds,
+    return {"bn_fwd": 8.0 * bn_all, "bn_bwd": bn_bwd_bytes + 8.0 * relu_bn, "relu_add_grad": add_grad_bytes, "map_vec4": 12.0 * adds,
             "maxpool_fwd": 6.0 * pool_in, "maxpool_bwd": 10.0 * pool_in, "sgd": 16.0 * params}
 
 

@@ -91,6 +91,18 @@ int    LTB_FN(set_fusion)(int on);
 int    LTB_FN(set_deterministic)(int on);
 int    LTB_FN(set_filter_cache)(int on);
 int    LTB_FN(params_changed)(void);
+/* Deferred zero fill of gradient buffers (no counterpart in the reference, whose arena hands out zeroed memory and whose
+ * gradient operators all add into their destination, TensorDslCublas.scala:18-25, TensorDslCPU.scala:575-692).  For the
+ * activation gradients of a convolutional network that is a zero fill of every buffer plus a read of those zeros by the
+ * first -- usually the only -- operator that adds into it.  grad_unset(d, n) declares the n floats at d, a fresh block that
+ * nothing has written, to be a gradient buffer whose zero fill is deferred: it COUNTS as zero.  The first entry point that
+ * meets exactly that block as an accumulation destination and is able to -- conv2d_bwd (dx, tensor-core path), bn_bwd (dx),
+ * the gradient of a same-shape add (da, db) -- writes its result instead of adding; every other entry point that is handed
+ * the block (any gradient operator, the transfers) fills it with zeros first, so results never depend on the declaration.
+ * grad_materialize(d, n) does that filling on request (before the caller reads the block by other means).  Declarations
+ * end with the arena span that holds the block (ltb_reset, ltb_free). */
+int    LTB_FN(grad_unset)(float* d, int64_t n);
+int    LTB_FN(grad_materialize)(float* d, int64_t n);
 int    LTB_FN(device_status)(void);                     /* 0, or LTB_E_DEVICE if a kernel's bounded wait expired */
 /* Failure detection on the device (no counterpart in the reference, whose kernels never wait on anything). Every spin wait
  * inside a kernel of this library (on a TMA or tensor-core completion barrier) gives up after a limit, records a code in

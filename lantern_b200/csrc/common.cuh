@@ -60,7 +60,7 @@ struct Context {
   cudaStream_t side = nullptr;        // second stream: the weight-gradient half of conv backward runs beside the data-gradient half
   cudaEvent_t fork_ev = nullptr, join_ev = nullptr;
   unsigned tune = 0;                  // LTB_TUNE (environment, read by ltb_init): switches single optimisations off for A/B measurements:
-                                      // 1 no in-kernel gather, 2 no tap-loop weight-grad from kept copies, 4 no kept copies, 8 no early first loads
+                                      // 1 no in-kernel gather, 2 no tap-loop weight-grad from kept copies, 4 no kept copies, 8 no early first loads, 32 deferred zero fill off (ltb_grad_unset fills at once)
   bool deterministic = false;         // split-K sums in a fixed order (clusters, slabs) instead of atomics (ltb_set_deterministic)
   bool filter_cache = false;          // per-tap filter forms kept across calls (ltb_set_filter_cache)
   bool fusion = false;                // look-ahead fusion of BN/add with ReLU (off unless the host opts in)
@@ -90,6 +90,15 @@ void cl_cache_drop_from(const void* p);
 void* step_alloc(size_t bytes);
 // A call is about to write [p, p + bytes): cached filter forms whose source overlaps it are stale (p == nullptr: all of them).
 void filter_cache_note_write(const void* p, size_t bytes);
+// Gradient buffers declared unset (ltb_grad_unset): logically zero, physically not yet written.
+//   grad_take_unset(p, bytes)  true when [p, p + bytes) is exactly one declared block: the caller WRITES its result instead
+//                              of adding (the declaration is consumed);
+//   grad_settle(p, bytes)      any other use of a block that starts at p: fill it with zeros now (on the current stream).
+// Both cost a look-up in a small host table, and nothing at all while no block is declared.
+bool grad_take_unset(const void* p, size_t bytes);
+int grad_settle(const void* p, size_t bytes);
+void grad_unset_drop_from(const void* p);
+void grad_unset_clear();
 bool comm_active();
 int comm_wait_stream(cudaStream_t s, const char* what);
 int comm_wait_event(cudaEvent_t ev, const char* what);
@@ -97,6 +106,8 @@ void profile_before(const char* name);
 void profile_after();
 
 #define LTB_REQUIRE(cond, ...) do { if (!(cond)) return ::ltb::fail(LTB_E_ARG, __VA_ARGS__); } while (0)
+// A gradient buffer that was declared unset and is about to be used in any way but as a whole, writable destination: zeros first.
+#define LTB_SETTLE(ptr) do { int rc_s_ = ::ltb::grad_settle((ptr), 0); if (rc_s_) return rc_s_; } while (0)
 #define LTB_CUDA(call) do { cudaError_t e_ = (call); if (e_ != cudaSuccess) return ::ltb::fail(LTB_E_CUDA, "%s failed: %s (%s:%d)", #call, cudaGetErrorString(e_), __FILE__, __LINE__); } while (0)
 #define LTB_INITED_NOFLUSH() do { if (!::ltb::g.inited) return ::ltb::fail(LTB_E_STATE, "%s: library not initialised (call ltb_init)", __func__); } while (0)
 // Every entry point first issues an operation held back by the look-ahead fusion; the few that may complete it use _NOFLUSH.

@@ -135,6 +135,7 @@ int ltb_shutdown(void) {
   cudaStreamSynchronize(g.stream); cudaStreamSynchronize(g.side); cudaStreamSynchronize(g.branch);
   filter_cache_clear(); cl_cache_clear();
   for (int i = 0; i < 16; ++i) { if (marker_ev[i]) cudaEventDestroy(marker_ev[i]); marker_ev[i] = nullptr; marker_set[i] = false; }
+  grad_unset_clear();
   release_all();
   return LTB_OK;
 }
@@ -200,6 +201,38 @@ static void* arena_alloc(size_t bytes, bool zero) {
 }
 }  // extern "C"
 namespace ltb {
+// ---- deferred zero fill of gradient buffers ------------------------------------------------------------------------------------
+// The reference hands out zeroed memory and every gradient entry point adds into its destination.  For the activation
+// gradients of a convolutional network that is a zero fill of every buffer plus a read of those zeros by the first (usually
+// only) operation that adds into it.  A caller may instead declare a fresh gradient buffer unset: the first accumulating entry
+// point that meets it as its whole destination and is able to (convolution data-grad, batch-norm backward, same-shape add
+// gradient) writes its result; every other entry point fills the block with zeros before it touches it.
+static std::vector<std::pair<const char*, size_t>> unset_blocks;
+static int unset_find(const void* p) {
+  for (size_t i = 0; i < unset_blocks.size(); ++i) if (unset_blocks[i].first == (const char*)p) return (int)i;
+  return -1;
+}
+bool grad_take_unset(const void* p, size_t bytes) {
+  if (unset_blocks.empty() || !p) return false;
+  const int i = unset_find(p);
+  if (i < 0) return false;
+  if (unset_blocks[i].second != bytes) return false;               // a part or more than the block: the caller settles it instead
+  unset_blocks[i] = unset_blocks.back(); unset_blocks.pop_back();
+  return true;
+}
+int grad_settle(const void* p, size_t) {
+  if (unset_blocks.empty() || !p) return LTB_OK;
+  const int i = unset_find(p);
+  if (i < 0) return LTB_OK;
+  const size_t bytes = unset_blocks[i].second;
+  unset_blocks[i] = unset_blocks.back(); unset_blocks.pop_back();
+  if (cudaMemsetAsync(const_cast<void*>(p), 0, bytes, g.stream) != cudaSuccess) return fail(LTB_E_CUDA, "zero fill of a deferred gradient buffer failed");
+  return LTB_OK;
+}
+void grad_unset_drop_from(const void* p) {
+  for (size_t i = 0; i < unset_blocks.size();) { if ((const void*)unset_blocks[i].first >= p) { unset_blocks[i] = unset_blocks.back(); unset_blocks.pop_back(); } else ++i; }
+}
+void grad_unset_clear() { unset_blocks.clear(); }
 void* step_alloc(size_t bytes) {
   if (!g.inited || g.keep_off) return nullptr;
   const size_t b = round_up(bytes ? bytes : 1);
@@ -209,6 +242,15 @@ void* step_alloc(size_t bytes) {
 }
 }  // namespace ltb
 extern "C" {
+// Deferred zero fill (see grad_take_unset): d must be a block of n floats that nothing has written since it was handed out.
+int ltb_grad_unset(float* d, int64_t n) {
+  LTB_INITED(); LTB_REQUIRE(d && n > 0, "ltb_grad_unset: bad argument");
+  if (g.tune & 32) { LTB_CUDA(cudaMemsetAsync(d, 0, (size_t)n * 4, g.stream)); return LTB_OK; }     // switch: plain zero fill at once
+  grad_settle(d, 0);                                                   // declared before and never used: start over
+  unset_blocks.emplace_back((const char*)d, (size_t)n * 4);
+  return LTB_OK;
+}
+int ltb_grad_materialize(float* d, int64_t n) { LTB_INITED(); LTB_REQUIRE(d && n >= 0, "ltb_grad_materialize: bad argument"); return grad_settle(d, (size_t)n * 4); }
 void* ltb_malloc(size_t bytes) { return arena_alloc(bytes, true); }
 void* ltb_malloc_uninit(size_t bytes) { return arena_alloc(bytes, false); }
 int ltb_free(void* p, size_t bytes) {
@@ -216,7 +258,7 @@ int ltb_free(void* p, size_t bytes) {
   size_t b = round_up(bytes ? bytes : 1);
   LTB_REQUIRE(p && b <= g.used && (char*)p == g.heap + g.used - b, "ltb_free: not the newest block (LIFO arena)");
   g.used -= b;
-  cl_cache_drop_from(p);
+  cl_cache_drop_from(p); grad_unset_drop_from(p);
   return LTB_OK;
 }
 void* ltb_mark(void) { return g.heap + g.used; }
@@ -227,6 +269,7 @@ int ltb_reset(void* mark) {
   LTB_REQUIRE(!g.branch_marked, "ltb_reset: a branch region is open (ltb_branch_join missing)");
   g.used = (size_t)(m - g.heap);   // zeroing happens when a block is handed out again by ltb_malloc
   g.top_used = 0; cl_cache_clear();  // the step's kept copies go with it
+  grad_unset_drop_from(m);           // and the declarations of blocks that no longer exist
   return LTB_OK;
 }
 size_t ltb_arena_used(void) { return g.used; }
@@ -234,17 +277,20 @@ size_t ltb_arena_used(void) { return g.used; }
 // ------------------------------------------------------------------ transfers (GPUOps.scala:51-95)
 int ltb_h2d(void* dst, const void* src, size_t bytes) {
   LTB_INITED(); filter_cache_note_write(dst, bytes); LTB_REQUIRE(dst && src, "ltb_h2d: null pointer");
+  { int rc_ = grad_settle(dst, bytes); if (rc_) return rc_; }
   if (bytes) LTB_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, g.stream));
   return LTB_OK;
 }
 int ltb_d2h(void* dst, const void* src, size_t bytes) {
   LTB_INITED(); LTB_REQUIRE(dst && src, "ltb_d2h: null pointer");
+  { int rc_ = grad_settle(src, bytes); if (rc_) return rc_; }
   LTB_REQUIRE(!g.capturing, "ltb_d2h: blocking read-back while recording a step");
   if (bytes) LTB_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, g.stream));
   return stream_wait("ltb_d2h");
 }
 int ltb_d2d(void* dst, const void* src, size_t bytes) {
   LTB_INITED(); filter_cache_note_write(dst, bytes); LTB_REQUIRE(dst && src, "ltb_d2d: null pointer");
+  { int rc_ = grad_settle(dst, bytes); if (!rc_) rc_ = grad_settle(src, bytes); if (rc_) return rc_; }
   if (bytes) LTB_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, g.stream));
   return LTB_OK;
 }
@@ -256,6 +302,7 @@ void* ltb_host_alloc(size_t bytes) {
 int ltb_host_free(void* p) { if (p) LTB_CUDA(cudaFreeHost(p)); return LTB_OK; }
 int ltb_d2h_async(void* dst, const void* src, size_t bytes) {
   LTB_INITED(); LTB_REQUIRE(dst && src, "ltb_d2h_async: null pointer");
+  { int rc_ = grad_settle(src, bytes); if (rc_) return rc_; }
   if (bytes) LTB_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, g.stream));
   return LTB_OK;
 }

@@ -38,11 +38,11 @@ int ltb_mm_dot(const float* a, const float* b, float* out, int m, int k, int n) 
   return gemm_any(a, false, b, false, out, m, n, k, 1.0f, false);
 }
 int ltb_add_dot_trans1(float* db, const float* a, const float* dc, int m, int k, int n) {   // dB[k,n] += A^T[k,m] dC[m,n]
-  LTB_INITED(); LTB_REQUIRE(db && a && dc && m > 0 && k > 0 && n > 0, "ltb_add_dot_trans1: bad argument");
+  LTB_INITED(); LTB_SETTLE(db); LTB_SETTLE(dc); LTB_REQUIRE(db && a && dc && m > 0 && k > 0 && n > 0, "ltb_add_dot_trans1: bad argument");
   return gemm_any(a, true, dc, false, db, k, n, m, 1.0f, true);
 }
 int ltb_add_dot_trans2(float* da, const float* dc, const float* b, int m, int k, int n) {   // dA[m,k] += dC[m,n] B^T[n,k]
-  LTB_INITED(); LTB_REQUIRE(da && dc && b && m > 0 && k > 0 && n > 0, "ltb_add_dot_trans2: bad argument");
+  LTB_INITED(); LTB_SETTLE(da); LTB_SETTLE(dc); LTB_REQUIRE(da && dc && b && m > 0 && k > 0 && n > 0, "ltb_add_dot_trans2: bad argument");
   return gemm_any(dc, false, b, true, da, m, k, n, 1.0f, true);
 }
 
@@ -53,7 +53,7 @@ int ltb_gemm(const float* a, int ta, const float* b, int tb, float alpha, float*
 }
 // gemm_grad: the eight cblas_sgemm calls of TensorDslCPU.scala:428-472, all with beta = 1.
 int ltb_gemm_grad(const float* a, float* da, int ta, const float* b, float* db, int tb, float alpha, const float* dc, int M, int N, int K) {
-  LTB_INITED(); LTB_REQUIRE(a && b && dc && M > 0 && N > 0 && K > 0, "ltb_gemm_grad: bad argument");
+  LTB_INITED(); LTB_SETTLE(da); LTB_SETTLE(db); LTB_SETTLE(dc); LTB_REQUIRE(a && b && dc && M > 0 && N > 0 && K > 0, "ltb_gemm_grad: bad argument");
   int rc = LTB_OK;
   if (!ta && !tb) {
     if (da) rc = gemm_any(dc, false, b, true, da, M, K, N, alpha, true);             // dA[M,K] += dC B^T
@@ -89,7 +89,9 @@ int ltb_conv2d_bwd(const float* x, float* dx, const float* w, float* dw, float* 
   LTB_INITED(); ConvDims d;
   LTB_REQUIRE(x && w && dy && conv_dims(d, N, C, H, W, K, R, S, sh, sw, ph, pw), "ltb_conv2d_bwd: bad argument");
   int rc = LTB_OK;
+  LTB_SETTLE(dy);
   if (covers_image(d) && d.R * d.S > 1) {
+    LTB_SETTLE(dx);
     const int crs = C * R * S;
     if (dw) rc = gemm_any(dy, true, x, false, dw, K, crs, N, 1.0f, true);           // dw[K][CHW] += dy^T x
     if (!rc && dx) rc = gemm_any(dy, false, w, false, dx, N, crs, K, 1.0f, true);   // dx[N][CHW] += dy w
@@ -100,6 +102,9 @@ int ltb_conv2d_bwd(const float* x, float* dx, const float* w, float* dw, float* 
   // half is issued on the side stream and the data-gradient half on the caller's, and the caller's stream waits for both
   // before the call returns: program order at the boundary is unchanged, and inside a recorded step the two become
   // parallel branches of the graph. Per-launch profiling keeps them serial so that each kernel is timed alone.
+  // dx declared unset (ltb_grad_unset): the engine's data-grad writes instead of adding; any other path starts from zeros
+  bool fresh = dx && g.math == LTB_MATH_TF32 && grad_take_unset(dx, (size_t)N * C * H * W * 4);
+  if (!fresh) LTB_SETTLE(dx);
   if (g.math == LTB_MATH_TF32) { rc = conv_bwd_prestage(dy, d, dx && dw); if (rc) return rc; }
   const bool overlap = dx && dw && !g.profiling && g.side != nullptr;
   const size_t arena_base = g.used;
@@ -116,8 +121,9 @@ int ltb_conv2d_bwd(const float* x, float* dx, const float* w, float* dw, float* 
   }
   if (overlap) g.stream = main_stream;
   if (dx && rc == LTB_OK) {
-    int r = g.math == LTB_MATH_TF32 ? conv_dgrad_tc(dy, w, dx, d) : 0;
-    if (r == 0) rc = conv_dgrad_fp32(dy, w, dx, d); else if (r < 0) rc = r;
+    int r = g.math == LTB_MATH_TF32 ? conv_dgrad_tc(dy, w, dx, d, &fresh) : 0;
+    if (r == 0 && fresh) { fresh = false; if (cudaMemsetAsync(dx, 0, (size_t)N * C * H * W * 4, g.stream) != cudaSuccess) rc = fail(LTB_E_CUDA, "ltb_conv2d_bwd: zero fill failed"); }
+    if (r == 0 && !rc) rc = conv_dgrad_fp32(dy, w, dx, d); else if (r < 0) rc = r;
   }
   if (overlap) {                                   // join, also on the error path: nothing may stay forked
     g.hold_workspace = false;

@@ -282,22 +282,23 @@ int flush_pending() {
   }
 }
 // The held in-place ReLU gradient and the gradient of a same-shape add in one pass:
-// m = y > 0 ? d : 0;  d = m;  da += m;  db += m   (da, db nullable).  n4 float4 items, then a scalar tail from `tail`.
-__global__ void relu_add_grad_kernel(const float* __restrict__ y, float* d, float* da, float* db, int64_t n4, int64_t tail, int64_t n) {
+// m = y > 0 ? d : 0;  d = m;  da += m;  db += m   (da, db nullable; fa / fb: that destination holds nothing yet and is written).
+// n4 float4 items, then a scalar tail from `tail`.
+__global__ void relu_add_grad_kernel(const float* __restrict__ y, float* d, float* da, float* db, int64_t n4, int64_t tail, int64_t n, int fa, int fb) {
   const int64_t i0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t i = i0; i < n4; i += stride) {
     const float4 yv = reinterpret_cast<const float4*>(y)[i];
     float4 m = reinterpret_cast<const float4*>(d)[i];
     m.x = yv.x > 0.0f ? m.x : 0.0f; m.y = yv.y > 0.0f ? m.y : 0.0f; m.z = yv.z > 0.0f ? m.z : 0.0f; m.w = yv.w > 0.0f ? m.w : 0.0f;
     reinterpret_cast<float4*>(d)[i] = m;
-    if (da) { float4 v = reinterpret_cast<float4*>(da)[i]; v.x += m.x; v.y += m.y; v.z += m.z; v.w += m.w; reinterpret_cast<float4*>(da)[i] = v; }
-    if (db) { float4 v = reinterpret_cast<float4*>(db)[i]; v.x += m.x; v.y += m.y; v.z += m.z; v.w += m.w; reinterpret_cast<float4*>(db)[i] = v; }
+    if (da) { float4 v = fa ? make_float4(0.f, 0.f, 0.f, 0.f) : reinterpret_cast<float4*>(da)[i]; v.x += m.x; v.y += m.y; v.z += m.z; v.w += m.w; reinterpret_cast<float4*>(da)[i] = v; }
+    if (db) { float4 v = fb ? make_float4(0.f, 0.f, 0.f, 0.f) : reinterpret_cast<float4*>(db)[i]; v.x += m.x; v.y += m.y; v.z += m.z; v.w += m.w; reinterpret_cast<float4*>(db)[i] = v; }
   }
   for (int64_t i = tail + i0; i < n; i += stride) {
     const float m = y[i] > 0.0f ? d[i] : 0.0f;
     d[i] = m;
-    if (da) da[i] += m;
-    if (db) db[i] += m;
+    if (da) da[i] = fa ? m : da[i] + m;
+    if (db) db[i] = fb ? m : db[i] + m;
   }
 }
 
@@ -350,15 +351,25 @@ int ltb_ew_binary_grad(int op, const float* a, float* da, const int* as, const f
     g.pending.kind = PEND_NONE;
     const bool vec = aligned16(y) && aligned16(d) && (!da || aligned16(da)) && (!db || aligned16(db));
     const int64_t n4 = vec ? n / 4 : 0;
-    LTB_LAUNCH(relu_add_grad_kernel, grid_for(n4 ? n4 : n, 256), 256, 0, y, d, da, db, n4, n4 * 4, n);
+    // a destination declared unset (ltb_grad_unset) is written instead of added into; da == db stays an accumulation
+    const int fa = da && da != db && grad_take_unset(da, (size_t)n * 4) ? 1 : 0, fb = db && da != db && grad_take_unset(db, (size_t)n * 4) ? 1 : 0;
+    LTB_SETTLE(d); if (!fa) LTB_SETTLE(da); if (!fb) LTB_SETTLE(db);
+    LTB_LAUNCH(relu_add_grad_kernel, grid_for(n4 ? n4 : n, 256), 256, 0, y, d, da, db, n4, n4 * 4, n, fa, fb);
     return LTB_OK;
   }
   if (g.pending.kind) { int rc = flush_pending(); if (rc) return rc; }
-  if (!ab && !bb && op == LTB_ADD) {   // the residual add of ResNet: da += dout, db += dout
-    int rc = da ? launch_map<2>(da, dout, nullptr, da, n, [] __device__(float g0, float c, float) { return g0 + c; }) : 0;
+  LTB_SETTLE(dout);
+  if (!ab && !bb && op == LTB_ADD) {   // the residual add of ResNet: da += dout, db += dout (a destination declared unset: da = dout)
+    const bool fa = da && da != db && grad_take_unset(da, (size_t)n * 4), fb = db && da != db && grad_take_unset(db, (size_t)n * 4);
+    if (!fa) LTB_SETTLE(da);
+    if (!fb) LTB_SETTLE(db);
+    int rc = !da ? 0 : fa ? launch_map<1>(dout, nullptr, nullptr, da, n, [] __device__(float c, float, float) { return c; })
+                          : launch_map<2>(da, dout, nullptr, da, n, [] __device__(float g0, float c, float) { return g0 + c; });
     if (rc) return rc;
-    return db ? launch_map<2>(db, dout, nullptr, db, n, [] __device__(float g0, float c, float) { return g0 + c; }) : LTB_OK;
+    return !db ? LTB_OK : fb ? launch_map<1>(dout, nullptr, nullptr, db, n, [] __device__(float c, float, float) { return c; })
+                             : launch_map<2>(db, dout, nullptr, db, n, [] __device__(float g0, float c, float) { return g0 + c; });
   }
+  LTB_SETTLE(da); LTB_SETTLE(db);
   if (!da && !db) return LTB_OK;
   LTB_LAUNCH(bcast_binary_grad_kernel, grid_for(n, 256), 256, 0, op, a, da, ab, b, db, bb, dout, p, n);
   return LTB_OK;
@@ -372,7 +383,7 @@ int ltb_ew_inplace_scalar(int op, float* x, float s, int64_t n) { return ltb_ew_
 
 // inplaceElementWiseOpWithBroadCastOrReduce: TensorDslCPU.scala:265-279.
 int ltb_ew_inplace(int op, float* x, const int* xs, const float* y, const int* ys, int rank) {
-  LTB_INITED(); { size_t cnt_ = 1; for (int i_ = 0; i_ < rank && i_ < 8 && xs; ++i_) cnt_ *= (size_t)(xs[i_] > 0 ? xs[i_] : 1); filter_cache_note_write(x, cnt_ * 4); } LTB_REQUIRE(x && y && op >= LTB_ADD && op <= LTB_DIV, "ltb_ew_inplace: bad argument");
+  LTB_INITED(); LTB_SETTLE(x); LTB_SETTLE(y); { size_t cnt_ = 1; for (int i_ = 0; i_ < rank && i_ < 8 && xs; ++i_) cnt_ *= (size_t)(xs[i_] > 0 ? xs[i_] : 1); filter_cache_note_write(x, cnt_ * 4); } LTB_REQUIRE(x && y && op >= LTB_ADD && op <= LTB_DIV, "ltb_ew_inplace: bad argument");
   Bcast p; int64_t n; bool xb, yb;
   LTB_REQUIRE(make_bcast(xs, ys, rank, p, n, xb, yb), "ltb_ew_inplace: shapes do not broadcast");
   if (!xb && !yb) return launch_map<2>(x, y, nullptr, x, n, [op] __device__(float u, float v, float) { return bin_op(op, u, v); });
@@ -404,7 +415,7 @@ int ltb_trans(const float* x, float* out, int rows, int cols) {
   return LTB_OK;
 }
 int ltb_trans_grad(float* dx, const float* dy, int rows, int cols) {
-  LTB_INITED(); LTB_REQUIRE(dx && dy && rows > 0 && cols > 0, "ltb_trans_grad: bad argument");
+  LTB_INITED(); LTB_SETTLE(dx); LTB_SETTLE(dy); LTB_REQUIRE(dx && dy && rows > 0 && cols > 0, "ltb_trans_grad: bad argument");
   // dy is [cols, rows]; dx[rows, cols] += dy^T
   LTB_LAUNCH(transpose_kernel<true>, dim3((rows + 31) / 32, (cols + 31) / 32), dim3(32, 8), 0, dy, dx, cols, rows);
   return LTB_OK;
@@ -426,6 +437,7 @@ int ltb_unary(int op, const float* x, float* out, int64_t n) {
 // TensorDslCudnn.scala:1392-1429); this library masks where y <= 0, which is the derivative of what was computed.
 int ltb_unary_grad(int op, const float* x, float* dx, const float* y, const float* dy, int64_t n, int in_place) {
   LTB_INITED(); LTB_REQUIRE(dx && dy && n >= 0 && op >= LTB_RELU && op <= LTB_SQUARE, "ltb_unary_grad: bad argument");
+  LTB_SETTLE(dx); LTB_SETTLE(dy);
   if (op == LTB_RELU && in_place) {
     LTB_REQUIRE(y, "ltb_unary_grad: relu in place needs the result");
     if (g.fusion && n > 0) { Pending h; h.kind = PEND_RELU_GRAD; h.n = n; h.relu_y = y; h.d = dx; g.pending = h; return LTB_OK; }   // BN backward or an add's gradient may absorb it
@@ -457,7 +469,7 @@ int ltb_dropout(const float* x, float* y, float* mask, float p, int64_t n) {
   return ltb_dropout_masked(x, y, mask, n);
 }
 int ltb_dropout_grad(float* dx, const float* mask, const float* dy, int64_t n) {
-  LTB_INITED(); LTB_REQUIRE(dx && mask && dy && n >= 0, "ltb_dropout_grad: bad argument");
+  LTB_INITED(); LTB_SETTLE(dx); LTB_SETTLE(dy); LTB_REQUIRE(dx && mask && dy && n >= 0, "ltb_dropout_grad: bad argument");
   return launch_map<3>(dx, mask, dy, dx, n, [] __device__(float g0, float m, float d) { return g0 + m * d; });
 }
 
@@ -477,13 +489,13 @@ int ltb_concat(float* out, const float* const* inputs, const int* dims, int n_in
   return LTB_OK;
 }
 int ltb_concat_grad(float* const* dinputs, const float* dout, const int* dims, int n_inputs, int outer, int inner) {
-  LTB_INITED(); LTB_REQUIRE(dinputs && dout && dims && n_inputs > 0 && outer > 0 && inner > 0, "ltb_concat_grad: bad argument");
+  LTB_INITED(); LTB_SETTLE(dout); LTB_REQUIRE(dinputs && dout && dims && n_inputs > 0 && outer > 0 && inner > 0, "ltb_concat_grad: bad argument");
   int64_t total = 0;
   for (int k = 0; k < n_inputs; ++k) { LTB_REQUIRE(dims[k] > 0, "ltb_concat_grad: bad input %d", k); total += dims[k]; }
   int64_t off = 0;
   for (int k = 0; k < n_inputs; ++k) {
     int64_t len = (int64_t)dims[k] * inner;
-    if (dinputs[k]) { int rc = copy_rows<true>(dinputs[k], len, dout + off, total * inner, len, outer); if (rc) return rc; }
+    if (dinputs[k]) { LTB_SETTLE(dinputs[k]); int rc = copy_rows<true>(dinputs[k], len, dout + off, total * inner, len, outer); if (rc) return rc; }
     off += len;
   }
   return LTB_OK;

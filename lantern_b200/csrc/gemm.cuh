@@ -19,7 +19,7 @@ int conv_bias_grad(const float* dy, float* dbias, const ConvDims& d);
 int gemm_tc(const float* a, bool a_kmajor, const float* b, bool b_kmajor, float* c, bool c_row_major,
             int M, int N, int K, float alpha, bool accumulate);
 int conv_fwd_tc(const float* x, const float* w, const float* bias, float* y, const ConvDims& d);
-int conv_dgrad_tc(const float* dy, const float* w, float* dx, const ConvDims& d);
+int conv_dgrad_tc(const float* dy, const float* w, float* dx, const ConvDims& d, bool* fresh);
 int conv_wgrad_tc(const float* x, const float* dy, float* dw, const ConvDims& d);
 // Before the two halves of a convolution's backward call are issued: stages what both will read (one channels-last copy of dy).
 int conv_bwd_prestage(const float* dy, const ConvDims& d, bool both_halves);

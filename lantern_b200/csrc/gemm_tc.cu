@@ -1139,21 +1139,21 @@ static int conv_fwd_taps(const float* x, const float* w, const float* bias, floa
   if (nx) temp_free(xr, nx);
   return rc ? rc : (ok ? 1 : 0);
 }
-static int conv_dgrad_taps(const float* dy, const float* w, float* dx, const ConvDims& d) {
+static int conv_dgrad_taps(const float* dy, const float* w, float* dx, const ConvDims& d, bool accumulate) {
   TcConvGeom gm; TcPlan p;
   if (!taps_geometry(d, gm) || !tc_plan_conv_taps_dgrad(p, dx, dx, dx, gm, true, g.sm_count)) return 0;
   float *dyr = cl_lookup(dy, d.N, d.K, d.oH * d.oW), *wd = nullptr; size_t ny = 0, nw = 0;
   int rc = dyr ? LTB_OK : channels_last(dy, d.N, d.K, d.oH * d.oW, &dyr, &ny); if (rc) return rc;
   if (!dyr) return 0;
   rc = tap_matrices(w, d, 1, &wd, &nw);
-  bool ok = !rc && wd && tc_plan_conv_taps_dgrad(p, dyr, wd, dx, gm, true, g.sm_count);
+  bool ok = !rc && wd && tc_plan_conv_taps_dgrad(p, dyr, wd, dx, gm, accumulate, g.sm_count);
   if (ok) rc = launch_plan(p, "tc_gemm_kernel[conv_dgrad taps]");
   if (wd && nw) temp_free(wd, nw);
   if (ny) temp_free(dyr, ny);
   return rc ? rc : (ok ? 1 : 0);
 }
 // Stride 2 (both directions): dx is the stride-1 data-gradient of dy with zeros inserted (to_rows_up2_kernel).
-static int conv_dgrad_taps_up2(const float* dy, const float* w, float* dx, const ConvDims& d) {
+static int conv_dgrad_taps_up2(const float* dy, const float* w, float* dx, const ConvDims& d, bool accumulate) {
   if (d.sh != 2 || d.sw != 2 || d.R * d.S == 1 || d.K % 32 || d.oW > 32 || d.N > 65535) return 0;   // 1x1: the unfolded form with its one-to-one fold is cheaper
   TcConvGeom gm; TcPlan p;
   gm.n_img = d.N; gm.C = d.C; gm.H = d.H; gm.W = d.W; gm.K = d.K; gm.R = d.R; gm.S = d.S; gm.ph = d.ph; gm.pw = d.pw;
@@ -1166,7 +1166,7 @@ static int conv_dgrad_taps_up2(const float* dy, const float* w, float* dx, const
   LTB_LAUNCH(to_rows_up2_kernel, dim3((gm.oH + 1) / 2, d.K / 32, d.N), 256, 0, dy, up, d.K, d.oH, d.oW, gm.oH, gm.oW);
   float* wd = nullptr; size_t nw = 0;
   int rc = tap_matrices(w, d, 1, &wd, &nw);
-  bool ok = !rc && wd && tc_plan_conv_taps_dgrad(p, up, wd, dx, gm, true, g.sm_count);
+  bool ok = !rc && wd && tc_plan_conv_taps_dgrad(p, up, wd, dx, gm, accumulate, g.sm_count);
   if (ok) rc = launch_plan(p, "tc_gemm_kernel[conv_dgrad taps up2]");
   if (wd && nw) temp_free(wd, nw);
   temp_free(up, nu);
@@ -1233,14 +1233,16 @@ int conv_fwd_tc(const float* x, const float* w, const float* bias, float* y, con
   return rc ? rc : (ok ? 1 : 0);
 }
 
-int conv_dgrad_tc(const float* dy, const float* w, float* dx, const ConvDims& d) {
+// *fresh: dx was declared unset (ltb_grad_unset) and holds nothing: a path that can writes its result instead of adding, the
+// unfold-and-fold path fills dx with zeros first; either way *fresh is false once dx holds data.
+int conv_dgrad_tc(const float* dy, const float* w, float* dx, const ConvDims& d, bool* fresh) {
   const int ck = d.C * d.R * d.S, pix = d.oH * d.oW;
   TcPlan p;
   const bool rows = tc_conv_needs_rows(pix), direct = is_pointwise(d);
   const int ldw = (ck + 31) / 32 * 32;                                     // N-major filter rows must be whole 128-byte chunks
   if (!tc_plan_conv_dgrad(p, dx, rows, dx, ldw, dx, d.N, ck, d.K, pix, direct, g.sm_count)) return 0;
-  { int t = conv_dgrad_taps(dy, w, dx, d); if (t != 0) return t; }
-  { int t = conv_dgrad_taps_up2(dy, w, dx, d); if (t != 0) return t; }
+  { int t = conv_dgrad_taps(dy, w, dx, d, !*fresh); if (t != 0) { if (t > 0) *fresh = false; return t; } }
+  { int t = conv_dgrad_taps_up2(dy, w, dx, d, !*fresh); if (t != 0) { if (t > 0) *fresh = false; return t; } }
   const bool gathered = rows && pix > 1 && !(g.tune & 1) && tc_gather_possible(dy, d.K, pix);    // dy of a small map: collected by the kernel itself
   const float* op = dy; bool r2; float* temp = nullptr; size_t tn = 0;
   ConvDims flat = d; flat.C = d.K;                               // dy is [N][K][pix]: staged like a pointwise activation with K channels
@@ -1250,10 +1252,14 @@ int conv_dgrad_tc(const float* dy, const float* w, float* dx, const ConvDims& d)
   if (!direct) { col = temp_alloc(ncol); if (!col) { if (temp) temp_free(temp, tn); return 0; } }
   float* wtemp; size_t wn; const float* wp;
   rc = padded_filter(w, d.K, ck, ldw, &wp, &wtemp, &wn);
-  bool ok = !rc && wp && tc_plan_conv_dgrad(p, op, rows, wp, ldw, direct ? dx : col, d.N, ck, d.K, pix, direct, g.sm_count);
+  bool ok = !rc && wp && tc_plan_conv_dgrad(p, op, rows, wp, ldw, direct ? dx : col, d.N, ck, d.K, pix, direct && !*fresh, g.sm_count);
+  if (ok && !direct && *fresh) {                                  // the fold-back adds into dx: start from zeros
+    if (cudaMemsetAsync(dx, 0, (size_t)d.N * d.C * d.H * d.W * 4, g.stream) != cudaSuccess) { ok = false; rc = fail(LTB_E_CUDA, "conv data-grad: zero fill failed"); }
+  }
   if (ok && gathered) tc_plan_gather(p, dy, d.N, d.K, pix);
   if (ok) rc = launch_plan(p, gathered ? "tc_gemm_kernel[conv_dgrad gather]" : "tc_gemm_kernel[conv_dgrad]");
   if (ok && !rc && !direct) rc = launch_fold(col, dx, d);
+  if (ok && !rc) *fresh = false;
   if (wtemp) temp_free(wtemp, wn);
   if (col) temp_free(col, ncol);
   if (temp) temp_free(temp, tn);

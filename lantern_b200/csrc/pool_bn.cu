@@ -333,7 +333,7 @@ __device__ __forceinline__ float4 relu_mask(float4 d, float4 m) {
 template <int VPT>
 __global__ void __launch_bounds__(512, 2) bn_bwd_cluster_kernel(const float* __restrict__ x, float* dy, float* dx, const float* __restrict__ gamma,
                                                              float* dgamma, float* dbeta, const float* __restrict__ mean, const float* __restrict__ istd,
-                                                             int N, int C, int HW, int per_cta, const float* mask_y) {
+                                                             int N, int C, int HW, int per_cta, const float* mask_y, int fresh) {
   cg::cluster_group cluster = cg::this_cluster();
   const unsigned K = cluster.num_blocks(), r = cluster.block_rank();
   const int c = blockIdx.x / K;
@@ -395,7 +395,7 @@ __global__ void __launch_bounds__(512, 2) bn_bwd_cluster_kernel(const float* __r
 #pragma unroll
     for (int j = 0; j < VPT; ++j) {
       const int t = begin + j * (int)blockDim.x + (int)threadIdx.x;
-      if (t < end) { const int n = t / hw4, i = t - n * hw4; o[j] = reinterpret_cast<const float4*>(dx + ((int64_t)n * C + c) * HW)[i]; }
+      if (t < end) { const int n = t / hw4, i = t - n * hw4; o[j] = fresh ? make_float4(0.f, 0.f, 0.f, 0.f) : reinterpret_cast<const float4*>(dx + ((int64_t)n * C + c) * HW)[i]; }   // fresh: dx holds nothing yet, the result is written
     }
 #pragma unroll
     for (int j = 0; j < VPT; ++j) {
@@ -415,7 +415,7 @@ __global__ void __launch_bounds__(512, 2) bn_bwd_cluster_kernel(const float* __r
       const int n = t / hw4, i = t - n * hw4;
       const int64_t off = ((int64_t)n * C + c) * HW;
       const float4 v = reinterpret_cast<const float4*>(x + off)[i], d = reinterpret_cast<const float4*>(dy + off)[i];
-      float4 o = reinterpret_cast<float4*>(dx + off)[i];
+      float4 o = fresh ? make_float4(0.f, 0.f, 0.f, 0.f) : reinterpret_cast<float4*>(dx + off)[i];
       o.x += ca * (d.x - cb - (v.x - mu) * is * cc); o.y += ca * (d.y - cb - (v.y - mu) * is * cc);
       o.z += ca * (d.z - cb - (v.z - mu) * is * cc); o.w += ca * (d.w - cb - (v.w - mu) * is * cc);
       reinterpret_cast<float4*>(dx + off)[i] = o;
@@ -511,7 +511,7 @@ __global__ void __launch_bounds__(512, 2) bn_fwd_packed_kernel(const float* x, f
 template <int VPT>
 __global__ void __launch_bounds__(512, 2) bn_bwd_packed_kernel(const float* __restrict__ x, float* dy, float* dx, const float* __restrict__ gamma,
                                                             float* dgamma, float* dbeta, const float* __restrict__ mean, const float* __restrict__ istd,
-                                                            int N, int C, int HW, const float* mask_y) {
+                                                            int N, int C, int HW, const float* mask_y, int fresh) {
   __shared__ float red[32];
   const int g = threadIdx.y, T = blockDim.x;
   const int c = blockIdx.x * blockDim.y + g;
@@ -549,7 +549,7 @@ __global__ void __launch_bounds__(512, 2) bn_bwd_packed_kernel(const float* __re
 #pragma unroll
   for (int j = 0; j < VPT; ++j) {
     const int t = j * T + (int)threadIdx.x;
-    if (t < total) { const int n = t / hw4, i = t - n * hw4; o[j] = reinterpret_cast<const float4*>(dx + ((int64_t)n * C + c) * HW)[i]; }
+    if (t < total) { const int n = t / hw4, i = t - n * hw4; o[j] = fresh ? make_float4(0.f, 0.f, 0.f, 0.f) : reinterpret_cast<const float4*>(dx + ((int64_t)n * C + c) * HW)[i]; }
   }
 #pragma unroll
   for (int j = 0; j < VPT; ++j) {
@@ -613,7 +613,7 @@ int ltb_maxpool_fwd(const float* x, float* y, int32_t* idx, int N, int C, int H,
   return LTB_OK;
 }
 int ltb_maxpool_bwd(float* dx, const float* dy, const int32_t* idx, int64_t n_out) {
-  LTB_INITED(); LTB_REQUIRE(dx && dy && idx && n_out >= 0, "ltb_maxpool_bwd: bad argument");
+  LTB_INITED(); LTB_SETTLE(dx); LTB_SETTLE(dy); LTB_REQUIRE(dx && dy && idx && n_out >= 0, "ltb_maxpool_bwd: bad argument");
   if (n_out) LTB_LAUNCH(maxpool_bwd_kernel, grid_for(n_out, 256), 256, 0, dx, dy, idx, n_out);
   return LTB_OK;
 }
@@ -626,7 +626,7 @@ int ltb_avgpool_fwd(const float* x, float* y, int N, int C, int H, int W, int kh
   return LTB_OK;
 }
 int ltb_avgpool_bwd(float* dx, const float* dy, int N, int C, int H, int W, int kh, int kw, int sh, int sw) {
-  LTB_INITED();
+  LTB_INITED(); { int rc_ = grad_settle(dx, 0); if (!rc_) rc_ = grad_settle(dy, 0); if (rc_) return rc_; }
   LTB_REQUIRE(dx && dy && N > 0 && C > 0 && kh >= 1 && kw >= 1 && sh >= 1 && sw >= 1 && H >= kh && W >= kw, "ltb_avgpool_bwd: bad argument");
   int oH = (H - kh) / sh + 1, oW = (W - kw) / sw + 1;
   int64_t n_in = (int64_t)N * C * H * W;
@@ -670,21 +670,26 @@ int ltb_bn_bwd(const float* x, float* dx, const float* dy, const float* gamma, f
   if (g.pending.kind == PEND_RELU_GRAD && cluster_path && g.pending.d == dy && g.pending.n == n && aligned16(g.pending.relu_y)) {
     mask_y = g.pending.relu_y; g.pending.kind = PEND_NONE;
   } else if (g.pending.kind) { int rc = flush_pending(); if (rc) return rc; }
+  // dx declared unset (ltb_grad_unset): the one-launch kernels write their result instead of adding; the three-kernel path
+  // fills it with zeros first.  dy itself is someone's gradient buffer too: it must hold data by now.
+  { int rc = grad_settle(dy, (size_t)n * 4); if (rc) return rc; }
+  const int fresh = dx && cluster_path && grad_take_unset(dx, (size_t)n * 4) ? 1 : 0;
+  if (dx && !fresh) { int rc = grad_settle(dx, (size_t)n * 4); if (rc) return rc; }
   if (cluster_path) {
     const BnClusterPlan p = bn_cluster_plan(N, C, HW);
     float* dyw = const_cast<float*>(dy);                           // written only when the held ReLU gradient is applied to it
     BnPackedPlan pk;
     if ((p.K == 1 || C >= 96) && bn_packed_plan(N, C, HW, kBnVptBwd, pk)) {
       LTB_LAUNCH(bn_bwd_packed_kernel<kBnVptBwd>, (unsigned)ceil_div(C, pk.G), dim3(pk.T, pk.G), 0, x, dyw, dx, gamma, dgamma, dbeta,
-                 save_mean, save_istd, N, C, HW, mask_y);
+                 save_mean, save_istd, N, C, HW, mask_y, fresh);
       return LTB_OK;
     }
     if (p.per_cta <= kBnVptBwd * p.threads)
       LTB_LAUNCH_CLUSTER(bn_bwd_cluster_kernel<kBnVptBwd>, dim3((unsigned)C * p.K), dim3(p.threads), p.K, x, dyw, dx, gamma, dgamma, dbeta,
-                         save_mean, save_istd, N, C, HW, p.per_cta, mask_y);
+                         save_mean, save_istd, N, C, HW, p.per_cta, mask_y, fresh);
     else
       LTB_LAUNCH_CLUSTER(bn_bwd_cluster_kernel<0>, dim3((unsigned)C * p.K), dim3(p.threads), p.K, x, dyw, dx, gamma, dgamma, dbeta,
-                         save_mean, save_istd, N, C, HW, p.per_cta, mask_y);
+                         save_mean, save_istd, N, C, HW, p.per_cta, mask_y, fresh);
     return LTB_OK;
   }
   LTB_LAUNCH(bn_reduce_kernel<1>, dim3(C, S), 256, 0, x, dy, save_mean, save_istd, g.cur_scratch(), N, C, HW);

@@ -274,7 +274,7 @@ int ltb_rnn_seq_fwd(const float* x, const int32_t* y, const float* h0, const flo
 
 int ltb_rnn_seq_bwd(const float* x, const int32_t* y, const float* h0, const float* Whh, const float* Who, const float* h, const float* logp,
                     const float* dloss, float* dWxh, float* dWhh, float* dbh, float* dWho, float* dbo, int T, int B, int V, int H) {
-  LTB_INITED(); LTB_REQUIRE(x && y && Whh && Who && h && logp && dloss && dWxh && dWhh && dbh && dWho && dbo && T > 0 && B > 0 && V > 0 && H > 0, "ltb_rnn_seq_bwd: bad argument");
+  LTB_INITED(); LTB_SETTLE(dloss); LTB_SETTLE(dWxh); LTB_SETTLE(dWhh); LTB_SETTLE(dbh); LTB_SETTLE(dWho); LTB_SETTLE(dbo); LTB_REQUIRE(x && y && Whh && Who && h && logp && dloss && dWxh && dWhh && dbh && dWho && dbo && T > 0 && B > 0 && V > 0 && H > 0, "ltb_rnn_seq_bwd: bad argument");
   int rows; size_t sf, sb;
   if (!seq_plan(T, B, V, H, &rows, &sf, &sb) || seq_opted_device != g.device) return fail(LTB_E_STATE, "ltb_rnn_seq_bwd: no forward call came before");
   const int ctas = (int)ceil_div(B, rows), n_sums = 2 * V * H + H * H + H + V;

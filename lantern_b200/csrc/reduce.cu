@@ -158,12 +158,12 @@ extern "C" {
 int ltb_sum(const float* x, float* out, int64_t n) { LTB_INITED(); LTB_REQUIRE(x && out && n >= 0, "ltb_sum: bad argument"); return full_sum(x, out, n, 1.0f); }
 int ltb_mean(const float* x, float* out, int64_t n) { LTB_INITED(); LTB_REQUIRE(x && out && n > 0, "ltb_mean: bad argument"); return full_sum(x, out, n, 1.0f / (float)n); }
 int ltb_sum_grad(float* dx, const float* dout, int64_t n) {
-  LTB_INITED(); LTB_REQUIRE(dx && dout && n >= 0, "ltb_sum_grad: bad argument");
+  LTB_INITED(); LTB_SETTLE(dx); LTB_SETTLE(dout); LTB_REQUIRE(dx && dout && n >= 0, "ltb_sum_grad: bad argument");
   if (n) LTB_LAUNCH(add_scalar_from_kernel, grid_for(n, 256), 256, 0, dx, dout, 1.0f, n);
   return LTB_OK;
 }
 int ltb_mean_grad(float* dx, const float* dout, int64_t n) {
-  LTB_INITED(); LTB_REQUIRE(dx && dout && n > 0, "ltb_mean_grad: bad argument");
+  LTB_INITED(); LTB_SETTLE(dx); LTB_SETTLE(dout); LTB_REQUIRE(dx && dout && n > 0, "ltb_mean_grad: bad argument");
   LTB_LAUNCH(add_scalar_from_kernel, grid_for(n, 256), 256, 0, dx, dout, 1.0f / (float)n, n);
   return LTB_OK;
 }
@@ -175,7 +175,7 @@ int ltb_sum_dim(const float* x, float* out, int outer, int d, int inner) {
   return LTB_OK;
 }
 int ltb_sum_dim_grad(float* dx, const float* dout, int outer, int d, int inner) {
-  LTB_INITED(); LTB_REQUIRE(dx && dout && outer > 0 && d > 0 && inner > 0, "ltb_sum_dim_grad: bad argument");
+  LTB_INITED(); LTB_SETTLE(dx); LTB_SETTLE(dout); LTB_REQUIRE(dx && dout && outer > 0 && d > 0 && inner > 0, "ltb_sum_dim_grad: bad argument");
   LTB_LAUNCH(sum_dim_grad_kernel, grid_for((int64_t)outer * d * inner, 256), 256, 0, dx, dout, outer, d, inner);
   return LTB_OK;
 }
@@ -238,11 +238,11 @@ int ltb_log_softmax(const float* x, float* y, int rows, int cols) {
   LTB_LAUNCH(softmax_kernel<1>, (unsigned)ceil_div((int64_t)rows * 32, 256), 256, 0, x, y, rows, cols); return LTB_OK;
 }
 int ltb_softmax_grad(float* dx, const float* y, const float* dy, int rows, int cols) {
-  LTB_INITED(); LTB_REQUIRE(dx && y && dy && rows > 0 && cols > 0, "ltb_softmax_grad: bad argument");
+  LTB_INITED(); LTB_SETTLE(dx); LTB_SETTLE(dy); LTB_REQUIRE(dx && y && dy && rows > 0 && cols > 0, "ltb_softmax_grad: bad argument");
   LTB_LAUNCH(softmax_grad_kernel<0>, (unsigned)ceil_div((int64_t)rows * 32, 256), 256, 0, dx, y, dy, rows, cols); return LTB_OK;
 }
 int ltb_log_softmax_grad(float* dx, const float* y, const float* dy, int rows, int cols) {
-  LTB_INITED(); LTB_REQUIRE(dx && y && dy && rows > 0 && cols > 0, "ltb_log_softmax_grad: bad argument");
+  LTB_INITED(); LTB_SETTLE(dx); LTB_SETTLE(dy); LTB_REQUIRE(dx && y && dy && rows > 0 && cols > 0, "ltb_log_softmax_grad: bad argument");
   LTB_LAUNCH(softmax_grad_kernel<1>, (unsigned)ceil_div((int64_t)rows * 32, 256), 256, 0, dx, y, dy, rows, cols); return LTB_OK;
 }
 // nllLoss / nllLoss_grad: TensorDslCPU.scala:1090-1110.
@@ -251,7 +251,7 @@ int ltb_nll(const float* x, const int32_t* t, float* out, int rows, int cols) {
   LTB_LAUNCH(nll_kernel, (rows + 127) / 128, 128, 0, x, t, out, rows, cols); return LTB_OK;
 }
 int ltb_nll_grad(float* dx, const float* dout, const int32_t* t, int rows, int cols) {
-  LTB_INITED(); LTB_REQUIRE(dx && dout && t && rows > 0 && cols > 0, "ltb_nll_grad: bad argument");
+  LTB_INITED(); LTB_SETTLE(dx); LTB_SETTLE(dout); LTB_REQUIRE(dx && dout && t && rows > 0 && cols > 0, "ltb_nll_grad: bad argument");
   LTB_LAUNCH(nll_grad_kernel, (rows + 127) / 128, 128, 0, dx, dout, t, rows, cols); return LTB_OK;
 }
 
@@ -261,7 +261,7 @@ int ltb_vv_dot(const float* x, const float* y, float* out, int n) {
   LTB_LAUNCH(dot_kernel, 1, 1024, 0, x, y, out, n); return LTB_OK;
 }
 int ltb_vv_dot_grad(float* dx, float* dy, const float* x, const float* y, const float* dout, int n) {
-  LTB_INITED(); LTB_REQUIRE(x && y && dout && n > 0, "ltb_vv_dot_grad: bad argument");
+  LTB_INITED(); LTB_SETTLE(dx); LTB_SETTLE(dy); LTB_SETTLE(dout); LTB_REQUIRE(x && y && dout && n > 0, "ltb_vv_dot_grad: bad argument");
   if (dx) LTB_LAUNCH(axpy_from_scalar_kernel, grid_for(n, 256), 256, 0, dx, y, dout, n);
   if (dy) LTB_LAUNCH(axpy_from_scalar_kernel, grid_for(n, 256), 256, 0, dy, x, dout, n);
   return LTB_OK;
@@ -343,7 +343,7 @@ int ltb_lstm_cell(const float* i, const float* u, const float* fl, const float* 
 int ltb_lstm_cell_grad(const float* i, float* di, const float* u, float* du, const float* fl, float* dfl, const float* cl, float* dcl,
                        const float* fr, float* dfr, const float* cr, float* dcr, const float* o, float* d_o,
                        const float* tc, const float* dc, const float* dh, int n) {
-  LTB_INITED();
+  LTB_INITED(); LTB_SETTLE(di); LTB_SETTLE(du); LTB_SETTLE(dfl); LTB_SETTLE(dcl); LTB_SETTLE(dfr); LTB_SETTLE(dcr); LTB_SETTLE(d_o); LTB_SETTLE(dc); LTB_SETTLE(dh);
   LTB_REQUIRE(i && di && u && du && o && d_o && tc && dc && dh && n > 0, "ltb_lstm_cell_grad: bad argument");
   LTB_REQUIRE((fl && dfl && cl && dcl && fr && dfr && cr && dcr) || (!fl && !dfl && !cl && !dcl && !fr && !dfr && !cr && !dcr),
               "ltb_lstm_cell_grad: the child operands and their gradients go together");
@@ -422,7 +422,7 @@ int ltb_affine_act_rows(const float* x0, const float* W0, int cols0, const float
 int ltb_affine_act_rows_grad(const float* x0, float* dx0, const float* W0, float* dW0, int cols0, const float* x1, float* dx1,
                              const float* W1, float* dW1, int cols1, float* dbias, int act, const float* out, const float* dout,
                              int batch, int width) {
-  LTB_INITED();
+  LTB_INITED(); LTB_SETTLE(dx0); LTB_SETTLE(dW0); LTB_SETTLE(dx1); LTB_SETTLE(dW1); LTB_SETTLE(dbias); LTB_SETTLE(dout);
   LTB_REQUIRE(x0 && W0 && dW0 && dbias && out && dout && cols0 > 0 && batch > 0 && width > 0, "ltb_affine_act_rows_grad: bad argument");
   LTB_REQUIRE((x1 == nullptr) == (W1 == nullptr) && (W1 == nullptr) == (dW1 == nullptr) && (!W1 || cols1 > 0) && (W1 || !dx1),
               "ltb_affine_act_rows_grad: x1, W1 and dW1 go together");
@@ -446,7 +446,7 @@ int ltb_affine_act(const float* W0, const float* a, int cols0, const float* W1, 
 }
 int ltb_affine_act_grad(const float* W0, float* dW0, const float* a, float* da, int cols0, const float* W1, float* dW1,
                         const float* b, float* db, int cols1, float* dbias, int act, const float* out, const float* dout, int rows) {
-  LTB_INITED();
+  LTB_INITED(); LTB_SETTLE(dW0); LTB_SETTLE(da); LTB_SETTLE(dW1); LTB_SETTLE(db); LTB_SETTLE(dbias); LTB_SETTLE(dout);
   LTB_REQUIRE(W0 && dW0 && a && dbias && out && dout && rows > 0 && cols0 > 0, "ltb_affine_act_grad: bad argument");
   LTB_REQUIRE((W1 == nullptr) == (b == nullptr) && (W1 == nullptr) == (dW1 == nullptr) && (!W1 || cols1 > 0), "ltb_affine_act_grad: W1, dW1 and b go together");
   LTB_REQUIRE(act == -1 || act == LTB_TANH || act == LTB_SIGMOID, "ltb_affine_act_grad: activation must be tanh, sigmoid or -1");
@@ -458,11 +458,11 @@ int ltb_mv_dot(const float* a, const float* x, float* out, int m, int k) {
   LTB_LAUNCH(gemv_rows_kernel<false>, (unsigned)ceil_div((int64_t)m * 32, 256), 256, 0, a, x, out, m, k); return LTB_OK;
 }
 int ltb_add_cartesian(float* da, const float* y, const float* dout, int m, int k) {
-  LTB_INITED(); LTB_REQUIRE(da && y && dout && m > 0 && k > 0, "ltb_add_cartesian: bad argument");
+  LTB_INITED(); LTB_SETTLE(da); LTB_SETTLE(dout); LTB_REQUIRE(da && y && dout && m > 0 && k > 0, "ltb_add_cartesian: bad argument");
   LTB_LAUNCH(outer_acc_kernel, grid_for((int64_t)m * k, 256), 256, 0, da, y, dout, m, k); return LTB_OK;
 }
 int ltb_add_composition(float* dx, const float* a, const float* dout, int m, int k) {
-  LTB_INITED(); LTB_REQUIRE(dx && a && dout && m > 0 && k > 0, "ltb_add_composition: bad argument");
+  LTB_INITED(); LTB_SETTLE(dx); LTB_SETTLE(dout); LTB_REQUIRE(dx && a && dout && m > 0 && k > 0, "ltb_add_composition: bad argument");
   LTB_LAUNCH(gemv_cols_kernel, (k + 127) / 128, 128, 0, a, dout, dx, m, k); return LTB_OK;
 }
 

@@ -23,6 +23,7 @@ _SIGS = {
     "model_set_table": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int]),
     "model_use_graph": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int]),
     "model_use_branches": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int]),
+    "model_use_deferred_zero": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int]),
     "model_use_fused_cells": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int]),
     "model_set_resident": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]),
     "model_step": (ctypes.c_float, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_float, ctypes.c_int]),
@@ -215,6 +216,11 @@ class Model:
     def use_branches(self, on=True):
         """Issue independent runs of calls (shortcut convolutions) as branch regions (default) or all in program order."""
         self.hp.fn["model_use_branches"](self.h, int(on))
+
+    def use_deferred_zero(self, on=True):
+        """Large activation gradients are declared unset instead of zero-filled (default); off: every gradient buffer is zeroed
+        when it is allocated, as the reference does.  Applies to every model of this library instance, from the next step on."""
+        self.hp.fn["model_use_deferred_zero"](self.h, int(on))
 
     def use_graph(self, on=True):
         self.hp.fn["model_use_graph"](self.h, int(on))

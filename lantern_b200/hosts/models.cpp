@@ -612,6 +612,9 @@ int HOST_FN(model_use_fused_cells)(void* m, int on) {
   M->fused_cells = on != 0; M->whole_sequence = on >= 2; return 0;
 }
 // Issue independent runs of calls as branch regions (default) or everything in program order on one stream.
+// Large activation gradients declared unset instead of zero-filled (ltb_grad_unset; default on).  Process-wide: it is a property
+// of how the tape allocates, not of one model.
+int HOST_FN(model_use_deferred_zero)(void*, int on) { deferred_grads() = on != 0; return 0; }
 int HOST_FN(model_use_branches)(void* m, int on) {
   Model* M = (Model*)m;
   if (M->graph) { BK(graph_destroy)(M->graph); M->graph = nullptr; }

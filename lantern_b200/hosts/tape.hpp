@@ -52,6 +52,21 @@ inline float* alloc_zero(int64_t n) {
   return (float*)BK(malloc)((size_t)n * 4);
 }
 
+// The gradient buffer of an activation.  Large ones (4 MB and more: the feature maps of the convolutional programs) are not
+// zero-filled but declared unset (ltb_grad_unset): the operator that would be the first to add into the buffer writes it
+// instead, and any other use fills it with zeros first, so results do not depend on the choice.  Off while tracing (the trace
+// reads every buffer) and by deferred_grads() = false.
+inline bool& tracing();
+inline bool& deferred_grads() { static bool on = true; return on; }
+inline float* alloc_grad(int64_t n) {
+  if (n >= (1 << 20) && deferred_grads() && !tracing()) {
+    float* p = alloc_value(n);
+    if (p) BK(grad_unset)(p, n);
+    return p;
+  }
+  return alloc_zero(n);
+}
+
 // Debug trace: when on, every tensor an operator allocates is remembered so that a step can be dumped
 // (per-tensor checksums of value and gradient) and two libraries compared operator by operator.
 inline bool& tracing() { static bool on = false; return on; }
@@ -61,7 +76,7 @@ inline TR traced(const TR& t) { if (tracing()) trace_list().push_back(t); return
 inline TR make(std::initializer_list<int> shp, bool with_grad = true) {
   TR t; t.rank = (int)shp.size(); int i = 0; for (int s : shp) t.shape[i++] = s;
   t.x = alloc_value(t.count());
-  if (with_grad) t.d = alloc_zero(t.count());
+  if (with_grad) t.d = alloc_grad(t.count());
   return traced(t);
 }
 inline TR view(const TR& t, std::initializer_list<int> shp) {   // Tensor.resize: same buffers, new shape
@@ -100,14 +115,14 @@ struct Tape {
       push([=] { BK(unary_grad)(LTB_RELU, in.x, in.d, in.x, in.d, n, 1); });
       return in;
     }
-    TR y = in; y.x = alloc_value(n); y.d = alloc_zero(n); y.is_input = false; traced(y);
+    TR y = in; y.x = alloc_value(n); y.d = alloc_grad(n); y.is_input = false; traced(y);
     BK(unary)(LTB_RELU, in.x, y.x, n);
     push([=] { BK(unary_grad)(LTB_RELU, in.x, in.d, y.x, y.d, n, 0); });
     return y;
   }
   TR unary(int op, const TR& in) {     // tanh / sigmoid / exp / log, TD.scala:1252-1316
     int64_t n = in.count();
-    TR y = in; y.x = alloc_value(n); y.d = alloc_zero(n); y.is_input = false; traced(y);
+    TR y = in; y.x = alloc_value(n); y.d = alloc_grad(n); y.is_input = false; traced(y);
     BK(unary)(op, in.x, y.x, n);
     push([=] { if (!in.is_input) BK(unary_grad)(op, in.x, in.d, y.x, y.d, n, 0); });
     return y;
@@ -140,7 +155,7 @@ struct Tape {
       s.r[i] = s.a[i] > s.b[i] ? s.a[i] : s.b[i];
     }
     TR y; y.rank = rank; for (int i = 0; i < rank; ++i) y.shape[i] = s.r[i];
-    y.x = alloc_value(y.count()); y.d = alloc_zero(y.count()); traced(y);
+    y.x = alloc_value(y.count()); y.d = alloc_grad(y.count()); traced(y);
     BK(ew_binary)(op, a.x, s.a, b.x, s.b, y.x, rank);
     push([=] { BK(ew_binary_grad)(op, a.x, a.is_input ? nullptr : a.d, s.a, b.x, b.is_input ? nullptr : b.d, s.b, y.d, rank); });
     return y;

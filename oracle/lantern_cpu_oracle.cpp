@@ -259,6 +259,10 @@ int ora_sync(void) { ProfScope prof_scope_("ora_sync"); return LTB_OK; }
 int ora_set_deterministic(int) { return LTB_OK; }   // the CPU build always sums in program order
 int ora_set_filter_cache(int) { return LTB_OK; }    // the CPU build reads OIHW filters as they are
 int ora_params_changed(void) { return LTB_OK; }
+// Deferred zero fill: the CPU restatement keeps the reference's plain rule (zeroed memory, every gradient added), so a block
+// declared unset is simply filled with zeros at once and nothing else changes.
+int ora_grad_unset(float* d, int64_t n) { ProfScope prof_scope_("ora_grad_unset"); REQUIRE(d && n > 0, "grad_unset: bad argument"); memset(d, 0, (size_t)n * 4); return LTB_OK; }
+int ora_grad_materialize(float*, int64_t) { return LTB_OK; }
 int ora_set_fusion(int) { ProfScope prof_scope_("ora_set_fusion"); return LTB_OK; }   // the CPU build executes every call at once
 int ora_set_math(int mode) { ProfScope prof_scope_("ora_set_math"); g.math = mode; return LTB_OK; }
 int ora_device_status(void) { return LTB_OK; }

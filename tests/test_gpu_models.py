@@ -166,6 +166,41 @@ def test_deterministic_mode_replays_bit_for_bit(cuda_lib):
         lib.reset(mark)
 
 
+@pytest.mark.parametrize("name,batch", [("resnet50_prefix", 32), ("resnet50", 8), ("squeezenet", 16)])
+def test_deferred_zero_fill_changes_no_bit(cuda_lib, name, batch):
+    """Large activation gradients declared unset (ltb_grad_unset: the first operator to add into them writes instead) against
+    every gradient buffer zero-filled at allocation, the reference's rule: three training steps in deterministic mode,
+    call by call and replayed from a recorded step, end in the same losses and the same parameters, bit for bit (ResNet-50
+    and its first block; SqueezeNet to its own run-to-run spread)."""
+    from lantern_b200.hosts import HostPrograms
+    lib = cuda_lib
+    mark = lib.mark()
+    lib.set_math(1); lib.set_deterministic(1)
+    hp = HostPrograms(lib)
+    try:
+        runs = []
+        for deferred, replay in ((False, False), (True, False), (True, True)):
+            m = hp.model(name, batch, seed=1)
+            m.use_deferred_zero(deferred); m.use_graph(replay)
+            losses = []
+            for s in range(3):
+                x, y = _batch(m, s, "normal")
+                m.step_async(x, y, 0.002); lib.sync(); losses.append(m.last_loss())
+            runs.append((losses, m.slab_params()))
+            m.close(); lib.reset(mark)
+        for losses, params in runs[1:]:
+            assert losses == runs[0][0], (losses, runs[0][0])
+            if name == "squeezenet":       # a few of its layers take CUDA-core paths whose split sums are added atomically: two runs of
+                # the SAME configuration already differ in some fifty parameters by 1e-10 (measured); so a bound, not bit equality
+                assert np.abs(params - runs[0][1]).max() <= 1e-7 * np.abs(runs[0][1]).max()
+            else:
+                assert np.array_equal(params, runs[0][1])
+    finally:
+        hp.fn["model_use_deferred_zero"](None, 1)
+        lib.set_deterministic(0)
+        lib.reset(mark)
+
+
 @pytest.mark.parametrize("batch,math,rtol", [(1, 0, FP32_RTOL), (256, 0, FP32_RTOL), (256, 1, TF32_RTOL)])
 def test_vanilla_rnn_gradients_and_adagrad_trajectory(oracle_lib, cuda_lib, batch, math, rtol):
     """min-char-rnn (vocabulary 80, hidden 100, 20 unrolled steps, batch 1 and 256): every gradient of one step, then

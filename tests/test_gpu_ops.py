@@ -625,6 +625,153 @@ def test_tree_node_and_gradient(ora, gpu, inner, classify_cell, Hd, L):
     check(f, ora, gpu)
 
 
+# ---------------------------------------------------------------------------------------------- deferred zero fill
+def _poisoned(b, shape):
+    """A gradient buffer full of NaN, declared unset: whatever adds into it without reading must leave no NaN behind."""
+    t = b.fromNumpy(np.full(shape, np.nan, np.float32))
+    b.lib.grad_unset(t.ptr, t.scalarCount)
+    return t
+
+
+@pytest.mark.parametrize("math", [0, 1])
+@pytest.mark.parametrize("cfg", [(64, 64, 1, 1, 0, 16, 32), (64, 64, 3, 1, 1, 16, 32), (128, 128, 3, 2, 1, 16, 16), (256, 512, 1, 2, 0, 16, 16),
+                                 (256, 1024, 1, 1, 0, 4, 32), (3, 64, 3, 1, 1, 32, 8), (20, 10, 5, 1, 0, 12, 4)],
+                         ids=lambda c: "%dto%d_k%d_s%d_h%d" % (c[0], c[1], c[2], c[3], c[5]))
+def test_conv_backward_into_an_unset_gradient_buffer(gpu, cfg, math):
+    """ltb_grad_unset: the data gradient of a convolution written into a buffer declared unset (and poisoned with NaN) equals
+    the data gradient added into a zero-filled buffer -- bit for bit in deterministic mode -- on every path: pointwise, tap
+    loop, stride 2 (up-sampled taps and unfold + fold), in-kernel gather, FP32 fallback; and a second backward call into the
+    same buffer adds, as always."""
+    C, K, k, s, p, H, N = cfg
+    b, lib = gpu, gpu.lib
+    lib.set_math(math); lib.set_deterministic(1)
+    try:
+        x0 = R(1).standard_normal((N, C, H, H)).astype(np.float32)
+        w0 = (R(2).standard_normal((K, C, k, k)) / np.sqrt(C * k * k)).astype(np.float32)
+        Ho = (H + 2 * p - k) // s + 1
+        dy0 = R(3).standard_normal((N, K, Ho, Ho)).astype(np.float32)
+        res = []
+        for unset in (False, True):
+            x, w = TensorR(b.fromNumpy(x0)), TensorR(b.fromNumpy(w0))
+            x.d = _poisoned(b, x0.shape) if unset else b.fill(x0.shape, 0.0)
+            w.d = b.fill(w0.shape, 0.0)
+            y = TensorR(b.empty(N, K, Ho, Ho), b.fromNumpy(dy0))
+            b.conv2D_batch_grad(x, None, w, y, None, (p, p), (s, s))
+            once = x.d.toCPU()
+            b.conv2D_batch_grad(x, None, w, y, None, (p, p), (s, s))
+            res.append((once, x.d.toCPU()))
+        assert np.isfinite(res[1][0]).all()
+        assert np.array_equal(res[0][0], res[1][0]) and np.array_equal(res[0][1], res[1][1])
+        assert np.abs(res[0][1]).max() > 1.5 * np.abs(res[0][0]).max() * 0.9          # the second call did add
+    finally:
+        lib.set_deterministic(0); lib.set_math(1)
+
+
+@pytest.mark.parametrize("shape", [(128, 64, 16, 16), (128, 256, 8, 8), (128, 1024, 4, 4), (32, 2048, 2, 2), (8, 5, 3, 3)])
+@pytest.mark.parametrize("with_relu", [False, True])
+def test_batch_norm_backward_into_an_unset_gradient_buffer(gpu, shape, with_relu):
+    """Batch-norm backward (cluster kernels, packed kernels, the three-kernel path for a pixel count that is no multiple of 4),
+    alone and with the held in-place ReLU gradient fused into it: dx written into an unset (NaN-poisoned) buffer equals dx
+    added into zeros, bit for bit; dgamma and dbeta unchanged."""
+    b, lib = gpu, gpu.lib
+    N, C, H, W = shape
+    x0 = R(4).standard_normal(shape).astype(np.float32)
+    dy0 = R(5).standard_normal(shape).astype(np.float32)
+    res = []
+    for unset in (False, True):
+        lib.set_fusion(1 if with_relu else 0)
+        try:
+            x = TensorR(b.fromNumpy(x0))
+            x.d = _poisoned(b, shape) if unset else b.fill(shape, 0.0)
+            gam, bet = TensorR(b.fill((C,), 1.5), b.fill((C,), 0.0)), TensorR(b.fill((C,), 0.1), b.fill((C,), 0.0))
+            rm, rv = b.fill((C,), 0.0), b.fill((C,), 1.0)
+            y, sm, si, _ = b.batchNormTraining(x.x, gam.x, bet.x, rm, rv)
+            yr = TensorR(y, b.fromNumpy(dy0))
+            if with_relu:
+                b.relu(y, inPlace=True)
+                b.relu_grad(yr, yr, inPlace=True)                      # held: the batch-norm backward below applies it
+            b.batchNorm_grad(x, yr, gam, bet, sm, si)
+            lib.sync()
+            res.append((x.d.toCPU(), gam.d.toCPU(), bet.d.toCPU(), yr.d.toCPU()))
+        finally:
+            lib.set_fusion(0)
+    assert np.isfinite(res[1][0]).all()
+    for a, c in zip(res[0], res[1]):
+        assert np.array_equal(a, c)
+
+
+@pytest.mark.parametrize("fused", [False, True])
+def test_add_gradient_into_unset_gradient_buffers(gpu, fused):
+    """The gradient of a same-shape add, plain and with the held in-place ReLU gradient fused in: one destination unset (written),
+    the other holding data (added into); then both unset."""
+    b, lib = gpu, gpu.lib
+    n = (64, 32, 8, 8)
+    y0 = R(6).standard_normal(n).astype(np.float32); d0 = R(7).standard_normal(n).astype(np.float32); pre = R(8).standard_normal(n).astype(np.float32)
+    res = []
+    for unset in (False, True):
+        lib.set_fusion(1 if fused else 0)
+        try:
+            out = []
+            for both in (False, True):
+                y = TensorR(b.fromNumpy(y0), b.fromNumpy(d0))
+                a = TensorR(b.fromNumpy(y0)); c = TensorR(b.fromNumpy(y0))
+                a.d = _poisoned(b, n) if unset else b.fill(n, 0.0)
+                c.d = (_poisoned(b, n) if unset else b.fill(n, 0.0)) if both else b.fromNumpy(pre)
+                if fused:
+                    b.relu_grad(y, y, inPlace=True)
+                sh = np.array(n, np.int32)
+                lib.ew_binary_grad(0, a.x.ptr, a.d.ptr, sh.ctypes.data, c.x.ptr, c.d.ptr, sh.ctypes.data, y.d.ptr, 4)
+                lib.sync()
+                out += [a.d.toCPU(), c.d.toCPU(), y.d.toCPU()]
+            res.append(out)
+        finally:
+            lib.set_fusion(0)
+    for a, c in zip(res[0], res[1]):
+        assert np.isfinite(c).all() and np.array_equal(a, c)
+
+
+def test_unset_buffers_are_zero_to_everything_else(gpu):
+    """Entry points that cannot write instead of adding fill an unset block with zeros first: max-pool and average-pool
+    backward, an activation's gradient, the transfers, ltb_grad_materialize; a part of a block is never taken as the whole;
+    ltb_reset forgets declarations of blocks above the mark."""
+    b, lib = gpu, gpu.lib
+    x0 = R(9).standard_normal((4, 8, 8, 8)).astype(np.float32)
+    x = b.fromNumpy(x0)
+    y, idx = b.maxPool2D_batch(x, (2, 2), (2, 2))
+    dy = b.fromNumpy(R(10).standard_normal((4, 8, 4, 4)).astype(np.float32))
+    ref, got = TensorR(x, b.fill(x0.shape, 0.0)), TensorR(x, _poisoned(b, x0.shape))
+    for t in (ref, got):
+        b.maxPool2D_batch_grad(t, TensorR(y, dy), idx)
+    assert np.array_equal(ref.d.toCPU(), got.d.toCPU())
+    ref, got = TensorR(x, b.fill(x0.shape, 0.0)), TensorR(x, _poisoned(b, x0.shape))
+    ya = b.averagePool2D_batch(x, (2, 2), (2, 2))
+    for t in (ref, got):
+        b.averagePool2D_batch_grad(t, TensorR(ya, dy), (2, 2), (2, 2))
+    assert np.array_equal(ref.d.toCPU(), got.d.toCPU())
+    ref, got = b.fill(x0.shape, 0.0), _poisoned(b, x0.shape)
+    for d in (ref, got):
+        lib.unary_grad(1, x.ptr, d.ptr, x.ptr, x.ptr, x.scalarCount, 0)            # tanh'(y) * dy added into d
+    assert np.array_equal(ref.toCPU(), got.toCPU())
+    assert not _poisoned(b, (1000,)).toCPU().any()                                  # a read-back sees zeros
+    t = _poisoned(b, (1000,)); lib.grad_materialize(t.ptr, 1000)
+    assert not t.toCPU().any()
+    # a part of a declared block: conv backward into the first half of a buffer must not leave the second half unset and undefined
+    big = _poisoned(b, (2, 4, 16, 8, 8))
+    w = TensorR(b.fromNumpy((R(11).standard_normal((8, 16, 1, 1)) / 4).astype(np.float32))); w.d = b.fill((8, 16, 1, 1), 0.0)
+    from lantern_b200.backend import Tensor
+    half = Tensor(b, big.ptr, (4, 16, 8, 8))
+    xin = TensorR(b.fromNumpy(R(12).standard_normal((4, 16, 8, 8)).astype(np.float32)), half)
+    yout = TensorR(b.empty(4, 8, 8, 8), b.fromNumpy(R(13).standard_normal((4, 8, 8, 8)).astype(np.float32)))
+    b.conv2D_batch_grad(xin, None, w, yout, None, (0, 0), (1, 1))
+    whole = big.toCPU()
+    assert np.isfinite(whole).all() and whole[0].any() and not whole[1].any()
+    mark = lib.mark()
+    t = _poisoned(b, (4096,))
+    lib.reset(mark)
+    t2 = b.fromNumpy(np.full((4096,), 3.0, np.float32))                              # the same address, now an ordinary tensor
+    assert t2.ptr == t.ptr and np.array_equal(t2.toCPU(), np.full((4096,), 3.0, np.float32))
+
+
 # ---------------------------------------------------------------------------------------------- branch regions
 @pytest.mark.parametrize("replay", [False, True])
 def test_branch_region_gives_the_results_of_program_order(gpu, replay):
