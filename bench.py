@@ -72,7 +72,9 @@ def hbm_bound_bytes(batch):
       relu_add_grad  ReLU gradient + residual-add gradient                y, d r/w, da r/w, db r/w      28 B / element
                      Gradient buffers of 2^20 elements and more are not zero-filled but written by the first operator that
                      would add into them (ltb_grad_unset: the host program's default), so for those tensors dx, da and db
-                     are written only: 12 (20) and 20 B / element.
+                     are written only: 12 (20) and 20 B / element.  At fusion level 2 (the host program's default) an absorbed
+                     ReLU gradient is not written back: 4 B / element less for the batch norms that absorb one (except the
+                     two-sweep kernel of the 33 MB maps) and for relu_add_grad.
       map_vec4       residual add + ReLU                                  a, b, out                     12 B / element
       maxpool_*      2x2 max pool forward (x, y, idx) and backward        6 and 10 B / input element
       sgd_*          x -= lr d; d = 0                                     16 B / parameter"""
@@ -96,7 +98,9 @@ def hbm_bound_bytes(batch):
     add_grad_bytes = float(sum((20.0 if big(batch * c * h * h) else 28.0) * batch * c * h * h * n for (c, h, n) in add_shapes))
     pool_in = batch * 64 * 32 * 32
     params = 23520842
-    return {"bn_fwd": 8.0 * bn_all, "bn_bwd": bn_bwd_bytes + 8.0 * relu_bn, "relu_add_grad": add_grad_bytes, "map_vec4": 12.0 * adds,
+    add_grad_bytes -= 4.0 * adds                    # level 2: d is not rewritten
+    two_sweep = float(batch * 64 * 32 * 32)         # the stem's map: its masked gradient is still written back
+    return {"bn_fwd": 8.0 * bn_all, "bn_bwd": bn_bwd_bytes + 4.0 * relu_bn + 4.0 * two_sweep, "relu_add_grad": add_grad_bytes, "map_vec4": 12.0 * adds,
             "maxpool_fwd": 6.0 * pool_in, "maxpool_bwd": 10.0 * pool_in, "sgd": 16.0 * params}
 
 

@@ -72,7 +72,11 @@ int    LTB_FN(set_math)(int mode);                      /* LTB_MATH_TF32 (defaul
  * in-place ReLU of their result joins the same kernel, and an in-place ReLU gradient is held so that the batch-norm
  * backward or add gradient that reads it applies it on the fly. Results are those of the separate calls; only the moment
  * of the launch moves: a held operation is issued by the next call of this library whatever it is (sync, copies,
- * get_stream and graph_end included). A host that enqueues its own work on the stream must call get_stream or sync first. */
+ * get_stream and graph_end included). A host that enqueues its own work on the stream must call get_stream or sync first.
+ * Level 2: in addition the caller declares that the gradient buffer an in-place ReLU gradient works on is not read again
+ * after the batch-norm backward or add gradient that absorbed it (true of every staged program: that operator is the
+ * buffer's only reader).  The absorbing kernel then applies the mask on load only and no longer writes the masked gradient
+ * back into that buffer; every result (dx, dgamma, dbeta, da, db) is unchanged. */
 int    LTB_FN(set_fusion)(int on);
 /* Filter cache, off by default (no counterpart in the reference, where cuDNN reads OIHW filters as they are). The tensor-core
  * engine reads the filter of an R x S convolution as one matrix per tap; forward and data-grad each need their own form, and

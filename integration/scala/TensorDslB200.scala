@@ -66,13 +66,15 @@ trait TensorDslB200 extends TensorDslCublas {
     private def product(xs: Seq[Rep[Int]]): Rep[Int] = xs.foldLeft(unit(1)) { case (a, b) => a * b }
 
     // ---- lifetime, arena, initialisation (TensorDifferentiation.scala:139-179) ---------------------------------------
-    // ltb_set_fusion(1): every device operation of a staged program goes through this library, so its one-call look-ahead
-    // (batch norm or add joined by the in-place ReLU that follows, and the mirror image in backward) is safe.
+    // ltb_set_fusion(2): every device operation of a staged program goes through this library, so its one-call look-ahead
+    // (batch norm or add joined by the in-place ReLU that follows, and the mirror image in backward) is safe; and in
+    // reverse-mode code the gradient of a tensor is read by the backward code of its producer only, so the buffer that an
+    // absorbed in-place ReLU gradient works on has no reader left (level 2: the mask is applied on load, not written back).
     // ltb_set_filter_cache(1): a staged program writes its filters only through the optimizer, transfer and fill entry
     // points, which is what the cache of per-tap filter forms relies on.
     override def setup(): Unit = {
       ltb("init", 0, "HEAP_SIZE")
-      ltb("set_fusion", 1)
+      ltb("set_fusion", 2)
       ltb("set_filter_cache", 1)
     }
     override def cleanup(): Unit = ltb("shutdown")

@@ -64,6 +64,7 @@ struct Context {
   bool deterministic = false;         // split-K sums in a fixed order (clusters, slabs) instead of atomics (ltb_set_deterministic)
   bool filter_cache = false;          // per-tap filter forms kept across calls (ltb_set_filter_cache)
   bool fusion = false;                // look-ahead fusion of BN/add with ReLU (off unless the host opts in)
+  bool fusion_no_writeback = false;   // level 2: an absorbed in-place ReLU gradient is applied on load only (its buffer is dead afterwards)
   Pending pending;
   bool hold_workspace = false;        // while two halves are in flight their staging blocks are released together at the end
   // Branch region (ltb_branch_mark .. ltb_branch_join): a run of calls issued on a third stream beside the caller's.

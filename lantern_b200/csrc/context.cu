@@ -154,7 +154,7 @@ static int stream_wait(const char* what) {
   return LTB_OK;
 }
 int ltb_sync(void) { LTB_INITED(); return stream_wait("ltb_sync"); }
-int ltb_set_fusion(int on) { LTB_INITED(); g.fusion = on != 0; return LTB_OK; }
+int ltb_set_fusion(int on) { LTB_INITED(); g.fusion = on != 0; g.fusion_no_writeback = on >= 2; return LTB_OK; }
 int ltb_set_filter_cache(int on) {
   LTB_INITED(); LTB_REQUIRE(!g.capturing, "ltb_set_filter_cache: not while recording a step");
   if (!on && g.filter_cache) { cudaStreamSynchronize(g.stream); cudaStreamSynchronize(g.side); cudaStreamSynchronize(g.branch); filter_cache_clear(); }

@@ -282,21 +282,22 @@ int flush_pending() {
   }
 }
 // The held in-place ReLU gradient and the gradient of a same-shape add in one pass:
-// m = y > 0 ? d : 0;  d = m;  da += m;  db += m   (da, db nullable; fa / fb: that destination holds nothing yet and is written).
+// m = y > 0 ? d : 0;  d = m;  da += m;  db += m   (da, db nullable; fa / fb: that destination holds nothing yet and is written; wb == 0: d itself is not
+// rewritten, its owner has declared it dead).
 // n4 float4 items, then a scalar tail from `tail`.
-__global__ void relu_add_grad_kernel(const float* __restrict__ y, float* d, float* da, float* db, int64_t n4, int64_t tail, int64_t n, int fa, int fb) {
+__global__ void relu_add_grad_kernel(const float* __restrict__ y, float* d, float* da, float* db, int64_t n4, int64_t tail, int64_t n, int fa, int fb, int wb) {
   const int64_t i0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t i = i0; i < n4; i += stride) {
     const float4 yv = reinterpret_cast<const float4*>(y)[i];
     float4 m = reinterpret_cast<const float4*>(d)[i];
     m.x = yv.x > 0.0f ? m.x : 0.0f; m.y = yv.y > 0.0f ? m.y : 0.0f; m.z = yv.z > 0.0f ? m.z : 0.0f; m.w = yv.w > 0.0f ? m.w : 0.0f;
-    reinterpret_cast<float4*>(d)[i] = m;
+    if (wb) reinterpret_cast<float4*>(d)[i] = m;
     if (da) { float4 v = fa ? make_float4(0.f, 0.f, 0.f, 0.f) : reinterpret_cast<float4*>(da)[i]; v.x += m.x; v.y += m.y; v.z += m.z; v.w += m.w; reinterpret_cast<float4*>(da)[i] = v; }
     if (db) { float4 v = fb ? make_float4(0.f, 0.f, 0.f, 0.f) : reinterpret_cast<float4*>(db)[i]; v.x += m.x; v.y += m.y; v.z += m.z; v.w += m.w; reinterpret_cast<float4*>(db)[i] = v; }
   }
   for (int64_t i = tail + i0; i < n; i += stride) {
     const float m = y[i] > 0.0f ? d[i] : 0.0f;
-    d[i] = m;
+    if (wb) d[i] = m;
     if (da) da[i] = fa ? m : da[i] + m;
     if (db) db[i] = fb ? m : db[i] + m;
   }
@@ -354,7 +355,7 @@ int ltb_ew_binary_grad(int op, const float* a, float* da, const int* as, const f
     // a destination declared unset (ltb_grad_unset) is written instead of added into; da == db stays an accumulation
     const int fa = da && da != db && grad_take_unset(da, (size_t)n * 4) ? 1 : 0, fb = db && da != db && grad_take_unset(db, (size_t)n * 4) ? 1 : 0;
     LTB_SETTLE(d); if (!fa) LTB_SETTLE(da); if (!fb) LTB_SETTLE(db);
-    LTB_LAUNCH(relu_add_grad_kernel, grid_for(n4 ? n4 : n, 256), 256, 0, y, d, da, db, n4, n4 * 4, n, fa, fb);
+    LTB_LAUNCH(relu_add_grad_kernel, grid_for(n4 ? n4 : n, 256), 256, 0, y, d, da, db, n4, n4 * 4, n, fa, fb, g.fusion_no_writeback ? 0 : 1);
     return LTB_OK;
   }
   if (g.pending.kind) { int rc = flush_pending(); if (rc) return rc; }

@@ -353,7 +353,7 @@ __global__ void __launch_bounds__(512, 2) bn_bwd_cluster_kernel(const float* __r
         const int n = t / hw4, i = t - n * hw4;
         const int64_t off = ((int64_t)n * C + c) * HW;
         kx[j] = reinterpret_cast<const float4*>(x + off)[i]; kd[j] = reinterpret_cast<const float4*>(dy + off)[i];
-        if (mask_y) { kd[j] = relu_mask(kd[j], reinterpret_cast<const float4*>(mask_y + off)[i]); reinterpret_cast<float4*>(dy + off)[i] = kd[j]; }
+        if (mask_y) { kd[j] = relu_mask(kd[j], reinterpret_cast<const float4*>(mask_y + off)[i]); if (!(fresh & 2)) reinterpret_cast<float4*>(dy + off)[i] = kd[j]; }
       }
     }
 #pragma unroll
@@ -372,7 +372,7 @@ __global__ void __launch_bounds__(512, 2) bn_bwd_cluster_kernel(const float* __r
       const int64_t off = ((int64_t)n * C + c) * HW;
       const float4 v = reinterpret_cast<const float4*>(x + off)[i];
       float4 d = reinterpret_cast<const float4*>(dy + off)[i];
-      if (mask_y) { d = relu_mask(d, reinterpret_cast<const float4*>(mask_y + off)[i]); reinterpret_cast<float4*>(dy + off)[i] = d; }
+      if (mask_y) { d = relu_mask(d, reinterpret_cast<const float4*>(mask_y + off)[i]); reinterpret_cast<float4*>(dy + off)[i] = d; }   // always written: the second sweep below reads dy again
       a += (d.x + d.y) + (d.z + d.w);
       b += (d.x * ((v.x - mu) * is) + d.y * ((v.y - mu) * is)) + (d.z * ((v.z - mu) * is) + d.w * ((v.w - mu) * is));
     }
@@ -395,7 +395,7 @@ __global__ void __launch_bounds__(512, 2) bn_bwd_cluster_kernel(const float* __r
 #pragma unroll
     for (int j = 0; j < VPT; ++j) {
       const int t = begin + j * (int)blockDim.x + (int)threadIdx.x;
-      if (t < end) { const int n = t / hw4, i = t - n * hw4; o[j] = fresh ? make_float4(0.f, 0.f, 0.f, 0.f) : reinterpret_cast<const float4*>(dx + ((int64_t)n * C + c) * HW)[i]; }   // fresh: dx holds nothing yet, the result is written
+      if (t < end) { const int n = t / hw4, i = t - n * hw4; o[j] = (fresh & 1) ? make_float4(0.f, 0.f, 0.f, 0.f) : reinterpret_cast<const float4*>(dx + ((int64_t)n * C + c) * HW)[i]; }   // bit 0 of fresh: dx holds nothing yet, the result is written (bit 1: an absorbed ReLU gradient is not written back)
     }
 #pragma unroll
     for (int j = 0; j < VPT; ++j) {
@@ -415,7 +415,7 @@ __global__ void __launch_bounds__(512, 2) bn_bwd_cluster_kernel(const float* __r
       const int n = t / hw4, i = t - n * hw4;
       const int64_t off = ((int64_t)n * C + c) * HW;
       const float4 v = reinterpret_cast<const float4*>(x + off)[i], d = reinterpret_cast<const float4*>(dy + off)[i];
-      float4 o = fresh ? make_float4(0.f, 0.f, 0.f, 0.f) : reinterpret_cast<float4*>(dx + off)[i];
+      float4 o = (fresh & 1) ? make_float4(0.f, 0.f, 0.f, 0.f) : reinterpret_cast<float4*>(dx + off)[i];
       o.x += ca * (d.x - cb - (v.x - mu) * is * cc); o.y += ca * (d.y - cb - (v.y - mu) * is * cc);
       o.z += ca * (d.z - cb - (v.z - mu) * is * cc); o.w += ca * (d.w - cb - (v.w - mu) * is * cc);
       reinterpret_cast<float4*>(dx + off)[i] = o;
@@ -527,7 +527,7 @@ __global__ void __launch_bounds__(512, 2) bn_bwd_packed_kernel(const float* __re
       const int n = t / hw4, i = t - n * hw4;
       const int64_t off = ((int64_t)n * C + c) * HW;
       kx[j] = reinterpret_cast<const float4*>(x + off)[i]; kd[j] = reinterpret_cast<const float4*>(dy + off)[i];
-      if (mask_y) { kd[j] = relu_mask(kd[j], reinterpret_cast<const float4*>(mask_y + off)[i]); reinterpret_cast<float4*>(dy + off)[i] = kd[j]; }
+      if (mask_y) { kd[j] = relu_mask(kd[j], reinterpret_cast<const float4*>(mask_y + off)[i]); if (!(fresh & 2)) reinterpret_cast<float4*>(dy + off)[i] = kd[j]; }
     }
   }
 #pragma unroll
@@ -549,7 +549,7 @@ __global__ void __launch_bounds__(512, 2) bn_bwd_packed_kernel(const float* __re
 #pragma unroll
   for (int j = 0; j < VPT; ++j) {
     const int t = j * T + (int)threadIdx.x;
-    if (t < total) { const int n = t / hw4, i = t - n * hw4; o[j] = fresh ? make_float4(0.f, 0.f, 0.f, 0.f) : reinterpret_cast<const float4*>(dx + ((int64_t)n * C + c) * HW)[i]; }
+    if (t < total) { const int n = t / hw4, i = t - n * hw4; o[j] = (fresh & 1) ? make_float4(0.f, 0.f, 0.f, 0.f) : reinterpret_cast<const float4*>(dx + ((int64_t)n * C + c) * HW)[i]; }
   }
 #pragma unroll
   for (int j = 0; j < VPT; ++j) {
@@ -673,8 +673,8 @@ int ltb_bn_bwd(const float* x, float* dx, const float* dy, const float* gamma, f
   // dx declared unset (ltb_grad_unset): the one-launch kernels write their result instead of adding; the three-kernel path
   // fills it with zeros first.  dy itself is someone's gradient buffer too: it must hold data by now.
   { int rc = grad_settle(dy, (size_t)n * 4); if (rc) return rc; }
-  const int fresh = dx && cluster_path && grad_take_unset(dx, (size_t)n * 4) ? 1 : 0;
-  if (dx && !fresh) { int rc = grad_settle(dx, (size_t)n * 4); if (rc) return rc; }
+  const int fresh = (dx && cluster_path && grad_take_unset(dx, (size_t)n * 4) ? 1 : 0) | (mask_y && g.fusion_no_writeback ? 2 : 0);
+  if (dx && !(fresh & 1)) { int rc = grad_settle(dx, (size_t)n * 4); if (rc) return rc; }
   if (cluster_path) {
     const BnClusterPlan p = bn_cluster_plan(N, C, HW);
     float* dyw = const_cast<float*>(dy);                           // written only when the held ReLU gradient is applied to it

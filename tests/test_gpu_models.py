@@ -189,7 +189,7 @@ def test_deferred_zero_fill_changes_no_bit(cuda_lib, name, batch):
             runs.append((losses, m.slab_params()))
             m.close(); lib.reset(mark)
         for losses, params in runs[1:]:
-            assert losses == runs[0][0], (losses, runs[0][0])
+            assert np.allclose(losses, runs[0][0], rtol=1e-6, atol=0) if name == "squeezenet" else losses == runs[0][0], (losses, runs[0][0])
             if name == "squeezenet":       # a few of its layers take CUDA-core paths whose split sums are added atomically: two runs of
                 # the SAME configuration already differ in some fifty parameters by 1e-10 (measured); so a bound, not bit equality
                 assert np.abs(params - runs[0][1]).max() <= 1e-7 * np.abs(runs[0][1]).max()

@@ -625,6 +625,39 @@ def test_tree_node_and_gradient(ora, gpu, inner, classify_cell, Hd, L):
     check(f, ora, gpu)
 
 
+@pytest.mark.parametrize("shape", [(128, 64, 16, 16), (128, 1024, 4, 4), (256, 64, 32, 32)])
+def test_fusion_level_two_changes_no_result(gpu, shape):
+    """ltb_set_fusion(2): the batch-norm backward / add gradient that absorbs a held in-place ReLU gradient applies the mask on
+    load and does not write the masked gradient back into the (dead) buffer.  dx, dgamma, dbeta, da and db are those of level
+    1, bit for bit -- for the register-resident kernels, the packed kernels and the two-sweep kernel of the largest maps --
+    and only the dead buffer itself may differ."""
+    b, lib = gpu, gpu.lib
+    N, C, H, W = shape
+    x0 = R(14).standard_normal(shape).astype(np.float32); dy0 = R(15).standard_normal(shape).astype(np.float32)
+    res = []
+    for level in (1, 2):
+        lib.set_fusion(level)
+        try:
+            x = TensorR(b.fromNumpy(x0)); x.d = b.fill(shape, 0.0)
+            gam, bet = TensorR(b.fill((C,), 1.5), b.fill((C,), 0.0)), TensorR(b.fill((C,), 0.1), b.fill((C,), 0.0))
+            y, sm, si, _ = b.batchNormTraining(x.x, gam.x, bet.x, b.fill((C,), 0.0), b.fill((C,), 1.0))
+            yr = TensorR(y, b.fromNumpy(dy0))
+            b.relu(y, inPlace=True)
+            b.relu_grad(yr, yr, inPlace=True)
+            b.batchNorm_grad(x, yr, gam, bet, sm, si)
+            # the add gradient absorbing the ReLU gradient of its output
+            z = TensorR(b.fromNumpy(x0), b.fromNumpy(dy0)); a = TensorR(b.fromNumpy(x0), b.fill(shape, 0.0)); c = TensorR(b.fromNumpy(x0), b.fromNumpy(dy0 * 0.5))
+            b.relu_grad(z, z, inPlace=True)
+            sh = np.array(shape, np.int32)
+            lib.ew_binary_grad(0, a.x.ptr, a.d.ptr, sh.ctypes.data, c.x.ptr, c.d.ptr, sh.ctypes.data, z.d.ptr, 4)
+            lib.sync()
+            res.append([x.d.toCPU(), gam.d.toCPU(), bet.d.toCPU(), a.d.toCPU(), c.d.toCPU()])
+        finally:
+            lib.set_fusion(0)
+    for u, v in zip(res[0], res[1]):
+        assert np.array_equal(u, v)
+
+
 # ---------------------------------------------------------------------------------------------- deferred zero fill
 def _poisoned(b, shape):
     """A gradient buffer full of NaN, declared unset: whatever adds into it without reading must leave no NaN behind."""
