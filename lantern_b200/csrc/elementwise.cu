@@ -496,7 +496,13 @@ int ltb_concat_grad(float* const* dinputs, const float* dout, const int* dims, i
   int64_t off = 0;
   for (int k = 0; k < n_inputs; ++k) {
     int64_t len = (int64_t)dims[k] * inner;
-    if (dinputs[k]) { LTB_SETTLE(dinputs[k]); int rc = copy_rows<true>(dinputs[k], len, dout + off, total * inner, len, outer); if (rc) return rc; }
+    if (dinputs[k]) {
+      // an input's gradient buffer declared unset (ltb_grad_unset) is written, any other is added into
+      const bool fresh = grad_take_unset(dinputs[k], (size_t)len * outer * 4);
+      if (!fresh) LTB_SETTLE(dinputs[k]);
+      int rc = fresh ? copy_rows<false>(dinputs[k], len, dout + off, total * inner, len, outer) : copy_rows<true>(dinputs[k], len, dout + off, total * inner, len, outer);
+      if (rc) return rc;
+    }
     off += len;
   }
   return LTB_OK;
