@@ -128,3 +128,21 @@ def test_rnn_whole_sequence_call_equals_operator_by_operator(oracle_lib):
     assert abs(res[0][0] - res[1][0]) <= 1e-6 * abs(res[1][0])
     for a, b in zip(res[0][1], res[1][1]):
         assert np.abs(a - b).max() <= 2e-5 * max(np.abs(b).max(), 1e-12)
+
+
+def test_deferred_zero_fill_is_invisible_on_the_oracle(oracle_lib):
+    """The host programs declare large activation gradients unset (grad_unset) instead of taking them zero-filled; the CPU
+    restatement keeps the reference's plain rule (it fills such a block with zeros at once), so a SqueezeNet step at batch 16
+    (feature maps of 1.5 M floats and more) gives the same loss and the same gradients either way, bit for bit."""
+    mark = oracle_lib.mark()
+    rng = np.random.default_rng(3)
+    x = rng.standard_normal(16 * 3072).astype(np.float32); y = rng.integers(0, 10, 16).astype(np.int32)
+    res = []
+    for deferred in (True, False):
+        m = _model(oracle_lib, "squeezenet", 16)
+        m.use_deferred_zero(deferred)
+        loss = m.step(x, y, 0.0, update=False)
+        res.append((loss, m.slab_grads()))
+        m.use_deferred_zero(True)
+        m.close(); oracle_lib.reset(mark)
+    assert res[0][0] == res[1][0] and np.array_equal(res[0][1], res[1][1])
