@@ -1,6 +1,8 @@
 // Planner of the TF32 tensor-core engine: see tc_plan.h.  Pure host code.
 #include "tc_plan.h"
 
+#include <cstdio>
+#include <cstdlib>
 #include <cstring>
 
 namespace ltb {
@@ -210,7 +212,25 @@ bool operand_mn_window(TcOperand& o, const float* act, int n_img, int eh, int ew
 // Tile width.  The MMA-issuing thread spends a few hundred cycles per k-iteration whatever the width, so narrow tiles
 // leave the tensor core idle; 128 columns with three stages lets two CTAs share an SM (one's epilogue and issue gaps
 // overlap the other's main loop).  Parallelism for small outputs comes from split-K, not from narrower tiles.
-int pick_bn(int n_extent, int, int) { return n_extent > 64 ? 128 : 64; }
+// Split policy knobs, read once from LTB_SPLIT="fill,min_iters,prefer64" (a sweep aid; the defaults are the measured optimum):
+// fill = CTAs per SM that split-K aims for (x 100), min_iters = fewest k-iterations a split may have, prefer64 = 64-wide tiles
+// whenever 128-wide ones would not cover the SMs.
+struct SplitKnobs { int fill100 = 100, min_iters = 8, prefer64 = 0; };
+const SplitKnobs& split_knobs() {
+  static SplitKnobs k = [] {
+    SplitKnobs v;
+    if (const char* e = std::getenv("LTB_SPLIT")) std::sscanf(e, "%d,%d,%d", &v.fill100, &v.min_iters, &v.prefer64);
+    if (v.fill100 < 10) v.fill100 = 10;
+    if (v.min_iters < 1) v.min_iters = 1;
+    return v;
+  }();
+  return k;
+}
+int pick_bn(int n_extent, int m_tiles, int sm_count) {
+  if (n_extent <= 64) return 64;
+  if (split_knobs().prefer64 && (int64_t)m_tiles * cdiv(n_extent, 128) * 10 < (int64_t)8 * sm_count) return 64;
+  return 128;
+}
 
 void finish(TcPlan& p, int M, int N, int k_iters, int sm_count, bool may_split) {
   p.M = M; p.N = N; p.k_iters = k_iters;
@@ -221,8 +241,8 @@ void finish(TcPlan& p, int M, int N, int k_iters, int sm_count, bool may_split) 
     // Split-K pays with atomic traffic (splits x the output) and a zero-fill, so it is used sparingly: measured on the
     // ResNet-50 layer set, the best step time comes from about one CTA per SM, at least eight k-iterations per split, and
     // no split at all once the tiles alone cover 80 % of the SMs (two CTAs per SM with four iterations each was 6 % slower).
-    int s = cdiv(sm_count, tiles);
-    int mx = k_iters / 8; if (mx < 1) mx = 1;
+    int s = cdiv(sm_count * split_knobs().fill100 / 100, tiles);
+    int mx = k_iters / split_knobs().min_iters; if (mx < 1) mx = 1;
     if (s > mx) s = mx;
     if ((int64_t)tiles * 10 >= (int64_t)8 * sm_count) s = 1;
     p.splits = s < 1 ? 1 : s;
