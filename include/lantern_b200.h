@@ -149,6 +149,14 @@ int   LTB_FN(d2h_async)(void* dst_pinned, const void* src, size_t bytes);
  * ltb_sync after every step.  Not allowed while recording a step. */
 int   LTB_FN(marker_record)(int slot);
 int   LTB_FN(marker_wait)(int slot);
+/* Uploads beside the compute work (no counterpart in the reference, whose training loops upload on the one stream and block,
+ * resnet50FromOnnx.scala:173-186).  upload copies from pinned host memory on the library's copy stream; it starts after
+ * marker `after` (-1: at once) -- the point of the compute stream up to which the destination was still being read.
+ * upload_marker records a marker on the copy stream (marker_wait on it tells the host that the staging buffer is free
+ * again); stream_wait_marker makes the compute stream wait for a marker on the device without blocking the host. */
+int   LTB_FN(upload)(void* dst, const void* src, size_t bytes, int after);
+int   LTB_FN(upload_marker)(int slot);
+int   LTB_FN(stream_wait_marker)(int slot);
 
 /* Fused affine map with activation on vectors, for the recursive models (one LSTM gate per call instead of five).  The
  * Backend trait has no such method; the reference fuses the same expression for its CPU backend only (Tensor.linearTanh /

@@ -58,6 +58,7 @@ struct Context {
   bool profiling = false;             // per-launch CUDA-event timing (ltb_profile)
   const char* label = nullptr;        // optional name override for the next launches
   cudaStream_t side = nullptr;        // second stream: the weight-gradient half of conv backward runs beside the data-gradient half
+  cudaStream_t copy = nullptr;        // uploads beside the compute work (ltb_upload)
   cudaEvent_t fork_ev = nullptr, join_ev = nullptr;
   unsigned tune = 0;                  // LTB_TUNE (environment, read by ltb_init): switches single optimisations off for A/B measurements:
                                       // 1 no in-kernel gather, 2 no tap-loop weight-grad from kept copies, 4 no kept copies, 8 no early first loads, 32 deferred zero fill off (ltb_grad_unset fills at once)

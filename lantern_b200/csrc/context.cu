@@ -66,6 +66,7 @@ static void release_all() {
   if (g.scratch) cudaFree(g.scratch);
   if (g.host_status) cudaFreeHost(g.host_status);
   if (g.side) cudaStreamDestroy(g.side);
+  if (g.copy) { cudaStreamSynchronize(g.copy); cudaStreamDestroy(g.copy); }
   if (g.fork_ev) cudaEventDestroy(g.fork_ev);
   if (g.join_ev) cudaEventDestroy(g.join_ev);
   if (g.own_stream && g.stream) cudaStreamDestroy(g.stream);
@@ -99,6 +100,7 @@ static int init_steps(int device, size_t heap_bytes) {
   g.scratch_bytes = (size_t)8 << 20;
   LTB_CUDA(cudaMalloc((void**)&g.scratch, g.scratch_bytes));
   LTB_CUDA(cudaStreamCreateWithFlags(&g.side, cudaStreamNonBlocking));
+  LTB_CUDA(cudaStreamCreateWithFlags(&g.copy, cudaStreamNonBlocking));
   LTB_CUDA(cudaEventCreateWithFlags(&g.fork_ev, cudaEventDisableTiming));
   LTB_CUDA(cudaEventCreateWithFlags(&g.join_ev, cudaEventDisableTiming));
   LTB_CUDA(cudaStreamCreateWithFlags(&g.branch, cudaStreamNonBlocking));
@@ -312,6 +314,32 @@ int ltb_marker_record(int slot) {
   if (!marker_ev[slot]) LTB_CUDA(cudaEventCreateWithFlags(&marker_ev[slot], cudaEventDisableTiming));
   LTB_CUDA(cudaEventRecord(marker_ev[slot], g.stream));
   marker_set[slot] = true;
+  return LTB_OK;
+}
+// Uploads beside the compute work.  ltb_upload copies from (pinned) host memory on the library's copy stream, after marker
+// `after` if one is named (the point of the compute stream up to which the destination was still being read); ltb_upload_marker
+// records a marker on the copy stream (the uploads so far are done when it is reached); ltb_stream_wait_marker makes the
+// COMPUTE stream wait for a marker on the device, without blocking the host.
+int ltb_upload(void* dst, const void* src, size_t bytes, int after) {
+  LTB_INITED(); LTB_REQUIRE(dst && src && after >= -1 && after < 16, "ltb_upload: bad argument");
+  LTB_REQUIRE(!g.capturing, "ltb_upload: not allowed while recording a step");
+  filter_cache_note_write(dst, bytes);
+  { int rc_ = grad_settle(dst, bytes); if (rc_) return rc_; }
+  if (after >= 0 && marker_set[after]) LTB_CUDA(cudaStreamWaitEvent(g.copy, marker_ev[after], 0));
+  if (bytes) LTB_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, g.copy));
+  return LTB_OK;
+}
+int ltb_upload_marker(int slot) {
+  LTB_INITED(); LTB_REQUIRE(slot >= 0 && slot < 16, "ltb_upload_marker: slot %d out of range", slot);
+  if (!marker_ev[slot]) LTB_CUDA(cudaEventCreateWithFlags(&marker_ev[slot], cudaEventDisableTiming));
+  LTB_CUDA(cudaEventRecord(marker_ev[slot], g.copy));
+  marker_set[slot] = true;
+  return LTB_OK;
+}
+int ltb_stream_wait_marker(int slot) {
+  LTB_INITED(); LTB_REQUIRE(slot >= 0 && slot < 16, "ltb_stream_wait_marker: slot %d out of range", slot);
+  LTB_REQUIRE(!g.capturing, "ltb_stream_wait_marker: not allowed while recording a step");
+  if (marker_set[slot]) LTB_CUDA(cudaStreamWaitEvent(g.stream, marker_ev[slot], 0));
   return LTB_OK;
 }
 int ltb_marker_wait(int slot) {

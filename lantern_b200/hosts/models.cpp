@@ -63,6 +63,7 @@ struct Model {
   bool feeding = false;
   int64_t submitted = 0;
   float* feed_x[2] = {nullptr, nullptr}; int32_t* feed_y[2] = {nullptr, nullptr}; float* feed_loss = nullptr;
+  float* dstage_x[2] = {nullptr, nullptr}; int32_t* dstage_y[2] = {nullptr, nullptr};   // device side of the two staging pairs (uploads run beside the step before)
 
   int declare(std::initializer_list<int> shape, int init, float scale = 0.f) {
     ParamDecl d; d.shape.assign(shape.begin(), shape.end()); d.init = init; d.scale = scale;
@@ -95,6 +96,7 @@ struct Model {
     dev_x = alloc_value((int64_t)batch * in_c * in_h * in_w);
     dev_y = (int32_t*)BK(malloc_uninit)((size_t)label_count * 4);
     dev_loss = alloc_value(1);
+    for (int p = 0; p < 2; ++p) { dstage_x[p] = alloc_value((int64_t)batch * in_c * in_h * in_w); dstage_y[p] = (int32_t*)BK(malloc_uninit)((size_t)label_count * 4); }
     if (logit_count > 0) dev_logits = alloc_value(logit_count);
     mark = BK(mark)();
   }
@@ -231,7 +233,12 @@ struct Model {
     const int p = (int)(submitted & 1);
     const size_t xb = (size_t)batch * in_c * in_h * in_w * 4;
     if (xh) { memcpy(sx, xh, xb); memcpy(sy, yh, (size_t)label_count * 4); }
-    if (BK(h2d)(dev_x, sx, xb) || BK(h2d)(dev_y, sy, (size_t)label_count * 4) || BK(marker_record)(p)) return -1;
+    // The upload runs on the copy stream beside the step before it (marker 4 + p: the device staging pair was read for the last
+    // time by step submitted - 2; marker p: the upload has left the host staging pair); the compute stream then waits for the
+    // upload on the device and moves the batch to where the recorded step reads it.
+    const size_t yb = (size_t)label_count * 4;
+    if (BK(upload)(dstage_x[p], sx, xb, submitted >= 2 ? 4 + p : -1) || BK(upload)(dstage_y[p], sy, yb, -1) || BK(upload_marker)(p)) return -1;
+    if (BK(stream_wait_marker)(p) || BK(d2d)(dev_x, dstage_x[p], xb) || BK(d2d)(dev_y, dstage_y[p], yb) || BK(marker_record)(4 + p)) return -1;
     if (step_async(nullptr, nullptr, lr, true)) return -1;
     if (BK(d2h_async)(feed_loss + p, dev_loss, 4) || BK(marker_record)(2 + p)) return -1;
     return submitted++;

@@ -1332,6 +1332,9 @@ int ora_branch_begin(void) { ProfScope prof_scope_("ora_branch_begin"); return L
 int ora_branch_end(void) { ProfScope prof_scope_("ora_branch_end"); return LTB_OK; }
 int ora_branch_join(void) { ProfScope prof_scope_("ora_branch_join"); return LTB_OK; }
 int ora_marker_record(int) { ProfScope prof_scope_("ora_marker_record"); return LTB_OK; }      // the CPU oracle runs every call to completion
+int ora_upload(void* d, const void* s, size_t n, int) { ProfScope prof_scope_("ora_upload"); memcpy(d, s, n); return LTB_OK; }      // one thread of control: copied at once
+int ora_upload_marker(int) { return LTB_OK; }
+int ora_stream_wait_marker(int) { return LTB_OK; }
 int ora_marker_wait(int) { ProfScope prof_scope_("ora_marker_wait"); return LTB_OK; }
 int ora_graph_begin(void) { ProfScope prof_scope_("ora_graph_begin"); return fail(LTB_E_ARG, "the CPU oracle does not record steps"); }
 void* ora_graph_end(void) { return nullptr; }
