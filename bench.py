@@ -389,7 +389,9 @@ def main():
                 "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
                 "dtype": args.math if args.math == "tf32" else "f32", "data": "synthetic",
                 "config": {"workload": "resnet50_cifar_train_step_sgd_lr0.1", "batch_per_gpu": BATCH, "global_batch": BATCH * world,
-                           "parallelism": "dp%d" % world, "replay": "cuda_graph", "l2": "per-step working set (~3 GB of activations and gradients) exceeds the 126 MB L2",
+                           "parallelism": "dp%d" % world, "replay": "cuda_graph",
+                           "library_switches": "look-ahead fusion level 2, operand cache, deferred zero fill of gradient buffers >= 4 MB, branch regions, split-K by atomics",
+                           "l2": "per-step working set (~3 GB of activations and gradients) exceeds the 126 MB L2",
                            "step_gflop": flops / 1e9},
                 "timing": {"blocks": len(blocks), "steps_per_block": args.steps, "block_ms_median": ms, "block_ms_min": min(blocks), "block_ms_max": max(blocks),
                            "timed_region_s": sum(blocks) / 1e3, "note": "value and ms_per_step are the median block of exactly `steps` steps"},
