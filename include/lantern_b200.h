@@ -91,7 +91,8 @@ int    LTB_FN(set_fusion)(int on);
  * in whatever order they finish, so the last bits of such a sum can differ from run to run. With this mode on, up to eight
  * splits form a thread-block cluster that adds its tiles up in a fixed order through shared memory, and larger splits go
  * through slabs of partial results summed in a fixed order by one more launch: a step of the tensor-core path then gives
- * the same bits on every run, at about a third more time in the contraction kernels. */
+ * the same bits on every run, at about a third more time in the contraction kernels.  The CUDA-core fallback paths (shapes the
+ * engine declines, the FP32 math mode) do not split over K at all in this mode. */
 int    LTB_FN(set_deterministic)(int on);
 int    LTB_FN(set_filter_cache)(int on);
 int    LTB_FN(params_changed)(void);

@@ -226,11 +226,12 @@ static int strided_gemm(const float* a, int64_t sam, int64_t sak, const float* b
   // A forward product with few output tiles and a long K (the 2048 -> 10 classifier: two tiles) would leave the machine to two
   // CTAs; when the output is a dense matrix it is zeroed and the product accumulated from K-splits like a gradient.
   const bool dense_c = (scn == 1 && scm == N) || (scm == 1 && scn == M);
-  if (!accumulate && K >= 1024 && tiles < g.sm_count && dense_c) {
+  // deterministic mode (ltb_set_deterministic): no split over K on the CUDA-core paths either -- their splits add atomically
+  if (!g.deterministic && !accumulate && K >= 1024 && tiles < g.sm_count && dense_c) {
     LTB_CUDA(cudaMemsetAsync(c, 0, (size_t)M * N * sizeof(float), g.stream));
     accumulate = true;
   }
-  if (accumulate && K >= 1024 && tiles < g.sm_count) { splits = (2 * g.sm_count + tiles - 1) / tiles; int mx = K / 256; if (splits > mx) splits = mx; if (splits < 1) splits = 1; }
+  if (!g.deterministic && accumulate && K >= 1024 && tiles < g.sm_count) { splits = (2 * g.sm_count + tiles - 1) / tiles; int mx = K / 256; if (splits > mx) splits = mx; if (splits < 1) splits = 1; }
   int kps = (int)ceil_div(ceil_div(K, splits), BKK) * BKK;
   grid.z = (unsigned)ceil_div(K, kps);
   MatLoadA la{a, sam, sak}; MatLoadB lb{b, sbk, sbn};
@@ -347,7 +348,7 @@ int conv_wgrad_fp32(const float* x, const float* dy, float* dw, const ConvDims& 
   int M = d.K, Nn = d.C * d.R * d.S, Kd = d.N * d.oH * d.oW;
   dim3 grid((M + BM - 1) / BM, (Nn + BN - 1) / BN, 1);
   int tiles = grid.x * grid.y;
-  int splits = (2 * g.sm_count + tiles - 1) / tiles; int mx = Kd / 128; if (splits > mx) splits = mx; if (splits < 1) splits = 1;
+  int splits = (2 * g.sm_count + tiles - 1) / tiles; int mx = Kd / 128; if (splits > mx) splits = mx; if (splits < 1 || g.deterministic) splits = 1;
   int kps = (int)ceil_div(ceil_div(Kd, splits), BKK) * BKK;
   grid.z = (unsigned)ceil_div(Kd, kps);
   if (grid.z == 1) LTB_LAUNCH((igemm_kernel<0, 0, ConvWgradA, ConvWgradB, MatStore<1>>), grid, 256, 0, M, Nn, Kd, kps, (ConvWgradA{dy, d}), (ConvWgradB{x, d}), (MatStore<1>{dw, (int64_t)Nn, 1, 1.0f}));
@@ -358,7 +359,7 @@ int conv_bias_grad(const float* dy, float* dbias, const ConvDims& d) {
   const int hw = d.oH * d.oW;
   int splits = (int)ceil_div(2 * g.sm_count, d.K);                      // about two blocks per SM in all
   if (splits > d.N) splits = d.N;
-  if ((int64_t)d.N * hw < 4096) splits = 1;                              // a few KB per channel: one block reads it at once
+  if ((int64_t)d.N * hw < 4096 || g.deterministic) splits = 1;           // a few KB per channel: one block reads it at once (deterministic mode: no atomics)
   const int ips = (int)ceil_div(d.N, splits);
   splits = (int)ceil_div(d.N, ips);
   const int threads = 256;
