@@ -256,6 +256,13 @@ typedef struct ltb_tree_node {
 } ltb_tree_node;
 int LTB_FN(tree_node_fwd)(const ltb_tree_node* node);
 int LTB_FN(tree_node_bwd)(const ltb_tree_node* node);
+/* One LEVEL of a tree -- `count` nodes that do not depend on one another (all leaves; then all nodes whose children are done;
+ * ...) -- in one call each way.  nodes_host and nodes_dev are the same array of descriptions in host memory (read by the call:
+ * checks, launch size) and in device memory (read by the kernels: the caller uploads the array once per tree); the nodes of
+ * the call are [first, first + count).  Results are those of tree_node_fwd / tree_node_bwd on each node; two nodes of one
+ * backward call may have a common child only if they are the same node's parents -- they are not, in a tree. */
+int LTB_FN(tree_nodes_fwd)(const ltb_tree_node* nodes_host, const ltb_tree_node* nodes_dev, int first, int count);
+int LTB_FN(tree_nodes_bwd)(const ltb_tree_node* nodes_host, const ltb_tree_node* nodes_dev, int first, int count);
 
 /* Branch regions (no counterpart in the reference, whose generated programs issue everything on one stream): two runs of
  * calls that do not depend on each other -- the shortcut convolution of a residual block and its main path, the two

@@ -304,17 +304,20 @@ constexpr int kNodeThreads = 256, kNodeWarps = kNodeThreads / 32;
 constexpr int kNodeMaxHidden = 512;                   // the backward prologue keeps 7 vectors of this length in shared memory
 
 __device__ unsigned node_done_count;                  // CTAs of the running forward launch that have stored their gates
+constexpr int kNodesPerLaunch = 128;
+__device__ unsigned nodes_done_count[kNodesPerLaunch]; // the same, one per node of a batched launch
 
 __device__ __forceinline__ float act_apply(int slot, float v) { return slot == 4 ? tanhf(v) : 1.0f / (1.0f + expf(-v)); }
 __device__ __forceinline__ int node_slot(bool inner, int g) { return inner ? g : (g == 0 ? 0 : g + 2); }   // leaf rows: slots 0, 3, 4
 
-__global__ void __launch_bounds__(kNodeThreads) tree_node_fwd_kernel(const ltb_tree_node P) {
+// bx: this CTA's index among the n_ctas CTAs that work on node P; done: their completion counter (zero between launches)
+__device__ __forceinline__ void node_fwd_body(const ltb_tree_node& P, unsigned* done, unsigned n_ctas, int bx) {
   __shared__ float s_in[kNodeMaxHidden];
   __shared__ float s_pred[32];
   __shared__ bool s_last;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int Hd = P.hidden, L = P.in_len, G = P.inner ? 5 : 3;
-  const int row = blockIdx.x * kNodeWarps + warp;
+  const int row = bx * kNodeWarps + warp;
   if (row < G * Hd) {
     const int slot = node_slot(P.inner, row / Hd), j = row % Hd;
     float a = 0.0f;
@@ -331,7 +334,7 @@ __global__ void __launch_bounds__(kNodeThreads) tree_node_fwd_kernel(const ltb_t
     if (lane == 0) { P.gates[slot * Hd + j] = act_apply(slot, a + P.bias[slot][j]); __threadfence(); }
   }
   __syncthreads();
-  if (tid == 0) { __threadfence(); s_last = atomicAdd(&node_done_count, 1u) == gridDim.x - 1; }
+  if (tid == 0) { __threadfence(); s_last = atomicAdd(done, 1u) == n_ctas - 1; }
   __syncthreads();
   if (!s_last) return;
   __threadfence();
@@ -363,13 +366,32 @@ __global__ void __launch_bounds__(kNodeThreads) tree_node_fwd_kernel(const ltb_t
       if (P.loss_l) loss += P.loss_l[0];
       if (P.loss_r) loss += P.loss_r[0];
       P.loss[0] = loss;
-      node_done_count = 0;                            // ready for the next launch
+      *done = 0;                                      // ready for the next launch
     }
   }
 }
+__global__ void __launch_bounds__(kNodeThreads) tree_node_fwd_kernel(const ltb_tree_node P) { node_fwd_body(P, &node_done_count, gridDim.x, (int)blockIdx.x); }
+// Several independent nodes (one level of a tree) in one launch: blockIdx.y picks the node out of an array in device memory,
+// the CTA copies its node's description into shared memory first.  done[] has one counter per node of the launch.
+__device__ __forceinline__ const ltb_tree_node& node_to_shared(const ltb_tree_node* nodes, int i) {
+  __shared__ ltb_tree_node sp;
+  const int* src = reinterpret_cast<const int*>(nodes + i); int* dst = reinterpret_cast<int*>(&sp);
+  for (int k = threadIdx.x; k < (int)(sizeof(ltb_tree_node) / 4); k += blockDim.x) dst[k] = src[k];
+  __syncthreads();
+  return sp;
+}
+__global__ void __launch_bounds__(kNodeThreads) tree_nodes_fwd_kernel(const ltb_tree_node* nodes) {
+  unsigned* done = nodes_done_count;
+  const ltb_tree_node& P = node_to_shared(nodes, (int)blockIdx.y);
+  const unsigned n_ctas = (unsigned)(((P.inner ? 5 : 3) * P.hidden + kNodeWarps - 1) / kNodeWarps);
+  if (blockIdx.x >= n_ctas) return;                                    // the grid is sized for an inner node; a leaf needs fewer CTAs
+  node_fwd_body(P, done + blockIdx.y, n_ctas, (int)blockIdx.x);
+}
 
 // Backward.  Grid: n_w CTAs of weight-gradient rows, then n_x CTAs of input-gradient partial sums (none for a leaf).
-__global__ void __launch_bounds__(kNodeThreads) tree_node_bwd_kernel(const ltb_tree_node P, int n_w) {
+// SHARED: several nodes of one launch add into the same parameter gradients (a level of a tree): those additions are atomic.
+template <bool SHARED>
+__device__ __forceinline__ void node_bwd_body(const ltb_tree_node& P, int n_w, int bx) {
   __shared__ float s_dpre[5 * kNodeMaxHidden];        // gradient at each gate's pre-activation
   __shared__ float s_dpred[32];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -391,38 +413,38 @@ __global__ void __launch_bounds__(kNodeThreads) tree_node_bwd_kernel(const ltb_t
       const float fl = P.gates[Hd + j], fr = P.gates[2 * Hd + j];
       s_dpre[1 * Hd + j] = (dct * P.cl[j]) * fl * (1.0f - fl);
       s_dpre[2 * Hd + j] = (dct * P.cr[j]) * fr * (1.0f - fr);
-      if (blockIdx.x == 0) {
+      if (bx == 0) {
         if (P.dcl) P.dcl[j] += dct * fl;
         if (P.dcr) P.dcr[j] += dct * fr;
       }
     }
-    if (blockIdx.x == 0) {
+    if (bx == 0) {
       const float v = P.classify_cell ? P.c[j] : P.h[j];
-      for (int k = 0; k < P.classes; ++k) P.dWhy[(size_t)k * Hd + j] += s_dpred[k] * v;
+      for (int k = 0; k < P.classes; ++k) { if (SHARED) atomicAdd(P.dWhy + (size_t)k * Hd + j, s_dpred[k] * v); else P.dWhy[(size_t)k * Hd + j] += s_dpred[k] * v; }
     }
   }
-  if (blockIdx.x == 0) {
-    if (tid < P.classes) P.dby[tid] += s_dpred[tid];
+  if (bx == 0) {
+    if (tid < P.classes) { if (SHARED) atomicAdd(P.dby + tid, s_dpred[tid]); else P.dby[tid] += s_dpred[tid]; }
     if (tid == 0) { if (P.dloss_l) P.dloss_l[0] += dl; if (P.dloss_r) P.dloss_r[0] += dl; }
   }
   __syncthreads();
-  if ((int)blockIdx.x < n_w) {
-    const int row = blockIdx.x * kNodeWarps + warp;
+  if (bx < n_w) {
+    const int row = bx * kNodeWarps + warp;
     if (row >= G * Hd) return;
     const int slot = node_slot(P.inner, row / Hd), j = row % Hd;
     const float dp = s_dpre[slot * Hd + j];
     float* d0 = P.dW[slot][0] + (size_t)j * L; const float* x0 = P.in[0];
-    for (int k = lane; k < L; k += 32) d0[k] += dp * x0[k];
+    for (int k = lane; k < L; k += 32) { if (SHARED) atomicAdd(d0 + k, dp * x0[k]); else d0[k] += dp * x0[k]; }
     if (P.inner) {
       float* d1 = P.dW[slot][1] + (size_t)j * L; const float* x1 = P.in[1];
-      for (int k = lane; k < L; k += 32) d1[k] += dp * x1[k];
+      for (int k = lane; k < L; k += 32) { if (SHARED) atomicAdd(d1 + k, dp * x1[k]); else d1[k] += dp * x1[k]; }
     }
     if (lane == 0) atomicAdd(P.dbias[slot] + j, dp);   // two slots may share a bias vector
     return;
   }
   // input gradients: warp = (input, block of 32 inputs, gate, block of 32 gate rows); din[k] += sum_j dpre[j] W[j][k]
   const int kb = (L + 31) / 32, jb = (Hd + 31) / 32;
-  int w = ((int)blockIdx.x - n_w) * kNodeWarps + warp;
+  int w = (bx - n_w) * kNodeWarps + warp;
   const int n_in = P.inner ? 2 : 1;
   if (w >= n_in * kb * G * jb) return;
   const int j0 = (w % jb) * 32; w /= jb;
@@ -435,6 +457,16 @@ __global__ void __launch_bounds__(kNodeThreads) tree_node_bwd_kernel(const ltb_t
   float a = 0.0f;
   for (int j = j0; j < j1; ++j) a += s_dpre[slot * Hd + j] * wm[(size_t)j * L + k];
   atomicAdd(din + k, a);
+}
+
+__global__ void __launch_bounds__(kNodeThreads) tree_node_bwd_kernel(const ltb_tree_node P, int n_w) { node_bwd_body<false>(P, n_w, (int)blockIdx.x); }
+__global__ void __launch_bounds__(kNodeThreads) tree_nodes_bwd_kernel(const ltb_tree_node* nodes) {
+  const ltb_tree_node& P = node_to_shared(nodes, (int)blockIdx.y);
+  const int G = P.inner ? 5 : 3, n_w = (G * P.hidden + kNodeWarps - 1) / kNodeWarps;
+  const bool any_din = P.din[0] || (P.inner && P.din[1]);
+  const int x_warps = any_din ? (P.inner ? 2 : 1) * ((P.in_len + 31) / 32) * G * ((P.hidden + 31) / 32) : 0;
+  if ((int)blockIdx.x >= n_w + (x_warps + kNodeWarps - 1) / kNodeWarps) return;
+  node_bwd_body<true>(P, n_w, (int)blockIdx.x);
 }
 
 }  // namespace ltb
@@ -476,6 +508,47 @@ int ltb_tree_node_bwd(const ltb_tree_node* n) {
   const bool any_din = n->din[0] || (n->inner && n->din[1]);
   const int x_warps = any_din ? (n->inner ? 2 : 1) * (int)ceil_div(n->in_len, 32) * G * (int)ceil_div(n->hidden, 32) : 0;
   LTB_LAUNCH(tree_node_bwd_kernel, (unsigned)(n_w + ceil_div(x_warps, kNodeWarps)), kNodeThreads, 0, *n, n_w);
+  return LTB_OK;
+}
+
+// One level of a tree -- `count` nodes that do not depend on one another -- in one launch each way.  nodes_host and nodes_dev
+// are the same array on the host (read here: checks, grid size) and in device memory (read by the kernels); the nodes of the
+// call are [first, first + count).
+int ltb_tree_nodes_fwd(const ltb_tree_node* nodes_host, const ltb_tree_node* nodes_dev, int first, int count) {
+  LTB_INITED(); LTB_REQUIRE(nodes_host && nodes_dev && first >= 0 && count > 0, "ltb_tree_nodes_fwd: bad argument");
+  for (int at = first; at < first + count; at += kNodesPerLaunch) {
+    const int n = first + count - at < kNodesPerLaunch ? first + count - at : kNodesPerLaunch;
+    int ctas = 1;
+    for (int i = at; i < at + n; ++i) {
+      if (int rc = tree_node_check(nodes_host + i, "ltb_tree_nodes_fwd")) return rc;
+      const int c = (int)ceil_div((nodes_host[i].inner ? 5 : 3) * nodes_host[i].hidden, kNodeWarps);
+      if (c > ctas) ctas = c;
+    }
+    LTB_LAUNCH(tree_nodes_fwd_kernel, dim3((unsigned)ctas, (unsigned)n), kNodeThreads, 0, nodes_dev + at);
+  }
+  return LTB_OK;
+}
+int ltb_tree_nodes_bwd(const ltb_tree_node* nodes_host, const ltb_tree_node* nodes_dev, int first, int count) {
+  LTB_INITED(); LTB_REQUIRE(nodes_host && nodes_dev && first >= 0 && count > 0, "ltb_tree_nodes_bwd: bad argument");
+  for (int at = first; at < first + count; at += kNodesPerLaunch) {
+    const int n = first + count - at < kNodesPerLaunch ? first + count - at : kNodesPerLaunch;
+    int ctas = 1;
+    for (int i = at; i < at + n; ++i) {
+      const ltb_tree_node* q = nodes_host + i;
+      if (int rc = tree_node_check(q, "ltb_tree_nodes_bwd")) return rc;
+      const int G = q->inner ? 5 : 3;
+      LTB_REQUIRE(q->dc && q->dh && q->dloss && q->dWhy && q->dby, "ltb_tree_nodes_bwd: missing gradient operand");
+      for (int g = 0; g < G; ++g) {
+        const int slot = q->inner ? g : (g == 0 ? 0 : g + 2);
+        LTB_REQUIRE(q->dW[slot][0] && q->dbias[slot] && (!q->inner || q->dW[slot][1]), "ltb_tree_nodes_bwd: missing gate gradient");
+      }
+      const bool any_din = q->din[0] || (q->inner && q->din[1]);
+      const int x_warps = any_din ? (q->inner ? 2 : 1) * (int)ceil_div(q->in_len, 32) * G * (int)ceil_div(q->hidden, 32) : 0;
+      const int c = (int)ceil_div(G * q->hidden, kNodeWarps) + (int)ceil_div(x_warps, kNodeWarps);
+      if (c > ctas) ctas = c;
+    }
+    LTB_LAUNCH(tree_nodes_bwd_kernel, dim3((unsigned)ctas, (unsigned)n), kNodeThreads, 0, nodes_dev + at);
+  }
   return LTB_OK;
 }
 

@@ -208,9 +208,10 @@ class Model:
         if rc:
             raise ValueError("model_set_table failed: %d" % rc)
 
-    def use_fused_cells(self, on=2):
-        """Recursive models: 0 one call per operator, as the reference stages them; 1 one fused call per gate or cell; 2 (the
-        default) in addition the vanilla RNN's whole unrolled sequence and a whole tree-LSTM node in one call."""
+    def use_fused_cells(self, on=3):
+        """Recursive models: 0 one call per operator, as the reference stages them; 1 one fused call per gate or cell; 2 in
+        addition the vanilla RNN's whole unrolled sequence and a whole tree-LSTM node in one call; 3 (the default) a whole
+        LEVEL of the tree in one call."""
         self.hp.fn["model_use_fused_cells"](self.h, int(on))
 
     def use_branches(self, on=True):

@@ -52,6 +52,7 @@ struct Model {
   bool early_reduce = false;   // this step runs data-parallel with an update: finished gradient ranges are summed during backward
   bool branches = true;        // independent runs of calls (shortcut convolutions) are issued as branch regions
   bool fused_cells = true;     // recursive models: one call per gate (ltb_affine_act) instead of one per operator
+  bool level_batches = true;   // tree-LSTM with whole nodes per call: a whole LEVEL of the tree per call (ltb_tree_nodes_fwd)
   bool whole_sequence = true;  // with fused cells: the vanilla RNN's whole unrolled sequence (ltb_rnn_seq_fwd) and a whole tree node (ltb_tree_node_fwd) in one call
   bool resident = false;       // read the batch from dev_x/dev_y instead of uploading it
   float* dev_x = nullptr; int32_t* dev_y = nullptr;
@@ -446,9 +447,75 @@ struct TreeLstm : Model {
     s.first = cell; s.second = hidden;
     return s;
   }
+  // The whole tree level by level (ltb_tree_nodes_fwd / _bwd): all leaves in one call, then all nodes whose children are done,
+  // and so on up to the root; the descriptions of all nodes are uploaded once.  A 25-leaf tree is some ten calls each way
+  // instead of 49.
+  std::vector<ltb_tree_node> level_nodes;          // sorted by height; kept until the backward calls have been issued
+  TR forward_levels(Tape& t, const int32_t* host, const int32_t* dev, int n) {
+    const int32_t *scores = dev + 1, *words = host + 1 + MAXN, *lch = host + 1 + 2 * MAXN, *rch = host + 1 + 3 * MAXN;
+    std::vector<int> height(n, -1), order(n), pos(n);
+    std::function<int(int)> hgt = [&](int i) -> int {
+      if (height[i] >= 0) return height[i];
+      if (lch[i] < 0) return height[i] = 0;
+      const int a = hgt(lch[i]), b = hgt(rch[i]);
+      return height[i] = 1 + (a > b ? a : b);
+    };
+    int top = 0;
+    for (int i = 0; i < n; ++i) { const int h = hgt(i); if (h > top) top = h; }
+    std::vector<int> first(top + 2, 0);
+    for (int i = 0; i < n; ++i) ++first[height[i] + 1];
+    for (int h = 0; h <= top; ++h) first[h + 1] += first[h];
+    { std::vector<int> fill(first.begin(), first.end() - 1); for (int i = 0; i < n; ++i) { pos[i] = fill[height[i]]++; order[pos[i]] = i; } }
+    const int64_t pitch = ((int64_t)Hd + 63) / 64 * 64, vstride = 8 * pitch + 64, gstride = 2 * pitch + 64;
+    float* vals = alloc_value(n * vstride);
+    float* grads = alloc_zero(n * gstride);
+    level_nodes.assign((size_t)n, ltb_tree_node{});
+    auto V = [&](int i) { return vals + (int64_t)pos[i] * vstride; };
+    auto G = [&](int i) { return grads + (int64_t)pos[i] * gstride; };
+    for (int i = 0; i < n; ++i) {
+      ltb_tree_node& q = level_nodes[(size_t)pos[i]];
+      const bool inner = lch[i] >= 0;
+      q.hidden = Hd; q.classes = O; q.inner = inner ? 1 : 0; q.classify_cell = pldi19 ? 1 : 0;
+      auto setW = [&](int slot, int k, int idx) { const TR w = P(idx); q.W[slot][k] = w.x; q.dW[slot][k] = w.d; };
+      auto setB = [&](int slot, int idx) { const TR b = P(idx); q.bias[slot] = b.x; q.dbias[slot] = b.d; };
+      if (!inner) {
+        q.in_len = E; q.in[0] = table + (int64_t)words[i] * E;
+        setW(0, 0, Wi); setW(3, 0, Wo); setW(4, 0, Wu); setB(0, bi); setB(3, bo); setB(4, bu);
+      } else {
+        const int l = lch[i], r = rch[i];
+        // the children's first state vector feeds the gates, their second one the cell (the PLDI19 application's exchanged roles:
+        // first = cell, second = hidden)
+        q.in_len = Hd;
+        q.in[0] = pldi19 ? V(l) + 5 * pitch : V(l) + 7 * pitch; q.din[0] = pldi19 ? G(l) : G(l) + pitch;
+        q.in[1] = pldi19 ? V(r) + 5 * pitch : V(r) + 7 * pitch; q.din[1] = pldi19 ? G(r) : G(r) + pitch;
+        q.cl = pldi19 ? V(l) + 7 * pitch : V(l) + 5 * pitch; q.dcl = pldi19 ? G(l) + pitch : G(l);
+        q.cr = pldi19 ? V(r) + 7 * pitch : V(r) + 5 * pitch; q.dcr = pldi19 ? G(r) + pitch : G(r);
+        q.loss_l = V(l) + 8 * pitch + 32; q.dloss_l = G(l) + 2 * pitch; q.loss_r = V(r) + 8 * pitch + 32; q.dloss_r = G(r) + 2 * pitch;
+        setW(0, 0, U0i); setW(0, 1, U1i); setW(1, 0, U00f); setW(1, 1, U01f); setW(2, 0, U10f); setW(2, 1, U11f);
+        setW(3, 0, U0o); setW(3, 1, U1o); setW(4, 0, U0u); setW(4, 1, U1u);
+        setB(0, bbi); setB(1, bbf); setB(2, bbf); setB(3, bbo); setB(4, bbu);
+      }
+      { const TR w = P(Why), b = P(by); q.Why = w.x; q.dWhy = w.d; q.by = b.x; q.dby = b.d; }
+      q.score = scores + i;
+      float* v = V(i); float* g = G(i);
+      q.gates = v; q.c = v + 5 * pitch; q.tc = v + 6 * pitch; q.h = v + 7 * pitch; q.logp = v + 8 * pitch; q.loss = v + 8 * pitch + 32;
+      q.dc = g; q.dh = g + pitch; q.dloss = g + 2 * pitch;
+    }
+    ltb_tree_node* dev_nodes = (ltb_tree_node*)BK(malloc_uninit)((size_t)n * sizeof(ltb_tree_node));
+    BK(h2d)(dev_nodes, level_nodes.data(), (size_t)n * sizeof(ltb_tree_node));
+    const ltb_tree_node* hn = level_nodes.data();
+    for (int h = 0; h <= top; ++h) {
+      const int f = first[h], c = first[h + 1] - first[h];
+      BK(tree_nodes_fwd)(hn, dev_nodes, f, c);
+      t.push([=] { BK(tree_nodes_bwd)(hn, dev_nodes, f, c); });
+    }
+    TR loss; loss.rank = 1; loss.shape[0] = 1; loss.x = V(0) + 8 * pitch + 32; loss.d = G(0) + 2 * pitch;
+    return loss;
+  }
   TR forward(Tape& t, const TR&, const int32_t* y) override {
     const int n = stage_y[0];
     if (n < 1 || n > MAXN) { TR z = make({1}); BK(fill)(z.x, 0.0f, 1); return z; }
+    if (fused_cells && whole_sequence && level_batches) return forward_levels(t, stage_y, y, n);
     return visit(t, stage_y, y, 0).loss;
   }
   void apply_update(float lr) override { BK(adagrad_update)(slab_x, slab_d, slab_h, lr, pldi19 ? 1.0f : 3.0e38f, 1, slab_count); }
@@ -617,7 +684,7 @@ int64_t HOST_FN(model_label_count)(void* m) { return ((Model*)m)->label_count; }
 int HOST_FN(model_use_fused_cells)(void* m, int on) {
   Model* M = (Model*)m;
   if (M->graph) { BK(graph_destroy)(M->graph); M->graph = nullptr; }
-  M->fused_cells = on != 0; M->whole_sequence = on >= 2; return 0;
+  M->fused_cells = on != 0; M->whole_sequence = on >= 2; M->level_batches = on >= 3; return 0;
 }
 // Issue independent runs of calls as branch regions (default) or everything in program order on one stream.
 // Large activation gradients declared unset instead of zero-filled (ltb_grad_unset; default on).  Process-wide: it is a property

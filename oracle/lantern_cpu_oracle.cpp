@@ -1320,6 +1320,17 @@ int ora_tree_node_bwd(const ltb_tree_node* n) { ProfScope prof_scope_("ora_tree_
   }
   return LTB_OK;
 }
+// One level of a tree: the nodes of the call one after the other (the CPU restatement has one memory: both arrays are the same).
+int ora_tree_nodes_fwd(const ltb_tree_node* nodes_host, const ltb_tree_node*, int first, int count) {
+  REQUIRE(nodes_host && first >= 0 && count > 0, "tree_nodes_fwd: bad argument");
+  for (int i = first; i < first + count; ++i) { int rc = ora_tree_node_fwd(nodes_host + i); if (rc) return rc; }
+  return LTB_OK;
+}
+int ora_tree_nodes_bwd(const ltb_tree_node* nodes_host, const ltb_tree_node*, int first, int count) {
+  REQUIRE(nodes_host && first >= 0 && count > 0, "tree_nodes_bwd: bad argument");
+  for (int i = first; i < first + count; ++i) { int rc = ora_tree_node_bwd(nodes_host + i); if (rc) return rc; }
+  return LTB_OK;
+}
 }  // extern "C"
 
 // ------------------------------------------------------------------ staging / replay: plain host equivalents.

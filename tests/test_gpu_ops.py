@@ -625,6 +625,79 @@ def test_tree_node_and_gradient(ora, gpu, inner, classify_cell, Hd, L):
     check(f, ora, gpu)
 
 
+@pytest.mark.parametrize("classify_cell", [0, 1])
+def test_tree_levels_and_gradient(ora, gpu, classify_cell):
+    """ltb_tree_nodes_fwd / ltb_tree_nodes_bwd: a small tree (four leaves, two inner nodes over them, the root) level by level --
+    three calls forward, three backward, node descriptions read from an array in device memory -- against the oracle running
+    the nodes one after the other: every node's cell, hidden vector and loss, the root's accumulated loss, and every weight
+    gradient."""
+    import ctypes
+    from lantern_b200 import parse_struct
+    Node = parse_struct("ltb_tree_node")
+    Hd, E, K, n = 150, 300, 5, 7
+    rng = R(31)
+    v = lambda *shape, scale=1.0: (rng.standard_normal(shape) * scale).astype(np.float32)
+    W = {"leaf%d" % g: v(Hd, E, scale=1 / np.sqrt(E)) for g in (0, 3, 4)}
+    W.update({"in%d%d" % (g, k): v(Hd, Hd, scale=1 / np.sqrt(Hd)) for g in range(5) for k in (0, 1)})
+    W.update({"bl%d" % g: v(Hd, scale=0.1) for g in (0, 3, 4)}); W.update({"bi%d" % g: v(Hd, scale=0.1) for g in (0, 1, 3, 4)})
+    W["Why"], W["by"] = v(K, Hd, scale=0.1), v(K, scale=0.1)
+    emb = v(4, E, scale=0.5)
+    scores0 = rng.integers(0, K, n).astype(np.int32)
+    kids = {4: (0, 1), 5: (2, 3), 6: (4, 5)}            # nodes 0..3 leaves, 4 and 5 over them, 6 the root; already sorted by height
+
+    def f(b):
+        lib = b.lib
+        w = {k: TensorR(b.fromNumpy(a), b.fromNumpy(a * 0.25)) for k, a in W.items()}
+        e, scores = b.fromNumpy(emb), b.fromNumpy(scores0)
+        pitch = 192
+        vals, grads = b.fill((n, 8 * pitch + 64), 0.0), b.fill((n, 2 * pitch + 64), 0.0)
+        V = lambda i: vals.ptr + 4 * i * (8 * pitch + 64)
+        G = lambda i: grads.ptr + 4 * i * (2 * pitch + 64)
+        first = 5 if classify_cell else 7                # which state vector the parent's gates read (cell or hidden), in pitches
+        arr = (Node * n)()
+        for i in range(n):
+            q = arr[i]
+            q.hidden, q.classes, q.classify_cell, q.inner = Hd, K, classify_cell, int(i >= 4)
+            if i < 4:
+                q.in_len = E
+                getattr(q, "in")[0] = e.ptr + 4 * i * E
+                for g in (0, 3, 4):
+                    q.W[g][0], q.dW[g][0], q.bias[g], q.dbias[g] = w["leaf%d" % g].x.ptr, w["leaf%d" % g].d.ptr, w["bl%d" % g].x.ptr, w["bl%d" % g].d.ptr
+            else:
+                l, r = kids[i]
+                q.in_len = Hd
+                getattr(q, "in")[0], getattr(q, "in")[1] = V(l) + 4 * first * pitch, V(r) + 4 * first * pitch
+                q.din[0], q.din[1] = G(l) + (0 if classify_cell else 4 * pitch), G(r) + (0 if classify_cell else 4 * pitch)
+                second = 7 if classify_cell else 5
+                q.cl, q.cr = V(l) + 4 * second * pitch, V(r) + 4 * second * pitch
+                q.dcl, q.dcr = G(l) + (4 * pitch if classify_cell else 0), G(r) + (4 * pitch if classify_cell else 0)
+                q.loss_l, q.loss_r = V(l) + 4 * (8 * pitch + 32), V(r) + 4 * (8 * pitch + 32)
+                q.dloss_l, q.dloss_r = G(l) + 4 * 2 * pitch, G(r) + 4 * 2 * pitch
+                for g in range(5):
+                    bk = "bi%d" % (1 if g == 2 else g)
+                    for k in (0, 1):
+                        q.W[g][k], q.dW[g][k] = w["in%d%d" % (g, k)].x.ptr, w["in%d%d" % (g, k)].d.ptr
+                    q.bias[g], q.dbias[g] = w[bk].x.ptr, w[bk].d.ptr
+            q.Why, q.by, q.dWhy, q.dby, q.score = w["Why"].x.ptr, w["by"].x.ptr, w["Why"].d.ptr, w["by"].d.ptr, scores.ptr + 4 * i
+            q.gates, q.c, q.tc, q.h = V(i), V(i) + 4 * 5 * pitch, V(i) + 4 * 6 * pitch, V(i) + 4 * 7 * pitch
+            q.logp, q.loss = V(i) + 4 * 8 * pitch, V(i) + 4 * (8 * pitch + 32)
+            q.dc, q.dh, q.dloss = G(i), G(i) + 4 * pitch, G(i) + 4 * 2 * pitch
+        nbytes = ctypes.sizeof(arr)
+        dev = lib.malloc_uninit(nbytes)
+        lib.h2d(dev, ctypes.addressof(arr), nbytes)
+        host = ctypes.addressof(arr)
+        for lo, cnt in ((0, 4), (4, 2), (6, 1)):
+            lib.tree_nodes_fwd(host, dev, lo, cnt)
+        one = np.array([1.0], np.float32)
+        lib.h2d(G(6) + 4 * 2 * pitch, one.ctypes.data, 4)                 # d(loss of the root) = 1
+        for lo, cnt in ((6, 1), (4, 2), (0, 4)):
+            lib.tree_nodes_bwd(host, dev, lo, cnt)
+        out = {"vals": vals.toCPU()[:, 5 * pitch:8 * pitch + 64], "grads": grads.toCPU()}
+        out.update({"d" + k: t.d.toCPU() for k, t in w.items()})
+        return out
+    check(f, ora, gpu)
+
+
 @pytest.mark.parametrize("shape", [(128, 64, 16, 16), (128, 1024, 4, 4), (256, 64, 32, 32)])
 def test_fusion_level_two_changes_no_result(gpu, shape):
     """ltb_set_fusion(2): the batch-norm backward / add gradient that absorbs a held in-place ReLU gradient applies the mask on

@@ -74,18 +74,19 @@ def test_treelstm_node_call_equals_operator_by_operator(oracle_lib, variant):
     from tests.test_gpu_models import _random_tree
     mark = oracle_lib.mark()
     x = np.zeros(1, np.float32)
-    for leaves in (1, 2, 9):
+    for leaves in (1, 2, 9, 30):
         y = _random_tree(np.random.default_rng(12 + leaves), leaves)
         res = []
-        for level in (2, 0):
+        for level in (3, 2, 0):                      # a whole level of the tree per call, a whole node per call, operator by operator
             m = _model(oracle_lib, variant, 1)
             m.use_fused_cells(level)
             loss = m.step(x, y, 0.0, update=False)
             res.append((loss, [m.grad(i) for i in range(m.num_params)]))
             m.close(); oracle_lib.reset(mark)
-        assert abs(res[0][0] - res[1][0]) <= 1e-6 * abs(res[1][0]), (leaves, res[0][0], res[1][0])
-        for i, (a, b) in enumerate(zip(res[0][1], res[1][1])):
-            assert np.abs(a - b).max() <= 1e-5 * max(np.abs(b).max(), 1e-12), (leaves, i)
+        for r in res[:2]:
+            assert abs(r[0] - res[2][0]) <= 1e-6 * abs(res[2][0]), (leaves, r[0], res[2][0])
+            for i, (a, b) in enumerate(zip(r[1], res[2][1])):
+                assert np.abs(a - b).max() <= 1e-5 * max(np.abs(b).max(), 1e-12), (leaves, i)
 
 
 def test_rnn_fused_cell_equals_operator_by_operator(oracle_lib):
