@@ -239,7 +239,9 @@ int main() {
   const int convs[][4] = {{2, 64, 64, 256}, {3, 64, 256, 256}, {4, 128, 96, 64}, {5, 256, 128, 64}, {11, 256, 128, 16}, {35, 512, 64, 4}, {1, 32, 48, 1024},
                           {8, 576, 64, 256}, {2, 40, 64, 32}, {3, 64, 64, 36}, {2, 2048, 512, 4}, {9, 1024, 256, 16}, {70, 512, 32, 1},
                           // filter rows that need padding (3x3 over 3, 16 and 48 channels; 1x1 over 16 and 48) and few output channels
-                          {2, 27, 96, 1024}, {3, 144, 64, 256}, {4, 16, 64, 256}, {2, 48, 192, 64}, {2, 432, 192, 64}, {3, 128, 12, 64}, {5, 48, 192, 16}};
+                          {2, 27, 96, 1024}, {3, 144, 64, 256}, {4, 16, 64, 256}, {2, 48, 192, 64}, {2, 432, 192, 64}, {3, 128, 12, 64}, {5, 48, 192, 16},
+                          // small images of a 3x3 or strided convolution: the kernel gathers from the unfolded matrix [n][(c, r, s)][p]
+                          {3, 2304, 256, 16}, {5, 4608, 128, 4}, {2, 72, 64, 16}};
   for (auto& c : convs) { int r = conv_case(c[0], c[1], c[2], c[3]); if (r < 0) ++bad; else taken += r; }
   const int taps[][9] = {{3, 64, 64, 16, 16, 3, 3, 1, 1}, {5, 128, 128, 8, 8, 3, 3, 1, 1}, {9, 64, 128, 4, 4, 3, 3, 1, 1}, {35, 64, 64, 2, 2, 3, 3, 1, 1},
                          {1, 32, 64, 32, 32, 3, 3, 1, 1}, {2, 64, 32, 16, 16, 3, 3, 0, 0}, {2, 64, 64, 8, 8, 5, 5, 2, 2}, {3, 96, 64, 8, 8, 1, 3, 0, 1},
