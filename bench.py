@@ -74,7 +74,8 @@ def hbm_bound_bytes(batch):
                      would add into them (ltb_grad_unset: the host program's default), so for those tensors dx, da and db
                      are written only: 12 (20) and 20 B / element.  At fusion level 2 (the host program's default) an absorbed
                      ReLU gradient is not written back: 4 B / element less for the batch norms that absorb one (except the
-                     two-sweep kernel of the 33 MB maps) and for relu_add_grad.
+                     two-sweep kernel of the 33 MB maps) and for relu_add_grad; and in the blocks without a shortcut convolution the
+                     batch-norm backward of the last layer absorbs the add gradient altogether.
       map_vec4       residual add + ReLU                                  a, b, out                     12 B / element
       maxpool_*      2x2 max pool forward (x, y, idx) and backward        6 and 10 B / input element
       sgd_*          x -= lr d; d = 0                                     16 B / parameter"""
@@ -100,6 +101,12 @@ def hbm_bound_bytes(batch):
     params = 23520842
     add_grad_bytes -= 4.0 * adds                    # level 2: d is not rewritten
     two_sweep = float(batch * 64 * 32 * 32)         # the stem's map: its masked gradient is still written back
+    # level 2, identity blocks (all but the first of each stage): the add gradient is absorbed by the batch-norm backward of the
+    # block's last layer, which then also reads the block's output (the mask) and writes the shortcut's gradient: 8 B / element more
+    # there, and no relu_add_grad launch (16 B / element) for those blocks
+    absorbed = float(sum(batch * c * h * h * (n - 1) for (c, h, n) in add_shapes))
+    add_grad_bytes -= 16.0 * absorbed
+    bn_bwd_bytes += 8.0 * absorbed
     return {"bn_fwd": 8.0 * bn_all, "bn_bwd": bn_bwd_bytes + 4.0 * relu_bn + 4.0 * two_sweep, "relu_add_grad": add_grad_bytes, "map_vec4": 12.0 * adds,
             "maxpool_fwd": 6.0 * pool_in, "maxpool_bwd": 10.0 * pool_in, "sgd": 16.0 * params}
 

@@ -18,7 +18,7 @@ constexpr size_t kGranule = 256;      // arena granule (TMA wants 16 B bases/str
 // for one call.  BN forward or a same-shape add followed by an in-place ReLU of their result become one kernel; an in-place
 // ReLU gradient followed by BN backward or by the add's gradient reading that buffer become one kernel.  Any other call
 // first issues the held operation on its own, so results never change; only the moment of the launch does.
-enum { PEND_NONE = 0, PEND_BN_FWD = 1, PEND_ADD = 2, PEND_RELU_GRAD = 3 };
+enum { PEND_NONE = 0, PEND_BN_FWD = 1, PEND_ADD = 2, PEND_RELU_GRAD = 3, PEND_RELU_ADD_GRAD = 4 };
 struct Pending {
   int kind = PEND_NONE;
   int64_t n = 0;
@@ -30,6 +30,9 @@ struct Pending {
   const float *a = nullptr, *b = nullptr; float* out = nullptr;
   // PEND_RELU_GRAD: d = relu_y > 0 ? d : 0
   const float* relu_y = nullptr; float* d = nullptr;
+  // PEND_RELU_ADD_GRAD (fusion level 2): m = relu_y > 0 ? d : 0; da += m; db += m, held so that the batch-norm backward whose dy is
+  // da (or db) reads m straight from d and writes the other destination itself; fa / fb: that destination holds nothing yet
+  float *da = nullptr, *db = nullptr; int fa = 0, fb = 0;
 };
 
 struct Context {
@@ -79,7 +82,8 @@ struct Context {
 extern Context g;
 
 int fail(int code, const char* fmt, ...);
-int flush_pending();                 // issues the held operation on its own (elementwise.cu)
+int flush_pending();
+int relu_add_grad_issue(const Pending& p);                 // issues the held operation on its own (elementwise.cu)
 // issue functions shared by the entry points and the flush (pool_bn.cu / elementwise.cu)
 int bn_fwd_issue(const Pending& p, bool relu);
 int add_issue(const float* a, const float* b, float* out, int64_t n, bool relu);

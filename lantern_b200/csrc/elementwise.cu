@@ -278,6 +278,7 @@ int flush_pending() {
     case PEND_BN_FWD: return bn_fwd_issue(p, false);
     case PEND_ADD: return add_issue(p.a, p.b, p.out, p.n, false);
     case PEND_RELU_GRAD: return relu_grad_issue(p.relu_y, p.d, p.n);
+    case PEND_RELU_ADD_GRAD: return relu_add_grad_issue(p);
     default: return LTB_OK;
   }
 }
@@ -301,6 +302,13 @@ __global__ void relu_add_grad_kernel(const float* __restrict__ y, float* d, floa
     if (da) da[i] = fa ? m : da[i] + m;
     if (db) db[i] = fb ? m : db[i] + m;
   }
+}
+
+int relu_add_grad_issue(const Pending& p) {
+  const bool vec = aligned16(p.relu_y) && aligned16(p.d) && (!p.da || aligned16(p.da)) && (!p.db || aligned16(p.db));
+  const int64_t n4 = vec ? p.n / 4 : 0;
+  LTB_LAUNCH(relu_add_grad_kernel, grid_for(n4 ? n4 : p.n, 256), 256, 0, p.relu_y, p.d, p.da, p.db, n4, n4 * 4, p.n, p.fa, p.fb, g.fusion_no_writeback ? 0 : 1);
+  return LTB_OK;
 }
 
 }  // namespace ltb
@@ -350,13 +358,14 @@ int ltb_ew_binary_grad(int op, const float* a, float* da, const int* as, const f
     // the held ReLU gradient of dout and this add's gradient in one pass (dout is rewritten with the masked values)
     const float* y = g.pending.relu_y; float* d = g.pending.d;
     g.pending.kind = PEND_NONE;
-    const bool vec = aligned16(y) && aligned16(d) && (!da || aligned16(da)) && (!db || aligned16(db));
-    const int64_t n4 = vec ? n / 4 : 0;
     // a destination declared unset (ltb_grad_unset) is written instead of added into; da == db stays an accumulation
     const int fa = da && da != db && grad_take_unset(da, (size_t)n * 4) ? 1 : 0, fb = db && da != db && grad_take_unset(db, (size_t)n * 4) ? 1 : 0;
     LTB_SETTLE(d); if (!fa) LTB_SETTLE(da); if (!fb) LTB_SETTLE(db);
-    LTB_LAUNCH(relu_add_grad_kernel, grid_for(n4 ? n4 : n, 256), 256, 0, y, d, da, db, n4, n4 * 4, n, fa, fb, g.fusion_no_writeback ? 0 : 1);
-    return LTB_OK;
+    Pending h; h.kind = PEND_RELU_ADD_GRAD; h.n = n; h.relu_y = y; h.d = d; h.da = da; h.db = db; h.fa = fa; h.fb = fb;
+    // level 2: held once more -- a batch-norm backward whose dy is one of the two destinations, written by nobody else before
+    // (fresh), reads the masked gradient straight from d and writes the other destination itself (ltb_bn_bwd)
+    if (g.fusion_no_writeback && da && db && da != db && (fa || fb)) { g.pending = h; return LTB_OK; }
+    return relu_add_grad_issue(h);
   }
   if (g.pending.kind) { int rc = flush_pending(); if (rc) return rc; }
   LTB_SETTLE(dout);

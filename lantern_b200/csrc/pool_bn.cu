@@ -333,7 +333,7 @@ __device__ __forceinline__ float4 relu_mask(float4 d, float4 m) {
 template <int VPT>
 __global__ void __launch_bounds__(512, 2) bn_bwd_cluster_kernel(const float* __restrict__ x, float* dy, float* dx, const float* __restrict__ gamma,
                                                              float* dgamma, float* dbeta, const float* __restrict__ mean, const float* __restrict__ istd,
-                                                             int N, int C, int HW, int per_cta, const float* mask_y, int fresh) {
+                                                             int N, int C, int HW, int per_cta, const float* mask_y, int fresh, float* extra) {
   cg::cluster_group cluster = cg::this_cluster();
   const unsigned K = cluster.num_blocks(), r = cluster.block_rank();
   const int c = blockIdx.x / K;
@@ -354,6 +354,11 @@ __global__ void __launch_bounds__(512, 2) bn_bwd_cluster_kernel(const float* __r
         const int64_t off = ((int64_t)n * C + c) * HW;
         kx[j] = reinterpret_cast<const float4*>(x + off)[i]; kd[j] = reinterpret_cast<const float4*>(dy + off)[i];
         if (mask_y) { kd[j] = relu_mask(kd[j], reinterpret_cast<const float4*>(mask_y + off)[i]); if (!(fresh & 2)) reinterpret_cast<float4*>(dy + off)[i] = kd[j]; }
+        if (extra) {                       // the absorbed add gradient's other destination: extra (+)= masked dy (bit 2 of fresh: it holds nothing yet)
+          float4 e = (fresh & 4) ? make_float4(0.f, 0.f, 0.f, 0.f) : reinterpret_cast<const float4*>(extra + off)[i];
+          e.x += kd[j].x; e.y += kd[j].y; e.z += kd[j].z; e.w += kd[j].w;
+          reinterpret_cast<float4*>(extra + off)[i] = e;
+        }
       }
     }
 #pragma unroll
@@ -373,6 +378,11 @@ __global__ void __launch_bounds__(512, 2) bn_bwd_cluster_kernel(const float* __r
       const float4 v = reinterpret_cast<const float4*>(x + off)[i];
       float4 d = reinterpret_cast<const float4*>(dy + off)[i];
       if (mask_y) { d = relu_mask(d, reinterpret_cast<const float4*>(mask_y + off)[i]); reinterpret_cast<float4*>(dy + off)[i] = d; }   // always written: the second sweep below reads dy again
+      if (extra) {
+        float4 e = (fresh & 4) ? make_float4(0.f, 0.f, 0.f, 0.f) : reinterpret_cast<const float4*>(extra + off)[i];
+        e.x += d.x; e.y += d.y; e.z += d.z; e.w += d.w;
+        reinterpret_cast<float4*>(extra + off)[i] = e;
+      }
       a += (d.x + d.y) + (d.z + d.w);
       b += (d.x * ((v.x - mu) * is) + d.y * ((v.y - mu) * is)) + (d.z * ((v.z - mu) * is) + d.w * ((v.w - mu) * is));
     }
@@ -511,7 +521,7 @@ __global__ void __launch_bounds__(512, 2) bn_fwd_packed_kernel(const float* x, f
 template <int VPT>
 __global__ void __launch_bounds__(512, 2) bn_bwd_packed_kernel(const float* __restrict__ x, float* dy, float* dx, const float* __restrict__ gamma,
                                                             float* dgamma, float* dbeta, const float* __restrict__ mean, const float* __restrict__ istd,
-                                                            int N, int C, int HW, const float* mask_y, int fresh) {
+                                                            int N, int C, int HW, const float* mask_y, int fresh, float* extra) {
   __shared__ float red[32];
   const int g = threadIdx.y, T = blockDim.x;
   const int c = blockIdx.x * blockDim.y + g;
@@ -528,6 +538,11 @@ __global__ void __launch_bounds__(512, 2) bn_bwd_packed_kernel(const float* __re
       const int64_t off = ((int64_t)n * C + c) * HW;
       kx[j] = reinterpret_cast<const float4*>(x + off)[i]; kd[j] = reinterpret_cast<const float4*>(dy + off)[i];
       if (mask_y) { kd[j] = relu_mask(kd[j], reinterpret_cast<const float4*>(mask_y + off)[i]); if (!(fresh & 2)) reinterpret_cast<float4*>(dy + off)[i] = kd[j]; }
+      if (extra) {
+        float4 e = (fresh & 4) ? make_float4(0.f, 0.f, 0.f, 0.f) : reinterpret_cast<const float4*>(extra + off)[i];
+        e.x += kd[j].x; e.y += kd[j].y; e.z += kd[j].z; e.w += kd[j].w;
+        reinterpret_cast<float4*>(extra + off)[i] = e;
+      }
     }
   }
 #pragma unroll
@@ -667,13 +682,24 @@ int ltb_bn_bwd(const float* x, float* dx, const float* dy, const float* gamma, f
   const bool cluster_path = vec && (int64_t)N * (HW >> 2) < ((int64_t)1 << 30);
   // a held in-place ReLU gradient on exactly this dy is applied by the kernel itself
   const float* mask_y = nullptr;
+  float* extra = nullptr; int extra_fresh = 0;
   if (g.pending.kind == PEND_RELU_GRAD && cluster_path && g.pending.d == dy && g.pending.n == n && aligned16(g.pending.relu_y)) {
     mask_y = g.pending.relu_y; g.pending.kind = PEND_NONE;
+  } else if (g.pending.kind == PEND_RELU_ADD_GRAD && cluster_path && g.pending.n == n && aligned16(g.pending.relu_y) && aligned16(g.pending.d) &&
+             aligned16(g.pending.da) && aligned16(g.pending.db) &&
+             ((g.pending.da == dy && g.pending.fa) || (g.pending.db == dy && g.pending.fb))) {
+    // The held ReLU + add gradient would write m = (y > 0 ? d : 0) into this dy, which nothing else has written: read m straight
+    // from d instead, and write the add's other destination here.  dy itself stays unwritten (its owner declared it dead after
+    // this call: fusion level 2).
+    const bool first = g.pending.da == dy;
+    extra = first ? g.pending.db : g.pending.da; extra_fresh = first ? g.pending.fb : g.pending.fa;
+    mask_y = g.pending.relu_y; dy = g.pending.d;
+    g.pending.kind = PEND_NONE;
   } else if (g.pending.kind) { int rc = flush_pending(); if (rc) return rc; }
   // dx declared unset (ltb_grad_unset): the one-launch kernels write their result instead of adding; the three-kernel path
   // fills it with zeros first.  dy itself is someone's gradient buffer too: it must hold data by now.
   { int rc = grad_settle(dy, (size_t)n * 4); if (rc) return rc; }
-  const int fresh = (dx && cluster_path && grad_take_unset(dx, (size_t)n * 4) ? 1 : 0) | (mask_y && g.fusion_no_writeback ? 2 : 0);
+  const int fresh = (dx && cluster_path && grad_take_unset(dx, (size_t)n * 4) ? 1 : 0) | (mask_y && g.fusion_no_writeback ? 2 : 0) | (extra_fresh ? 4 : 0);
   if (dx && !(fresh & 1)) { int rc = grad_settle(dx, (size_t)n * 4); if (rc) return rc; }
   if (cluster_path) {
     const BnClusterPlan p = bn_cluster_plan(N, C, HW);
@@ -681,15 +707,15 @@ int ltb_bn_bwd(const float* x, float* dx, const float* dy, const float* gamma, f
     BnPackedPlan pk;
     if ((p.K == 1 || C >= 96) && bn_packed_plan(N, C, HW, kBnVptBwd, pk)) {
       LTB_LAUNCH(bn_bwd_packed_kernel<kBnVptBwd>, (unsigned)ceil_div(C, pk.G), dim3(pk.T, pk.G), 0, x, dyw, dx, gamma, dgamma, dbeta,
-                 save_mean, save_istd, N, C, HW, mask_y, fresh);
+                 save_mean, save_istd, N, C, HW, mask_y, fresh, extra);
       return LTB_OK;
     }
     if (p.per_cta <= kBnVptBwd * p.threads)
       LTB_LAUNCH_CLUSTER(bn_bwd_cluster_kernel<kBnVptBwd>, dim3((unsigned)C * p.K), dim3(p.threads), p.K, x, dyw, dx, gamma, dgamma, dbeta,
-                         save_mean, save_istd, N, C, HW, p.per_cta, mask_y, fresh);
+                         save_mean, save_istd, N, C, HW, p.per_cta, mask_y, fresh, extra);
     else
       LTB_LAUNCH_CLUSTER(bn_bwd_cluster_kernel<0>, dim3((unsigned)C * p.K), dim3(p.threads), p.K, x, dyw, dx, gamma, dgamma, dbeta,
-                         save_mean, save_istd, N, C, HW, p.per_cta, mask_y, fresh);
+                         save_mean, save_istd, N, C, HW, p.per_cta, mask_y, fresh, extra);
     return LTB_OK;
   }
   LTB_LAUNCH(bn_reduce_kernel<1>, dim3(C, S), 256, 0, x, dy, save_mean, save_istd, g.cur_scratch(), N, C, HW);

@@ -731,6 +731,44 @@ def test_fusion_level_two_changes_no_result(gpu, shape):
         assert np.array_equal(u, v)
 
 
+@pytest.mark.parametrize("shape", [(128, 256, 16, 16), (128, 128, 8, 8), (128, 1024, 4, 4), (64, 2048, 2, 2)])
+@pytest.mark.parametrize("other_fresh", [False, True])
+def test_bn_backward_absorbs_the_add_gradient(gpu, shape, other_fresh):
+    """Fusion level 2, the end of a residual block backwards: in-place ReLU gradient of the block's output, gradient of the add
+    (main path + shortcut), batch-norm backward of the main path's last layer.  When the main path's gradient buffer was
+    declared unset, the add gradient is held once more and the batch-norm backward reads the masked gradient straight from
+    the block output's gradient, writing the shortcut's share itself: dx, dgamma, dbeta and the shortcut gradient are those
+    of level 1, bit for bit (two-sweep, register-resident and packed kernels; the shortcut's buffer unset or holding data)."""
+    b, lib = gpu, gpu.lib
+    N, C, H, W = shape
+    x0 = R(21).standard_normal(shape).astype(np.float32); out0 = R(22).standard_normal(shape).astype(np.float32)
+    d0 = R(23).standard_normal(shape).astype(np.float32); pre = R(24).standard_normal(shape).astype(np.float32)
+    res = []
+    for level in (1, 2):
+        lib.set_fusion(level)
+        try:
+            l0 = lib.kernel_launches()
+            x = TensorR(b.fromNumpy(x0)); x.d = b.fill(shape, 0.0)                          # the last convolution's output and its gradient
+            gam, bet = TensorR(b.fill((C,), 1.5), b.fill((C,), 0.0)), TensorR(b.fill((C,), 0.1), b.fill((C,), 0.0))
+            z, sm, si, _ = b.batchNormTraining(x.x, gam.x, bet.x, b.fill((C,), 0.0), b.fill((C,), 1.0))
+            lib.sync()
+            zr = TensorR(z, _poisoned(b, shape))                                             # main path: gradient buffer declared unset
+            sc = TensorR(b.fromNumpy(x0), _poisoned(b, shape) if other_fresh else b.fromNumpy(pre))   # shortcut
+            out = TensorR(b.fromNumpy(out0), b.fromNumpy(d0))                                # the block's output (after ReLU) and its gradient
+            lib.sync(); l1 = lib.kernel_launches()
+            b.relu_grad(out, out, inPlace=True)
+            sh = np.array(shape, np.int32)
+            lib.ew_binary_grad(0, zr.x.ptr, zr.d.ptr, sh.ctypes.data, sc.x.ptr, sc.d.ptr, sh.ctypes.data, out.d.ptr, 4)
+            b.batchNorm_grad(x, zr, gam, bet, sm, si)
+            lib.sync()
+            res.append([x.d.toCPU(), gam.d.toCPU(), bet.d.toCPU(), sc.d.toCPU(), lib.kernel_launches() - l1])
+        finally:
+            lib.set_fusion(0)
+    for u, v in zip(res[0][:4], res[1][:4]):
+        assert np.isfinite(v).all() and np.array_equal(u, v)
+    assert res[1][4] == res[0][4] - 1                                                        # one launch fewer: the add gradient went into the batch norm
+
+
 # ---------------------------------------------------------------------------------------------- deferred zero fill
 def _poisoned(b, shape):
     """A gradient buffer full of NaN, declared unset: whatever adds into it without reading must leave no NaN behind."""
