@@ -225,12 +225,15 @@ def test_predictions_are_bit_exact(libs, math):
 
 def test_the_tf32_step_trains_as_the_fp32_step_does(cuda_lib):
     """Loss trajectories on the GPU, TF32 against FP32 math, same weights and batches: SqueezeNet (batch 64, 40 steps, the
-    configuration's lr 0.005) and ResNet-50 (batch 32, 30 steps).  Per-step equality is not expected (see the module
-    comment); both runs must bring the loss down, and to the same level."""
+    configuration's lr 0.005) and ResNet-50 (batch 32, 30 steps, lr 0.002).  Per-step equality is not expected (see the module
+    comment); both runs must bring the loss down, and to the same level.  The ResNet step size is one at which the loss falls
+    from the first step on: at lr 0.02 on two batches the loss first climbs to 10-19 and the step at which it comes back down
+    (25 to 35) differs from run to run within ONE math mode, so nothing about the two modes can be read off such a run; at
+    0.002 repeated runs of either mode end within 0.46-0.53 of each other after 30 steps."""
     lib = cuda_lib
     mark = lib.mark()
     try:
-        for name, b, steps, lr, batches in (("squeezenet", 64, 40, 0.005, 4), ("resnet50", 32, 30, 0.02, 2)):
+        for name, b, steps, lr, batches, fall, apart in (("squeezenet", 64, 40, 0.005, 4, 0.8, 0.5), ("resnet50", 32, 30, 0.002, 2, 0.4, 0.1)):
             tr = {}
             for math in (0, 1):
                 lib.set_math(math)
@@ -241,12 +244,12 @@ def test_the_tf32_step_trains_as_the_fp32_step_does(cuda_lib):
                 tr[math] = np.array(ls); m.close(); lib.reset(mark)
             print(name, "fp32", np.round(tr[0][::5], 3), "tf32", np.round(tr[1][::5], 3))
             assert np.all(np.isfinite(tr[0])) and np.all(np.isfinite(tr[1]))
-            first, end32, endtf = tr[0][0], tr[0][-6:].min(), tr[1][-6:].min()     # the ResNet runs climb before they fall (lr 0.02 on two batches): the best of the last steps
+            first, end32, endtf = tr[0][0], tr[0][-6:].min(), tr[1][-6:].min()     # the two batches differ in loss: the best of the last steps
             # the first step is the same step; the tensor core TRUNCATES its operands to TF32 (a bias toward zero of up to 1e-3 per
             # product), which the large logits of an untrained SqueezeNet turn into 1 % of its loss of 6.7
             assert abs(tr[1][0] - first) <= 0.02 * first
-            assert end32 < 0.8 * first and endtf < 0.8 * first, (first, end32, endtf)
-            assert abs(endtf - end32) <= 0.5 * first, (first, end32, endtf)
+            assert end32 < fall * first and endtf < fall * first, (first, end32, endtf)
+            assert abs(endtf - end32) <= apart * first, (first, end32, endtf)
     finally:
         lib.set_math(1)
         lib.reset(mark)
