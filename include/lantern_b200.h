@@ -76,7 +76,11 @@ int    LTB_FN(set_math)(int mode);                      /* LTB_MATH_TF32 (defaul
  * Level 2: in addition the caller declares that the gradient buffer an in-place ReLU gradient works on is not read again
  * after the batch-norm backward or add gradient that absorbed it (true of every staged program: that operator is the
  * buffer's only reader).  The absorbing kernel then applies the mask on load only and no longer writes the masked gradient
- * back into that buffer; every result (dx, dgamma, dbeta, da, db) is unchanged. */
+ * back into that buffer; every result (dx, dgamma, dbeta, da, db) is unchanged.
+ * Level 3: in addition the caller declares that a batch-norm result whose next two calls are a same-shape add with it as one
+ * operand and an in-place ReLU of the sum has no other reader (true of a residual block's last batch norm; NOT something
+ * reverse-mode structure guarantees, so a generic staged program stays at level 2).  The three calls then become one kernel
+ * that writes the sum and never the batch norm's own result; the sum and the saved / running statistics are unchanged. */
 int    LTB_FN(set_fusion)(int on);
 /* Filter cache, off by default (no counterpart in the reference, where cuDNN reads OIHW filters as they are). The tensor-core
  * engine reads the filter of an R x S convolution as one matrix per tap; forward and data-grad each need their own form, and

@@ -18,7 +18,7 @@ constexpr size_t kGranule = 256;      // arena granule (TMA wants 16 B bases/str
 // for one call.  BN forward or a same-shape add followed by an in-place ReLU of their result become one kernel; an in-place
 // ReLU gradient followed by BN backward or by the add's gradient reading that buffer become one kernel.  Any other call
 // first issues the held operation on its own, so results never change; only the moment of the launch does.
-enum { PEND_NONE = 0, PEND_BN_FWD = 1, PEND_ADD = 2, PEND_RELU_GRAD = 3, PEND_RELU_ADD_GRAD = 4 };
+enum { PEND_NONE = 0, PEND_BN_FWD = 1, PEND_ADD = 2, PEND_RELU_GRAD = 3, PEND_RELU_ADD_GRAD = 4, PEND_BN_ADD = 5 };
 struct Pending {
   int kind = PEND_NONE;
   int64_t n = 0;
@@ -33,6 +33,8 @@ struct Pending {
   // PEND_RELU_ADD_GRAD (fusion level 2): m = relu_y > 0 ? d : 0; da += m; db += m, held so that the batch-norm backward whose dy is
   // da (or db) reads m straight from d and writes the other destination itself; fa / fb: that destination holds nothing yet
   float *da = nullptr, *db = nullptr; int fa = 0, fb = 0;
+  // PEND_BN_ADD (fusion level 3): the PEND_BN_FWD fields, then out = y + a with y the held batch norm's result; an in-place ReLU of
+  // out makes the three one kernel that never writes y
 };
 
 struct Context {
@@ -68,6 +70,7 @@ struct Context {
   bool deterministic = false;         // split-K sums in a fixed order (clusters, slabs) instead of atomics (ltb_set_deterministic)
   bool filter_cache = false;          // per-tap filter forms kept across calls (ltb_set_filter_cache)
   bool fusion = false;                // look-ahead fusion of BN/add with ReLU (off unless the host opts in)
+  bool fusion_single_use = false;     // level 3: a batch-norm result consumed by add + in-place ReLU has no other reader and is not written
   bool fusion_no_writeback = false;   // level 2: an absorbed in-place ReLU gradient is applied on load only (its buffer is dead afterwards)
   Pending pending;
   bool hold_workspace = false;        // while two halves are in flight their staging blocks are released together at the end

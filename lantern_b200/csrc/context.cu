@@ -156,7 +156,7 @@ static int stream_wait(const char* what) {
   return LTB_OK;
 }
 int ltb_sync(void) { LTB_INITED(); return stream_wait("ltb_sync"); }
-int ltb_set_fusion(int on) { LTB_INITED(); g.fusion = on != 0; g.fusion_no_writeback = on >= 2; return LTB_OK; }
+int ltb_set_fusion(int on) { LTB_INITED(); g.fusion = on != 0; g.fusion_no_writeback = on >= 2; g.fusion_single_use = on >= 3; return LTB_OK; }
 int ltb_set_filter_cache(int on) {
   LTB_INITED(); LTB_REQUIRE(!g.capturing, "ltb_set_filter_cache: not while recording a step");
   if (!on && g.filter_cache) { cudaStreamSynchronize(g.stream); cudaStreamSynchronize(g.side); cudaStreamSynchronize(g.branch); filter_cache_clear(); }
@@ -246,7 +246,7 @@ void* step_alloc(size_t bytes) {
 extern "C" {
 // Deferred zero fill (see grad_take_unset): d must be a block of n floats that nothing has written since it was handed out.
 int ltb_grad_unset(float* d, int64_t n) {
-  LTB_INITED(); LTB_REQUIRE(d && n > 0, "ltb_grad_unset: bad argument");
+  LTB_INITED_NOFLUSH(); LTB_REQUIRE(d && n > 0, "ltb_grad_unset: bad argument");       // bookkeeping on a buffer no held operation can name yet: nothing is issued
   if (g.tune & 32) { LTB_CUDA(cudaMemsetAsync(d, 0, (size_t)n * 4, g.stream)); return LTB_OK; }     // switch: plain zero fill at once
   grad_settle(d, 0);                                                   // declared before and never used: start over
   unset_blocks.emplace_back((const char*)d, (size_t)n * 4);

@@ -279,6 +279,11 @@ int flush_pending() {
     case PEND_ADD: return add_issue(p.a, p.b, p.out, p.n, false);
     case PEND_RELU_GRAD: return relu_grad_issue(p.relu_y, p.d, p.n);
     case PEND_RELU_ADD_GRAD: return relu_add_grad_issue(p);
+    case PEND_BN_ADD: {                                         // no ReLU came: the two operations on their own, y written
+      Pending q = p; q.kind = PEND_BN_FWD;
+      int rc = bn_fwd_issue(q, false);
+      return rc ? rc : add_issue(p.y, p.a, p.out, p.n, false);
+    }
     default: return LTB_OK;
   }
 }
@@ -338,9 +343,18 @@ int ltb_clip(float* x, float bound, int64_t n) {
 
 // elementWiseOpWithBroadCast: TensorDslCPU.scala:227-244.
 int ltb_ew_binary(int op, const float* a, const int* as, const float* b, const int* bs, float* out, int rank) {
-  LTB_INITED(); LTB_REQUIRE(a && b && out && op >= LTB_ADD && op <= LTB_DIV, "ltb_ew_binary: bad argument");
+  LTB_INITED_NOFLUSH(); LTB_REQUIRE(a && b && out && op >= LTB_ADD && op <= LTB_DIV, "ltb_ew_binary: bad argument");
   Bcast p; int64_t n; bool ab, bb;
   LTB_REQUIRE(make_bcast(as, bs, rank, p, n, ab, bb), "ltb_ew_binary: shapes do not broadcast");
+  if (g.pending.kind == PEND_BN_FWD && g.fusion_single_use && !ab && !bb && op == LTB_ADD && g.pending.n == n && a != b &&
+      (a == g.pending.y || b == g.pending.y)) {                 // the held batch norm's result plus a shortcut: held once more, for the ReLU
+    const float* other = a == g.pending.y ? b : a;
+    if (out != g.pending.y && out != g.pending.x && out != other && aligned16(other) && aligned16(out)) {
+      g.pending.kind = PEND_BN_ADD; g.pending.a = other; g.pending.out = out;
+      return LTB_OK;
+    }
+  }
+  if (g.pending.kind) { int rc = flush_pending(); if (rc) return rc; }
   if (!ab && !bb && op == LTB_ADD) {
     if (g.fusion && n > 0) { Pending h; h.kind = PEND_ADD; h.n = n; h.a = a; h.b = b; h.out = out; g.pending = h; return LTB_OK; }   // an in-place ReLU of out may join it
     return add_issue(a, b, out, n, false);
@@ -438,6 +452,7 @@ int ltb_unary(int op, const float* x, float* out, int64_t n) {
     const Pending h = g.pending;
     if (h.kind == PEND_BN_FWD && h.y == out) { g.pending.kind = PEND_NONE; return bn_fwd_issue(h, true); }
     if (h.kind == PEND_ADD && h.out == out) { g.pending.kind = PEND_NONE; return add_issue(h.a, h.b, h.out, h.n, true); }
+    if (h.kind == PEND_BN_ADD && h.out == out) { g.pending.kind = PEND_NONE; return bn_fwd_issue(h, true); }
   }
   if (g.pending.kind) { int rc = flush_pending(); if (rc) return rc; }
   return launch_map<1>(x, nullptr, nullptr, out, n, [op] __device__(float v, float, float) { return un_op(op, v); });

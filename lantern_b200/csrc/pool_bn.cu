@@ -235,6 +235,12 @@ static BnClusterPlan bn_cluster_plan(int N, int C, int HW) {
   return p;
 }
 
+// add != null in the forward kernels below (fusion level 3, a residual block's last layer): the normalised value is not
+// written to y; `add` is added to it, the ReLU applied, and the sum goes where the held add would have put it (the
+// launcher passes that destination as y).  The value is rounded to a float before the addition exactly as the separate
+// kernels would have rounded it on its way through memory, so the result is the same bit for bit.
+__device__ __forceinline__ float4 add4(float4 v, float4 s) { v.x += s.x; v.y += s.y; v.z += s.z; v.w += s.w; return v; }
+
 // VPT > 0: the CTA's slice is at most VPT float4 per thread and stays in registers between the two sweeps (all loads of a
 // thread are issued back to back); VPT == 0: any slice length, the second sweep re-reads it.
 constexpr int kBnVpt = 8;          // forward: x
@@ -243,7 +249,7 @@ constexpr int kBnVptBwd = 4;       // backward keeps x, dy and dx: half the slic
 template <int VPT>
 __global__ void __launch_bounds__(512, 2) bn_fwd_cluster_kernel(const float* x, float* y, const float* __restrict__ gamma, const float* __restrict__ beta,
                                                              float* run_mean, float* run_var, float* save_mean, float* save_istd,
-                                                             int N, int C, int HW, int per_cta, float eps, float momentum, int relu) {
+                                                             int N, int C, int HW, int per_cta, float eps, float momentum, int relu, const float* __restrict__ add) {
   cg::cluster_group cluster = cg::this_cluster();
   const unsigned K = cluster.num_blocks(), r = cluster.block_rank();
   const int c = blockIdx.x / K;
@@ -306,6 +312,7 @@ __global__ void __launch_bounds__(512, 2) bn_fwd_cluster_kernel(const float* x, 
         const int n = t / hw4, i = t - n * hw4;
         float4 v = keep[j];
         v.x = (v.x - mu) * sc + sh; v.y = (v.y - mu) * sc + sh; v.z = (v.z - mu) * sc + sh; v.w = (v.w - mu) * sc + sh;
+        if (add) v = add4(v, reinterpret_cast<const float4*>(add + ((int64_t)n * C + c) * HW)[i]);
         if (relu) { v.x = v.x < 0.0f ? 0.0f : v.x; v.y = v.y < 0.0f ? 0.0f : v.y; v.z = v.z < 0.0f ? 0.0f : v.z; v.w = v.w < 0.0f ? 0.0f : v.w; }
         reinterpret_cast<float4*>(y + ((int64_t)n * C + c) * HW)[i] = v;
       }
@@ -317,6 +324,7 @@ __global__ void __launch_bounds__(512, 2) bn_fwd_cluster_kernel(const float* x, 
       const int64_t off = ((int64_t)n * C + c) * HW;
       float4 v = reinterpret_cast<const float4*>(x + off)[i];
       v.x = (v.x - mu) * sc + sh; v.y = (v.y - mu) * sc + sh; v.z = (v.z - mu) * sc + sh; v.w = (v.w - mu) * sc + sh;
+      if (add) v = add4(v, reinterpret_cast<const float4*>(add + off)[i]);
       if (relu) { v.x = v.x < 0.0f ? 0.0f : v.x; v.y = v.y < 0.0f ? 0.0f : v.y; v.z = v.z < 0.0f ? 0.0f : v.z; v.w = v.w < 0.0f ? 0.0f : v.w; }
       reinterpret_cast<float4*>(y + off)[i] = v;
     }
@@ -467,7 +475,7 @@ __device__ __forceinline__ void row_sum2(float& a, float& b, float* red) {
 template <int VPT>
 __global__ void __launch_bounds__(512, 2) bn_fwd_packed_kernel(const float* x, float* y, const float* __restrict__ gamma, const float* __restrict__ beta,
                                                             float* run_mean, float* run_var, float* save_mean, float* save_istd,
-                                                            int N, int C, int HW, float eps, float momentum, int relu) {
+                                                            int N, int C, int HW, float eps, float momentum, int relu, const float* __restrict__ add) {
   __shared__ float red[32];
   __shared__ float stat[16][2];
   const int g = threadIdx.y, T = blockDim.x;
@@ -512,6 +520,7 @@ __global__ void __launch_bounds__(512, 2) bn_fwd_packed_kernel(const float* x, f
       const int n = t / hw4, i = t - n * hw4;
       float4 v = keep[j];
       v.x = (v.x - mu) * sc + sh; v.y = (v.y - mu) * sc + sh; v.z = (v.z - mu) * sc + sh; v.w = (v.w - mu) * sc + sh;
+      if (add) v = add4(v, reinterpret_cast<const float4*>(add + ((int64_t)n * C + c) * HW)[i]);
       if (relu) { v.x = v.x < 0.0f ? 0.0f : v.x; v.y = v.y < 0.0f ? 0.0f : v.y; v.z = v.z < 0.0f ? 0.0f : v.z; v.w = v.w < 0.0f ? 0.0f : v.w; }
       reinterpret_cast<float4*>(y + ((int64_t)n * C + c) * HW)[i] = v;
     }
@@ -587,22 +596,25 @@ static int bn_splits(int N, int C) {
   return s < 1 ? 1 : s;
 }
 
-// Issues a BN forward described by `p` (the cluster path), optionally with the ReLU of its result.
+// Issues a BN forward described by `p` (the cluster path), optionally with the ReLU of its result; a PEND_BN_ADD also adds
+// p.a and writes p.out instead of p.y.
 int bn_fwd_issue(const Pending& p, bool relu) {
   const BnClusterPlan c = bn_cluster_plan(p.N, p.C, p.HW);
   const int r = relu ? 1 : 0;
+  const float* add = p.kind == PEND_BN_ADD ? p.a : nullptr;
+  float* y = p.kind == PEND_BN_ADD ? p.out : p.y;
   BnPackedPlan pk;
   if ((c.K == 1 || p.C >= 96) && bn_packed_plan(p.N, p.C, p.HW, kBnVpt, pk)) {
-    LTB_LAUNCH(bn_fwd_packed_kernel<kBnVpt>, (unsigned)ceil_div(p.C, pk.G), dim3(pk.T, pk.G), 0, p.x, p.y, p.gamma, p.beta, p.run_mean, p.run_var,
-               p.save_mean, p.save_istd, p.N, p.C, p.HW, p.eps, p.momentum, r);
+    LTB_LAUNCH(bn_fwd_packed_kernel<kBnVpt>, (unsigned)ceil_div(p.C, pk.G), dim3(pk.T, pk.G), 0, p.x, y, p.gamma, p.beta, p.run_mean, p.run_var,
+               p.save_mean, p.save_istd, p.N, p.C, p.HW, p.eps, p.momentum, r, add);
     return LTB_OK;
   }
   if (c.per_cta <= kBnVpt * c.threads)
-    LTB_LAUNCH_CLUSTER(bn_fwd_cluster_kernel<kBnVpt>, dim3((unsigned)p.C * c.K), dim3(c.threads), c.K, p.x, p.y, p.gamma, p.beta, p.run_mean, p.run_var,
-                       p.save_mean, p.save_istd, p.N, p.C, p.HW, c.per_cta, p.eps, p.momentum, r);
+    LTB_LAUNCH_CLUSTER(bn_fwd_cluster_kernel<kBnVpt>, dim3((unsigned)p.C * c.K), dim3(c.threads), c.K, p.x, y, p.gamma, p.beta, p.run_mean, p.run_var,
+                       p.save_mean, p.save_istd, p.N, p.C, p.HW, c.per_cta, p.eps, p.momentum, r, add);
   else
-    LTB_LAUNCH_CLUSTER(bn_fwd_cluster_kernel<0>, dim3((unsigned)p.C * c.K), dim3(c.threads), c.K, p.x, p.y, p.gamma, p.beta, p.run_mean, p.run_var,
-                       p.save_mean, p.save_istd, p.N, p.C, p.HW, c.per_cta, p.eps, p.momentum, r);
+    LTB_LAUNCH_CLUSTER(bn_fwd_cluster_kernel<0>, dim3((unsigned)p.C * c.K), dim3(c.threads), c.K, p.x, y, p.gamma, p.beta, p.run_mean, p.run_var,
+                       p.save_mean, p.save_istd, p.N, p.C, p.HW, c.per_cta, p.eps, p.momentum, r, add);
   return LTB_OK;
 }
 

@@ -643,8 +643,9 @@ extern "C" {
 
 void* HOST_FN(model_create)(const char* name, int batch, int seed) {
   std::string n(name);
-  BK(set_fusion)(2);     // generated programs issue every device operation through the library: the one-call look-ahead is safe, and a
-                         // gradient buffer has no reader after the operator that absorbs its in-place ReLU gradient (level 2)
+  BK(set_fusion)(3);     // generated programs issue every device operation through the library: the one-call look-ahead is safe, and a
+                         // gradient buffer has no reader after the operator that absorbs its in-place ReLU gradient (level 2); in the
+                         // networks of this file the last batch norm of a residual block is read by the block's sum only (level 3)
   BK(set_filter_cache)(1);   // and they write parameters only through the optimizer, transfer and fill entry points
   if (n == "mnist") return new Mnist(batch, seed);
   if (n == "resnet50") return new ResNet50(batch, seed);
@@ -804,7 +805,7 @@ int HOST_FN(model_trace)(void* m, const float* x_host, const int32_t* y_host, ch
   tracing() = true; trace_list().clear();
   BK(set_fusion)(1);     // the trace reads every gradient buffer after the step: masked gradients are written back as the separate calls would
   M->step(x_host, y_host, 0.0f, false);
-  BK(set_fusion)(2);
+  BK(set_fusion)(3);
   tracing() = false;
   strncpy(buf, M->trace_text.c_str(), len - 1); buf[len - 1] = 0;
   return (int)M->trace_text.size();

@@ -769,6 +769,44 @@ def test_bn_backward_absorbs_the_add_gradient(gpu, shape, other_fresh):
     assert res[1][4] == res[0][4] - 1                                                        # one launch fewer: the add gradient went into the batch norm
 
 
+@pytest.mark.parametrize("shape", [(128, 256, 16, 16), (128, 64, 32, 32), (128, 512, 8, 8), (128, 1024, 4, 4), (64, 2048, 2, 2), (8, 20, 6, 6), (4, 6, 5, 5)])
+@pytest.mark.parametrize("order", ["bn_first", "shortcut_first"])
+def test_bn_forward_absorbs_the_add_and_relu(gpu, shape, order):
+    """Fusion level 3, the end of a residual block forwards: batch norm of the main path's last layer, its result plus the
+    shortcut, ReLU in place on the sum.  One kernel does the three and never writes the batch norm's own result; the sum, the
+    saved statistics and the running statistics are those of level 2, bit for bit (packed, register-resident and two-sweep
+    kernels; either operand order).  When something other than the ReLU follows the add, the two operations are issued on
+    their own and the batch norm's result is written as at level 2."""
+    b, lib = gpu, gpu.lib
+    N, C, H, W = shape
+    x0 = R(31).standard_normal(shape).astype(np.float32) * 2 + 0.5; s0 = R(32).standard_normal(shape).astype(np.float32)
+    res = []
+    for level, then_relu in ((2, True), (3, True), (2, False), (3, False)):
+        lib.set_fusion(level)
+        try:
+            x, sc = b.fromNumpy(x0), b.fromNumpy(s0)
+            gam, bet, rm, rv = b.fill((C,), 1.5), b.fill((C,), 0.1), b.fill((C,), 0.0), b.fill((C,), 1.0)
+            lib.sync(); l0 = lib.kernel_launches()
+            z, sm, si, _ = b.batchNormTraining(x, gam, bet, rm, rv)
+            out = (b.plus(z, sc) if order == "bn_first" else b.plus(sc, z))[0]
+            if then_relu:
+                b.relu(out, inPlace=True)
+            else:
+                out = b.mul(out, out)[0]                                                      # reads the sum: the held operations are issued first
+            lib.sync()
+            res.append([out.toCPU(), sm.toCPU(), si.toCPU(), rm.toCPU(), rv.toCPU(), z.toCPU() if not (level == 3 and then_relu) else None,
+                        lib.kernel_launches() - l0])
+        finally:
+            lib.set_fusion(0)
+    for u, v in ((res[0], res[1]), (res[2], res[3])):
+        for p, q in zip(u[:5], v[:5]):
+            assert np.isfinite(q).all() and np.array_equal(p, q)
+    assert np.array_equal(res[2][5], res[3][5]) and np.array_equal(res[0][5], res[2][5])      # the batch norm's own result, wherever it is written
+    vec = (H * W) % 4 == 0
+    assert res[1][6] == (res[0][6] - 1 if vec else res[0][6])                                # one launch instead of two (the one-launch batch norm needs rows of whole float4)
+    assert res[3][6] == res[2][6]
+
+
 # ---------------------------------------------------------------------------------------------- deferred zero fill
 def _poisoned(b, shape):
     """A gradient buffer full of NaN, declared unset: whatever adds into it without reading must leave no NaN behind."""
