@@ -731,7 +731,7 @@ def test_fusion_level_two_changes_no_result(gpu, shape):
         assert np.array_equal(u, v)
 
 
-@pytest.mark.parametrize("shape", [(128, 256, 16, 16), (128, 128, 8, 8), (128, 1024, 4, 4), (64, 2048, 2, 2)])
+@pytest.mark.parametrize("shape", [(128, 64, 32, 32), (128, 256, 16, 16), (128, 128, 8, 8), (128, 1024, 4, 4), (64, 2048, 2, 2)])
 @pytest.mark.parametrize("other_fresh", [False, True])
 def test_bn_backward_absorbs_the_add_gradient(gpu, shape, other_fresh):
     """Fusion level 2, the end of a residual block backwards: in-place ReLU gradient of the block's output, gradient of the add
