@@ -72,7 +72,8 @@ int    LTB_FN(set_math)(int mode);                      /* LTB_MATH_TF32 (defaul
  * in-place ReLU of their result joins the same kernel, and an in-place ReLU gradient is held so that the batch-norm
  * backward or add gradient that reads it applies it on the fly. Results are those of the separate calls; only the moment
  * of the launch moves: a held operation is issued by the next call of this library whatever it is (sync, copies,
- * get_stream and graph_end included). A host that enqueues its own work on the stream must call get_stream or sync first.
+ * get_stream and graph_end included; malloc, malloc_uninit and grad_unset only keep books on a block no held operation can
+ * name yet and issue nothing). A host that enqueues its own work on the stream must call get_stream or sync first.
  * Level 2: in addition the caller declares that the gradient buffer an in-place ReLU gradient works on is not read again
  * after the batch-norm backward or add gradient that absorbed it (true of every staged program: that operator is the
  * buffer's only reader).  The absorbing kernel then applies the mask on load only and no longer writes the masked gradient
