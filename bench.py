@@ -408,8 +408,8 @@ def main():
                 "e2e": {"value": e2e, "unit": "samples/s", "ms_per_step": ms_e2e / args.steps, "h2d_bytes_per_step": BATCH * 3072 * 4 + BATCH * 4, "d2h_bytes_per_step": 4,
                         "blocks": len(blocks_e2e),
                         "note": "timed from before the first host-to-device copy to after the last loss read-back; the host-fed loop replays its own "
-                                "recordings of the step (inputs in two alternating staging blocks), and two recordings of the same step differ by up "
-                                "to 3 % in speed, so this figure can land on either side of `value`"},
+                                "recording of the step (the batch moves from two alternating staging blocks to a fixed device address), and two "
+                                "recordings of the same step differ by up to 3 % in speed, so this figure can land on either side of `value`"},
                 "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline, "roofline_hbm": roofline_hbm,
                 "staging_ms_per_step": s_ms, "staging_launches_per_step": s_n, "device_status": status,
                 "loss": {"resident_last": loss_resident, "e2e_first": losses[3] if len(losses) > 3 else None, "e2e_last": losses[-1]},
